@@ -1,0 +1,265 @@
+"""CPU oracle for the quantised fused-MoE path.  TEST INFRASTRUCTURE ONLY.
+
+This file restates, for the CPU, the algorithms the reference (tingqli/pyhip) uses to judge
+its own MoE kernels.  Nothing in the shipped package imports it: only tests, the smoke check
+and the benchmark's CPU-baseline leg do.  Each function names the reference lines it follows.
+
+Pinning: `torch_moe_oracle` and `moe_sorting_oracle` are checked bit-for-bit against outputs of
+the reference's own functions (extracted from its test files and executed on CPU) stored under
+tests/golden/, and the sorter additionally against the worked example in the reference's
+sorting-kernel documentation.  The MXFP4 / FP8 weight quantisers of the reference live in an
+un-vendored third-party module (aiter, no pinned version); for them the parity is unpinned and
+the encodings follow ck_tile's numeric headers instead (pk_fp4.hpp, e8m0.hpp).
+"""
+from __future__ import annotations
+
+import numpy as np
+import torch
+
+_E2M1 = np.array([0.0, 0.5, 1.0, 1.5, 2.0, 3.0, 4.0, 6.0,
+                  -0.0, -0.5, -1.0, -1.5, -2.0, -3.0, -4.0, -6.0], dtype=np.float32)
+
+
+# --------------------------------------------------------------------------------------
+# metrics
+# --------------------------------------------------------------------------------------
+def calc_diff(x: torch.Tensor, y: torch.Tensor) -> float:
+    """1 - 2<x,y>/(|x|^2+|y|^2) in float64 (src/misc.py:131-141)."""
+    x, y = x.double(), y.double()
+    den = (x * x + y * y).sum()
+    if den == 0:
+        return 0.0
+    return float(1 - 2 * (x * y).sum() / den)
+
+
+def cosine(x: torch.Tensor, y: torch.Tensor) -> float:
+    x, y = x.double().flatten(), y.double().flatten()
+    den = x.norm() * y.norm()
+    return 1.0 if den == 0 else float((x @ y) / den)
+
+
+def max_abs(x: torch.Tensor, y: torch.Tensor) -> float:
+    return float((x.double() - y.double()).abs().max()) if x.numel() else 0.0
+
+
+# --------------------------------------------------------------------------------------
+# weight formats
+# --------------------------------------------------------------------------------------
+def dequant_mxfp4(packed: torch.Tensor, scale: torch.Tensor, dtype=torch.bfloat16) -> torch.Tensor:
+    """Packed E2M1 (low nibble = even element) times 2**(e-127) per 32 along K, then cast
+    (tests/contrib/moe/test_moe.py:164-166; pk_fp4.hpp:122-129; e8m0.hpp:12-24)."""
+    p = packed.cpu().numpy().astype(np.uint8)
+    codes = np.empty(p.shape[:-1] + (p.shape[-1] * 2,), dtype=np.uint8)
+    codes[..., 0::2] = p & 0xF
+    codes[..., 1::2] = p >> 4
+    vals = _E2M1[codes]
+    K = vals.shape[-1]
+    sc = np.ldexp(np.float32(1.0), scale.cpu().numpy().astype(np.int32) - 127).astype(np.float32)
+    out = vals.reshape(vals.shape[:-1] + (K // 32, 32)) * sc[..., None]
+    return torch.from_numpy(out.reshape(vals.shape)).to(dtype)
+
+
+def dequant_fp8_128x128(q: torch.Tensor, scale: torch.Tensor, dtype=torch.bfloat16) -> torch.Tensor:
+    """e4m3 value cast to bf16, times the fp32 scale of its 128x128 block, cast to bf16
+    (tests/contrib/moe/test_moe.py:243-245)."""
+    *lead, N, K = q.shape
+    blk = q.to(dtype).reshape(*lead, N // 128, 128, K // 128, 128)
+    out = (blk * scale.reshape(*lead, N // 128, 1, K // 128, 1)).to(dtype)
+    return out.reshape(*lead, N, K)
+
+
+# --------------------------------------------------------------------------------------
+# token -> expert sort / align
+# --------------------------------------------------------------------------------------
+def moe_sorting_oracle(topk_ids, topk_weights, num_experts: int, block_size: int,
+                       expert_mask=None):
+    """Group (token, k) pairs by expert, stable in token-major order, pad every non-empty
+    expert to a multiple of ``block_size`` with the sentinel (topk<<24)|num_tokens and weight
+    0, one expert id per block.
+
+    Follows src/contrib/fused_moe.py:56-100 (with the pad length being ``block_size`` rather
+    than that function's literal 256) and ck_tile's reference_moe_sorting with
+    skip_experts_with_zero_token=true and the (k<<24)|token packing
+    (archive/ck_tile/ck_tile/host/reference/reference_moe_sorting.hpp:14-117): a masked-out
+    expert emits nothing and does not advance the emitted (local) expert id; an empty
+    unmasked expert emits nothing but does advance it.
+
+    Returns numpy arrays (sorted_ids u32, sorted_weights f32, sorted_expert_ids i32,
+    num_valid_ids i32[2]); the arrays are sized to the worst case and only the prefix
+    [0, num_valid_ids[0]) is defined (the tail is filled with sentinel / 0 / -1 here)."""
+    ids = np.asarray(topk_ids.cpu() if torch.is_tensor(topk_ids) else topk_ids).astype(np.int64)
+    w = np.asarray(topk_weights.cpu() if torch.is_tensor(topk_weights) else topk_weights,
+                   dtype=np.float32)
+    T, K = ids.shape
+    B = block_size
+    nblk_max = (T * K + num_experts * (B - 1) + B - 1) // B
+    sentinel = np.uint32((K << 24) | T)
+    sorted_ids = np.full(nblk_max * B, sentinel, dtype=np.uint32)
+    sorted_w = np.zeros(nblk_max * B, dtype=np.float32)
+    sorted_e = np.full(nblk_max, -1, dtype=np.int32)
+
+    flat = ids.reshape(-1)
+    order = np.argsort(flat, kind="stable")           # token-major, then k, inside an expert
+    counts = np.bincount(flat, minlength=num_experts)[:num_experts]
+    tok = (order // K).astype(np.uint32)
+    kk = (order % K).astype(np.uint32)
+    packed = (kk << np.uint32(24)) | tok
+    starts = np.concatenate([[0], np.cumsum(counts)])
+
+    pos = 0
+    local_id = 0
+    for e in range(num_experts):
+        if expert_mask is not None and int(expert_mask[e]) == 0:
+            continue
+        n = int(counts[e])
+        if n == 0:
+            local_id += 1
+            continue
+        sl = slice(starts[e], starts[e] + n)
+        sorted_ids[pos:pos + n] = packed[sl]
+        sorted_w[pos:pos + n] = w.reshape(-1)[order[sl]]
+        nb = (n + B - 1) // B
+        sorted_e[pos // B: pos // B + nb] = local_id
+        pos += nb * B
+        local_id += 1
+    num_valid = np.array([pos, T], dtype=np.int32)
+    return sorted_ids, sorted_w, sorted_e, num_valid
+
+
+# --------------------------------------------------------------------------------------
+# end-to-end layer
+# --------------------------------------------------------------------------------------
+def _gateup_activation(gate, up, activation="silu", swiglu_limit=None):
+    """tests/contrib/moe/test_moe.py:73-83."""
+    if activation == "silu":
+        return torch.nn.functional.silu(gate) * up
+    if activation == "swiglu":
+        lim = float(swiglu_limit) if swiglu_limit else 7.0
+        dt = gate.dtype
+        g = gate.float().clamp(max=lim)
+        u = up.float().clamp(min=-lim, max=lim)
+        return (g * torch.sigmoid(1.702 * g) * (u + 1.0)).to(dt)
+    raise ValueError(activation)
+
+
+def torch_moe_oracle(hidden, w1, w2, topk_weight, topk_ids, activation="silu",
+                     swiglu_limit=None, expert_weights=None):
+    """The reference's dequantise-then-matmul layer (tests/contrib/moe/test_moe.py:86-118):
+    expert by expert, bf16 matmuls, silu(gate)*up, times the routing weight, cast to the
+    activation dtype and accumulated into the output with index_add_ in expert order.
+
+    ``w1`` [E,2I,H] / ``w2`` [E,H,I] are dequantised weights in the activation dtype, or
+    ``expert_weights(e) -> (w1_e, w2_e)`` produces them one expert at a time (bounds host
+    memory for the large configurations)."""
+    T, H = hidden.shape
+    ids = topk_ids.long()
+    out = torch.zeros((T, H), dtype=hidden.dtype)
+    E = w1.shape[0] if expert_weights is None else None
+    e_list = range(E) if expert_weights is None else sorted(set(ids.flatten().tolist()))
+    ids_kt = ids.t().contiguous()                     # [K, T]: where() walks k-major like the
+    for e in e_list:                                  # reference's permuted one-hot mask
+        k_idx, t_idx = torch.where(ids_kt == e)
+        if t_idx.numel() == 0:
+            continue
+        w1_e, w2_e = (w1[e], w2[e]) if expert_weights is None else expert_weights(e)
+        inter = w1_e.shape[0] // 2
+        cur = hidden[t_idx]
+        act = _gateup_activation(cur @ w1_e[:inter].t(), cur @ w1_e[inter:].t(),
+                                 activation, swiglu_limit)
+        y = (act @ w2_e.t()) * topk_weight[t_idx, k_idx, None]
+        out.index_add_(0, t_idx, y.to(hidden.dtype))
+    return out
+
+
+def torch_moe_oracle_mxfp4(hidden, w1_q, w1_s, w2_q, w2_s, topk_weight, topk_ids, **kw):
+    """Same layer from packed MXFP4 tensors; dequantises one expert at a time."""
+    def ew(e):
+        return dequant_mxfp4(w1_q[e], w1_s[e], hidden.dtype), dequant_mxfp4(w2_q[e], w2_s[e], hidden.dtype)
+    return torch_moe_oracle(hidden, None, None, topk_weight, topk_ids, expert_weights=ew, **kw)
+
+
+def torch_moe_oracle_fp8(hidden, w1_q, w1_s, w2_q, w2_s, topk_weight, topk_ids, **kw):
+    def ew(e):
+        return (dequant_fp8_128x128(w1_q[e], w1_s[e], hidden.dtype),
+                dequant_fp8_128x128(w2_q[e], w2_s[e], hidden.dtype))
+    return torch_moe_oracle(hidden, None, None, topk_weight, topk_ids, expert_weights=ew, **kw)
+
+
+# --------------------------------------------------------------------------------------
+# per-stage (sorted-block) form, as the reference's block reference does it
+# --------------------------------------------------------------------------------------
+def moe_gemm_oracle(topk: int, block_m: int, sorted_ids, sorted_expert_ids, sorted_weights,
+                    num_valid_ids, inp, weight, is_gateup: bool, out_dtype=torch.bfloat16):
+    """One grouped GEMM driven by the sort arrays, fp32 matmul per live block
+    (src/contrib/moe_gemm_ref.py:93-141).  ``weight`` is dequantised [E, OC, IC].
+    gate-up: inp [T,H] -> out [T,topk,OC/2] (silu(g)*u);  down: inp [T,topk,IC] -> out [T,OC]
+    accumulated with the routing weights in block order."""
+    sorted_ids = torch.as_tensor(np.asarray(sorted_ids).astype(np.int64))
+    sorted_expert_ids = np.asarray(sorted_expert_ids)
+    sorted_weights = torch.as_tensor(np.asarray(sorted_weights))
+    T = inp.shape[0]
+    OC = weight.shape[1]
+    out = torch.zeros((T, topk, OC // 2) if is_gateup else (T, OC), dtype=out_dtype)
+    for b in range(len(sorted_expert_ids)):
+        if b * block_m >= int(num_valid_ids[0]):
+            break
+        ids = sorted_ids[b * block_m:(b + 1) * block_m]
+        tok, kk = ids & 0xFFFFFF, ids >> 24
+        valid = kk < topk
+        w_e = weight[int(sorted_expert_ids[b])].float()
+        src = inp[tok[valid]] if is_gateup else inp[tok[valid], kk[valid]]
+        act = src.float() @ w_e.t()
+        if is_gateup:
+            act = torch.nn.functional.silu(act[:, :OC // 2]) * act[:, OC // 2:]
+            out[tok[valid], kk[valid]] = act.to(out_dtype)
+        else:
+            tw = sorted_weights[b * block_m:(b + 1) * block_m][valid]
+            out[tok[valid]] += act.to(out_dtype) * tw[:, None]
+    return out
+
+
+# --------------------------------------------------------------------------------------
+# activation quantiser used by the sm_100a kernels (two-term e4m3 with per-32 E8M0 scales)
+# --------------------------------------------------------------------------------------
+def _floor_log2_biased(a: np.ndarray) -> np.ndarray:
+    """Biased exponent field of float32 ``a`` (= floor(log2 a)+127 for normal a)."""
+    return ((a.astype(np.float32).view(np.uint32) >> 23) & 0xFF).astype(np.int32)
+
+
+def _e4m3_round(v: np.ndarray) -> np.ndarray:
+    t = torch.from_numpy(np.ascontiguousarray(v, dtype=np.float32)).clamp(-448.0, 448.0)
+    return t.to(torch.float8_e4m3fn)
+
+
+def hilo8_quant(x: torch.Tensor):
+    """Restatement of the device activation quantiser: per 32 along K,
+    e = max(biased_exponent(amax) - 7, 0), q = e4m3_rne(x * 2**(127-e)); the residual
+    x - q*2**(e-127) is quantised the same way.  Returns
+    (q_hi, e_hi, q_lo, e_lo) with q_* float8_e4m3fn [..., K] and e_* uint8 [..., K/32]."""
+    xf = x.float().numpy()
+    K = xf.shape[-1]
+    blk = xf.reshape(xf.shape[:-1] + (K // 32, 32))
+
+    def one(b):
+        amax = np.abs(b).max(axis=-1)
+        e = np.maximum(_floor_log2_biased(amax) - 7, 0)
+        inv = np.ldexp(np.float32(1.0), 127 - e).astype(np.float32)
+        q = _e4m3_round(b * inv[..., None])
+        deq = q.float().numpy() * np.ldexp(np.float32(1.0), e - 127).astype(np.float32)[..., None]
+        return q, e.astype(np.uint8), deq
+
+    q_hi, e_hi, d_hi = one(blk)
+    q_lo, e_lo, _ = one(blk - d_hi)
+    shp = xf.shape
+    return (q_hi.reshape(shp), torch.from_numpy(e_hi), q_lo.reshape(shp), torch.from_numpy(e_lo))
+
+
+def hilo8_dequant(q_hi, e_hi, q_lo, e_lo) -> torch.Tensor:
+    K = q_hi.shape[-1]
+
+    def one(q, e):
+        s = np.ldexp(np.float32(1.0), e.numpy().astype(np.int32) - 127).astype(np.float32)
+        v = q.float().numpy().reshape(q.shape[:-1] + (K // 32, 32)) * s[..., None]
+        return v.reshape(q.shape)
+
+    return torch.from_numpy(one(q_hi, e_hi) + one(q_lo, e_lo))
