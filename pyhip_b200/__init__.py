@@ -1,0 +1,5 @@
+"""B200-native fused-MoE operator behind the call surface of tingqli/pyhip's quantised MoE path."""
+from .fused_moe import (ActivationType, QuantType, PreparedWeights, fused_moe, moe_sorting,  # noqa: F401
+                        prepare_weights)
+
+__all__ = ["ActivationType", "QuantType", "PreparedWeights", "fused_moe", "moe_sorting", "prepare_weights"]

@@ -1,0 +1,239 @@
+// extern "C" surface of libb200moe.so: argument validation, workspace arithmetic, weight
+// preparation and the stage-by-stage / whole-layer entry points.
+#include <stdarg.h>
+#include <stdio.h>
+#include <string.h>
+
+#include "internal.h"
+
+namespace b200moe {
+
+static thread_local char g_err[512] = "";
+
+int set_error(int code, const char* fmt, ...) {
+  va_list ap;
+  va_start(ap, fmt);
+  vsnprintf(g_err, sizeof(g_err), fmt, ap);
+  va_end(ap);
+  return code;
+}
+
+static int check_shape(const b200moe_shape* s) {
+  B200_CHECK_ARG(s != nullptr, "shape is NULL");
+  B200_CHECK_ARG(s->T >= 0 && s->T < (1 << 24), "T=%d outside [0, 2^24)", s->T);
+  B200_CHECK_ARG(s->K >= 1 && s->K <= 32, "K=%d outside [1,32]", s->K);
+  B200_CHECK_ARG(s->E >= 1 && s->E_route >= s->E && s->E_route <= 1024, "E=%d / E_route=%d invalid", s->E,
+                 s->E_route);
+  B200_CHECK_ARG(s->B == 32 || s->B == 64 || s->B == 128, "B=%d not in {32,64,128}", s->B);
+  B200_CHECK_ARG(s->H >= 32 && s->H % 32 == 0, "H=%d must be a positive multiple of 32", s->H);
+  B200_CHECK_ARG(s->I >= 32 && s->I % 32 == 0, "I=%d must be a positive multiple of 32", s->I);
+  B200_CHECK_ARG(s->H % 8 == 0, "H must be a multiple of 8");
+  B200_CHECK_ARG(s->weight_format == B200MOE_W_MXFP4, "weight_format %d is not supported by this build",
+                 s->weight_format);
+  B200_CHECK_ARG(s->activation == B200MOE_ACT_SILU || s->activation == B200MOE_ACT_SWIGLU,
+                 "activation %d unknown", s->activation);
+  return 0;
+}
+
+static int64_t kp_of(int k) { return round_up64(k, 128); }
+
+}  // namespace b200moe
+
+using namespace b200moe;
+
+extern "C" {
+
+int b200moe_version(void) { return B200MOE_VERSION; }
+
+const char* b200moe_last_error(void) { return g_err; }
+
+int b200moe_workspace_layout(const b200moe_shape* s, b200moe_workspace* ws) {
+  if (int rc = check_shape(s)) return rc;
+  B200_CHECK_ARG(ws != nullptr, "workspace descriptor is NULL");
+  const int64_t P = (int64_t)s->T * s->K;
+  const int64_t nblk = (P + (int64_t)s->E_route * (s->B - 1) + s->B - 1) / s->B;
+  const int64_t L = std::max<int64_t>(nblk, 1) * s->B;
+  const int64_t L128 = round_up64(L, 128);
+  const int64_t HP = kp_of(s->H), IP = kp_of(s->I);
+  int64_t off = 0;
+  auto take = [&](int64_t bytes) {
+    int64_t o = off;
+    off += round_up64(std::max<int64_t>(bytes, 16), 1024);
+    return o;
+  };
+  memset(ws, 0, sizeof(*ws));
+  ws->max_rows = L;
+  ws->off_sorted_ids = take(L * 4);
+  ws->off_sorted_w = take(L * 4);
+  ws->off_sorted_e = take(L / s->B * 4);
+  ws->off_num_valid = take(8);
+  ws->off_loc = take(std::max<int64_t>(P, 1) * 4);
+  ws->off_status = take(64);
+  ws->off_xq_hi = take(L * HP);
+  ws->off_xq_lo = take(L * HP);
+  ws->off_xsf_hi = take(L128 / 128 * (HP / 128) * kSfChunk);
+  ws->off_xsf_lo = take(L128 / 128 * (HP / 128) * kSfChunk);
+  ws->off_hq_hi = take(L * IP);
+  ws->off_hq_lo = take(L * IP);
+  ws->off_hsf_hi = take(L128 / 128 * (IP / 128) * kSfChunk);
+  ws->off_hsf_lo = take(L128 / 128 * (IP / 128) * kSfChunk);
+  ws->off_out2 = take(L * s->H * 2);
+  ws->total_bytes = off;
+  return 0;
+}
+
+int b200moe_prepared_bytes(const b200moe_shape* s, int which, int64_t* data_bytes, int64_t* scale_bytes) {
+  if (int rc = check_shape(s)) return rc;
+  B200_CHECK_ARG(which == 1 || which == 2, "which=%d must be 1 or 2", which);
+  const int parts = which == 1 ? 2 : 1;
+  const int rpp = which == 1 ? s->I : s->H;
+  const int Kd = which == 1 ? s->H : s->I;
+  const int64_t KP = kp_of(Kd);
+  if (data_bytes) *data_bytes = (int64_t)s->E * parts * rpp * (KP / 2) + 256;
+  if (scale_bytes) *scale_bytes = (int64_t)s->E * parts * ((rpp + 127) / 128) * (KP / 128) * kSfChunk;
+  return 0;
+}
+
+int b200moe_prepare_weights(const b200moe_shape* s, int which, const void* w_q, const void* w_s, void* out_data,
+                            void* out_scale, void* stream) {
+  if (int rc = check_shape(s)) return rc;
+  B200_CHECK_ARG(which == 1 || which == 2, "which=%d must be 1 or 2", which);
+  B200_CHECK_ARG(w_q && w_s && out_data && out_scale, "prepare_weights: NULL pointer");
+  B200_CHECK_ARG(((uintptr_t)out_data & 31) == 0 && ((uintptr_t)out_scale & 15) == 0,
+                 "prepare_weights: output buffers must be 32-byte aligned");
+  cudaStream_t st = (cudaStream_t)stream;
+  const int parts = which == 1 ? 2 : 1;
+  const int rpp = which == 1 ? s->I : s->H;
+  const int Kd = which == 1 ? s->H : s->I;
+  const int64_t KP = kp_of(Kd);
+  const int64_t rows = (int64_t)s->E * parts * rpp;
+  if (KP != Kd) B200_CHECK_CUDA(cudaMemsetAsync(out_data, 0, rows * (KP / 2) + 256, st));
+  B200_CHECK_CUDA(cudaMemcpy2DAsync(out_data, KP / 2, w_q, Kd / 2, Kd / 2, rows, cudaMemcpyDeviceToDevice, st));
+  return launch_repack_scales(w_s, out_scale, s->E, parts, rpp, Kd, st);
+}
+
+int b200moe_sort_align(const int32_t* topk_ids, const float* topk_weight, int32_t T, int32_t K, int32_t E_route,
+                       int32_t B, const int32_t* expert_mask, uint32_t* sorted_ids, float* sorted_weights,
+                       int32_t* sorted_expert_ids, int32_t* num_valid_ids, int32_t* loc, void* stream) {
+  B200_CHECK_ARG(T >= 0 && T < (1 << 24) && K >= 1 && K <= 255, "sort_align: T=%d K=%d out of range", T, K);
+  B200_CHECK_ARG(B >= 1, "sort_align: B=%d", B);
+  B200_CHECK_ARG(sorted_ids && sorted_weights && sorted_expert_ids && num_valid_ids, "sort_align: NULL output");
+  B200_CHECK_ARG(T == 0 || (topk_ids && topk_weight), "sort_align: NULL input");
+  return launch_sort_align(topk_ids, topk_weight, T, K, E_route, B, expert_mask, sorted_ids, sorted_weights,
+                           sorted_expert_ids, num_valid_ids, loc, (cudaStream_t)stream);
+}
+
+int b200moe_quant_rows(const void* src_bf16, int32_t src_mode, const uint32_t* sorted_ids,
+                       const int32_t* num_valid_ids, int32_t T, int32_t K, int32_t Kd, int64_t max_rows, void* q_hi,
+                       void* q_lo, void* sf_hi, void* sf_lo, void* stream) {
+  B200_CHECK_ARG(src_mode == 0 || src_mode == 1, "quant_rows: src_mode=%d", src_mode);
+  B200_CHECK_ARG(sorted_ids && num_valid_ids && q_hi && q_lo && sf_hi && sf_lo, "quant_rows: NULL pointer");
+  B200_CHECK_ARG(T == 0 || src_bf16, "quant_rows: NULL source");
+  B200_CHECK_ARG(((uintptr_t)src_bf16 & 15) == 0, "quant_rows: source must be 16-byte aligned");
+  return launch_quant_rows(src_bf16, src_mode, sorted_ids, num_valid_ids, T, K, Kd, max_rows, q_hi, q_lo, sf_hi,
+                           sf_lo, (cudaStream_t)stream);
+}
+
+static void fill_common(GemmArgs& g, const b200moe_shape* s, const b200moe_workspace* ws, uint8_t* base) {
+  g.N = s->B;
+  g.E = s->E;
+  g.topk = s->K;
+  g.T = s->T;
+  g.activation = s->activation;
+  g.swiglu_limit = s->swiglu_limit > 0.f ? s->swiglu_limit : 7.0f;
+  g.max_rows = ws->max_rows;
+  g.sorted_ids = (const uint32_t*)(base + ws->off_sorted_ids);
+  g.sorted_e = (const int32_t*)(base + ws->off_sorted_e);
+  g.num_valid = (const int32_t*)(base + ws->off_num_valid);
+  g.status = (int32_t*)(base + ws->off_status);
+}
+
+int b200moe_gateup(const b200moe_shape* s, const b200moe_workspace* ws, void* workspace, const void* w1_data,
+                   const void* w1_scale, void* h_out, void* stream) {
+  if (int rc = check_shape(s)) return rc;
+  B200_CHECK_ARG(ws && workspace && w1_data && w1_scale, "gateup: NULL pointer");
+  B200_CHECK_ARG(((uintptr_t)workspace & 1023) == 0, "gateup: workspace must be 1024-byte aligned");
+  uint8_t* base = (uint8_t*)workspace;
+  GemmArgs g = {};
+  fill_common(g, s, ws, base);
+  g.gateup = true;
+  g.rows = s->I;
+  g.Kd = s->H;
+  g.w_data = w1_data;
+  g.w_scale = w1_scale;
+  g.a_hi = base + ws->off_xq_hi;
+  g.a_lo = base + ws->off_xq_lo;
+  g.asf_hi = base + ws->off_xsf_hi;
+  g.asf_lo = base + ws->off_xsf_lo;
+  g.h_out = h_out;
+  g.oq_hi = base + ws->off_hq_hi;
+  g.oq_lo = base + ws->off_hq_lo;
+  g.osf_hi = base + ws->off_hsf_hi;
+  g.osf_lo = base + ws->off_hsf_lo;
+  g.out_kp = (int)kp_of(s->I);
+  return launch_grouped_gemm(g, (cudaStream_t)stream);
+}
+
+int b200moe_down(const b200moe_shape* s, const b200moe_workspace* ws, void* workspace, const void* w2_data,
+                 const void* w2_scale, void* stream) {
+  if (int rc = check_shape(s)) return rc;
+  B200_CHECK_ARG(ws && workspace && w2_data && w2_scale, "down: NULL pointer");
+  B200_CHECK_ARG(((uintptr_t)workspace & 1023) == 0, "down: workspace must be 1024-byte aligned");
+  uint8_t* base = (uint8_t*)workspace;
+  GemmArgs g = {};
+  fill_common(g, s, ws, base);
+  g.gateup = false;
+  g.rows = s->H;
+  g.Kd = s->I;
+  g.w_data = w2_data;
+  g.w_scale = w2_scale;
+  g.a_hi = base + ws->off_hq_hi;
+  g.a_lo = base + ws->off_hq_lo;
+  g.asf_hi = base + ws->off_hsf_hi;
+  g.asf_lo = base + ws->off_hsf_lo;
+  g.out2 = base + ws->off_out2;
+  return launch_grouped_gemm(g, (cudaStream_t)stream);
+}
+
+int b200moe_combine(const b200moe_shape* s, const b200moe_workspace* ws, void* workspace, const float* topk_weight,
+                    void* y_bf16, void* stream) {
+  if (int rc = check_shape(s)) return rc;
+  B200_CHECK_ARG(ws && workspace && (s->T == 0 || (topk_weight && y_bf16)), "combine: NULL pointer");
+  B200_CHECK_ARG(((uintptr_t)y_bf16 & 15) == 0, "combine: output must be 16-byte aligned");
+  uint8_t* base = (uint8_t*)workspace;
+  return launch_combine(base + ws->off_out2, (const int32_t*)(base + ws->off_loc), topk_weight, y_bf16, s->T, s->K,
+                        s->H, (cudaStream_t)stream);
+}
+
+int b200moe_forward(const b200moe_shape* s, const b200moe_workspace* ws, void* workspace, const void* x_bf16,
+                    const int32_t* topk_ids, const float* topk_weight, const int32_t* expert_mask,
+                    const void* w1_data, const void* w1_scale, const void* w2_data, const void* w2_scale,
+                    void* y_bf16, void* stream) {
+  if (int rc = check_shape(s)) return rc;
+  B200_CHECK_ARG(ws && workspace, "forward: NULL workspace");
+  if (s->T == 0) return 0;
+  B200_CHECK_ARG(x_bf16 && topk_ids && topk_weight && y_bf16, "forward: NULL tensor");
+  uint8_t* base = (uint8_t*)workspace;
+  int rc = b200moe_sort_align(topk_ids, topk_weight, s->T, s->K, s->E_route, s->B, expert_mask,
+                              (uint32_t*)(base + ws->off_sorted_ids), (float*)(base + ws->off_sorted_w),
+                              (int32_t*)(base + ws->off_sorted_e), (int32_t*)(base + ws->off_num_valid),
+                              (int32_t*)(base + ws->off_loc), stream);
+  if (rc) return rc;
+  rc = b200moe_quant_rows(x_bf16, 0, (const uint32_t*)(base + ws->off_sorted_ids),
+                          (const int32_t*)(base + ws->off_num_valid), s->T, s->K, s->H, ws->max_rows,
+                          base + ws->off_xq_hi, base + ws->off_xq_lo, base + ws->off_xsf_hi, base + ws->off_xsf_lo,
+                          stream);
+  if (rc) return rc;
+  rc = b200moe_gateup(s, ws, workspace, w1_data, w1_scale, nullptr, stream);
+  if (rc) return rc;
+  rc = b200moe_down(s, ws, workspace, w2_data, w2_scale, stream);
+  if (rc) return rc;
+  return b200moe_combine(s, ws, workspace, topk_weight, y_bf16, stream);
+}
+
+int b200moe_debug_probe(int which, const void* in, void* out, void* stream) {
+  B200_CHECK_ARG(in && out, "debug_probe: NULL pointer");
+  return run_debug_probe(which, in, out, (cudaStream_t)stream);
+}
+
+}  // extern "C"

@@ -1,0 +1,75 @@
+// Declarations shared by the translation units of libb200moe.so.
+#pragma once
+#include <cuda.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "../../include/b200moe.h"
+
+namespace b200moe {
+
+int set_error(int code, const char* fmt, ...);
+
+#define B200_CHECK_ARG(cond, ...)                      \
+  do {                                                 \
+    if (!(cond)) return b200moe::set_error(-1, __VA_ARGS__); \
+  } while (0)
+
+#define B200_CHECK_CUDA(expr)                                                                  \
+  do {                                                                                         \
+    cudaError_t _e = (expr);                                                                   \
+    if (_e != cudaSuccess)                                                                     \
+      return b200moe::set_error((int)_e, "%s failed: %s", #expr, cudaGetErrorString(_e));      \
+  } while (0)
+
+static inline int64_t round_up64(int64_t x, int64_t m) { return (x + m - 1) / m * m; }
+
+// scale-factor chunk: 128 rows x 4 scales in tensor-memory order
+constexpr int kSfChunk = 512;
+__host__ __device__ static inline int sf_chunk_offset(int row_in_128, int j) {
+  return (row_in_128 & 31) * 16 + (row_in_128 >> 5) * 4 + j;
+}
+
+// launchers (moe_aux.cu)
+int launch_sort_align(const int32_t* ids, const float* w, int T, int K, int E, int B, const int32_t* mask,
+                      uint32_t* sorted_ids, float* sorted_w, int32_t* sorted_e, int32_t* num_valid,
+                      int32_t* loc, cudaStream_t st);
+int launch_quant_rows(const void* src, int src_mode, const uint32_t* sorted_ids, const int32_t* num_valid,
+                      int T, int K, int Kd, int64_t max_rows, void* q_hi, void* q_lo, void* sf_hi, void* sf_lo,
+                      cudaStream_t st);
+int launch_combine(const void* out2, const int32_t* loc, const float* topk_w, void* y, int T, int K, int H,
+                   cudaStream_t st);
+int launch_repack_scales(const void* w_s, void* out, int E, int parts, int rows_per_part, int Kd,
+                         cudaStream_t st);
+
+// grouped GEMM (moe_gemm_sm100.cu)
+struct GemmArgs {
+  bool gateup;
+  int N;               // token tile (= sort block B)
+  int rows;            // weight rows per part (I for gate-up, H for down)
+  int Kd;              // reduction length (H for gate-up, I for down)
+  int E;               // experts in the weight image
+  int topk, T;
+  int activation;
+  float swiglu_limit;
+  int64_t max_rows;
+  const void* w_data;  // [E, parts*rows, KP/2]
+  const void* w_scale; // [E, parts, MT, KB, 512]
+  const void* a_hi;    // [max_rows, KP] e4m3
+  const void* a_lo;
+  const void* asf_hi;  // [max_rows/128, KB, 512]
+  const void* asf_lo;
+  const uint32_t* sorted_ids;
+  const int32_t* sorted_e;
+  const int32_t* num_valid;
+  int32_t* status;
+  // outputs
+  void* h_out;         // gate-up: bf16 [T, topk, I] or null
+  void* oq_hi; void* oq_lo; void* osf_hi; void* osf_lo;   // gate-up fused re-quantisation
+  int out_kp;          // row pitch of oq_* (I padded to 128) and chunk count per row block
+  void* out2;          // down: bf16 [max_rows, H]
+};
+int launch_grouped_gemm(const GemmArgs& a, cudaStream_t st);
+int run_debug_probe(int which, const void* in, void* out, cudaStream_t st);
+
+}  // namespace b200moe

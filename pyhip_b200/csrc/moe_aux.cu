@@ -1,0 +1,338 @@
+// Integer / byte kernels around the grouped GEMMs: token->expert sort/align, activation
+// quantise-and-gather, scale repack, weighted combine.  All HBM- or latency-bound.
+#include <cuda_bf16.h>
+#include <cuda_fp8.h>
+
+#include "internal.h"
+
+namespace b200moe {
+
+// =====================================================================================
+// sort / align  (contract: src/contrib/fused_moe.py:56-100 of the reference; ck_tile
+// reference_moe_sorting.hpp:14-117).  One CTA; every warp owns a contiguous slice of the
+// flattened [T*K] id array, so slice order == the required stable token-major order.
+// No atomics: ranks come from warp match/popc and per-warp counters, hence deterministic.
+// =====================================================================================
+constexpr int kSortWarps = 32;
+
+__device__ __forceinline__ int sort_fetch_expert(const int32_t* ids, const int32_t* mask, int i, int P, int E) {
+  if (i >= P) return -1;
+  int e = ids[i];
+  if (e < 0 || e >= E) return -1;
+  if (mask != nullptr && mask[e] == 0) return -1;
+  return e;
+}
+
+__global__ void __launch_bounds__(kSortWarps * 32, 1)
+sort_align_kernel(const int32_t* __restrict__ ids, const float* __restrict__ w, int T, int K, int E, int B,
+                  const int32_t* __restrict__ mask, uint32_t* __restrict__ sorted_ids,
+                  float* __restrict__ sorted_w, int32_t* __restrict__ sorted_e,
+                  int32_t* __restrict__ num_valid, int32_t* __restrict__ loc) {
+  extern __shared__ int32_t sm[];
+  int32_t* cnt = sm;                        // [kSortWarps][E] per-warp counts, then running offsets
+  int32_t* base = sm + kSortWarps * E;      // [E] first sorted row of the expert
+  int32_t* total = base + E;                // [E]
+  int32_t* lid = total + E;                 // [E] emitted (local) expert id
+  unsigned long long* wsum =                // [33] scan scratch, 8-byte aligned
+      reinterpret_cast<unsigned long long*>(sm + ((kSortWarps * E + 3 * E + 1) & ~1));
+
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int P = T * K;
+  const int seg = ((P + kSortWarps - 1) / kSortWarps + 31) & ~31;
+  const int seg_lo = warp * seg, seg_hi = min(P, seg_lo + seg);
+
+  for (int i = tid; i < kSortWarps * E; i += blockDim.x) cnt[i] = 0;
+  __syncthreads();
+
+  // pass 1: per-warp histogram of its slice
+  for (int i0 = seg_lo; i0 < seg_hi; i0 += 32) {
+    int e = sort_fetch_expert(ids, mask, i0 + lane, seg_hi, E);
+    unsigned same = __match_any_sync(0xffffffffu, e);
+    if (e >= 0 && lane == __ffs(same) - 1) cnt[warp * E + e] += __popc(same);
+  }
+  __syncthreads();
+
+  // per-expert (one thread each, E <= blockDim.x): warp offsets inside the expert, padded
+  // size, and whether the expert advances the emitted (local) expert id
+  {
+    const int e = tid;
+    int padded = 0, live = 0;
+    if (e < E) {
+      int run = 0;
+      for (int wv = 0; wv < kSortWarps; ++wv) {
+        int c = cnt[wv * E + e];
+        cnt[wv * E + e] = run;
+        run += c;
+      }
+      total[e] = run;
+      padded = (run + B - 1) / B * B;
+      live = (mask == nullptr || mask[e] != 0) ? 1 : 0;
+    }
+    // block-wide exclusive scan of (padded, live), packed in one 64-bit word
+    const unsigned long long v = ((unsigned long long)(unsigned)padded << 32) | (unsigned)live;
+    unsigned long long incl = v;
+    for (int d = 1; d < 32; d <<= 1) {
+      unsigned long long o = __shfl_up_sync(0xffffffffu, incl, d);
+      if (lane >= d) incl += o;
+    }
+    if (lane == 31) wsum[warp] = incl;
+    __syncthreads();
+    if (warp == 0) {
+      const unsigned long long s = wsum[lane];
+      unsigned long long si = s;
+      for (int d = 1; d < 32; d <<= 1) {
+        unsigned long long o = __shfl_up_sync(0xffffffffu, si, d);
+        if (lane >= d) si += o;
+      }
+      wsum[lane] = si - s;
+      if (lane == 31) wsum[32] = si;
+    }
+    __syncthreads();
+    const unsigned long long excl = wsum[warp] + incl - v;
+    if (e < E) {
+      base[e] = (int)(excl >> 32);
+      lid[e] = (int)(excl & 0xffffffffu);
+    }
+    if (tid == 0) {
+      num_valid[0] = (int)(wsum[32] >> 32);
+      num_valid[1] = T;
+    }
+  }
+  __syncthreads();
+
+  // pass 2: stable scatter
+  const uint32_t lt_mask = (1u << lane) - 1u;
+  for (int i0 = seg_lo; i0 < seg_hi; i0 += 32) {
+    int i = i0 + lane;
+    int e = sort_fetch_expert(ids, mask, i, seg_hi, E);
+    unsigned same = __match_any_sync(0xffffffffu, e);
+    int pos = -1;
+    if (e >= 0) pos = base[e] + cnt[warp * E + e] + __popc(same & lt_mask);
+    __syncwarp();
+    if (e >= 0 && lane == __ffs(same) - 1) cnt[warp * E + e] += __popc(same);
+    __syncwarp();
+    if (i < seg_hi) {
+      if (pos >= 0) {
+        sorted_ids[pos] = ((uint32_t)(i % K) << 24) | (uint32_t)(i / K);
+        sorted_w[pos] = w[i];
+      }
+      if (loc != nullptr) loc[i] = pos;
+    }
+  }
+
+  // padding rows and per-block expert ids
+  const uint32_t sentinel = ((uint32_t)K << 24) | (uint32_t)T;
+  for (int e = tid; e < E; e += blockDim.x) {
+    int n = total[e];
+    if (n == 0) continue;
+    int b0 = base[e], n_pad = (n + B - 1) / B * B;
+    for (int p = b0 + n; p < b0 + n_pad; ++p) {
+      sorted_ids[p] = sentinel;
+      sorted_w[p] = 0.f;
+    }
+    for (int blk = b0 / B; blk < (b0 + n_pad) / B; ++blk) sorted_e[blk] = lid[e];
+  }
+}
+
+int launch_sort_align(const int32_t* ids, const float* w, int T, int K, int E, int B, const int32_t* mask,
+                      uint32_t* sorted_ids, float* sorted_w, int32_t* sorted_e, int32_t* num_valid,
+                      int32_t* loc, cudaStream_t st) {
+  B200_CHECK_ARG(E >= 1 && E <= kSortWarps * 32, "sort_align: E=%d outside [1,%d]", E, kSortWarps * 32);
+  size_t smem = (size_t)(kSortWarps * E + 3 * E + 2) * sizeof(int32_t) + 34 * sizeof(unsigned long long);
+  B200_CHECK_ARG(smem <= 200 * 1024, "sort_align: E=%d needs %zu bytes of shared memory", E, smem);
+  static bool attr_set = false;
+  if (!attr_set) {
+    B200_CHECK_CUDA(cudaFuncSetAttribute(sort_align_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         200 * 1024));
+    attr_set = true;
+  }
+  sort_align_kernel<<<1, kSortWarps * 32, smem, st>>>(ids, w, T, K, E, B, mask, sorted_ids, sorted_w, sorted_e,
+                                                      num_valid, loc);
+  B200_CHECK_CUDA(cudaGetLastError());
+  return 0;
+}
+
+// =====================================================================================
+// activation quantiser: bf16 row -> two e4m3 terms with per-32 E8M0 scales, written in
+// sorted-row order.  One thread per 32-element block.
+//   e  = max(biased_exponent(amax) - 7, 0);  q = e4m3_rne(x * 2^(127-e));  r = x - q*2^(e-127)
+//   the residual r is quantised the same way (second term).
+// =====================================================================================
+__device__ __forceinline__ float pow2_from_biased(int e) {   // 2^(e-127), e in [0,254]
+  return __uint_as_float(e == 0 ? 0x00400000u : ((uint32_t)e << 23));
+}
+
+__device__ __forceinline__ void quant_block32(const float (&x)[32], uint8_t (&q)[32], float (&resid)[32],
+                                              int& e_out) {
+  float amax = 0.f;
+#pragma unroll
+  for (int i = 0; i < 32; ++i) amax = fmaxf(amax, fabsf(x[i]));
+  int e = max((int)((__float_as_uint(amax) >> 23) & 0xFF) - 7, 0);
+  float inv = __uint_as_float((uint32_t)(254 - e) << 23);
+  float sc = pow2_from_biased(e);
+#pragma unroll
+  for (int i = 0; i < 32; i += 2) {
+    float2 v = make_float2(x[i] * inv, x[i + 1] * inv);
+    __nv_fp8x2_storage_t p = __nv_cvt_float2_to_fp8x2(v, __NV_SATFINITE, __NV_E4M3);
+    q[i] = (uint8_t)(p & 0xFF);
+    q[i + 1] = (uint8_t)(p >> 8);
+    __half2_raw h = __nv_cvt_fp8x2_to_halfraw2(p, __NV_E4M3);
+    float2 f = __half22float2(*reinterpret_cast<__half2*>(&h));
+    resid[i] = x[i] - f.x * sc;
+    resid[i + 1] = x[i + 1] - f.y * sc;
+  }
+  e_out = e;
+}
+
+__global__ void __launch_bounds__(256)
+quant_rows_kernel(const __nv_bfloat16* __restrict__ src, int src_mode, const uint32_t* __restrict__ sorted_ids,
+                  const int32_t* __restrict__ num_valid, int T, int K, int Kd, int KP, int64_t max_rows,
+                  uint8_t* __restrict__ q_hi, uint8_t* __restrict__ q_lo, uint8_t* __restrict__ sf_hi,
+                  uint8_t* __restrict__ sf_lo) {
+  const int nb = KP / 32;
+  const int KB = KP / 128;
+  const int64_t rows_live = min((int64_t)num_valid[0], max_rows);
+  for (int64_t g = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; g < rows_live * nb;
+       g += (int64_t)gridDim.x * blockDim.x) {
+    const int64_t r = g / nb;
+    const int j = (int)(g % nb);
+    const uint32_t id = sorted_ids[r];
+    const int tok = (int)(id & 0xFFFFFFu), kk = (int)(id >> 24);
+    const bool valid = (kk < K) && (tok < T) && (j * 32 < Kd);
+    uint4 hi[2] = {}, lo[2] = {};
+    int e_hi = 0, e_lo = 0;
+    if (valid) {
+      const int64_t srow = (src_mode == 0) ? (int64_t)tok : ((int64_t)tok * K + kk);
+      const uint4* p = reinterpret_cast<const uint4*>(src + srow * Kd + j * 32);
+      float x[32], r1[32], r2[32];
+      uint8_t qa[32], qb[32];
+#pragma unroll
+      for (int v = 0; v < 4; ++v) {
+        uint4 u = p[v];
+        const __nv_bfloat162* b2 = reinterpret_cast<const __nv_bfloat162*>(&u);
+#pragma unroll
+        for (int t = 0; t < 4; ++t) {
+          float2 f = __bfloat1622float2(b2[t]);
+          x[v * 8 + t * 2] = f.x;
+          x[v * 8 + t * 2 + 1] = f.y;
+        }
+      }
+      quant_block32(x, qa, r1, e_hi);
+      quant_block32(r1, qb, r2, e_lo);
+      memcpy(hi, qa, 32);
+      memcpy(lo, qb, 32);
+    }
+    uint4* dh = reinterpret_cast<uint4*>(q_hi + r * KP + j * 32);
+    uint4* dl = reinterpret_cast<uint4*>(q_lo + r * KP + j * 32);
+    dh[0] = hi[0]; dh[1] = hi[1];
+    dl[0] = lo[0]; dl[1] = lo[1];
+    const int64_t chunk = ((r >> 7) * KB + (j >> 2)) * kSfChunk + sf_chunk_offset((int)(r & 127), j & 3);
+    sf_hi[chunk] = (uint8_t)e_hi;
+    sf_lo[chunk] = (uint8_t)e_lo;
+  }
+}
+
+int launch_quant_rows(const void* src, int src_mode, const uint32_t* sorted_ids, const int32_t* num_valid,
+                      int T, int K, int Kd, int64_t max_rows, void* q_hi, void* q_lo, void* sf_hi, void* sf_lo,
+                      cudaStream_t st) {
+  B200_CHECK_ARG(Kd % 32 == 0, "quant_rows: Kd=%d must be a multiple of 32", Kd);
+  const int KP = (int)round_up64(Kd, 128);
+  int64_t work = max_rows * (KP / 32);
+  int blocks = (int)std::min<int64_t>((work + 255) / 256, 148 * 16);
+  if (blocks < 1) blocks = 1;
+  quant_rows_kernel<<<blocks, 256, 0, st>>>(reinterpret_cast<const __nv_bfloat16*>(src), src_mode, sorted_ids,
+                                            num_valid, T, K, Kd, KP, max_rows, (uint8_t*)q_hi, (uint8_t*)q_lo,
+                                            (uint8_t*)sf_hi, (uint8_t*)sf_lo);
+  B200_CHECK_CUDA(cudaGetLastError());
+  return 0;
+}
+
+// =====================================================================================
+// combine: y[t,:] = sum over the token's pairs, in ascending sorted position (= ascending
+// expert id), of bf16(out2[loc] * w), each partial sum rounded to bf16 -- the arithmetic of
+// the reference's index_add_ loop (tests/contrib/moe/test_moe.py:107-117).
+// =====================================================================================
+constexpr int kMaxTopk = 32;
+
+__global__ void __launch_bounds__(256)
+combine_kernel(const __nv_bfloat16* __restrict__ out2, const int32_t* __restrict__ loc,
+               const float* __restrict__ topk_w, __nv_bfloat16* __restrict__ y, int T, int K, int H) {
+  const int vec_per_row = H / 8;
+  for (int64_t g = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; g < (int64_t)T * vec_per_row;
+       g += (int64_t)gridDim.x * blockDim.x) {
+    const int t = (int)(g / vec_per_row), c = (int)(g % vec_per_row) * 8;
+    float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+    int last = -1;
+    for (int it = 0; it < K; ++it) {
+      int best = 0x7fffffff, best_k = -1;
+      for (int k = 0; k < K; ++k) {
+        int p = loc[t * K + k];
+        if (p > last && p < best) { best = p; best_k = k; }
+      }
+      if (best_k < 0) break;
+      last = best;
+      const float wv = topk_w[t * K + best_k];
+      uint4 u = *reinterpret_cast<const uint4*>(out2 + (int64_t)best * H + c);
+      const __nv_bfloat16* d = reinterpret_cast<const __nv_bfloat16*>(&u);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        float contrib = __bfloat162float(__float2bfloat16_rn(__bfloat162float(d[i]) * wv));
+        acc[i] = __bfloat162float(__float2bfloat16_rn(acc[i] + contrib));
+      }
+    }
+    uint4 o;
+    __nv_bfloat16* ob = reinterpret_cast<__nv_bfloat16*>(&o);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) ob[i] = __float2bfloat16_rn(acc[i]);
+    *reinterpret_cast<uint4*>(y + (int64_t)t * H + c) = o;
+  }
+}
+
+int launch_combine(const void* out2, const int32_t* loc, const float* topk_w, void* y, int T, int K, int H,
+                   cudaStream_t st) {
+  B200_CHECK_ARG(H % 8 == 0 && K <= kMaxTopk, "combine: H %% 8 != 0 or K > %d", kMaxTopk);
+  if (T == 0) return 0;
+  int64_t work = (int64_t)T * (H / 8);
+  int blocks = (int)std::min<int64_t>((work + 255) / 256, 148 * 16);
+  combine_kernel<<<blocks, 256, 0, st>>>((const __nv_bfloat16*)out2, loc, topk_w, (__nv_bfloat16*)y, T, K, H);
+  B200_CHECK_CUDA(cudaGetLastError());
+  return 0;
+}
+
+// =====================================================================================
+// weight-scale repack: [E, parts*rows, Kd/32] bytes -> [E, parts, MT, KB, 512] chunks in
+// tensor-memory order; rows / k-blocks that do not exist get exponent 127 (= 1.0).
+// =====================================================================================
+__global__ void __launch_bounds__(256)
+repack_scales_kernel(const uint8_t* __restrict__ src, uint8_t* __restrict__ dst, int E, int parts, int rpp,
+                     int nsf, int MT, int KB) {
+  const int64_t total = (int64_t)E * parts * MT * KB * kSfChunk;
+  for (int64_t g = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; g < total;
+       g += (int64_t)gridDim.x * blockDim.x) {
+    int off = (int)(g % kSfChunk);
+    int64_t c = g / kSfChunk;
+    int kb = (int)(c % KB); c /= KB;
+    int mt = (int)(c % MT); c /= MT;
+    int part = (int)(c % parts);
+    int e = (int)(c / parts);
+    int r_local = (off >> 4) + 32 * ((off & 15) >> 2);
+    int j = off & 3;
+    int row = mt * 128 + r_local, kidx = kb * 4 + j;
+    uint8_t v = 127;
+    if (row < rpp && kidx < nsf) v = src[((int64_t)e * parts * rpp + (int64_t)part * rpp + row) * nsf + kidx];
+    dst[g] = v;
+  }
+}
+
+int launch_repack_scales(const void* w_s, void* out, int E, int parts, int rows_per_part, int Kd,
+                         cudaStream_t st) {
+  const int KB = (int)round_up64(Kd, 128) / 128, MT = (rows_per_part + 127) / 128;
+  int64_t total = (int64_t)E * parts * MT * KB * kSfChunk;
+  int blocks = (int)std::min<int64_t>((total + 255) / 256, 148 * 32);
+  repack_scales_kernel<<<blocks, 256, 0, st>>>((const uint8_t*)w_s, (uint8_t*)out, E, parts, rows_per_part,
+                                               Kd / 32, MT, KB);
+  B200_CHECK_CUDA(cudaGetLastError());
+  return 0;
+}
+
+}  // namespace b200moe

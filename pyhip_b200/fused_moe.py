@@ -1,0 +1,275 @@
+"""`fused_moe` -- the reference's operator surface (src/contrib/fused_moe.py:128-155 of
+tingqli/pyhip) in front of the sm_100a kernels.
+
+Same positional / keyword names and argument meaning as the reference; the aiter enums it takes
+(`ActivationType`, `QuantType`) are re-declared here because aiter is not a dependency.  The
+reference wrapper accepts QuantType.No and per_128x128 and reaches MXFP4 only through its raw
+kernels (tests/contrib/moe/test_moe.py:347-374, 638-771); this wrapper adds per_1x32 to the same
+signature: ``w1``/``w2`` are packed E2M1 (uint8 or float4_e2m1fn_x2, low nibble = even element)
+and ``w1_scale``/``w2_scale`` are E8M0 bytes ``[E*N, Kd/32]`` (or ``[E, N, Kd/32]``).
+
+Work is enqueued on ``torch.cuda.current_stream()`` and never synchronises.
+"""
+from __future__ import annotations
+
+import ctypes
+import enum
+import weakref
+
+import torch
+
+from . import _lib
+
+
+class ActivationType(enum.IntEnum):
+    No = -1
+    Silu = 0
+    Gelu = 1
+    Swiglu = 2
+
+
+class QuantType(enum.IntEnum):
+    No = 0
+    per_Tensor = 1
+    per_Token = 2
+    per_1x32 = 3
+    per_1x128 = 4
+    per_128x128 = 5
+
+
+def _ptr(t):
+    return None if t is None else ctypes.c_void_p(t.data_ptr())
+
+
+def _stream():
+    return ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+
+
+def pick_block(T: int, K: int, E: int) -> int:
+    """Rows per sorted block (= token tile of the GEMMs).  Small when few tokens reach each
+    expert so the weight-streaming regime wastes no tensor work on padding; the reference makes
+    the same decode/prefill split on T*K/E (src/contrib/fused_moe.py:285-300,358-362)."""
+    per_expert = (T * K) / max(E, 1)
+    if per_expert <= 32:
+        return 32
+    if per_expert <= 96:
+        return 64
+    return 128
+
+
+class PreparedWeights:
+    """Device-layout image of one layer's MXFP4 expert weights, built once (the counterpart of
+    the reference's weight pre-shuffle, src/misc.py:114-128)."""
+
+    def __init__(self, w1, w1_scale, w2, w2_scale):
+        if not w1.is_cuda:
+            raise ValueError("weights must be CUDA tensors")
+        w1 = w1.view(torch.uint8) if w1.dtype != torch.uint8 else w1
+        w2 = w2.view(torch.uint8) if w2.dtype != torch.uint8 else w2
+        s1 = w1_scale.view(torch.uint8) if w1_scale.dtype != torch.uint8 else w1_scale
+        s2 = w2_scale.view(torch.uint8) if w2_scale.dtype != torch.uint8 else w2_scale
+        E, N1, Kh = w1.shape
+        self.E, self.I, self.H = E, N1 // 2, Kh * 2
+        if tuple(w2.shape) != (E, self.H, self.I // 2):
+            raise ValueError(f"w2 shape {tuple(w2.shape)} does not match w1 {tuple(w1.shape)}")
+        if s1.numel() != E * N1 * (self.H // 32) or s2.numel() != E * self.H * (self.I // 32):
+            raise ValueError("scale tensors must hold one E8M0 byte per 32 weights")
+        if int(s1.max()) > 254 or int(s2.max()) > 254:
+            raise ValueError("E8M0 scale 0xFF (NaN) is not a valid weight scale")
+        L = _lib.lib()
+        shape = _lib.Shape(T=0, K=1, E=E, E_route=E, H=self.H, I=self.I, B=32, weight_format=_lib.W_MXFP4,
+                           activation=0, swiglu_limit=0.0)
+        out = []
+        for which, wq, ws in ((1, w1, s1), (2, w2, s2)):
+            db, sb = ctypes.c_int64(), ctypes.c_int64()
+            _lib.check(L.b200moe_prepared_bytes(ctypes.byref(shape), which, ctypes.byref(db), ctypes.byref(sb)),
+                       "prepared_bytes")
+            data = torch.empty(db.value, dtype=torch.uint8, device=w1.device)
+            scale = torch.empty(sb.value, dtype=torch.uint8, device=w1.device)
+            _lib.check(L.b200moe_prepare_weights(ctypes.byref(shape), which, _ptr(wq.contiguous()),
+                                                 _ptr(ws.contiguous()), _ptr(data), _ptr(scale), _stream()),
+                       "prepare_weights")
+            out += [data, scale]
+        self.w1_data, self.w1_scale, self.w2_data, self.w2_scale = out
+        self.device = w1.device
+
+
+_prepared_cache: dict = {}
+_workspace_cache: dict = {}
+
+
+def prepare_weights(w1, w1_scale, w2, w2_scale) -> PreparedWeights:
+    """Cached by the identity of the four tensors (weights are static across calls)."""
+    key = (w1.data_ptr(), w1_scale.data_ptr(), w2.data_ptr(), w2_scale.data_ptr(), tuple(w1.shape))
+    hit = _prepared_cache.get(key)
+    if hit is not None and hit[0]() is w1:
+        return hit[1]
+    pw = PreparedWeights(w1, w1_scale, w2, w2_scale)
+    _prepared_cache[key] = (weakref.ref(w1), pw)
+    return pw
+
+
+class MoEPlan:
+    """Shape, workspace layout and workspace tensor of one (T, K, E, H, I, B) problem."""
+
+    def __init__(self, T, K, E, E_route, H, I, B, activation, swiglu_limit, device):
+        self.shape = _lib.Shape(T=T, K=K, E=E, E_route=E_route, H=H, I=I, B=B, weight_format=_lib.W_MXFP4,
+                                activation=activation, swiglu_limit=float(swiglu_limit))
+        self.ws = _lib.workspace_layout(self.shape)
+        self.buf = torch.empty(self.ws.total_bytes + 1024, dtype=torch.uint8, device=device)
+        off = (-self.buf.data_ptr()) % 1024
+        self.base = self.buf.data_ptr() + off
+        self._view = self.buf[off:off + self.ws.total_bytes]
+        self.status().zero_()
+
+    def region(self, name: str, nbytes: int, dtype=torch.uint8):
+        off = getattr(self.ws, "off_" + name)
+        return self._view[off:off + nbytes].view(dtype)
+
+    def status(self):
+        return self.region("status", 64, torch.int32)
+
+    def sort_outputs(self):
+        L, B = self.ws.max_rows, self.shape.B
+        return (self.region("sorted_ids", L * 4, torch.int32), self.region("sorted_w", L * 4, torch.float32),
+                self.region("sorted_e", L // B * 4, torch.int32), self.region("num_valid", 8, torch.int32),
+                self.region("loc", max(self.shape.T * self.shape.K, 1) * 4, torch.int32))
+
+    # ---- stage-by-stage entry points (the raw-kernel surface the reference's tests drive,
+    # tests/contrib/moe/test_moe.py:638-771) -------------------------------------------------
+    def _args(self):
+        return ctypes.byref(self.shape), ctypes.byref(self.ws), ctypes.c_void_p(self.base)
+
+    def sort(self, topk_ids, topk_weight, expert_mask=None):
+        s = self.shape
+        ids_o, w_o, e_o, nv_o, loc_o = self.sort_outputs()
+        _lib.check(_lib.lib().b200moe_sort_align(
+            _ptr(topk_ids), _ptr(topk_weight), s.T, s.K, s.E_route, s.B, _ptr(expert_mask), _ptr(ids_o),
+            _ptr(w_o), _ptr(e_o), _ptr(nv_o), _ptr(loc_o), _stream()), "sort_align")
+        return ids_o, w_o, e_o, nv_o, loc_o
+
+    def quant_input(self, x):
+        s, ws = self.shape, self.ws
+        ids_o, _, _, nv_o, _ = self.sort_outputs()
+        base = self.base
+        _lib.check(_lib.lib().b200moe_quant_rows(
+            _ptr(x), 0, _ptr(ids_o), _ptr(nv_o), s.T, s.K, s.H, ws.max_rows,
+            ctypes.c_void_p(base + ws.off_xq_hi), ctypes.c_void_p(base + ws.off_xq_lo),
+            ctypes.c_void_p(base + ws.off_xsf_hi), ctypes.c_void_p(base + ws.off_xsf_lo), _stream()),
+            "quant_rows")
+
+    def quant_hidden(self, h):
+        """h: bf16 [T, K, I] -> operand rows of the down GEMM."""
+        s, ws = self.shape, self.ws
+        ids_o, _, _, nv_o, _ = self.sort_outputs()
+        base = self.base
+        _lib.check(_lib.lib().b200moe_quant_rows(
+            _ptr(h), 1, _ptr(ids_o), _ptr(nv_o), s.T, s.K, s.I, ws.max_rows,
+            ctypes.c_void_p(base + ws.off_hq_hi), ctypes.c_void_p(base + ws.off_hq_lo),
+            ctypes.c_void_p(base + ws.off_hsf_hi), ctypes.c_void_p(base + ws.off_hsf_lo), _stream()),
+            "quant_rows")
+
+    def gateup(self, pw, h_out=None):
+        _lib.check(_lib.lib().b200moe_gateup(*self._args(), _ptr(pw.w1_data), _ptr(pw.w1_scale), _ptr(h_out),
+                                             _stream()), "gateup")
+
+    def down(self, pw):
+        _lib.check(_lib.lib().b200moe_down(*self._args(), _ptr(pw.w2_data), _ptr(pw.w2_scale), _stream()), "down")
+
+    def combine(self, topk_weight, y):
+        _lib.check(_lib.lib().b200moe_combine(*self._args(), _ptr(topk_weight), _ptr(y), _stream()), "combine")
+
+    def check_status(self):
+        """Host read of the device-side error words (synchronises; for tests and debugging)."""
+        st = self.status().cpu().tolist()
+        if st[0] != 0 or st[2] != 0:
+            raise _lib.B200MoEError(f"device status: wait gave up at 0x{st[0]:x} in CTA {st[1]}, "
+                                    f"bad expert id flag {st[2]}")
+
+
+def get_plan(T, K, E, E_route, H, I, B, activation, swiglu_limit, device) -> MoEPlan:
+    key = (T, K, E, E_route, H, I, B, activation, float(swiglu_limit), str(device))
+    plan = _workspace_cache.get(key)
+    if plan is None:
+        if len(_workspace_cache) > 16:
+            _workspace_cache.clear()
+        plan = MoEPlan(T, K, E, E_route, H, I, B, activation, swiglu_limit, device)
+        _workspace_cache[key] = plan
+    return plan
+
+
+def moe_forward(plan: MoEPlan, pw: PreparedWeights, hidden_states, topk_weight, topk_ids, expert_mask=None,
+                out=None):
+    """One layer call through the C ABI (sort -> quantise -> gate-up -> down -> combine)."""
+    T, H = hidden_states.shape
+    if out is None:
+        out = torch.empty((T, H), dtype=torch.bfloat16, device=hidden_states.device)
+    if T == 0:
+        return out
+    _lib.check(_lib.lib().b200moe_forward(
+        ctypes.byref(plan.shape), ctypes.byref(plan.ws), ctypes.c_void_p(plan.base), _ptr(hidden_states),
+        _ptr(topk_ids), _ptr(topk_weight), _ptr(expert_mask), _ptr(pw.w1_data), _ptr(pw.w1_scale),
+        _ptr(pw.w2_data), _ptr(pw.w2_scale), _ptr(out), _stream()), "forward")
+    return out
+
+
+def fused_moe(hidden_states, w1, w2, topk_weight, topk_ids, expert_mask=None,
+              activation=ActivationType.Silu, quant_type=QuantType.No, doweight_stage1=False,
+              w1_scale=None, w2_scale=None, a1_scale=None, a2_scale=None, block_size_M=None,
+              num_local_tokens=None, moe_sorting_dispatch_policy=0, dtype=None, hidden_pad=0,
+              intermediate_pad=0, bias1=None, bias2=None, splitk=0, method="auto",
+              swiglu_limit=7.0):
+    """bf16 hidden states [T,H], router top-k ids [T,K] int32 and weights [T,K] fp32, packed
+    expert weights with their scales -> bf16 [T,H].  Unsupported combinations raise, as the
+    reference asserts (src/contrib/fused_moe.py:252-266)."""
+    if not hidden_states.is_cuda:
+        raise RuntimeError("fused_moe runs on a CUDA device only (sm_100a); there is no CPU path")
+    if hidden_states.dtype != torch.bfloat16:
+        raise TypeError("hidden_states must be bfloat16")
+    if int(quant_type) != QuantType.per_1x32:
+        raise NotImplementedError(f"quant_type={quant_type!r}: this build implements per_1x32 (MXFP4) weights")
+    if int(activation) not in (ActivationType.Silu, ActivationType.Swiglu):
+        raise NotImplementedError(f"activation={activation!r}: Silu and Swiglu are implemented")
+    if doweight_stage1 or bias1 is not None or bias2 is not None or a1_scale is not None or a2_scale is not None:
+        raise NotImplementedError("doweight_stage1 / bias / pre-quantised activations are not implemented")
+    if num_local_tokens is not None or hidden_pad or intermediate_pad:
+        raise NotImplementedError("num_local_tokens / padding arguments are not implemented")
+    if w1_scale is None or w2_scale is None:
+        raise ValueError("per_1x32 needs w1_scale and w2_scale")
+    if dtype not in (None, torch.bfloat16):
+        raise NotImplementedError("output dtype must be bfloat16")
+    T, H = hidden_states.shape
+    K = topk_ids.shape[1]
+    pw = prepare_weights(w1, w1_scale, w2, w2_scale)
+    if pw.H != H:
+        raise ValueError(f"hidden size {H} does not match weights ({pw.H})")
+    E_route = pw.E if expert_mask is None else int(expert_mask.numel())
+    B = int(block_size_M) if block_size_M else pick_block(T, K, pw.E)
+    act = _lib.ACT_SILU if int(activation) == ActivationType.Silu else _lib.ACT_SWIGLU
+    plan = get_plan(T, K, pw.E, E_route, H, pw.I, B, act, swiglu_limit, hidden_states.device)
+    ids = topk_ids if topk_ids.dtype == torch.int32 else topk_ids.to(torch.int32)
+    tw = topk_weight if topk_weight.dtype == torch.float32 else topk_weight.float()
+    mask = None if expert_mask is None else expert_mask.to(torch.int32).contiguous()
+    return moe_forward(plan, pw, hidden_states.contiguous(), tw.contiguous(), ids.contiguous(), mask)
+
+
+def moe_sorting(topk_ids, topk_weights, num_experts, model_dim, moebuf_dtype, block_size=32, expert_mask=None,
+                num_local_tokens=None, dispatch_policy=0):
+    """Same outputs as the reference's sorter (src/contrib/fused_moe.py:56-100):
+    (sorted_ids, sorted_weights, sorted_expert_ids, num_valid_ids, moe_out)."""
+    if num_local_tokens is not None:
+        raise NotImplementedError("num_local_tokens")
+    T, K = topk_ids.shape
+    dev = topk_ids.device
+    nblk = (T * K + num_experts * (block_size - 1) + block_size - 1) // block_size
+    sorted_ids = torch.empty(nblk * block_size, dtype=torch.int32, device=dev)
+    sorted_w = torch.empty(nblk * block_size, dtype=torch.float32, device=dev)
+    sorted_e = torch.empty(nblk, dtype=torch.int32, device=dev)
+    num_valid = torch.empty(2, dtype=torch.int32, device=dev)
+    moe_out = torch.zeros((T, model_dim), dtype=moebuf_dtype, device=dev)
+    mask = None if expert_mask is None else expert_mask.to(torch.int32).contiguous()
+    _lib.check(_lib.lib().b200moe_sort_align(
+        _ptr(topk_ids.to(torch.int32).contiguous()), _ptr(topk_weights.float().contiguous()), T, K, num_experts,
+        block_size, _ptr(mask), _ptr(sorted_ids), _ptr(sorted_w), _ptr(sorted_e), _ptr(num_valid), None,
+        _stream()), "sort_align")
+    return sorted_ids, sorted_w, sorted_e, num_valid, moe_out

@@ -1,0 +1,50 @@
+"""GPU tier: known-answer probes of the two hardware data paths the GEMM main loop relies on --
+the copy engine's FP4 unpacking into 128-byte-swizzled shared memory, and the shared->tensor
+memory scale copy."""
+import ctypes
+import pathlib
+
+import numpy as np
+import pytest
+import torch
+
+from pyhip_b200 import _lib
+
+pytestmark = pytest.mark.gpu
+OUT = pathlib.Path(__file__).resolve().parents[1] / "gpurun_out"
+
+
+def _probe(which, inp: torch.Tensor, out_words: int):
+    out = torch.zeros(out_words, dtype=torch.int32, device="cuda:0")
+    _lib.check(_lib.lib().b200moe_debug_probe(which, ctypes.c_void_p(inp.data_ptr()), ctypes.c_void_p(out.data_ptr()),
+                                              ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)), "probe")
+    torch.cuda.synchronize()
+    return out.cpu().numpy()
+
+
+def test_tma_fp4_unpack_image():
+    g = torch.Generator().manual_seed(0)
+    src = torch.randint(0, 256, (128, 64), dtype=torch.uint8, generator=g)
+    raw = _probe(1, src.cuda(), 4096 + 1)
+    assert raw[4096] == 0, "TMA wait ran out"
+    img = raw[:4096].view(np.uint8).reshape(128, 128)
+    OUT.mkdir(exist_ok=True)
+    np.save(OUT / "probe_tma_fp4_image.npy", img)
+    s = src.numpy()
+    for r in range(128):
+        for c in range(8):                       # logical 16-element group -> swizzled 16-byte chunk
+            phys = (c ^ (r & 7)) * 16
+            assert np.array_equal(img[r, phys:phys + 8], s[r, c * 8:c * 8 + 8]), (r, c)
+
+
+def test_scale_copy_to_tensor_memory_layout():
+    src = torch.arange(128, dtype=torch.int32) * 0x01010101 + 0x03020100   # distinct bytes
+    src = (torch.arange(512, dtype=torch.int64) % 251).to(torch.uint8)
+    raw = _probe(2, src.cuda(), 512 + 1)
+    assert raw[512] == 0, "tcgen05.cp wait ran out"
+    got = raw[:512].astype(np.uint32).reshape(128, 4)
+    OUT.mkdir(exist_ok=True)
+    np.save(OUT / "probe_utccp.npy", got)
+    words = src.numpy().view(np.uint32).reshape(32, 4)       # 32 rows x 16 bytes
+    for lane in range(128):
+        assert np.array_equal(got[lane], words[lane % 32]), lane
