@@ -84,10 +84,12 @@ int b200moe_sort_align(const int32_t* topk_ids, const float* topk_weight, int32_
 /* Quantise bf16 rows into the two-term e4m3 + E8M0/32 operand format, gathered into sorted-row
  * order (stands where the reference calls aiter's per_1x32 activation quantiser followed by
  * moe_mxfp4_sort, tests/contrib/moe/test_moe.py:665-679).
- *   src_mode 0: src is [T, Kd], row = token.   src_mode 1: src is [T, K, Kd], row = token*K + k. */
+ *   src_mode 0: src is [T, Kd], row = token.   src_mode 1: src is [T, K, Kd], row = token*K + k.
+ *   q_*: e4m3 [max_rows, Kd padded to 128]; sf_*: one 512-byte scale chunk per (block of B sorted
+ *   rows, 128-wide k-block), row r of the block and scale j at byte (r%32)*16 + (r/32)*4 + j. */
 int b200moe_quant_rows(const void* src_bf16, int32_t src_mode, const uint32_t* sorted_ids,
-                       const int32_t* num_valid_ids, int32_t T, int32_t K, int32_t Kd, int64_t max_rows,
-                       void* q_hi, void* q_lo, void* sf_hi, void* sf_lo, void* stream);
+                       const int32_t* num_valid_ids, int32_t T, int32_t K, int32_t Kd, int32_t B,
+                       int64_t max_rows, void* q_hi, void* q_lo, void* sf_hi, void* sf_lo, void* stream);
 
 /* Gate-up grouped GEMM + activation: replaces moe_2stage_splitk(with_silu=True) /
  * moe_gemm_mxfp4(gate_up=True) (src/contrib/moe.py:362-702, src/contrib/moe_gemm_mxfp4.py:972-1290).

@@ -35,7 +35,9 @@ def calc_diff(x: torch.Tensor, y: torch.Tensor) -> float:
 def cosine(x: torch.Tensor, y: torch.Tensor) -> float:
     x, y = x.double().flatten(), y.double().flatten()
     den = x.norm() * y.norm()
-    return 1.0 if den == 0 else float((x @ y) / den)
+    if den == 0:
+        return 1.0 if x.norm() == y.norm() else 0.0
+    return float((x @ y) / den)
 
 
 def max_abs(x: torch.Tensor, y: torch.Tensor) -> float:

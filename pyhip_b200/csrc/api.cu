@@ -53,7 +53,7 @@ int b200moe_workspace_layout(const b200moe_shape* s, b200moe_workspace* ws) {
   const int64_t P = (int64_t)s->T * s->K;
   const int64_t nblk = (P + (int64_t)s->E_route * (s->B - 1) + s->B - 1) / s->B;
   const int64_t L = std::max<int64_t>(nblk, 1) * s->B;
-  const int64_t L128 = round_up64(L, 128);
+  const int64_t nb = L / s->B;   // one scale chunk per sorted block and k-block
   const int64_t HP = kp_of(s->H), IP = kp_of(s->I);
   int64_t off = 0;
   auto take = [&](int64_t bytes) {
@@ -71,12 +71,12 @@ int b200moe_workspace_layout(const b200moe_shape* s, b200moe_workspace* ws) {
   ws->off_status = take(64);
   ws->off_xq_hi = take(L * HP);
   ws->off_xq_lo = take(L * HP);
-  ws->off_xsf_hi = take(L128 / 128 * (HP / 128) * kSfChunk);
-  ws->off_xsf_lo = take(L128 / 128 * (HP / 128) * kSfChunk);
+  ws->off_xsf_hi = take(nb * (HP / 128) * kSfChunk);
+  ws->off_xsf_lo = take(nb * (HP / 128) * kSfChunk);
   ws->off_hq_hi = take(L * IP);
   ws->off_hq_lo = take(L * IP);
-  ws->off_hsf_hi = take(L128 / 128 * (IP / 128) * kSfChunk);
-  ws->off_hsf_lo = take(L128 / 128 * (IP / 128) * kSfChunk);
+  ws->off_hsf_hi = take(nb * (IP / 128) * kSfChunk);
+  ws->off_hsf_lo = take(nb * (IP / 128) * kSfChunk);
   ws->off_out2 = take(L * s->H * 2);
   ws->total_bytes = off;
   return 0;
@@ -124,13 +124,13 @@ int b200moe_sort_align(const int32_t* topk_ids, const float* topk_weight, int32_
 }
 
 int b200moe_quant_rows(const void* src_bf16, int32_t src_mode, const uint32_t* sorted_ids,
-                       const int32_t* num_valid_ids, int32_t T, int32_t K, int32_t Kd, int64_t max_rows, void* q_hi,
-                       void* q_lo, void* sf_hi, void* sf_lo, void* stream) {
+                       const int32_t* num_valid_ids, int32_t T, int32_t K, int32_t Kd, int32_t B, int64_t max_rows,
+                       void* q_hi, void* q_lo, void* sf_hi, void* sf_lo, void* stream) {
   B200_CHECK_ARG(src_mode == 0 || src_mode == 1, "quant_rows: src_mode=%d", src_mode);
   B200_CHECK_ARG(sorted_ids && num_valid_ids && q_hi && q_lo && sf_hi && sf_lo, "quant_rows: NULL pointer");
   B200_CHECK_ARG(T == 0 || src_bf16, "quant_rows: NULL source");
   B200_CHECK_ARG(((uintptr_t)src_bf16 & 15) == 0, "quant_rows: source must be 16-byte aligned");
-  return launch_quant_rows(src_bf16, src_mode, sorted_ids, num_valid_ids, T, K, Kd, max_rows, q_hi, q_lo, sf_hi,
+  return launch_quant_rows(src_bf16, src_mode, sorted_ids, num_valid_ids, T, K, Kd, B, max_rows, q_hi, q_lo, sf_hi,
                            sf_lo, (cudaStream_t)stream);
 }
 
@@ -220,7 +220,7 @@ int b200moe_forward(const b200moe_shape* s, const b200moe_workspace* ws, void* w
                               (int32_t*)(base + ws->off_loc), stream);
   if (rc) return rc;
   rc = b200moe_quant_rows(x_bf16, 0, (const uint32_t*)(base + ws->off_sorted_ids),
-                          (const int32_t*)(base + ws->off_num_valid), s->T, s->K, s->H, ws->max_rows,
+                          (const int32_t*)(base + ws->off_num_valid), s->T, s->K, s->H, s->B, ws->max_rows,
                           base + ws->off_xq_hi, base + ws->off_xq_lo, base + ws->off_xsf_hi, base + ws->off_xsf_lo,
                           stream);
   if (rc) return rc;

@@ -35,7 +35,7 @@ int launch_sort_align(const int32_t* ids, const float* w, int T, int K, int E, i
                       uint32_t* sorted_ids, float* sorted_w, int32_t* sorted_e, int32_t* num_valid,
                       int32_t* loc, cudaStream_t st);
 int launch_quant_rows(const void* src, int src_mode, const uint32_t* sorted_ids, const int32_t* num_valid,
-                      int T, int K, int Kd, int64_t max_rows, void* q_hi, void* q_lo, void* sf_hi, void* sf_lo,
+                      int T, int K, int Kd, int B, int64_t max_rows, void* q_hi, void* q_lo, void* sf_hi, void* sf_lo,
                       cudaStream_t st);
 int launch_combine(const void* out2, const int32_t* loc, const float* topk_w, void* y, int T, int K, int H,
                    cudaStream_t st);
@@ -57,7 +57,7 @@ struct GemmArgs {
   const void* w_scale; // [E, parts, MT, KB, 512]
   const void* a_hi;    // [max_rows, KP] e4m3
   const void* a_lo;
-  const void* asf_hi;  // [max_rows/128, KB, 512]
+  const void* asf_hi;  // [max_rows/N, KB, 512], rows block-local
   const void* asf_lo;
   const uint32_t* sorted_ids;
   const int32_t* sorted_e;

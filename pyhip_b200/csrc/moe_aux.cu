@@ -186,7 +186,7 @@ __device__ __forceinline__ void quant_block32(const float (&x)[32], uint8_t (&q)
 
 __global__ void __launch_bounds__(256)
 quant_rows_kernel(const __nv_bfloat16* __restrict__ src, int src_mode, const uint32_t* __restrict__ sorted_ids,
-                  const int32_t* __restrict__ num_valid, int T, int K, int Kd, int KP, int64_t max_rows,
+                  const int32_t* __restrict__ num_valid, int T, int K, int Kd, int KP, int B, int64_t max_rows,
                   uint8_t* __restrict__ q_hi, uint8_t* __restrict__ q_lo, uint8_t* __restrict__ sf_hi,
                   uint8_t* __restrict__ sf_lo) {
   const int nb = KP / 32;
@@ -226,22 +226,25 @@ quant_rows_kernel(const __nv_bfloat16* __restrict__ src, int src_mode, const uin
     uint4* dl = reinterpret_cast<uint4*>(q_lo + r * KP + j * 32);
     dh[0] = hi[0]; dh[1] = hi[1];
     dl[0] = lo[0]; dl[1] = lo[1];
-    const int64_t chunk = ((r >> 7) * KB + (j >> 2)) * kSfChunk + sf_chunk_offset((int)(r & 127), j & 3);
+    // one 512-byte scale chunk per (sorted block, k-block); rows are block-local so that a
+    // block's scales start at TMEM lane 0 of a 4-column-aligned group
+    const int64_t chunk = ((r / B) * KB + (j >> 2)) * kSfChunk + sf_chunk_offset((int)(r % B), j & 3);
     sf_hi[chunk] = (uint8_t)e_hi;
     sf_lo[chunk] = (uint8_t)e_lo;
   }
 }
 
 int launch_quant_rows(const void* src, int src_mode, const uint32_t* sorted_ids, const int32_t* num_valid,
-                      int T, int K, int Kd, int64_t max_rows, void* q_hi, void* q_lo, void* sf_hi, void* sf_lo,
+                      int T, int K, int Kd, int B, int64_t max_rows, void* q_hi, void* q_lo, void* sf_hi, void* sf_lo,
                       cudaStream_t st) {
+  B200_CHECK_ARG(B == 32 || B == 64 || B == 128, "quant_rows: B=%d not in {32,64,128}", B);
   B200_CHECK_ARG(Kd % 32 == 0, "quant_rows: Kd=%d must be a multiple of 32", Kd);
   const int KP = (int)round_up64(Kd, 128);
   int64_t work = max_rows * (KP / 32);
   int blocks = (int)std::min<int64_t>((work + 255) / 256, 148 * 16);
   if (blocks < 1) blocks = 1;
   quant_rows_kernel<<<blocks, 256, 0, st>>>(reinterpret_cast<const __nv_bfloat16*>(src), src_mode, sorted_ids,
-                                            num_valid, T, K, Kd, KP, max_rows, (uint8_t*)q_hi, (uint8_t*)q_lo,
+                                            num_valid, T, K, Kd, KP, B, max_rows, (uint8_t*)q_hi, (uint8_t*)q_lo,
                                             (uint8_t*)sf_hi, (uint8_t*)sf_lo);
   B200_CHECK_CUDA(cudaGetLastError());
   return 0;

@@ -30,7 +30,8 @@ namespace b200moe {
 constexpr int kThreads = 192;
 constexpr int kTileM = 128;          // weight rows per MMA
 constexpr int kTileK = 128;          // K per pipeline stage (4 MMA K-steps of 32)
-constexpr int kATileBytes = kTileM * kTileK;   // FP4 unpacked to one byte per element
+constexpr int kATileBytes = kTileM * kTileK;   // FP4 unpacked to one byte per element in shared memory
+constexpr int kATileTxBytes = kTileM * kTileK / 2;   // the copy engine counts the packed bytes it read
 constexpr int kMaxStages = 12;
 constexpr int kTmemCols = 512;
 constexpr int kSfCol0 = 448;         // scale columns: 2 buffers x {A0, A1, Bhi, Blo} x 4 columns
@@ -90,7 +91,7 @@ moe_grouped_gemm_kernel(const __grid_constant__ GemmParams p) {
   const int N = p.N;
   const int b_bytes = N * kTileK;
   const int stage_bytes = NA * kATileBytes + 2 * b_bytes + 4 * kSfChunk;
-  const uint32_t stage_tx = NA * kATileBytes + 2 * b_bytes + (NA + 2) * kSfChunk;
+  const uint32_t stage_tx = NA * kATileTxBytes + 2 * b_bytes + (NA + 2) * kSfChunk;
   const int S = p.stages;
   const int acc_stride = NA * N;
   const int n_acc = (2 * acc_stride <= 256) ? 2 : 1;
@@ -141,8 +142,8 @@ moe_grouped_gemm_kernel(const __grid_constant__ GemmParams p) {
         if (e < 0 || e >= p.E) { p.status[2] = 1; e = 0; }
         const int r0 = b * N;
         const uint8_t* sfa = p.w_scale + ((int64_t)e * p.parts * p.MT + m) * p.KB * kSfChunk;
-        const uint8_t* sfb_hi = p.asf_hi + (int64_t)(r0 >> 7) * p.KB * kSfChunk;
-        const uint8_t* sfb_lo = p.asf_lo + (int64_t)(r0 >> 7) * p.KB * kSfChunk;
+        const uint8_t* sfb_hi = p.asf_hi + (int64_t)b * p.KB * kSfChunk;
+        const uint8_t* sfb_lo = p.asf_lo + (int64_t)b * p.KB * kSfChunk;
         for (int kb = 0; kb < p.KB; ++kb) {
           if (!mbar_wait(smem_u32(&ctl->empty[stage]), phase ^ 1, abort_word, 0x100 + stage)) { ok = false; break; }
           uint8_t* st = stage0 + (size_t)stage * stage_bytes;
@@ -184,9 +185,6 @@ moe_grouped_gemm_kernel(const __grid_constant__ GemmParams p) {
       uint32_t sf_buf = 0;          // scale columns alternate between two TMEM buffers
       bool ok = true;
       for (int w = blockIdx.x; w < total_work && ok; w += gridDim.x) {
-        const int b = w / p.MT;
-        const int r0 = b * N;
-        const uint32_t sfb_off = (uint32_t)((r0 & 127) >> 5);
         if (!mbar_wait(smem_u32(&ctl->tmem_empty[acc]), acc_phase ^ 1, abort_word, 0x200 + acc)) break;
         tc_fence_after_sync();
         const uint32_t d0 = tmem_base + acc * acc_stride;
@@ -210,12 +208,12 @@ moe_grouped_gemm_kernel(const __grid_constant__ GemmParams p) {
             const uint64_t da0 = make_desc_sw128(a0 + k * 32);
             const uint64_t dbh = make_desc_sw128(bh + k * 32);
             const uint64_t dbl = make_desc_sw128(bl + k * 32);
-            mma_mxf8f6f4(d0, da0, dbh, idesc, sfc + 0, sfc + 8 + sfb_off, accum);
-            mma_mxf8f6f4(d0, da0, dbl, idesc, sfc + 0, sfc + 12 + sfb_off, 1);
+            mma_mxf8f6f4(d0, da0, dbh, idesc, sfc + 0, sfc + 8, accum);
+            mma_mxf8f6f4(d0, da0, dbl, idesc, sfc + 0, sfc + 12, 1);
             if (GATEUP) {
               const uint64_t da1 = make_desc_sw128(a0 + kATileBytes + k * 32);
-              mma_mxf8f6f4(d0 + N, da1, dbh, idesc, sfc + 4, sfc + 8 + sfb_off, accum);
-              mma_mxf8f6f4(d0 + N, da1, dbl, idesc, sfc + 4, sfc + 12 + sfb_off, 1);
+              mma_mxf8f6f4(d0 + N, da1, dbh, idesc, sfc + 4, sfc + 8, accum);
+              mma_mxf8f6f4(d0 + N, da1, dbl, idesc, sfc + 4, sfc + 12, 1);
             }
           }
           tc_commit(smem_u32(&ctl->empty[stage]));
@@ -280,7 +278,7 @@ moe_grouped_gemm_kernel(const __grid_constant__ GemmParams p) {
               p.oq_hi[r * p.out_kp + j] = q1;
               p.oq_lo[r * p.out_kp + j] = q2;
               if (lane == 0) {
-                const int64_t off = ((r >> 7) * p.out_kb + m) * kSfChunk + sf_chunk_offset((int)(r & 127), quad);
+                const int64_t off = ((int64_t)b * p.out_kb + m) * kSfChunk + sf_chunk_offset(c0 + n, quad);
                 p.osf_hi[off] = (uint8_t)e1;
                 p.osf_lo[off] = (uint8_t)e2;
               }
@@ -459,7 +457,7 @@ probe_tma_fp4_kernel(const __grid_constant__ CUtensorMap map, uint32_t* out) {
   fence_proxy_async_smem();
   __syncthreads();
   if (threadIdx.x == 0) {
-    mbar_expect_tx(smem_u32(&bar), kATileBytes);
+    mbar_expect_tx(smem_u32(&bar), kATileTxBytes);
     tma_load_3d(smem_u32(smem), &map, smem_u32(&bar), 0, 0, 0);
     mbar_wait(smem_u32(&bar), 0, &abort_word, 1);
   }

@@ -153,7 +153,7 @@ class MoEPlan:
         ids_o, _, _, nv_o, _ = self.sort_outputs()
         base = self.base
         _lib.check(_lib.lib().b200moe_quant_rows(
-            _ptr(x), 0, _ptr(ids_o), _ptr(nv_o), s.T, s.K, s.H, ws.max_rows,
+            _ptr(x), 0, _ptr(ids_o), _ptr(nv_o), s.T, s.K, s.H, s.B, ws.max_rows,
             ctypes.c_void_p(base + ws.off_xq_hi), ctypes.c_void_p(base + ws.off_xq_lo),
             ctypes.c_void_p(base + ws.off_xsf_hi), ctypes.c_void_p(base + ws.off_xsf_lo), _stream()),
             "quant_rows")
@@ -164,7 +164,7 @@ class MoEPlan:
         ids_o, _, _, nv_o, _ = self.sort_outputs()
         base = self.base
         _lib.check(_lib.lib().b200moe_quant_rows(
-            _ptr(h), 1, _ptr(ids_o), _ptr(nv_o), s.T, s.K, s.I, ws.max_rows,
+            _ptr(h), 1, _ptr(ids_o), _ptr(nv_o), s.T, s.K, s.I, s.B, ws.max_rows,
             ctypes.c_void_p(base + ws.off_hq_hi), ctypes.c_void_p(base + ws.off_hq_lo),
             ctypes.c_void_p(base + ws.off_hsf_hi), ctypes.c_void_p(base + ws.off_hsf_lo), _stream()),
             "quant_rows")

@@ -1,0 +1,91 @@
+"""CPU tier: the expert-parallel dispatch/combine plumbing with gloo ranks (world size 2 and 4),
+including a rank that never joins the exchange (failure detection by timeout, no GPU involved)."""
+import datetime
+import os
+import socket
+
+import pytest
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+from oracle import moe_oracle as orc
+from pyhip_b200 import ep, synth
+
+
+def _free_port():
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+def _worker(rank, world, port, fail_rank, q):
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    torch.set_num_threads(1)
+    dist.init_process_group("gloo", rank=rank, world_size=world,
+                            timeout=datetime.timedelta(seconds=8 if fail_rank is not None else 60))
+    try:
+        T, H, I, E, K = 24, 128, 64, 8, 3
+        w = synth.make_weights_mxfp4(E, H, I, seed=2)
+        w1, w2 = orc.dequant_mxfp4(w[0], w[1]), orc.dequant_mxfp4(w[2], w[3])
+        x = synth.make_hidden(T, H, seed=10 + rank)
+        tw, ids = synth.make_routing(T, E, K, "zipf", seed=10 + rank)
+        El = E // world
+        lo = rank * El
+
+        def local_fn(xr, twr, ids_local):
+            return orc.torch_moe_oracle(xr, w1[lo:lo + El], w2[lo:lo + El], twr, ids_local)
+
+        layer = ep.ExpertParallelMoE(None, None, None, None, E, rank, world, local_fn=local_fn)
+        if fail_rank == rank:
+            q.put((rank, "skipped"))
+            return
+        try:
+            y = layer.forward(x, tw, ids)
+        except Exception as e:  # noqa: BLE001 - the surviving rank must see an error, not hang
+            q.put((rank, "error:" + type(e).__name__))
+            return
+        ref = orc.torch_moe_oracle(x, w1, w2, tw, ids)
+        q.put((rank, (orc.cosine(y, ref), orc.max_abs(y, ref))))
+    finally:
+        try:
+            dist.destroy_process_group()
+        except Exception:  # noqa: BLE001
+            pass
+
+
+def _spawn(world, fail_rank=None):
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_worker, args=(r, world, port, fail_rank, q)) for r in range(world)]
+    for p in procs:
+        p.start()
+    res = dict(q.get(timeout=120) for _ in range(world))
+    for p in procs:
+        p.join(timeout=60)
+    return res
+
+
+def test_plan_dispatch_groups_tokens_once_per_rank():
+    ids = torch.tensor([[0, 1, 7], [4, 5, 6], [3, 4, 0]], dtype=torch.int32)
+    rows, counts = ep.plan_dispatch(ids, 4, 2)
+    assert counts.tolist() == [2, 3]
+    assert rows.tolist() == [0, 2, 0, 1, 2]
+    y = ep.scatter_back(torch.ones(5, 4), rows, 3)
+    assert y[:, 0].tolist() == [2.0, 1.0, 2.0]
+
+
+@pytest.mark.parametrize("world", [2, 4])
+def test_expert_parallel_matches_single_process_oracle(world):
+    res = _spawn(world)
+    for r in range(world):
+        cos, mx = res[r]
+        assert cos > 0.9999 and mx < 5e-3, (r, cos, mx)
+
+
+def test_rank_that_never_joins_is_detected_by_timeout():
+    res = _spawn(2, fail_rank=1)
+    assert res[1] == "skipped"
+    assert isinstance(res[0], str) and res[0].startswith("error:")

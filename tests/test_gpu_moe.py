@@ -44,9 +44,9 @@ def _assert_close(y, ref, what=""):
     assert cos >= COS and mx <= MAX_ABS, f"{what}: cosine {cos:.6f} max_abs {mx:.3e}"
 
 
-def _sfchunks_to_rows(sf: np.ndarray, rows: int, KB: int) -> np.ndarray:
-    """[rows/128, KB, 512] scale chunks in tensor-memory order -> [rows, KB*4]."""
-    c = sf.reshape(-1, KB, 32, 4, 4)                 # [blk, kb, r%32, r/32, j]
+def _sfchunks_to_rows(sf: np.ndarray, rows: int, KB: int, B: int) -> np.ndarray:
+    """[rows/B, KB, 512] scale chunks (block-local rows, tensor-memory order) -> [rows, KB*4]."""
+    c = sf.reshape(-1, KB, 32, 4, 4)[:, :, :, :B // 32]           # [blk, kb, r%32, r/32, j]
     return c.transpose(0, 3, 2, 1, 4).reshape(-1, KB * 4)[:rows]
 
 
@@ -61,9 +61,9 @@ def test_quantised_rows_match_oracle_bit_for_bit():
     HP = (H + 127) // 128 * 128
     q_hi = plan.region("xq_hi", plan.ws.max_rows * HP).cpu().numpy().reshape(-1, HP)[:n]
     q_lo = plan.region("xq_lo", plan.ws.max_rows * HP).cpu().numpy().reshape(-1, HP)[:n]
-    nch = (plan.ws.max_rows + 127) // 128 * (HP // 128) * 512
-    sf_hi = _sfchunks_to_rows(plan.region("xsf_hi", nch).cpu().numpy(), n, HP // 128)
-    sf_lo = _sfchunks_to_rows(plan.region("xsf_lo", nch).cpu().numpy(), n, HP // 128)
+    nch = plan.ws.max_rows // 32 * (HP // 128) * 512
+    sf_hi = _sfchunks_to_rows(plan.region("xsf_hi", nch).cpu().numpy(), n, HP // 128, 32)
+    sf_lo = _sfchunks_to_rows(plan.region("xsf_lo", nch).cpu().numpy(), n, HP // 128, 32)
     sid = s_ids.cpu().numpy().view(np.uint32)[:n]
     tok, kk = sid & 0xFFFFFF, sid >> 24
     eq_hi, ee_hi, eq_lo, ee_lo = orc.hilo8_quant(x)
