@@ -125,6 +125,8 @@ int b200moe_forward(const b200moe_shape* shape, const b200moe_workspace* ws, voi
  *              from `in` (8192 bytes) -> `out` receives the 16384-byte shared-memory image.
  *   which = 2: 512 bytes `in` -> shared -> tcgen05.cp 32x128b.warpx4 -> tcgen05.ld;
  *              `out` receives u32 [128 lanes][4 columns].
+ *   which = 3: tensor-core issue-rate measurement; `in` = i32 {kind (0 mxf8f6f4, 1 mxf4), N,
+ *              count, accumulators}; `out` = u32 {issue cycles, cycles until complete, status}.
  * out[last] status word: 0 = ok, non-zero = a bounded wait ran out. */
 int b200moe_debug_probe(int which, const void* in, void* out, void* stream);
 

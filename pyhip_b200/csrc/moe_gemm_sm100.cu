@@ -503,6 +503,62 @@ __global__ void __launch_bounds__(128, 1) probe_utccp_kernel(const uint32_t* in,
   if (warp == 0) tmem_dealloc(tbase, 32);
 }
 
+// Issue-rate probe: `count` dependent MMAs of shape 128 x N into `nacc` alternating accumulators,
+// one commit, one bounded wait; reports clock cycles.  Operand contents are irrelevant (zeros).
+__global__ void __launch_bounds__(128, 1) probe_mma_rate_kernel(const int32_t* cfg, uint32_t* out) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  __shared__ uint64_t bar;
+  __shared__ uint32_t tmem_slot, abort_word;
+  const int kind = cfg[0], N = cfg[1], count = cfg[2], nacc = cfg[3];
+  const int warp = threadIdx.x >> 5;
+  for (int i = threadIdx.x; i < (16384 + 32768 + 1024) / 4; i += blockDim.x) reinterpret_cast<uint32_t*>(smem)[i] = 0;
+  if (threadIdx.x == 0) {
+    abort_word = 0;
+    mbar_init(smem_u32(&bar), 1);
+    fence_mbar_init();
+  }
+  fence_proxy_async_smem();
+  if (warp == 0) {
+    tmem_alloc(smem_u32(&tmem_slot), 512);
+    tmem_relinquish();
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tbase = tmem_slot;
+  if (threadIdx.x == 0) {
+    const uint32_t a = smem_u32(smem), b = a + 16384, sf = b + 32768;
+    tc_copy_sf_32x128b(tbase + 448, make_desc_sf(sf));
+    tc_copy_sf_32x128b(tbase + 452, make_desc_sf(sf + 512));
+    tc_copy_sf_32x128b(tbase + 456, make_desc_sf(sf));
+    const long long t0 = clock64();
+    for (int i = 0; i < count; ++i) {
+      const int k = i & 3;
+      const uint32_t d = tbase + (i % nacc) * N;
+      if (kind == 0) {
+        const uint32_t idesc = make_idesc_block_scaled(kFmtE2M1_f8f6f4, kFmtE4M3, 128, N, k, k);
+        mma_mxf8f6f4(d, make_desc_sw128(a + k * 32), make_desc_sw128(b + k * 32), idesc, tbase + 448, tbase + 452,
+                     i >= nacc);
+      } else {
+        const uint32_t idesc = make_idesc_block_scaled(kFmtE2M1_mxf4, kFmtE2M1_mxf4, 128, N, (k & 1) * 2, (k & 1) * 2);
+        mma_mxf4(d, make_desc_sw128(a + (k & 1) * 32), make_desc_sw128(b + (k & 1) * 32), idesc, tbase + 448,
+                 tbase + 452, i >= nacc);
+      }
+    }
+    const long long t1 = clock64();
+    tc_commit(smem_u32(&bar));
+    mbar_wait(smem_u32(&bar), 0, &abort_word, 3);
+    const long long t2 = clock64();
+    out[0] = (uint32_t)(t1 - t0);
+    out[1] = (uint32_t)(t2 - t0);
+    out[2] = abort_word;
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  if (warp == 0) tmem_dealloc(tbase, 512);
+}
+
 int run_debug_probe(int which, const void* in, void* out, cudaStream_t st) {
   if (which == 1) {
     CUtensorMap map;
@@ -518,6 +574,17 @@ int run_debug_probe(int which, const void* in, void* out, cudaStream_t st) {
   }
   if (which == 2) {
     probe_utccp_kernel<<<1, 128, 0, st>>>((const uint32_t*)in, (uint32_t*)out);
+    B200_CHECK_CUDA(cudaGetLastError());
+    return 0;
+  }
+  if (which == 3) {
+    static bool attr = false;
+    if (!attr) {
+      B200_CHECK_CUDA(cudaFuncSetAttribute(probe_mma_rate_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                           65536));
+      attr = true;
+    }
+    probe_mma_rate_kernel<<<1, 128, 16384 + 32768 + 1024 + 1024, st>>>((const int32_t*)in, (uint32_t*)out);
     B200_CHECK_CUDA(cudaGetLastError());
     return 0;
   }
