@@ -33,8 +33,8 @@ UNIT = "tokens/s"
 def parse():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=50)
-    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--steps", type=int, default=1000)
+    ap.add_argument("--warmup", type=int, default=10)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--tokens", type=int, default=64, help="tokens per GPU per step")
     ap.add_argument("--sweep", action="store_true", help="also time T in {1,8,32,64,256,8192} (extra keys)")
@@ -59,7 +59,7 @@ class ClockSampler:
         self.proc = None
         try:
             self.proc = subprocess.Popen(["nvidia-smi", "-i", str(index), f"--query-gpu={self.Q}",
-                                          "--format=csv,noheader,nounits", "-lms", "100"],
+                                          "--format=csv,noheader,nounits", "-lms", "50"],
                                          stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
         except OSError:
             self.proc = None
@@ -268,7 +268,7 @@ def run_b200(args):
                              f"{info['experts_hit']} hit experts ({info['sample_seconds']} s), scaled to all hit experts"}
         line = {"metric": METRIC, "value": value, "unit": UNIT, "n_gpus": 1, "steps": args.steps,
                 "warmup": args.warmup, "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "weak",
-                "vs_baseline": None, "dtype": "mxfp4 weights x 2-term e4m3 activations, f32 accumulate",
+                "vs_baseline": None, "dtype": "mxfp4 weights x 3-term fp4 activations (kind::mxf4), f32 accumulate",
                 "data": "synthetic",
                 "config": {"workload": f"gptoss_decode H{H} I{I} E{E} top{K} T{T} mxfp4", "block": B,
                            "l2": "inputs larger than L2: %.2f GB of expert weights streamed per step" %
@@ -309,7 +309,7 @@ def run_b200(args):
     if rank == 0:
         line = {"metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
                 "warmup": args.warmup, "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "weak",
-                "vs_baseline": None, "dtype": "mxfp4 weights x 2-term e4m3 activations, f32 accumulate",
+                "vs_baseline": None, "dtype": "mxfp4 weights x 3-term fp4 activations (kind::mxf4), f32 accumulate",
                 "data": "synthetic",
                 "config": {"workload": f"gptoss_decode H{H} I{I} E{E} top{K} T{T}/gpu mxfp4 expert-parallel",
                            "parallelism": f"ep{world}", "l2": "inputs larger than L2 (expert weights streamed)"},

@@ -30,12 +30,15 @@ extern "C" {
 
 /* Shape of one MoE layer call.  B (rows per sorted block = token tile of the GEMMs) is 32, 64
  * or 128.  E is the number of experts whose weights are present (local experts under expert
- * parallelism); E_route is the size of the routing id space (E_route >= E; equal without a mask). */
+ * parallelism); E_route is the size of the routing id space (E_route >= E; equal without a mask).
+ * act_terms: how many packed-FP4 terms represent one activation row inside the GEMMs (2..4;
+ * 0 = default 3; 4 reproduces bf16 activations to ~1e-4 of the block maximum). */
 typedef struct b200moe_shape {
   int32_t T, K, E, E_route, H, I, B;
   int32_t weight_format;
   int32_t activation;
   float swiglu_limit;
+  int32_t act_terms;
 } b200moe_shape;
 
 /* Byte sizes and offsets of the caller-provided workspace (all offsets 1024-byte aligned). */
@@ -48,8 +51,10 @@ typedef struct b200moe_workspace {
   int64_t off_num_valid;     /* i32 [2]         {padded row total, T}                        */
   int64_t off_loc;           /* i32 [T*K]       sorted position of pair (t,k), -1 if dropped */
   int64_t off_status;        /* i32 [16]        device-side error words, 0 = clean           */
-  int64_t off_xq_hi, off_xq_lo, off_xsf_hi, off_xsf_lo; /* quantised input rows, sorted order   */
-  int64_t off_hq_hi, off_hq_lo, off_hsf_hi, off_hsf_lo; /* quantised gate-up output, same order */
+  int64_t off_xq;            /* u8 [terms, Lmax, Hpad/2]  layer input as packed-FP4 terms, sorted order */
+  int64_t off_xsf;           /* E8M0 scale chunks of xq                                      */
+  int64_t off_hq;            /* u8 [terms, Lmax, Ipad/2]  gate-up output, same form           */
+  int64_t off_hsf;           /* E8M0 scale chunks of hq                                      */
   int64_t off_out2;          /* bf16 [Lmax, H]  down-projection rows in sorted order         */
 } b200moe_workspace;
 
@@ -59,18 +64,17 @@ const char* b200moe_last_error(void);
 /* Fills *ws for `shape`.  Pure host arithmetic. */
 int b200moe_workspace_layout(const b200moe_shape* shape, b200moe_workspace* ws);
 
-/* Bytes of the prepared (device-layout) image of one weight tensor: which = 1 (w1, [E,2I,H]) or
- * 2 (w2, [E,H,I]); *data_bytes for the element image, *scale_bytes for the scale image. */
-int b200moe_prepared_bytes(const b200moe_shape* shape, int which, int64_t* data_bytes, int64_t* scale_bytes);
+/* Bytes of the prepared scale image of one weight tensor: which = 1 (w1, [E,2I,H]) or
+ * 2 (w2, [E,H,I]). */
+int b200moe_prepared_scale_bytes(const b200moe_shape* shape, int which, int64_t* scale_bytes);
 
-/* One-off repack of canonical weights into the layout the GEMMs stream (K padded to 128 with
- * zero codes; scales regrouped into 128-row x 4-scale chunks in tensor-memory order).  Plays the
- * part of the reference's pre-shuffle (src/misc.py:114-128, tests/contrib/moe/test_moe.py:167-172).
- *   w_q   : u8  [E, R, Kd/2]   (R = 2I, Kd = H for which=1; R = H, Kd = I for which=2)
- *   w_s   : u8  [E, R, Kd/32]
- */
-int b200moe_prepare_weights(const b200moe_shape* shape, int which, const void* w_q, const void* w_s,
-                            void* out_data, void* out_scale, void* stream);
+/* One-off regrouping of a weight tensor's E8M0 scales into 128-row x 4-scale chunks in
+ * tensor-memory order (the packed FP4 weights themselves are consumed in place, in their canonical
+ * [E, R, Kd/2] layout).  Plays the part of the reference's e8m0_shuffle / shuffle_weight
+ * pre-shuffle (src/misc.py:114-128, tests/contrib/moe/test_moe.py:167-172).
+ *   w_s : u8 [E, R, Kd/32]   (R = 2I, Kd = H for which=1; R = H, Kd = I for which=2) */
+int b200moe_prepare_scales(const b200moe_shape* shape, int which, const void* w_s, void* out_scale,
+                           void* stream);
 
 /* Token->expert sort/align: replaces aiter.moe_sorting as called at src/contrib/fused_moe.py:283,
  * 301-305 and 368-372 (contract: fused_moe.py:56-100; ck_tile reference_moe_sorting.hpp:14-117).
@@ -81,30 +85,33 @@ int b200moe_sort_align(const int32_t* topk_ids, const float* topk_weight, int32_
                        float* sorted_weights, int32_t* sorted_expert_ids, int32_t* num_valid_ids,
                        int32_t* loc, void* stream);
 
-/* Quantise bf16 rows into the two-term e4m3 + E8M0/32 operand format, gathered into sorted-row
- * order (stands where the reference calls aiter's per_1x32 activation quantiser followed by
- * moe_mxfp4_sort, tests/contrib/moe/test_moe.py:665-679).
+/* Quantise bf16 rows into `terms` packed-FP4 (E2M1) terms with E8M0 scales per 32, gathered into
+ * sorted-row order (stands where the reference calls aiter's per_1x32 activation quantiser
+ * followed by moe_mxfp4_sort, tests/contrib/moe/test_moe.py:665-679).
  *   src_mode 0: src is [T, Kd], row = token.   src_mode 1: src is [T, K, Kd], row = token*K + k.
- *   q_*: e4m3 [max_rows, Kd padded to 128]; sf_*: one 512-byte scale chunk per (block of B sorted
- *   rows, 128-wide k-block), row r of the block and scale j at byte (r%32)*16 + (r/32)*4 + j. */
+ *   consumer: 2 if the rows feed the gate-up GEMM, 1 if they feed the down GEMM (selects the
+ *   scale-chunk grouping that GEMM expects).
+ *   q: u8 [terms, max_rows, Kpad/2], Kpad = Kd rounded up to 128.  sf: per (block of B sorted
+ *   rows, 128-wide k-block) a group of 512-byte chunks. */
 int b200moe_quant_rows(const void* src_bf16, int32_t src_mode, const uint32_t* sorted_ids,
                        const int32_t* num_valid_ids, int32_t T, int32_t K, int32_t Kd, int32_t B,
-                       int64_t max_rows, void* q_hi, void* q_lo, void* sf_hi, void* sf_lo, void* stream);
+                       int32_t terms, int32_t consumer, int64_t max_rows, void* q, void* sf, void* stream);
 
 /* Gate-up grouped GEMM + activation: replaces moe_2stage_splitk(with_silu=True) /
  * moe_gemm_mxfp4(gate_up=True) (src/contrib/moe.py:362-702, src/contrib/moe_gemm_mxfp4.py:972-1290).
- * Consumes the quantised rows in workspace (xq_*), the prepared w1 image and the sort arrays.
+ * Consumes the quantised rows in workspace (xq), the canonical packed w1 [E,2I,H/2], its prepared
+ * scale image and the sort arrays.
  *   h_out != NULL : bf16 [T, K, I] scattered by (token,k) like the reference (moe.py:651-655)
- *   h_out == NULL : the result is re-quantised in sorted-row order into workspace hq_* for
+ *   h_out == NULL : the result is re-quantised in sorted-row order into workspace hq for
  *                   b200moe_down (fused path). */
 int b200moe_gateup(const b200moe_shape* shape, const b200moe_workspace* ws, void* workspace,
-                   const void* w1_data, const void* w1_scale, void* h_out, void* stream);
+                   const void* w1_q, const void* w1_scale_prepared, void* h_out, void* stream);
 
 /* Down grouped GEMM: replaces moe_2stage_splitk(with_silu=False) / moe_gemm_mxfp4(gate_up=False)
- * (src/contrib/moe.py:703-787, src/contrib/moe_gemm_mxfp4.py:1291-1398).  Reads workspace hq_*,
+ * (src/contrib/moe.py:703-787, src/contrib/moe_gemm_mxfp4.py:1291-1398).  Reads workspace hq,
  * writes bf16 rows in sorted order to workspace out2. */
 int b200moe_down(const b200moe_shape* shape, const b200moe_workspace* ws, void* workspace,
-                 const void* w2_data, const void* w2_scale, void* stream);
+                 const void* w2_q, const void* w2_scale_prepared, void* stream);
 
 /* Weighted combine back to token order: y[t] = sum_k w[t,k] * out2[loc[t,k]] accumulated in bf16
  * in ascending expert order, the order of the reference's torch oracle
@@ -117,15 +124,15 @@ int b200moe_combine(const b200moe_shape* shape, const b200moe_workspace* ws, voi
  * Replaces the body of pyhip.contrib.fused_moe.fused_moe (src/contrib/fused_moe.py:268-576). */
 int b200moe_forward(const b200moe_shape* shape, const b200moe_workspace* ws, void* workspace,
                     const void* x_bf16, const int32_t* topk_ids, const float* topk_weight,
-                    const int32_t* expert_mask, const void* w1_data, const void* w1_scale,
-                    const void* w2_data, const void* w2_scale, void* y_bf16, void* stream);
+                    const int32_t* expert_mask, const void* w1_q, const void* w1_scale_prepared,
+                    const void* w2_q, const void* w2_scale_prepared, void* y_bf16, void* stream);
 
 /* Hardware known-answer probes used by the GPU test-suite (tiny, single CTA, bounded waits).
- *   which = 1: TMA load of one 128x128 FP4 tile (16-byte-aligned unpacking, 128-byte swizzle)
- *              from `in` (8192 bytes) -> `out` receives the 16384-byte shared-memory image.
+ *   which = 1: TMA load of one 128x128 packed-FP4 tile (64-byte swizzle) from `in` (8192 bytes)
+ *              -> `out` receives the 8192-byte shared-memory image.
  *   which = 2: 512 bytes `in` -> shared -> tcgen05.cp 32x128b.warpx4 -> tcgen05.ld;
  *              `out` receives u32 [128 lanes][4 columns].
- *   which = 3: tensor-core issue-rate measurement; `in` = i32 {kind (0 mxf8f6f4, 1 mxf4), N,
+ *   which = 3: tensor-core issue-rate measurement (kind::mxf4, 128 x N x 64); `in` = i32 {0, N,
  *              count, accumulators}; `out` = u32 {issue cycles, cycles until complete, status}.
  * out[last] status word: 0 = ok, non-zero = a bounded wait ran out. */
 int b200moe_debug_probe(int which, const void* in, void* out, void* stream);

@@ -221,47 +221,44 @@ def moe_gemm_oracle(topk: int, block_m: int, sorted_ids, sorted_expert_ids, sort
 
 
 # --------------------------------------------------------------------------------------
-# activation quantiser used by the sm_100a kernels (two-term e4m3 with per-32 E8M0 scales)
+# activation quantiser used by the sm_100a kernels (sum of packed-FP4 terms, E8M0 scale per 32)
 # --------------------------------------------------------------------------------------
-def _floor_log2_biased(a: np.ndarray) -> np.ndarray:
+def _biased_exponent(a: np.ndarray) -> np.ndarray:
     """Biased exponent field of float32 ``a`` (= floor(log2 a)+127 for normal a)."""
     return ((a.astype(np.float32).view(np.uint32) >> 23) & 0xFF).astype(np.int32)
 
 
-def _e4m3_round(v: np.ndarray) -> np.ndarray:
-    t = torch.from_numpy(np.ascontiguousarray(v, dtype=np.float32)).clamp(-448.0, 448.0)
-    return t.to(torch.float8_e4m3fn)
+def _e2m1_rne(v: np.ndarray) -> np.ndarray:
+    """float32 -> E2M1 code (round to nearest, ties to the even code, saturating at 6; the sign
+    bit is kept even when the magnitude rounds to zero)."""
+    a = np.abs(v)
+    code = ((a > 0.25).astype(np.uint8) + (a >= 0.75) + (a > 1.25) + (a >= 1.75) + (a > 2.5)
+            + (a >= 3.5) + (a > 5.0)).astype(np.uint8)
+    return code | (np.signbit(v).astype(np.uint8) << 3)
 
 
-def hilo8_quant(x: torch.Tensor):
-    """Restatement of the device activation quantiser: per 32 along K,
-    e = max(biased_exponent(amax) - 7, 0), q = e4m3_rne(x * 2**(127-e)); the residual
-    x - q*2**(e-127) is quantised the same way.  Returns
-    (q_hi, e_hi, q_lo, e_lo) with q_* float8_e4m3fn [..., K] and e_* uint8 [..., K/32]."""
+def fp4_terms_quant(x: torch.Tensor, terms: int = 3):
+    """Restatement of the device activation quantiser.  Per 32 along K and per term t:
+    e = max(biased_exponent(amax(r)) - 2, 0), code = e2m1_rne(r * 2**(127-e)),
+    r <- r - value(code) * 2**(e-127), starting from r = x.
+    Returns (codes uint8 [terms, ..., K], exps uint8 [terms, ..., K/32])."""
     xf = x.float().numpy()
     K = xf.shape[-1]
-    blk = xf.reshape(xf.shape[:-1] + (K // 32, 32))
-
-    def one(b):
-        amax = np.abs(b).max(axis=-1)
-        e = np.maximum(_floor_log2_biased(amax) - 7, 0)
+    r = xf.reshape(xf.shape[:-1] + (K // 32, 32)).copy()
+    codes, exps = [], []
+    for _ in range(terms):
+        amax = np.abs(r).max(axis=-1)
+        e = np.maximum(_biased_exponent(amax) - 2, 0)
         inv = np.ldexp(np.float32(1.0), 127 - e).astype(np.float32)
-        q = _e4m3_round(b * inv[..., None])
-        deq = q.float().numpy() * np.ldexp(np.float32(1.0), e - 127).astype(np.float32)[..., None]
-        return q, e.astype(np.uint8), deq
-
-    q_hi, e_hi, d_hi = one(blk)
-    q_lo, e_lo, _ = one(blk - d_hi)
-    shp = xf.shape
-    return (q_hi.reshape(shp), torch.from_numpy(e_hi), q_lo.reshape(shp), torch.from_numpy(e_lo))
+        c = _e2m1_rne(r * inv[..., None])
+        r = r - _E2M1[c] * np.ldexp(np.float32(1.0), e - 127).astype(np.float32)[..., None]
+        codes.append(c.reshape(xf.shape))
+        exps.append(e.astype(np.uint8))
+    return np.stack(codes), np.stack(exps)
 
 
-def hilo8_dequant(q_hi, e_hi, q_lo, e_lo) -> torch.Tensor:
-    K = q_hi.shape[-1]
-
-    def one(q, e):
-        s = np.ldexp(np.float32(1.0), e.numpy().astype(np.int32) - 127).astype(np.float32)
-        v = q.float().numpy().reshape(q.shape[:-1] + (K // 32, 32)) * s[..., None]
-        return v.reshape(q.shape)
-
-    return torch.from_numpy(one(q_hi, e_hi) + one(q_lo, e_lo))
+def fp4_terms_dequant(codes: np.ndarray, exps: np.ndarray) -> torch.Tensor:
+    K = codes.shape[-1]
+    v = _E2M1[codes].reshape(codes.shape[:-1] + (K // 32, 32))
+    v = v * np.ldexp(np.float32(1.0), exps.astype(np.int32) - 127).astype(np.float32)[..., None]
+    return torch.from_numpy(v.reshape(codes.shape).sum(axis=0))

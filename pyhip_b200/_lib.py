@@ -30,12 +30,12 @@ class Shape(ctypes.Structure):
     _fields_ = [("T", ctypes.c_int32), ("K", ctypes.c_int32), ("E", ctypes.c_int32),
                 ("E_route", ctypes.c_int32), ("H", ctypes.c_int32), ("I", ctypes.c_int32),
                 ("B", ctypes.c_int32), ("weight_format", ctypes.c_int32),
-                ("activation", ctypes.c_int32), ("swiglu_limit", ctypes.c_float)]
+                ("activation", ctypes.c_int32), ("swiglu_limit", ctypes.c_float),
+                ("act_terms", ctypes.c_int32)]
 
 
 _WS_FIELDS = ["total_bytes", "max_rows", "off_sorted_ids", "off_sorted_w", "off_sorted_e",
-              "off_num_valid", "off_loc", "off_status", "off_xq_hi", "off_xq_lo", "off_xsf_hi",
-              "off_xsf_lo", "off_hq_hi", "off_hq_lo", "off_hsf_hi", "off_hsf_lo", "off_out2"]
+              "off_num_valid", "off_loc", "off_status", "off_xq", "off_xsf", "off_hq", "off_hsf", "off_out2"]
 
 
 class Workspace(ctypes.Structure):
@@ -43,7 +43,7 @@ class Workspace(ctypes.Structure):
 
 
 EXPORTS = ["b200moe_version", "b200moe_last_error", "b200moe_workspace_layout",
-           "b200moe_prepared_bytes", "b200moe_prepare_weights", "b200moe_sort_align",
+           "b200moe_prepared_scale_bytes", "b200moe_prepare_scales", "b200moe_sort_align",
            "b200moe_quant_rows", "b200moe_gateup", "b200moe_down", "b200moe_combine",
            "b200moe_forward", "b200moe_debug_probe"]
 
@@ -77,10 +77,10 @@ def lib() -> ctypes.CDLL:
     L.b200moe_version.restype = ctypes.c_int
     L.b200moe_last_error.restype = ctypes.c_char_p
     L.b200moe_workspace_layout.argtypes = [sp, wp]
-    L.b200moe_prepared_bytes.argtypes = [sp, ctypes.c_int, ctypes.POINTER(i64), ctypes.POINTER(i64)]
-    L.b200moe_prepare_weights.argtypes = [sp, ctypes.c_int, vp, vp, vp, vp, vp]
+    L.b200moe_prepared_scale_bytes.argtypes = [sp, ctypes.c_int, ctypes.POINTER(i64)]
+    L.b200moe_prepare_scales.argtypes = [sp, ctypes.c_int, vp, vp, vp]
     L.b200moe_sort_align.argtypes = [vp, vp, i32, i32, i32, i32, vp, vp, vp, vp, vp, vp, vp]
-    L.b200moe_quant_rows.argtypes = [vp, i32, vp, vp, i32, i32, i32, i32, i64, vp, vp, vp, vp, vp]
+    L.b200moe_quant_rows.argtypes = [vp, i32, vp, vp, i32, i32, i32, i32, i32, i32, i64, vp, vp, vp]
     L.b200moe_gateup.argtypes = [sp, wp, vp, vp, vp, vp, vp]
     L.b200moe_down.argtypes = [sp, wp, vp, vp, vp, vp]
     L.b200moe_combine.argtypes = [sp, wp, vp, vp, vp, vp]

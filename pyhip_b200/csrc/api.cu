@@ -32,10 +32,13 @@ static int check_shape(const b200moe_shape* s) {
                  s->weight_format);
   B200_CHECK_ARG(s->activation == B200MOE_ACT_SILU || s->activation == B200MOE_ACT_SWIGLU,
                  "activation %d unknown", s->activation);
+  B200_CHECK_ARG(s->act_terms == 0 || (s->act_terms >= 2 && s->act_terms <= 4), "act_terms=%d not in {0,2,3,4}",
+                 s->act_terms);
   return 0;
 }
 
 static int64_t kp_of(int k) { return round_up64(k, 128); }
+static int terms_of(const b200moe_shape* s) { return s->act_terms == 0 ? 3 : s->act_terms; }
 
 }  // namespace b200moe
 
@@ -50,10 +53,11 @@ const char* b200moe_last_error(void) { return g_err; }
 int b200moe_workspace_layout(const b200moe_shape* s, b200moe_workspace* ws) {
   if (int rc = check_shape(s)) return rc;
   B200_CHECK_ARG(ws != nullptr, "workspace descriptor is NULL");
+  const int NT = terms_of(s);
   const int64_t P = (int64_t)s->T * s->K;
   const int64_t nblk = (P + (int64_t)s->E_route * (s->B - 1) + s->B - 1) / s->B;
   const int64_t L = std::max<int64_t>(nblk, 1) * s->B;
-  const int64_t nb = L / s->B;   // one scale chunk per sorted block and k-block
+  const int64_t nb = L / s->B;   // one scale chunk group per sorted block and k-block
   const int64_t HP = kp_of(s->H), IP = kp_of(s->I);
   int64_t off = 0;
   auto take = [&](int64_t bytes) {
@@ -69,47 +73,35 @@ int b200moe_workspace_layout(const b200moe_shape* s, b200moe_workspace* ws) {
   ws->off_num_valid = take(8);
   ws->off_loc = take(std::max<int64_t>(P, 1) * 4);
   ws->off_status = take(64);
-  ws->off_xq_hi = take(L * HP);
-  ws->off_xq_lo = take(L * HP);
-  ws->off_xsf_hi = take(nb * (HP / 128) * kSfChunk);
-  ws->off_xsf_lo = take(nb * (HP / 128) * kSfChunk);
-  ws->off_hq_hi = take(L * IP);
-  ws->off_hq_lo = take(L * IP);
-  ws->off_hsf_hi = take(nb * (IP / 128) * kSfChunk);
-  ws->off_hsf_lo = take(nb * (IP / 128) * kSfChunk);
+  ws->off_xq = take(NT * L * (HP / 2));
+  ws->off_xsf = take(nb * (HP / 128) * act_sf_chunks(NT, act_term_stride(s->B, NT, 2)) * kSfChunk);
+  ws->off_hq = take(NT * L * (IP / 2));
+  ws->off_hsf = take(nb * (IP / 128) * act_sf_chunks(NT, act_term_stride(s->B, NT, 1)) * kSfChunk);
   ws->off_out2 = take(L * s->H * 2);
   ws->total_bytes = off;
   return 0;
 }
 
-int b200moe_prepared_bytes(const b200moe_shape* s, int which, int64_t* data_bytes, int64_t* scale_bytes) {
+int b200moe_prepared_scale_bytes(const b200moe_shape* s, int which, int64_t* scale_bytes) {
   if (int rc = check_shape(s)) return rc;
   B200_CHECK_ARG(which == 1 || which == 2, "which=%d must be 1 or 2", which);
+  B200_CHECK_ARG(scale_bytes != nullptr, "scale_bytes is NULL");
   const int parts = which == 1 ? 2 : 1;
   const int rpp = which == 1 ? s->I : s->H;
   const int Kd = which == 1 ? s->H : s->I;
-  const int64_t KP = kp_of(Kd);
-  if (data_bytes) *data_bytes = (int64_t)s->E * parts * rpp * (KP / 2) + 256;
-  if (scale_bytes) *scale_bytes = (int64_t)s->E * parts * ((rpp + 127) / 128) * (KP / 128) * kSfChunk;
+  *scale_bytes = (int64_t)s->E * parts * ((rpp + 127) / 128) * (kp_of(Kd) / 128) * kSfChunk;
   return 0;
 }
 
-int b200moe_prepare_weights(const b200moe_shape* s, int which, const void* w_q, const void* w_s, void* out_data,
-                            void* out_scale, void* stream) {
+int b200moe_prepare_scales(const b200moe_shape* s, int which, const void* w_s, void* out_scale, void* stream) {
   if (int rc = check_shape(s)) return rc;
   B200_CHECK_ARG(which == 1 || which == 2, "which=%d must be 1 or 2", which);
-  B200_CHECK_ARG(w_q && w_s && out_data && out_scale, "prepare_weights: NULL pointer");
-  B200_CHECK_ARG(((uintptr_t)out_data & 31) == 0 && ((uintptr_t)out_scale & 15) == 0,
-                 "prepare_weights: output buffers must be 32-byte aligned");
-  cudaStream_t st = (cudaStream_t)stream;
+  B200_CHECK_ARG(w_s && out_scale, "prepare_scales: NULL pointer");
+  B200_CHECK_ARG(((uintptr_t)out_scale & 15) == 0, "prepare_scales: output must be 16-byte aligned");
   const int parts = which == 1 ? 2 : 1;
   const int rpp = which == 1 ? s->I : s->H;
   const int Kd = which == 1 ? s->H : s->I;
-  const int64_t KP = kp_of(Kd);
-  const int64_t rows = (int64_t)s->E * parts * rpp;
-  if (KP != Kd) B200_CHECK_CUDA(cudaMemsetAsync(out_data, 0, rows * (KP / 2) + 256, st));
-  B200_CHECK_CUDA(cudaMemcpy2DAsync(out_data, KP / 2, w_q, Kd / 2, Kd / 2, rows, cudaMemcpyDeviceToDevice, st));
-  return launch_repack_scales(w_s, out_scale, s->E, parts, rpp, Kd, st);
+  return launch_repack_scales(w_s, out_scale, s->E, parts, rpp, Kd, (cudaStream_t)stream);
 }
 
 int b200moe_sort_align(const int32_t* topk_ids, const float* topk_weight, int32_t T, int32_t K, int32_t E_route,
@@ -124,18 +116,21 @@ int b200moe_sort_align(const int32_t* topk_ids, const float* topk_weight, int32_
 }
 
 int b200moe_quant_rows(const void* src_bf16, int32_t src_mode, const uint32_t* sorted_ids,
-                       const int32_t* num_valid_ids, int32_t T, int32_t K, int32_t Kd, int32_t B, int64_t max_rows,
-                       void* q_hi, void* q_lo, void* sf_hi, void* sf_lo, void* stream) {
+                       const int32_t* num_valid_ids, int32_t T, int32_t K, int32_t Kd, int32_t B, int32_t terms,
+                       int32_t consumer, int64_t max_rows, void* q, void* sf, void* stream) {
   B200_CHECK_ARG(src_mode == 0 || src_mode == 1, "quant_rows: src_mode=%d", src_mode);
-  B200_CHECK_ARG(sorted_ids && num_valid_ids && q_hi && q_lo && sf_hi && sf_lo, "quant_rows: NULL pointer");
+  B200_CHECK_ARG(consumer == 1 || consumer == 2, "quant_rows: consumer=%d must be 1 (down) or 2 (gate-up)", consumer);
+  B200_CHECK_ARG(sorted_ids && num_valid_ids && q && sf, "quant_rows: NULL pointer");
   B200_CHECK_ARG(T == 0 || src_bf16, "quant_rows: NULL source");
-  B200_CHECK_ARG(((uintptr_t)src_bf16 & 15) == 0, "quant_rows: source must be 16-byte aligned");
-  return launch_quant_rows(src_bf16, src_mode, sorted_ids, num_valid_ids, T, K, Kd, B, max_rows, q_hi, q_lo, sf_hi,
-                           sf_lo, (cudaStream_t)stream);
+  B200_CHECK_ARG(((uintptr_t)src_bf16 & 15) == 0 && ((uintptr_t)q & 15) == 0,
+                 "quant_rows: source and destination must be 16-byte aligned");
+  return launch_quant_rows(src_bf16, src_mode, sorted_ids, num_valid_ids, T, K, Kd, B, terms, consumer, max_rows, q,
+                           sf, (cudaStream_t)stream);
 }
 
 static void fill_common(GemmArgs& g, const b200moe_shape* s, const b200moe_workspace* ws, uint8_t* base) {
   g.N = s->B;
+  g.NT = terms_of(s);
   g.E = s->E;
   g.topk = s->K;
   g.T = s->T;
@@ -148,10 +143,10 @@ static void fill_common(GemmArgs& g, const b200moe_shape* s, const b200moe_works
   g.status = (int32_t*)(base + ws->off_status);
 }
 
-int b200moe_gateup(const b200moe_shape* s, const b200moe_workspace* ws, void* workspace, const void* w1_data,
+int b200moe_gateup(const b200moe_shape* s, const b200moe_workspace* ws, void* workspace, const void* w1_q,
                    const void* w1_scale, void* h_out, void* stream) {
   if (int rc = check_shape(s)) return rc;
-  B200_CHECK_ARG(ws && workspace && w1_data && w1_scale, "gateup: NULL pointer");
+  B200_CHECK_ARG(ws && workspace && w1_q && w1_scale, "gateup: NULL pointer");
   B200_CHECK_ARG(((uintptr_t)workspace & 1023) == 0, "gateup: workspace must be 1024-byte aligned");
   uint8_t* base = (uint8_t*)workspace;
   GemmArgs g = {};
@@ -159,25 +154,21 @@ int b200moe_gateup(const b200moe_shape* s, const b200moe_workspace* ws, void* wo
   g.gateup = true;
   g.rows = s->I;
   g.Kd = s->H;
-  g.w_data = w1_data;
+  g.w_data = w1_q;
   g.w_scale = w1_scale;
-  g.a_hi = base + ws->off_xq_hi;
-  g.a_lo = base + ws->off_xq_lo;
-  g.asf_hi = base + ws->off_xsf_hi;
-  g.asf_lo = base + ws->off_xsf_lo;
+  g.a_q = base + ws->off_xq;
+  g.asf = base + ws->off_xsf;
   g.h_out = h_out;
-  g.oq_hi = base + ws->off_hq_hi;
-  g.oq_lo = base + ws->off_hq_lo;
-  g.osf_hi = base + ws->off_hsf_hi;
-  g.osf_lo = base + ws->off_hsf_lo;
+  g.oq = base + ws->off_hq;
+  g.osf = base + ws->off_hsf;
   g.out_kp = (int)kp_of(s->I);
   return launch_grouped_gemm(g, (cudaStream_t)stream);
 }
 
-int b200moe_down(const b200moe_shape* s, const b200moe_workspace* ws, void* workspace, const void* w2_data,
+int b200moe_down(const b200moe_shape* s, const b200moe_workspace* ws, void* workspace, const void* w2_q,
                  const void* w2_scale, void* stream) {
   if (int rc = check_shape(s)) return rc;
-  B200_CHECK_ARG(ws && workspace && w2_data && w2_scale, "down: NULL pointer");
+  B200_CHECK_ARG(ws && workspace && w2_q && w2_scale, "down: NULL pointer");
   B200_CHECK_ARG(((uintptr_t)workspace & 1023) == 0, "down: workspace must be 1024-byte aligned");
   uint8_t* base = (uint8_t*)workspace;
   GemmArgs g = {};
@@ -185,12 +176,10 @@ int b200moe_down(const b200moe_shape* s, const b200moe_workspace* ws, void* work
   g.gateup = false;
   g.rows = s->H;
   g.Kd = s->I;
-  g.w_data = w2_data;
+  g.w_data = w2_q;
   g.w_scale = w2_scale;
-  g.a_hi = base + ws->off_hq_hi;
-  g.a_lo = base + ws->off_hq_lo;
-  g.asf_hi = base + ws->off_hsf_hi;
-  g.asf_lo = base + ws->off_hsf_lo;
+  g.a_q = base + ws->off_hq;
+  g.asf = base + ws->off_hsf;
   g.out2 = base + ws->off_out2;
   return launch_grouped_gemm(g, (cudaStream_t)stream);
 }
@@ -207,7 +196,7 @@ int b200moe_combine(const b200moe_shape* s, const b200moe_workspace* ws, void* w
 
 int b200moe_forward(const b200moe_shape* s, const b200moe_workspace* ws, void* workspace, const void* x_bf16,
                     const int32_t* topk_ids, const float* topk_weight, const int32_t* expert_mask,
-                    const void* w1_data, const void* w1_scale, const void* w2_data, const void* w2_scale,
+                    const void* w1_q, const void* w1_scale, const void* w2_q, const void* w2_scale,
                     void* y_bf16, void* stream) {
   if (int rc = check_shape(s)) return rc;
   B200_CHECK_ARG(ws && workspace, "forward: NULL workspace");
@@ -220,13 +209,12 @@ int b200moe_forward(const b200moe_shape* s, const b200moe_workspace* ws, void* w
                               (int32_t*)(base + ws->off_loc), stream);
   if (rc) return rc;
   rc = b200moe_quant_rows(x_bf16, 0, (const uint32_t*)(base + ws->off_sorted_ids),
-                          (const int32_t*)(base + ws->off_num_valid), s->T, s->K, s->H, s->B, ws->max_rows,
-                          base + ws->off_xq_hi, base + ws->off_xq_lo, base + ws->off_xsf_hi, base + ws->off_xsf_lo,
-                          stream);
+                          (const int32_t*)(base + ws->off_num_valid), s->T, s->K, s->H, s->B, terms_of(s), 2,
+                          ws->max_rows, base + ws->off_xq, base + ws->off_xsf, stream);
   if (rc) return rc;
-  rc = b200moe_gateup(s, ws, workspace, w1_data, w1_scale, nullptr, stream);
+  rc = b200moe_gateup(s, ws, workspace, w1_q, w1_scale, nullptr, stream);
   if (rc) return rc;
-  rc = b200moe_down(s, ws, workspace, w2_data, w2_scale, stream);
+  rc = b200moe_down(s, ws, workspace, w2_q, w2_scale, stream);
   if (rc) return rc;
   return b200moe_combine(s, ws, workspace, topk_weight, y_bf16, stream);
 }

@@ -29,13 +29,33 @@ constexpr int kSfChunk = 512;
 __host__ __device__ static inline int sf_chunk_offset(int row_in_128, int j) {
   return (row_in_128 & 31) * 16 + (row_in_128 >> 5) * 4 + j;
 }
+// Activation operand layout, shared by the quantisers and the GEMM that consumes their output.
+// NT terms per row.  "Merged": the terms of a block are stacked along the MMA's N (one
+// instruction, N = NT*B) -- possible when that fits an instruction (<= 256) and two accumulator
+// buffers of `parts` tiles fit tensor memory; otherwise every term is its own instruction.
+// Scales: per (sorted block, 128-wide k-block) a group of 512-byte chunks; term t, block-local
+// row r sit at virtual row v = t*TS + r (TS = B when merged, 128 otherwise): chunk v/128.
+constexpr int kAccColsLimit = 448;
+__host__ __device__ static inline bool act_merged(int B, int NT, int parts) {
+  return NT * B <= 256 && 2 * parts * NT * B <= kAccColsLimit;
+}
+__host__ __device__ static inline int act_term_stride(int B, int NT, int parts) {
+  return act_merged(B, NT, parts) ? B : 128;
+}
+__host__ __device__ static inline int act_sf_chunks(int NT, int TS) { return (NT * TS + 127) / 128; }
+__host__ __device__ static inline int64_t act_sf_index(int64_t block, int kb, int KB, int B, int NT, int TS,
+                                                       int term, int r, int j) {
+  (void)B;
+  const int v = term * TS + r;
+  return ((block * KB + kb) * act_sf_chunks(NT, TS) + (v >> 7)) * kSfChunk + sf_chunk_offset(v & 127, j);
+}
 
 // launchers (moe_aux.cu)
 int launch_sort_align(const int32_t* ids, const float* w, int T, int K, int E, int B, const int32_t* mask,
                       uint32_t* sorted_ids, float* sorted_w, int32_t* sorted_e, int32_t* num_valid,
                       int32_t* loc, cudaStream_t st);
 int launch_quant_rows(const void* src, int src_mode, const uint32_t* sorted_ids, const int32_t* num_valid,
-                      int T, int K, int Kd, int B, int64_t max_rows, void* q_hi, void* q_lo, void* sf_hi, void* sf_lo,
+                      int T, int K, int Kd, int B, int NT, int parts, int64_t max_rows, void* q, void* sf,
                       cudaStream_t st);
 int launch_combine(const void* out2, const int32_t* loc, const float* topk_w, void* y, int T, int K, int H,
                    cudaStream_t st);
@@ -53,19 +73,18 @@ struct GemmArgs {
   int activation;
   float swiglu_limit;
   int64_t max_rows;
-  const void* w_data;  // [E, parts*rows, KP/2]
-  const void* w_scale; // [E, parts, MT, KB, 512]
-  const void* a_hi;    // [max_rows, KP] e4m3
-  const void* a_lo;
-  const void* asf_hi;  // [max_rows/N, KB, 512], rows block-local
-  const void* asf_lo;
+  int NT;              // activation terms
+  const void* w_data;  // canonical packed FP4 [E, parts*rows, Kd/2], used in place
+  const void* w_scale; // [E, MT, KB, parts, 512]
+  const void* a_q;     // [NT, max_rows, KP/2] packed FP4 terms
+  const void* asf;     // [max_rows/N, KB, chunks, 512]
   const uint32_t* sorted_ids;
   const int32_t* sorted_e;
   const int32_t* num_valid;
   int32_t* status;
   // outputs
   void* h_out;         // gate-up: bf16 [T, topk, I] or null
-  void* oq_hi; void* oq_lo; void* osf_hi; void* osf_lo;   // gate-up fused re-quantisation
+  void* oq; void* osf;   // gate-up fused re-quantisation ([NT, max_rows, out_kp/2] + scale chunks)
   int out_kp;          // row pitch of oq_* (I padded to 128) and chunk count per row block
   void* out2;          // down: bf16 [max_rows, H]
 };

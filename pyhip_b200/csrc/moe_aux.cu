@@ -1,6 +1,7 @@
 // Integer / byte kernels around the grouped GEMMs: token->expert sort/align, activation
 // quantise-and-gather, scale repack, weighted combine.  All HBM- or latency-bound.
 #include <cuda_bf16.h>
+#include <cuda_fp4.h>
 #include <cuda_fp8.h>
 
 #include "internal.h"
@@ -153,44 +154,49 @@ int launch_sort_align(const int32_t* ids, const float* w, int T, int K, int E, i
 }
 
 // =====================================================================================
-// activation quantiser: bf16 row -> two e4m3 terms with per-32 E8M0 scales, written in
-// sorted-row order.  One thread per 32-element block.
-//   e  = max(biased_exponent(amax) - 7, 0);  q = e4m3_rne(x * 2^(127-e));  r = x - q*2^(e-127)
-//   the residual r is quantised the same way (second term).
+// activation quantiser: bf16 row -> NT packed-FP4 (E2M1) terms with per-32 E8M0 scales, written
+// in sorted-row order.  One thread per 32-element block.  Term t quantises what the previous
+// terms left over:
+//   e = max(biased_exponent(amax(r)) - 2, 0);  q = e2m1_rne_sat(r * 2^(127-e));  r -= q * 2^(e-127)
+// (amax/2^(e-127) lies in [4,8): the OCP MX scale rule; values above 6 saturate and the next
+// term picks up the rest).  Three terms reproduce a bf16 input to ~2e-3 of the block maximum,
+// four terms to ~1e-4.
 // =====================================================================================
 __device__ __forceinline__ float pow2_from_biased(int e) {   // 2^(e-127), e in [0,254]
   return __uint_as_float(e == 0 ? 0x00400000u : ((uint32_t)e << 23));
 }
 
-__device__ __forceinline__ void quant_block32(const float (&x)[32], uint8_t (&q)[32], float (&resid)[32],
-                                              int& e_out) {
+// quantise 32 floats to E2M1 with a shared scale; q: 16 bytes (low nibble = even element);
+// x is replaced by the residual
+__device__ __forceinline__ int quant_block32_fp4(float (&x)[32], uint4& q) {
   float amax = 0.f;
 #pragma unroll
   for (int i = 0; i < 32; ++i) amax = fmaxf(amax, fabsf(x[i]));
-  int e = max((int)((__float_as_uint(amax) >> 23) & 0xFF) - 7, 0);
-  float inv = __uint_as_float((uint32_t)(254 - e) << 23);
-  float sc = pow2_from_biased(e);
+  const int e = max((int)((__float_as_uint(amax) >> 23) & 0xFF) - 2, 0);
+  const float inv = __uint_as_float((uint32_t)(254 - e) << 23);
+  const float sc = pow2_from_biased(e);
+  uint32_t w[4] = {0, 0, 0, 0};
 #pragma unroll
   for (int i = 0; i < 32; i += 2) {
-    float2 v = make_float2(x[i] * inv, x[i + 1] * inv);
-    __nv_fp8x2_storage_t p = __nv_cvt_float2_to_fp8x2(v, __NV_SATFINITE, __NV_E4M3);
-    q[i] = (uint8_t)(p & 0xFF);
-    q[i + 1] = (uint8_t)(p >> 8);
-    __half2_raw h = __nv_cvt_fp8x2_to_halfraw2(p, __NV_E4M3);
-    float2 f = __half22float2(*reinterpret_cast<__half2*>(&h));
-    resid[i] = x[i] - f.x * sc;
-    resid[i + 1] = x[i + 1] - f.y * sc;
+    const __nv_fp4x2_storage_t pk =
+        __nv_cvt_float2_to_fp4x2(make_float2(x[i] * inv, x[i + 1] * inv), __NV_E2M1, cudaRoundNearest);
+    w[i >> 3] |= (uint32_t)pk << (((i >> 1) & 3) * 8);
+    __half2_raw h = __nv_cvt_fp4x2_to_halfraw2(pk, __NV_E2M1);
+    const float2 f = __half22float2(*reinterpret_cast<__half2*>(&h));
+    x[i] -= f.x * sc;
+    x[i + 1] -= f.y * sc;
   }
-  e_out = e;
+  q = make_uint4(w[0], w[1], w[2], w[3]);
+  return e;
 }
 
 __global__ void __launch_bounds__(256)
 quant_rows_kernel(const __nv_bfloat16* __restrict__ src, int src_mode, const uint32_t* __restrict__ sorted_ids,
-                  const int32_t* __restrict__ num_valid, int T, int K, int Kd, int KP, int B, int64_t max_rows,
-                  uint8_t* __restrict__ q_hi, uint8_t* __restrict__ q_lo, uint8_t* __restrict__ sf_hi,
-                  uint8_t* __restrict__ sf_lo) {
+                  const int32_t* __restrict__ num_valid, int T, int K, int Kd, int KP, int B, int NT, int TS,
+                  int64_t max_rows, uint8_t* __restrict__ q, uint8_t* __restrict__ sf) {
   const int nb = KP / 32;
   const int KB = KP / 128;
+  const int64_t term_stride = max_rows * (KP / 2);
   const int64_t rows_live = min((int64_t)num_valid[0], max_rows);
   for (int64_t g = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; g < rows_live * nb;
        g += (int64_t)gridDim.x * blockDim.x) {
@@ -199,13 +205,10 @@ quant_rows_kernel(const __nv_bfloat16* __restrict__ src, int src_mode, const uin
     const uint32_t id = sorted_ids[r];
     const int tok = (int)(id & 0xFFFFFFu), kk = (int)(id >> 24);
     const bool valid = (kk < K) && (tok < T) && (j * 32 < Kd);
-    uint4 hi[2] = {}, lo[2] = {};
-    int e_hi = 0, e_lo = 0;
+    float x[32];
     if (valid) {
       const int64_t srow = (src_mode == 0) ? (int64_t)tok : ((int64_t)tok * K + kk);
       const uint4* p = reinterpret_cast<const uint4*>(src + srow * Kd + j * 32);
-      float x[32], r1[32], r2[32];
-      uint8_t qa[32], qb[32];
 #pragma unroll
       for (int v = 0; v < 4; ++v) {
         uint4 u = p[v];
@@ -217,35 +220,32 @@ quant_rows_kernel(const __nv_bfloat16* __restrict__ src, int src_mode, const uin
           x[v * 8 + t * 2 + 1] = f.y;
         }
       }
-      quant_block32(x, qa, r1, e_hi);
-      quant_block32(r1, qb, r2, e_lo);
-      memcpy(hi, qa, 32);
-      memcpy(lo, qb, 32);
+    } else {
+#pragma unroll
+      for (int i = 0; i < 32; ++i) x[i] = 0.f;
     }
-    uint4* dh = reinterpret_cast<uint4*>(q_hi + r * KP + j * 32);
-    uint4* dl = reinterpret_cast<uint4*>(q_lo + r * KP + j * 32);
-    dh[0] = hi[0]; dh[1] = hi[1];
-    dl[0] = lo[0]; dl[1] = lo[1];
-    // one 512-byte scale chunk per (sorted block, k-block); rows are block-local so that a
-    // block's scales start at TMEM lane 0 of a 4-column-aligned group
-    const int64_t chunk = ((r / B) * KB + (j >> 2)) * kSfChunk + sf_chunk_offset((int)(r % B), j & 3);
-    sf_hi[chunk] = (uint8_t)e_hi;
-    sf_lo[chunk] = (uint8_t)e_lo;
+    for (int t = 0; t < NT; ++t) {
+      uint4 pk;
+      const int e = quant_block32_fp4(x, pk);
+      *reinterpret_cast<uint4*>(q + t * term_stride + r * (KP / 2) + j * 16) = pk;
+      sf[act_sf_index(r / B, j >> 2, KB, B, NT, TS, t, (int)(r % B), j & 3)] = (uint8_t)e;
+    }
   }
 }
 
 int launch_quant_rows(const void* src, int src_mode, const uint32_t* sorted_ids, const int32_t* num_valid,
-                      int T, int K, int Kd, int B, int64_t max_rows, void* q_hi, void* q_lo, void* sf_hi, void* sf_lo,
+                      int T, int K, int Kd, int B, int NT, int parts, int64_t max_rows, void* q, void* sf,
                       cudaStream_t st) {
   B200_CHECK_ARG(B == 32 || B == 64 || B == 128, "quant_rows: B=%d not in {32,64,128}", B);
+  B200_CHECK_ARG(NT >= 2 && NT <= 4, "quant_rows: %d activation terms (2..4 supported)", NT);
   B200_CHECK_ARG(Kd % 32 == 0, "quant_rows: Kd=%d must be a multiple of 32", Kd);
   const int KP = (int)round_up64(Kd, 128);
   int64_t work = max_rows * (KP / 32);
   int blocks = (int)std::min<int64_t>((work + 255) / 256, 148 * 16);
   if (blocks < 1) blocks = 1;
   quant_rows_kernel<<<blocks, 256, 0, st>>>(reinterpret_cast<const __nv_bfloat16*>(src), src_mode, sorted_ids,
-                                            num_valid, T, K, Kd, KP, B, max_rows, (uint8_t*)q_hi, (uint8_t*)q_lo,
-                                            (uint8_t*)sf_hi, (uint8_t*)sf_lo);
+                                            num_valid, T, K, Kd, KP, B, NT, act_term_stride(B, NT, parts), max_rows,
+                                            (uint8_t*)q, (uint8_t*)sf);
   B200_CHECK_CUDA(cudaGetLastError());
   return 0;
 }
@@ -303,7 +303,7 @@ int launch_combine(const void* out2, const int32_t* loc, const float* topk_w, vo
 }
 
 // =====================================================================================
-// weight-scale repack: [E, parts*rows, Kd/32] bytes -> [E, parts, MT, KB, 512] chunks in
+// weight-scale repack: [E, parts*rows, Kd/32] bytes -> [E, MT, KB, parts, 512] chunks in
 // tensor-memory order; rows / k-blocks that do not exist get exponent 127 (= 1.0).
 // =====================================================================================
 __global__ void __launch_bounds__(256)
@@ -314,10 +314,10 @@ repack_scales_kernel(const uint8_t* __restrict__ src, uint8_t* __restrict__ dst,
        g += (int64_t)gridDim.x * blockDim.x) {
     int off = (int)(g % kSfChunk);
     int64_t c = g / kSfChunk;
+    int part = (int)(c % parts); c /= parts;
     int kb = (int)(c % KB); c /= KB;
-    int mt = (int)(c % MT); c /= MT;
-    int part = (int)(c % parts);
-    int e = (int)(c / parts);
+    int mt = (int)(c % MT);
+    int e = (int)(c / MT);
     int r_local = (off >> 4) + 32 * ((off & 15) >> 2);
     int j = off & 3;
     int row = mt * 128 + r_local, kidx = kb * 4 + j;

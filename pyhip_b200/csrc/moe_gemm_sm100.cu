@@ -1,22 +1,32 @@
-// Grouped GEMMs of the MoE layer on the sm_100a tensor cores.
+// Grouped GEMMs of the MoE layer on the sm_100a tensor cores: tcgen05.mma kind::mxf4 with
+// per-32 E8M0 block scales on both operands.
 //
 // Orientation ("swap-AB"): the MMA's M side holds 128 weight rows, its N side holds the token
-// tile of one sorted block (N = 32/64/128), so ragged token counts cost N-padding, never M.
-//     D[128 weight rows, N tokens] += W4[128, K] * A8[N, K]^T      (tcgen05.mma kind::mxf8f6f4)
-// W4: MXFP4 weights streamed by TMA straight from HBM (FP4 in memory, unpacked to the 16-byte
-//     aligned shared-memory form by the copy engine), E8M0 scale per 32 along K.
-// A8: activations as two e4m3 terms (value + residual), each with E8M0 scales per 32 along K;
-//     both terms accumulate into the same TMEM tile, which reproduces bf16 activations to
-//     ~2^-9 relative without any dequantisation arithmetic in the main loop.
-// Block scales travel shared memory -> tensor memory with tcgen05.cp and are consumed by the MMA.
+// tile of one sorted block (B = 32/64/128 rows), so ragged token counts cost N-padding, never M.
+//     D[128 weight rows, tokens] += W4[128, K] * A4[tokens, K]^T
+// W4: the MXFP4 weights exactly as they sit in HBM (packed E2M1, canonical layout, no repack):
+//     TMA brings 128x128 tiles into 64-byte-swizzled shared memory; the K tail (K not a multiple
+//     of 128) and the row tail are filled with zeros by the copy engine and never fetched.
+// A4: an activation row is a SUM of NT packed-FP4 terms (value, residual, residual of the
+//     residual ...), each with its own E8M0 scales per 32 along K.  Three terms carry a bf16
+//     activation to ~2e-3 of its block maximum, which keeps the layer within cosine 0.9999 of the
+//     bf16-activation oracle, while every product still runs at the FP4 tensor rate and nothing
+//     is dequantised in the main loop.  The terms of a block are stacked along N when they fit
+//     one instruction (N = NT*B <= 256; the epilogue adds the column groups), otherwise each term
+//     is its own instruction into the same accumulator.
+// Block scales travel shared memory -> tensor memory with tcgen05.cp and are applied by the MMA.
 //
 // Warp roles (192 threads): warp 0 = TMA producer, warp 1 = MMA issuer + TMEM owner,
 // warps 2-5 = epilogue (one TMEM lane quadrant each).  Persistent CTAs walk the work list
 // (sorted block, 128-row weight tile) in block-major order so that the CTAs running at the same
 // time share activation tiles and neighbouring blocks of an expert share weight tiles in L2.
+// The issuing threads are the scarce resource at small token tiles, so a pipeline stage is
+// four copy instructions (weights, activations, two scale groups) and descriptors are kept as
+// precomputed 32-bit halves.
 // All barrier waits are bounded; a wait that runs out sets status[] and the CTA unwinds
 // (frees its tensor memory) instead of spinning.
 #include <cuda_bf16.h>
+#include <cuda_fp4.h>
 #include <cuda_fp8.h>
 
 #include <algorithm>
@@ -29,28 +39,30 @@ namespace b200moe {
 
 constexpr int kThreads = 192;
 constexpr int kTileM = 128;          // weight rows per MMA
-constexpr int kTileK = 128;          // K per pipeline stage (4 MMA K-steps of 32)
-constexpr int kATileBytes = kTileM * kTileK;   // FP4 unpacked to one byte per element in shared memory
-constexpr int kATileTxBytes = kTileM * kTileK / 2;   // the copy engine counts the packed bytes it read
-constexpr int kMaxStages = 12;
+constexpr int kTileK = 128;          // K per pipeline stage (2 MMA K-steps of 64)
+constexpr int kRowBytes = kTileK / 2;                // one tile row: 128 packed FP4 = 64 bytes
+constexpr int kATileBytes = kTileM * kRowBytes;      // 8 KB
+constexpr int kMaxStages = 16;
+constexpr int kMaxTerms = 4;
 constexpr int kTmemCols = 512;
-constexpr int kSfCol0 = 448;         // scale columns: 2 buffers x {A0, A1, Bhi, Blo} x 4 columns
-constexpr int kSmemLimit = 232448;   // 227 KB
+constexpr int kSfCol0 = kAccColsLimit;   // scale columns: 2 buffers x {A: 8 columns, B: up to 16 columns}
+constexpr int kSmemLimit = 232448;       // 227 KB
 
 struct GemmParams {
-  CUtensorMap tmA0, tmA1, tmBhi, tmBlo;
-  const uint8_t* w_scale;
-  const uint8_t* asf_hi;
-  const uint8_t* asf_lo;
+  CUtensorMap tmW;     // weights     (K, rows, parts, E)         box (128, 128, parts, 1)
+  CUtensorMap tmA;     // activations (KP, max_rows, NT terms)    box (128, B, NT)
+  const uint8_t* w_scale;   // [E, MT, KB, parts, 512]
+  const uint8_t* asf;       // [blocks, KB, chunks, 512]
   const uint32_t* sorted_ids;
   const int32_t* sorted_e;
   const int32_t* num_valid;
   int32_t* status;
   __nv_bfloat16* h_out;
-  uint8_t* oq_hi; uint8_t* oq_lo; uint8_t* osf_hi; uint8_t* osf_lo;
+  uint8_t* oq; uint8_t* osf;
   __nv_bfloat16* out2;
   int64_t max_rows;
-  int N, rows, KB, MT, E, topk, T, parts, stages, out_kp, out_kb, activation;
+  int64_t oq_term_stride;
+  int B, NT, rows, KB, MT, E, topk, T, stages, out_kp, out_kb, out_ts, activation;
   float swiglu_limit;
 };
 
@@ -62,6 +74,22 @@ struct SmemCtl {
   uint32_t tmem_base;
   uint32_t abort_word;
 };
+
+// geometry shared by host and device
+struct StageGeom {
+  int a_bytes, b_bytes, sfa_bytes, sfb_bytes, stage_bytes;
+  uint32_t tx_bytes;
+};
+__host__ __device__ inline StageGeom stage_geom(int parts, int B, int NT) {
+  StageGeom g;
+  g.a_bytes = parts * kATileBytes;
+  g.b_bytes = NT * B * kRowBytes;
+  g.sfa_bytes = parts * kSfChunk;
+  g.sfb_bytes = act_sf_chunks(NT, act_term_stride(B, NT, parts)) * kSfChunk;
+  g.stage_bytes = (g.a_bytes + g.b_bytes + g.sfa_bytes + g.sfb_bytes + 1023) & ~1023;
+  g.tx_bytes = (uint32_t)(g.a_bytes + g.b_bytes + g.sfa_bytes + g.sfb_bytes);
+  return g;
+}
 
 __device__ __forceinline__ float bf16r(float x) { return __bfloat162float(__float2bfloat16_rn(x)); }
 
@@ -79,22 +107,67 @@ __device__ __forceinline__ float gateup_act(float g, float u, int activation, fl
   return bf16r(g * (1.f / (1.f + __expf(-1.702f * g))) * (u + 1.f));
 }
 
+// descriptor halves: the high word is constant per layout, the low word carries the address
+constexpr uint32_t kDescHiSw64 = (512u >> 4) | (1u << 14) | (4u << 29);   // SBO 512, version 1, 64-byte swizzle
+constexpr uint32_t kDescHiSf = (128u >> 4) | (1u << 14);                   // SBO 128, version 1, no swizzle
+__device__ __forceinline__ uint32_t desc_lo_sw(uint32_t saddr) { return ((saddr >> 4) & 0x3FFFu) | (1u << 16); }
+__device__ __forceinline__ uint32_t desc_lo_sf(uint32_t saddr) { return (saddr >> 4) & 0x3FFFu; }
+
+// D[tmem] (+)= A[smem] * B[smem]^T, packed FP4 x packed FP4, K = 64, two E8M0 scales per row
+__device__ __forceinline__ void umma_mxf4(uint32_t d_tmem, uint32_t a_lo, uint32_t b_lo, uint32_t idesc,
+                                          uint32_t sfa_tmem, uint32_t sfb_tmem, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t.reg .b64 da, db;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "mov.b64 da, {%1, %7};\n\t"
+      "mov.b64 db, {%2, %7};\n\t"
+      "tcgen05.mma.cta_group::1.kind::mxf4.block_scale.block32 [%0], da, db, %3, [%5], [%6], p;\n\t}"
+      ::"r"(d_tmem), "r"(a_lo), "r"(b_lo), "r"(idesc), "r"(accumulate), "r"(sfa_tmem), "r"(sfb_tmem),
+        "r"(kDescHiSw64)
+      : "memory");
+}
+__device__ __forceinline__ void utccp_sf(uint32_t taddr, uint32_t lo) {
+  asm volatile(
+      "{\n\t.reg .b64 d;\n\t"
+      "mov.b64 d, {%1, %2};\n\t"
+      "tcgen05.cp.cta_group::1.32x128b.warpx4 [%0], d;\n\t}"
+      ::"r"(taddr), "r"(lo), "r"(kDescHiSf)
+      : "memory");
+}
+__device__ __forceinline__ void tmem_ld_32x32b_x16(uint32_t taddr, uint32_t (&r)[16]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+        "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+      : "r"(taddr)
+      : "memory");
+}
+__device__ __forceinline__ void tma_load_4d(uint32_t dst, const CUtensorMap* map, uint32_t bar, int c0, int c1,
+                                            int c2, int c3) {
+  asm volatile(
+      "cp.async.bulk.tensor.4d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6}], [%2];"
+      ::"r"(dst), "l"(map), "r"(bar), "r"(c0), "r"(c1), "r"(c2), "r"(c3)
+      : "memory");
+}
+
 template <bool GATEUP>
 __global__ void __launch_bounds__(kThreads, 1)
 moe_grouped_gemm_kernel(const __grid_constant__ GemmParams p) {
   constexpr int NA = GATEUP ? 2 : 1;
   extern __shared__ uint8_t smem_raw[];
-  // 1024-byte alignment for the 128-byte swizzle atoms
+  // 1024-byte alignment covers every swizzle atom used here
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   SmemCtl* ctl = reinterpret_cast<SmemCtl*>(smem);
-  uint8_t* stage0 = smem + 1024;
-  const int N = p.N;
-  const int b_bytes = N * kTileK;
-  const int stage_bytes = NA * kATileBytes + 2 * b_bytes + 4 * kSfChunk;
-  const uint32_t stage_tx = NA * kATileTxBytes + 2 * b_bytes + (NA + 2) * kSfChunk;
+  const uint32_t stage0 = smem_u32(smem) + 1024;
+  const int B = p.B, NT = p.NT;
+  const StageGeom geo = stage_geom(NA, B, NT);
   const int S = p.stages;
-  const int acc_stride = NA * N;
-  const int n_acc = (2 * acc_stride <= 256) ? 2 : 1;
+  const bool merged = act_merged(B, NT, NA);   // all terms in one MMA (N = NT*B)
+  const int ncol = merged ? NT * B : B;        // TMEM columns of one accumulator
+  const int acc_cols = NA * ncol;
+  const int n_acc = (2 * acc_cols <= kAccColsLimit) ? 2 : 1;
+  const int sfb_chunks = geo.sfb_bytes / kSfChunk;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   volatile uint32_t* abort_word = &ctl->abort_word;
@@ -122,44 +195,37 @@ moe_grouped_gemm_kernel(const __grid_constant__ GemmParams p) {
   const uint32_t tmem_base = ctl->tmem_base;
 
   const int64_t rows_live = min((int64_t)p.num_valid[0], p.max_rows);
-  const int n_blocks = (int)(rows_live / N);
+  const int n_blocks = (int)(rows_live / B);
   const int total_work = n_blocks * p.MT;
 
   if (warp == 0) {
     // ------------------------------------------------------------------ TMA producer
     if (lane == 0) {
-      prefetch_tensormap(&p.tmA0);
-      if (GATEUP) prefetch_tensormap(&p.tmA1);
-      prefetch_tensormap(&p.tmBhi);
-      prefetch_tensormap(&p.tmBlo);
+      prefetch_tensormap(&p.tmW);
+      prefetch_tensormap(&p.tmA);
       int stage = 0;
       uint32_t phase = 0;
       int64_t issued = 0;
       bool ok = true;
+      const int64_t sfa_step = (int64_t)NA * kSfChunk;
       for (int w = blockIdx.x; w < total_work && ok; w += gridDim.x) {
-        const int b = w / p.MT, m = w % p.MT;
+        const int b = w / p.MT, m = w - b * p.MT;
         int e = p.sorted_e[b];
         if (e < 0 || e >= p.E) { p.status[2] = 1; e = 0; }
-        const int r0 = b * N;
-        const uint8_t* sfa = p.w_scale + ((int64_t)e * p.parts * p.MT + m) * p.KB * kSfChunk;
-        const uint8_t* sfb_hi = p.asf_hi + (int64_t)b * p.KB * kSfChunk;
-        const uint8_t* sfb_lo = p.asf_lo + (int64_t)b * p.KB * kSfChunk;
+        const int r0 = b * B;
+        const uint8_t* sfa = p.w_scale + ((int64_t)e * p.MT + m) * p.KB * sfa_step;
+        const uint8_t* sfb = p.asf + (int64_t)b * p.KB * geo.sfb_bytes;
         for (int kb = 0; kb < p.KB; ++kb) {
           if (!mbar_wait(smem_u32(&ctl->empty[stage]), phase ^ 1, abort_word, 0x100 + stage)) { ok = false; break; }
-          uint8_t* st = stage0 + (size_t)stage * stage_bytes;
+          const uint32_t st = stage0 + (uint32_t)stage * geo.stage_bytes;
           const uint32_t full = smem_u32(&ctl->full[stage]);
-          mbar_expect_tx(full, stage_tx);
-          tma_load_3d(smem_u32(st), &p.tmA0, full, kb * kTileK, m * kTileM, e);
-          if (GATEUP) tma_load_3d(smem_u32(st + kATileBytes), &p.tmA1, full, kb * kTileK, m * kTileM, e);
-          uint8_t* sb = st + NA * kATileBytes;
-          tma_load_2d(smem_u32(sb), &p.tmBhi, full, kb * kTileK, r0);
-          tma_load_2d(smem_u32(sb + b_bytes), &p.tmBlo, full, kb * kTileK, r0);
-          uint8_t* sf = sb + 2 * b_bytes;
-          bulk_load(smem_u32(sf), sfa + (int64_t)kb * kSfChunk, kSfChunk, full);
-          if (GATEUP)
-            bulk_load(smem_u32(sf + kSfChunk), sfa + ((int64_t)p.MT * p.KB + kb) * kSfChunk, kSfChunk, full);
-          bulk_load(smem_u32(sf + 2 * kSfChunk), sfb_hi + (int64_t)kb * kSfChunk, kSfChunk, full);
-          bulk_load(smem_u32(sf + 3 * kSfChunk), sfb_lo + (int64_t)kb * kSfChunk, kSfChunk, full);
+          mbar_expect_tx(full, geo.tx_bytes);
+          tma_load_4d(st, &p.tmW, full, kb * kTileK, m * kTileM, 0, e);
+          tma_load_3d(st + geo.a_bytes, &p.tmA, full, kb * kTileK, r0, 0);
+          bulk_load(st + geo.a_bytes + geo.b_bytes, sfa, (uint32_t)geo.sfa_bytes, full);
+          bulk_load(st + geo.a_bytes + geo.b_bytes + geo.sfa_bytes, sfb, (uint32_t)geo.sfb_bytes, full);
+          sfa += sfa_step;
+          sfb += geo.sfb_bytes;
           ++issued;
           if (++stage == S) { stage = 0; phase ^= 1; }
         }
@@ -177,123 +243,159 @@ moe_grouped_gemm_kernel(const __grid_constant__ GemmParams p) {
     }
   } else if (warp == 1) {
     // ------------------------------------------------------------------ MMA issuer
-    if (lane == 0) {
-      int stage = 0;
-      uint32_t phase = 0;
-      int acc = 0;
-      uint32_t acc_phase = 0;
-      uint32_t sf_buf = 0;          // scale columns alternate between two TMEM buffers
-      bool ok = true;
-      for (int w = blockIdx.x; w < total_work && ok; w += gridDim.x) {
-        if (!mbar_wait(smem_u32(&ctl->tmem_empty[acc]), acc_phase ^ 1, abort_word, 0x200 + acc)) break;
-        tc_fence_after_sync();
-        const uint32_t d0 = tmem_base + acc * acc_stride;
-        for (int kb = 0; kb < p.KB; ++kb) {
-          if (!mbar_wait(smem_u32(&ctl->full[stage]), phase, abort_word, 0x300 + stage)) { ok = false; break; }
-          tc_fence_after_sync();
-          uint8_t* st = stage0 + (size_t)stage * stage_bytes;
-          const uint32_t a0 = smem_u32(st);
-          const uint32_t bh = a0 + NA * kATileBytes, bl = bh + b_bytes;
-          const uint32_t sf = bl + b_bytes;
-          const uint32_t sfc = tmem_base + kSfCol0 + sf_buf * 16;
-          sf_buf ^= 1;
-          tc_copy_sf_32x128b(sfc + 0, make_desc_sf(sf));
-          if (GATEUP) tc_copy_sf_32x128b(sfc + 4, make_desc_sf(sf + kSfChunk));
-          tc_copy_sf_32x128b(sfc + 8, make_desc_sf(sf + 2 * kSfChunk));
-          tc_copy_sf_32x128b(sfc + 12, make_desc_sf(sf + 3 * kSfChunk));
+    // The whole warp walks the loop (uniform control flow); lane 0 issues.
+    uint32_t idesc[2];
 #pragma unroll
-          for (int k = 0; k < 4; ++k) {
-            const uint32_t idesc = make_idesc_block_scaled(kFmtE2M1_f8f6f4, kFmtE4M3, kTileM, N, k, k);
-            const uint32_t accum = (kb | k) != 0;
-            const uint64_t da0 = make_desc_sw128(a0 + k * 32);
-            const uint64_t dbh = make_desc_sw128(bh + k * 32);
-            const uint64_t dbl = make_desc_sw128(bl + k * 32);
-            mma_mxf8f6f4(d0, da0, dbh, idesc, sfc + 0, sfc + 8, accum);
-            mma_mxf8f6f4(d0, da0, dbl, idesc, sfc + 0, sfc + 12, 1);
-            if (GATEUP) {
-              const uint64_t da1 = make_desc_sw128(a0 + kATileBytes + k * 32);
-              mma_mxf8f6f4(d0 + N, da1, dbh, idesc, sfc + 4, sfc + 8, accum);
-              mma_mxf8f6f4(d0 + N, da1, dbl, idesc, sfc + 4, sfc + 12, 1);
+    for (int s = 0; s < 2; ++s)
+      idesc[s] = make_idesc_block_scaled(kFmtE2M1_mxf4, kFmtE2M1_mxf4, kTileM, (uint32_t)ncol, 2 * s, 2 * s);
+    const uint32_t term_lo = (uint32_t)(B * kRowBytes) >> 4;   // descriptor step from one term to the next
+    int stage = 0;
+    uint32_t phase = 0;
+    int acc = 0;
+    uint32_t acc_phase = 0;
+    uint32_t sf_buf = 0;            // scale columns alternate between two TMEM buffers
+    bool ok = true;
+    for (int w = blockIdx.x; w < total_work && ok; w += gridDim.x) {
+      if (!mbar_wait(smem_u32(&ctl->tmem_empty[acc]), acc_phase ^ 1, abort_word, 0x200 + acc)) break;
+      tc_fence_after_sync();
+      const uint32_t d0 = tmem_base + acc * acc_cols;
+      for (int kb = 0; kb < p.KB; ++kb) {
+        if (!mbar_wait(smem_u32(&ctl->full[stage]), phase, abort_word, 0x300 + stage)) { ok = false; break; }
+        tc_fence_after_sync();
+        if (lane == 0) {
+          const uint32_t st = stage0 + (uint32_t)stage * geo.stage_bytes;
+          const uint32_t a_lo = desc_lo_sw(st);
+          const uint32_t b_lo = desc_lo_sw(st + geo.a_bytes);
+          const uint32_t sf_lo = desc_lo_sf(st + geo.a_bytes + geo.b_bytes);
+          const uint32_t sfa_t = tmem_base + kSfCol0 + sf_buf * 32;
+          const uint32_t sfb_t = sfa_t + 8;
+          utccp_sf(sfa_t, sf_lo);
+          if (GATEUP) utccp_sf(sfa_t + 4, sf_lo + (kSfChunk >> 4));
+          for (int c = 0; c < sfb_chunks; ++c)
+            utccp_sf(sfb_t + 4 * c, sf_lo + ((geo.sfa_bytes + c * kSfChunk) >> 4));
+          const uint32_t first = kb != 0;
+          if (merged) {
+#pragma unroll
+            for (int s = 0; s < 2; ++s) {
+              umma_mxf4(d0, a_lo + 2 * s, b_lo + 2 * s, idesc[s], sfa_t, sfb_t, s == 0 ? first : 1u);
+              if (GATEUP)
+                umma_mxf4(d0 + ncol, a_lo + (kATileBytes >> 4) + 2 * s, b_lo + 2 * s, idesc[s], sfa_t + 4, sfb_t,
+                          s == 0 ? first : 1u);
+            }
+          } else {
+#pragma unroll
+            for (int s = 0; s < 2; ++s) {
+              for (int t = 0; t < NT; ++t) {
+                const uint32_t accum = (s == 0 && t == 0) ? first : 1u;
+                umma_mxf4(d0, a_lo + 2 * s, b_lo + t * term_lo + 2 * s, idesc[s], sfa_t, sfb_t + 4 * t, accum);
+                if (GATEUP)
+                  umma_mxf4(d0 + ncol, a_lo + (kATileBytes >> 4) + 2 * s, b_lo + t * term_lo + 2 * s, idesc[s],
+                            sfa_t + 4, sfb_t + 4 * t, accum);
+              }
             }
           }
           tc_commit(smem_u32(&ctl->empty[stage]));
-          if (++stage == S) { stage = 0; phase ^= 1; }
         }
-        if (!ok) break;
-        tc_commit(smem_u32(&ctl->tmem_full[acc]));
-        if (n_acc == 2) { acc ^= 1; if (acc == 0) acc_phase ^= 1; } else { acc_phase ^= 1; }
+        __syncwarp();
+        sf_buf ^= 1;
+        if (++stage == S) { stage = 0; phase ^= 1; }
       }
+      if (!ok) break;
+      if (lane == 0) tc_commit(smem_u32(&ctl->tmem_full[acc]));
+      __syncwarp();
+      if (n_acc == 2) { acc ^= 1; if (acc == 0) acc_phase ^= 1; } else { acc_phase ^= 1; }
     }
   } else {
     // ------------------------------------------------------------------ epilogue warps
     const int quad = warp & 3;                 // TMEM lanes [32*quad, 32*quad+32)
     const int row_local = quad * 32 + lane;
+    const int64_t oq_pitch = p.out_kp / 2;
     int acc = 0;
     uint32_t acc_phase = 0;
     for (int w = blockIdx.x; w < total_work; w += gridDim.x) {
-      const int b = w / p.MT, m = w % p.MT;
-      const int r0 = b * N;
+      const int b = w / p.MT, m = w - b * p.MT;
+      const int r0 = b * B;
       const int j = m * kTileM + row_local;    // output feature of this thread
+      // valid rows are a prefix of the block (padding sentinels follow)
+      int nvalid = 0;
+      for (int q = 0; q < B; q += 32) {
+        const uint32_t id = p.sorted_ids[r0 + q + lane];
+        nvalid += __popc(__ballot_sync(0xffffffffu, (int)(id >> 24) < p.topk && (int)(id & 0xFFFFFFu) < p.T));
+      }
       if (!mbar_wait(smem_u32(&ctl->tmem_full[acc]), acc_phase, abort_word, 0x400 + acc)) break;
       tc_fence_after_sync();
-      const uint32_t t0 = tmem_base + ((uint32_t)(quad * 32) << 16) + acc * acc_stride;
-      for (int c0 = 0; c0 < N; c0 += 32) {
-        uint32_t g[32], u[32];
-        tmem_ld_32x32b_x32(t0 + c0, g);
-        if (GATEUP) tmem_ld_32x32b_x32(t0 + N + c0, u);
+      const uint32_t t0 = tmem_base + ((uint32_t)(quad * 32) << 16) + acc * acc_cols;
+      const bool j_ok = j < p.rows;
+      uint32_t my_id = 0;
+      for (int c0 = 0; c0 < nvalid; c0 += 16) {
+        uint32_t g[16], u[16];
+        tmem_ld_32x32b_x16(t0 + c0, g);
+        if (GATEUP) tmem_ld_32x32b_x16(t0 + ncol + c0, u);
         tmem_ld_wait();
-        const uint32_t my_id = p.sorted_ids[r0 + c0 + lane];
+        if (merged) {
+          // the terms were separate column groups of one instruction: add them up
+          for (int t = 1; t < NT; ++t) {
+            uint32_t g2[16], u2[16];
+            tmem_ld_32x32b_x16(t0 + t * B + c0, g2);
+            if (GATEUP) tmem_ld_32x32b_x16(t0 + ncol + t * B + c0, u2);
+            tmem_ld_wait();
+#pragma unroll
+            for (int n = 0; n < 16; ++n) {
+              g[n] = __float_as_uint(__uint_as_float(g[n]) + __uint_as_float(g2[n]));
+              if (GATEUP) u[n] = __float_as_uint(__uint_as_float(u[n]) + __uint_as_float(u2[n]));
+            }
+          }
+        }
+        if ((c0 & 31) == 0) my_id = p.sorted_ids[r0 + c0 + lane];
         if (GATEUP) {
-          const bool j_ok = j < p.rows;
           if (p.h_out != nullptr) {
 #pragma unroll
-            for (int n = 0; n < 32; ++n) {
-              const uint32_t id = __shfl_sync(0xffffffffu, my_id, n);
-              const int tok = (int)(id & 0xFFFFFFu), kk = (int)(id >> 24);
-              const float v = gateup_act(__uint_as_float(g[n]), __uint_as_float(u[n]), p.activation,
-                                         p.swiglu_limit);
-              if (j_ok && kk < p.topk && tok < p.T)
-                p.h_out[((int64_t)tok * p.topk + kk) * p.rows + j] = __float2bfloat16_rn(v);
+            for (int n = 0; n < 16; ++n) {
+              const uint32_t id = __shfl_sync(0xffffffffu, my_id, (c0 & 31) + n);
+              if (c0 + n < nvalid) {
+                const int tok = (int)(id & 0xFFFFFFu), kk = (int)(id >> 24);
+                const float v = gateup_act(__uint_as_float(g[n]), __uint_as_float(u[n]), p.activation,
+                                           p.swiglu_limit);
+                if (j_ok) p.h_out[((int64_t)tok * p.topk + kk) * p.rows + j] = __float2bfloat16_rn(v);
+              }
             }
           } else {
             // fused re-quantisation of h into the operand format of the down GEMM; the 32
             // lanes of a warp are one 32-wide scale block along the feature axis
 #pragma unroll
-            for (int n = 0; n < 32; ++n) {
-              float v = gateup_act(__uint_as_float(g[n]), __uint_as_float(u[n]), p.activation, p.swiglu_limit);
-              if (!j_ok) v = 0.f;
-              const int64_t r = (int64_t)r0 + c0 + n;
-              // first term
-              uint32_t amax = __reduce_max_sync(0xffffffffu, __float_as_uint(v) & 0x7fffffffu);
-              int e1 = max((int)(amax >> 23) - 7, 0);
-              float inv = __uint_as_float((uint32_t)(254 - e1) << 23);
-              __nv_fp8_storage_t q1 = __nv_cvt_float_to_fp8(v * inv, __NV_SATFINITE, __NV_E4M3);
-              float back = __half2float(__half(__nv_cvt_fp8_to_halfraw(q1, __NV_E4M3)));
-              float res = v - back * __uint_as_float(e1 == 0 ? 0x00400000u : ((uint32_t)e1 << 23));
-              // residual term
-              uint32_t amax2 = __reduce_max_sync(0xffffffffu, __float_as_uint(res) & 0x7fffffffu);
-              int e2 = max((int)(amax2 >> 23) - 7, 0);
-              float inv2 = __uint_as_float((uint32_t)(254 - e2) << 23);
-              __nv_fp8_storage_t q2 = __nv_cvt_float_to_fp8(res * inv2, __NV_SATFINITE, __NV_E4M3);
-              p.oq_hi[r * p.out_kp + j] = q1;
-              p.oq_lo[r * p.out_kp + j] = q2;
-              if (lane == 0) {
-                const int64_t off = ((int64_t)b * p.out_kb + m) * kSfChunk + sf_chunk_offset(c0 + n, quad);
-                p.osf_hi[off] = (uint8_t)e1;
-                p.osf_lo[off] = (uint8_t)e2;
+            for (int n = 0; n < 16; ++n) {
+              if (c0 + n < nvalid) {
+                float res = gateup_act(__uint_as_float(g[n]), __uint_as_float(u[n]), p.activation, p.swiglu_limit);
+                if (!j_ok) res = 0.f;
+                const int64_t r = (int64_t)r0 + c0 + n;
+                for (int t = 0; t < NT; ++t) {
+                  const uint32_t amax = __reduce_max_sync(0xffffffffu, __float_as_uint(res) & 0x7fffffffu);
+                  const int e = max((int)(amax >> 23) - 2, 0);
+                  const float inv = __uint_as_float((uint32_t)(254 - e) << 23);
+                  const __nv_fp4x2_storage_t code =
+                      __nv_cvt_float2_to_fp4x2(make_float2(res * inv, 0.f), __NV_E2M1, cudaRoundNearest);
+                  __half2_raw hb = __nv_cvt_fp4x2_to_halfraw2(code, __NV_E2M1);
+                  const float back = __half2float(__half(__half_raw{hb.x}));
+                  res -= back * __uint_as_float(e == 0 ? 0x00400000u : ((uint32_t)e << 23));
+                  const uint32_t mine = (uint32_t)code & 0xFu;
+                  const uint32_t next = __shfl_down_sync(0xffffffffu, mine, 1);
+                  if ((lane & 1) == 0)
+                    p.oq[t * p.oq_term_stride + r * oq_pitch + (j >> 1)] = (uint8_t)(mine | (next << 4));
+                  if (lane == 0)
+                    p.osf[act_sf_index(b, m, p.out_kb, B, NT, p.out_ts, t, c0 + n, quad)] = (uint8_t)e;
+                }
               }
             }
           }
         } else {
-          if (j < p.rows) {
+          if (j_ok) {
 #pragma unroll
-            for (int n = 0; n < 32; ++n) {
-              const int64_t r = (int64_t)r0 + c0 + n;
-              p.out2[r * p.rows + j] = __float2bfloat16_rn(__uint_as_float(g[n]));
+            for (int n = 0; n < 16; ++n) {
+              if (c0 + n < nvalid)
+                p.out2[((int64_t)r0 + c0 + n) * p.rows + j] = __float2bfloat16_rn(__uint_as_float(g[n]));
             }
           }
         }
-        (void)my_id;
       }
       tc_fence_before_sync();
       __syncwarp();
@@ -333,22 +435,6 @@ static EncodeTiledFn get_encode_fn() {
   return fn;
 }
 
-static int encode_map(CUtensorMap* map, CUtensorMapDataType type, int rank, const void* base,
-                      const cuuint64_t* dims, const cuuint64_t* strides, const cuuint32_t* box,
-                      CUtensorMapL2promotion promo, const char* what) {
-  EncodeTiledFn fn = get_encode_fn();
-  if (fn == nullptr) return set_error(-2, "cuTensorMapEncodeTiled is not available from the driver");
-  cuuint32_t estr[5] = {1, 1, 1, 1, 1};
-  CUresult r = fn(map, type, (cuuint32_t)rank, const_cast<void*>(base), dims, strides, box, estr,
-                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, promo,
-                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-  if (r != CUDA_SUCCESS)
-    return set_error(-3, "cuTensorMapEncodeTiled(%s) failed with CUresult %d (base %p dims %llu,%llu,%llu)", what,
-                     (int)r, base, (unsigned long long)dims[0], (unsigned long long)dims[1],
-                     (unsigned long long)(rank > 2 ? dims[2] : 0));
-  return 0;
-}
-
 static int device_sm_count() {
   static int sms[64] = {};
   int dev = 0;
@@ -361,60 +447,70 @@ static int device_sm_count() {
   return n;
 }
 
+static int encode_map_sw(CUtensorMap* map, CUtensorMapDataType type, int rank, const void* base,
+                         const cuuint64_t* dims, const cuuint64_t* strides, const cuuint32_t* box,
+                         CUtensorMapSwizzle swizzle, CUtensorMapL2promotion promo, const char* what) {
+  EncodeTiledFn fn = get_encode_fn();
+  if (fn == nullptr) return set_error(-2, "cuTensorMapEncodeTiled is not available from the driver");
+  cuuint32_t estr[5] = {1, 1, 1, 1, 1};
+  CUresult r = fn(map, type, (cuuint32_t)rank, const_cast<void*>(base), dims, strides, box, estr,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, swizzle, promo, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS)
+    return set_error(-3, "cuTensorMapEncodeTiled(%s) failed with CUresult %d (base %p dims %llu,%llu,%llu)", what,
+                     (int)r, base, (unsigned long long)dims[0], (unsigned long long)dims[1],
+                     (unsigned long long)(rank > 2 ? dims[2] : 0));
+  return 0;
+}
+
 int launch_grouped_gemm(const GemmArgs& a, cudaStream_t st) {
   B200_CHECK_ARG(a.N == 32 || a.N == 64 || a.N == 128, "grouped gemm: token tile %d not in {32,64,128}", a.N);
+  B200_CHECK_ARG(a.NT >= 2 && a.NT <= kMaxTerms, "grouped gemm: %d activation terms (2..4 supported)", a.NT);
   B200_CHECK_ARG(a.Kd % 32 == 0 && a.rows > 0 && a.E > 0, "grouped gemm: bad shape");
-  B200_CHECK_ARG(a.max_rows % a.N == 0, "grouped gemm: max_rows %% N != 0");
+  B200_CHECK_ARG(a.max_rows % a.N == 0, "grouped gemm: max_rows %% B != 0");
+  B200_CHECK_ARG(((uintptr_t)a.w_data & 15) == 0 && ((uintptr_t)a.a_q & 15) == 0,
+                 "grouped gemm: operand tensors must be 16-byte aligned");
   const int KP = (int)round_up64(a.Kd, kTileK);
   const int parts = a.gateup ? 2 : 1;
   GemmParams p;
   memset(&p, 0, sizeof(p));
-  p.N = a.N; p.rows = a.rows; p.KB = KP / kTileK; p.MT = (a.rows + kTileM - 1) / kTileM;
-  p.E = a.E; p.topk = a.topk; p.T = a.T; p.parts = parts; p.activation = a.activation;
+  p.B = a.N; p.NT = a.NT; p.rows = a.rows; p.KB = KP / kTileK; p.MT = (a.rows + kTileM - 1) / kTileM;
+  p.E = a.E; p.topk = a.topk; p.T = a.T; p.activation = a.activation;
   p.swiglu_limit = a.swiglu_limit; p.max_rows = a.max_rows;
-  p.w_scale = (const uint8_t*)a.w_scale; p.asf_hi = (const uint8_t*)a.asf_hi; p.asf_lo = (const uint8_t*)a.asf_lo;
+  p.w_scale = (const uint8_t*)a.w_scale; p.asf = (const uint8_t*)a.asf;
   p.sorted_ids = a.sorted_ids; p.sorted_e = a.sorted_e; p.num_valid = a.num_valid; p.status = a.status;
-  p.h_out = (__nv_bfloat16*)a.h_out; p.oq_hi = (uint8_t*)a.oq_hi; p.oq_lo = (uint8_t*)a.oq_lo;
-  p.osf_hi = (uint8_t*)a.osf_hi; p.osf_lo = (uint8_t*)a.osf_lo; p.out_kp = a.out_kp; p.out_kb = a.out_kp / kTileK;
+  p.h_out = (__nv_bfloat16*)a.h_out; p.oq = (uint8_t*)a.oq; p.osf = (uint8_t*)a.osf;
+  p.out_kp = a.out_kp; p.out_kb = a.out_kp / kTileK; p.out_ts = act_term_stride(a.N, a.NT, 1);
+  p.oq_term_stride = a.max_rows * (int64_t)(a.out_kp / 2);
   p.out2 = (__nv_bfloat16*)a.out2;
   if (a.gateup && a.h_out == nullptr)
-    B200_CHECK_ARG(a.out_kp == (int)round_up64(a.rows, kTileK) && a.oq_hi && a.oq_lo && a.osf_hi && a.osf_lo,
+    B200_CHECK_ARG(a.out_kp == (int)round_up64(a.rows, kTileK) && a.oq && a.osf,
                    "gate-up: fused output buffers missing");
 
-  // weights: FP4 pairs in memory, [E, parts*rows, KP/2] bytes
-  const cuuint64_t row_pitch = (cuuint64_t)KP / 2;
+  // weights: canonical packed FP4 [E, parts, rows, Kd/2]; K and row tails are zero-filled by TMA
+  const cuuint64_t row_pitch = (cuuint64_t)a.Kd / 2;
   {
-    cuuint64_t dims[3] = {(cuuint64_t)KP, (cuuint64_t)a.rows, (cuuint64_t)a.E};
-    cuuint64_t strides[2] = {row_pitch, row_pitch * (cuuint64_t)a.rows * parts};
-    cuuint32_t box[3] = {kTileK, kTileM, 1};
-    const uint8_t* base = (const uint8_t*)a.w_data;
-    int rc = encode_map(&p.tmA0, CU_TENSOR_MAP_DATA_TYPE_16U4_ALIGN16B, 3, base, dims, strides, box,
-                        CU_TENSOR_MAP_L2_PROMOTION_L2_256B, "weights part 0");
+    cuuint64_t dims[4] = {(cuuint64_t)a.Kd, (cuuint64_t)a.rows, (cuuint64_t)parts, (cuuint64_t)a.E};
+    cuuint64_t strides[3] = {row_pitch, row_pitch * (cuuint64_t)a.rows, row_pitch * (cuuint64_t)a.rows * parts};
+    cuuint32_t box[4] = {kTileK, kTileM, (cuuint32_t)parts, 1};
+    int rc = encode_map_sw(&p.tmW, CU_TENSOR_MAP_DATA_TYPE_16U4_ALIGN8B, 4, a.w_data, dims, strides, box,
+                           CU_TENSOR_MAP_SWIZZLE_64B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, "weights");
     if (rc) return rc;
-    if (a.gateup) {
-      rc = encode_map(&p.tmA1, CU_TENSOR_MAP_DATA_TYPE_16U4_ALIGN16B, 3, base + row_pitch * a.rows, dims, strides,
-                      box, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, "weights part 1");
-      if (rc) return rc;
-    }
   }
   {
-    cuuint64_t dims[2] = {(cuuint64_t)KP, (cuuint64_t)a.max_rows};
-    cuuint64_t strides[1] = {(cuuint64_t)KP};
-    cuuint32_t box[2] = {kTileK, (cuuint32_t)a.N};
-    int rc = encode_map(&p.tmBhi, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, a.a_hi, dims, strides, box,
-                        CU_TENSOR_MAP_L2_PROMOTION_L2_128B, "activations hi");
-    if (rc) return rc;
-    rc = encode_map(&p.tmBlo, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, a.a_lo, dims, strides, box,
-                    CU_TENSOR_MAP_L2_PROMOTION_L2_128B, "activations lo");
+    cuuint64_t dims[3] = {(cuuint64_t)KP, (cuuint64_t)a.max_rows, (cuuint64_t)a.NT};
+    cuuint64_t strides[2] = {(cuuint64_t)KP / 2, (cuuint64_t)(KP / 2) * (cuuint64_t)a.max_rows};
+    cuuint32_t box[3] = {kTileK, (cuuint32_t)a.N, (cuuint32_t)a.NT};
+    int rc = encode_map_sw(&p.tmA, CU_TENSOR_MAP_DATA_TYPE_16U4_ALIGN8B, 3, a.a_q, dims, strides, box,
+                           CU_TENSOR_MAP_SWIZZLE_64B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, "activations");
     if (rc) return rc;
   }
 
-  const int stage_bytes = parts * kATileBytes + 2 * a.N * kTileK + 4 * kSfChunk;
-  int stages = (kSmemLimit - 2048) / stage_bytes;
+  const StageGeom geo = stage_geom(parts, a.N, a.NT);
+  int stages = (kSmemLimit - 2048) / geo.stage_bytes;
   stages = std::min(stages, kMaxStages);
   B200_CHECK_ARG(stages >= 2, "grouped gemm: tile does not fit shared memory");
   p.stages = stages;
-  const size_t smem = 2048 + (size_t)stages * stage_bytes;
+  const size_t smem = 2048 + (size_t)stages * geo.stage_bytes;
 
   const int64_t max_work = (a.max_rows / a.N) * p.MT;
   const int grid = (int)std::min<int64_t>(device_sm_count(), std::max<int64_t>(max_work, 1));
@@ -440,7 +536,7 @@ int launch_grouped_gemm(const GemmArgs& a, cudaStream_t st) {
 }
 
 // ------------------------------------------------------------------------------------
-// known-answer probes of the two hardware paths the main loop depends on
+// known-answer probes of the hardware paths the main loop depends on
 // ------------------------------------------------------------------------------------
 __global__ void __launch_bounds__(128, 1)
 probe_tma_fp4_kernel(const __grid_constant__ CUtensorMap map, uint32_t* out) {
@@ -457,7 +553,7 @@ probe_tma_fp4_kernel(const __grid_constant__ CUtensorMap map, uint32_t* out) {
   fence_proxy_async_smem();
   __syncthreads();
   if (threadIdx.x == 0) {
-    mbar_expect_tx(smem_u32(&bar), kATileTxBytes);
+    mbar_expect_tx(smem_u32(&bar), kATileBytes);
     tma_load_3d(smem_u32(smem), &map, smem_u32(&bar), 0, 0, 0);
     mbar_wait(smem_u32(&bar), 0, &abort_word, 1);
   }
@@ -487,7 +583,7 @@ __global__ void __launch_bounds__(128, 1) probe_utccp_kernel(const uint32_t* in,
   tc_fence_after_sync();
   const uint32_t tbase = tmem_slot;
   if (threadIdx.x == 0) {
-    tc_copy_sf_32x128b(tbase, make_desc_sf(smem_u32(chunk)));
+    utccp_sf(tbase, desc_lo_sf(smem_u32(chunk)));
     tc_commit(smem_u32(&bar));
     mbar_wait(smem_u32(&bar), 0, &abort_word, 2);
   }
@@ -503,16 +599,16 @@ __global__ void __launch_bounds__(128, 1) probe_utccp_kernel(const uint32_t* in,
   if (warp == 0) tmem_dealloc(tbase, 32);
 }
 
-// Issue-rate probe: `count` dependent MMAs of shape 128 x N into `nacc` alternating accumulators,
+// Issue-rate probe: `count` MMAs of shape 128 x N x 64 alternating between `nacc` accumulators,
 // one commit, one bounded wait; reports clock cycles.  Operand contents are irrelevant (zeros).
 __global__ void __launch_bounds__(128, 1) probe_mma_rate_kernel(const int32_t* cfg, uint32_t* out) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   __shared__ uint64_t bar;
   __shared__ uint32_t tmem_slot, abort_word;
-  const int kind = cfg[0], N = cfg[1], count = cfg[2], nacc = cfg[3];
+  const int N = cfg[1], count = cfg[2], nacc = cfg[3];
   const int warp = threadIdx.x >> 5;
-  for (int i = threadIdx.x; i < (16384 + 32768 + 1024) / 4; i += blockDim.x) reinterpret_cast<uint32_t*>(smem)[i] = 0;
+  for (int i = threadIdx.x; i < (8192 + 16384 + 1024) / 4; i += blockDim.x) reinterpret_cast<uint32_t*>(smem)[i] = 0;
   if (threadIdx.x == 0) {
     abort_word = 0;
     mbar_init(smem_u32(&bar), 1);
@@ -528,23 +624,20 @@ __global__ void __launch_bounds__(128, 1) probe_mma_rate_kernel(const int32_t* c
   tc_fence_after_sync();
   const uint32_t tbase = tmem_slot;
   if (threadIdx.x == 0) {
-    const uint32_t a = smem_u32(smem), b = a + 16384, sf = b + 32768;
-    tc_copy_sf_32x128b(tbase + 448, make_desc_sf(sf));
-    tc_copy_sf_32x128b(tbase + 452, make_desc_sf(sf + 512));
-    tc_copy_sf_32x128b(tbase + 456, make_desc_sf(sf));
+    const uint32_t a = smem_u32(smem), b = a + 8192, sf = b + 16384;
+    utccp_sf(tbase + 448, desc_lo_sf(sf));
+    utccp_sf(tbase + 456, desc_lo_sf(sf + 512));
+    utccp_sf(tbase + 460, desc_lo_sf(sf + 512));
+    uint32_t idesc[2];
+    for (int s = 0; s < 2; ++s) idesc[s] = make_idesc_block_scaled(kFmtE2M1_mxf4, kFmtE2M1_mxf4, 128, N, 2 * s, 2 * s);
+    const uint32_t a_lo = desc_lo_sw(a), b_lo = desc_lo_sw(b);
+    const uint32_t d1 = tbase + (nacc > 1 ? N : 0);
     const long long t0 = clock64();
-    for (int i = 0; i < count; ++i) {
-      const int k = i & 3;
-      const uint32_t d = tbase + (i % nacc) * N;
-      if (kind == 0) {
-        const uint32_t idesc = make_idesc_block_scaled(kFmtE2M1_f8f6f4, kFmtE4M3, 128, N, k, k);
-        mma_mxf8f6f4(d, make_desc_sw128(a + k * 32), make_desc_sw128(b + k * 32), idesc, tbase + 448, tbase + 452,
-                     i >= nacc);
-      } else {
-        const uint32_t idesc = make_idesc_block_scaled(kFmtE2M1_mxf4, kFmtE2M1_mxf4, 128, N, (k & 1) * 2, (k & 1) * 2);
-        mma_mxf4(d, make_desc_sw128(a + (k & 1) * 32), make_desc_sw128(b + (k & 1) * 32), idesc, tbase + 448,
-                 tbase + 452, i >= nacc);
-      }
+    for (int i = 0; i < count; i += 4) {
+      umma_mxf4(tbase, a_lo, b_lo, idesc[0], tbase + 448, tbase + 456, 1);
+      umma_mxf4(d1, a_lo, b_lo, idesc[0], tbase + 448, tbase + 456, 1);
+      umma_mxf4(tbase, a_lo + 2, b_lo + 2, idesc[1], tbase + 448, tbase + 456, 1);
+      umma_mxf4(d1, a_lo + 2, b_lo + 2, idesc[1], tbase + 448, tbase + 456, 1);
     }
     const long long t1 = clock64();
     tc_commit(smem_u32(&bar));
@@ -565,8 +658,8 @@ int run_debug_probe(int which, const void* in, void* out, cudaStream_t st) {
     cuuint64_t dims[3] = {128, 128, 1};
     cuuint64_t strides[2] = {64, 64 * 128};
     cuuint32_t box[3] = {128, 128, 1};
-    int rc = encode_map(&map, CU_TENSOR_MAP_DATA_TYPE_16U4_ALIGN16B, 3, in, dims, strides, box,
-                        CU_TENSOR_MAP_L2_PROMOTION_NONE, "probe tile");
+    int rc = encode_map_sw(&map, CU_TENSOR_MAP_DATA_TYPE_16U4_ALIGN8B, 3, in, dims, strides, box,
+                           CU_TENSOR_MAP_SWIZZLE_64B, CU_TENSOR_MAP_L2_PROMOTION_NONE, "probe tile");
     if (rc) return rc;
     probe_tma_fp4_kernel<<<1, 128, kATileBytes + 1024, st>>>(map, (uint32_t*)out);
     B200_CHECK_CUDA(cudaGetLastError());
@@ -578,13 +671,7 @@ int run_debug_probe(int which, const void* in, void* out, cudaStream_t st) {
     return 0;
   }
   if (which == 3) {
-    static bool attr = false;
-    if (!attr) {
-      B200_CHECK_CUDA(cudaFuncSetAttribute(probe_mma_rate_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                           65536));
-      attr = true;
-    }
-    probe_mma_rate_kernel<<<1, 128, 16384 + 32768 + 1024 + 1024, st>>>((const int32_t*)in, (uint32_t*)out);
+    probe_mma_rate_kernel<<<1, 128, 8192 + 16384 + 1024 + 1024, st>>>((const int32_t*)in, (uint32_t*)out);
     B200_CHECK_CUDA(cudaGetLastError());
     return 0;
   }

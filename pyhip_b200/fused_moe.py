@@ -58,14 +58,15 @@ def pick_block(T: int, K: int, E: int) -> int:
 
 
 class PreparedWeights:
-    """Device-layout image of one layer's MXFP4 expert weights, built once (the counterpart of
-    the reference's weight pre-shuffle, src/misc.py:114-128)."""
+    """One layer's MXFP4 expert weights as the kernels consume them: the packed E2M1 tensors in
+    place (canonical layout, no copy) plus a regrouped image of their E8M0 scales, built once
+    (the counterpart of the reference's scale pre-shuffle, tests/contrib/moe/test_moe.py:167)."""
 
     def __init__(self, w1, w1_scale, w2, w2_scale):
         if not w1.is_cuda:
             raise ValueError("weights must be CUDA tensors")
-        w1 = w1.view(torch.uint8) if w1.dtype != torch.uint8 else w1
-        w2 = w2.view(torch.uint8) if w2.dtype != torch.uint8 else w2
+        w1 = (w1.view(torch.uint8) if w1.dtype != torch.uint8 else w1).contiguous()
+        w2 = (w2.view(torch.uint8) if w2.dtype != torch.uint8 else w2).contiguous()
         s1 = w1_scale.view(torch.uint8) if w1_scale.dtype != torch.uint8 else w1_scale
         s2 = w2_scale.view(torch.uint8) if w2_scale.dtype != torch.uint8 else w2_scale
         E, N1, Kh = w1.shape
@@ -78,19 +79,18 @@ class PreparedWeights:
             raise ValueError("E8M0 scale 0xFF (NaN) is not a valid weight scale")
         L = _lib.lib()
         shape = _lib.Shape(T=0, K=1, E=E, E_route=E, H=self.H, I=self.I, B=32, weight_format=_lib.W_MXFP4,
-                           activation=0, swiglu_limit=0.0)
+                           activation=0, swiglu_limit=0.0, act_terms=0)
         out = []
-        for which, wq, ws in ((1, w1, s1), (2, w2, s2)):
-            db, sb = ctypes.c_int64(), ctypes.c_int64()
-            _lib.check(L.b200moe_prepared_bytes(ctypes.byref(shape), which, ctypes.byref(db), ctypes.byref(sb)),
-                       "prepared_bytes")
-            data = torch.empty(db.value, dtype=torch.uint8, device=w1.device)
+        for which, ws in ((1, s1), (2, s2)):
+            sb = ctypes.c_int64()
+            _lib.check(L.b200moe_prepared_scale_bytes(ctypes.byref(shape), which, ctypes.byref(sb)),
+                       "prepared_scale_bytes")
             scale = torch.empty(sb.value, dtype=torch.uint8, device=w1.device)
-            _lib.check(L.b200moe_prepare_weights(ctypes.byref(shape), which, _ptr(wq.contiguous()),
-                                                 _ptr(ws.contiguous()), _ptr(data), _ptr(scale), _stream()),
-                       "prepare_weights")
-            out += [data, scale]
-        self.w1_data, self.w1_scale, self.w2_data, self.w2_scale = out
+            _lib.check(L.b200moe_prepare_scales(ctypes.byref(shape), which, _ptr(ws.contiguous()), _ptr(scale),
+                                                _stream()), "prepare_scales")
+            out.append(scale)
+        self.w1_data, self.w2_data = w1, w2            # consumed in place
+        self.w1_scale, self.w2_scale = out
         self.device = w1.device
 
 
@@ -112,9 +112,10 @@ def prepare_weights(w1, w1_scale, w2, w2_scale) -> PreparedWeights:
 class MoEPlan:
     """Shape, workspace layout and workspace tensor of one (T, K, E, H, I, B) problem."""
 
-    def __init__(self, T, K, E, E_route, H, I, B, activation, swiglu_limit, device):
+    def __init__(self, T, K, E, E_route, H, I, B, activation, swiglu_limit, device, act_terms=0):
         self.shape = _lib.Shape(T=T, K=K, E=E, E_route=E_route, H=H, I=I, B=B, weight_format=_lib.W_MXFP4,
-                                activation=activation, swiglu_limit=float(swiglu_limit))
+                                activation=activation, swiglu_limit=float(swiglu_limit), act_terms=act_terms)
+        self.terms = act_terms or 3
         self.ws = _lib.workspace_layout(self.shape)
         self.buf = torch.empty(self.ws.total_bytes + 1024, dtype=torch.uint8, device=device)
         off = (-self.buf.data_ptr()) % 1024
@@ -153,9 +154,8 @@ class MoEPlan:
         ids_o, _, _, nv_o, _ = self.sort_outputs()
         base = self.base
         _lib.check(_lib.lib().b200moe_quant_rows(
-            _ptr(x), 0, _ptr(ids_o), _ptr(nv_o), s.T, s.K, s.H, s.B, ws.max_rows,
-            ctypes.c_void_p(base + ws.off_xq_hi), ctypes.c_void_p(base + ws.off_xq_lo),
-            ctypes.c_void_p(base + ws.off_xsf_hi), ctypes.c_void_p(base + ws.off_xsf_lo), _stream()),
+            _ptr(x), 0, _ptr(ids_o), _ptr(nv_o), s.T, s.K, s.H, s.B, self.terms, 2, ws.max_rows,
+            ctypes.c_void_p(base + ws.off_xq), ctypes.c_void_p(base + ws.off_xsf), _stream()),
             "quant_rows")
 
     def quant_hidden(self, h):
@@ -164,9 +164,8 @@ class MoEPlan:
         ids_o, _, _, nv_o, _ = self.sort_outputs()
         base = self.base
         _lib.check(_lib.lib().b200moe_quant_rows(
-            _ptr(h), 1, _ptr(ids_o), _ptr(nv_o), s.T, s.K, s.I, s.B, ws.max_rows,
-            ctypes.c_void_p(base + ws.off_hq_hi), ctypes.c_void_p(base + ws.off_hq_lo),
-            ctypes.c_void_p(base + ws.off_hsf_hi), ctypes.c_void_p(base + ws.off_hsf_lo), _stream()),
+            _ptr(h), 1, _ptr(ids_o), _ptr(nv_o), s.T, s.K, s.I, s.B, self.terms, 1, ws.max_rows,
+            ctypes.c_void_p(base + ws.off_hq), ctypes.c_void_p(base + ws.off_hsf), _stream()),
             "quant_rows")
 
     def gateup(self, pw, h_out=None):
@@ -187,13 +186,13 @@ class MoEPlan:
                                     f"bad expert id flag {st[2]}")
 
 
-def get_plan(T, K, E, E_route, H, I, B, activation, swiglu_limit, device) -> MoEPlan:
-    key = (T, K, E, E_route, H, I, B, activation, float(swiglu_limit), str(device))
+def get_plan(T, K, E, E_route, H, I, B, activation, swiglu_limit, device, act_terms=0) -> MoEPlan:
+    key = (T, K, E, E_route, H, I, B, activation, float(swiglu_limit), str(device), act_terms)
     plan = _workspace_cache.get(key)
     if plan is None:
         if len(_workspace_cache) > 16:
             _workspace_cache.clear()
-        plan = MoEPlan(T, K, E, E_route, H, I, B, activation, swiglu_limit, device)
+        plan = MoEPlan(T, K, E, E_route, H, I, B, activation, swiglu_limit, device, act_terms)
         _workspace_cache[key] = plan
     return plan
 
@@ -218,9 +217,10 @@ def fused_moe(hidden_states, w1, w2, topk_weight, topk_ids, expert_mask=None,
               w1_scale=None, w2_scale=None, a1_scale=None, a2_scale=None, block_size_M=None,
               num_local_tokens=None, moe_sorting_dispatch_policy=0, dtype=None, hidden_pad=0,
               intermediate_pad=0, bias1=None, bias2=None, splitk=0, method="auto",
-              swiglu_limit=7.0):
+              swiglu_limit=7.0, act_terms=0):
     """bf16 hidden states [T,H], router top-k ids [T,K] int32 and weights [T,K] fp32, packed
-    expert weights with their scales -> bf16 [T,H].  Unsupported combinations raise, as the
+    expert weights with their scales -> bf16 [T,H].  ``act_terms`` (extension, 0 = default 3):
+    number of packed-FP4 terms that carry one activation row inside the GEMMs (2..4).  Unsupported combinations raise, as the
     reference asserts (src/contrib/fused_moe.py:252-266)."""
     if not hidden_states.is_cuda:
         raise RuntimeError("fused_moe runs on a CUDA device only (sm_100a); there is no CPU path")
@@ -246,7 +246,7 @@ def fused_moe(hidden_states, w1, w2, topk_weight, topk_ids, expert_mask=None,
     E_route = pw.E if expert_mask is None else int(expert_mask.numel())
     B = int(block_size_M) if block_size_M else pick_block(T, K, pw.E)
     act = _lib.ACT_SILU if int(activation) == ActivationType.Silu else _lib.ACT_SWIGLU
-    plan = get_plan(T, K, pw.E, E_route, H, pw.I, B, act, swiglu_limit, hidden_states.device)
+    plan = get_plan(T, K, pw.E, E_route, H, pw.I, B, act, swiglu_limit, hidden_states.device, act_terms)
     ids = topk_ids if topk_ids.dtype == torch.int32 else topk_ids.to(torch.int32)
     tw = topk_weight if topk_weight.dtype == torch.float32 else topk_weight.float()
     mask = None if expert_mask is None else expert_mask.to(torch.int32).contiguous()

@@ -27,25 +27,25 @@ def test_every_declared_symbol_is_exported(L):
 
 
 def test_struct_sizes_match_header():
-    assert ctypes.sizeof(_lib.Shape) == 40
-    assert ctypes.sizeof(_lib.Workspace) == 17 * 8
+    assert ctypes.sizeof(_lib.Shape) == 44
+    assert ctypes.sizeof(_lib.Workspace) == 13 * 8
 
 
 def test_workspace_layout_arithmetic(L):
     s = _lib.Shape(T=64, K=4, E=128, E_route=128, H=2880, I=2880, B=32, weight_format=0, activation=0,
-                   swiglu_limit=7.0)
+                   swiglu_limit=7.0, act_terms=0)
     ws = _lib.workspace_layout(s)
     assert ws.max_rows == (64 * 4 + 128 * 31 + 31) // 32 * 32
     offs = [getattr(ws, n) for n in _lib._WS_FIELDS if n.startswith("off_")]
     assert offs == sorted(offs) and all(o % 1024 == 0 for o in offs)
     assert ws.total_bytes > offs[-1]
-    assert ws.off_xq_lo - ws.off_xq_hi >= ws.max_rows * 2944
+    assert ws.off_xsf - ws.off_xq >= 3 * ws.max_rows * 2944 // 2
 
 
 @pytest.mark.parametrize("field,value", [("B", 48), ("H", 100), ("I", 0), ("K", 0), ("T", 1 << 24),
-                                         ("weight_format", 7), ("activation", 9), ("E_route", 4)])
+                                         ("weight_format", 7), ("activation", 9), ("E_route", 4), ("act_terms", 5)])
 def test_bad_shapes_are_rejected(L, field, value):
-    s = _lib.Shape(T=8, K=2, E=8, E_route=8, H=256, I=128, B=32, weight_format=0, activation=0, swiglu_limit=7.0)
+    s = _lib.Shape(T=8, K=2, E=8, E_route=8, H=256, I=128, B=32, weight_format=0, activation=0, swiglu_limit=7.0, act_terms=0)
     setattr(s, field, value)
     ws = _lib.Workspace()
     rc = L.b200moe_workspace_layout(ctypes.byref(s), ctypes.byref(ws))
@@ -56,7 +56,7 @@ def test_bad_shapes_are_rejected(L, field, value):
 
 
 def test_null_pointers_are_rejected_without_launch(L):
-    s = _lib.Shape(T=8, K=2, E=8, E_route=8, H=256, I=128, B=32, weight_format=0, activation=0, swiglu_limit=7.0)
+    s = _lib.Shape(T=8, K=2, E=8, E_route=8, H=256, I=128, B=32, weight_format=0, activation=0, swiglu_limit=7.0, act_terms=0)
     ws = _lib.workspace_layout(s)
     assert L.b200moe_gateup(ctypes.byref(s), ctypes.byref(ws), None, None, None, None, None) < 0
     assert L.b200moe_down(ctypes.byref(s), ctypes.byref(ws), None, None, None, None) < 0
@@ -64,10 +64,10 @@ def test_null_pointers_are_rejected_without_launch(L):
                              None, None, None) < 0
     assert L.b200moe_sort_align(None, None, 4, 2, 8, 32, None, None, None, None, None, None, None) < 0
     assert L.b200moe_debug_probe(1, None, None, None) < 0
-    db, sb = ctypes.c_int64(), ctypes.c_int64()
-    assert L.b200moe_prepared_bytes(ctypes.byref(s), 3, ctypes.byref(db), ctypes.byref(sb)) < 0
-    assert L.b200moe_prepared_bytes(ctypes.byref(s), 1, ctypes.byref(db), ctypes.byref(sb)) == 0
-    assert db.value == 8 * 2 * 128 * 128 + 256 and sb.value == 8 * 2 * 1 * 2 * 512
+    sb = ctypes.c_int64()
+    assert L.b200moe_prepared_scale_bytes(ctypes.byref(s), 3, ctypes.byref(sb)) < 0
+    assert L.b200moe_prepared_scale_bytes(ctypes.byref(s), 1, ctypes.byref(sb)) == 0
+    assert sb.value == 8 * 2 * 1 * 2 * 512
 
 
 def test_python_surface_fails_loudly_without_cuda():

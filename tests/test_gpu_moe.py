@@ -44,38 +44,46 @@ def _assert_close(y, ref, what=""):
     assert cos >= COS and mx <= MAX_ABS, f"{what}: cosine {cos:.6f} max_abs {mx:.3e}"
 
 
-def _sfchunks_to_rows(sf: np.ndarray, rows: int, KB: int, B: int) -> np.ndarray:
-    """[rows/B, KB, 512] scale chunks (block-local rows, tensor-memory order) -> [rows, KB*4]."""
-    c = sf.reshape(-1, KB, 32, 4, 4)[:, :, :, :B // 32]           # [blk, kb, r%32, r/32, j]
-    return c.transpose(0, 3, 2, 1, 4).reshape(-1, KB * 4)[:rows]
+def _sf_rows(sf: np.ndarray, rows: int, KB: int, B: int, NT: int, TS: int) -> np.ndarray:
+    """Scale chunks [blocks, KB, chunks, 512] -> [NT, rows, KB*4].  Term t, block-local row r sit at
+    virtual row v = t*TS + r: chunk v/128, byte (v%32)*16 + ((v%128)/32)*4 + j."""
+    chunks = (NT * TS + 127) // 128
+    c = sf.reshape(-1, KB, chunks, 32, 4, 4)                      # [blk, kb, chunk, v%32, (v%128)/32, j]
+    v = c.transpose(0, 2, 4, 3, 1, 5).reshape(c.shape[0], chunks * 128, KB * 4)   # [blk, v, kb*4+j]
+    return np.stack([v[:, t * TS:t * TS + B].reshape(-1, KB * 4)[:rows] for t in range(NT)])
 
 
-def test_quantised_rows_match_oracle_bit_for_bit():
-    T, H, I, E, K = 40, 288, 160, 8, 2             # H, I multiples of 32 but not of 128
+_E2M1 = np.array([0, .5, 1, 1.5, 2, 3, 4, 6, -0., -.5, -1, -1.5, -2, -3, -4, -6], dtype=np.float32)
+
+
+@pytest.mark.parametrize("NT", [3, 4, 2])
+def test_quantised_rows_match_oracle_bit_for_bit(NT):
+    T, H, I, E, K, B = 40, 288, 160, 8, 2, 32      # H, I multiples of 32 but not of 128
     x, tw, ids, w = _case(T, H, I, E, K, seed=4)
-    plan = get_plan(T, K, E, E, H, I, 32, 0, 7.0, torch.device(DEV))
+    plan = get_plan(T, K, E, E, H, I, B, 0, 7.0, torch.device(DEV), act_terms=NT)
     s_ids, _, _, nv, _ = plan.sort(ids.to(DEV), tw.to(DEV))
     plan.quant_input(x.to(DEV))
     torch.cuda.synchronize()
     n = int(nv[0])
+    L = plan.ws.max_rows
     HP = (H + 127) // 128 * 128
-    q_hi = plan.region("xq_hi", plan.ws.max_rows * HP).cpu().numpy().reshape(-1, HP)[:n]
-    q_lo = plan.region("xq_lo", plan.ws.max_rows * HP).cpu().numpy().reshape(-1, HP)[:n]
-    nch = plan.ws.max_rows // 32 * (HP // 128) * 512
-    sf_hi = _sfchunks_to_rows(plan.region("xsf_hi", nch).cpu().numpy(), n, HP // 128, 32)
-    sf_lo = _sfchunks_to_rows(plan.region("xsf_lo", nch).cpu().numpy(), n, HP // 128, 32)
+    packed = plan.region("xq", NT * L * HP // 2).cpu().numpy().reshape(NT, L, HP // 2)[:, :n]
+    codes = np.empty((NT, n, HP), dtype=np.uint8)
+    codes[..., 0::2], codes[..., 1::2] = packed & 0xF, packed >> 4
+    # the gate-up GEMM stacks the terms along N when that fits tensor memory twice over
+    TS = B if (NT * B <= 256 and 2 * 2 * NT * B <= 448) else 128
+    nch = L // B * (HP // 128) * ((NT * TS + 127) // 128) * 512
+    sf = _sf_rows(plan.region("xsf", nch).cpu().numpy(), n, HP // 128, B, NT, TS)
     sid = s_ids.cpu().numpy().view(np.uint32)[:n]
     tok, kk = sid & 0xFFFFFF, sid >> 24
-    eq_hi, ee_hi, eq_lo, ee_lo = orc.hilo8_quant(x)
+    ecodes, eexps = orc.fp4_terms_quant(x, NT)
     for r in range(n):
         if kk[r] < K:
-            assert np.array_equal(q_hi[r, :H], eq_hi[tok[r]].view(torch.uint8).numpy()), r
-            assert np.array_equal(q_lo[r, :H], eq_lo[tok[r]].view(torch.uint8).numpy()), r
-            assert np.array_equal(sf_hi[r, :H // 32], ee_hi[tok[r]].numpy()), r
-            assert np.array_equal(sf_lo[r, :H // 32], ee_lo[tok[r]].numpy()), r
+            assert np.array_equal(_E2M1[codes[:, r, :H]], _E2M1[ecodes[:, tok[r]]]), r
+            assert np.array_equal(sf[:, r, :H // 32], eexps[:, tok[r]]), r
         else:
-            assert not q_hi[r].any() and not q_lo[r].any()
-        assert not q_hi[r, H:].any() and not q_lo[r, H:].any()
+            assert not (codes[:, r] & 7).any()
+        assert not (codes[:, r, H:] & 7).any()
 
 
 @pytest.mark.parametrize("T,H,I,E,K,B", [(32, 512, 256, 8, 2, 32), (40, 288, 160, 8, 2, 32),
@@ -116,11 +124,15 @@ def test_unfused_stage_chain_matches_layer_oracle(T, H, I, E, K, B):
     _assert_close(y.cpu(), ref, "stage chain")
 
 
-def test_tiny_config_layer():
+@pytest.mark.parametrize("terms", [0, 2, 4])
+def test_tiny_config_layer(terms):
     c = synth.CONFIGS["tiny"]
     x, tw, ids, w = _case(c.T, c.H, c.I, c.E, c.K)
     ref = orc.torch_moe_oracle_mxfp4(x, *w, tw, ids)
-    _assert_close(_run_layer(x, tw, ids, w), ref, "tiny")
+    y = _run_layer(x, tw, ids, w, act_terms=terms)
+    _assert_close(y, ref, f"tiny terms={terms}")
+    if terms != 2:
+        assert orc.cosine(y, ref) > 0.9999
 
 
 def test_layer_matches_reference_golden_vectors():
