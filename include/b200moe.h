@@ -28,8 +28,8 @@ extern "C" {
 #define B200MOE_ACT_SILU 0   /* silu(gate) * up                        (test_moe.py:74-75) */
 #define B200MOE_ACT_SWIGLU 1 /* clamped gate*sigmoid(1.702 gate)*(up+1) (test_moe.py:76-81) */
 
-/* Shape of one MoE layer call.  B (rows per sorted block = token tile of the GEMMs) is 32, 64
- * or 128.  E is the number of experts whose weights are present (local experts under expert
+/* Shape of one MoE layer call.  B (rows per sorted block = token tile of the GEMMs) is 16, 32,
+ * 64 or 128.  E is the number of experts whose weights are present (local experts under expert
  * parallelism); E_route is the size of the routing id space (E_route >= E; equal without a mask).
  * act_terms: how many packed-FP4 terms represent one activation row inside the GEMMs (2..4;
  * 0 = default 3; 4 reproduces bf16 activations to ~1e-4 of the block maximum). */
@@ -68,7 +68,7 @@ int b200moe_workspace_layout(const b200moe_shape* shape, b200moe_workspace* ws);
  * 2 (w2, [E,H,I]). */
 int b200moe_prepared_scale_bytes(const b200moe_shape* shape, int which, int64_t* scale_bytes);
 
-/* One-off regrouping of a weight tensor's E8M0 scales into 128-row x 4-scale chunks in
+/* One-off regrouping of a weight tensor's E8M0 scales into pairs of 128-row x 4-scale chunks in
  * tensor-memory order (the packed FP4 weights themselves are consumed in place, in their canonical
  * [E, R, Kd/2] layout).  Plays the part of the reference's e8m0_shuffle / shuffle_weight
  * pre-shuffle (src/misc.py:114-128, tests/contrib/moe/test_moe.py:167-172).
@@ -89,13 +89,11 @@ int b200moe_sort_align(const int32_t* topk_ids, const float* topk_weight, int32_
  * sorted-row order (stands where the reference calls aiter's per_1x32 activation quantiser
  * followed by moe_mxfp4_sort, tests/contrib/moe/test_moe.py:665-679).
  *   src_mode 0: src is [T, Kd], row = token.   src_mode 1: src is [T, K, Kd], row = token*K + k.
- *   consumer: 2 if the rows feed the gate-up GEMM, 1 if they feed the down GEMM (selects the
- *   scale-chunk grouping that GEMM expects).
  *   q: u8 [terms, max_rows, Kpad/2], Kpad = Kd rounded up to 128.  sf: per (block of B sorted
  *   rows, 128-wide k-block) a group of 512-byte chunks. */
 int b200moe_quant_rows(const void* src_bf16, int32_t src_mode, const uint32_t* sorted_ids,
                        const int32_t* num_valid_ids, int32_t T, int32_t K, int32_t Kd, int32_t B,
-                       int32_t terms, int32_t consumer, int64_t max_rows, void* q, void* sf, void* stream);
+                       int32_t terms, int64_t max_rows, void* q, void* sf, void* stream);
 
 /* Gate-up grouped GEMM + activation: replaces moe_2stage_splitk(with_silu=True) /
  * moe_gemm_mxfp4(gate_up=True) (src/contrib/moe.py:362-702, src/contrib/moe_gemm_mxfp4.py:972-1290).

@@ -80,7 +80,7 @@ def lib() -> ctypes.CDLL:
     L.b200moe_prepared_scale_bytes.argtypes = [sp, ctypes.c_int, ctypes.POINTER(i64)]
     L.b200moe_prepare_scales.argtypes = [sp, ctypes.c_int, vp, vp, vp]
     L.b200moe_sort_align.argtypes = [vp, vp, i32, i32, i32, i32, vp, vp, vp, vp, vp, vp, vp]
-    L.b200moe_quant_rows.argtypes = [vp, i32, vp, vp, i32, i32, i32, i32, i32, i32, i64, vp, vp, vp]
+    L.b200moe_quant_rows.argtypes = [vp, i32, vp, vp, i32, i32, i32, i32, i32, i64, vp, vp, vp]
     L.b200moe_gateup.argtypes = [sp, wp, vp, vp, vp, vp, vp]
     L.b200moe_down.argtypes = [sp, wp, vp, vp, vp, vp]
     L.b200moe_combine.argtypes = [sp, wp, vp, vp, vp, vp]

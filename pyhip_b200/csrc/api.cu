@@ -24,7 +24,7 @@ static int check_shape(const b200moe_shape* s) {
   B200_CHECK_ARG(s->K >= 1 && s->K <= 32, "K=%d outside [1,32]", s->K);
   B200_CHECK_ARG(s->E >= 1 && s->E_route >= s->E && s->E_route <= 1024, "E=%d / E_route=%d invalid", s->E,
                  s->E_route);
-  B200_CHECK_ARG(s->B == 32 || s->B == 64 || s->B == 128, "B=%d not in {32,64,128}", s->B);
+  B200_CHECK_ARG(s->B == 16 || s->B == 32 || s->B == 64 || s->B == 128, "B=%d not in {16,32,64,128}", s->B);
   B200_CHECK_ARG(s->H >= 32 && s->H % 32 == 0, "H=%d must be a positive multiple of 32", s->H);
   B200_CHECK_ARG(s->I >= 32 && s->I % 32 == 0, "I=%d must be a positive multiple of 32", s->I);
   B200_CHECK_ARG(s->H % 8 == 0, "H must be a multiple of 8");
@@ -76,7 +76,7 @@ int b200moe_workspace_layout(const b200moe_shape* s, b200moe_workspace* ws) {
   ws->off_xq = take(NT * L * (HP / 2));
   ws->off_xsf = take(nb * (HP / 128) * act_sf_chunks(NT, act_term_stride(s->B, NT, 2)) * kSfChunk);
   ws->off_hq = take(NT * L * (IP / 2));
-  ws->off_hsf = take(nb * (IP / 128) * act_sf_chunks(NT, act_term_stride(s->B, NT, 1)) * kSfChunk);
+  ws->off_hsf = take(nb * (IP / 128) * act_sf_chunks(NT, act_term_stride(s->B, NT, 2)) * kSfChunk);
   ws->off_out2 = take(L * s->H * 2);
   ws->total_bytes = off;
   return 0;
@@ -86,10 +86,10 @@ int b200moe_prepared_scale_bytes(const b200moe_shape* s, int which, int64_t* sca
   if (int rc = check_shape(s)) return rc;
   B200_CHECK_ARG(which == 1 || which == 2, "which=%d must be 1 or 2", which);
   B200_CHECK_ARG(scale_bytes != nullptr, "scale_bytes is NULL");
-  const int parts = which == 1 ? 2 : 1;
-  const int rpp = which == 1 ? s->I : s->H;
+  // two 128-row tiles per chunk pair: (gate, up) of one feature tile, or two consecutive down tiles
+  const int groups = which == 1 ? (s->I + 127) / 128 : (s->H + 255) / 256;
   const int Kd = which == 1 ? s->H : s->I;
-  *scale_bytes = (int64_t)s->E * parts * ((rpp + 127) / 128) * (kp_of(Kd) / 128) * kSfChunk;
+  *scale_bytes = (int64_t)s->E * groups * (kp_of(Kd) / 128) * 2 * kSfChunk;
   return 0;
 }
 
@@ -98,10 +98,8 @@ int b200moe_prepare_scales(const b200moe_shape* s, int which, const void* w_s, v
   B200_CHECK_ARG(which == 1 || which == 2, "which=%d must be 1 or 2", which);
   B200_CHECK_ARG(w_s && out_scale, "prepare_scales: NULL pointer");
   B200_CHECK_ARG(((uintptr_t)out_scale & 15) == 0, "prepare_scales: output must be 16-byte aligned");
-  const int parts = which == 1 ? 2 : 1;
-  const int rpp = which == 1 ? s->I : s->H;
   const int Kd = which == 1 ? s->H : s->I;
-  return launch_repack_scales(w_s, out_scale, s->E, parts, rpp, Kd, (cudaStream_t)stream);
+  return launch_repack_scales(w_s, out_scale, s->E, which == 1, which == 1 ? s->I : s->H, Kd, (cudaStream_t)stream);
 }
 
 int b200moe_sort_align(const int32_t* topk_ids, const float* topk_weight, int32_t T, int32_t K, int32_t E_route,
@@ -117,15 +115,14 @@ int b200moe_sort_align(const int32_t* topk_ids, const float* topk_weight, int32_
 
 int b200moe_quant_rows(const void* src_bf16, int32_t src_mode, const uint32_t* sorted_ids,
                        const int32_t* num_valid_ids, int32_t T, int32_t K, int32_t Kd, int32_t B, int32_t terms,
-                       int32_t consumer, int64_t max_rows, void* q, void* sf, void* stream) {
+                       int64_t max_rows, void* q, void* sf, void* stream) {
   B200_CHECK_ARG(src_mode == 0 || src_mode == 1, "quant_rows: src_mode=%d", src_mode);
-  B200_CHECK_ARG(consumer == 1 || consumer == 2, "quant_rows: consumer=%d must be 1 (down) or 2 (gate-up)", consumer);
   B200_CHECK_ARG(sorted_ids && num_valid_ids && q && sf, "quant_rows: NULL pointer");
   B200_CHECK_ARG(T == 0 || src_bf16, "quant_rows: NULL source");
   B200_CHECK_ARG(((uintptr_t)src_bf16 & 15) == 0 && ((uintptr_t)q & 15) == 0,
                  "quant_rows: source and destination must be 16-byte aligned");
-  return launch_quant_rows(src_bf16, src_mode, sorted_ids, num_valid_ids, T, K, Kd, B, terms, consumer, max_rows, q,
-                           sf, (cudaStream_t)stream);
+  return launch_quant_rows(src_bf16, src_mode, sorted_ids, num_valid_ids, T, K, Kd, B, terms, max_rows, q, sf,
+                           (cudaStream_t)stream);
 }
 
 static void fill_common(GemmArgs& g, const b200moe_shape* s, const b200moe_workspace* ws, uint8_t* base) {
@@ -209,7 +206,7 @@ int b200moe_forward(const b200moe_shape* s, const b200moe_workspace* ws, void* w
                               (int32_t*)(base + ws->off_loc), stream);
   if (rc) return rc;
   rc = b200moe_quant_rows(x_bf16, 0, (const uint32_t*)(base + ws->off_sorted_ids),
-                          (const int32_t*)(base + ws->off_num_valid), s->T, s->K, s->H, s->B, terms_of(s), 2,
+                          (const int32_t*)(base + ws->off_num_valid), s->T, s->K, s->H, s->B, terms_of(s),
                           ws->max_rows, base + ws->off_xq, base + ws->off_xsf, stream);
   if (rc) return rc;
   rc = b200moe_gateup(s, ws, workspace, w1_q, w1_scale, nullptr, stream);

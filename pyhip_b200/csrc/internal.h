@@ -55,12 +55,10 @@ int launch_sort_align(const int32_t* ids, const float* w, int T, int K, int E, i
                       uint32_t* sorted_ids, float* sorted_w, int32_t* sorted_e, int32_t* num_valid,
                       int32_t* loc, cudaStream_t st);
 int launch_quant_rows(const void* src, int src_mode, const uint32_t* sorted_ids, const int32_t* num_valid,
-                      int T, int K, int Kd, int B, int NT, int parts, int64_t max_rows, void* q, void* sf,
-                      cudaStream_t st);
+                      int T, int K, int Kd, int B, int NT, int64_t max_rows, void* q, void* sf, cudaStream_t st);
 int launch_combine(const void* out2, const int32_t* loc, const float* topk_w, void* y, int T, int K, int H,
                    cudaStream_t st);
-int launch_repack_scales(const void* w_s, void* out, int E, int parts, int rows_per_part, int Kd,
-                         cudaStream_t st);
+int launch_repack_scales(const void* w_s, void* out, int E, bool gateup, int rows, int Kd, cudaStream_t st);
 
 // grouped GEMM (moe_gemm_sm100.cu)
 struct GemmArgs {
@@ -75,7 +73,7 @@ struct GemmArgs {
   int64_t max_rows;
   int NT;              // activation terms
   const void* w_data;  // canonical packed FP4 [E, parts*rows, Kd/2], used in place
-  const void* w_scale; // [E, MT, KB, parts, 512]
+  const void* w_scale; // [E, MT, KB, 2, 512]
   const void* a_q;     // [NT, max_rows, KP/2] packed FP4 terms
   const void* asf;     // [max_rows/N, KB, chunks, 512]
   const uint32_t* sorted_ids;

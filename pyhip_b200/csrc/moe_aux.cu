@@ -234,9 +234,8 @@ quant_rows_kernel(const __nv_bfloat16* __restrict__ src, int src_mode, const uin
 }
 
 int launch_quant_rows(const void* src, int src_mode, const uint32_t* sorted_ids, const int32_t* num_valid,
-                      int T, int K, int Kd, int B, int NT, int parts, int64_t max_rows, void* q, void* sf,
-                      cudaStream_t st) {
-  B200_CHECK_ARG(B == 32 || B == 64 || B == 128, "quant_rows: B=%d not in {32,64,128}", B);
+                      int T, int K, int Kd, int B, int NT, int64_t max_rows, void* q, void* sf, cudaStream_t st) {
+  B200_CHECK_ARG(B == 16 || B == 32 || B == 64 || B == 128, "quant_rows: B=%d not in {16,32,64,128}", B);
   B200_CHECK_ARG(NT >= 2 && NT <= 4, "quant_rows: %d activation terms (2..4 supported)", NT);
   B200_CHECK_ARG(Kd % 32 == 0, "quant_rows: Kd=%d must be a multiple of 32", Kd);
   const int KP = (int)round_up64(Kd, 128);
@@ -244,7 +243,7 @@ int launch_quant_rows(const void* src, int src_mode, const uint32_t* sorted_ids,
   int blocks = (int)std::min<int64_t>((work + 255) / 256, 148 * 16);
   if (blocks < 1) blocks = 1;
   quant_rows_kernel<<<blocks, 256, 0, st>>>(reinterpret_cast<const __nv_bfloat16*>(src), src_mode, sorted_ids,
-                                            num_valid, T, K, Kd, KP, B, NT, act_term_stride(B, NT, parts), max_rows,
+                                            num_valid, T, K, Kd, KP, B, NT, act_term_stride(B, NT, 2), max_rows,
                                             (uint8_t*)q, (uint8_t*)sf);
   B200_CHECK_CUDA(cudaGetLastError());
   return 0;
@@ -303,37 +302,43 @@ int launch_combine(const void* out2, const int32_t* loc, const float* topk_w, vo
 }
 
 // =====================================================================================
-// weight-scale repack: [E, parts*rows, Kd/32] bytes -> [E, MT, KB, parts, 512] chunks in
-// tensor-memory order; rows / k-blocks that do not exist get exponent 127 (= 1.0).
+// weight-scale repack: [E, R, Kd/32] bytes -> [E, MT, KB, 2, 512] chunks in tensor-memory order.
+// A chunk = 128 rows x 4 scales.  The two chunks of a group are the tiles one pipeline stage
+// carries: gate rows [mt*128, +128) and up rows I + [mt*128, +128) of w1 (R = 2I), or rows
+// [mt*256, +128) and [mt*256+128, +128) of w2 (R = H).  Rows / k-blocks that do not exist get
+// exponent 127 (= 1.0).
 // =====================================================================================
 __global__ void __launch_bounds__(256)
-repack_scales_kernel(const uint8_t* __restrict__ src, uint8_t* __restrict__ dst, int E, int parts, int rpp,
+repack_scales_kernel(const uint8_t* __restrict__ src, uint8_t* __restrict__ dst, int E, int gateup, int rows,
                      int nsf, int MT, int KB) {
-  const int64_t total = (int64_t)E * parts * MT * KB * kSfChunk;
+  const int64_t total = (int64_t)E * MT * KB * 2 * kSfChunk;
+  const int R = gateup ? 2 * rows : rows;
   for (int64_t g = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; g < total;
        g += (int64_t)gridDim.x * blockDim.x) {
     int off = (int)(g % kSfChunk);
     int64_t c = g / kSfChunk;
-    int part = (int)(c % parts); c /= parts;
+    int part = (int)(c % 2); c /= 2;
     int kb = (int)(c % KB); c /= KB;
     int mt = (int)(c % MT);
     int e = (int)(c / MT);
     int r_local = (off >> 4) + 32 * ((off & 15) >> 2);
     int j = off & 3;
-    int row = mt * 128 + r_local, kidx = kb * 4 + j;
+    int kidx = kb * 4 + j;
+    int row_in = gateup ? mt * 128 + r_local : (2 * mt + part) * 128 + r_local;   // row inside its part
+    int row = gateup ? part * rows + row_in : row_in;
     uint8_t v = 127;
-    if (row < rpp && kidx < nsf) v = src[((int64_t)e * parts * rpp + (int64_t)part * rpp + row) * nsf + kidx];
+    if (row_in < rows && kidx < nsf) v = src[((int64_t)e * R + row) * nsf + kidx];
     dst[g] = v;
   }
 }
 
-int launch_repack_scales(const void* w_s, void* out, int E, int parts, int rows_per_part, int Kd,
-                         cudaStream_t st) {
-  const int KB = (int)round_up64(Kd, 128) / 128, MT = (rows_per_part + 127) / 128;
-  int64_t total = (int64_t)E * parts * MT * KB * kSfChunk;
+int launch_repack_scales(const void* w_s, void* out, int E, bool gateup, int rows, int Kd, cudaStream_t st) {
+  const int KB = (int)round_up64(Kd, 128) / 128;
+  const int MT = gateup ? (rows + 127) / 128 : (rows + 255) / 256;
+  int64_t total = (int64_t)E * MT * KB * 2 * kSfChunk;
   int blocks = (int)std::min<int64_t>((total + 255) / 256, 148 * 32);
-  repack_scales_kernel<<<blocks, 256, 0, st>>>((const uint8_t*)w_s, (uint8_t*)out, E, parts, rows_per_part,
-                                               Kd / 32, MT, KB);
+  repack_scales_kernel<<<blocks, 256, 0, st>>>((const uint8_t*)w_s, (uint8_t*)out, E, gateup ? 1 : 0, rows, Kd / 32,
+                                               MT, KB);
   B200_CHECK_CUDA(cudaGetLastError());
   return 0;
 }

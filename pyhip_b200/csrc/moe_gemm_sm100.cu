@@ -16,6 +16,9 @@
 //     is its own instruction into the same accumulator.
 // Block scales travel shared memory -> tensor memory with tcgen05.cp and are applied by the MMA.
 //
+// A pipeline stage always carries TWO 128-row weight tiles that share one activation tile: the
+// gate and the up rows of the same features (gate-up GEMM), or two consecutive row tiles of
+// the down projection.
 // Warp roles (192 threads): warp 0 = TMA producer, warp 1 = MMA issuer + TMEM owner,
 // warps 2-5 = epilogue (one TMEM lane quadrant each).  Persistent CTAs walk the work list
 // (sorted block, 128-row weight tile) in block-major order so that the CTAs running at the same
@@ -49,9 +52,9 @@ constexpr int kSfCol0 = kAccColsLimit;   // scale columns: 2 buffers x {A: 8 col
 constexpr int kSmemLimit = 232448;       // 227 KB
 
 struct GemmParams {
-  CUtensorMap tmW;     // weights     (K, rows, parts, E)         box (128, 128, parts, 1)
+  CUtensorMap tmW;     // weights: gate-up (K, I, 2, E) box (128,128,2,1); down (K, H, 1, E) box (128,256,1,1)
   CUtensorMap tmA;     // activations (KP, max_rows, NT terms)    box (128, B, NT)
-  const uint8_t* w_scale;   // [E, MT, KB, parts, 512]
+  const uint8_t* w_scale;   // [E, MT, KB, 2, 512]
   const uint8_t* asf;       // [blocks, KB, chunks, 512]
   const uint32_t* sorted_ids;
   const int32_t* sorted_e;
@@ -154,7 +157,7 @@ __device__ __forceinline__ void tma_load_4d(uint32_t dst, const CUtensorMap* map
 template <bool GATEUP>
 __global__ void __launch_bounds__(kThreads, 1)
 moe_grouped_gemm_kernel(const __grid_constant__ GemmParams p) {
-  constexpr int NA = GATEUP ? 2 : 1;
+  constexpr int NA = 2;   // weight tiles per stage
   extern __shared__ uint8_t smem_raw[];
   // 1024-byte alignment covers every swizzle atom used here
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -220,7 +223,7 @@ moe_grouped_gemm_kernel(const __grid_constant__ GemmParams p) {
           const uint32_t st = stage0 + (uint32_t)stage * geo.stage_bytes;
           const uint32_t full = smem_u32(&ctl->full[stage]);
           mbar_expect_tx(full, geo.tx_bytes);
-          tma_load_4d(st, &p.tmW, full, kb * kTileK, m * kTileM, 0, e);
+          tma_load_4d(st, &p.tmW, full, kb * kTileK, m * (GATEUP ? kTileM : 2 * kTileM), 0, e);
           tma_load_3d(st + geo.a_bytes, &p.tmA, full, kb * kTileK, r0, 0);
           bulk_load(st + geo.a_bytes + geo.b_bytes, sfa, (uint32_t)geo.sfa_bytes, full);
           bulk_load(st + geo.a_bytes + geo.b_bytes + geo.sfa_bytes, sfb, (uint32_t)geo.sfb_bytes, full);
@@ -270,7 +273,7 @@ moe_grouped_gemm_kernel(const __grid_constant__ GemmParams p) {
           const uint32_t sfa_t = tmem_base + kSfCol0 + sf_buf * 32;
           const uint32_t sfb_t = sfa_t + 8;
           utccp_sf(sfa_t, sf_lo);
-          if (GATEUP) utccp_sf(sfa_t + 4, sf_lo + (kSfChunk >> 4));
+          utccp_sf(sfa_t + 4, sf_lo + (kSfChunk >> 4));
           for (int c = 0; c < sfb_chunks; ++c)
             utccp_sf(sfb_t + 4 * c, sf_lo + ((geo.sfa_bytes + c * kSfChunk) >> 4));
           const uint32_t first = kb != 0;
@@ -278,9 +281,8 @@ moe_grouped_gemm_kernel(const __grid_constant__ GemmParams p) {
 #pragma unroll
             for (int s = 0; s < 2; ++s) {
               umma_mxf4(d0, a_lo + 2 * s, b_lo + 2 * s, idesc[s], sfa_t, sfb_t, s == 0 ? first : 1u);
-              if (GATEUP)
-                umma_mxf4(d0 + ncol, a_lo + (kATileBytes >> 4) + 2 * s, b_lo + 2 * s, idesc[s], sfa_t + 4, sfb_t,
-                          s == 0 ? first : 1u);
+              umma_mxf4(d0 + ncol, a_lo + (kATileBytes >> 4) + 2 * s, b_lo + 2 * s, idesc[s], sfa_t + 4, sfb_t,
+                        s == 0 ? first : 1u);
             }
           } else {
 #pragma unroll
@@ -288,9 +290,8 @@ moe_grouped_gemm_kernel(const __grid_constant__ GemmParams p) {
               for (int t = 0; t < NT; ++t) {
                 const uint32_t accum = (s == 0 && t == 0) ? first : 1u;
                 umma_mxf4(d0, a_lo + 2 * s, b_lo + t * term_lo + 2 * s, idesc[s], sfa_t, sfb_t + 4 * t, accum);
-                if (GATEUP)
-                  umma_mxf4(d0 + ncol, a_lo + (kATileBytes >> 4) + 2 * s, b_lo + t * term_lo + 2 * s, idesc[s],
-                            sfa_t + 4, sfb_t + 4 * t, accum);
+                umma_mxf4(d0 + ncol, a_lo + (kATileBytes >> 4) + 2 * s, b_lo + t * term_lo + 2 * s, idesc[s],
+                          sfa_t + 4, sfb_t + 4 * t, accum);
               }
             }
           }
@@ -315,11 +316,12 @@ moe_grouped_gemm_kernel(const __grid_constant__ GemmParams p) {
     for (int w = blockIdx.x; w < total_work; w += gridDim.x) {
       const int b = w / p.MT, m = w - b * p.MT;
       const int r0 = b * B;
-      const int j = m * kTileM + row_local;    // output feature of this thread
+      // output feature of this thread: gate-up pairs gate/up of feature j; down holds j and j+128
+      const int j = (GATEUP ? m * kTileM : m * 2 * kTileM) + row_local;
       // valid rows are a prefix of the block (padding sentinels follow)
       int nvalid = 0;
       for (int q = 0; q < B; q += 32) {
-        const uint32_t id = p.sorted_ids[r0 + q + lane];
+        const uint32_t id = (q + lane < B) ? p.sorted_ids[r0 + q + lane] : 0xFFFFFFFFu;
         nvalid += __popc(__ballot_sync(0xffffffffu, (int)(id >> 24) < p.topk && (int)(id & 0xFFFFFFu) < p.T));
       }
       if (!mbar_wait(smem_u32(&ctl->tmem_full[acc]), acc_phase, abort_word, 0x400 + acc)) break;
@@ -330,23 +332,23 @@ moe_grouped_gemm_kernel(const __grid_constant__ GemmParams p) {
       for (int c0 = 0; c0 < nvalid; c0 += 16) {
         uint32_t g[16], u[16];
         tmem_ld_32x32b_x16(t0 + c0, g);
-        if (GATEUP) tmem_ld_32x32b_x16(t0 + ncol + c0, u);
+        tmem_ld_32x32b_x16(t0 + ncol + c0, u);
         tmem_ld_wait();
         if (merged) {
           // the terms were separate column groups of one instruction: add them up
           for (int t = 1; t < NT; ++t) {
             uint32_t g2[16], u2[16];
             tmem_ld_32x32b_x16(t0 + t * B + c0, g2);
-            if (GATEUP) tmem_ld_32x32b_x16(t0 + ncol + t * B + c0, u2);
+            tmem_ld_32x32b_x16(t0 + ncol + t * B + c0, u2);
             tmem_ld_wait();
 #pragma unroll
             for (int n = 0; n < 16; ++n) {
               g[n] = __float_as_uint(__uint_as_float(g[n]) + __uint_as_float(g2[n]));
-              if (GATEUP) u[n] = __float_as_uint(__uint_as_float(u[n]) + __uint_as_float(u2[n]));
+              u[n] = __float_as_uint(__uint_as_float(u[n]) + __uint_as_float(u2[n]));
             }
           }
         }
-        if ((c0 & 31) == 0) my_id = p.sorted_ids[r0 + c0 + lane];
+        if ((c0 & 31) == 0 && GATEUP) my_id = p.sorted_ids[min(r0 + c0 + lane, r0 + B - 1)];
         if (GATEUP) {
           if (p.h_out != nullptr) {
 #pragma unroll
@@ -388,11 +390,13 @@ moe_grouped_gemm_kernel(const __grid_constant__ GemmParams p) {
             }
           }
         } else {
-          if (j_ok) {
+          const bool j2_ok = j + kTileM < p.rows;
 #pragma unroll
-            for (int n = 0; n < 16; ++n) {
-              if (c0 + n < nvalid)
-                p.out2[((int64_t)r0 + c0 + n) * p.rows + j] = __float2bfloat16_rn(__uint_as_float(g[n]));
+          for (int n = 0; n < 16; ++n) {
+            if (c0 + n < nvalid) {
+              __nv_bfloat16* row = p.out2 + ((int64_t)r0 + c0 + n) * p.rows + j;
+              if (j_ok) row[0] = __float2bfloat16_rn(__uint_as_float(g[n]));
+              if (j2_ok) row[kTileM] = __float2bfloat16_rn(__uint_as_float(u[n]));
             }
           }
         }
@@ -463,35 +467,38 @@ static int encode_map_sw(CUtensorMap* map, CUtensorMapDataType type, int rank, c
 }
 
 int launch_grouped_gemm(const GemmArgs& a, cudaStream_t st) {
-  B200_CHECK_ARG(a.N == 32 || a.N == 64 || a.N == 128, "grouped gemm: token tile %d not in {32,64,128}", a.N);
+  B200_CHECK_ARG(a.N == 16 || a.N == 32 || a.N == 64 || a.N == 128, "grouped gemm: token tile %d not in {16,32,64,128}",
+                 a.N);
   B200_CHECK_ARG(a.NT >= 2 && a.NT <= kMaxTerms, "grouped gemm: %d activation terms (2..4 supported)", a.NT);
   B200_CHECK_ARG(a.Kd % 32 == 0 && a.rows > 0 && a.E > 0, "grouped gemm: bad shape");
   B200_CHECK_ARG(a.max_rows % a.N == 0, "grouped gemm: max_rows %% B != 0");
   B200_CHECK_ARG(((uintptr_t)a.w_data & 15) == 0 && ((uintptr_t)a.a_q & 15) == 0,
                  "grouped gemm: operand tensors must be 16-byte aligned");
   const int KP = (int)round_up64(a.Kd, kTileK);
-  const int parts = a.gateup ? 2 : 1;
   GemmParams p;
   memset(&p, 0, sizeof(p));
-  p.B = a.N; p.NT = a.NT; p.rows = a.rows; p.KB = KP / kTileK; p.MT = (a.rows + kTileM - 1) / kTileM;
+  p.B = a.N; p.NT = a.NT; p.rows = a.rows; p.KB = KP / kTileK;
+  p.MT = a.gateup ? (a.rows + kTileM - 1) / kTileM : (a.rows + 2 * kTileM - 1) / (2 * kTileM);
   p.E = a.E; p.topk = a.topk; p.T = a.T; p.activation = a.activation;
   p.swiglu_limit = a.swiglu_limit; p.max_rows = a.max_rows;
   p.w_scale = (const uint8_t*)a.w_scale; p.asf = (const uint8_t*)a.asf;
   p.sorted_ids = a.sorted_ids; p.sorted_e = a.sorted_e; p.num_valid = a.num_valid; p.status = a.status;
   p.h_out = (__nv_bfloat16*)a.h_out; p.oq = (uint8_t*)a.oq; p.osf = (uint8_t*)a.osf;
-  p.out_kp = a.out_kp; p.out_kb = a.out_kp / kTileK; p.out_ts = act_term_stride(a.N, a.NT, 1);
+  p.out_kp = a.out_kp; p.out_kb = a.out_kp / kTileK; p.out_ts = act_term_stride(a.N, a.NT, 2);
   p.oq_term_stride = a.max_rows * (int64_t)(a.out_kp / 2);
   p.out2 = (__nv_bfloat16*)a.out2;
   if (a.gateup && a.h_out == nullptr)
     B200_CHECK_ARG(a.out_kp == (int)round_up64(a.rows, kTileK) && a.oq && a.osf,
                    "gate-up: fused output buffers missing");
 
-  // weights: canonical packed FP4 [E, parts, rows, Kd/2]; K and row tails are zero-filled by TMA
+  // weights: canonical packed FP4, gate-up [E, 2, I, H/2] / down [E, H, I/2]; K and row tails are
+  // zero-filled by TMA
   const cuuint64_t row_pitch = (cuuint64_t)a.Kd / 2;
   {
-    cuuint64_t dims[4] = {(cuuint64_t)a.Kd, (cuuint64_t)a.rows, (cuuint64_t)parts, (cuuint64_t)a.E};
+    const cuuint64_t parts = a.gateup ? 2 : 1;
+    cuuint64_t dims[4] = {(cuuint64_t)a.Kd, (cuuint64_t)a.rows, parts, (cuuint64_t)a.E};
     cuuint64_t strides[3] = {row_pitch, row_pitch * (cuuint64_t)a.rows, row_pitch * (cuuint64_t)a.rows * parts};
-    cuuint32_t box[4] = {kTileK, kTileM, (cuuint32_t)parts, 1};
+    cuuint32_t box[4] = {kTileK, a.gateup ? (cuuint32_t)kTileM : 2u * kTileM, a.gateup ? 2u : 1u, 1};
     int rc = encode_map_sw(&p.tmW, CU_TENSOR_MAP_DATA_TYPE_16U4_ALIGN8B, 4, a.w_data, dims, strides, box,
                            CU_TENSOR_MAP_SWIZZLE_64B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, "weights");
     if (rc) return rc;
@@ -505,7 +512,7 @@ int launch_grouped_gemm(const GemmArgs& a, cudaStream_t st) {
     if (rc) return rc;
   }
 
-  const StageGeom geo = stage_geom(parts, a.N, a.NT);
+  const StageGeom geo = stage_geom(2, a.N, a.NT);
   int stages = (kSmemLimit - 2048) / geo.stage_bytes;
   stages = std::min(stages, kMaxStages);
   B200_CHECK_ARG(stages >= 2, "grouped gemm: tile does not fit shared memory");

@@ -50,9 +50,11 @@ def pick_block(T: int, K: int, E: int) -> int:
     expert so the weight-streaming regime wastes no tensor work on padding; the reference makes
     the same decode/prefill split on T*K/E (src/contrib/fused_moe.py:285-300,358-362)."""
     per_expert = (T * K) / max(E, 1)
-    if per_expert <= 32:
+    if per_expert <= 4:
+        return 16
+    if per_expert <= 20:
         return 32
-    if per_expert <= 96:
+    if per_expert <= 80:
         return 64
     return 128
 
@@ -154,7 +156,7 @@ class MoEPlan:
         ids_o, _, _, nv_o, _ = self.sort_outputs()
         base = self.base
         _lib.check(_lib.lib().b200moe_quant_rows(
-            _ptr(x), 0, _ptr(ids_o), _ptr(nv_o), s.T, s.K, s.H, s.B, self.terms, 2, ws.max_rows,
+            _ptr(x), 0, _ptr(ids_o), _ptr(nv_o), s.T, s.K, s.H, s.B, self.terms, ws.max_rows,
             ctypes.c_void_p(base + ws.off_xq), ctypes.c_void_p(base + ws.off_xsf), _stream()),
             "quant_rows")
 
@@ -164,7 +166,7 @@ class MoEPlan:
         ids_o, _, _, nv_o, _ = self.sort_outputs()
         base = self.base
         _lib.check(_lib.lib().b200moe_quant_rows(
-            _ptr(h), 1, _ptr(ids_o), _ptr(nv_o), s.T, s.K, s.I, s.B, self.terms, 1, ws.max_rows,
+            _ptr(h), 1, _ptr(ids_o), _ptr(nv_o), s.T, s.K, s.I, s.B, self.terms, ws.max_rows,
             ctypes.c_void_p(base + ws.off_hq), ctypes.c_void_p(base + ws.off_hsf), _stream()),
             "quant_rows")
 
