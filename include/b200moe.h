@@ -125,6 +125,22 @@ int b200moe_forward(const b200moe_shape* shape, const b200moe_workspace* ws, voi
                     const int32_t* expert_mask, const void* w1_q, const void* w1_scale_prepared,
                     const void* w2_q, const void* w2_scale_prepared, void* y_bf16, void* stream);
 
+/* Whole layer WITHOUT a caller-provided workspace.  No counterpart in the reference (pyhip's
+ * wrapper lets torch allocate its intermediates on every call).  It exists for hosts that cannot
+ * allocate device memory when the layer runs -- e.g. a serving process that gave all free HBM to
+ * its cache pool at start-up, or a foreign-language host with no allocator binding.  The scratch
+ * lives in a fixed array inside the library image: B200MOE_STATIC_SCRATCH_BYTES are held on every
+ * GPU that loads the library, until it is unloaded.  A shape whose workspace layout
+ * (b200moe_workspace_layout) is larger is refused with an argument error.  All calls on a device
+ * share that array: calls whose GPU work may overlap must be serialised by the caller.  The first
+ * call on each device performs a one-time address look-up and should be made outside stream
+ * capture.  Same arguments and result as b200moe_forward otherwise; allocates nothing. */
+#define B200MOE_STATIC_SCRATCH_BYTES (48ll << 20)
+int b200moe_forward_static(const b200moe_shape* shape, const void* x_bf16, const int32_t* topk_ids,
+                           const float* topk_weight, const int32_t* expert_mask, const void* w1_q,
+                           const void* w1_scale_prepared, const void* w2_q, const void* w2_scale_prepared,
+                           void* y_bf16, void* stream);
+
 /* Hardware known-answer probes used by the GPU test-suite (tiny, single CTA, bounded waits).
  *   which = 1: TMA load of one 128x128 packed-FP4 tile (64-byte swizzle) from `in` (8192 bytes)
  *              -> `out` receives the 8192-byte shared-memory image.
