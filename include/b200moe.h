@@ -28,8 +28,8 @@ extern "C" {
 #define B200MOE_ACT_SILU 0   /* silu(gate) * up                        (test_moe.py:74-75) */
 #define B200MOE_ACT_SWIGLU 1 /* clamped gate*sigmoid(1.702 gate)*(up+1) (test_moe.py:76-81) */
 
-/* Shape of one MoE layer call.  B (rows per sorted block = token tile of the GEMMs) is 16, 32,
- * 64 or 128.  E is the number of experts whose weights are present (local experts under expert
+/* Shape of one MoE layer call.  B (rows per sorted block = token tile of the GEMMs) is a multiple
+ * of 16 up to 128.  E is the number of experts whose weights are present (local experts under expert
  * parallelism); E_route is the size of the routing id space (E_route >= E; equal without a mask).
  * act_terms: how many packed-FP4 terms represent one activation row inside the GEMMs (2..4;
  * 0 = default 3; 4 reproduces bf16 activations to ~1e-4 of the block maximum). */

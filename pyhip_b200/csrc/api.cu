@@ -24,7 +24,7 @@ static int check_shape(const b200moe_shape* s) {
   B200_CHECK_ARG(s->K >= 1 && s->K <= 32, "K=%d outside [1,32]", s->K);
   B200_CHECK_ARG(s->E >= 1 && s->E_route >= s->E && s->E_route <= 1024, "E=%d / E_route=%d invalid", s->E,
                  s->E_route);
-  B200_CHECK_ARG(s->B == 16 || s->B == 32 || s->B == 64 || s->B == 128, "B=%d not in {16,32,64,128}", s->B);
+  B200_CHECK_ARG(s->B >= 16 && s->B <= 128 && s->B % 16 == 0, "B=%d is not a multiple of 16 in [16,128]", s->B);
   B200_CHECK_ARG(s->H >= 32 && s->H % 32 == 0, "H=%d must be a positive multiple of 32", s->H);
   B200_CHECK_ARG(s->I >= 32 && s->I % 32 == 0, "I=%d must be a positive multiple of 32", s->I);
   B200_CHECK_ARG(s->H % 8 == 0, "H must be a multiple of 8");

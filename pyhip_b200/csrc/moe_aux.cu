@@ -235,7 +235,7 @@ quant_rows_kernel(const __nv_bfloat16* __restrict__ src, int src_mode, const uin
 
 int launch_quant_rows(const void* src, int src_mode, const uint32_t* sorted_ids, const int32_t* num_valid,
                       int T, int K, int Kd, int B, int NT, int64_t max_rows, void* q, void* sf, cudaStream_t st) {
-  B200_CHECK_ARG(B == 16 || B == 32 || B == 64 || B == 128, "quant_rows: B=%d not in {16,32,64,128}", B);
+  B200_CHECK_ARG(B >= 16 && B <= 128 && B % 16 == 0, "quant_rows: B=%d is not a multiple of 16 in [16,128]", B);
   B200_CHECK_ARG(NT >= 2 && NT <= 4, "quant_rows: %d activation terms (2..4 supported)", NT);
   B200_CHECK_ARG(Kd % 32 == 0, "quant_rows: Kd=%d must be a multiple of 32", Kd);
   const int KP = (int)round_up64(Kd, 128);

@@ -19,8 +19,10 @@
 // A pipeline stage always carries TWO 128-row weight tiles that share one activation tile: the
 // gate and the up rows of the same features (gate-up GEMM), or two consecutive row tiles of
 // the down projection.
-// Warp roles (192 threads): warp 0 = TMA producer, warp 1 = MMA issuer + TMEM owner,
-// warps 2-5 = epilogue (one TMEM lane quadrant each).  Persistent CTAs walk the work list
+// Warp roles (320 threads): warp 0 = TMA producer, warp 1 = MMA issuer + TMEM owner,
+// warps 2-9 = epilogue (two per TMEM lane quadrant).  The gate-up epilogue applies the activation,
+// parks the bf16 result in a shared-memory staging tile and re-quantises it block-wise into the
+// down GEMM's operand format, overlapped with the next tile's main loop.  Persistent CTAs walk the work list
 // (sorted block, 128-row weight tile) in block-major order so that the CTAs running at the same
 // time share activation tiles and neighbouring blocks of an expert share weight tiles in L2.
 // The issuing threads are the scarce resource at small token tiles, so a pipeline stage is
@@ -40,8 +42,9 @@
 
 namespace b200moe {
 
-constexpr int kThreads = 192;
+constexpr int kThreads = 320;          // TMA warp, MMA warp, 8 epilogue warps
 constexpr int kTileM = 128;          // weight rows per MMA
+constexpr int kStagePitch = kTileM * 2 + 16;   // bytes per token row of the bf16 staging tile
 constexpr int kTileK = 128;          // K per pipeline stage (2 MMA K-steps of 64)
 constexpr int kRowBytes = kTileK / 2;                // one tile row: 128 packed FP4 = 64 bytes
 constexpr int kATileBytes = kTileM * kRowBytes;      // 8 KB
@@ -102,12 +105,12 @@ __device__ __forceinline__ float gateup_act(float g, float u, int activation, fl
   g = bf16r(g);
   u = bf16r(u);
   if (activation == B200MOE_ACT_SILU) {
-    float s = bf16r(g / (1.f + __expf(-g)));
+    float s = bf16r(g * __frcp_rn(1.f + __expf(-g)));
     return bf16r(s * u);
   }
   g = fminf(g, limit);
   u = fminf(fmaxf(u, -limit), limit);
-  return bf16r(g * (1.f / (1.f + __expf(-1.702f * g))) * (u + 1.f));
+  return bf16r(g * __frcp_rn(1.f + __expf(-1.702f * g)) * (u + 1.f));
 }
 
 // descriptor halves: the high word is constant per layout, the low word carries the address
@@ -146,6 +149,53 @@ __device__ __forceinline__ void tmem_ld_32x32b_x16(uint32_t taddr, uint32_t (&r)
       : "r"(taddr)
       : "memory");
 }
+// named barriers among the eight epilogue warps (barrier 0 belongs to __syncthreads)
+__device__ __forceinline__ void epi_sync() { asm volatile("bar.sync 2, 256;" ::: "memory"); }
+__device__ __forceinline__ bool epi_all(bool pred) {
+  uint32_t out;
+  asm volatile(
+      "{\n\t.reg .pred p, q;\n\t"
+      "setp.ne.b32 p, %1, 0;\n\t"
+      "bar.red.and.pred q, 1, 256, p;\n\t"
+      "selp.u32 %0, 1, 0, q;\n\t}"
+      : "=r"(out)
+      : "r"((uint32_t)pred)
+      : "memory");
+  return out != 0;
+}
+__device__ __forceinline__ void st_shared_u16(uint32_t addr, unsigned short v) {
+  asm volatile("st.shared.u16 [%0], %1;" ::"r"(addr), "h"(v) : "memory");
+}
+__device__ __forceinline__ uint4 ld_shared_v4(uint32_t addr) {
+  uint4 v;
+  asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(addr));
+  return v;
+}
+
+// quantise 32 floats to E2M1 with a shared E8M0 scale (same rule as the stand-alone quantiser):
+// q gets 16 bytes (low nibble = even element), x is replaced by the residual
+__device__ __forceinline__ int quant_block32_fp4(float (&x)[32], uint4& q) {
+  float amax = 0.f;
+#pragma unroll
+  for (int i = 0; i < 32; ++i) amax = fmaxf(amax, fabsf(x[i]));
+  const int e = max((int)((__float_as_uint(amax) >> 23) & 0xFF) - 2, 0);
+  const float inv = __uint_as_float((uint32_t)(254 - e) << 23);
+  const float sc = __uint_as_float(e == 0 ? 0x00400000u : ((uint32_t)e << 23));
+  uint32_t w[4] = {0, 0, 0, 0};
+#pragma unroll
+  for (int i = 0; i < 32; i += 2) {
+    const __nv_fp4x2_storage_t pk =
+        __nv_cvt_float2_to_fp4x2(make_float2(x[i] * inv, x[i + 1] * inv), __NV_E2M1, cudaRoundNearest);
+    w[i >> 3] |= (uint32_t)pk << (((i >> 1) & 3) * 8);
+    __half2_raw h = __nv_cvt_fp4x2_to_halfraw2(pk, __NV_E2M1);
+    const float2 f = __half22float2(*reinterpret_cast<__half2*>(&h));
+    x[i] -= f.x * sc;
+    x[i + 1] -= f.y * sc;
+  }
+  q = make_uint4(w[0], w[1], w[2], w[3]);
+  return e;
+}
+
 __device__ __forceinline__ void tma_load_4d(uint32_t dst, const CUtensorMap* map, uint32_t bar, int c0, int c1,
                                             int c2, int c3) {
   asm volatile(
@@ -182,7 +232,7 @@ moe_grouped_gemm_kernel(const __grid_constant__ GemmParams p) {
     }
     for (int a = 0; a < 2; ++a) {
       mbar_init(smem_u32(&ctl->tmem_full[a]), 1);
-      mbar_init(smem_u32(&ctl->tmem_empty[a]), 4);
+      mbar_init(smem_u32(&ctl->tmem_empty[a]), 8);
     }
     ctl->abort_word = 0;
     fence_mbar_init();
@@ -308,9 +358,16 @@ moe_grouped_gemm_kernel(const __grid_constant__ GemmParams p) {
     }
   } else {
     // ------------------------------------------------------------------ epilogue warps
+    // Eight warps: warp w reads TMEM lanes [32*(w%4), +32) (the hardware's lane-quadrant rule);
+    // the two warps of a quadrant split the token columns in alternating groups of 16.
+    const int ew = warp - 2;                   // 0..7
     const int quad = warp & 3;                 // TMEM lanes [32*quad, 32*quad+32)
+    const int half = ew >> 2;
+    const int tid_e = ew * 32 + lane;          // 0..255
     const int row_local = quad * 32 + lane;
     const int64_t oq_pitch = p.out_kp / 2;
+    const uint32_t stg = stage0 + (uint32_t)S * geo.stage_bytes;   // bf16 staging tile [B][kStagePitch]
+    const bool fused = GATEUP && p.h_out == nullptr;
     int acc = 0;
     uint32_t acc_phase = 0;
     for (int w = blockIdx.x; w < total_work; w += gridDim.x) {
@@ -324,12 +381,14 @@ moe_grouped_gemm_kernel(const __grid_constant__ GemmParams p) {
         const uint32_t id = (q + lane < B) ? p.sorted_ids[r0 + q + lane] : 0xFFFFFFFFu;
         nvalid += __popc(__ballot_sync(0xffffffffu, (int)(id >> 24) < p.topk && (int)(id & 0xFFFFFFu) < p.T));
       }
-      if (!mbar_wait(smem_u32(&ctl->tmem_full[acc]), acc_phase, abort_word, 0x400 + acc)) break;
+      // all eight warps take the same decision, so nobody is left alone at a later barrier
+      const bool ok = mbar_wait(smem_u32(&ctl->tmem_full[acc]), acc_phase, abort_word, 0x400 + acc);
+      if (!epi_all(ok)) break;
       tc_fence_after_sync();
       const uint32_t t0 = tmem_base + ((uint32_t)(quad * 32) << 16) + acc * acc_cols;
       const bool j_ok = j < p.rows;
       uint32_t my_id = 0;
-      for (int c0 = 0; c0 < nvalid; c0 += 16) {
+      for (int c0 = half * 16; c0 < nvalid; c0 += 32) {
         uint32_t g[16], u[16];
         tmem_ld_32x32b_x16(t0 + c0, g);
         tmem_ld_32x32b_x16(t0 + ncol + c0, u);
@@ -348,12 +407,12 @@ moe_grouped_gemm_kernel(const __grid_constant__ GemmParams p) {
             }
           }
         }
-        if ((c0 & 31) == 0 && GATEUP) my_id = p.sorted_ids[min(r0 + c0 + lane, r0 + B - 1)];
         if (GATEUP) {
-          if (p.h_out != nullptr) {
+          if (!fused) {
+            my_id = p.sorted_ids[min(r0 + c0 + lane, r0 + B - 1)];
 #pragma unroll
             for (int n = 0; n < 16; ++n) {
-              const uint32_t id = __shfl_sync(0xffffffffu, my_id, (c0 & 31) + n);
+              const uint32_t id = __shfl_sync(0xffffffffu, my_id, n);
               if (c0 + n < nvalid) {
                 const int tok = (int)(id & 0xFFFFFFu), kk = (int)(id >> 24);
                 const float v = gateup_act(__uint_as_float(g[n]), __uint_as_float(u[n]), p.activation,
@@ -362,30 +421,15 @@ moe_grouped_gemm_kernel(const __grid_constant__ GemmParams p) {
               }
             }
           } else {
-            // fused re-quantisation of h into the operand format of the down GEMM; the 32
-            // lanes of a warp are one 32-wide scale block along the feature axis
+            // h (already rounded to bf16, as the oracle's h is) goes to the staging tile,
+            // token-major, for the block-wise re-quantisation below
 #pragma unroll
             for (int n = 0; n < 16; ++n) {
               if (c0 + n < nvalid) {
-                float res = gateup_act(__uint_as_float(g[n]), __uint_as_float(u[n]), p.activation, p.swiglu_limit);
-                if (!j_ok) res = 0.f;
-                const int64_t r = (int64_t)r0 + c0 + n;
-                for (int t = 0; t < NT; ++t) {
-                  const uint32_t amax = __reduce_max_sync(0xffffffffu, __float_as_uint(res) & 0x7fffffffu);
-                  const int e = max((int)(amax >> 23) - 2, 0);
-                  const float inv = __uint_as_float((uint32_t)(254 - e) << 23);
-                  const __nv_fp4x2_storage_t code =
-                      __nv_cvt_float2_to_fp4x2(make_float2(res * inv, 0.f), __NV_E2M1, cudaRoundNearest);
-                  __half2_raw hb = __nv_cvt_fp4x2_to_halfraw2(code, __NV_E2M1);
-                  const float back = __half2float(__half(__half_raw{hb.x}));
-                  res -= back * __uint_as_float(e == 0 ? 0x00400000u : ((uint32_t)e << 23));
-                  const uint32_t mine = (uint32_t)code & 0xFu;
-                  const uint32_t next = __shfl_down_sync(0xffffffffu, mine, 1);
-                  if ((lane & 1) == 0)
-                    p.oq[t * p.oq_term_stride + r * oq_pitch + (j >> 1)] = (uint8_t)(mine | (next << 4));
-                  if (lane == 0)
-                    p.osf[act_sf_index(b, m, p.out_kb, B, NT, p.out_ts, t, c0 + n, quad)] = (uint8_t)e;
-                }
+                float v = gateup_act(__uint_as_float(g[n]), __uint_as_float(u[n]), p.activation, p.swiglu_limit);
+                if (!j_ok) v = 0.f;
+                st_shared_u16(stg + (uint32_t)(c0 + n) * kStagePitch + row_local * 2,
+                              __bfloat16_as_ushort(__float2bfloat16_rn(v)));
               }
             }
           }
@@ -402,9 +446,37 @@ moe_grouped_gemm_kernel(const __grid_constant__ GemmParams p) {
         }
       }
       tc_fence_before_sync();
-      __syncwarp();
+      if (fused) epi_sync(); else __syncwarp();      // staging tile complete, TMEM reads done
       if (lane == 0) mbar_arrive(smem_u32(&ctl->tmem_empty[acc]));
       if (n_acc == 2) { acc ^= 1; if (acc == 0) acc_phase ^= 1; } else { acc_phase ^= 1; }
+
+      if (fused) {
+        // Re-quantise h into the operand format of the down GEMM: one thread per (token row,
+        // 32-feature block), NT packed-FP4 terms with an E8M0 scale each -- the same arithmetic
+        // as the stand-alone quantiser -- written as 16-byte vectors in sorted-row order.
+        for (int unit = tid_e; unit < nvalid * 4; unit += 256) {
+          const int n = unit >> 2, q = unit & 3;
+          float x[32];
+#pragma unroll
+          for (int v4 = 0; v4 < 4; ++v4) {
+            const uint4 raw = ld_shared_v4(stg + (uint32_t)n * kStagePitch + q * 64 + v4 * 16);
+            const __nv_bfloat162* b2 = reinterpret_cast<const __nv_bfloat162*>(&raw);
+#pragma unroll
+            for (int t = 0; t < 4; ++t) {
+              const float2 f = __bfloat1622float2(b2[t]);
+              x[v4 * 8 + t * 2] = f.x;
+              x[v4 * 8 + t * 2 + 1] = f.y;
+            }
+          }
+          const int64_t r = (int64_t)r0 + n;
+          for (int t = 0; t < NT; ++t) {
+            uint4 pk;
+            const int e = quant_block32_fp4(x, pk);
+            *reinterpret_cast<uint4*>(p.oq + t * p.oq_term_stride + r * oq_pitch + (m * kTileM + q * 32) / 2) = pk;
+            p.osf[act_sf_index(b, m, p.out_kb, B, NT, p.out_ts, t, n, q)] = (uint8_t)e;
+          }
+        }
+      }
     }
   }
 
@@ -467,7 +539,7 @@ static int encode_map_sw(CUtensorMap* map, CUtensorMapDataType type, int rank, c
 }
 
 int launch_grouped_gemm(const GemmArgs& a, cudaStream_t st) {
-  B200_CHECK_ARG(a.N == 16 || a.N == 32 || a.N == 64 || a.N == 128, "grouped gemm: token tile %d not in {16,32,64,128}",
+  B200_CHECK_ARG(a.N >= 16 && a.N <= 128 && a.N % 16 == 0, "grouped gemm: token tile %d is not a multiple of 16 in [16,128]",
                  a.N);
   B200_CHECK_ARG(a.NT >= 2 && a.NT <= kMaxTerms, "grouped gemm: %d activation terms (2..4 supported)", a.NT);
   B200_CHECK_ARG(a.Kd % 32 == 0 && a.rows > 0 && a.E > 0, "grouped gemm: bad shape");
@@ -513,11 +585,12 @@ int launch_grouped_gemm(const GemmArgs& a, cudaStream_t st) {
   }
 
   const StageGeom geo = stage_geom(2, a.N, a.NT);
-  int stages = (kSmemLimit - 2048) / geo.stage_bytes;
+  const int staging = (a.gateup && a.h_out == nullptr) ? a.N * kStagePitch : 0;
+  int stages = (kSmemLimit - 2048 - staging) / geo.stage_bytes;
   stages = std::min(stages, kMaxStages);
   B200_CHECK_ARG(stages >= 2, "grouped gemm: tile does not fit shared memory");
   p.stages = stages;
-  const size_t smem = 2048 + (size_t)stages * geo.stage_bytes;
+  const size_t smem = 2048 + (size_t)stages * geo.stage_bytes + staging;
 
   const int64_t max_work = (a.max_rows / a.N) * p.MT;
   const int grid = (int)std::min<int64_t>(device_sm_count(), std::max<int64_t>(max_work, 1));

@@ -54,9 +54,9 @@ def pick_block(T: int, K: int, E: int) -> int:
         return 16
     if per_expert <= 20:
         return 32
-    if per_expert <= 80:
+    if per_expert <= 48:
         return 64
-    return 128
+    return 96          # largest tile whose two accumulator buffers fit tensor memory
 
 
 class PreparedWeights:

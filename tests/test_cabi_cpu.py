@@ -42,7 +42,7 @@ def test_workspace_layout_arithmetic(L):
     assert ws.off_xsf - ws.off_xq >= 3 * ws.max_rows * 2944 // 2
 
 
-@pytest.mark.parametrize("field,value", [("B", 48), ("H", 100), ("I", 0), ("K", 0), ("T", 1 << 24),
+@pytest.mark.parametrize("field,value", [("B", 40), ("H", 100), ("I", 0), ("K", 0), ("T", 1 << 24),
                                          ("weight_format", 7), ("activation", 9), ("E_route", 4), ("act_terms", 5)])
 def test_bad_shapes_are_rejected(L, field, value):
     s = _lib.Shape(T=8, K=2, E=8, E_route=8, H=256, I=128, B=32, weight_format=0, activation=0, swiglu_limit=7.0, act_terms=0)
