@@ -142,8 +142,8 @@ int b200moe_forward_static(const b200moe_shape* shape, const void* x_bf16, const
                            void* y_bf16, void* stream);
 
 /* Hardware known-answer probes used by the GPU test-suite (tiny, single CTA, bounded waits).
- *   which = 1: TMA load of one 128x128 packed-FP4 tile (64-byte swizzle) from `in` (8192 bytes)
- *              -> `out` receives the 8192-byte shared-memory image.
+ *   which = 1: TMA load of one 128-row x 256-element packed-FP4 tile (128-byte swizzle) from `in`
+ *              (16384 bytes) -> `out` receives the 16384-byte shared-memory image.
  *   which = 2: 512 bytes `in` -> shared -> tcgen05.cp 32x128b.warpx4 -> tcgen05.ld;
  *              `out` receives u32 [128 lanes][4 columns].
  *   which = 3: tensor-core issue-rate measurement (kind::mxf4, 128 x N x 64); `in` = i32 {0, N,

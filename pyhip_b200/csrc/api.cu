@@ -37,7 +37,7 @@ static int check_shape(const b200moe_shape* s) {
   return 0;
 }
 
-static int64_t kp_of(int k) { return round_up64(k, 128); }
+static int64_t kp_of(int k) { return round_up64(k, kKPad); }
 static int terms_of(const b200moe_shape* s) { return s->act_terms == 0 ? 3 : s->act_terms; }
 
 }  // namespace b200moe

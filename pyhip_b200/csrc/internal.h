@@ -35,7 +35,8 @@ __host__ __device__ static inline int sf_chunk_offset(int row_in_128, int j) {
 // buffers of `parts` tiles fit tensor memory; otherwise every term is its own instruction.
 // Scales: per (sorted block, 128-wide k-block) a group of 512-byte chunks; term t, block-local
 // row r sit at virtual row v = t*TS + r (TS = B when merged, 128 otherwise): chunk v/128.
-constexpr int kAccColsLimit = 448;
+constexpr int kAccColsLimit = 416;   // TMEM columns left for accumulators (the rest holds scales)
+constexpr int kKPad = 256;           // activation K is padded to the K extent of one pipeline stage
 __host__ __device__ static inline bool act_merged(int B, int NT, int parts) {
   return NT * B <= 256 && 2 * parts * NT * B <= kAccColsLimit;
 }

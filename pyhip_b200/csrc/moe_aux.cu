@@ -238,7 +238,7 @@ int launch_quant_rows(const void* src, int src_mode, const uint32_t* sorted_ids,
   B200_CHECK_ARG(B >= 16 && B <= 128 && B % 16 == 0, "quant_rows: B=%d is not a multiple of 16 in [16,128]", B);
   B200_CHECK_ARG(NT >= 2 && NT <= 4, "quant_rows: %d activation terms (2..4 supported)", NT);
   B200_CHECK_ARG(Kd % 32 == 0, "quant_rows: Kd=%d must be a multiple of 32", Kd);
-  const int KP = (int)round_up64(Kd, 128);
+  const int KP = (int)round_up64(Kd, kKPad);
   int64_t work = max_rows * (KP / 32);
   int blocks = (int)std::min<int64_t>((work + 255) / 256, 148 * 16);
   if (blocks < 1) blocks = 1;
@@ -333,7 +333,7 @@ repack_scales_kernel(const uint8_t* __restrict__ src, uint8_t* __restrict__ dst,
 }
 
 int launch_repack_scales(const void* w_s, void* out, int E, bool gateup, int rows, int Kd, cudaStream_t st) {
-  const int KB = (int)round_up64(Kd, 128) / 128;
+  const int KB = (int)round_up64(Kd, kKPad) / 128;
   const int MT = gateup ? (rows + 127) / 128 : (rows + 255) / 256;
   int64_t total = (int64_t)E * MT * KB * 2 * kSfChunk;
   int blocks = (int)std::min<int64_t>((total + 255) / 256, 148 * 32);

@@ -45,13 +45,14 @@ namespace b200moe {
 constexpr int kThreads = 320;          // TMA warp, MMA warp, 8 epilogue warps
 constexpr int kTileM = 128;          // weight rows per MMA
 constexpr int kStagePitch = kTileM * 2 + 16;   // bytes per token row of the bf16 staging tile
-constexpr int kTileK = 128;          // K per pipeline stage (2 MMA K-steps of 64)
-constexpr int kRowBytes = kTileK / 2;                // one tile row: 128 packed FP4 = 64 bytes
-constexpr int kATileBytes = kTileM * kRowBytes;      // 8 KB
+constexpr int kTileK = kKPad;        // K per pipeline stage: 256 (4 MMA K-steps of 64, 2 scale k-blocks of 128)
+constexpr int kSub = kTileK / 128;   // scale k-blocks per stage
+constexpr int kRowBytes = kTileK / 2;                // one tile row: 256 packed FP4 = 128 bytes = one swizzle span
+constexpr int kATileBytes = kTileM * kRowBytes;      // 16 KB
 constexpr int kMaxStages = 16;
 constexpr int kMaxTerms = 4;
 constexpr int kTmemCols = 512;
-constexpr int kSfCol0 = kAccColsLimit;   // scale columns: 2 buffers x {A: 8 columns, B: up to 16 columns}
+constexpr int kSfCol0 = kAccColsLimit;   // scale columns: 2 buffers x 48 = per k-block {A: 8 columns, B: up to 16}
 constexpr int kSmemLimit = 232448;       // 227 KB
 
 struct GemmParams {
@@ -90,8 +91,8 @@ __host__ __device__ inline StageGeom stage_geom(int parts, int B, int NT) {
   StageGeom g;
   g.a_bytes = parts * kATileBytes;
   g.b_bytes = NT * B * kRowBytes;
-  g.sfa_bytes = parts * kSfChunk;
-  g.sfb_bytes = act_sf_chunks(NT, act_term_stride(B, NT, parts)) * kSfChunk;
+  g.sfa_bytes = kSub * parts * kSfChunk;
+  g.sfb_bytes = kSub * act_sf_chunks(NT, act_term_stride(B, NT, parts)) * kSfChunk;
   g.stage_bytes = (g.a_bytes + g.b_bytes + g.sfa_bytes + g.sfb_bytes + 1023) & ~1023;
   g.tx_bytes = (uint32_t)(g.a_bytes + g.b_bytes + g.sfa_bytes + g.sfb_bytes);
   return g;
@@ -114,7 +115,7 @@ __device__ __forceinline__ float gateup_act(float g, float u, int activation, fl
 }
 
 // descriptor halves: the high word is constant per layout, the low word carries the address
-constexpr uint32_t kDescHiSw64 = (512u >> 4) | (1u << 14) | (4u << 29);   // SBO 512, version 1, 64-byte swizzle
+constexpr uint32_t kDescHiSw = (1024u >> 4) | (1u << 14) | (2u << 29);   // SBO 1024, version 1, 128-byte swizzle
 constexpr uint32_t kDescHiSf = (128u >> 4) | (1u << 14);                   // SBO 128, version 1, no swizzle
 __device__ __forceinline__ uint32_t desc_lo_sw(uint32_t saddr) { return ((saddr >> 4) & 0x3FFFu) | (1u << 16); }
 __device__ __forceinline__ uint32_t desc_lo_sf(uint32_t saddr) { return (saddr >> 4) & 0x3FFFu; }
@@ -129,7 +130,7 @@ __device__ __forceinline__ void umma_mxf4(uint32_t d_tmem, uint32_t a_lo, uint32
       "mov.b64 db, {%2, %7};\n\t"
       "tcgen05.mma.cta_group::1.kind::mxf4.block_scale.block32 [%0], da, db, %3, [%5], [%6], p;\n\t}"
       ::"r"(d_tmem), "r"(a_lo), "r"(b_lo), "r"(idesc), "r"(accumulate), "r"(sfa_tmem), "r"(sfb_tmem),
-        "r"(kDescHiSw64)
+        "r"(kDescHiSw)
       : "memory");
 }
 __device__ __forceinline__ void utccp_sf(uint32_t taddr, uint32_t lo) {
@@ -220,7 +221,7 @@ moe_grouped_gemm_kernel(const __grid_constant__ GemmParams p) {
   const int ncol = merged ? NT * B : B;        // TMEM columns of one accumulator
   const int acc_cols = NA * ncol;
   const int n_acc = (2 * acc_cols <= kAccColsLimit) ? 2 : 1;
-  const int sfb_chunks = geo.sfb_bytes / kSfChunk;
+  const int sfb_chunks = geo.sfb_bytes / (kSub * kSfChunk);   // per 128-wide k-block
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   volatile uint32_t* abort_word = &ctl->abort_word;
@@ -260,13 +261,13 @@ moe_grouped_gemm_kernel(const __grid_constant__ GemmParams p) {
       uint32_t phase = 0;
       int64_t issued = 0;
       bool ok = true;
-      const int64_t sfa_step = (int64_t)NA * kSfChunk;
+      const int64_t sfa_step = geo.sfa_bytes;
       for (int w = blockIdx.x; w < total_work && ok; w += gridDim.x) {
         const int b = w / p.MT, m = w - b * p.MT;
         int e = p.sorted_e[b];
         if (e < 0 || e >= p.E) { p.status[2] = 1; e = 0; }
         const int r0 = b * B;
-        const uint8_t* sfa = p.w_scale + ((int64_t)e * p.MT + m) * p.KB * sfa_step;
+        const uint8_t* sfa = p.w_scale + ((int64_t)e * p.MT + m) * p.KB * sfa_step;   // KB stages of kSub k-blocks
         const uint8_t* sfb = p.asf + (int64_t)b * p.KB * geo.sfb_bytes;
         for (int kb = 0; kb < p.KB; ++kb) {
           if (!mbar_wait(smem_u32(&ctl->empty[stage]), phase ^ 1, abort_word, 0x100 + stage)) { ok = false; break; }
@@ -320,28 +321,35 @@ moe_grouped_gemm_kernel(const __grid_constant__ GemmParams p) {
           const uint32_t a_lo = desc_lo_sw(st);
           const uint32_t b_lo = desc_lo_sw(st + geo.a_bytes);
           const uint32_t sf_lo = desc_lo_sf(st + geo.a_bytes + geo.b_bytes);
-          const uint32_t sfa_t = tmem_base + kSfCol0 + sf_buf * 32;
-          const uint32_t sfb_t = sfa_t + 8;
-          utccp_sf(sfa_t, sf_lo);
-          utccp_sf(sfa_t + 4, sf_lo + (kSfChunk >> 4));
-          for (int c = 0; c < sfb_chunks; ++c)
-            utccp_sf(sfb_t + 4 * c, sf_lo + ((geo.sfa_bytes + c * kSfChunk) >> 4));
+          // scale columns of this stage: per 128-wide k-block {A: gate/up or tile pair, 8 columns}
+          // then {B: up to 16 columns}
+          const uint32_t sfa_t = tmem_base + kSfCol0 + sf_buf * 48;
+          const uint32_t sfb_t = sfa_t + 16;
+#pragma unroll
+          for (int kk = 0; kk < kSub; ++kk) {
+            utccp_sf(sfa_t + 8 * kk, sf_lo + ((kk * 2 * kSfChunk) >> 4));
+            utccp_sf(sfa_t + 8 * kk + 4, sf_lo + ((kk * 2 * kSfChunk + kSfChunk) >> 4));
+            for (int c = 0; c < sfb_chunks; ++c)
+              utccp_sf(sfb_t + 16 * kk + 4 * c, sf_lo + ((geo.sfa_bytes + (kk * sfb_chunks + c) * kSfChunk) >> 4));
+          }
           const uint32_t first = kb != 0;
           if (merged) {
 #pragma unroll
-            for (int s = 0; s < 2; ++s) {
-              umma_mxf4(d0, a_lo + 2 * s, b_lo + 2 * s, idesc[s], sfa_t, sfb_t, s == 0 ? first : 1u);
-              umma_mxf4(d0 + ncol, a_lo + (kATileBytes >> 4) + 2 * s, b_lo + 2 * s, idesc[s], sfa_t + 4, sfb_t,
+            for (int s = 0; s < 2 * kSub; ++s) {
+              const uint32_t sa = sfa_t + 8 * (s >> 1), sb = sfb_t + 16 * (s >> 1);
+              umma_mxf4(d0, a_lo + 2 * s, b_lo + 2 * s, idesc[s & 1], sa, sb, s == 0 ? first : 1u);
+              umma_mxf4(d0 + ncol, a_lo + (kATileBytes >> 4) + 2 * s, b_lo + 2 * s, idesc[s & 1], sa + 4, sb,
                         s == 0 ? first : 1u);
             }
           } else {
 #pragma unroll
-            for (int s = 0; s < 2; ++s) {
+            for (int s = 0; s < 2 * kSub; ++s) {
+              const uint32_t sa = sfa_t + 8 * (s >> 1), sb = sfb_t + 16 * (s >> 1);
               for (int t = 0; t < NT; ++t) {
                 const uint32_t accum = (s == 0 && t == 0) ? first : 1u;
-                umma_mxf4(d0, a_lo + 2 * s, b_lo + t * term_lo + 2 * s, idesc[s], sfa_t, sfb_t + 4 * t, accum);
-                umma_mxf4(d0 + ncol, a_lo + (kATileBytes >> 4) + 2 * s, b_lo + t * term_lo + 2 * s, idesc[s],
-                          sfa_t + 4, sfb_t + 4 * t, accum);
+                umma_mxf4(d0, a_lo + 2 * s, b_lo + t * term_lo + 2 * s, idesc[s & 1], sa, sb + 4 * t, accum);
+                umma_mxf4(d0 + ncol, a_lo + (kATileBytes >> 4) + 2 * s, b_lo + t * term_lo + 2 * s, idesc[s & 1],
+                          sa + 4, sb + 4 * t, accum);
               }
             }
           }
@@ -476,6 +484,19 @@ moe_grouped_gemm_kernel(const __grid_constant__ GemmParams p) {
             p.osf[act_sf_index(b, m, p.out_kb, B, NT, p.out_ts, t, n, q)] = (uint8_t)e;
           }
         }
+        // the K padding of the down GEMM (features beyond the last weight tile) must hold zeros
+        // and a finite scale: the CTA that owns the last tile writes it
+        if (m == p.MT - 1) {
+          const int pad_blocks = (p.out_kp - p.MT * kTileM) / 32;
+          for (int unit = tid_e; unit < nvalid * pad_blocks; unit += 256) {
+            const int n = unit / pad_blocks, qb = p.MT * 4 + unit % pad_blocks;   // 32-feature block index
+            const int64_t r = (int64_t)r0 + n;
+            for (int t = 0; t < NT; ++t) {
+              *reinterpret_cast<uint4*>(p.oq + t * p.oq_term_stride + r * oq_pitch + qb * 16) = make_uint4(0, 0, 0, 0);
+              p.osf[act_sf_index(b, qb >> 2, p.out_kb, B, NT, p.out_ts, t, n, qb & 3)] = 0;
+            }
+          }
+        }
       }
     }
   }
@@ -556,7 +577,7 @@ int launch_grouped_gemm(const GemmArgs& a, cudaStream_t st) {
   p.w_scale = (const uint8_t*)a.w_scale; p.asf = (const uint8_t*)a.asf;
   p.sorted_ids = a.sorted_ids; p.sorted_e = a.sorted_e; p.num_valid = a.num_valid; p.status = a.status;
   p.h_out = (__nv_bfloat16*)a.h_out; p.oq = (uint8_t*)a.oq; p.osf = (uint8_t*)a.osf;
-  p.out_kp = a.out_kp; p.out_kb = a.out_kp / kTileK; p.out_ts = act_term_stride(a.N, a.NT, 2);
+  p.out_kp = a.out_kp; p.out_kb = a.out_kp / 128; p.out_ts = act_term_stride(a.N, a.NT, 2);
   p.oq_term_stride = a.max_rows * (int64_t)(a.out_kp / 2);
   p.out2 = (__nv_bfloat16*)a.out2;
   if (a.gateup && a.h_out == nullptr)
@@ -572,7 +593,7 @@ int launch_grouped_gemm(const GemmArgs& a, cudaStream_t st) {
     cuuint64_t strides[3] = {row_pitch, row_pitch * (cuuint64_t)a.rows, row_pitch * (cuuint64_t)a.rows * parts};
     cuuint32_t box[4] = {kTileK, a.gateup ? (cuuint32_t)kTileM : 2u * kTileM, a.gateup ? 2u : 1u, 1};
     int rc = encode_map_sw(&p.tmW, CU_TENSOR_MAP_DATA_TYPE_16U4_ALIGN8B, 4, a.w_data, dims, strides, box,
-                           CU_TENSOR_MAP_SWIZZLE_64B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, "weights");
+                           CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, "weights");
     if (rc) return rc;
   }
   {
@@ -580,7 +601,7 @@ int launch_grouped_gemm(const GemmArgs& a, cudaStream_t st) {
     cuuint64_t strides[2] = {(cuuint64_t)KP / 2, (cuuint64_t)(KP / 2) * (cuuint64_t)a.max_rows};
     cuuint32_t box[3] = {kTileK, (cuuint32_t)a.N, (cuuint32_t)a.NT};
     int rc = encode_map_sw(&p.tmA, CU_TENSOR_MAP_DATA_TYPE_16U4_ALIGN8B, 3, a.a_q, dims, strides, box,
-                           CU_TENSOR_MAP_SWIZZLE_64B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, "activations");
+                           CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, "activations");
     if (rc) return rc;
   }
 
@@ -688,7 +709,7 @@ __global__ void __launch_bounds__(128, 1) probe_mma_rate_kernel(const int32_t* c
   __shared__ uint32_t tmem_slot, abort_word;
   const int N = cfg[1], count = cfg[2], nacc = cfg[3];
   const int warp = threadIdx.x >> 5;
-  for (int i = threadIdx.x; i < (8192 + 16384 + 1024) / 4; i += blockDim.x) reinterpret_cast<uint32_t*>(smem)[i] = 0;
+  for (int i = threadIdx.x; i < (16384 + 32768 + 1024) / 4; i += blockDim.x) reinterpret_cast<uint32_t*>(smem)[i] = 0;
   if (threadIdx.x == 0) {
     abort_word = 0;
     mbar_init(smem_u32(&bar), 1);
@@ -704,7 +725,7 @@ __global__ void __launch_bounds__(128, 1) probe_mma_rate_kernel(const int32_t* c
   tc_fence_after_sync();
   const uint32_t tbase = tmem_slot;
   if (threadIdx.x == 0) {
-    const uint32_t a = smem_u32(smem), b = a + 8192, sf = b + 16384;
+    const uint32_t a = smem_u32(smem), b = a + 16384, sf = b + 32768;
     utccp_sf(tbase + 448, desc_lo_sf(sf));
     utccp_sf(tbase + 456, desc_lo_sf(sf + 512));
     utccp_sf(tbase + 460, desc_lo_sf(sf + 512));
@@ -735,11 +756,11 @@ __global__ void __launch_bounds__(128, 1) probe_mma_rate_kernel(const int32_t* c
 int run_debug_probe(int which, const void* in, void* out, cudaStream_t st) {
   if (which == 1) {
     CUtensorMap map;
-    cuuint64_t dims[3] = {128, 128, 1};
-    cuuint64_t strides[2] = {64, 64 * 128};
-    cuuint32_t box[3] = {128, 128, 1};
+    cuuint64_t dims[3] = {256, 128, 1};
+    cuuint64_t strides[2] = {128, 128 * 128};
+    cuuint32_t box[3] = {256, 128, 1};
     int rc = encode_map_sw(&map, CU_TENSOR_MAP_DATA_TYPE_16U4_ALIGN8B, 3, in, dims, strides, box,
-                           CU_TENSOR_MAP_SWIZZLE_64B, CU_TENSOR_MAP_L2_PROMOTION_NONE, "probe tile");
+                           CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_NONE, "probe tile");
     if (rc) return rc;
     probe_tma_fp4_kernel<<<1, 128, kATileBytes + 1024, st>>>(map, (uint32_t*)out);
     B200_CHECK_CUDA(cudaGetLastError());
@@ -751,7 +772,13 @@ int run_debug_probe(int which, const void* in, void* out, cudaStream_t st) {
     return 0;
   }
   if (which == 3) {
-    probe_mma_rate_kernel<<<1, 128, 8192 + 16384 + 1024 + 1024, st>>>((const int32_t*)in, (uint32_t*)out);
+    static bool attr = false;
+    if (!attr) {
+      B200_CHECK_CUDA(cudaFuncSetAttribute(probe_mma_rate_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                           65536));
+      attr = true;
+    }
+    probe_mma_rate_kernel<<<1, 128, 16384 + 32768 + 1024 + 1024, st>>>((const int32_t*)in, (uint32_t*)out);
     B200_CHECK_CUDA(cudaGetLastError());
     return 0;
   }

@@ -39,7 +39,7 @@ def test_workspace_layout_arithmetic(L):
     offs = [getattr(ws, n) for n in _lib._WS_FIELDS if n.startswith("off_")]
     assert offs == sorted(offs) and all(o % 1024 == 0 for o in offs)
     assert ws.total_bytes > offs[-1]
-    assert ws.off_xsf - ws.off_xq >= 3 * ws.max_rows * 2944 // 2
+    assert ws.off_xsf - ws.off_xq >= 3 * ws.max_rows * 3072 // 2
 
 
 @pytest.mark.parametrize("field,value", [("B", 40), ("H", 100), ("I", 0), ("K", 0), ("T", 1 << 24),

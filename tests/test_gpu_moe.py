@@ -66,7 +66,7 @@ def test_quantised_rows_match_oracle_bit_for_bit(NT):
     torch.cuda.synchronize()
     n = int(nv[0])
     L = plan.ws.max_rows
-    HP = (H + 127) // 128 * 128
+    HP = (H + 255) // 256 * 256
     packed = plan.region("xq", NT * L * HP // 2).cpu().numpy().reshape(NT, L, HP // 2)[:, :n]
     codes = np.empty((NT, n, HP), dtype=np.uint8)
     codes[..., 0::2], codes[..., 1::2] = packed & 0xF, packed >> 4

@@ -24,16 +24,16 @@ def _probe(which, inp: torch.Tensor, out_words: int):
 
 def test_tma_fp4_unpack_image():
     g = torch.Generator().manual_seed(0)
-    src = torch.randint(0, 256, (128, 64), dtype=torch.uint8, generator=g)
-    raw = _probe(1, src.cuda(), 2048 + 1)
-    assert raw[2048] == 0, "TMA wait ran out"
-    img = raw[:2048].view(np.uint8).reshape(128, 64)
+    src = torch.randint(0, 256, (128, 128), dtype=torch.uint8, generator=g)
+    raw = _probe(1, src.cuda(), 4096 + 1)
+    assert raw[4096] == 0, "TMA wait ran out"
+    img = raw[:4096].view(np.uint8).reshape(128, 128)
     OUT.mkdir(exist_ok=True)
     np.save(OUT / "probe_tma_fp4_image.npy", img)
     s = src.numpy()
     for r in range(128):
-        for c in range(4):                       # logical 16-byte chunk -> 64-byte-swizzled position
-            phys = (c ^ ((r >> 1) & 3)) * 16
+        for c in range(8):                       # logical 16-byte chunk -> 128-byte-swizzled position
+            phys = (c ^ (r & 7)) * 16
             assert np.array_equal(img[r, phys:phys + 16], s[r, c * 16:c * 16 + 16]), (r, c)
 
 
