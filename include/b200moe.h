@@ -146,8 +146,8 @@ int b200moe_forward_static(const b200moe_shape* shape, const void* x_bf16, const
  *              (16384 bytes) -> `out` receives the 16384-byte shared-memory image.
  *   which = 2: 512 bytes `in` -> shared -> tcgen05.cp 32x128b.warpx4 -> tcgen05.ld;
  *              `out` receives u32 [128 lanes][4 columns].
- *   which = 3: tensor-core issue-rate measurement (kind::mxf4, 128 x N x 64); `in` = i32 {0, N,
- *              count, accumulators}; `out` = u32 {issue cycles, cycles until complete, status}.
+ *   which = 3: tensor-core issue-rate measurement (kind::mxf4, 128 x N x 64); `in` = i32 {scale copies per
+ *              four MMAs, N, count, accumulators}; `out` = u32 {issue cycles, cycles until complete, status}.
  * out[last] status word: 0 = ok, non-zero = a bounded wait ran out. */
 int b200moe_debug_probe(int which, const void* in, void* out, void* stream);
 

@@ -42,7 +42,7 @@
 
 namespace b200moe {
 
-constexpr int kThreads = 320;          // TMA warp, MMA warp, 8 epilogue warps
+constexpr int kThreads = 448;          // TMA warp, MMA warp, 8 epilogue warps, 4 scale-loader warps
 constexpr int kTileM = 128;          // weight rows per MMA
 constexpr int kStagePitch = kTileM * 2 + 16;   // bytes per token row of the bf16 staging tile
 constexpr int kTileK = kKPad;        // K per pipeline stage: 256 (4 MMA K-steps of 64, 2 scale k-blocks of 128)
@@ -78,6 +78,8 @@ struct SmemCtl {
   uint64_t empty[kMaxStages];
   uint64_t tmem_full[2];
   uint64_t tmem_empty[2];
+  uint64_t sf_full[2];      // scale columns of a TMEM scale buffer are in place
+  uint64_t sf_empty[2];     // ... and have been consumed by the MMAs that use them
   uint32_t tmem_base;
   uint32_t abort_word;
 };
@@ -150,6 +152,22 @@ __device__ __forceinline__ void tmem_ld_32x32b_x16(uint32_t taddr, uint32_t (&r)
       : "r"(taddr)
       : "memory");
 }
+__device__ __forceinline__ void tmem_st_32x32b_x4(uint32_t taddr, const uint4& v) {
+  asm volatile("tcgen05.st.sync.aligned.32x32b.x4.b32 [%0], {%1, %2, %3, %4};" ::"r"(taddr), "r"(v.x), "r"(v.y),
+               "r"(v.z), "r"(v.w)
+               : "memory");
+}
+__device__ __forceinline__ void tmem_st_32x32b_x16(uint32_t taddr, const uint4& a, const uint4& b, const uint4& c,
+                                                   const uint4& d) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], "
+      "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16};" ::"r"(taddr),
+      "r"(a.x), "r"(a.y), "r"(a.z), "r"(a.w), "r"(b.x), "r"(b.y), "r"(b.z), "r"(b.w), "r"(c.x), "r"(c.y), "r"(c.z),
+      "r"(c.w), "r"(d.x), "r"(d.y), "r"(d.z), "r"(d.w)
+      : "memory");
+}
+__device__ __forceinline__ void tmem_st_wait() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
+
 // named barriers among the eight epilogue warps (barrier 0 belongs to __syncthreads)
 __device__ __forceinline__ void epi_sync() { asm volatile("bar.sync 2, 256;" ::: "memory"); }
 __device__ __forceinline__ bool epi_all(bool pred) {
@@ -234,6 +252,8 @@ moe_grouped_gemm_kernel(const __grid_constant__ GemmParams p) {
     for (int a = 0; a < 2; ++a) {
       mbar_init(smem_u32(&ctl->tmem_full[a]), 1);
       mbar_init(smem_u32(&ctl->tmem_empty[a]), 8);
+      mbar_init(smem_u32(&ctl->sf_full[a]), 4);
+      mbar_init(smem_u32(&ctl->sf_empty[a]), 1);
     }
     ctl->abort_word = 0;
     fence_mbar_init();
@@ -261,6 +281,7 @@ moe_grouped_gemm_kernel(const __grid_constant__ GemmParams p) {
       uint32_t phase = 0;
       int64_t issued = 0;
       bool ok = true;
+      long long t_wait = 0;
       const int64_t sfa_step = geo.sfa_bytes;
       for (int w = blockIdx.x; w < total_work && ok; w += gridDim.x) {
         const int b = w / p.MT, m = w - b * p.MT;
@@ -270,7 +291,9 @@ moe_grouped_gemm_kernel(const __grid_constant__ GemmParams p) {
         const uint8_t* sfa = p.w_scale + ((int64_t)e * p.MT + m) * p.KB * sfa_step;   // KB stages of kSub k-blocks
         const uint8_t* sfb = p.asf + (int64_t)b * p.KB * geo.sfb_bytes;
         for (int kb = 0; kb < p.KB; ++kb) {
+          const long long tw0 = clock64();
           if (!mbar_wait(smem_u32(&ctl->empty[stage]), phase ^ 1, abort_word, 0x100 + stage)) { ok = false; break; }
+          t_wait += clock64() - tw0;
           const uint32_t st = stage0 + (uint32_t)stage * geo.stage_bytes;
           const uint32_t full = smem_u32(&ctl->full[stage]);
           mbar_expect_tx(full, geo.tx_bytes);
@@ -284,6 +307,7 @@ moe_grouped_gemm_kernel(const __grid_constant__ GemmParams p) {
           if (++stage == S) { stage = 0; phase ^= 1; }
         }
       }
+      if (blockIdx.x == 0) p.status[4] = (int32_t)(t_wait >> 10);   // profiling: kilo-cycles waiting for a free stage
       if (!ok || *abort_word) {
         // unwinding: let this CTA's copies still in flight land before shared memory is released
         const int64_t first = issued > S ? issued - S : 0;
@@ -307,31 +331,30 @@ moe_grouped_gemm_kernel(const __grid_constant__ GemmParams p) {
     uint32_t phase = 0;
     int acc = 0;
     uint32_t acc_phase = 0;
-    uint32_t sf_buf = 0;            // scale columns alternate between two TMEM buffers
+    uint32_t sf_buf = 0, sf_phase = 0;   // scale columns alternate between two TMEM buffers
     bool ok = true;
+    long long t_wait_acc = 0, t_wait_full = 0;
+    const long long t_begin = clock64();
     for (int w = blockIdx.x; w < total_work && ok; w += gridDim.x) {
+      const long long ta0 = clock64();
       if (!mbar_wait(smem_u32(&ctl->tmem_empty[acc]), acc_phase ^ 1, abort_word, 0x200 + acc)) break;
+      t_wait_acc += clock64() - ta0;
       tc_fence_after_sync();
       const uint32_t d0 = tmem_base + acc * acc_cols;
       for (int kb = 0; kb < p.KB; ++kb) {
+        const long long tf0 = clock64();
         if (!mbar_wait(smem_u32(&ctl->full[stage]), phase, abort_word, 0x300 + stage)) { ok = false; break; }
+        if (!mbar_wait(smem_u32(&ctl->sf_full[sf_buf]), sf_phase, abort_word, 0x500 + sf_buf)) { ok = false; break; }
+        t_wait_full += clock64() - tf0;
         tc_fence_after_sync();
         if (lane == 0) {
           const uint32_t st = stage0 + (uint32_t)stage * geo.stage_bytes;
           const uint32_t a_lo = desc_lo_sw(st);
           const uint32_t b_lo = desc_lo_sw(st + geo.a_bytes);
-          const uint32_t sf_lo = desc_lo_sf(st + geo.a_bytes + geo.b_bytes);
-          // scale columns of this stage: per 128-wide k-block {A: gate/up or tile pair, 8 columns}
-          // then {B: up to 16 columns}
+          // scale columns of this stage (written by the scale-loader warps): per 128-wide k-block
+          // {A: gate/up or tile pair, 8 columns}, then {B: up to 16 columns}
           const uint32_t sfa_t = tmem_base + kSfCol0 + sf_buf * 48;
           const uint32_t sfb_t = sfa_t + 16;
-#pragma unroll
-          for (int kk = 0; kk < kSub; ++kk) {
-            utccp_sf(sfa_t + 8 * kk, sf_lo + ((kk * 2 * kSfChunk) >> 4));
-            utccp_sf(sfa_t + 8 * kk + 4, sf_lo + ((kk * 2 * kSfChunk + kSfChunk) >> 4));
-            for (int c = 0; c < sfb_chunks; ++c)
-              utccp_sf(sfb_t + 16 * kk + 4 * c, sf_lo + ((geo.sfa_bytes + (kk * sfb_chunks + c) * kSfChunk) >> 4));
-          }
           const uint32_t first = kb != 0;
           if (merged) {
 #pragma unroll
@@ -345,17 +368,22 @@ moe_grouped_gemm_kernel(const __grid_constant__ GemmParams p) {
 #pragma unroll
             for (int s = 0; s < 2 * kSub; ++s) {
               const uint32_t sa = sfa_t + 8 * (s >> 1), sb = sfb_t + 16 * (s >> 1);
-              for (int t = 0; t < NT; ++t) {
-                const uint32_t accum = (s == 0 && t == 0) ? first : 1u;
-                umma_mxf4(d0, a_lo + 2 * s, b_lo + t * term_lo + 2 * s, idesc[s & 1], sa, sb + 4 * t, accum);
-                umma_mxf4(d0 + ncol, a_lo + (kATileBytes >> 4) + 2 * s, b_lo + t * term_lo + 2 * s, idesc[s & 1],
-                          sa + 4, sb + 4 * t, accum);
+#pragma unroll
+              for (int t = 0; t < kMaxTerms; ++t) {
+                if (t < NT) {
+                  const uint32_t accum = (s == 0 && t == 0) ? first : 1u;
+                  umma_mxf4(d0, a_lo + 2 * s, b_lo + t * term_lo + 2 * s, idesc[s & 1], sa, sb + 4 * t, accum);
+                  umma_mxf4(d0 + ncol, a_lo + (kATileBytes >> 4) + 2 * s, b_lo + t * term_lo + 2 * s, idesc[s & 1],
+                            sa + 4, sb + 4 * t, accum);
+                }
               }
             }
           }
           tc_commit(smem_u32(&ctl->empty[stage]));
+          tc_commit(smem_u32(&ctl->sf_empty[sf_buf]));
         }
         __syncwarp();
+        if (sf_buf == 1) sf_phase ^= 1;
         sf_buf ^= 1;
         if (++stage == S) { stage = 0; phase ^= 1; }
       }
@@ -363,6 +391,52 @@ moe_grouped_gemm_kernel(const __grid_constant__ GemmParams p) {
       if (lane == 0) tc_commit(smem_u32(&ctl->tmem_full[acc]));
       __syncwarp();
       if (n_acc == 2) { acc ^= 1; if (acc == 0) acc_phase ^= 1; } else { acc_phase ^= 1; }
+    }
+    if (blockIdx.x == 0 && lane == 0) {   // profiling: kilo-cycles of the MMA warp: total, waiting for data, for TMEM
+      p.status[5] = (int32_t)((clock64() - t_begin) >> 10);
+      p.status[6] = (int32_t)(t_wait_full >> 10);
+      p.status[7] = (int32_t)(t_wait_acc >> 10);
+    }
+  } else if (warp >= 10) {
+    // ------------------------------------------------------------------ scale-loader warps
+    // Four warps, one per TMEM lane quadrant.  A scale chunk in shared memory is 32 rows x 16
+    // bytes; lane l of every quadrant needs row l (the MMA expects the 32-row image replicated
+    // in all four quadrants), so each warp reads the chunk and stores it to its own quadrant
+    // with tcgen05.st -- this keeps the scale traffic out of the MMA issue stream.
+    const uint32_t lane_base = (uint32_t)((warp & 3) * 32) << 16;
+    int stage = 0;
+    uint32_t phase = 0, sf_buf = 0, sf_phase = 0;
+    bool ok = true;
+    for (int w = blockIdx.x; w < total_work && ok; w += gridDim.x) {
+      for (int kb = 0; kb < p.KB; ++kb) {
+        if (!mbar_wait(smem_u32(&ctl->full[stage]), phase, abort_word, 0x600 + stage) ||
+            !mbar_wait(smem_u32(&ctl->sf_empty[sf_buf]), sf_phase ^ 1, abort_word, 0x700 + sf_buf)) {
+          ok = false;
+          break;
+        }
+        const uint32_t sf_s = stage0 + (uint32_t)stage * geo.stage_bytes + geo.a_bytes + geo.b_bytes + lane * 16;
+        const uint32_t sfa_t = tmem_base + lane_base + kSfCol0 + sf_buf * 48;
+        uint4 a0 = ld_shared_v4(sf_s), a1 = ld_shared_v4(sf_s + kSfChunk), a2 = ld_shared_v4(sf_s + 2 * kSfChunk),
+              a3 = ld_shared_v4(sf_s + 3 * kSfChunk);
+        tmem_st_32x32b_x16(sfa_t, a0, a1, a2, a3);
+#pragma unroll
+        for (int kk = 0; kk < kSub; ++kk) {
+#pragma unroll
+          for (int c = 0; c < kMaxTerms; ++c) {
+            if (c < sfb_chunks) {
+              const uint4 v = ld_shared_v4(sf_s + geo.sfa_bytes + (kk * sfb_chunks + c) * kSfChunk);
+              tmem_st_32x32b_x4(sfa_t + 16 + 16 * kk + 4 * c, v);
+            }
+          }
+        }
+        tmem_st_wait();
+        tc_fence_before_sync();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(smem_u32(&ctl->sf_full[sf_buf]));
+        if (sf_buf == 1) sf_phase ^= 1;
+        sf_buf ^= 1;
+        if (++stage == S) { stage = 0; phase ^= 1; }
+      }
     }
   } else {
     // ------------------------------------------------------------------ epilogue warps
@@ -378,6 +452,8 @@ moe_grouped_gemm_kernel(const __grid_constant__ GemmParams p) {
     const bool fused = GATEUP && p.h_out == nullptr;
     int acc = 0;
     uint32_t acc_phase = 0;
+    long long t_wait_epi = 0;
+    const long long t_begin_epi = clock64();
     for (int w = blockIdx.x; w < total_work; w += gridDim.x) {
       const int b = w / p.MT, m = w - b * p.MT;
       const int r0 = b * B;
@@ -390,8 +466,10 @@ moe_grouped_gemm_kernel(const __grid_constant__ GemmParams p) {
         nvalid += __popc(__ballot_sync(0xffffffffu, (int)(id >> 24) < p.topk && (int)(id & 0xFFFFFFu) < p.T));
       }
       // all eight warps take the same decision, so nobody is left alone at a later barrier
+      const long long te0 = clock64();
       const bool ok = mbar_wait(smem_u32(&ctl->tmem_full[acc]), acc_phase, abort_word, 0x400 + acc);
       if (!epi_all(ok)) break;
+      t_wait_epi += clock64() - te0;
       tc_fence_after_sync();
       const uint32_t t0 = tmem_base + ((uint32_t)(quad * 32) << 16) + acc * acc_cols;
       const bool j_ok = j < p.rows;
@@ -498,6 +576,10 @@ moe_grouped_gemm_kernel(const __grid_constant__ GemmParams p) {
           }
         }
       }
+    }
+    if (blockIdx.x == 0 && tid_e == 0) {   // profiling: kilo-cycles of an epilogue warp: total, waiting for a tile
+      p.status[8] = (int32_t)((clock64() - t_begin_epi) >> 10);
+      p.status[9] = (int32_t)(t_wait_epi >> 10);
     }
   }
 
@@ -733,8 +815,11 @@ __global__ void __launch_bounds__(128, 1) probe_mma_rate_kernel(const int32_t* c
     for (int s = 0; s < 2; ++s) idesc[s] = make_idesc_block_scaled(kFmtE2M1_mxf4, kFmtE2M1_mxf4, 128, N, 2 * s, 2 * s);
     const uint32_t a_lo = desc_lo_sw(a), b_lo = desc_lo_sw(b);
     const uint32_t d1 = tbase + (nacc > 1 ? N : 0);
+    const int ncp = cfg[0];      // scale copies (tcgen05.cp) issued before every group of four MMAs
+    const uint32_t sf_lo = desc_lo_sf(sf);
     const long long t0 = clock64();
     for (int i = 0; i < count; i += 4) {
+      for (int c = 0; c < ncp; ++c) utccp_sf(tbase + 448 + 4 * (c & 7) + ((i >> 2) & 1) * 32, sf_lo + ((c & 1) << 5));
       umma_mxf4(tbase, a_lo, b_lo, idesc[0], tbase + 448, tbase + 456, 1);
       umma_mxf4(d1, a_lo, b_lo, idesc[0], tbase + 448, tbase + 456, 1);
       umma_mxf4(tbase, a_lo + 2, b_lo + 2, idesc[1], tbase + 448, tbase + 456, 1);
