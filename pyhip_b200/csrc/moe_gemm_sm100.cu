@@ -2,11 +2,11 @@
 // per-32 E8M0 block scales on both operands.
 //
 // Orientation ("swap-AB"): the MMA's M side holds 128 weight rows, its N side holds the token
-// tile of one sorted block (B = 32/64/128 rows), so ragged token counts cost N-padding, never M.
+// tile of one sorted block (B rows, a multiple of 16), so ragged token counts cost N-padding only.
 //     D[128 weight rows, tokens] += W4[128, K] * A4[tokens, K]^T
 // W4: the MXFP4 weights exactly as they sit in HBM (packed E2M1, canonical layout, no repack):
-//     TMA brings 128x128 tiles into 64-byte-swizzled shared memory; the K tail (K not a multiple
-//     of 128) and the row tail are filled with zeros by the copy engine and never fetched.
+//     TMA brings 128-row x 256-element tiles (128-byte rows = one swizzle span) into shared
+//     memory; the K tail and the row tail are filled with zeros by the copy engine, never fetched.
 // A4: an activation row is a SUM of NT packed-FP4 terms (value, residual, residual of the
 //     residual ...), each with its own E8M0 scales per 32 along K.  Three terms carry a bf16
 //     activation to ~2e-3 of its block maximum, which keeps the layer within cosine 0.9999 of the
@@ -14,22 +14,27 @@
 //     is dequantised in the main loop.  The terms of a block are stacked along N when they fit
 //     one instruction (N = NT*B <= 256; the epilogue adds the column groups), otherwise each term
 //     is its own instruction into the same accumulator.
-// Block scales travel shared memory -> tensor memory with tcgen05.cp and are applied by the MMA.
 //
-// A pipeline stage always carries TWO 128-row weight tiles that share one activation tile: the
-// gate and the up rows of the same features (gate-up GEMM), or two consecutive row tiles of
-// the down projection.
-// Warp roles (320 threads): warp 0 = TMA producer, warp 1 = MMA issuer + TMEM owner,
-// warps 2-9 = epilogue (two per TMEM lane quadrant).  The gate-up epilogue applies the activation,
-// parks the bf16 result in a shared-memory staging tile and re-quantises it block-wise into the
-// down GEMM's operand format, overlapped with the next tile's main loop.  Persistent CTAs walk the work list
-// (sorted block, 128-row weight tile) in block-major order so that the CTAs running at the same
-// time share activation tiles and neighbouring blocks of an expert share weight tiles in L2.
-// The issuing threads are the scarce resource at small token tiles, so a pipeline stage is
-// four copy instructions (weights, activations, two scale groups) and descriptors are kept as
-// precomputed 32-bit halves.
-// All barrier waits are bounded; a wait that runs out sets status[] and the CTA unwinds
-// (frees its tensor memory) instead of spinning.
+// A pipeline stage (K = 256) carries TWO 128-row weight tiles that share one activation tile: the
+// gate and the up rows of the same features (gate-up GEMM), or two consecutive row tiles of the
+// down projection.  It is four copy instructions: weights, all activation terms, two scale groups.
+//
+// Warp roles (448 threads):
+//   warp 0      TMA producer
+//   warp 1      MMA issuer + TMEM owner (whole warp walks the loop, lane 0 issues; descriptors are
+//               precomputed 32-bit halves -- the issuing thread is the scarce resource)
+//   warps 2-9   epilogue, two per TMEM lane quadrant: activation with the oracle's bf16 roundings,
+//               bf16 staging tile in shared memory, block-wise re-quantisation into the down GEMM's
+//               operand format, overlapped with the next tile's main loop (two TMEM accumulators)
+//   warps 10-13 scale loaders: copy the stage's E8M0 scale chunks shared memory -> registers ->
+//               tensor memory (tcgen05.st, one warp per lane quadrant, two TMEM scale buffers).
+//               tcgen05.cp would do the same copy but runs in the MMA's own in-order pipe at
+//               ~70-100 cycles per chunk, which was the limiter at small token tiles.
+// Persistent CTAs walk the work list (sorted block, weight tile pair) in block-major order so that
+// CTAs running at the same time share activation tiles and neighbouring blocks of an expert share
+// weight tiles in L2.
+// All barrier waits are bounded; a wait that runs out sets status[] and the CTA unwinds (frees its
+// tensor memory) instead of spinning.  status[4..9] carry cycle counters of CTA 0's roles.
 #include <cuda_bf16.h>
 #include <cuda_fp4.h>
 #include <cuda_fp8.h>
@@ -56,8 +61,8 @@ constexpr int kSfCol0 = kAccColsLimit;   // scale columns: 2 buffers x 48 = per 
 constexpr int kSmemLimit = 232448;       // 227 KB
 
 struct GemmParams {
-  CUtensorMap tmW;     // weights: gate-up (K, I, 2, E) box (128,128,2,1); down (K, H, 1, E) box (128,256,1,1)
-  CUtensorMap tmA;     // activations (KP, max_rows, NT terms)    box (128, B, NT)
+  CUtensorMap tmW;     // weights: gate-up (K, I, 2, E) box (256,128,2,1); down (K, H, 1, E) box (256,256,1,1)
+  CUtensorMap tmA;     // activations (KP, max_rows, NT terms)    box (256, B, NT)
   const uint8_t* w_scale;   // [E, MT, KB, 2, 512]
   const uint8_t* asf;       // [blocks, KB, chunks, 512]
   const uint32_t* sorted_ids;
