@@ -13,6 +13,12 @@ convention (`expert_mask`, src/contrib/fused_moe.py:134,210-212) and a single-pr
   4. combine all-to-all-v of the per-rank partial outputs back to the source rank, summed there
      in fp32 in ascending rank (= ascending expert) order.
 
+For small batches (decode) the exchange degenerates gracefully into its fixed-shape form: every
+rank receives every token (all-gather of rows and routing), runs its local experts on all of them
+and the partial outputs are summed back with a reduce-scatter.  No counts, no host read, constant
+shapes from step to step -- at T <= `small_batch` tokens per rank the bytes are irrelevant and the
+two latencies saved are not.
+
 All collectives are NCCL (`torch.distributed`); device kernels never touch peer memory.  The
 integer plumbing (`plan_dispatch`, `scatter_back`) is backend-agnostic and is exercised with gloo
 CPU ranks in the tests.
@@ -55,11 +61,13 @@ class ExpertParallelMoE:
     `fused_moe` on this rank's prepared weights."""
 
     def __init__(self, w1, w1_scale, w2, w2_scale, num_experts: int, rank: int, world: int,
-                 group: Optional[dist.ProcessGroup] = None, local_fn: Optional[Callable] = None):
+                 group: Optional[dist.ProcessGroup] = None, local_fn: Optional[Callable] = None,
+                 small_batch: int = 512):
         if num_experts % world:
             raise ValueError("num_experts must be divisible by the number of ranks")
         self.E, self.rank, self.world, self.group = num_experts, rank, world, group
         self.E_local = num_experts // world
+        self.small_batch = small_batch
         if local_fn is None:
             from .fused_moe import QuantType, fused_moe
 
@@ -72,6 +80,35 @@ class ExpertParallelMoE:
         dist.all_to_all_single(out, inp, out_splits, in_splits, group=self.group)
 
     def forward(self, x: torch.Tensor, topk_weight: torch.Tensor, topk_ids: torch.Tensor) -> torch.Tensor:
+        if x.shape[0] <= self.small_batch:
+            return self.forward_gathered(x, topk_weight, topk_ids)
+        return self.forward_dispatch(x, topk_weight, topk_ids)
+
+    def forward_gathered(self, x, topk_weight, topk_ids):
+        """Fixed-shape exchange: all-gather rows + routing, local experts over all W*T rows (rows
+        routed elsewhere are dropped by the sorter), reduce-scatter of the partial outputs.
+        Every rank must call with the same T."""
+        T, H = x.shape
+        K = topk_ids.shape[1]
+        W = self.world
+        x_all = torch.empty(W * T, H, dtype=x.dtype, device=x.device)
+        dist.all_gather_into_tensor(x_all, x.contiguous(), group=self.group)
+        meta = torch.cat([topk_ids.to(torch.int32), topk_weight.to(torch.float32).view(torch.int32)], dim=1)
+        meta_all = torch.empty(W * T, 2 * K, dtype=torch.int32, device=x.device)
+        dist.all_gather_into_tensor(meta_all, meta.contiguous(), group=self.group)
+        local_ids = (meta_all[:, :K] - self.rank * self.E_local).contiguous()
+        tw_all = meta_all[:, K:].contiguous().view(torch.float32)
+        y_part = self.local_fn(x_all, tw_all, local_ids)
+        y = torch.empty(T, H, dtype=x.dtype, device=x.device)
+        if dist.get_backend(self.group) == "nccl":
+            dist.reduce_scatter_tensor(y, y_part.contiguous(), op=dist.ReduceOp.SUM, group=self.group)
+        else:                                   # gloo has no reduce-scatter: sum everywhere, keep own slice
+            acc = y_part.float()
+            dist.all_reduce(acc, group=self.group)
+            y.copy_(acc[self.rank * T:(self.rank + 1) * T])
+        return y
+
+    def forward_dispatch(self, x: torch.Tensor, topk_weight: torch.Tensor, topk_ids: torch.Tensor) -> torch.Tensor:
         T, H = x.shape
         K = topk_ids.shape[1]
         send_rows, send_counts = plan_dispatch(topk_ids, self.E_local, self.world)

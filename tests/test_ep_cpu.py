@@ -19,7 +19,7 @@ def _free_port():
         return s.getsockname()[1]
 
 
-def _worker(rank, world, port, fail_rank, q):
+def _worker(rank, world, port, fail_rank, q, small_batch=0):
     os.environ["MASTER_ADDR"] = "127.0.0.1"
     os.environ["MASTER_PORT"] = str(port)
     torch.set_num_threads(1)
@@ -37,7 +37,8 @@ def _worker(rank, world, port, fail_rank, q):
         def local_fn(xr, twr, ids_local):
             return orc.torch_moe_oracle(xr, w1[lo:lo + El], w2[lo:lo + El], twr, ids_local)
 
-        layer = ep.ExpertParallelMoE(None, None, None, None, E, rank, world, local_fn=local_fn)
+        layer = ep.ExpertParallelMoE(None, None, None, None, E, rank, world, local_fn=local_fn,
+                                     small_batch=small_batch)
         if fail_rank == rank:
             q.put((rank, "skipped"))
             return
@@ -55,11 +56,11 @@ def _worker(rank, world, port, fail_rank, q):
             pass
 
 
-def _spawn(world, fail_rank=None):
+def _spawn(world, fail_rank=None, small_batch=0):
     ctx = mp.get_context("spawn")
     q = ctx.Queue()
     port = _free_port()
-    procs = [ctx.Process(target=_worker, args=(r, world, port, fail_rank, q)) for r in range(world)]
+    procs = [ctx.Process(target=_worker, args=(r, world, port, fail_rank, q, small_batch)) for r in range(world)]
     for p in procs:
         p.start()
     res = dict(q.get(timeout=120) for _ in range(world))
@@ -77,9 +78,10 @@ def test_plan_dispatch_groups_tokens_once_per_rank():
     assert y[:, 0].tolist() == [2.0, 1.0, 2.0]
 
 
-@pytest.mark.parametrize("world", [2, 4])
-def test_expert_parallel_matches_single_process_oracle(world):
-    res = _spawn(world)
+@pytest.mark.parametrize("world,small_batch", [(2, 0), (4, 0), (2, 512)])
+def test_expert_parallel_matches_single_process_oracle(world, small_batch):
+    """small_batch=0 forces the all-to-all-v dispatch/combine, 512 the gathered fixed-shape form."""
+    res = _spawn(world, small_batch=small_batch)
     for r in range(world):
         cos, mx = res[r]
         assert cos > 0.9999 and mx < 5e-3, (r, cos, mx)
