@@ -95,10 +95,20 @@ int b200moe_quant_rows(const void* src_bf16, int32_t src_mode, const uint32_t* s
                        const int32_t* num_valid_ids, int32_t T, int32_t K, int32_t Kd, int32_t B,
                        int32_t terms, int64_t max_rows, void* q, void* sf, void* stream);
 
+/* Same for FP8 128x128-block weights (weight_format B200MOE_W_FP8_128): two e4m3 terms with E8M0
+ * scales per 32 (stands where the reference calls aiter's per_1x128 activation quantiser,
+ * src/contrib/fused_moe.py:276-281,375-381).  Kd must be a multiple of 128.
+ *   q: u8 [2, max_rows, Kd];  sf: per (block of B sorted rows, 128-wide k-block) two 512-byte chunks. */
+int b200moe_quant_rows_e4m3(const void* src_bf16, int32_t src_mode, const uint32_t* sorted_ids,
+                            const int32_t* num_valid_ids, int32_t T, int32_t K, int32_t Kd, int32_t B,
+                            int64_t max_rows, void* q, void* sf, void* stream);
+
 /* Gate-up grouped GEMM + activation: replaces moe_2stage_splitk(with_silu=True) /
  * moe_gemm_mxfp4(gate_up=True) (src/contrib/moe.py:362-702, src/contrib/moe_gemm_mxfp4.py:972-1290).
  * Consumes the quantised rows in workspace (xq), the canonical packed w1 [E,2I,H/2], its prepared
  * scale image and the sort arrays.
+ *   With weight_format B200MOE_W_FP8_128 (replaces moe_gemm_8wave_g1u1, src/contrib/moe_gemm_8wave.py:131-765):
+ *   w1_q is e4m3 [E,2I,H] and w1_scale_prepared is the raw fp32 [E, 2I/128, H/128] scale tensor.
  *   h_out != NULL : bf16 [T, K, I] scattered by (token,k) like the reference (moe.py:651-655)
  *   h_out == NULL : the result is re-quantised in sorted-row order into workspace hq for
  *                   b200moe_down (fused path). */

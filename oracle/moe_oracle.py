@@ -262,3 +262,23 @@ def fp4_terms_dequant(codes: np.ndarray, exps: np.ndarray) -> torch.Tensor:
     v = _E2M1[codes].reshape(codes.shape[:-1] + (K // 32, 32))
     v = v * np.ldexp(np.float32(1.0), exps.astype(np.int32) - 127).astype(np.float32)[..., None]
     return torch.from_numpy(v.reshape(codes.shape).sum(axis=0))
+
+
+def e4m3_terms_quant(x: torch.Tensor, terms: int = 2):
+    """Activation operand of the FP8 GEMMs: per 32 along K and per term,
+    e = max(biased_exponent(amax(r)) - 7, 0), q = e4m3_rne(r * 2**(127-e)), r <- r - q * 2**(e-127).
+    Returns (q float8_e4m3fn [terms, ..., K], exps uint8 [terms, ..., K/32])."""
+    xf = x.float().numpy()
+    K = xf.shape[-1]
+    r = xf.reshape(xf.shape[:-1] + (K // 32, 32)).copy()
+    qs, exps = [], []
+    for _ in range(terms):
+        amax = np.abs(r).max(axis=-1)
+        e = np.maximum(_biased_exponent(amax) - 7, 0)
+        inv = np.ldexp(np.float32(1.0), 127 - e).astype(np.float32)
+        q = torch.from_numpy(np.ascontiguousarray(r * inv[..., None], dtype=np.float32)).clamp(-448.0, 448.0) \
+            .to(torch.float8_e4m3fn)
+        r = r - q.float().numpy() * np.ldexp(np.float32(1.0), e - 127).astype(np.float32)[..., None]
+        qs.append(q.reshape(xf.shape))
+        exps.append(e.astype(np.uint8))
+    return torch.stack(qs), np.stack(exps)

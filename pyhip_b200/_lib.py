@@ -18,7 +18,7 @@ import subprocess
 PKG_DIR = pathlib.Path(__file__).resolve().parent
 CSRC = PKG_DIR / "csrc"
 LIB_PATH = PKG_DIR / "libb200moe.so"
-SOURCES = ["api.cu", "moe_aux.cu", "moe_gemm_sm100.cu", "forward_static.cu"]
+SOURCES = ["api.cu", "moe_aux.cu", "moe_gemm_sm100.cu", "moe_gemm_fp8_sm100.cu", "forward_static.cu"]
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
               "-shared", "-Xcompiler", "-fPIC"]
 
@@ -44,7 +44,7 @@ class Workspace(ctypes.Structure):
 
 EXPORTS = ["b200moe_version", "b200moe_last_error", "b200moe_workspace_layout",
            "b200moe_prepared_scale_bytes", "b200moe_prepare_scales", "b200moe_sort_align",
-           "b200moe_quant_rows", "b200moe_gateup", "b200moe_down", "b200moe_combine",
+           "b200moe_quant_rows", "b200moe_quant_rows_e4m3", "b200moe_gateup", "b200moe_down", "b200moe_combine",
            "b200moe_forward", "b200moe_forward_static", "b200moe_debug_probe"]
 
 
@@ -81,6 +81,7 @@ def lib() -> ctypes.CDLL:
     L.b200moe_prepare_scales.argtypes = [sp, ctypes.c_int, vp, vp, vp]
     L.b200moe_sort_align.argtypes = [vp, vp, i32, i32, i32, i32, vp, vp, vp, vp, vp, vp, vp]
     L.b200moe_quant_rows.argtypes = [vp, i32, vp, vp, i32, i32, i32, i32, i32, i64, vp, vp, vp]
+    L.b200moe_quant_rows_e4m3.argtypes = [vp, i32, vp, vp, i32, i32, i32, i32, i64, vp, vp, vp]
     L.b200moe_gateup.argtypes = [sp, wp, vp, vp, vp, vp, vp]
     L.b200moe_down.argtypes = [sp, wp, vp, vp, vp, vp]
     L.b200moe_combine.argtypes = [sp, wp, vp, vp, vp, vp]

@@ -28,8 +28,12 @@ static int check_shape(const b200moe_shape* s) {
   B200_CHECK_ARG(s->H >= 32 && s->H % 32 == 0, "H=%d must be a positive multiple of 32", s->H);
   B200_CHECK_ARG(s->I >= 32 && s->I % 32 == 0, "I=%d must be a positive multiple of 32", s->I);
   B200_CHECK_ARG(s->H % 8 == 0, "H must be a multiple of 8");
-  B200_CHECK_ARG(s->weight_format == B200MOE_W_MXFP4, "weight_format %d is not supported by this build",
-                 s->weight_format);
+  B200_CHECK_ARG(s->weight_format == B200MOE_W_MXFP4 || s->weight_format == B200MOE_W_FP8_128,
+                 "weight_format %d unknown", s->weight_format);
+  if (s->weight_format == B200MOE_W_FP8_128) {
+    B200_CHECK_ARG(s->H % 128 == 0 && s->I % 128 == 0, "FP8 128x128 weights need H and I to be multiples of 128");
+    B200_CHECK_ARG(s->B <= 96, "FP8 128x128 weights: B=%d exceeds 96", s->B);
+  }
   B200_CHECK_ARG(s->activation == B200MOE_ACT_SILU || s->activation == B200MOE_ACT_SWIGLU,
                  "activation %d unknown", s->activation);
   B200_CHECK_ARG(s->act_terms == 0 || (s->act_terms >= 2 && s->act_terms <= 4), "act_terms=%d not in {0,2,3,4}",
@@ -53,7 +57,8 @@ const char* b200moe_last_error(void) { return g_err; }
 int b200moe_workspace_layout(const b200moe_shape* s, b200moe_workspace* ws) {
   if (int rc = check_shape(s)) return rc;
   B200_CHECK_ARG(ws != nullptr, "workspace descriptor is NULL");
-  const int NT = terms_of(s);
+  const bool fp8w = s->weight_format == B200MOE_W_FP8_128;
+  const int NT = fp8w ? 2 : terms_of(s);
   const int64_t P = (int64_t)s->T * s->K;
   const int64_t nblk = (P + (int64_t)s->E_route * (s->B - 1) + s->B - 1) / s->B;
   const int64_t L = std::max<int64_t>(nblk, 1) * s->B;
@@ -73,10 +78,17 @@ int b200moe_workspace_layout(const b200moe_shape* s, b200moe_workspace* ws) {
   ws->off_num_valid = take(8);
   ws->off_loc = take(std::max<int64_t>(P, 1) * 4);
   ws->off_status = take(64);
-  ws->off_xq = take(NT * L * (HP / 2));
-  ws->off_xsf = take(nb * (HP / 128) * act_sf_chunks(NT, act_term_stride(s->B, NT, 2)) * kSfChunk);
-  ws->off_hq = take(NT * L * (IP / 2));
-  ws->off_hsf = take(nb * (IP / 128) * act_sf_chunks(NT, act_term_stride(s->B, NT, 2)) * kSfChunk);
+  if (fp8w) {   // two e4m3 terms, one byte per element, one scale chunk per term
+    ws->off_xq = take(2 * L * s->H);
+    ws->off_xsf = take(nb * (s->H / 128) * 2 * kSfChunk);
+    ws->off_hq = take(2 * L * s->I);
+    ws->off_hsf = take(nb * (s->I / 128) * 2 * kSfChunk);
+  } else {
+    ws->off_xq = take(NT * L * (HP / 2));
+    ws->off_xsf = take(nb * (HP / 128) * act_sf_chunks(NT, act_term_stride(s->B, NT, 2)) * kSfChunk);
+    ws->off_hq = take(NT * L * (IP / 2));
+    ws->off_hsf = take(nb * (IP / 128) * act_sf_chunks(NT, act_term_stride(s->B, NT, 2)) * kSfChunk);
+  }
   ws->off_out2 = take(L * s->H * 2);
   ws->total_bytes = off;
   return 0;
@@ -86,6 +98,7 @@ int b200moe_prepared_scale_bytes(const b200moe_shape* s, int which, int64_t* sca
   if (int rc = check_shape(s)) return rc;
   B200_CHECK_ARG(which == 1 || which == 2, "which=%d must be 1 or 2", which);
   B200_CHECK_ARG(scale_bytes != nullptr, "scale_bytes is NULL");
+  B200_CHECK_ARG(s->weight_format == B200MOE_W_MXFP4, "FP8 128x128 scales are consumed in place: nothing to prepare");
   // two 128-row tiles per chunk pair: (gate, up) of one feature tile, or two consecutive down tiles
   const int groups = which == 1 ? (s->I + 127) / 128 : (s->H + 255) / 256;
   const int Kd = which == 1 ? s->H : s->I;
@@ -97,6 +110,7 @@ int b200moe_prepare_scales(const b200moe_shape* s, int which, const void* w_s, v
   if (int rc = check_shape(s)) return rc;
   B200_CHECK_ARG(which == 1 || which == 2, "which=%d must be 1 or 2", which);
   B200_CHECK_ARG(w_s && out_scale, "prepare_scales: NULL pointer");
+  B200_CHECK_ARG(s->weight_format == B200MOE_W_MXFP4, "FP8 128x128 scales are consumed in place: nothing to prepare");
   B200_CHECK_ARG(((uintptr_t)out_scale & 15) == 0, "prepare_scales: output must be 16-byte aligned");
   const int Kd = which == 1 ? s->H : s->I;
   return launch_repack_scales(w_s, out_scale, s->E, which == 1, which == 1 ? s->I : s->H, Kd, (cudaStream_t)stream);
@@ -123,6 +137,18 @@ int b200moe_quant_rows(const void* src_bf16, int32_t src_mode, const uint32_t* s
                  "quant_rows: source and destination must be 16-byte aligned");
   return launch_quant_rows(src_bf16, src_mode, sorted_ids, num_valid_ids, T, K, Kd, B, terms, max_rows, q, sf,
                            (cudaStream_t)stream);
+}
+
+int b200moe_quant_rows_e4m3(const void* src_bf16, int32_t src_mode, const uint32_t* sorted_ids,
+                            const int32_t* num_valid_ids, int32_t T, int32_t K, int32_t Kd, int32_t B,
+                            int64_t max_rows, void* q, void* sf, void* stream) {
+  B200_CHECK_ARG(src_mode == 0 || src_mode == 1, "quant_rows: src_mode=%d", src_mode);
+  B200_CHECK_ARG(sorted_ids && num_valid_ids && q && sf, "quant_rows: NULL pointer");
+  B200_CHECK_ARG(T == 0 || src_bf16, "quant_rows: NULL source");
+  B200_CHECK_ARG(((uintptr_t)src_bf16 & 15) == 0 && ((uintptr_t)q & 15) == 0,
+                 "quant_rows: source and destination must be 16-byte aligned");
+  return launch_quant_rows_e4m3(src_bf16, src_mode, sorted_ids, num_valid_ids, T, K, Kd, B, max_rows, q, sf,
+                                (cudaStream_t)stream);
 }
 
 static void fill_common(GemmArgs& g, const b200moe_shape* s, const b200moe_workspace* ws, uint8_t* base) {
@@ -158,6 +184,10 @@ int b200moe_gateup(const b200moe_shape* s, const b200moe_workspace* ws, void* wo
   g.h_out = h_out;
   g.oq = base + ws->off_hq;
   g.osf = base + ws->off_hsf;
+  if (s->weight_format == B200MOE_W_FP8_128) {
+    g.out_kp = s->I;
+    return launch_grouped_gemm_fp8(g, (cudaStream_t)stream);
+  }
   g.out_kp = (int)kp_of(s->I);
   return launch_grouped_gemm(g, (cudaStream_t)stream);
 }
@@ -178,6 +208,7 @@ int b200moe_down(const b200moe_shape* s, const b200moe_workspace* ws, void* work
   g.a_q = base + ws->off_hq;
   g.asf = base + ws->off_hsf;
   g.out2 = base + ws->off_out2;
+  if (s->weight_format == B200MOE_W_FP8_128) return launch_grouped_gemm_fp8(g, (cudaStream_t)stream);
   return launch_grouped_gemm(g, (cudaStream_t)stream);
 }
 
@@ -205,9 +236,14 @@ int b200moe_forward(const b200moe_shape* s, const b200moe_workspace* ws, void* w
                               (int32_t*)(base + ws->off_sorted_e), (int32_t*)(base + ws->off_num_valid),
                               (int32_t*)(base + ws->off_loc), stream);
   if (rc) return rc;
-  rc = b200moe_quant_rows(x_bf16, 0, (const uint32_t*)(base + ws->off_sorted_ids),
-                          (const int32_t*)(base + ws->off_num_valid), s->T, s->K, s->H, s->B, terms_of(s),
-                          ws->max_rows, base + ws->off_xq, base + ws->off_xsf, stream);
+  if (s->weight_format == B200MOE_W_FP8_128)
+    rc = b200moe_quant_rows_e4m3(x_bf16, 0, (const uint32_t*)(base + ws->off_sorted_ids),
+                                 (const int32_t*)(base + ws->off_num_valid), s->T, s->K, s->H, s->B, ws->max_rows,
+                                 base + ws->off_xq, base + ws->off_xsf, stream);
+  else
+    rc = b200moe_quant_rows(x_bf16, 0, (const uint32_t*)(base + ws->off_sorted_ids),
+                            (const int32_t*)(base + ws->off_num_valid), s->T, s->K, s->H, s->B, terms_of(s),
+                            ws->max_rows, base + ws->off_xq, base + ws->off_xsf, stream);
   if (rc) return rc;
   rc = b200moe_gateup(s, ws, workspace, w1_q, w1_scale, nullptr, stream);
   if (rc) return rc;

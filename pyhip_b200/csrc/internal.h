@@ -88,6 +88,15 @@ struct GemmArgs {
   void* out2;          // down: bf16 [max_rows, H]
 };
 int launch_grouped_gemm(const GemmArgs& a, cudaStream_t st);
+// FP8 128x128-block variant (moe_gemm_fp8_sm100.cu): w_data = e4m3 bytes [E, parts*rows, Kd], w_scale = fp32
+// [E, parts*rows/128, Kd/128] (used in place), a_q = two e4m3 terms [2, max_rows, Kd], NT ignored
+int launch_grouped_gemm_fp8(const GemmArgs& a, cudaStream_t st);
+int launch_quant_rows_e4m3(const void* src, int src_mode, const uint32_t* sorted_ids, const int32_t* num_valid,
+                           int T, int K, int Kd, int B, int64_t max_rows, void* q, void* sf, cudaStream_t st);
+int encode_map_sw(CUtensorMap* map, CUtensorMapDataType type, int rank, const void* base, const cuuint64_t* dims,
+                  const cuuint64_t* strides, const cuuint32_t* box, CUtensorMapSwizzle swizzle,
+                  CUtensorMapL2promotion promo, const char* what);
+int device_sm_count();
 int run_debug_probe(int which, const void* in, void* out, cudaStream_t st);
 
 }  // namespace b200moe

@@ -1,10 +1,6 @@
 // Integer / byte kernels around the grouped GEMMs: token->expert sort/align, activation
 // quantise-and-gather, scale repack, weighted combine.  All HBM- or latency-bound.
-#include <cuda_bf16.h>
-#include <cuda_fp4.h>
-#include <cuda_fp8.h>
-
-#include "internal.h"
+#include "gemm_common.cuh"
 
 namespace b200moe {
 
@@ -162,34 +158,6 @@ int launch_sort_align(const int32_t* ids, const float* w, int T, int K, int E, i
 // term picks up the rest).  Three terms reproduce a bf16 input to ~2e-3 of the block maximum,
 // four terms to ~1e-4.
 // =====================================================================================
-__device__ __forceinline__ float pow2_from_biased(int e) {   // 2^(e-127), e in [0,254]
-  return __uint_as_float(e == 0 ? 0x00400000u : ((uint32_t)e << 23));
-}
-
-// quantise 32 floats to E2M1 with a shared scale; q: 16 bytes (low nibble = even element);
-// x is replaced by the residual
-__device__ __forceinline__ int quant_block32_fp4(float (&x)[32], uint4& q) {
-  float amax = 0.f;
-#pragma unroll
-  for (int i = 0; i < 32; ++i) amax = fmaxf(amax, fabsf(x[i]));
-  const int e = max((int)((__float_as_uint(amax) >> 23) & 0xFF) - 2, 0);
-  const float inv = __uint_as_float((uint32_t)(254 - e) << 23);
-  const float sc = pow2_from_biased(e);
-  uint32_t w[4] = {0, 0, 0, 0};
-#pragma unroll
-  for (int i = 0; i < 32; i += 2) {
-    const __nv_fp4x2_storage_t pk =
-        __nv_cvt_float2_to_fp4x2(make_float2(x[i] * inv, x[i + 1] * inv), __NV_E2M1, cudaRoundNearest);
-    w[i >> 3] |= (uint32_t)pk << (((i >> 1) & 3) * 8);
-    __half2_raw h = __nv_cvt_fp4x2_to_halfraw2(pk, __NV_E2M1);
-    const float2 f = __half22float2(*reinterpret_cast<__half2*>(&h));
-    x[i] -= f.x * sc;
-    x[i + 1] -= f.y * sc;
-  }
-  q = make_uint4(w[0], w[1], w[2], w[3]);
-  return e;
-}
-
 __global__ void __launch_bounds__(256)
 quant_rows_kernel(const __nv_bfloat16* __restrict__ src, int src_mode, const uint32_t* __restrict__ sorted_ids,
                   const int32_t* __restrict__ num_valid, int T, int K, int Kd, int KP, int B, int NT, int TS,
@@ -245,6 +213,67 @@ int launch_quant_rows(const void* src, int src_mode, const uint32_t* sorted_ids,
   quant_rows_kernel<<<blocks, 256, 0, st>>>(reinterpret_cast<const __nv_bfloat16*>(src), src_mode, sorted_ids,
                                             num_valid, T, K, Kd, KP, B, NT, act_term_stride(B, NT, 2), max_rows,
                                             (uint8_t*)q, (uint8_t*)sf);
+  B200_CHECK_CUDA(cudaGetLastError());
+  return 0;
+}
+
+// two-term e4m3 variant (operand of the FP8 GEMMs): q [2, max_rows, Kd] bytes, one scale chunk
+// per term (virtual row = term*128 + r)
+__global__ void __launch_bounds__(256)
+quant_rows_e4m3_kernel(const __nv_bfloat16* __restrict__ src, int src_mode, const uint32_t* __restrict__ sorted_ids,
+                       const int32_t* __restrict__ num_valid, int T, int K, int Kd, int B, int64_t max_rows,
+                       uint8_t* __restrict__ q, uint8_t* __restrict__ sf) {
+  const int nb = Kd / 32;
+  const int KB = Kd / 128;
+  const int64_t term_stride = max_rows * Kd;
+  const int64_t rows_live = min((int64_t)num_valid[0], max_rows);
+  for (int64_t g = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; g < rows_live * nb;
+       g += (int64_t)gridDim.x * blockDim.x) {
+    const int64_t r = g / nb;
+    const int j = (int)(g % nb);
+    const uint32_t id = sorted_ids[r];
+    const int tok = (int)(id & 0xFFFFFFu), kk = (int)(id >> 24);
+    const bool valid = (kk < K) && (tok < T);
+    float x[32];
+    if (valid) {
+      const int64_t srow = (src_mode == 0) ? (int64_t)tok : ((int64_t)tok * K + kk);
+      const uint4* p = reinterpret_cast<const uint4*>(src + srow * Kd + j * 32);
+#pragma unroll
+      for (int v = 0; v < 4; ++v) {
+        uint4 u = p[v];
+        const __nv_bfloat162* b2 = reinterpret_cast<const __nv_bfloat162*>(&u);
+#pragma unroll
+        for (int t = 0; t < 4; ++t) {
+          float2 f = __bfloat1622float2(b2[t]);
+          x[v * 8 + t * 2] = f.x;
+          x[v * 8 + t * 2 + 1] = f.y;
+        }
+      }
+    } else {
+#pragma unroll
+      for (int i = 0; i < 32; ++i) x[i] = 0.f;
+    }
+#pragma unroll
+    for (int t = 0; t < 2; ++t) {
+      uint4 q0, q1;
+      const int e = quant_block32_e4m3(x, q0, q1);
+      uint4* dst = reinterpret_cast<uint4*>(q + t * term_stride + r * Kd + j * 32);
+      dst[0] = q0;
+      dst[1] = q1;
+      sf[act_sf_index(r / B, j >> 2, KB, B, 2, 128, t, (int)(r % B), j & 3)] = (uint8_t)e;
+    }
+  }
+}
+
+int launch_quant_rows_e4m3(const void* src, int src_mode, const uint32_t* sorted_ids, const int32_t* num_valid,
+                           int T, int K, int Kd, int B, int64_t max_rows, void* q, void* sf, cudaStream_t st) {
+  B200_CHECK_ARG(B >= 16 && B <= 96 && B % 16 == 0, "quant_rows (e4m3): B=%d is not a multiple of 16 in [16,96]", B);
+  B200_CHECK_ARG(Kd % 128 == 0, "quant_rows (e4m3): Kd=%d must be a multiple of 128", Kd);
+  int64_t work = max_rows * (Kd / 32);
+  int blocks = (int)std::min<int64_t>((work + 255) / 256, 148 * 16);
+  if (blocks < 1) blocks = 1;
+  quant_rows_e4m3_kernel<<<blocks, 256, 0, st>>>(reinterpret_cast<const __nv_bfloat16*>(src), src_mode, sorted_ids,
+                                                 num_valid, T, K, Kd, B, max_rows, (uint8_t*)q, (uint8_t*)sf);
   B200_CHECK_CUDA(cudaGetLastError());
   return 0;
 }

@@ -1,0 +1,455 @@
+// Grouped GEMMs for FP8 (e4m3) expert weights with one fp32 scale per 128x128 block
+// (the format of tests/contrib/moe/test_moe.py:201-260 of the reference; DeepSeek-V3 style).
+//
+// Same orientation and warp roles as the MXFP4 kernels (moe_gemm_sm100.cu): 128 weight rows on
+// the MMA's M side, the token tile of one sorted block on N, two weight tiles per pipeline stage,
+// TMA producer / MMA issuer / 8 epilogue warps / 4 scale-loader warps, bounded waits.
+// What differs:
+//   * tcgen05.mma kind::mxf8f6f4.block_scale, e4m3 x e4m3, K = 32 per instruction.  Activations
+//     are two e4m3 terms (value + residual) with E8M0 scales per 32 -- exact for bf16 inputs up to
+//     ~2^-9 of the block maximum -- applied by the tensor core; the weight operand's E8M0 scale is
+//     the constant 1.0.
+//   * a 128-block fp32 scale is not a power of two, so it cannot ride in the MMA.  One pipeline
+//     stage is exactly one 128-wide k-block: its MMAs OVERWRITE a TMEM accumulator, the epilogue
+//     warps read it, multiply by the block's weight scale (one scalar per weight tile and k-block)
+//     and add into fp32 registers -- the two-level accumulation the reference's FP8 kernel does
+//     with its FIFO + fmac (src/contrib/moe_gemm_8wave.py:386-405).  Two TMEM accumulator buffers
+//     let the next k-block's MMAs run under the promotion of the current one.
+#include <algorithm>
+#include <mutex>
+
+#include "gemm_common.cuh"
+
+namespace b200moe {
+
+namespace fp8 {
+
+constexpr int kThreads = 448;
+constexpr int kTileM = 128;
+constexpr int kTileK = 128;                      // one weight-scale block per stage
+constexpr int kATileBytes = kTileM * kTileK;     // 16 KB (one byte per element)
+constexpr int kMaxStages = 12;
+constexpr int kTmemCols = 512;
+constexpr int kSfCol0 = kAccColsLimit;           // scale columns: A (constant) 4, then 2 buffers x 8 for B
+constexpr int kSmemLimit = 232448;
+constexpr int kStagePitch = kTileM * 2 + 16;
+constexpr int kMaxChunks = 3;                    // 16-column groups per epilogue warp (token tile <= 96)
+constexpr int kTerms = 2;
+
+struct Params {
+  CUtensorMap tmW;     // weights: gate-up (K, I, 2, E) box (128,128,2,1); down (K, H, 1, E) box (128,256,1,1), bytes
+  CUtensorMap tmA;     // activations (K, max_rows, 2 terms) box (128, B, 2), bytes
+  const float* w_scale;     // gate-up [E, 2I/128, K/128]; down [E, H/128, K/128]
+  const uint8_t* asf;       // [blocks, KB, 2 chunks, 512]
+  const uint32_t* sorted_ids;
+  const int32_t* sorted_e;
+  const int32_t* num_valid;
+  int32_t* status;
+  __nv_bfloat16* h_out;
+  uint8_t* oq; uint8_t* osf;
+  __nv_bfloat16* out2;
+  int64_t max_rows;
+  int64_t oq_term_stride;
+  int B, rows, KB, MT, E, topk, T, stages, out_k, out_kb, activation;
+  float swiglu_limit;
+};
+
+struct SmemCtl {
+  uint64_t full[kMaxStages];
+  uint64_t empty[kMaxStages];
+  uint64_t tmem_full[2];
+  uint64_t tmem_empty[2];
+  uint64_t sf_full[2];
+  uint64_t sf_empty[2];
+  uint32_t tmem_base;
+  uint32_t abort_word;
+};
+
+struct StageGeom {
+  int a_bytes, b_bytes, sfb_bytes, stage_bytes;
+  uint32_t tx_bytes;
+};
+__host__ __device__ inline StageGeom stage_geom(int B) {
+  StageGeom g;
+  g.a_bytes = 2 * kATileBytes;
+  g.b_bytes = kTerms * B * kTileK;
+  g.sfb_bytes = kTerms * kSfChunk;       // one chunk per term (virtual row = term*128 + r)
+  g.stage_bytes = (g.a_bytes + g.b_bytes + g.sfb_bytes + 1023) & ~1023;
+  g.tx_bytes = (uint32_t)(g.a_bytes + g.b_bytes + g.sfb_bytes);
+  return g;
+}
+
+template <bool GATEUP>
+__global__ void __launch_bounds__(kThreads, 1) moe_grouped_gemm_fp8_kernel(const __grid_constant__ Params p) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  SmemCtl* ctl = reinterpret_cast<SmemCtl*>(smem);
+  const uint32_t stage0 = smem_u32(smem) + 1024;
+  const int B = p.B;
+  const StageGeom geo = stage_geom(B);
+  const int S = p.stages;
+  const int acc_cols = 2 * B;                  // two weight tiles x B token columns, per accumulator buffer
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  volatile uint32_t* abort_word = &ctl->abort_word;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < S; ++s) {
+      mbar_init(smem_u32(&ctl->full[s]), 1);
+      mbar_init(smem_u32(&ctl->empty[s]), 1);
+    }
+    for (int a = 0; a < 2; ++a) {
+      mbar_init(smem_u32(&ctl->tmem_full[a]), 1);
+      mbar_init(smem_u32(&ctl->tmem_empty[a]), 8);
+      mbar_init(smem_u32(&ctl->sf_full[a]), 4);
+      mbar_init(smem_u32(&ctl->sf_empty[a]), 1);
+    }
+    ctl->abort_word = 0;
+    fence_mbar_init();
+    fence_proxy_async_smem();
+  }
+  if (warp == 1) {
+    tmem_alloc(smem_u32(&ctl->tmem_base), kTmemCols);
+    tmem_relinquish();
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem_base = ctl->tmem_base;
+
+  const int64_t rows_live = min((int64_t)p.num_valid[0], p.max_rows);
+  const int n_blocks = (int)(rows_live / B);
+  const int total_work = n_blocks * p.MT;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------------ TMA producer
+    if (lane == 0) {
+      prefetch_tensormap(&p.tmW);
+      prefetch_tensormap(&p.tmA);
+      int stage = 0;
+      uint32_t phase = 0;
+      int64_t issued = 0;
+      bool ok = true;
+      for (int w = blockIdx.x; w < total_work && ok; w += gridDim.x) {
+        const int b = w / p.MT, m = w - b * p.MT;
+        int e = p.sorted_e[b];
+        if (e < 0 || e >= p.E) { p.status[2] = 1; e = 0; }
+        const int r0 = b * B;
+        const uint8_t* sfb = p.asf + (int64_t)b * p.KB * geo.sfb_bytes;
+        for (int kb = 0; kb < p.KB; ++kb) {
+          if (!mbar_wait(smem_u32(&ctl->empty[stage]), phase ^ 1, abort_word, 0x100 + stage)) { ok = false; break; }
+          const uint32_t st = stage0 + (uint32_t)stage * geo.stage_bytes;
+          const uint32_t full = smem_u32(&ctl->full[stage]);
+          mbar_expect_tx(full, geo.tx_bytes);
+          tma_load_4d(st, &p.tmW, full, kb * kTileK, m * (GATEUP ? kTileM : 2 * kTileM), 0, e);
+          tma_load_3d(st + geo.a_bytes, &p.tmA, full, kb * kTileK, r0, 0);
+          bulk_load(st + geo.a_bytes + geo.b_bytes, sfb, (uint32_t)geo.sfb_bytes, full);
+          sfb += geo.sfb_bytes;
+          ++issued;
+          if (++stage == S) { stage = 0; phase ^= 1; }
+        }
+      }
+      if (!ok || *abort_word) {
+        const int64_t first = issued > S ? issued - S : 0;
+        for (int64_t i = first; i < issued; ++i) {
+          const uint32_t bar = smem_u32(&ctl->full[i % S]);
+          const uint32_t par = (uint32_t)((i / S) & 1);
+          const uint64_t t0 = global_timer_ns();
+          while (!mbar_try_wait(bar, par) && global_timer_ns() - t0 < 200000000ull) {}
+        }
+      }
+    }
+  } else if (warp >= 10) {
+    // ------------------------------------------------------------------ scale-loader warps
+    // Weight operand: E8M0 scale 1.0 everywhere, written once.  Activation operand: the two terms'
+    // scale chunks of every stage, shared memory -> registers -> this warp's TMEM lane quadrant.
+    const uint32_t lane_base = (uint32_t)((warp & 3) * 32) << 16;
+    tmem_st_32x32b_x4(tmem_base + lane_base + kSfCol0, make_uint4(0x7F7F7F7Fu, 0x7F7F7F7Fu, 0x7F7F7F7Fu, 0x7F7F7F7Fu));
+    int stage = 0;
+    uint32_t phase = 0, sf_buf = 0, sf_phase = 0;
+    bool ok = true;
+    for (int w = blockIdx.x; w < total_work && ok; w += gridDim.x) {
+      for (int kb = 0; kb < p.KB; ++kb) {
+        if (!mbar_wait(smem_u32(&ctl->full[stage]), phase, abort_word, 0x600 + stage) ||
+            !mbar_wait(smem_u32(&ctl->sf_empty[sf_buf]), sf_phase ^ 1, abort_word, 0x700 + sf_buf)) {
+          ok = false;
+          break;
+        }
+        const uint32_t sf_s = stage0 + (uint32_t)stage * geo.stage_bytes + geo.a_bytes + geo.b_bytes + lane * 16;
+        const uint32_t sfb_t = tmem_base + lane_base + kSfCol0 + 4 + sf_buf * 8;
+        tmem_st_32x32b_x4(sfb_t, ld_shared_v4(sf_s));
+        tmem_st_32x32b_x4(sfb_t + 4, ld_shared_v4(sf_s + kSfChunk));
+        tmem_st_wait();
+        tc_fence_before_sync();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(smem_u32(&ctl->sf_full[sf_buf]));
+        if (sf_buf == 1) sf_phase ^= 1;
+        sf_buf ^= 1;
+        if (++stage == S) { stage = 0; phase ^= 1; }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------------ MMA issuer
+    uint32_t idesc[4];
+#pragma unroll
+    for (int k = 0; k < 4; ++k) idesc[k] = make_idesc_block_scaled(kFmtE4M3, kFmtE4M3, kTileM, (uint32_t)B, k, k);
+    const uint32_t term_lo = (uint32_t)(B * kTileK) >> 4;
+    const uint32_t sfa_t = tmem_base + kSfCol0;
+    int stage = 0;
+    uint32_t phase = 0, acc = 0, acc_phase = 0, sf_buf = 0, sf_phase = 0;
+    bool ok = true;
+    for (int w = blockIdx.x; w < total_work && ok; w += gridDim.x) {
+      for (int kb = 0; kb < p.KB; ++kb) {
+        // every k-block gets its own accumulator buffer: the epilogue promotes it with the
+        // block's fp32 weight scale while the next k-block is being multiplied
+        if (!mbar_wait(smem_u32(&ctl->tmem_empty[acc]), acc_phase ^ 1, abort_word, 0x200 + acc) ||
+            !mbar_wait(smem_u32(&ctl->full[stage]), phase, abort_word, 0x300 + stage) ||
+            !mbar_wait(smem_u32(&ctl->sf_full[sf_buf]), sf_phase, abort_word, 0x500 + sf_buf)) {
+          ok = false;
+          break;
+        }
+        tc_fence_after_sync();
+        if (lane == 0) {
+          const uint32_t st = stage0 + (uint32_t)stage * geo.stage_bytes;
+          const uint32_t a_lo = desc_lo_sw(st);
+          const uint32_t b_lo = desc_lo_sw(st + geo.a_bytes);
+          const uint32_t sfb_t = sfa_t + 4 + sf_buf * 8;
+          const uint32_t d0 = tmem_base + acc * acc_cols;
+#pragma unroll
+          for (int k = 0; k < 4; ++k) {
+#pragma unroll
+            for (int t = 0; t < kTerms; ++t) {
+              const uint32_t accum = (k | t) != 0;
+              umma_mxf8(d0, a_lo + 2 * k, b_lo + t * term_lo + 2 * k, idesc[k], sfa_t, sfb_t + 4 * t, accum);
+              umma_mxf8(d0 + B, a_lo + (kATileBytes >> 4) + 2 * k, b_lo + t * term_lo + 2 * k, idesc[k], sfa_t,
+                        sfb_t + 4 * t, accum);
+            }
+          }
+          tc_commit(smem_u32(&ctl->empty[stage]));
+          tc_commit(smem_u32(&ctl->sf_empty[sf_buf]));
+          tc_commit(smem_u32(&ctl->tmem_full[acc]));
+        }
+        __syncwarp();
+        if (sf_buf == 1) sf_phase ^= 1;
+        sf_buf ^= 1;
+        if (acc == 1) acc_phase ^= 1;
+        acc ^= 1;
+        if (++stage == S) { stage = 0; phase ^= 1; }
+      }
+    }
+  } else {
+    // ------------------------------------------------------------------ epilogue warps
+    const int ew = warp - 2;
+    const int quad = warp & 3;
+    const int half = ew >> 2;                  // the two warps of a quadrant take alternating 16-column groups
+    const int tid_e = ew * 32 + lane;
+    const int row_local = quad * 32 + lane;
+    const uint32_t stg = stage0 + (uint32_t)S * geo.stage_bytes;
+    const bool fused = GATEUP && p.h_out == nullptr;
+    const int row_blocks = (GATEUP ? 2 * p.rows : p.rows) / kTileM;   // weight-scale rows per expert
+    uint32_t acc = 0, acc_phase = 0;
+    bool alive = true;
+    for (int w = blockIdx.x; w < total_work && alive; w += gridDim.x) {
+      const int b = w / p.MT, m = w - b * p.MT;
+      const int r0 = b * B;
+      int e = p.sorted_e[b];
+      if (e < 0 || e >= p.E) e = 0;
+      const int j = (GATEUP ? m * kTileM : m * 2 * kTileM) + row_local;
+      const int rb0 = GATEUP ? m : 2 * m;
+      const int rb1 = GATEUP ? p.rows / kTileM + m : min(2 * m + 1, row_blocks - 1);
+      const float* s0 = p.w_scale + ((int64_t)e * row_blocks + rb0) * p.KB;
+      const float* s1 = p.w_scale + ((int64_t)e * row_blocks + rb1) * p.KB;
+      int nvalid = 0;
+      for (int q = 0; q < B; q += 32) {
+        const uint32_t id = (q + lane < B) ? p.sorted_ids[r0 + q + lane] : 0xFFFFFFFFu;
+        nvalid += __popc(__ballot_sync(0xffffffffu, (int)(id >> 24) < p.topk && (int)(id & 0xFFFFFFu) < p.T));
+      }
+      float ag[kMaxChunks * 16], au[kMaxChunks * 16];
+#pragma unroll
+      for (int i = 0; i < kMaxChunks * 16; ++i) { ag[i] = 0.f; au[i] = 0.f; }
+
+      for (int kb = 0; kb < p.KB; ++kb) {
+        const bool ok = mbar_wait(smem_u32(&ctl->tmem_full[acc]), acc_phase, abort_word, 0x400 + acc);
+        if (!epi_all(ok)) { alive = false; break; }
+        tc_fence_after_sync();
+        const float sc0 = s0[kb], sc1 = s1[kb];
+        const uint32_t t0 = tmem_base + ((uint32_t)(quad * 32) << 16) + acc * acc_cols;
+#pragma unroll
+        for (int ci = 0; ci < kMaxChunks; ++ci) {
+          const int c0 = (2 * ci + half) * 16;
+          if (c0 < nvalid) {
+            uint32_t g[16], u[16];
+            tmem_ld_32x32b_x16(t0 + c0, g);
+            tmem_ld_32x32b_x16(t0 + B + c0, u);
+            tmem_ld_wait();
+#pragma unroll
+            for (int n = 0; n < 16; ++n) {
+              ag[ci * 16 + n] = fmaf(sc0, __uint_as_float(g[n]), ag[ci * 16 + n]);
+              au[ci * 16 + n] = fmaf(sc1, __uint_as_float(u[n]), au[ci * 16 + n]);
+            }
+          }
+        }
+        tc_fence_before_sync();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(smem_u32(&ctl->tmem_empty[acc]));
+        if (acc == 1) acc_phase ^= 1;
+        acc ^= 1;
+      }
+      if (!alive) break;
+
+      // ---- tile finished: activation / stores from the register accumulators
+      const bool j_ok = j < p.rows;
+#pragma unroll
+      for (int ci = 0; ci < kMaxChunks; ++ci) {
+        const int c0 = (2 * ci + half) * 16;
+        if (c0 < nvalid) {
+          if (GATEUP) {
+            if (!fused) {
+              const uint32_t my_id = p.sorted_ids[min(r0 + c0 + lane, r0 + B - 1)];
+#pragma unroll
+              for (int n = 0; n < 16; ++n) {
+                const uint32_t id = __shfl_sync(0xffffffffu, my_id, n);
+                if (c0 + n < nvalid) {
+                  const int tok = (int)(id & 0xFFFFFFu), kk = (int)(id >> 24);
+                  const float v = gateup_act(ag[ci * 16 + n], au[ci * 16 + n], p.activation, p.swiglu_limit);
+                  if (j_ok) p.h_out[((int64_t)tok * p.topk + kk) * p.rows + j] = __float2bfloat16_rn(v);
+                }
+              }
+            } else {
+#pragma unroll
+              for (int n = 0; n < 16; ++n) {
+                if (c0 + n < nvalid) {
+                  float v = gateup_act(ag[ci * 16 + n], au[ci * 16 + n], p.activation, p.swiglu_limit);
+                  if (!j_ok) v = 0.f;
+                  st_shared_u16(stg + (uint32_t)(c0 + n) * kStagePitch + row_local * 2,
+                                __bfloat16_as_ushort(__float2bfloat16_rn(v)));
+                }
+              }
+            }
+          } else {
+            const bool j2_ok = j + kTileM < p.rows;
+#pragma unroll
+            for (int n = 0; n < 16; ++n) {
+              if (c0 + n < nvalid) {
+                __nv_bfloat16* row = p.out2 + ((int64_t)r0 + c0 + n) * p.rows + j;
+                if (j_ok) row[0] = __float2bfloat16_rn(ag[ci * 16 + n]);
+                if (j2_ok) row[kTileM] = __float2bfloat16_rn(au[ci * 16 + n]);
+              }
+            }
+          }
+        }
+      }
+      if (fused) {
+        epi_sync();
+        // h tile -> two e4m3 terms with E8M0 scales per 32 features, sorted-row order
+        for (int unit = tid_e; unit < nvalid * 4; unit += 256) {
+          const int n = unit >> 2, q = unit & 3;
+          float x[32];
+#pragma unroll
+          for (int v4 = 0; v4 < 4; ++v4) {
+            const uint4 raw = ld_shared_v4(stg + (uint32_t)n * kStagePitch + q * 64 + v4 * 16);
+            const __nv_bfloat162* b2 = reinterpret_cast<const __nv_bfloat162*>(&raw);
+#pragma unroll
+            for (int t = 0; t < 4; ++t) {
+              const float2 f = __bfloat1622float2(b2[t]);
+              x[v4 * 8 + t * 2] = f.x;
+              x[v4 * 8 + t * 2 + 1] = f.y;
+            }
+          }
+          const int64_t r = (int64_t)r0 + n;
+#pragma unroll
+          for (int t = 0; t < kTerms; ++t) {
+            uint4 q0, q1;
+            const int ex = quant_block32_e4m3(x, q0, q1);
+            uint4* dst = reinterpret_cast<uint4*>(p.oq + t * p.oq_term_stride + r * p.out_k + m * kTileM + q * 32);
+            dst[0] = q0;
+            dst[1] = q1;
+            p.osf[act_sf_index(b, m, p.out_kb, B, kTerms, 128, t, n, q)] = (uint8_t)ex;
+          }
+        }
+        epi_sync();     // the staging tile may be overwritten by the next tile
+      }
+    }
+  }
+
+  __syncwarp();
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  if (threadIdx.x == 0 && ctl->abort_word != 0) {
+    p.status[0] = (int32_t)ctl->abort_word;
+    p.status[1] = (int32_t)blockIdx.x;
+  }
+  if (warp == 1) tmem_dealloc(tmem_base, kTmemCols);
+}
+
+}  // namespace fp8
+
+int launch_grouped_gemm_fp8(const GemmArgs& a, cudaStream_t st) {
+  using namespace fp8;
+  B200_CHECK_ARG(a.N >= 16 && a.N <= 96 && a.N % 16 == 0, "fp8 grouped gemm: token tile %d is not a multiple of 16 in [16,96]",
+                 a.N);
+  B200_CHECK_ARG(a.Kd % 128 == 0 && a.rows % 128 == 0 && a.E > 0, "fp8 grouped gemm: K and rows must be multiples of 128");
+  B200_CHECK_ARG(a.max_rows % a.N == 0, "fp8 grouped gemm: max_rows %% B != 0");
+  B200_CHECK_ARG(((uintptr_t)a.w_data & 15) == 0 && ((uintptr_t)a.a_q & 15) == 0 && ((uintptr_t)a.w_scale & 3) == 0,
+                 "fp8 grouped gemm: operand tensors must be 16-byte aligned");
+  Params p;
+  memset(&p, 0, sizeof(p));
+  p.B = a.N; p.rows = a.rows; p.KB = a.Kd / kTileK;
+  p.MT = a.gateup ? a.rows / kTileM : (a.rows + 2 * kTileM - 1) / (2 * kTileM);
+  p.E = a.E; p.topk = a.topk; p.T = a.T; p.activation = a.activation; p.swiglu_limit = a.swiglu_limit;
+  p.max_rows = a.max_rows;
+  p.w_scale = (const float*)a.w_scale; p.asf = (const uint8_t*)a.asf;
+  p.sorted_ids = a.sorted_ids; p.sorted_e = a.sorted_e; p.num_valid = a.num_valid; p.status = a.status;
+  p.h_out = (__nv_bfloat16*)a.h_out; p.oq = (uint8_t*)a.oq; p.osf = (uint8_t*)a.osf;
+  p.out_k = a.out_kp; p.out_kb = a.out_kp / 128; p.oq_term_stride = a.max_rows * (int64_t)a.out_kp;
+  p.out2 = (__nv_bfloat16*)a.out2;
+  if (a.gateup && a.h_out == nullptr)
+    B200_CHECK_ARG(a.out_kp == a.rows && a.oq && a.osf, "fp8 gate-up: fused output buffers missing");
+  {
+    const cuuint64_t parts = a.gateup ? 2 : 1, pitch = (cuuint64_t)a.Kd;
+    cuuint64_t dims[4] = {(cuuint64_t)a.Kd, (cuuint64_t)a.rows, parts, (cuuint64_t)a.E};
+    cuuint64_t strides[3] = {pitch, pitch * (cuuint64_t)a.rows, pitch * (cuuint64_t)a.rows * parts};
+    cuuint32_t box[4] = {kTileK, a.gateup ? (cuuint32_t)kTileM : 2u * kTileM, a.gateup ? 2u : 1u, 1};
+    int rc = encode_map_sw(&p.tmW, CU_TENSOR_MAP_DATA_TYPE_UINT8, 4, a.w_data, dims, strides, box,
+                           CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, "fp8 weights");
+    if (rc) return rc;
+  }
+  {
+    cuuint64_t dims[3] = {(cuuint64_t)a.Kd, (cuuint64_t)a.max_rows, (cuuint64_t)kTerms};
+    cuuint64_t strides[2] = {(cuuint64_t)a.Kd, (cuuint64_t)a.Kd * (cuuint64_t)a.max_rows};
+    cuuint32_t box[3] = {kTileK, (cuuint32_t)a.N, (cuuint32_t)kTerms};
+    int rc = encode_map_sw(&p.tmA, CU_TENSOR_MAP_DATA_TYPE_UINT8, 3, a.a_q, dims, strides, box,
+                           CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, "fp8 activations");
+    if (rc) return rc;
+  }
+  const StageGeom geo = stage_geom(a.N);
+  const int staging = (a.gateup && a.h_out == nullptr) ? a.N * kStagePitch : 0;
+  int stages = std::min((kSmemLimit - 2048 - staging) / geo.stage_bytes, kMaxStages);
+  B200_CHECK_ARG(stages >= 2, "fp8 grouped gemm: tile does not fit shared memory");
+  p.stages = stages;
+  const size_t smem = 2048 + (size_t)stages * geo.stage_bytes + staging;
+  const int64_t max_work = (a.max_rows / a.N) * p.MT;
+  const int grid = (int)std::min<int64_t>(device_sm_count(), std::max<int64_t>(max_work, 1));
+  static bool attr[2][64] = {};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  bool& done = attr[a.gateup ? 1 : 0][dev & 63];
+  if (a.gateup) {
+    if (!done)
+      B200_CHECK_CUDA(cudaFuncSetAttribute(moe_grouped_gemm_fp8_kernel<true>,
+                                           cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemLimit));
+    done = true;
+    moe_grouped_gemm_fp8_kernel<true><<<grid, kThreads, smem, st>>>(p);
+  } else {
+    if (!done)
+      B200_CHECK_CUDA(cudaFuncSetAttribute(moe_grouped_gemm_fp8_kernel<false>,
+                                           cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemLimit));
+    done = true;
+    moe_grouped_gemm_fp8_kernel<false><<<grid, kThreads, smem, st>>>(p);
+  }
+  B200_CHECK_CUDA(cudaGetLastError());
+  return 0;
+}
+
+}  // namespace b200moe

@@ -96,17 +96,38 @@ class PreparedWeights:
         self.device = w1.device
 
 
+class PreparedWeightsFP8:
+    """FP8 (e4m3) expert weights with one fp32 scale per 128x128 block
+    (tests/contrib/moe/test_moe.py:201-260): consumed entirely in place."""
+
+    def __init__(self, w1, w1_scale, w2, w2_scale):
+        if not w1.is_cuda:
+            raise ValueError("weights must be CUDA tensors")
+        E, N1, H = w1.shape
+        self.E, self.I, self.H = E, N1 // 2, H
+        if tuple(w2.shape) != (E, H, self.I):
+            raise ValueError(f"w2 shape {tuple(w2.shape)} does not match w1 {tuple(w1.shape)}")
+        if H % 128 or self.I % 128:
+            raise ValueError("per_128x128 weights need H and I to be multiples of 128")
+        if w1_scale.numel() != E * (N1 // 128) * (H // 128) or w2_scale.numel() != E * (H // 128) * (self.I // 128):
+            raise ValueError("scale tensors must hold one fp32 scale per 128x128 block")
+        self.w1_data, self.w2_data = w1.contiguous().view(torch.uint8), w2.contiguous().view(torch.uint8)
+        self.w1_scale, self.w2_scale = w1_scale.float().contiguous(), w2_scale.float().contiguous()
+        self.device = w1.device
+
+
 _prepared_cache: dict = {}
 _workspace_cache: dict = {}
 
 
-def prepare_weights(w1, w1_scale, w2, w2_scale) -> PreparedWeights:
+def prepare_weights(w1, w1_scale, w2, w2_scale, weight_format=_lib.W_MXFP4):
     """Cached by the identity of the four tensors (weights are static across calls)."""
-    key = (w1.data_ptr(), w1_scale.data_ptr(), w2.data_ptr(), w2_scale.data_ptr(), tuple(w1.shape))
+    key = (w1.data_ptr(), w1_scale.data_ptr(), w2.data_ptr(), w2_scale.data_ptr(), tuple(w1.shape), weight_format)
     hit = _prepared_cache.get(key)
     if hit is not None and hit[0]() is w1:
         return hit[1]
-    pw = PreparedWeights(w1, w1_scale, w2, w2_scale)
+    cls = PreparedWeightsFP8 if weight_format == _lib.W_FP8_128 else PreparedWeights
+    pw = cls(w1, w1_scale, w2, w2_scale)
     _prepared_cache[key] = (weakref.ref(w1), pw)
     return pw
 
@@ -114,10 +135,12 @@ def prepare_weights(w1, w1_scale, w2, w2_scale) -> PreparedWeights:
 class MoEPlan:
     """Shape, workspace layout and workspace tensor of one (T, K, E, H, I, B) problem."""
 
-    def __init__(self, T, K, E, E_route, H, I, B, activation, swiglu_limit, device, act_terms=0):
-        self.shape = _lib.Shape(T=T, K=K, E=E, E_route=E_route, H=H, I=I, B=B, weight_format=_lib.W_MXFP4,
+    def __init__(self, T, K, E, E_route, H, I, B, activation, swiglu_limit, device, act_terms=0,
+                 weight_format=_lib.W_MXFP4):
+        self.shape = _lib.Shape(T=T, K=K, E=E, E_route=E_route, H=H, I=I, B=B, weight_format=weight_format,
                                 activation=activation, swiglu_limit=float(swiglu_limit), act_terms=act_terms)
         self.terms = act_terms or 3
+        self.fp8 = weight_format == _lib.W_FP8_128
         self.ws = _lib.workspace_layout(self.shape)
         self.buf = torch.empty(self.ws.total_bytes + 1024, dtype=torch.uint8, device=device)
         off = (-self.buf.data_ptr()) % 1024
@@ -155,6 +178,11 @@ class MoEPlan:
         s, ws = self.shape, self.ws
         ids_o, _, _, nv_o, _ = self.sort_outputs()
         base = self.base
+        if self.fp8:
+            _lib.check(_lib.lib().b200moe_quant_rows_e4m3(
+                _ptr(x), 0, _ptr(ids_o), _ptr(nv_o), s.T, s.K, s.H, s.B, ws.max_rows,
+                ctypes.c_void_p(base + ws.off_xq), ctypes.c_void_p(base + ws.off_xsf), _stream()), "quant_rows_e4m3")
+            return
         _lib.check(_lib.lib().b200moe_quant_rows(
             _ptr(x), 0, _ptr(ids_o), _ptr(nv_o), s.T, s.K, s.H, s.B, self.terms, ws.max_rows,
             ctypes.c_void_p(base + ws.off_xq), ctypes.c_void_p(base + ws.off_xsf), _stream()),
@@ -165,6 +193,11 @@ class MoEPlan:
         s, ws = self.shape, self.ws
         ids_o, _, _, nv_o, _ = self.sort_outputs()
         base = self.base
+        if self.fp8:
+            _lib.check(_lib.lib().b200moe_quant_rows_e4m3(
+                _ptr(h), 1, _ptr(ids_o), _ptr(nv_o), s.T, s.K, s.I, s.B, ws.max_rows,
+                ctypes.c_void_p(base + ws.off_hq), ctypes.c_void_p(base + ws.off_hsf), _stream()), "quant_rows_e4m3")
+            return
         _lib.check(_lib.lib().b200moe_quant_rows(
             _ptr(h), 1, _ptr(ids_o), _ptr(nv_o), s.T, s.K, s.I, s.B, self.terms, ws.max_rows,
             ctypes.c_void_p(base + ws.off_hq), ctypes.c_void_p(base + ws.off_hsf), _stream()),
@@ -188,13 +221,14 @@ class MoEPlan:
                                     f"bad expert id flag {st[2]}")
 
 
-def get_plan(T, K, E, E_route, H, I, B, activation, swiglu_limit, device, act_terms=0) -> MoEPlan:
-    key = (T, K, E, E_route, H, I, B, activation, float(swiglu_limit), str(device), act_terms)
+def get_plan(T, K, E, E_route, H, I, B, activation, swiglu_limit, device, act_terms=0,
+             weight_format=_lib.W_MXFP4) -> MoEPlan:
+    key = (T, K, E, E_route, H, I, B, activation, float(swiglu_limit), str(device), act_terms, weight_format)
     plan = _workspace_cache.get(key)
     if plan is None:
         if len(_workspace_cache) > 16:
             _workspace_cache.clear()
-        plan = MoEPlan(T, K, E, E_route, H, I, B, activation, swiglu_limit, device, act_terms)
+        plan = MoEPlan(T, K, E, E_route, H, I, B, activation, swiglu_limit, device, act_terms, weight_format)
         _workspace_cache[key] = plan
     return plan
 
@@ -228,8 +262,9 @@ def fused_moe(hidden_states, w1, w2, topk_weight, topk_ids, expert_mask=None,
         raise RuntimeError("fused_moe runs on a CUDA device only (sm_100a); there is no CPU path")
     if hidden_states.dtype != torch.bfloat16:
         raise TypeError("hidden_states must be bfloat16")
-    if int(quant_type) != QuantType.per_1x32:
-        raise NotImplementedError(f"quant_type={quant_type!r}: this build implements per_1x32 (MXFP4) weights")
+    if int(quant_type) not in (QuantType.per_1x32, QuantType.per_128x128):
+        raise NotImplementedError(f"quant_type={quant_type!r}: per_1x32 (MXFP4) and per_128x128 (FP8) are implemented")
+    fmt = _lib.W_MXFP4 if int(quant_type) == QuantType.per_1x32 else _lib.W_FP8_128
     if int(activation) not in (ActivationType.Silu, ActivationType.Swiglu):
         raise NotImplementedError(f"activation={activation!r}: Silu and Swiglu are implemented")
     if doweight_stage1 or bias1 is not None or bias2 is not None or a1_scale is not None or a2_scale is not None:
@@ -237,18 +272,18 @@ def fused_moe(hidden_states, w1, w2, topk_weight, topk_ids, expert_mask=None,
     if num_local_tokens is not None or hidden_pad or intermediate_pad:
         raise NotImplementedError("num_local_tokens / padding arguments are not implemented")
     if w1_scale is None or w2_scale is None:
-        raise ValueError("per_1x32 needs w1_scale and w2_scale")
+        raise ValueError("quantised weights need w1_scale and w2_scale")
     if dtype not in (None, torch.bfloat16):
         raise NotImplementedError("output dtype must be bfloat16")
     T, H = hidden_states.shape
     K = topk_ids.shape[1]
-    pw = prepare_weights(w1, w1_scale, w2, w2_scale)
+    pw = prepare_weights(w1, w1_scale, w2, w2_scale, fmt)
     if pw.H != H:
         raise ValueError(f"hidden size {H} does not match weights ({pw.H})")
     E_route = pw.E if expert_mask is None else int(expert_mask.numel())
     B = int(block_size_M) if block_size_M else pick_block(T, K, pw.E)
     act = _lib.ACT_SILU if int(activation) == ActivationType.Silu else _lib.ACT_SWIGLU
-    plan = get_plan(T, K, pw.E, E_route, H, pw.I, B, act, swiglu_limit, hidden_states.device, act_terms)
+    plan = get_plan(T, K, pw.E, E_route, H, pw.I, B, act, swiglu_limit, hidden_states.device, act_terms, fmt)
     ids = topk_ids if topk_ids.dtype == torch.int32 else topk_ids.to(torch.int32)
     tw = topk_weight if topk_weight.dtype == torch.float32 else topk_weight.float()
     mask = None if expert_mask is None else expert_mask.to(torch.int32).contiguous()

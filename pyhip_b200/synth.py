@@ -104,6 +104,22 @@ def make_weights_fp8(E: int, H: int, I: int, seed: int = 0, experts=None):
     return w1_q, w1_s, w2_q, w2_s
 
 
+def make_weights_fp8_fast(E: int, H: int, I: int, seed: int = 0, device="cpu", distinct: int = 4):
+    """Benchmark-sized FP8 weights: ``distinct`` experts drawn and quantised as in make_weights_fp8,
+    the others repeat them with rows rolled by the expert index."""
+    base = make_weights_fp8(distinct, H, I, seed)
+    outs = []
+    for t in base:
+        t = t.to(device)
+        if t.dtype == torch.float8_e4m3fn:      # roll whole 128-row blocks so data and scales stay aligned
+            reps = [torch.roll(t[e % distinct].view(torch.uint8), shifts=128 * (e // distinct), dims=0) for e in range(E)]
+            outs.append(torch.stack(reps).view(torch.float8_e4m3fn))
+        else:
+            reps = [torch.roll(t[e % distinct], shifts=e // distinct, dims=0) for e in range(E)]
+            outs.append(torch.stack(reps))
+    return tuple(outs)
+
+
 def algorithmic_flops(T: int, K: int, H: int, I: int) -> float:
     """6*H*I*T*K (tests/contrib/moe/test_moe.py:274)."""
     return 6.0 * H * I * T * K

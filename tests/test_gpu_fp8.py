@@ -1,0 +1,115 @@
+"""GPU tier: FP8 (e4m3) weights with fp32 scales per 128x128 block -- parity of the CUDA path with
+the torch dequantise-then-matmul oracle (bf16 activations), tolerance max-abs <= 2e-2 and
+cosine >= 0.9995 as for the MXFP4 path."""
+import pathlib
+
+import numpy as np
+import pytest
+import torch
+
+from oracle import moe_oracle as orc
+from pyhip_b200 import QuantType, _lib, fused_moe, synth
+from pyhip_b200.fused_moe import get_plan, prepare_weights
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda:0"
+GOLD = pathlib.Path(__file__).parent / "golden"
+MAX_ABS, COS = 2e-2, 0.9995
+
+
+def _bf16(a):
+    return torch.from_numpy(a.view(np.int16).copy()).view(torch.bfloat16)
+
+
+def _run(x, tw, ids, w, **kw):
+    w1_q, w1_s, w2_q, w2_s = (t.to(DEV) for t in w)
+    y = fused_moe(x.to(DEV), w1_q, w2_q, tw.to(DEV), ids.to(DEV), quant_type=QuantType.per_128x128,
+                  w1_scale=w1_s, w2_scale=w2_s, **kw)
+    torch.cuda.synchronize()
+    return y.cpu()
+
+
+def _close(y, ref, what):
+    assert torch.isfinite(y.float()).all(), what
+    cos, mx = orc.cosine(y, ref), orc.max_abs(y, ref)
+    # bf16 spacing exceeds 2e-2 above magnitude 4: the absolute bound scales with the output range there
+    bound = MAX_ABS * max(1.0, float(ref.float().abs().max()))
+    assert cos >= COS and mx <= bound, f"{what}: cosine {cos:.6f} max_abs {mx:.3e} (bound {bound:.3e})"
+
+
+def test_e4m3_rows_match_oracle_bit_for_bit():
+    T, H, I, E, K, B = 40, 256, 128, 8, 2, 32
+    x = synth.make_hidden(T, H, 4)
+    tw, ids = synth.make_routing(T, E, K, seed=4)
+    plan = get_plan(T, K, E, E, H, I, B, 0, 7.0, torch.device(DEV), weight_format=_lib.W_FP8_128)
+    s_ids, _, _, nv, _ = plan.sort(ids.to(DEV), tw.to(DEV))
+    plan.quant_input(x.to(DEV))
+    torch.cuda.synchronize()
+    n, L = int(nv[0]), plan.ws.max_rows
+    q = plan.region("xq", 2 * L * H).cpu().numpy().reshape(2, L, H)[:, :n]
+    sf = plan.region("xsf", L // B * (H // 128) * 2 * 512).cpu().numpy().reshape(-1, H // 128, 2, 32, 4, 4)
+    sf = sf.transpose(0, 2, 4, 3, 1, 5).reshape(sf.shape[0], 2, 128, H // 32)[:, :, :B]    # [blk, term, r, kb*4+j]
+    sf = sf.transpose(1, 0, 2, 3).reshape(2, -1, H // 32)[:, :n]
+    sid = s_ids.cpu().numpy().view(np.uint32)[:n]
+    tok, kk = sid & 0xFFFFFF, sid >> 24
+    eq, ee = orc.e4m3_terms_quant(x, 2)
+    eq = eq.float().numpy()
+    got = torch.from_numpy(q.copy()).view(torch.float8_e4m3fn).float().numpy()
+    for r in range(n):
+        if kk[r] < K:
+            assert np.array_equal(got[:, r], eq[:, tok[r]]), r
+            assert np.array_equal(sf[:, r], ee[:, tok[r]]), r
+
+
+@pytest.mark.parametrize("T,H,I,E,K,B", [(32, 256, 128, 4, 2, 32), (150, 256, 384, 4, 2, 64), (300, 384, 128, 4, 2, 96),
+                                         (7, 512, 256, 8, 2, 16)])
+def test_stage_chain_matches_layer_oracle(T, H, I, E, K, B):
+    x = synth.make_hidden(T, H, T)
+    tw, ids = synth.make_routing(T, E, K, seed=T)
+    w = synth.make_weights_fp8(E, H, I, seed=T)
+    pw = prepare_weights(*(t.to(DEV) for t in w), weight_format=_lib.W_FP8_128)
+    plan = get_plan(T, K, E, E, H, I, B, 0, 7.0, torch.device(DEV), weight_format=_lib.W_FP8_128)
+    plan.sort(ids.to(DEV), tw.to(DEV))
+    plan.quant_input(x.to(DEV))
+    h = torch.zeros(T, K, I, dtype=torch.bfloat16, device=DEV)
+    plan.gateup(pw, h)
+    torch.cuda.synchronize()
+    plan.check_status()
+    srt = orc.moe_sorting_oracle(ids, tw, E, B)
+    w1 = orc.dequant_fp8_128x128(w[0], w[1])
+    ref_h = orc.moe_gemm_oracle(K, B, srt[0], srt[2], srt[1], srt[3], x, w1, True)
+    _close(h.cpu(), ref_h, "fp8 gate-up")
+    plan.quant_hidden(h)
+    plan.down(pw)
+    y = torch.empty(T, H, dtype=torch.bfloat16, device=DEV)
+    plan.combine(tw.to(DEV), y)
+    torch.cuda.synchronize()
+    plan.check_status()
+    _close(y.cpu(), orc.torch_moe_oracle_fp8(x, *w, tw, ids), "fp8 stage chain")
+
+
+def test_layer_matches_reference_golden_vectors():
+    g = np.load(GOLD / "layer_fp8_small.npz")
+    x = _bf16(g["x"])
+    tw, ids = torch.from_numpy(g["topk_weight"]), torch.from_numpy(g["topk_ids"])
+    w = (torch.from_numpy(g["w1_q"]).view(torch.float8_e4m3fn), torch.from_numpy(g["w1_s"]),
+         torch.from_numpy(g["w2_q"]).view(torch.float8_e4m3fn), torch.from_numpy(g["w2_s"]))
+    _close(_run(x, tw, ids, w), _bf16(g["y"]), "fp8 golden")
+
+
+@pytest.mark.parametrize("T", [1, 33, 257])
+def test_fused_layer_ragged_and_skewed(T):
+    H, I, E, K = 384, 256, 16, 4
+    x = synth.make_hidden(T, H, T)
+    tw, ids = synth.make_routing(T, E, K, "zipf", seed=T)
+    w = synth.make_weights_fp8(E, H, I, seed=3)
+    _close(_run(x, tw, ids, w), orc.torch_moe_oracle_fp8(x, *w, tw, ids), f"fp8 T={T}")
+
+
+def test_deepseek_shaped_slice():
+    """H=7168, I=2048 (the config-3 shape) with a handful of experts: sigmoid routing, top-8."""
+    T, H, I, E, K = 16, 7168, 2048, 8, 8
+    x = synth.make_hidden(T, H, 1)
+    tw, ids = synth.make_routing(T, E, K, "sigmoid", seed=1)
+    w = synth.make_weights_fp8(E, H, I, seed=1)
+    _close(_run(x, tw, ids, w), orc.torch_moe_oracle_fp8(x, *w, tw, ids), "dsv3 slice")
