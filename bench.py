@@ -36,7 +36,9 @@ def parse():
     ap.add_argument("--steps", type=int, default=1000)
     ap.add_argument("--warmup", type=int, default=10)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
-    ap.add_argument("--tokens", type=int, default=64, help="tokens per GPU per step")
+    ap.add_argument("--tokens", type=int, default=0, help="tokens per GPU per step (0 = the workload's own)")
+    ap.add_argument("--workload", default="gptoss_decode", choices=["gptoss_decode", "gptoss_prefill", "dsv3_ep"],
+                    help="gptoss_*: MXFP4 weights (BASELINE configs 1, 2); dsv3_ep: FP8 128x128 weights (config 3)")
     ap.add_argument("--sweep", action="store_true", help="also time T in {1,8,32,64,256,8192} (extra keys)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     return ap.parse_args()
@@ -123,7 +125,7 @@ def run_reference(args):
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
-    T = args.tokens
+    T = args.tokens or shape.T
     rates, info = [], None
     for _ in range(max(1, min(args.warmup, 1))):
         cpu_oracle_rate(T, shape, 2)
@@ -187,19 +189,26 @@ def run_b200(args):
         dist_mod.init_process_group("nccl", device_id=dev)
         dist = dist_mod
 
-    shape = synth.CONFIGS["gptoss_decode"]
-    T, H, I, E, K = args.tokens, shape.H, shape.I, shape.E, shape.K
+    shape = synth.CONFIGS[args.workload]
+    T, H, I, E, K = (args.tokens or shape.T), shape.H, shape.I, shape.E, shape.K
     launches_per_step = 5
+    fp8 = shape.wq == "fp8_128"
+    qt = QuantType.per_128x128 if fp8 else QuantType.per_1x32
+    fmt = 1 if fp8 else 0
+    make_w = synth.make_weights_fp8_fast if fp8 else synth.make_weights_mxfp4_fast
+    wbytes = (1.0 + 4.0 / 16384) if fp8 else (0.5 + 1.0 / 32)
+    dtype_s = ("fp8-e4m3 128x128-block weights x 2-term e4m3 activations (kind::mxf8f6f4), f32 accumulate" if fp8 else
+               "mxfp4 weights x 3-term fp4 activations (kind::mxf4), f32 accumulate")
 
     if world == 1:
-        w = synth.make_weights_mxfp4_fast(E, H, I, seed=0, device=dev)
-        pw = prepare_weights(*w)
+        w = make_w(E, H, I, seed=0, device=dev)
+        pw = prepare_weights(*w, weight_format=fmt)
         x = synth.make_hidden(T, H, 0)
         tw, ids = synth.make_routing(T, E, K, shape.routing, 0)
         hit = len(set(ids.flatten().tolist()))
         xd, twd, idsd = x.to(dev), tw.to(dev), ids.to(dev)
         B = pick_block(T, K, E)
-        plan = get_plan(T, K, E, E, H, I, B, 0, 7.0, dev)
+        plan = get_plan(T, K, E, E, H, I, B, 0, 7.0, dev, weight_format=fmt)
         y = torch.empty(T, H, dtype=torch.bfloat16, device=dev)
 
         def step():
@@ -219,7 +228,7 @@ def run_b200(args):
             xg = xh.to(dev, non_blocking=True)
             tg = twh.to(dev, non_blocking=True)
             ig = idsh.to(dev, non_blocking=True)
-            out = fused_moe(xg, w[0], w[2], tg, ig, quant_type=QuantType.per_1x32, w1_scale=w[1], w2_scale=w[3])
+            out = fused_moe(xg, w[0], w[2], tg, ig, quant_type=qt, w1_scale=w[1], w2_scale=w[3])
             yh.copy_(out, non_blocking=True)
 
         ms_e2e = time_steps(step_e2e, args.steps, args.warmup)
@@ -233,20 +242,20 @@ def run_b200(args):
         ms_gu = time_steps(lambda: plan.gateup(pw, None), args.steps, args.warmup)
         ms_dn = time_steps(lambda: plan.down(pw), args.steps, args.warmup)
         per_launch_s = ms_gu * 1e-3 / args.steps
-        gu_bytes = hit * 2.0 * H * I * (0.5 + 1.0 / 32) + T * H * 2.0
+        gu_bytes = hit * 2.0 * H * I * wbytes + T * H * 2.0
         peak, peak_kind = measured_peaks()
         achieved = gu_bytes / per_launch_s / 1e9
         roofline = {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
                     "traffic": None, "kernel": "moe_grouped_gemm_kernel<gate-up>", "peak_kind": peak_kind,
                     "us_per_launch": per_launch_s * 1e6, "down_us_per_launch": ms_dn * 1e3 / args.steps,
                     "algorithmic_bytes": gu_bytes}
-        layer_bytes = synth.algorithmic_bytes(T, H, I, hit, "mxfp4")
+        layer_bytes = synth.algorithmic_bytes(T, H, I, hit, shape.wq)
         extra = {"layer_gbs": layer_bytes / (ms * 1e-3 / args.steps) / 1e9,
                  "layer_frac_of_hbm_peak": layer_bytes / (ms * 1e-3 / args.steps) / 1e9 / peak,
                  "layer_tflops": synth.algorithmic_flops(T, K, H, I) / (ms * 1e-3 / args.steps) / 1e12,
                  "experts_hit": hit}
         sweep = None
-        if args.sweep:
+        if args.sweep and not fp8:
             sweep = []
             for Ts in (1, 8, 32, 64, 256, 8192):
                 xs = synth.make_hidden(Ts, H, 0).to(dev)
@@ -261,18 +270,18 @@ def run_b200(args):
                               "gbs": synth.algorithmic_bytes(Ts, H, I, u) / (us * 1e-6) / 1e9,
                               "tflops": synth.algorithmic_flops(Ts, K, H, I) / (us * 1e-6) / 1e12})
         cpu = None
-        if not args.no_cpu_baseline:
+        if not args.no_cpu_baseline and not fp8:
             r, info = cpu_oracle_rate(T, shape, 4)
             cpu = {"value": r, "unit": UNIT, "cores": os.cpu_count(), "kind": "port",
                    "sample": f"torch dequantise-then-matmul oracle on {info['experts_sampled']} of "
                              f"{info['experts_hit']} hit experts ({info['sample_seconds']} s), scaled to all hit experts"}
         line = {"metric": METRIC, "value": value, "unit": UNIT, "n_gpus": 1, "steps": args.steps,
                 "warmup": args.warmup, "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "weak",
-                "vs_baseline": None, "dtype": "mxfp4 weights x 3-term fp4 activations (kind::mxf4), f32 accumulate",
+                "vs_baseline": None, "dtype": dtype_s,
                 "data": "synthetic",
-                "config": {"workload": f"gptoss_decode H{H} I{I} E{E} top{K} T{T} mxfp4", "block": B,
+                "config": {"workload": f"{args.workload} H{H} I{I} E{E} top{K} T{T} {shape.wq}", "block": B,
                            "l2": "inputs larger than L2: %.2f GB of expert weights streamed per step" %
-                                 (hit * 3.0 * H * I * (0.5 + 1 / 32) / 1e9)},
+                                 (hit * 3.0 * H * I * wbytes / 1e9)},
                 "clocks": clocks, "e2e": e2e, "gpu_launches": launches_per_step * args.steps,
                 "roofline": roofline, "cpu_baseline": cpu, "layer": extra}
         if sweep:
@@ -284,8 +293,8 @@ def run_b200(args):
     from pyhip_b200 import ep
     E_local = E // world
     experts = list(range(rank * E_local, (rank + 1) * E_local))
-    w_full = synth.make_weights_mxfp4_fast(E_local, H, I, seed=rank, device=dev)
-    layer = ep.ExpertParallelMoE(w_full[0], w_full[1], w_full[2], w_full[3], E, rank, world)
+    w_full = make_w(E_local, H, I, seed=rank, device=dev)
+    layer = ep.ExpertParallelMoE(w_full[0], w_full[1], w_full[2], w_full[3], E, rank, world, quant_type=qt)
     x = synth.make_hidden(T, H, rank)
     tw, ids = synth.make_routing(T, E, K, shape.routing, rank)
     xd, twd, idsd = x.to(dev), tw.to(dev), ids.to(dev)
@@ -309,9 +318,9 @@ def run_b200(args):
     if rank == 0:
         line = {"metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
                 "warmup": args.warmup, "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "weak",
-                "vs_baseline": None, "dtype": "mxfp4 weights x 3-term fp4 activations (kind::mxf4), f32 accumulate",
+                "vs_baseline": None, "dtype": dtype_s,
                 "data": "synthetic",
-                "config": {"workload": f"gptoss_decode H{H} I{I} E{E} top{K} T{T}/gpu mxfp4 expert-parallel",
+                "config": {"workload": f"{args.workload} H{H} I{I} E{E} top{K} T{T}/gpu {shape.wq} expert-parallel",
                            "parallelism": f"ep{world}", "l2": "inputs larger than L2 (expert weights streamed)"},
                 "clocks": clocks,
                 "e2e": {"value": T * world * args.steps / (ms_e2e * 1e-3), "unit": UNIT,

@@ -62,7 +62,7 @@ class ExpertParallelMoE:
 
     def __init__(self, w1, w1_scale, w2, w2_scale, num_experts: int, rank: int, world: int,
                  group: Optional[dist.ProcessGroup] = None, local_fn: Optional[Callable] = None,
-                 small_batch: int = 512):
+                 small_batch: int = 512, quant_type=None):
         if num_experts % world:
             raise ValueError("num_experts must be divisible by the number of ranks")
         self.E, self.rank, self.world, self.group = num_experts, rank, world, group
@@ -70,10 +70,10 @@ class ExpertParallelMoE:
         self.small_batch = small_batch
         if local_fn is None:
             from .fused_moe import QuantType, fused_moe
+            qt = QuantType.per_1x32 if quant_type is None else quant_type
 
             def local_fn(x, tw, ids):
-                return fused_moe(x, w1, w2, tw, ids, quant_type=QuantType.per_1x32, w1_scale=w1_scale,
-                                 w2_scale=w2_scale)
+                return fused_moe(x, w1, w2, tw, ids, quant_type=qt, w1_scale=w1_scale, w2_scale=w2_scale)
         self.local_fn = local_fn
 
     def _a2a(self, out, inp, out_splits, in_splits):
