@@ -44,6 +44,14 @@ def parse():
     return ap.parse_args()
 
 
+def profiled_traffic(workload, T):
+    """DRAM bytes per gate-up launch from the committed ncu capture of this workload, else None."""
+    f = ROOT / "profiles" / "gemm_mxf4_gptoss_decode_T64_traffic.json"
+    if workload == "gptoss_decode" and T == 64 and f.exists():
+        return json.loads(f.read_text()).get("gateup_dram_bytes")
+    return None
+
+
 def measured_peaks():
     p = ROOT / "MEASURED_PEAKS.json"
     if p.exists():
@@ -246,7 +254,7 @@ def run_b200(args):
         peak, peak_kind = measured_peaks()
         achieved = gu_bytes / per_launch_s / 1e9
         roofline = {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
-                    "traffic": None, "kernel": "moe_grouped_gemm_kernel<gate-up>", "peak_kind": peak_kind,
+                    "traffic": profiled_traffic(args.workload, T), "kernel": "moe_grouped_gemm_kernel<gate-up>", "peak_kind": peak_kind,
                     "us_per_launch": per_launch_s * 1e6, "down_us_per_launch": ms_dn * 1e3 / args.steps,
                     "algorithmic_bytes": gu_bytes}
         layer_bytes = synth.algorithmic_bytes(T, H, I, hit, shape.wq)
