@@ -19,10 +19,11 @@
 // gate and the up rows of the same features (gate-up GEMM), or two consecutive row tiles of the
 // down projection.  It is four copy instructions: weights, all activation terms, two scale groups.
 //
-// Warp roles (448 threads):
+// Warp roles (480 threads):
 //   warp 0      TMA producer
-//   warp 1      MMA issuer + TMEM owner (whole warp walks the loop, lane 0 issues; descriptors are
-//               precomputed 32-bit halves -- the issuing thread is the scarce resource)
+//   warps 1,14  MMA issuers, one per weight tile of the stage (whole warp walks the loop, lane 0
+//               issues; descriptors are precomputed 32-bit halves -- an issuing thread manages
+//               about one instruction per 100 cycles, so two of them); warp 1 owns the TMEM
 //   warps 2-9   epilogue, two per TMEM lane quadrant: activation with the oracle's bf16 roundings,
 //               bf16 staging tile in shared memory, block-wise re-quantisation into the down GEMM's
 //               operand format, overlapped with the next tile's main loop (two TMEM accumulators)
@@ -46,7 +47,8 @@
 
 namespace b200moe {
 
-constexpr int kThreads = 448;          // TMA warp, MMA warp, 8 epilogue warps, 4 scale-loader warps
+constexpr int kThreads = 480;          // TMA warp, MMA warp, 8 epilogue warps, 4 scale-loader warps, 2nd MMA warp
+constexpr int kMma2Warp = 14;          // issues the MMAs of the stage's second weight tile
 constexpr int kTileM = 128;          // weight rows per MMA
 constexpr int kStagePitch = kTileM * 2 + 16;   // bytes per token row of the bf16 staging tile
 constexpr int kTileK = kKPad;        // K per pipeline stage: 256 (4 MMA K-steps of 64, 2 scale k-blocks of 128)
@@ -128,13 +130,13 @@ moe_grouped_gemm_kernel(const __grid_constant__ GemmParams p) {
   if (threadIdx.x == 0) {
     for (int s = 0; s < S; ++s) {
       mbar_init(smem_u32(&ctl->full[s]), 1);
-      mbar_init(smem_u32(&ctl->empty[s]), 1);
+      mbar_init(smem_u32(&ctl->empty[s]), 2);      // one commit per MMA warp
     }
     for (int a = 0; a < 2; ++a) {
-      mbar_init(smem_u32(&ctl->tmem_full[a]), 1);
+      mbar_init(smem_u32(&ctl->tmem_full[a]), 2);
       mbar_init(smem_u32(&ctl->tmem_empty[a]), 8);
       mbar_init(smem_u32(&ctl->sf_full[a]), 4);
-      mbar_init(smem_u32(&ctl->sf_empty[a]), 1);
+      mbar_init(smem_u32(&ctl->sf_empty[a]), 2);
     }
     ctl->abort_word = 0;
     fence_mbar_init();
@@ -200,9 +202,13 @@ moe_grouped_gemm_kernel(const __grid_constant__ GemmParams p) {
         }
       }
     }
-  } else if (warp == 1) {
-    // ------------------------------------------------------------------ MMA issuer
-    // The whole warp walks the loop (uniform control flow); lane 0 issues.
+  } else if (warp == 1 || warp == kMma2Warp) {
+    // ------------------------------------------------------------------ MMA issuers
+    // Two warps, one per weight tile of the stage (gate / up, or the two down tiles): a single
+    // issuing thread tops out near 100 cycles per instruction, two double the issue rate and
+    // write disjoint accumulators.  The whole warp walks the loop (uniform control flow); lane 0
+    // issues.  Every barrier this role completes counts two arrivals.
+    const uint32_t part = (warp == 1) ? 0u : 1u;
     uint32_t idesc[2];
 #pragma unroll
     for (int s = 0; s < 2; ++s)
@@ -221,7 +227,7 @@ moe_grouped_gemm_kernel(const __grid_constant__ GemmParams p) {
       if (!mbar_wait(smem_u32(&ctl->tmem_empty[acc]), acc_phase ^ 1, abort_word, 0x200 + acc)) break;
       t_wait_acc += clock64() - ta0;
       tc_fence_after_sync();
-      const uint32_t d0 = tmem_base + acc * acc_cols;
+      const uint32_t d0 = tmem_base + acc * acc_cols + part * ncol;
       for (int kb = 0; kb < p.KB; ++kb) {
         const long long tf0 = clock64();
         if (!mbar_wait(smem_u32(&ctl->full[stage]), phase, abort_word, 0x300 + stage)) { ok = false; break; }
@@ -230,20 +236,18 @@ moe_grouped_gemm_kernel(const __grid_constant__ GemmParams p) {
         tc_fence_after_sync();
         if (lane == 0) {
           const uint32_t st = stage0 + (uint32_t)stage * geo.stage_bytes;
-          const uint32_t a_lo = desc_lo_sw(st);
+          const uint32_t a_lo = desc_lo_sw(st + part * kATileBytes);
           const uint32_t b_lo = desc_lo_sw(st + geo.a_bytes);
           // scale columns of this stage (written by the scale-loader warps): per 128-wide k-block
           // {A: gate/up or tile pair, 8 columns}, then {B: up to 16 columns}
-          const uint32_t sfa_t = tmem_base + kSfCol0 + sf_buf * 48;
-          const uint32_t sfb_t = sfa_t + 16;
+          const uint32_t sfa_t = tmem_base + kSfCol0 + sf_buf * 48 + 4 * part;
+          const uint32_t sfb_t = tmem_base + kSfCol0 + sf_buf * 48 + 16;
           const uint32_t first = kb != 0;
           if (merged) {
 #pragma unroll
             for (int s = 0; s < 2 * kSub; ++s) {
               const uint32_t sa = sfa_t + 8 * (s >> 1), sb = sfb_t + 16 * (s >> 1);
               umma_mxf4(d0, a_lo + 2 * s, b_lo + 2 * s, idesc[s & 1], sa, sb, s == 0 ? first : 1u);
-              umma_mxf4(d0 + ncol, a_lo + (kATileBytes >> 4) + 2 * s, b_lo + 2 * s, idesc[s & 1], sa + 4, sb,
-                        s == 0 ? first : 1u);
             }
           } else {
 #pragma unroll
@@ -254,8 +258,6 @@ moe_grouped_gemm_kernel(const __grid_constant__ GemmParams p) {
                 if (t < NT) {
                   const uint32_t accum = (s == 0 && t == 0) ? first : 1u;
                   umma_mxf4(d0, a_lo + 2 * s, b_lo + t * term_lo + 2 * s, idesc[s & 1], sa, sb + 4 * t, accum);
-                  umma_mxf4(d0 + ncol, a_lo + (kATileBytes >> 4) + 2 * s, b_lo + t * term_lo + 2 * s, idesc[s & 1],
-                            sa + 4, sb + 4 * t, accum);
                 }
               }
             }
@@ -273,7 +275,7 @@ moe_grouped_gemm_kernel(const __grid_constant__ GemmParams p) {
       __syncwarp();
       if (n_acc == 2) { acc ^= 1; if (acc == 0) acc_phase ^= 1; } else { acc_phase ^= 1; }
     }
-    if (blockIdx.x == 0 && lane == 0) {   // profiling: kilo-cycles of the MMA warp: total, waiting for data, for TMEM
+    if (blockIdx.x == 0 && lane == 0 && part == 0) {   // profiling: kilo-cycles of an MMA warp: total, waiting for data, for TMEM
       p.status[5] = (int32_t)((clock64() - t_begin) >> 10);
       p.status[6] = (int32_t)(t_wait_full >> 10);
       p.status[7] = (int32_t)(t_wait_acc >> 10);

@@ -248,6 +248,22 @@ def moe_forward(plan: MoEPlan, pw: PreparedWeights, hidden_states, topk_weight, 
     return out
 
 
+def capture_forward(plan: MoEPlan, pw, hidden_states, topk_weight, topk_ids, expert_mask=None, out=None):
+    """Capture one layer call (five kernel launches, no host synchronisation inside) into a CUDA
+    graph.  Returns (graph, out): ``graph.replay()`` re-runs the layer on the same tensors -- the
+    caller refreshes their contents in place between replays.  Decode-sized calls are bound by the
+    host's launch rate rather than by the GPU; a replay removes that cost."""
+    T, H = hidden_states.shape
+    if out is None:
+        out = torch.empty((T, H), dtype=torch.bfloat16, device=hidden_states.device)
+    moe_forward(plan, pw, hidden_states, topk_weight, topk_ids, expert_mask, out)   # first-use set-up outside capture
+    torch.cuda.synchronize()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        moe_forward(plan, pw, hidden_states, topk_weight, topk_ids, expert_mask, out)
+    return graph, out
+
+
 def fused_moe(hidden_states, w1, w2, topk_weight, topk_ids, expert_mask=None,
               activation=ActivationType.Silu, quant_type=QuantType.No, doweight_stage1=False,
               w1_scale=None, w2_scale=None, a1_scale=None, a2_scale=None, block_size_M=None,
