@@ -37,7 +37,7 @@ def parse():
     ap.add_argument("--warmup", type=int, default=10)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--tokens", type=int, default=0, help="tokens per GPU per step (0 = the workload's own)")
-    ap.add_argument("--workload", default="gptoss_decode", choices=["gptoss_decode", "gptoss_prefill", "dsv3_ep"],
+    ap.add_argument("--workload", default="gptoss_decode", choices=["gptoss_decode", "gptoss_prefill", "dsv3_ep", "mixtral_skew"],
                     help="gptoss_*: MXFP4 weights (BASELINE configs 1, 2); dsv3_ep: FP8 128x128 weights (config 3)")
     ap.add_argument("--sweep", action="store_true", help="also time T in {1,8,32,64,256,8192} (extra keys)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
@@ -53,12 +53,43 @@ def profiled_traffic(workload, T):
     return None
 
 
-def measured_peaks():
+def measured_peaks(key="hbm_gbs"):
+    """(peak, "measured"|"fallback") from the driver-written peaks file; `key` is hbm_gbs,
+    bf16_tflops (burst) or bf16_tflops_sustained."""
     p = ROOT / "MEASURED_PEAKS.json"
     if p.exists():
         d = json.loads(p.read_text())
-        return float(d["hbm_gbs"]), "measured"
-    return 6650.0, "fallback"
+        if key in d:
+            return float(d[key]), "measured " + key
+    return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}[key], "fallback " + key
+
+
+def fp4_dense_rate(dev, n=256, count=40000):
+    """Dense FP4 tensor rate of the whole chip in TFLOP/s: every SM issues `count` block-scaled
+    kind::mxf4 MMAs of 128 x n x 64 from resident shared-memory tiles (the library's rate probe),
+    timed with stream events after one warm-up launch."""
+    import ctypes
+    import torch
+    from pyhip_b200 import _lib
+    sms = torch.cuda.get_device_properties(dev).multi_processor_count
+    cfg = torch.tensor([0, n, count, 1], dtype=torch.int32, device=dev)
+    out = torch.zeros(sms * 3, dtype=torch.int32, device=dev)
+    st = ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+
+    def run():
+        _lib.check(_lib.lib().b200moe_debug_probe(4, ctypes.c_void_p(cfg.data_ptr()), ctypes.c_void_p(out.data_ptr()), st),
+                   "debug_probe")
+    run()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(3):
+        run()
+    e1.record()
+    torch.cuda.synchronize()
+    if int(out.view(-1, 3)[:, 2].abs().max()) != 0:
+        return None
+    return 3.0 * sms * count * 2.0 * 128 * n * 64 / (e0.elapsed_time(e1) * 1e-3) / 1e12
 
 
 class ClockSampler:
@@ -102,57 +133,75 @@ class ClockSampler:
                 "samples": len(sm)}
 
 
-def cpu_oracle_rate(T, shape, sample_experts, seed=0, repeats=1):
-    """tokens/s of the CPU oracle, measured on the first `sample_experts` experts that the batch
-    hits (weights dequantised inside the expert loop, as the baseline definition says) and scaled
-    by (experts hit / experts sampled)."""
+def cpu_oracle_rate(T, shape, sample_experts, seed=0, target_seconds=10.0):
+    """tokens/s of the CPU oracle, measured on the first experts that the batch hits (weights
+    dequantised inside the expert loop, as the baseline definition says) and scaled to the whole
+    batch: by experts hit where dequantising an expert dominates (fewer than 64 rows per expert),
+    by (token, expert) pairs where the matmuls do.  A first pass over `sample_experts` experts
+    sizes a second pass of about `target_seconds` of CPU work."""
     import torch
     from oracle import moe_oracle as orc
     from pyhip_b200 import synth
     torch.set_num_threads(os.cpu_count() or 1)
     x = synth.make_hidden(T, shape.H, seed)
-    tw, ids = synth.make_routing(T, shape.E, shape.K, shape.routing, seed)
+    tw, ids = synth.make_routing(T, shape.E, shape.K, shape.routing, seed, skew_seed=0)
     hit = sorted(set(ids.flatten().tolist()))
-    sample = hit[:sample_experts]
-    w = synth.make_weights_mxfp4(max(sample) + 1, shape.H, shape.I, seed, experts=sample)
-    keep = torch.zeros(shape.E, dtype=torch.bool)
-    keep[sample] = True
-    ids_s = torch.where(keep[ids.long()], ids, torch.full_like(ids, -1))
-    best = None
-    for _ in range(repeats):
+    fp8 = shape.wq == "fp8_128"
+    make = synth.make_weights_fp8 if fp8 else synth.make_weights_mxfp4
+    run = orc.torch_moe_oracle_fp8 if fp8 else orc.torch_moe_oracle_mxfp4
+
+    def one(n):
+        sample = hit[:n]
+        w = make(max(sample) + 1, shape.H, shape.I, seed, experts=sample)
+        keep = torch.zeros(shape.E, dtype=torch.bool)
+        keep[sample] = True
+        ids_s = torch.where(keep[ids.long()], ids, torch.full_like(ids, -1))
         t0 = time.perf_counter()
-        orc.torch_moe_oracle_mxfp4(x, *w, tw, ids_s)
-        dt = time.perf_counter() - t0
-        best = dt if best is None else min(best, dt)
-    full = best * len(hit) / len(sample)
-    return T / full, {"experts_hit": len(hit), "experts_sampled": len(sample), "sample_seconds": round(best, 3)}
+        run(x, *w, tw, ids_s)
+        return time.perf_counter() - t0, len(sample), int(keep[ids.long()].sum())
+
+    dt, n, pairs_s = one(min(sample_experts, len(hit)))
+    more = min(len(hit), 32, int(n * target_seconds / max(dt, 1e-3)))
+    if more > n:
+        dt, n, pairs_s = one(more)
+    pairs = ids.numel()
+    by_pairs = pairs / shape.E >= 64
+    full = dt * (pairs / pairs_s if by_pairs else len(hit) / n)
+    return T / full, {"experts_hit": len(hit), "experts_sampled": n, "sample_seconds": round(dt, 3),
+                      "scaled_by": "pairs" if by_pairs else "experts"}
+
+
+def cpu_sample_text(info):
+    return (f"torch dequantise-then-matmul oracle on {info['experts_sampled']} of {info['experts_hit']} hit experts "
+            f"({info['sample_seconds']} s), scaled to the whole batch by {info['scaled_by']}")
 
 
 def run_reference(args):
     from pyhip_b200 import synth
-    shape = synth.CONFIGS["gptoss_decode"]
+    shape = synth.CONFIGS[args.workload]
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
     T = args.tokens or shape.T
+    n_sample = 4 if T * shape.K / shape.E < 64 else 1
     rates, info = [], None
-    for _ in range(max(1, min(args.warmup, 1))):
-        cpu_oracle_rate(T, shape, 2)
     t_start = time.perf_counter()
+    for _ in range(max(1, min(args.warmup, 1))):
+        cpu_oracle_rate(T, shape, n_sample, target_seconds=0.0)
     for _ in range(max(1, args.steps)):
-        r, info = cpu_oracle_rate(T, shape, 4)
+        r, info = cpu_oracle_rate(T, shape, n_sample)
         rates.append(r)
-        if time.perf_counter() - t_start > 150:
+        if time.perf_counter() - t_start > 120:
             break
     v = statistics.median(rates)
     line = {
         "impl": "reference", "metric": METRIC, "value": v, "unit": UNIT, "n_gpus": args.gpus, "steps": len(rates),
         "warmup": args.warmup, "ms_per_step": 1e3 * T / v, "higher_is_better": True, "scaling": "weak",
         "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-        "config": {"workload": f"gptoss_decode H2880 I2880 E128 top4 T{T} mxfp4", "l2": "n/a (CPU)"},
+        "config": {"workload": f"{args.workload} H{shape.H} I{shape.I} E{shape.E} top{shape.K} T{T} {shape.wq}",
+                   "l2": "n/a (CPU)"},
         "cpu_baseline": {"value": v, "unit": UNIT, "cores": os.cpu_count(), "kind": "port",
-                         "sample": f"torch dequantise-then-matmul oracle on {info['experts_sampled']} of "
-                                   f"{info['experts_hit']} hit experts per step, scaled to all hit experts"},
+                         "sample": cpu_sample_text(info)},
         "e2e": {"value": v, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
     }
     print(json.dumps(line), flush=True)
@@ -200,20 +249,24 @@ def run_b200(args):
 
     shape = synth.CONFIGS[args.workload]
     T, H, I, E, K = (args.tokens or shape.T), shape.H, shape.I, shape.E, shape.K
+    strong = args.workload == "mixtral_skew"        # this configuration states a global token count
+    if strong and world > 1:
+        T //= world
     launches_per_step = 5
     fp8 = shape.wq == "fp8_128"
     qt = QuantType.per_128x128 if fp8 else QuantType.per_1x32
     fmt = 1 if fp8 else 0
+    distinct = 2 if 3.0 * H * I > 1e8 else (4 if fp8 else 8)   # experts drawn on the host (the rest repeat them)
     make_w = synth.make_weights_fp8_fast if fp8 else synth.make_weights_mxfp4_fast
     wbytes = (1.0 + 4.0 / 16384) if fp8 else (0.5 + 1.0 / 32)
     dtype_s = ("fp8-e4m3 128x128-block weights x 2-term e4m3 activations (kind::mxf8f6f4), f32 accumulate" if fp8 else
                "mxfp4 weights x 3-term fp4 activations (kind::mxf4), f32 accumulate")
 
     if world == 1:
-        w = make_w(E, H, I, seed=0, device=dev)
+        w = make_w(E, H, I, seed=0, device=dev, distinct=min(distinct, E))
         pw = prepare_weights(*w, weight_format=fmt)
         x = synth.make_hidden(T, H, 0)
-        tw, ids = synth.make_routing(T, E, K, shape.routing, 0)
+        tw, ids = synth.make_routing(T, E, K, shape.routing, 0, skew_seed=0)
         hit = len(set(ids.flatten().tolist()))
         xd, twd, idsd = x.to(dev), tw.to(dev), ids.to(dev)
         B = pick_block(T, K, E)
@@ -262,19 +315,35 @@ def run_b200(args):
         ms_dn = time_steps(lambda: plan.down(pw), args.steps, args.warmup)
         per_launch_s = ms_gu * 1e-3 / args.steps
         gu_bytes = hit * 2.0 * H * I * wbytes + T * H * 2.0
+        gu_flops = 4.0 * T * K * H * I
         peak, peak_kind = measured_peaks()
         achieved = gu_bytes / per_launch_s / 1e9
-        roofline = {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
-                    "traffic": profiled_traffic(args.workload, T), "kernel": "moe_grouped_gemm_kernel<gate-up>", "peak_kind": peak_kind,
-                    "us_per_launch": per_launch_s * 1e6, "down_us_per_launch": ms_dn * 1e3 / args.steps,
-                    "algorithmic_bytes": gu_bytes}
+        hbm_time = gu_bytes / (peak * 1e9)
+        tpeak, tpeak_kind = measured_peaks("bf16_tflops_sustained" if ms_gu > 500 else "bf16_tflops")
+        if gu_flops / (tpeak * 1e12) > hbm_time:
+            # compute-bound launch: report against the measured dense bf16 rate (the only tensor peak the
+            # peaks file carries) and, beside it, the dense FP4 MMA rate measured here on every SM at once
+            fp4 = fp4_dense_rate(dev)
+            ach = gu_flops / per_launch_s / 1e12
+            roofline = {"bound": "tensor", "achieved": ach, "peak": tpeak, "unit": "TFLOP/s", "frac": ach / tpeak,
+                        "traffic": profiled_traffic(args.workload, T), "kernel": "moe_grouped_gemm_kernel<gate-up>",
+                        "peak_kind": tpeak_kind + " (dense bf16 GEMM)", "us_per_launch": per_launch_s * 1e6,
+                        "down_us_per_launch": ms_dn * 1e3 / args.steps, "algorithmic_flops": gu_flops,
+                        "fp4_dense_measured_tflops": fp4, "frac_of_fp4_measured": ach / fp4 if fp4 else None,
+                        "frac_of_fp4_nominal_9pf": ach / 9000.0,
+                        "note": "three packed-FP4 activation terms per product: the MMA work is 3x the algorithmic flops"}
+        else:
+            roofline = {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
+                        "traffic": profiled_traffic(args.workload, T), "kernel": "moe_grouped_gemm_kernel<gate-up>",
+                        "peak_kind": peak_kind, "us_per_launch": per_launch_s * 1e6,
+                        "down_us_per_launch": ms_dn * 1e3 / args.steps, "algorithmic_bytes": gu_bytes}
         layer_bytes = synth.algorithmic_bytes(T, H, I, hit, shape.wq)
         extra = {"layer_gbs": layer_bytes / (ms * 1e-3 / args.steps) / 1e9,
                  "layer_frac_of_hbm_peak": layer_bytes / (ms * 1e-3 / args.steps) / 1e9 / peak,
                  "layer_tflops": synth.algorithmic_flops(T, K, H, I) / (ms * 1e-3 / args.steps) / 1e12,
                  "experts_hit": hit}
         sweep = None
-        if args.sweep and not fp8:
+        if args.sweep and args.workload.startswith("gptoss"):
             sweep = []
             for Ts in (1, 8, 32, 64, 256, 8192):
                 xs = synth.make_hidden(Ts, H, 0).to(dev)
@@ -295,11 +364,9 @@ def run_b200(args):
                               "gbs": synth.algorithmic_bytes(Ts, H, I, u) / (us * 1e-6) / 1e9,
                               "tflops": synth.algorithmic_flops(Ts, K, H, I) / (us * 1e-6) / 1e12})
         cpu = None
-        if not args.no_cpu_baseline and not fp8:
-            r, info = cpu_oracle_rate(T, shape, 4)
-            cpu = {"value": r, "unit": UNIT, "cores": os.cpu_count(), "kind": "port",
-                   "sample": f"torch dequantise-then-matmul oracle on {info['experts_sampled']} of "
-                             f"{info['experts_hit']} hit experts ({info['sample_seconds']} s), scaled to all hit experts"}
+        if not args.no_cpu_baseline:
+            r, info = cpu_oracle_rate(T, shape, 4 if T * K / E < 64 else 1)
+            cpu = {"value": r, "unit": UNIT, "cores": os.cpu_count(), "kind": "port", "sample": cpu_sample_text(info)}
         line = {"metric": METRIC, "value": value, "unit": UNIT, "n_gpus": 1, "steps": args.steps,
                 "warmup": args.warmup, "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "weak",
                 "vs_baseline": None, "dtype": dtype_s,
@@ -318,11 +385,10 @@ def run_b200(args):
     # ------------------------------------------------------------------ expert parallel, N > 1
     from pyhip_b200 import ep
     E_local = E // world
-    experts = list(range(rank * E_local, (rank + 1) * E_local))
-    w_full = make_w(E_local, H, I, seed=rank, device=dev)
+    w_full = make_w(E_local, H, I, seed=rank, device=dev, distinct=min(distinct, E_local))
     layer = ep.ExpertParallelMoE(w_full[0], w_full[1], w_full[2], w_full[3], E, rank, world, quant_type=qt)
     x = synth.make_hidden(T, H, rank)
-    tw, ids = synth.make_routing(T, E, K, shape.routing, rank)
+    tw, ids = synth.make_routing(T, E, K, shape.routing, rank, skew_seed=0)
     xd, twd, idsd = x.to(dev), tw.to(dev), ids.to(dev)
 
     def step():
@@ -341,18 +407,58 @@ def run_b200(args):
         yh.copy_(out, non_blocking=True)
 
     ms_e2e = time_steps(step_e2e, args.steps, args.warmup, dist)
+
+    # ---- per-rank time inside the local experts (load balance), three extra steps
+    layer.busy_events = []
+    for _ in range(3):
+        step()
+    torch.cuda.synchronize()
+    busy = statistics.median(a.elapsed_time(b) for a, b in layer.busy_events) if layer.busy_events else 0.0
+    layer.busy_events = None
+    busy_t = torch.tensor([busy], device=dev)
+    busy_all = [torch.zeros_like(busy_t) for _ in range(world)]
+    dist.all_gather(busy_all, busy_t)
+
+    # ---- dominant kernel on this rank's rows (gate-up grouped GEMM), timed alone on rank 0
+    roofline = None
+    if rank == 0 and layer.last_local is not None:
+        xr, twr, idr = layer.last_local
+        n = xr.shape[0]
+        pw = prepare_weights(*w_full, weight_format=fmt)
+        plan = get_plan(n, K, E_local, E_local, H, I, pick_block(n, K, E_local), 0, 7.0, dev, weight_format=fmt)
+        plan.sort(idr.contiguous(), twr.contiguous())
+        plan.quant_input(xr)
+        k_steps = max(3, min(args.steps, 50))
+        ms_gu = time_steps(lambda: plan.gateup(pw, None), k_steps, 3)
+        plan.check_status()
+        idc = idr.flatten()
+        hit_l = int(torch.unique(idc[(idc >= 0) & (idc < E_local)]).numel())
+        pairs_l = int(((idc >= 0) & (idc < E_local)).sum())
+        per = ms_gu * 1e-3 / k_steps
+        peak, peak_kind = measured_peaks()
+        gu_bytes = hit_l * 2.0 * H * I * wbytes + n * H * 2.0
+        roofline = {"bound": "hbm", "achieved": gu_bytes / per / 1e9, "peak": peak, "unit": "GB/s",
+                    "frac": gu_bytes / per / 1e9 / peak, "traffic": None, "peak_kind": peak_kind,
+                    "kernel": "moe_grouped_gemm_kernel<gate-up> on rank 0's received rows", "us_per_launch": per * 1e6,
+                    "algorithmic_bytes": gu_bytes, "tflops": 4.0 * pairs_l * H * I / per / 1e12,
+                    "rows": n, "pairs": pairs_l, "experts_hit": hit_l}
+    dist.barrier()
     if rank == 0:
         line = {"metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
-                "warmup": args.warmup, "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "weak",
+                "warmup": args.warmup, "ms_per_step": ms / args.steps, "higher_is_better": True,
+                "scaling": "strong" if strong else "weak",
                 "vs_baseline": None, "dtype": dtype_s,
                 "data": "synthetic",
                 "config": {"workload": f"{args.workload} H{H} I{I} E{E} top{K} T{T}/gpu {shape.wq} expert-parallel",
-                           "parallelism": f"ep{world}", "l2": "inputs larger than L2 (expert weights streamed)"},
+                           "parallelism": f"ep{world}", "l2": "inputs larger than L2 (expert weights streamed)",
+                           "exchange": "all-gather + reduce-scatter" if T <= layer.small_batch else
+                                       "all-to-all-v dispatch and combine"},
                 "clocks": clocks,
                 "e2e": {"value": T * world * args.steps / (ms_e2e * 1e-3), "unit": UNIT,
                         "h2d_bytes_per_step": x.numel() * 2 + tw.numel() * 4 + ids.numel() * 4,
                         "d2h_bytes_per_step": T * H * 2},
-                "gpu_launches": launches_per_step * args.steps}
+                "gpu_launches": launches_per_step * args.steps, "roofline": roofline, "cpu_baseline": None,
+                "local_expert_ms_per_rank": [round(float(b.item()), 4) for b in busy_all]}
         print(json.dumps(line), flush=True)
     dist.destroy_process_group()
 

@@ -157,7 +157,7 @@ def torch_moe_oracle(hidden, w1, w2, topk_weight, topk_ids, activation="silu",
     ids = topk_ids.long()
     out = torch.zeros((T, H), dtype=hidden.dtype)
     E = w1.shape[0] if expert_weights is None else None
-    e_list = range(E) if expert_weights is None else sorted(set(ids.flatten().tolist()))
+    e_list = range(E) if expert_weights is None else sorted(e for e in set(ids.flatten().tolist()) if e >= 0)
     ids_kt = ids.t().contiguous()                     # [K, T]: where() walks k-major like the
     for e in e_list:                                  # reference's permuted one-hot mask
         k_idx, t_idx = torch.where(ids_kt == e)

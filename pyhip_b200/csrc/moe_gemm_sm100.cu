@@ -666,7 +666,7 @@ __global__ void __launch_bounds__(128, 1) probe_utccp_kernel(const uint32_t* in,
 }
 
 // Issue-rate probe: `count` MMAs of shape 128 x N x 64 alternating between `nacc` accumulators,
-// one commit, one bounded wait; reports clock cycles.  Operand contents are irrelevant (zeros).
+// one commit, one bounded wait; reports clock cycles.  The results are never read back.
 __global__ void __launch_bounds__(128, 1) probe_mma_rate_kernel(const int32_t* cfg, uint32_t* out) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -674,7 +674,9 @@ __global__ void __launch_bounds__(128, 1) probe_mma_rate_kernel(const int32_t* c
   __shared__ uint32_t tmem_slot, abort_word;
   const int N = cfg[1], count = cfg[2], nacc = cfg[3];
   const int warp = threadIdx.x >> 5;
-  for (int i = threadIdx.x; i < (16384 + 32768 + 1024) / 4; i += blockDim.x) reinterpret_cast<uint32_t*>(smem)[i] = 0;
+  // pseudo-random FP4 operands (realistic switching activity) and unit scales
+  for (int i = threadIdx.x; i < (16384 + 32768 + 1024) / 4; i += blockDim.x)
+    reinterpret_cast<uint32_t*>(smem)[i] = (i < (16384 + 32768) / 4) ? (uint32_t)(i + 1) * 2654435761u : 0x7F7F7F7Fu;
   if (threadIdx.x == 0) {
     abort_word = 0;
     mbar_init(smem_u32(&bar), 1);
@@ -712,9 +714,10 @@ __global__ void __launch_bounds__(128, 1) probe_mma_rate_kernel(const int32_t* c
     tc_commit(smem_u32(&bar));
     mbar_wait(smem_u32(&bar), 0, &abort_word, 3);
     const long long t2 = clock64();
-    out[0] = (uint32_t)(t1 - t0);
-    out[1] = (uint32_t)(t2 - t0);
-    out[2] = abort_word;
+    uint32_t* o = out + 3 * blockIdx.x;
+    o[0] = (uint32_t)(t1 - t0);
+    o[1] = (uint32_t)(t2 - t0);
+    o[2] = abort_word;
   }
   tc_fence_before_sync();
   __syncthreads();
@@ -739,14 +742,15 @@ int run_debug_probe(int which, const void* in, void* out, cudaStream_t st) {
     B200_CHECK_CUDA(cudaGetLastError());
     return 0;
   }
-  if (which == 3) {
+  if (which == 3 || which == 4) {
     static bool attr = false;
     if (!attr) {
       B200_CHECK_CUDA(cudaFuncSetAttribute(probe_mma_rate_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                            65536));
       attr = true;
     }
-    probe_mma_rate_kernel<<<1, 128, 16384 + 32768 + 1024 + 1024, st>>>((const int32_t*)in, (uint32_t*)out);
+    const int grid = (which == 4) ? device_sm_count() : 1;
+    probe_mma_rate_kernel<<<grid, 128, 16384 + 32768 + 1024 + 1024, st>>>((const int32_t*)in, (uint32_t*)out);
     B200_CHECK_CUDA(cudaGetLastError());
     return 0;
   }

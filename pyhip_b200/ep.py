@@ -75,6 +75,19 @@ class ExpertParallelMoE:
             def local_fn(x, tw, ids):
                 return fused_moe(x, w1, w2, tw, ids, quant_type=qt, w1_scale=w1_scale, w2_scale=w2_scale)
         self.local_fn = local_fn
+        self.last_local = None      # (rows, weights, local ids) of the latest local call, for measurement
+        self.busy_events = None     # set to a list to collect (start, end) CUDA events around the local call
+
+    def _local(self, x, tw, ids):
+        self.last_local = (x, tw, ids)
+        if self.busy_events is None:
+            return self.local_fn(x, tw, ids)
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        y = self.local_fn(x, tw, ids)
+        e1.record()
+        self.busy_events.append((e0, e1))
+        return y
 
     def _a2a(self, out, inp, out_splits, in_splits):
         dist.all_to_all_single(out, inp, out_splits, in_splits, group=self.group)
@@ -98,7 +111,7 @@ class ExpertParallelMoE:
         dist.all_gather_into_tensor(meta_all, meta.contiguous(), group=self.group)
         local_ids = (meta_all[:, :K] - self.rank * self.E_local).contiguous()
         tw_all = meta_all[:, K:].contiguous().view(torch.float32)
-        y_part = self.local_fn(x_all, tw_all, local_ids)
+        y_part = self._local(x_all, tw_all, local_ids)
         y = torch.empty(T, H, dtype=x.dtype, device=x.device)
         if dist.get_backend(self.group) == "nccl":
             dist.reduce_scatter_tensor(y, y_part.contiguous(), op=dist.ReduceOp.SUM, group=self.group)
@@ -127,7 +140,7 @@ class ExpertParallelMoE:
         self._a2a(tw_recv, topk_weight[send_rows].contiguous(), r_splits, s_splits)
 
         local_ids = ids_recv - self.rank * self.E_local      # foreign experts land outside [0, E_local)
-        y_part = self.local_fn(x_recv, tw_recv, local_ids) if n_recv else x_recv
+        y_part = self._local(x_recv, tw_recv, local_ids) if n_recv else x_recv
         y_back = torch.empty(len(send_rows), H, dtype=x.dtype, device=x.device)
         self._a2a(y_back, y_part.contiguous(), s_splits, r_splits)
         return scatter_back(y_back, send_rows, T)

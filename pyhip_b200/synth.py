@@ -36,16 +36,18 @@ CONFIGS = {
 }
 
 
-def make_routing(T: int, E: int, K: int, routing: str = "softmax", seed: int = 0):
+def make_routing(T: int, E: int, K: int, routing: str = "softmax", seed: int = 0, skew_seed=None):
     """fp32 N(0,1) logits -> (topk_weight f32 [T,K], topk_ids i32 [T,K]).
 
     softmax: softmax -> top-k -> renormalise.  sigmoid: sigmoid -> top-k -> renormalise.
     zipf: logits + b_e with b_e = -1.2*ln(rank_e) under a seeded rank permutation (Zipf-like
-    expert load), then the softmax recipe."""
+    expert load), then the softmax recipe.  ``skew_seed``: draw that permutation from its own
+    generator, so that ranks with different ``seed`` share one expert popularity order."""
     g = torch.Generator().manual_seed(seed * 1000003 + 17)
     logits = torch.randn(T, E, generator=g, dtype=torch.float32)
     if routing == "zipf":
-        rank = torch.randperm(E, generator=g).float() + 1.0
+        gp = g if skew_seed is None else torch.Generator().manual_seed(skew_seed * 1000003 + 41)
+        rank = torch.randperm(E, generator=gp).float() + 1.0
         logits = logits + (-1.2 * torch.log(rank))[None, :]
     scores = torch.sigmoid(logits) if routing == "sigmoid" else torch.softmax(logits, dim=-1)
     w, ids = torch.topk(scores, K, dim=-1)
