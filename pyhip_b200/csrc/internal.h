@@ -97,6 +97,24 @@ int encode_map_sw(CUtensorMap* map, CUtensorMapDataType type, int rank, const vo
                   const cuuint64_t* strides, const cuuint32_t* box, CUtensorMapSwizzle swizzle,
                   CUtensorMapL2promotion promo, const char* what);
 int device_sm_count();
+
+// Launch `kernel` so that it may begin (prologue only: every kernel of this library calls
+// grid_dep_wait() before it touches global memory) while the previous kernel in the stream drains.
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch_chained(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t st,
+                                  Args&&... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = st;
+  cudaLaunchAttribute at[1];
+  at[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  at[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = at;
+  cfg.numAttrs = 1;
+  return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+}
 int run_debug_probe(int which, const void* in, void* out, cudaStream_t st);
 
 }  // namespace b200moe

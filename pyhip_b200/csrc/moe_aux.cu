@@ -33,6 +33,8 @@ sort_align_kernel(const int32_t* __restrict__ ids, const float* __restrict__ w, 
   unsigned long long* wsum =                // [33] scan scratch, 8-byte aligned
       reinterpret_cast<unsigned long long*>(sm + ((kSortWarps * E + 3 * E + 1) & ~1));
 
+  grid_dep_launch();
+  grid_dep_wait();     // the previous call on this stream may still read the arrays written below
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int P = T * K;
   const int seg = ((P + kSortWarps - 1) / kSortWarps + 31) & ~31;
@@ -143,9 +145,8 @@ int launch_sort_align(const int32_t* ids, const float* w, int T, int K, int E, i
                                          200 * 1024));
     attr_set = true;
   }
-  sort_align_kernel<<<1, kSortWarps * 32, smem, st>>>(ids, w, T, K, E, B, mask, sorted_ids, sorted_w, sorted_e,
-                                                      num_valid, loc);
-  B200_CHECK_CUDA(cudaGetLastError());
+  B200_CHECK_CUDA(launch_chained(sort_align_kernel, dim3(1), dim3(kSortWarps * 32), smem, st, ids, w, T, K, E, B, mask,
+                                 sorted_ids, sorted_w, sorted_e, num_valid, loc));
   return 0;
 }
 
@@ -165,6 +166,8 @@ quant_rows_kernel(const __nv_bfloat16* __restrict__ src, int src_mode, const uin
   const int nb = KP / 32;
   const int KB = KP / 128;
   const int64_t term_stride = max_rows * (KP / 2);
+  grid_dep_launch();
+  grid_dep_wait();
   const int64_t rows_live = min((int64_t)num_valid[0], max_rows);
   for (int64_t g = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; g < rows_live * nb;
        g += (int64_t)gridDim.x * blockDim.x) {
@@ -210,10 +213,9 @@ int launch_quant_rows(const void* src, int src_mode, const uint32_t* sorted_ids,
   int64_t work = max_rows * (KP / 32);
   int blocks = (int)std::min<int64_t>((work + 255) / 256, 148 * 16);
   if (blocks < 1) blocks = 1;
-  quant_rows_kernel<<<blocks, 256, 0, st>>>(reinterpret_cast<const __nv_bfloat16*>(src), src_mode, sorted_ids,
-                                            num_valid, T, K, Kd, KP, B, NT, act_term_stride(B, NT, 2), max_rows,
-                                            (uint8_t*)q, (uint8_t*)sf);
-  B200_CHECK_CUDA(cudaGetLastError());
+  B200_CHECK_CUDA(launch_chained(quant_rows_kernel, dim3(blocks), dim3(256), 0, st,
+                                 reinterpret_cast<const __nv_bfloat16*>(src), src_mode, sorted_ids, num_valid, T, K, Kd,
+                                 KP, B, NT, act_term_stride(B, NT, 2), max_rows, (uint8_t*)q, (uint8_t*)sf));
   return 0;
 }
 
@@ -226,6 +228,8 @@ quant_rows_e4m3_kernel(const __nv_bfloat16* __restrict__ src, int src_mode, cons
   const int nb = Kd / 32;
   const int KB = Kd / 128;
   const int64_t term_stride = max_rows * Kd;
+  grid_dep_launch();
+  grid_dep_wait();
   const int64_t rows_live = min((int64_t)num_valid[0], max_rows);
   for (int64_t g = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; g < rows_live * nb;
        g += (int64_t)gridDim.x * blockDim.x) {
@@ -272,9 +276,9 @@ int launch_quant_rows_e4m3(const void* src, int src_mode, const uint32_t* sorted
   int64_t work = max_rows * (Kd / 32);
   int blocks = (int)std::min<int64_t>((work + 255) / 256, 148 * 16);
   if (blocks < 1) blocks = 1;
-  quant_rows_e4m3_kernel<<<blocks, 256, 0, st>>>(reinterpret_cast<const __nv_bfloat16*>(src), src_mode, sorted_ids,
-                                                 num_valid, T, K, Kd, B, max_rows, (uint8_t*)q, (uint8_t*)sf);
-  B200_CHECK_CUDA(cudaGetLastError());
+  B200_CHECK_CUDA(launch_chained(quant_rows_e4m3_kernel, dim3(blocks), dim3(256), 0, st,
+                                 reinterpret_cast<const __nv_bfloat16*>(src), src_mode, sorted_ids, num_valid, T, K, Kd,
+                                 B, max_rows, (uint8_t*)q, (uint8_t*)sf));
   return 0;
 }
 
@@ -289,6 +293,8 @@ __global__ void __launch_bounds__(256)
 combine_kernel(const __nv_bfloat16* __restrict__ out2, const int32_t* __restrict__ loc,
                const float* __restrict__ topk_w, __nv_bfloat16* __restrict__ y, int T, int K, int H) {
   const int vec_per_row = H / 8;
+  grid_dep_launch();
+  grid_dep_wait();
   for (int64_t g = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; g < (int64_t)T * vec_per_row;
        g += (int64_t)gridDim.x * blockDim.x) {
     const int t = (int)(g / vec_per_row), c = (int)(g % vec_per_row) * 8;
@@ -325,8 +331,8 @@ int launch_combine(const void* out2, const int32_t* loc, const float* topk_w, vo
   if (T == 0) return 0;
   int64_t work = (int64_t)T * (H / 8);
   int blocks = (int)std::min<int64_t>((work + 255) / 256, 148 * 16);
-  combine_kernel<<<blocks, 256, 0, st>>>((const __nv_bfloat16*)out2, loc, topk_w, (__nv_bfloat16*)y, T, K, H);
-  B200_CHECK_CUDA(cudaGetLastError());
+  B200_CHECK_CUDA(launch_chained(combine_kernel, dim3(blocks), dim3(256), 0, st, (const __nv_bfloat16*)out2, loc,
+                                 topk_w, (__nv_bfloat16*)y, T, K, H));
   return 0;
 }
 

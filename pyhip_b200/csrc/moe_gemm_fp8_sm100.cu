@@ -116,6 +116,8 @@ __global__ void __launch_bounds__(kThreads, 1) moe_grouped_gemm_fp8_kernel(const
   __syncthreads();
   tc_fence_after_sync();
   const uint32_t tmem_base = ctl->tmem_base;
+  grid_dep_launch();   // tensor memory is held: the next kernel's CTAs may be scheduled
+  grid_dep_wait();     // predecessor complete: sort arrays and quantised activations are valid
 
   const int64_t rows_live = min((int64_t)p.num_valid[0], p.max_rows);
   const int n_blocks = (int)(rows_live / B);
@@ -440,13 +442,13 @@ int launch_grouped_gemm_fp8(const GemmArgs& a, cudaStream_t st) {
       B200_CHECK_CUDA(cudaFuncSetAttribute(moe_grouped_gemm_fp8_kernel<true>,
                                            cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemLimit));
     done = true;
-    moe_grouped_gemm_fp8_kernel<true><<<grid, kThreads, smem, st>>>(p);
+    B200_CHECK_CUDA(launch_chained(moe_grouped_gemm_fp8_kernel<true>, dim3(grid), dim3(kThreads), smem, st, p));
   } else {
     if (!done)
       B200_CHECK_CUDA(cudaFuncSetAttribute(moe_grouped_gemm_fp8_kernel<false>,
                                            cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemLimit));
     done = true;
-    moe_grouped_gemm_fp8_kernel<false><<<grid, kThreads, smem, st>>>(p);
+    B200_CHECK_CUDA(launch_chained(moe_grouped_gemm_fp8_kernel<false>, dim3(grid), dim3(kThreads), smem, st, p));
   }
   B200_CHECK_CUDA(cudaGetLastError());
   return 0;

@@ -150,6 +150,10 @@ moe_grouped_gemm_kernel(const __grid_constant__ GemmParams p) {
   __syncthreads();
   tc_fence_after_sync();
   const uint32_t tmem_base = ctl->tmem_base;
+  // This CTA holds its tensor memory now, so CTAs of the next kernel may be scheduled beside it without
+  // starving it; the sort arrays and quantised activations are valid once the predecessor has completed.
+  grid_dep_launch();
+  grid_dep_wait();
 
   const int64_t rows_live = min((int64_t)p.num_valid[0], p.max_rows);
   const int n_blocks = (int)(rows_live / B);
@@ -589,13 +593,13 @@ int launch_grouped_gemm(const GemmArgs& a, cudaStream_t st) {
       B200_CHECK_CUDA(cudaFuncSetAttribute(moe_grouped_gemm_kernel<true>,
                                            cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemLimit));
     done = true;
-    moe_grouped_gemm_kernel<true><<<grid, kThreads, smem, st>>>(p);
+    B200_CHECK_CUDA(launch_chained(moe_grouped_gemm_kernel<true>, dim3(grid), dim3(kThreads), smem, st, p));
   } else {
     if (!done)
       B200_CHECK_CUDA(cudaFuncSetAttribute(moe_grouped_gemm_kernel<false>,
                                            cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemLimit));
     done = true;
-    moe_grouped_gemm_kernel<false><<<grid, kThreads, smem, st>>>(p);
+    B200_CHECK_CUDA(launch_chained(moe_grouped_gemm_kernel<false>, dim3(grid), dim3(kThreads), smem, st, p));
   }
   B200_CHECK_CUDA(cudaGetLastError());
   return 0;

@@ -25,6 +25,13 @@ __device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
 __device__ __forceinline__ void fence_mbar_init() {
   asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
 }
+// Programmatic dependent launch: a kernel launched with the programmatic-serialisation attribute may
+// start while its predecessor in the stream still runs.  grid_dep_wait() returns once the predecessor
+// has completed and its writes are visible (no-op without the attribute); grid_dep_launch() lets the
+// successor's CTAs be scheduled as soon as every CTA of this grid has issued it or exited.
+__device__ __forceinline__ void grid_dep_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void grid_dep_launch() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
 __device__ __forceinline__ void fence_proxy_async_smem() {
   asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
 }
