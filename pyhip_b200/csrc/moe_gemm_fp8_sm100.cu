@@ -24,7 +24,10 @@ namespace b200moe {
 
 namespace fp8 {
 
-constexpr int kThreads = 448;
+constexpr int kThreads = 512;                   // 4 warpgroups: {TMA, MMA, 2 idle}, 2 x epilogue, scale loaders
+// registers per thread after reallocation: 8 epilogue warps, warpgroup 0 (producer, issuers, store warp),
+// 4 scale-loader warps: 256*184 + 128*104 + 128*40 = the 64K registers of an SM
+constexpr int kRegsEpilogue = 184, kRegsWg0 = 104, kRegsSf = 40;
 constexpr int kTileM = 128;
 constexpr int kTileK = 128;                      // one weight-scale block per stage
 constexpr int kATileBytes = kTileM * kTileK;     // 16 KB (one byte per element)
@@ -35,6 +38,8 @@ constexpr int kSmemLimit = 232448;
 constexpr int kStagePitch = kTileM * 2 + 16;
 constexpr int kMaxChunks = 3;                    // 16-column groups per epilogue warp (token tile <= 96)
 constexpr int kTerms = 2;
+constexpr int kCtlBytes = 4096;                  // barriers + the current tile's weight-block scales
+constexpr int kMaxKB = 128;                      // k-blocks per row whose scales fit the control region
 
 struct Params {
   CUtensorMap tmW;     // weights: gate-up (K, I, 2, E) box (128,128,2,1); down (K, H, 1, E) box (128,256,1,1), bytes
@@ -57,13 +62,16 @@ struct Params {
 struct SmemCtl {
   uint64_t full[kMaxStages];
   uint64_t empty[kMaxStages];
-  uint64_t tmem_full[2];
-  uint64_t tmem_empty[2];
+  uint64_t tmem_full[4];      // [accumulator buffer * 2 + weight tile]
+  uint64_t tmem_empty[4];
   uint64_t sf_full[2];
   uint64_t sf_empty[2];
+  uint64_t stg_full, stg_empty;   // staging tile of the fused gate-up output: epilogue warps -> store warp
   uint32_t tmem_base;
   uint32_t abort_word;
+  float wscale[2][2][kMaxKB];   // [tile parity][weight tile][k-block]
 };
+static_assert(sizeof(SmemCtl) <= kCtlBytes, "control region");
 
 struct StageGeom {
   int a_bytes, b_bytes, sfb_bytes, stage_bytes;
@@ -84,7 +92,7 @@ __global__ void __launch_bounds__(kThreads, 1) moe_grouped_gemm_fp8_kernel(const
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   SmemCtl* ctl = reinterpret_cast<SmemCtl*>(smem);
-  const uint32_t stage0 = smem_u32(smem) + 1024;
+  const uint32_t stage0 = smem_u32(smem) + kCtlBytes;
   const int B = p.B;
   const StageGeom geo = stage_geom(B);
   const int S = p.stages;
@@ -96,14 +104,18 @@ __global__ void __launch_bounds__(kThreads, 1) moe_grouped_gemm_fp8_kernel(const
   if (threadIdx.x == 0) {
     for (int s = 0; s < S; ++s) {
       mbar_init(smem_u32(&ctl->full[s]), 1);
-      mbar_init(smem_u32(&ctl->empty[s]), 1);
+      mbar_init(smem_u32(&ctl->empty[s]), 2);      // one commit per MMA warp
     }
     for (int a = 0; a < 2; ++a) {
-      mbar_init(smem_u32(&ctl->tmem_full[a]), 1);
-      mbar_init(smem_u32(&ctl->tmem_empty[a]), 8);
+      for (int h = 0; h < 2; ++h) {
+        mbar_init(smem_u32(&ctl->tmem_full[2 * a + h]), 1);
+        mbar_init(smem_u32(&ctl->tmem_empty[2 * a + h]), 8);
+      }
       mbar_init(smem_u32(&ctl->sf_full[a]), 4);
-      mbar_init(smem_u32(&ctl->sf_empty[a]), 1);
+      mbar_init(smem_u32(&ctl->sf_empty[a]), 2);
     }
+    mbar_init(smem_u32(&ctl->stg_full), 8);
+    mbar_init(smem_u32(&ctl->stg_empty), 1);
     ctl->abort_word = 0;
     fence_mbar_init();
     fence_proxy_async_smem();
@@ -116,6 +128,9 @@ __global__ void __launch_bounds__(kThreads, 1) moe_grouped_gemm_fp8_kernel(const
   __syncthreads();
   tc_fence_after_sync();
   const uint32_t tmem_base = ctl->tmem_base;
+  // the epilogue warpgroups (warps 4..11) hold the promoted fp32 accumulators in registers: they take the
+  // registers that the producer / issuer / scale-loader warpgroups do not need
+  // (the reallocation itself is the first statement of each warpgroup's branch below)
   grid_dep_launch();   // tensor memory is held: the next kernel's CTAs may be scheduled
   grid_dep_wait();     // predecessor complete: sort arrays and quantised activations are valid
 
@@ -123,45 +138,156 @@ __global__ void __launch_bounds__(kThreads, 1) moe_grouped_gemm_fp8_kernel(const
   const int n_blocks = (int)(rows_live / B);
   const int total_work = n_blocks * p.MT;
 
-  if (warp == 0) {
-    // ------------------------------------------------------------------ TMA producer
-    if (lane == 0) {
-      prefetch_tensormap(&p.tmW);
-      prefetch_tensormap(&p.tmA);
+  if (warp < 4) {
+    // warpgroup 0: TMA producer (warp 0), MMA issuers (warps 1, 2), store warp (warp 3)
+    reg_release<kRegsWg0>();
+    if (warp == 0) {
+      // ------------------------------------------------------------------ TMA producer
+      if (lane == 0) {
+        prefetch_tensormap(&p.tmW);
+        prefetch_tensormap(&p.tmA);
+        int stage = 0;
+        uint32_t phase = 0;
+        int64_t issued = 0;
+        bool ok = true;
+        for (int w = blockIdx.x; w < total_work && ok; w += gridDim.x) {
+          const int b = w / p.MT, m = w - b * p.MT;
+          int e = p.sorted_e[b];
+          if (e < 0 || e >= p.E) { p.status[2] = 1; e = 0; }
+          const int r0 = b * B;
+          const uint8_t* sfb = p.asf + (int64_t)b * p.KB * geo.sfb_bytes;
+          for (int kb = 0; kb < p.KB; ++kb) {
+            if (!mbar_wait(smem_u32(&ctl->empty[stage]), phase ^ 1, abort_word, 0x100 + stage)) { ok = false; break; }
+            const uint32_t st = stage0 + (uint32_t)stage * geo.stage_bytes;
+            const uint32_t full = smem_u32(&ctl->full[stage]);
+            mbar_expect_tx(full, geo.tx_bytes);
+            tma_load_4d(st, &p.tmW, full, kb * kTileK, m * (GATEUP ? kTileM : 2 * kTileM), 0, e);
+            tma_load_3d(st + geo.a_bytes, &p.tmA, full, kb * kTileK, r0, 0);
+            bulk_load(st + geo.a_bytes + geo.b_bytes, sfb, (uint32_t)geo.sfb_bytes, full);
+            sfb += geo.sfb_bytes;
+            ++issued;
+            if (++stage == S) { stage = 0; phase ^= 1; }
+          }
+        }
+        if (!ok || *abort_word) {
+          const int64_t first = issued > S ? issued - S : 0;
+          for (int64_t i = first; i < issued; ++i) {
+            const uint32_t bar = smem_u32(&ctl->full[i % S]);
+            const uint32_t par = (uint32_t)((i / S) & 1);
+            const uint64_t t0 = global_timer_ns();
+            while (!mbar_try_wait(bar, par) && global_timer_ns() - t0 < 200000000ull) {}
+          }
+        }
+      }
+    } else if (warp <= 2) {
+      // ------------------------------------------------------------------ MMA issuers: warp 1 multiplies the
+      // first weight tile of every stage, warp 2 the second, each into its own accumulator columns
+      const uint32_t part = (uint32_t)(warp - 1);
+      uint32_t idesc[4];
+  #pragma unroll
+      for (int k = 0; k < 4; ++k) idesc[k] = make_idesc_block_scaled(kFmtE4M3, kFmtE4M3, kTileM, (uint32_t)B, k, k);
+      const uint32_t term_lo = (uint32_t)(B * kTileK) >> 4;
+      const uint32_t sfa_t = tmem_base + kSfCol0;
       int stage = 0;
-      uint32_t phase = 0;
-      int64_t issued = 0;
+      uint32_t phase = 0, acc = 0, acc_phase = 0, sf_buf = 0, sf_phase = 0;
       bool ok = true;
+      long long t_acc = 0, t_full = 0, t_sf = 0;     // profiling: cycles spent in each wait
+      const long long t_begin = clock64();
       for (int w = blockIdx.x; w < total_work && ok; w += gridDim.x) {
-        const int b = w / p.MT, m = w - b * p.MT;
-        int e = p.sorted_e[b];
-        if (e < 0 || e >= p.E) { p.status[2] = 1; e = 0; }
-        const int r0 = b * B;
-        const uint8_t* sfb = p.asf + (int64_t)b * p.KB * geo.sfb_bytes;
         for (int kb = 0; kb < p.KB; ++kb) {
-          if (!mbar_wait(smem_u32(&ctl->empty[stage]), phase ^ 1, abort_word, 0x100 + stage)) { ok = false; break; }
-          const uint32_t st = stage0 + (uint32_t)stage * geo.stage_bytes;
-          const uint32_t full = smem_u32(&ctl->full[stage]);
-          mbar_expect_tx(full, geo.tx_bytes);
-          tma_load_4d(st, &p.tmW, full, kb * kTileK, m * (GATEUP ? kTileM : 2 * kTileM), 0, e);
-          tma_load_3d(st + geo.a_bytes, &p.tmA, full, kb * kTileK, r0, 0);
-          bulk_load(st + geo.a_bytes + geo.b_bytes, sfb, (uint32_t)geo.sfb_bytes, full);
-          sfb += geo.sfb_bytes;
-          ++issued;
+          // every k-block gets its own accumulator buffer: the epilogue promotes it with the
+          // block's fp32 weight scale while the next k-block is being multiplied
+          const long long c0 = clock64();
+          ok = mbar_wait(smem_u32(&ctl->tmem_empty[2 * acc + part]), acc_phase ^ 1, abort_word, 0x200 + 2 * acc + part);
+          const long long c1 = clock64();
+          ok = ok && mbar_wait(smem_u32(&ctl->full[stage]), phase, abort_word, 0x300 + stage);
+          const long long c2 = clock64();
+          ok = ok && mbar_wait(smem_u32(&ctl->sf_full[sf_buf]), sf_phase, abort_word, 0x500 + sf_buf);
+          t_acc += c1 - c0;
+          t_full += c2 - c1;
+          t_sf += clock64() - c2;
+          if (!ok) break;
+          tc_fence_after_sync();
+          if (lane == 0) {
+            const uint32_t st = stage0 + (uint32_t)stage * geo.stage_bytes;
+            const uint32_t a_lo = desc_lo_sw(st + part * kATileBytes);
+            const uint32_t b_lo = desc_lo_sw(st + geo.a_bytes);
+            const uint32_t sfb_t = sfa_t + 4 + sf_buf * 8;
+            const uint32_t d0 = tmem_base + acc * acc_cols + part * B;
+  #pragma unroll
+            for (int k = 0; k < 4; ++k) {
+  #pragma unroll
+              for (int t = 0; t < kTerms; ++t)
+                umma_mxf8(d0, a_lo + 2 * k, b_lo + t * term_lo + 2 * k, idesc[k], sfa_t, sfb_t + 4 * t, (k | t) != 0);
+            }
+            tc_commit(smem_u32(&ctl->empty[stage]));
+            tc_commit(smem_u32(&ctl->sf_empty[sf_buf]));
+            tc_commit(smem_u32(&ctl->tmem_full[2 * acc + part]));
+          }
+          __syncwarp();
+          if (sf_buf == 1) sf_phase ^= 1;
+          sf_buf ^= 1;
+          if (acc == 1) acc_phase ^= 1;
+          acc ^= 1;
           if (++stage == S) { stage = 0; phase ^= 1; }
         }
       }
-      if (!ok || *abort_word) {
-        const int64_t first = issued > S ? issued - S : 0;
-        for (int64_t i = first; i < issued; ++i) {
-          const uint32_t bar = smem_u32(&ctl->full[i % S]);
-          const uint32_t par = (uint32_t)((i / S) & 1);
-          const uint64_t t0 = global_timer_ns();
-          while (!mbar_try_wait(bar, par) && global_timer_ns() - t0 < 200000000ull) {}
+      if (blockIdx.x == 0 && lane == 0 && part == 0) {   // kilo-cycles: issuer total, waiting for data, for an accumulator, for scales
+        p.status[5] = (int32_t)((clock64() - t_begin) >> 10);
+        p.status[6] = (int32_t)(t_full >> 10);
+        p.status[7] = (int32_t)(t_acc >> 10);
+        p.status[4] = (int32_t)(t_sf >> 10);
+      }
+    } else if (warp == 3) {
+      // ------------------------------------------------------------------ store warp (fused gate-up only):
+      // takes each finished h tile from the staging buffer, re-quantises it into two e4m3 terms with
+      // E8M0 scales per 32 features and writes it out in sorted-row order, while the epilogue warps
+      // are already promoting the next tile
+      if (GATEUP && p.h_out == nullptr) {
+        const uint32_t stg = stage0 + (uint32_t)S * geo.stage_bytes;
+        uint32_t ph = 0;
+        for (int w = blockIdx.x; w < total_work; w += gridDim.x) {
+          const int b = w / p.MT, m = w - b * p.MT;
+          const int r0 = b * B;
+          int nvalid = 0;
+          for (int q = 0; q < B; q += 32) {
+            const uint32_t id = (q + lane < B) ? p.sorted_ids[r0 + q + lane] : 0xFFFFFFFFu;
+            nvalid += __popc(__ballot_sync(0xffffffffu, (int)(id >> 24) < p.topk && (int)(id & 0xFFFFFFu) < p.T));
+          }
+          if (!mbar_wait(smem_u32(&ctl->stg_full), ph, abort_word, 0x900)) break;
+          for (int unit = lane; unit < nvalid * 4; unit += 32) {
+            const int n = unit >> 2, q = unit & 3;
+            float x[32];
+  #pragma unroll
+            for (int v4 = 0; v4 < 4; ++v4) {
+              const uint4 raw = ld_shared_v4(stg + (uint32_t)n * kStagePitch + q * 64 + v4 * 16);
+              const __nv_bfloat162* b2 = reinterpret_cast<const __nv_bfloat162*>(&raw);
+  #pragma unroll
+              for (int t = 0; t < 4; ++t) {
+                const float2 f = __bfloat1622float2(b2[t]);
+                x[v4 * 8 + t * 2] = f.x;
+                x[v4 * 8 + t * 2 + 1] = f.y;
+              }
+            }
+            const int64_t r = (int64_t)r0 + n;
+  #pragma unroll
+            for (int t = 0; t < kTerms; ++t) {
+              uint4 q0, q1;
+              const int ex = quant_block32_e4m3(x, q0, q1);
+              uint4* dst = reinterpret_cast<uint4*>(p.oq + t * p.oq_term_stride + r * p.out_k + m * kTileM + q * 32);
+              dst[0] = q0;
+              dst[1] = q1;
+              p.osf[act_sf_index(b, m, p.out_kb, B, kTerms, 128, t, n, q)] = (uint8_t)ex;
+            }
+          }
+          __syncwarp();
+          if (lane == 0) mbar_arrive(smem_u32(&ctl->stg_empty));
+          ph ^= 1;
         }
       }
     }
-  } else if (warp >= 10) {
+  } else if (warp >= 12) {
+    reg_release<kRegsSf>();
     // ------------------------------------------------------------------ scale-loader warps
     // Weight operand: E8M0 scale 1.0 everywhere, written once.  Activation operand: the two terms'
     // scale chunks of every stage, shared memory -> registers -> this warp's TMEM lane quadrant.
@@ -190,58 +316,10 @@ __global__ void __launch_bounds__(kThreads, 1) moe_grouped_gemm_fp8_kernel(const
         if (++stage == S) { stage = 0; phase ^= 1; }
       }
     }
-  } else if (warp == 1) {
-    // ------------------------------------------------------------------ MMA issuer
-    uint32_t idesc[4];
-#pragma unroll
-    for (int k = 0; k < 4; ++k) idesc[k] = make_idesc_block_scaled(kFmtE4M3, kFmtE4M3, kTileM, (uint32_t)B, k, k);
-    const uint32_t term_lo = (uint32_t)(B * kTileK) >> 4;
-    const uint32_t sfa_t = tmem_base + kSfCol0;
-    int stage = 0;
-    uint32_t phase = 0, acc = 0, acc_phase = 0, sf_buf = 0, sf_phase = 0;
-    bool ok = true;
-    for (int w = blockIdx.x; w < total_work && ok; w += gridDim.x) {
-      for (int kb = 0; kb < p.KB; ++kb) {
-        // every k-block gets its own accumulator buffer: the epilogue promotes it with the
-        // block's fp32 weight scale while the next k-block is being multiplied
-        if (!mbar_wait(smem_u32(&ctl->tmem_empty[acc]), acc_phase ^ 1, abort_word, 0x200 + acc) ||
-            !mbar_wait(smem_u32(&ctl->full[stage]), phase, abort_word, 0x300 + stage) ||
-            !mbar_wait(smem_u32(&ctl->sf_full[sf_buf]), sf_phase, abort_word, 0x500 + sf_buf)) {
-          ok = false;
-          break;
-        }
-        tc_fence_after_sync();
-        if (lane == 0) {
-          const uint32_t st = stage0 + (uint32_t)stage * geo.stage_bytes;
-          const uint32_t a_lo = desc_lo_sw(st);
-          const uint32_t b_lo = desc_lo_sw(st + geo.a_bytes);
-          const uint32_t sfb_t = sfa_t + 4 + sf_buf * 8;
-          const uint32_t d0 = tmem_base + acc * acc_cols;
-#pragma unroll
-          for (int k = 0; k < 4; ++k) {
-#pragma unroll
-            for (int t = 0; t < kTerms; ++t) {
-              const uint32_t accum = (k | t) != 0;
-              umma_mxf8(d0, a_lo + 2 * k, b_lo + t * term_lo + 2 * k, idesc[k], sfa_t, sfb_t + 4 * t, accum);
-              umma_mxf8(d0 + B, a_lo + (kATileBytes >> 4) + 2 * k, b_lo + t * term_lo + 2 * k, idesc[k], sfa_t,
-                        sfb_t + 4 * t, accum);
-            }
-          }
-          tc_commit(smem_u32(&ctl->empty[stage]));
-          tc_commit(smem_u32(&ctl->sf_empty[sf_buf]));
-          tc_commit(smem_u32(&ctl->tmem_full[acc]));
-        }
-        __syncwarp();
-        if (sf_buf == 1) sf_phase ^= 1;
-        sf_buf ^= 1;
-        if (acc == 1) acc_phase ^= 1;
-        acc ^= 1;
-        if (++stage == S) { stage = 0; phase ^= 1; }
-      }
-    }
   } else {
-    // ------------------------------------------------------------------ epilogue warps
-    const int ew = warp - 2;
+    // ------------------------------------------------------------------ epilogue warps (4..11)
+    reg_acquire<kRegsEpilogue>();
+    const int ew = warp - 4;
     const int quad = warp & 3;
     const int half = ew >> 2;                  // the two warps of a quadrant take alternating 16-column groups
     const int tid_e = ew * 32 + lane;
@@ -251,6 +329,10 @@ __global__ void __launch_bounds__(kThreads, 1) moe_grouped_gemm_fp8_kernel(const
     const int row_blocks = (GATEUP ? 2 * p.rows : p.rows) / kTileM;   // weight-scale rows per expert
     uint32_t acc = 0, acc_phase = 0;
     bool alive = true;
+    long long t_wait_epi = 0, t_ld = 0, t_fma = 0;
+    int tile_par = 0;
+    uint32_t stg_phase = 0;
+    const long long t_begin_epi = clock64();
     for (int w = blockIdx.x; w < total_work && alive; w += gridDim.x) {
       const int b = w / p.MT, m = w - b * p.MT;
       const int r0 = b * B;
@@ -270,34 +352,51 @@ __global__ void __launch_bounds__(kThreads, 1) moe_grouped_gemm_fp8_kernel(const
 #pragma unroll
       for (int i = 0; i < kMaxChunks * 16; ++i) { ag[i] = 0.f; au[i] = 0.f; }
 
-      for (int kb = 0; kb < p.KB; ++kb) {
-        const bool ok = mbar_wait(smem_u32(&ctl->tmem_full[acc]), acc_phase, abort_word, 0x400 + acc);
-        if (!epi_all(ok)) { alive = false; break; }
-        tc_fence_after_sync();
-        const float sc0 = s0[kb], sc1 = s1[kb];
-        const uint32_t t0 = tmem_base + ((uint32_t)(quad * 32) << 16) + acc * acc_cols;
+      // the tile's weight-block scales go to shared memory first: a global load inside the k loop would sit
+      // in front of every accumulator hand-back (the arrive has release semantics)
+      float (*ws)[kMaxKB] = ctl->wscale[tile_par];
+      for (int i = tid_e; i < 2 * p.KB; i += 256) ws[i >= p.KB][i >= p.KB ? i - p.KB : i] = (i >= p.KB ? s1 : s0)[i >= p.KB ? i - p.KB : i];
+      tile_par ^= 1;
+      epi_sync();
+      for (int kb = 0; kb < p.KB && alive; ++kb) {
+        const float sc[2] = {ws[0][kb], ws[1][kb]};
 #pragma unroll
-        for (int ci = 0; ci < kMaxChunks; ++ci) {
-          const int c0 = (2 * ci + half) * 16;
-          if (c0 < nvalid) {
-            uint32_t g[16], u[16];
-            tmem_ld_32x32b_x16(t0 + c0, g);
-            tmem_ld_32x32b_x16(t0 + B + c0, u);
-            tmem_ld_wait();
+        for (int part = 0; part < 2; ++part) {
+          const long long te0 = clock64();
+          const bool ok = mbar_wait(smem_u32(&ctl->tmem_full[2 * acc + part]), acc_phase, abort_word, 0x400 + 2 * acc + part);
+          t_wait_epi += clock64() - te0;
+          if (!ok) { alive = false; break; }      // the vote after the k loop takes every warp out together
+          tc_fence_after_sync();
+          const uint32_t t0 = tmem_base + ((uint32_t)(quad * 32) << 16) + acc * acc_cols + part * B;
+          // this warp's 16-column groups of the tile -> registers; the accumulator is handed back to the
+          // MMA warp before the values are scaled and added
+          uint32_t v[kMaxChunks][16];
 #pragma unroll
-            for (int n = 0; n < 16; ++n) {
-              ag[ci * 16 + n] = fmaf(sc0, __uint_as_float(g[n]), ag[ci * 16 + n]);
-              au[ci * 16 + n] = fmaf(sc1, __uint_as_float(u[n]), au[ci * 16 + n]);
+          for (int ci = 0; ci < kMaxChunks; ++ci)
+            if ((2 * ci + half) * 16 < nvalid) tmem_ld_32x32b_x16(t0 + (2 * ci + half) * 16, v[ci]);
+          tmem_ld_wait();
+          tc_fence_before_sync();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(smem_u32(&ctl->tmem_empty[2 * acc + part]));
+#pragma unroll
+          for (int ci = 0; ci < kMaxChunks; ++ci) {
+            if ((2 * ci + half) * 16 < nvalid) {
+#pragma unroll
+              for (int n = 0; n < 16; ++n) {
+                if (part == 0) ag[ci * 16 + n] = fmaf(sc[0], __uint_as_float(v[ci][n]), ag[ci * 16 + n]);
+                else au[ci * 16 + n] = fmaf(sc[1], __uint_as_float(v[ci][n]), au[ci * 16 + n]);
+              }
             }
           }
         }
-        tc_fence_before_sync();
-        __syncwarp();
-        if (lane == 0) mbar_arrive(smem_u32(&ctl->tmem_empty[acc]));
         if (acc == 1) acc_phase ^= 1;
         acc ^= 1;
       }
-      if (!alive) break;
+      // one vote per tile: a warp whose wait gave up has set the shared abort word, so the others'
+      // waits return at once and every epilogue warp leaves before the next named barrier
+      if (fused && alive) alive = mbar_wait(smem_u32(&ctl->stg_empty), stg_phase ^ 1, abort_word, 0x800);
+      if (!epi_all(alive)) break;
+      const long long tt0 = clock64();
 
       // ---- tile finished: activation / stores from the register accumulators
       const bool j_ok = j < p.rows;
@@ -341,36 +440,18 @@ __global__ void __launch_bounds__(kThreads, 1) moe_grouped_gemm_fp8_kernel(const
           }
         }
       }
-      if (fused) {
-        epi_sync();
-        // h tile -> two e4m3 terms with E8M0 scales per 32 features, sorted-row order
-        for (int unit = tid_e; unit < nvalid * 4; unit += 256) {
-          const int n = unit >> 2, q = unit & 3;
-          float x[32];
-#pragma unroll
-          for (int v4 = 0; v4 < 4; ++v4) {
-            const uint4 raw = ld_shared_v4(stg + (uint32_t)n * kStagePitch + q * 64 + v4 * 16);
-            const __nv_bfloat162* b2 = reinterpret_cast<const __nv_bfloat162*>(&raw);
-#pragma unroll
-            for (int t = 0; t < 4; ++t) {
-              const float2 f = __bfloat1622float2(b2[t]);
-              x[v4 * 8 + t * 2] = f.x;
-              x[v4 * 8 + t * 2 + 1] = f.y;
-            }
-          }
-          const int64_t r = (int64_t)r0 + n;
-#pragma unroll
-          for (int t = 0; t < kTerms; ++t) {
-            uint4 q0, q1;
-            const int ex = quant_block32_e4m3(x, q0, q1);
-            uint4* dst = reinterpret_cast<uint4*>(p.oq + t * p.oq_term_stride + r * p.out_k + m * kTileM + q * 32);
-            dst[0] = q0;
-            dst[1] = q1;
-            p.osf[act_sf_index(b, m, p.out_kb, B, kTerms, 128, t, n, q)] = (uint8_t)ex;
-          }
-        }
-        epi_sync();     // the staging tile may be overwritten by the next tile
+      if (fused) {          // hand the staged tile to the store warp
+        __syncwarp();
+        if (lane == 0) mbar_arrive(smem_u32(&ctl->stg_full));
+        stg_phase ^= 1;
       }
+      t_fma += clock64() - tt0;
+    }
+    if (blockIdx.x == 0 && tid_e == 0) {     // kilo-cycles: epilogue total, waiting for an accumulator
+      p.status[8] = (int32_t)((clock64() - t_begin_epi) >> 10);
+      p.status[9] = (int32_t)(t_wait_epi >> 10);
+      p.status[10] = (int32_t)(t_ld >> 10);
+      p.status[11] = (int32_t)(t_fma >> 10);
     }
   }
 
@@ -393,6 +474,7 @@ int launch_grouped_gemm_fp8(const GemmArgs& a, cudaStream_t st) {
                  a.N);
   B200_CHECK_ARG(a.Kd % 128 == 0 && a.rows % 128 == 0 && a.E > 0, "fp8 grouped gemm: K and rows must be multiples of 128");
   B200_CHECK_ARG(a.max_rows % a.N == 0, "fp8 grouped gemm: max_rows %% B != 0");
+  B200_CHECK_ARG(a.Kd / kTileK <= kMaxKB, "fp8 grouped gemm: K=%d exceeds %d", a.Kd, kMaxKB * kTileK);
   B200_CHECK_ARG(((uintptr_t)a.w_data & 15) == 0 && ((uintptr_t)a.a_q & 15) == 0 && ((uintptr_t)a.w_scale & 3) == 0,
                  "fp8 grouped gemm: operand tensors must be 16-byte aligned");
   Params p;
@@ -427,10 +509,10 @@ int launch_grouped_gemm_fp8(const GemmArgs& a, cudaStream_t st) {
   }
   const StageGeom geo = stage_geom(a.N);
   const int staging = (a.gateup && a.h_out == nullptr) ? a.N * kStagePitch : 0;
-  int stages = std::min((kSmemLimit - 2048 - staging) / geo.stage_bytes, kMaxStages);
+  int stages = std::min((kSmemLimit - 1024 - kCtlBytes - staging) / geo.stage_bytes, kMaxStages);
   B200_CHECK_ARG(stages >= 2, "fp8 grouped gemm: tile does not fit shared memory");
   p.stages = stages;
-  const size_t smem = 2048 + (size_t)stages * geo.stage_bytes + staging;
+  const size_t smem = 1024 + kCtlBytes + (size_t)stages * geo.stage_bytes + staging;
   const int64_t max_work = (a.max_rows / a.N) * p.MT;
   const int grid = (int)std::min<int64_t>(device_sm_count(), std::max<int64_t>(max_work, 1));
   static bool attr[2][64] = {};

@@ -32,6 +32,14 @@ __device__ __forceinline__ void fence_mbar_init() {
 __device__ __forceinline__ void grid_dep_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 __device__ __forceinline__ void grid_dep_launch() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 
+// Register reallocation between the warpgroups (4 consecutive warps) of a CTA.  Every warp of a
+// warpgroup must execute the same call.  An increase blocks until other warpgroups have released
+// enough registers, so the releasing calls are made unconditionally before any role-specific exit.
+template <int N>
+__device__ __forceinline__ void reg_release() { asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(N)); }
+template <int N>
+__device__ __forceinline__ void reg_acquire() { asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(N)); }
+
 __device__ __forceinline__ void fence_proxy_async_smem() {
   asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
 }
@@ -54,6 +62,20 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
   return ok != 0;
 }
 
+// try_wait with a suspend-time hint: the thread may stay suspended in hardware for up to `hint_ns`
+// (it resumes as soon as the phase completes), so a waiting warp does not compete for issue slots.
+__device__ __forceinline__ bool mbar_try_wait_hint(uint32_t bar, uint32_t parity, uint32_t hint_ns) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity), "r"(hint_ns)
+      : "memory");
+  return ok != 0;
+}
+
 // Bounded wait.  `abort_word` lives in shared memory and is shared by all roles of the CTA:
 // once any wait gives up (about two seconds) every other wait returns false promptly.
 constexpr uint64_t kWaitLimitNs = 2000000000ull;
@@ -63,7 +85,7 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
   if (mbar_try_wait(bar, parity)) return true;
   uint64_t t0 = global_timer_ns();
   uint32_t spins = 0;
-  while (!mbar_try_wait(bar, parity)) {
+  while (!mbar_try_wait_hint(bar, parity, 2000u)) {
     if ((++spins & 63u) == 0) {
       if (*abort_word) return false;
       if (global_timer_ns() - t0 > kWaitLimitNs) {

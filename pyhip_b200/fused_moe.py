@@ -13,6 +13,7 @@ Work is enqueued on ``torch.cuda.current_stream()`` and never synchronises.
 from __future__ import annotations
 
 import ctypes
+import math
 import enum
 import weakref
 
@@ -48,7 +49,12 @@ def _stream():
 def pick_block(T: int, K: int, E: int) -> int:
     """Rows per sorted block (= token tile of the GEMMs).  Small when few tokens reach each
     expert so the weight-streaming regime wastes no tensor work on padding; the reference makes
-    the same decode/prefill split on T*K/E (src/contrib/fused_moe.py:285-300,358-362)."""
+    the same decode/prefill split on T*K/E (src/contrib/fused_moe.py:285-300,358-362).
+
+    In the compute-bound regime the tile is chosen by a cost model: an expert that receives n
+    rows costs ceil(n/B) MMA column tiles, each reading a 128-row weight tile plus B token rows
+    from shared memory, so cost(B) = E[ceil(n/B)] * (128 + B) with n ~ Normal(mu, mu(1-1/E)) under
+    uniform routing.  96 is the largest tile whose two accumulator buffers fit tensor memory."""
     per_expert = (T * K) / max(E, 1)
     if per_expert <= 4:
         return 16
@@ -56,7 +62,19 @@ def pick_block(T: int, K: int, E: int) -> int:
         return 32
     if per_expert <= 48:
         return 64
-    return 96          # largest tile whose two accumulator buffers fit tensor memory
+    sigma = math.sqrt(max(per_expert * (1.0 - 1.0 / max(E, 1)), 1e-6))
+    lo, hi = max(1, int(per_expert - 4 * sigma)), int(per_expert + 4 * sigma) + 1
+    best, best_cost = 96, None
+    for B in (96, 80, 64, 48):
+        wsum = cost = 0.0
+        for n in range(lo, hi + 1):
+            wgt = math.exp(-0.5 * ((n - per_expert) / sigma) ** 2)
+            wsum += wgt
+            cost += wgt * (-(-n // B)) * (128 + B)
+        cost /= wsum
+        if best_cost is None or cost < best_cost * 0.98:      # prefer the larger tile on a near tie
+            best, best_cost = B, cost
+    return best
 
 
 class PreparedWeights:

@@ -61,7 +61,7 @@ def test_e4m3_rows_match_oracle_bit_for_bit():
             assert np.array_equal(sf[:, r], ee[:, tok[r]]), r
 
 
-@pytest.mark.parametrize("T,H,I,E,K,B", [(32, 256, 128, 4, 2, 32), (150, 256, 384, 4, 2, 64), (300, 384, 128, 4, 2, 96),
+@pytest.mark.parametrize("T,H,I,E,K,B", [(32, 256, 128, 4, 2, 32), (150, 256, 384, 4, 2, 64), (300, 384, 128, 4, 2, 96), (260, 256, 256, 4, 2, 80),
                                          (7, 512, 256, 8, 2, 16)])
 def test_stage_chain_matches_layer_oracle(T, H, I, E, K, B):
     x = synth.make_hidden(T, H, T)

@@ -153,7 +153,7 @@ def test_ragged_token_counts(T):
     _assert_close(_run_layer(x, tw, ids, w), ref, f"T={T}")
 
 
-@pytest.mark.parametrize("B", [16, 32, 48, 64, 96, 128])
+@pytest.mark.parametrize("B", [16, 32, 48, 64, 80, 96, 112, 128])
 def test_block_sizes_and_skew(B):
     T, H, I, E, K = 400, 256, 256, 8, 2
     x, tw, ids, w = _case(T, H, I, E, K, routing="zipf", seed=9)
