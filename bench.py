@@ -72,7 +72,7 @@ def fp4_dense_rate(dev, n=256, count=40000):
     import torch
     from pyhip_b200 import _lib
     sms = torch.cuda.get_device_properties(dev).multi_processor_count
-    cfg = torch.tensor([0, n, count, 1], dtype=torch.int32, device=dev)
+    cfg = torch.tensor([0, n, count, 1, 0, 0, 0, 0], dtype=torch.int32, device=dev)
     out = torch.zeros(sms * 3, dtype=torch.int32, device=dev)
     st = ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
 

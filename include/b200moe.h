@@ -157,7 +157,8 @@ int b200moe_forward_static(const b200moe_shape* shape, const void* x_bf16, const
  *   which = 2: 512 bytes `in` -> shared -> tcgen05.cp 32x128b.warpx4 -> tcgen05.ld;
  *              `out` receives u32 [128 lanes][4 columns].
  *   which = 3: tensor-core issue-rate measurement (kind::mxf4, 128 x N x 64); `in` = i32 {scale copies per
- *              four MMAs, N, count, accumulators}; `out` = u32 {issue cycles, cycles until complete, status}.
+ *              four MMAs, N, count, accumulators, extra commit every so many groups of four MMAs (0 = none),
+ *              issue mode (0 lane test, 1 elected lane, 2 whole warp with the election inside each MMA)}; `out` = u32 {issue cycles, cycles until complete, status}.
  *   which = 4: the same measurement on one CTA per SM at once (whole-chip dense FP4 rate when timed by
  *              the caller with stream events); `out` = u32 [SM count][3].
  * out[last] status word: 0 = ok, non-zero = a bounded wait ran out. */

@@ -208,7 +208,8 @@ __global__ void __launch_bounds__(kThreads, 1) moe_grouped_gemm_fp8_kernel(const
           t_sf += clock64() - c2;
           if (!ok) break;
           tc_fence_after_sync();
-          if (lane == 0) {
+          __syncwarp();
+          if (elect_one()) {       // one issuing lane; descriptors stay in uniform registers
             const uint32_t st = stage0 + (uint32_t)stage * geo.stage_bytes;
             const uint32_t a_lo = desc_lo_sw(st + part * kATileBytes);
             const uint32_t b_lo = desc_lo_sw(st + geo.a_bytes);

@@ -76,6 +76,7 @@ struct GemmParams {
   int64_t max_rows;
   int64_t oq_term_stride;
   int B, NT, rows, KB, MT, E, topk, T, stages, out_kp, out_kb, out_ts, activation;
+  int k_tail_steps;    // 64-wide k-steps of the last stage that hold data (the rest of it is zero padding)
   float swiglu_limit;
 };
 
@@ -238,7 +239,8 @@ moe_grouped_gemm_kernel(const __grid_constant__ GemmParams p) {
         if (!mbar_wait(smem_u32(&ctl->sf_full[sf_buf]), sf_phase, abort_word, 0x500 + sf_buf)) { ok = false; break; }
         t_wait_full += clock64() - tf0;
         tc_fence_after_sync();
-        if (lane == 0) {
+        __syncwarp();
+        if (elect_one()) {       // one issuing lane; descriptors stay in uniform registers
           const uint32_t st = stage0 + (uint32_t)stage * geo.stage_bytes;
           const uint32_t a_lo = desc_lo_sw(st + part * kATileBytes);
           const uint32_t b_lo = desc_lo_sw(st + geo.a_bytes);
@@ -247,11 +249,12 @@ moe_grouped_gemm_kernel(const __grid_constant__ GemmParams p) {
           const uint32_t sfa_t = tmem_base + kSfCol0 + sf_buf * 48 + 4 * part;
           const uint32_t sfb_t = tmem_base + kSfCol0 + sf_buf * 48 + 16;
           const uint32_t first = kb != 0;
+          const int nsteps = (kb == p.KB - 1) ? p.k_tail_steps : 2 * kSub;   // skip k-steps that are all padding
           if (merged) {
 #pragma unroll
             for (int s = 0; s < 2 * kSub; ++s) {
               const uint32_t sa = sfa_t + 8 * (s >> 1), sb = sfb_t + 16 * (s >> 1);
-              umma_mxf4(d0, a_lo + 2 * s, b_lo + 2 * s, idesc[s & 1], sa, sb, s == 0 ? first : 1u);
+              if (s < nsteps) umma_mxf4(d0, a_lo + 2 * s, b_lo + 2 * s, idesc[s & 1], sa, sb, s == 0 ? first : 1u);
             }
           } else {
 #pragma unroll
@@ -259,7 +262,7 @@ moe_grouped_gemm_kernel(const __grid_constant__ GemmParams p) {
               const uint32_t sa = sfa_t + 8 * (s >> 1), sb = sfb_t + 16 * (s >> 1);
 #pragma unroll
               for (int t = 0; t < kMaxTerms; ++t) {
-                if (t < NT) {
+                if (t < NT && s < nsteps) {
                   const uint32_t accum = (s == 0 && t == 0) ? first : 1u;
                   umma_mxf4(d0, a_lo + 2 * s, b_lo + t * term_lo + 2 * s, idesc[s & 1], sa, sb + 4 * t, accum);
                 }
@@ -541,6 +544,7 @@ int launch_grouped_gemm(const GemmArgs& a, cudaStream_t st) {
   memset(&p, 0, sizeof(p));
   p.B = a.N; p.NT = a.NT; p.rows = a.rows; p.KB = KP / kTileK;
   p.MT = a.gateup ? (a.rows + kTileM - 1) / kTileM : (a.rows + 2 * kTileM - 1) / (2 * kTileM);
+  p.k_tail_steps = (a.Kd - (p.KB - 1) * kTileK + 63) / 64;
   p.E = a.E; p.topk = a.topk; p.T = a.T; p.activation = a.activation;
   p.swiglu_limit = a.swiglu_limit; p.max_rows = a.max_rows;
   p.w_scale = (const uint8_t*)a.w_scale; p.asf = (const uint8_t*)a.asf;
@@ -669,14 +673,63 @@ __global__ void __launch_bounds__(128, 1) probe_utccp_kernel(const uint32_t* in,
   if (warp == 0) tmem_dealloc(tbase, 32);
 }
 
+template <int MODE>
+__device__ __forceinline__ void probe_issue(const int32_t* cfg, uint32_t* out, uint32_t tbase, uint32_t a, uint32_t bar,
+                                            uint32_t bar2, volatile uint32_t* abort_word) {
+  const int N = cfg[1], count = cfg[2], nacc = cfg[3], commit_every = cfg[4];
+  const bool one = (MODE != 2) || (threadIdx.x & 31) == 0;    // the lane that does the bookkeeping
+  const uint32_t b = a + 16384, sf = b + 32768;
+  if (one) {
+    utccp_sf(tbase + 448, desc_lo_sf(sf));
+    utccp_sf(tbase + 456, desc_lo_sf(sf + 512));
+    utccp_sf(tbase + 460, desc_lo_sf(sf + 512));
+  }
+  uint32_t idesc[2];
+  for (int s = 0; s < 2; ++s) idesc[s] = make_idesc_block_scaled(kFmtE2M1_mxf4, kFmtE2M1_mxf4, 128, N, 2 * s, 2 * s);
+  const uint32_t a_lo = desc_lo_sw(a), b_lo = desc_lo_sw(b);
+  const uint32_t d1 = tbase + (nacc > 1 ? N : 0);
+  const int ncp = cfg[0];      // scale copies (tcgen05.cp) issued before every group of four MMAs
+  const uint32_t sf_lo = desc_lo_sf(sf);
+  int since_commit = 0;
+  const long long t0 = clock64();
+  for (int i = 0; i < count; i += 4) {
+    if (one)
+      for (int c = 0; c < ncp; ++c) utccp_sf(tbase + 448 + 4 * (c & 7) + ((i >> 2) & 1) * 32, sf_lo + ((c & 1) << 5));
+    if (MODE == 2) {
+      umma_mxf4_warp(tbase, a_lo, b_lo, idesc[0], tbase + 448, tbase + 456, 1);
+      umma_mxf4_warp(d1, a_lo, b_lo, idesc[0], tbase + 448, tbase + 456, 1);
+      umma_mxf4_warp(tbase, a_lo + 2, b_lo + 2, idesc[1], tbase + 448, tbase + 456, 1);
+      umma_mxf4_warp(d1, a_lo + 2, b_lo + 2, idesc[1], tbase + 448, tbase + 456, 1);
+    } else {
+      umma_mxf4(tbase, a_lo, b_lo, idesc[0], tbase + 448, tbase + 456, 1);
+      umma_mxf4(d1, a_lo, b_lo, idesc[0], tbase + 448, tbase + 456, 1);
+      umma_mxf4(tbase, a_lo + 2, b_lo + 2, idesc[1], tbase + 448, tbase + 456, 1);
+      umma_mxf4(d1, a_lo + 2, b_lo + 2, idesc[1], tbase + 448, tbase + 456, 1);
+    }
+    if (commit_every > 0 && ++since_commit == commit_every) {
+      since_commit = 0;
+      if (one) tc_commit(bar2);
+    }
+  }
+  const long long t1 = clock64();
+  if (one) tc_commit(bar);
+  mbar_wait(bar, 0, abort_word, 3);
+  const long long t2 = clock64();
+  if (one) {
+    uint32_t* o = out + 3 * blockIdx.x;
+    o[0] = (uint32_t)(t1 - t0);
+    o[1] = (uint32_t)(t2 - t0);
+    o[2] = *abort_word;
+  }
+}
+
 // Issue-rate probe: `count` MMAs of shape 128 x N x 64 alternating between `nacc` accumulators,
 // one commit, one bounded wait; reports clock cycles.  The results are never read back.
 __global__ void __launch_bounds__(128, 1) probe_mma_rate_kernel(const int32_t* cfg, uint32_t* out) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-  __shared__ uint64_t bar;
+  __shared__ uint64_t bar, bar2;
   __shared__ uint32_t tmem_slot, abort_word;
-  const int N = cfg[1], count = cfg[2], nacc = cfg[3];
   const int warp = threadIdx.x >> 5;
   // pseudo-random FP4 operands (realistic switching activity) and unit scales
   for (int i = threadIdx.x; i < (16384 + 32768 + 1024) / 4; i += blockDim.x)
@@ -684,6 +737,7 @@ __global__ void __launch_bounds__(128, 1) probe_mma_rate_kernel(const int32_t* c
   if (threadIdx.x == 0) {
     abort_word = 0;
     mbar_init(smem_u32(&bar), 1);
+    mbar_init(smem_u32(&bar2), 1);
     fence_mbar_init();
   }
   fence_proxy_async_smem();
@@ -695,33 +749,16 @@ __global__ void __launch_bounds__(128, 1) probe_mma_rate_kernel(const int32_t* c
   __syncthreads();
   tc_fence_after_sync();
   const uint32_t tbase = tmem_slot;
-  if (threadIdx.x == 0) {
-    const uint32_t a = smem_u32(smem), b = a + 16384, sf = b + 32768;
-    utccp_sf(tbase + 448, desc_lo_sf(sf));
-    utccp_sf(tbase + 456, desc_lo_sf(sf + 512));
-    utccp_sf(tbase + 460, desc_lo_sf(sf + 512));
-    uint32_t idesc[2];
-    for (int s = 0; s < 2; ++s) idesc[s] = make_idesc_block_scaled(kFmtE2M1_mxf4, kFmtE2M1_mxf4, 128, N, 2 * s, 2 * s);
-    const uint32_t a_lo = desc_lo_sw(a), b_lo = desc_lo_sw(b);
-    const uint32_t d1 = tbase + (nacc > 1 ? N : 0);
-    const int ncp = cfg[0];      // scale copies (tcgen05.cp) issued before every group of four MMAs
-    const uint32_t sf_lo = desc_lo_sf(sf);
-    const long long t0 = clock64();
-    for (int i = 0; i < count; i += 4) {
-      for (int c = 0; c < ncp; ++c) utccp_sf(tbase + 448 + 4 * (c & 7) + ((i >> 2) & 1) * 32, sf_lo + ((c & 1) << 5));
-      umma_mxf4(tbase, a_lo, b_lo, idesc[0], tbase + 448, tbase + 456, 1);
-      umma_mxf4(d1, a_lo, b_lo, idesc[0], tbase + 448, tbase + 456, 1);
-      umma_mxf4(tbase, a_lo + 2, b_lo + 2, idesc[1], tbase + 448, tbase + 456, 1);
-      umma_mxf4(d1, a_lo + 2, b_lo + 2, idesc[1], tbase + 448, tbase + 456, 1);
-    }
-    const long long t1 = clock64();
-    tc_commit(smem_u32(&bar));
-    mbar_wait(smem_u32(&bar), 0, &abort_word, 3);
-    const long long t2 = clock64();
-    uint32_t* o = out + 3 * blockIdx.x;
-    o[0] = (uint32_t)(t1 - t0);
-    o[1] = (uint32_t)(t2 - t0);
-    o[2] = abort_word;
+  const uint32_t sbase = smem_u32(smem);
+  // three ways to confine the issue to one thread: a lane test, an elected lane around the loop, or the whole
+  // warp running the loop with the election inside each MMA
+  const int mode = cfg[5];
+  if (mode == 0) {
+    if (threadIdx.x == 0) probe_issue<0>(cfg, out, tbase, sbase, smem_u32(&bar), smem_u32(&bar2), &abort_word);
+  } else if (mode == 1) {
+    if (warp == 0 && elect_one()) probe_issue<1>(cfg, out, tbase, sbase, smem_u32(&bar), smem_u32(&bar2), &abort_word);
+  } else {
+    if (warp == 0) probe_issue<2>(cfg, out, tbase, sbase, smem_u32(&bar), smem_u32(&bar2), &abort_word);
   }
   tc_fence_before_sync();
   __syncthreads();

@@ -40,6 +40,19 @@ __device__ __forceinline__ void reg_release() { asm volatile("setmaxnreg.dec.syn
 template <int N>
 __device__ __forceinline__ void reg_acquire() { asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(N)); }
 
+// True in exactly one lane of a fully converged warp.  Unlike a test of the lane index, the compiler knows
+// that the guarded region has a single active thread and keeps warp-uniform values (descriptors, addresses)
+// in uniform registers for the tcgen05 instructions issued there.
+__device__ __forceinline__ bool elect_one() {
+  uint32_t pred;
+  asm volatile(
+      "{\n\t.reg .pred P;\n\t"
+      "elect.sync _|P, 0xffffffff;\n\t"
+      "selp.u32 %0, 1, 0, P;\n\t}"
+      : "=r"(pred));
+  return pred != 0;
+}
+
 __device__ __forceinline__ void fence_proxy_async_smem() {
   asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
 }
