@@ -39,6 +39,8 @@ def parse():
     ap.add_argument("--tokens", type=int, default=0, help="tokens per GPU per step (0 = the workload's own)")
     ap.add_argument("--workload", default="gptoss_decode", choices=["gptoss_decode", "gptoss_prefill", "dsv3_ep", "mixtral_skew"],
                     help="gptoss_*: MXFP4 weights (BASELINE configs 1, 2); dsv3_ep: FP8 128x128 weights (config 3)")
+    ap.add_argument("--ep-chunks", type=int, default=0,
+                    help="N>1: slices of the pipelined dispatch/combine exchange (0 = chosen from the shape)")
     ap.add_argument("--sweep", action="store_true", help="also time T in {1,8,32,64,256,8192} (extra keys)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-graph", action="store_true", help="time direct launches instead of CUDA-graph replays")
@@ -386,7 +388,8 @@ def run_b200(args):
     from pyhip_b200 import ep
     E_local = E // world
     w_full = make_w(E_local, H, I, seed=rank, device=dev, distinct=min(distinct, E_local))
-    layer = ep.ExpertParallelMoE(w_full[0], w_full[1], w_full[2], w_full[3], E, rank, world, quant_type=qt)
+    layer = ep.ExpertParallelMoE(w_full[0], w_full[1], w_full[2], w_full[3], E, rank, world, quant_type=qt,
+                                 dispatch_chunks=args.ep_chunks or None)
     x = synth.make_hidden(T, H, rank)
     tw, ids = synth.make_routing(T, E, K, shape.routing, rank, skew_seed=0)
     xd, twd, idsd = x.to(dev), tw.to(dev), ids.to(dev)
@@ -415,6 +418,14 @@ def run_b200(args):
     torch.cuda.synchronize()
     busy = statistics.median(a.elapsed_time(b) for a, b in layer.busy_events) if layer.busy_events else 0.0
     layer.busy_events = None
+    # ---- where one step's time goes on rank 0 (marks inside the dispatch/combine call), one extra step
+    phases = None
+    if T > layer.small_batch:
+        layer.trace = []
+        step()
+        torch.cuda.synchronize()
+        tr, layer.trace = layer.trace, None
+        phases = [(tr[i + 1][0], round(tr[i][1].elapsed_time(tr[i + 1][1]), 3)) for i in range(len(tr) - 1)]
     busy_t = torch.tensor([busy], device=dev)
     busy_all = [torch.zeros_like(busy_t) for _ in range(world)]
     dist.all_gather(busy_all, busy_t)
@@ -458,7 +469,8 @@ def run_b200(args):
                         "h2d_bytes_per_step": x.numel() * 2 + tw.numel() * 4 + ids.numel() * 4,
                         "d2h_bytes_per_step": T * H * 2},
                 "gpu_launches": launches_per_step * args.steps, "roofline": roofline, "cpu_baseline": None,
-                "local_expert_ms_per_rank": [round(float(b.item()), 4) for b in busy_all]}
+                "local_expert_ms_per_rank": [round(float(b.item()), 4) for b in busy_all],
+                "rank0_phase_ms": phases}
         print(json.dumps(line), flush=True)
     dist.destroy_process_group()
 

@@ -151,6 +151,14 @@ int b200moe_forward_static(const b200moe_shape* shape, const void* x_bf16, const
                            const void* w1_scale_prepared, const void* w2_q, const void* w2_scale_prepared,
                            void* y_bf16, void* stream);
 
+/* Expert-parallel combine.  No counterpart in the reference, which has no dispatch/combine (expert
+ * parallelism exists there only as the expert_mask input convention, src/contrib/fused_moe.py:134,210-212).
+ * y[t,:] = sum over s in [0, slots) of rows[pos[t*slots + s], :] for pos >= 0, accumulated in fp32 in
+ * ascending slot order (slot = owner rank = ascending expert range) and rounded to bf16 once.
+ *   rows: bf16 [n, H] partial outputs returned by the owner ranks;  pos: i32 [T, slots], -1 = no row. */
+int b200moe_gather_sum(const void* rows_bf16, const int32_t* pos, int32_t T, int32_t slots, int32_t H,
+                       void* y_bf16, void* stream);
+
 /* Hardware known-answer probes used by the GPU test-suite (tiny, single CTA, bounded waits).
  *   which = 1: TMA load of one 128-row x 256-element packed-FP4 tile (128-byte swizzle) from `in`
  *              (16384 bytes) -> `out` receives the 16384-byte shared-memory image.

@@ -252,6 +252,15 @@ int b200moe_forward(const b200moe_shape* s, const b200moe_workspace* ws, void* w
   return b200moe_combine(s, ws, workspace, topk_weight, y_bf16, stream);
 }
 
+int b200moe_gather_sum(const void* rows_bf16, const int32_t* pos, int32_t T, int32_t slots, int32_t H, void* y_bf16,
+                       void* stream) {
+  B200_CHECK_ARG(T >= 0 && slots >= 1 && H > 0, "gather_sum: bad sizes T=%d slots=%d H=%d", T, slots, H);
+  if (T == 0) return 0;
+  B200_CHECK_ARG(rows_bf16 && pos && y_bf16, "gather_sum: NULL pointer");
+  B200_CHECK_ARG(((uintptr_t)rows_bf16 & 15) == 0 && ((uintptr_t)y_bf16 & 15) == 0, "gather_sum: 16-byte alignment");
+  return launch_gather_sum(rows_bf16, pos, y_bf16, T, slots, H, (cudaStream_t)stream);
+}
+
 int b200moe_debug_probe(int which, const void* in, void* out, void* stream) {
   B200_CHECK_ARG(in && out, "debug_probe: NULL pointer");
   return run_debug_probe(which, in, out, (cudaStream_t)stream);

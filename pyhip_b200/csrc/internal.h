@@ -57,6 +57,7 @@ int launch_sort_align(const int32_t* ids, const float* w, int T, int K, int E, i
                       int32_t* loc, cudaStream_t st);
 int launch_quant_rows(const void* src, int src_mode, const uint32_t* sorted_ids, const int32_t* num_valid,
                       int T, int K, int Kd, int B, int NT, int64_t max_rows, void* q, void* sf, cudaStream_t st);
+int launch_gather_sum(const void* rows, const int32_t* pos, void* y, int T, int S, int H, cudaStream_t st);
 int launch_combine(const void* out2, const int32_t* loc, const float* topk_w, void* y, int T, int K, int H,
                    cudaStream_t st);
 int launch_repack_scales(const void* w_s, void* out, int E, bool gateup, int rows, int Kd, cudaStream_t st);

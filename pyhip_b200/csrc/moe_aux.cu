@@ -337,6 +337,50 @@ int launch_combine(const void* out2, const int32_t* loc, const float* topk_w, vo
 }
 
 // =====================================================================================
+// expert-parallel combine: y[t,:] = sum over the slots s of rows[pos[t,s],:] (pos < 0: no row), added
+// in fp32 in ascending slot order (slot = owner rank, i.e. ascending expert range) and rounded once.
+// =====================================================================================
+__global__ void __launch_bounds__(256)
+gather_sum_kernel(const __nv_bfloat16* __restrict__ rows, const int32_t* __restrict__ pos,
+                  __nv_bfloat16* __restrict__ y, int T, int S, int H) {
+  const int vec_per_row = H / 8;
+  grid_dep_launch();
+  grid_dep_wait();
+  for (int64_t g = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; g < (int64_t)T * vec_per_row;
+       g += (int64_t)gridDim.x * blockDim.x) {
+    const int t = (int)(g / vec_per_row), c = (int)(g % vec_per_row) * 8;
+    float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+    for (int s = 0; s < S; ++s) {
+      const int p = pos[(int64_t)t * S + s];
+      if (p < 0) continue;
+      const uint4 raw = *reinterpret_cast<const uint4*>(rows + (int64_t)p * H + c);
+      const __nv_bfloat162* b2 = reinterpret_cast<const __nv_bfloat162*>(&raw);
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const float2 f = __bfloat1622float2(b2[i]);
+        acc[2 * i] += f.x;
+        acc[2 * i + 1] += f.y;
+      }
+    }
+    uint4 out;
+    __nv_bfloat162* o2 = reinterpret_cast<__nv_bfloat162*>(&out);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) o2[i] = __floats2bfloat162_rn(acc[2 * i], acc[2 * i + 1]);
+    *reinterpret_cast<uint4*>(y + (int64_t)t * H + c) = out;
+  }
+}
+
+int launch_gather_sum(const void* rows, const int32_t* pos, void* y, int T, int S, int H, cudaStream_t st) {
+  B200_CHECK_ARG(H % 8 == 0 && S >= 1, "gather_sum: H %% 8 != 0 or no slots");
+  if (T == 0) return 0;
+  int64_t work = (int64_t)T * (H / 8);
+  int blocks = (int)std::min<int64_t>((work + 255) / 256, 148 * 16);
+  B200_CHECK_CUDA(launch_chained(gather_sum_kernel, dim3(blocks), dim3(256), 0, st, (const __nv_bfloat16*)rows, pos,
+                                 (__nv_bfloat16*)y, T, S, H));
+  return 0;
+}
+
+// =====================================================================================
 // weight-scale repack: [E, R, Kd/32] bytes -> [E, MT, KB, 2, 512] chunks in tensor-memory order.
 // A chunk = 128 rows x 4 scales.  The two chunks of a group are the tiles one pipeline stage
 // carries: gate rows [mt*128, +128) and up rows I + [mt*128, +128) of w1 (R = 2I), or rows

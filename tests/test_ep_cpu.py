@@ -19,7 +19,7 @@ def _free_port():
         return s.getsockname()[1]
 
 
-def _worker(rank, world, port, fail_rank, q, small_batch=0):
+def _worker(rank, world, port, fail_rank, q, small_batch=0, chunks=1):
     os.environ["MASTER_ADDR"] = "127.0.0.1"
     os.environ["MASTER_PORT"] = str(port)
     torch.set_num_threads(1)
@@ -38,7 +38,7 @@ def _worker(rank, world, port, fail_rank, q, small_batch=0):
             return orc.torch_moe_oracle(xr, w1[lo:lo + El], w2[lo:lo + El], twr, ids_local)
 
         layer = ep.ExpertParallelMoE(None, None, None, None, E, rank, world, local_fn=local_fn,
-                                     small_batch=small_batch)
+                                     small_batch=small_batch, dispatch_chunks=chunks)
         if fail_rank == rank:
             q.put((rank, "skipped"))
             return
@@ -56,11 +56,11 @@ def _worker(rank, world, port, fail_rank, q, small_batch=0):
             pass
 
 
-def _spawn(world, fail_rank=None, small_batch=0):
+def _spawn(world, fail_rank=None, small_batch=0, chunks=1):
     ctx = mp.get_context("spawn")
     q = ctx.Queue()
     port = _free_port()
-    procs = [ctx.Process(target=_worker, args=(r, world, port, fail_rank, q, small_batch)) for r in range(world)]
+    procs = [ctx.Process(target=_worker, args=(r, world, port, fail_rank, q, small_batch, chunks)) for r in range(world)]
     for p in procs:
         p.start()
     res = dict(q.get(timeout=120) for _ in range(world))
@@ -78,10 +78,32 @@ def test_plan_dispatch_groups_tokens_once_per_rank():
     assert y[:, 0].tolist() == [2.0, 1.0, 2.0]
 
 
-@pytest.mark.parametrize("world,small_batch", [(2, 0), (4, 0), (2, 512)])
-def test_expert_parallel_matches_single_process_oracle(world, small_batch):
-    """small_batch=0 forces the all-to-all-v dispatch/combine, 512 the gathered fixed-shape form."""
-    res = _spawn(world, small_batch=small_batch)
+@pytest.mark.parametrize("T,E,K,world", [(37, 16, 4, 4), (5, 8, 2, 2), (64, 32, 8, 8)])
+def test_plan_positions_matches_plan_dispatch(T, E, K, world):
+    """The fixed-shape planner (no host read) lists the same rows in the same order as the compact one,
+    and its position table inverts that list."""
+    _, ids = synth.make_routing(T, E, K, "zipf", seed=T)
+    rows, counts = ep.plan_dispatch(ids, E // world, world)
+    pos, counts2, rows_padded = ep.plan_positions(ids, E // world, world)
+    assert counts.tolist() == counts2.tolist()
+    n = int(counts.sum())
+    assert rows_padded[:n].tolist() == rows.tolist()
+    for t in range(T):
+        for d in range(world):
+            p_ = int(pos[t, d])
+            owns = bool(((ids[t] // (E // world)) == d).any())
+            assert (p_ >= 0) == owns
+            if owns:
+                assert int(rows[p_]) == t
+    y_rows = torch.randn(n, 16).to(torch.bfloat16)
+    assert torch.equal(ep.gather_sum(y_rows, pos), ep.scatter_back(y_rows, rows, T))
+
+
+@pytest.mark.parametrize("world,small_batch,chunks", [(2, 0, 1), (4, 0, 1), (2, 512, 1), (2, 0, 3), (4, 0, 2)])
+def test_expert_parallel_matches_single_process_oracle(world, small_batch, chunks):
+    """small_batch=0 forces the all-to-all-v dispatch/combine (in `chunks` pipelined slices), 512 the
+    gathered fixed-shape form."""
+    res = _spawn(world, small_batch=small_batch, chunks=chunks)
     for r in range(world):
         cos, mx = res[r]
         assert cos > 0.9999 and mx < 5e-3, (r, cos, mx)

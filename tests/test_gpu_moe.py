@@ -213,3 +213,32 @@ def test_gptoss_shape_decode_round_trip_properties():
     _assert_close(y, ref, "gpt-oss T=8")
     y2 = _run_layer(x, tw * 0.5, ids, w)
     assert orc.cosine(y2.float() * 2, y.float()) > 0.99999
+
+
+def test_gptoss_prefill_slice_scaled_bound():
+    """Compute-bound regime (token tile 96, per-term MMAs) on an 8-expert slice of the gpt-oss shape.
+    Outputs reach magnitude 2, where one bf16 step is 1.56e-2: the absolute bound is scaled by
+    max(1, |ref|max) there (two roundings of the oracle's own chain already differ by a step)."""
+    T, H, I, E, K = 1024, 2880, 2880, 8, 4
+    x = synth.make_hidden(T, H, 2)
+    tw, ids = synth.make_routing(T, E, K, seed=2)
+    w = synth.make_weights_mxfp4(E, H, I, seed=2)
+    ref = orc.torch_moe_oracle_mxfp4(x, *w, tw, ids)
+    y = _run_layer(x, tw, ids, w)
+    cos, mx = orc.cosine(y, ref), orc.max_abs(y, ref)
+    bound = MAX_ABS * max(1.0, float(ref.float().abs().max()))
+    assert cos >= 0.9999 and mx <= bound, f"cosine {cos:.6f} max_abs {mx:.3e} bound {bound:.3e}"
+
+
+def test_gather_sum_kernel_matches_fp32_sum():
+    """Expert-parallel combine kernel: fp32 accumulation in slot order, one rounding."""
+    from pyhip_b200 import ep
+    T, S, H, n = 300, 8, 2880, 1200
+    g = torch.Generator().manual_seed(5)
+    rows = torch.randn(n, H, generator=g).to(torch.bfloat16)
+    pos = torch.randint(-1, n, (T, S), generator=g, dtype=torch.int32)
+    pos[7] = -1                                    # a token nobody answered stays zero
+    want = ep.gather_sum(rows, pos)                # CPU arithmetic
+    got = ep.gather_sum(rows.to(DEV), pos.to(DEV)).cpu()
+    assert torch.equal(got, want)
+    assert float(got[7].float().abs().max()) == 0.0
