@@ -15,9 +15,11 @@ GEMM (the dominant kernel) against the measured HBM copy rate; `cpu_baseline` = 
 timed on a bounded sample of the same workload.  `--impl reference` times only that CPU path.
 """
 import argparse
+import dataclasses
 import json
 import os
 import pathlib
+import re
 import statistics
 import subprocess
 import sys
@@ -39,6 +41,8 @@ def parse():
     ap.add_argument("--tokens", type=int, default=0, help="tokens per GPU per step (0 = the workload's own)")
     ap.add_argument("--workload", default="gptoss_decode", choices=["gptoss_decode", "gptoss_prefill", "dsv3_ep", "mixtral_skew"],
                     help="gptoss_*: MXFP4 weights (BASELINE configs 1, 2); dsv3_ep: FP8 128x128 weights (config 3)")
+    ap.add_argument("--experts", type=int, default=0,
+                    help="override the number of experts (0 = the workload's own); for small profiling captures")
     ap.add_argument("--ep-chunks", type=int, default=0,
                     help="N>1: slices of the pipelined dispatch/combine exchange (0 = chosen from the shape)")
     ap.add_argument("--sweep", action="store_true", help="also time T in {1,8,32,64,256,8192} (extra keys)")
@@ -47,11 +51,16 @@ def parse():
     return ap.parse_args()
 
 
-def profiled_traffic(workload, T):
-    """DRAM bytes per gate-up launch from the committed ncu capture of this workload, else None."""
-    f = ROOT / "profiles" / "gemm_mxf4_gptoss_decode_T64_traffic.json"
-    if workload == "gptoss_decode" and T == 64 and f.exists():
-        return json.loads(f.read_text()).get("gateup_dram_bytes")
+def profiled_traffic(workload, T, E):
+    """DRAM bytes per gate-up launch from the committed ncu summary of this workload, else None."""
+    name = {("gptoss_decode", 64, 128): "gemm_mxf4_gptoss_decode_T64.md",
+            ("gptoss_prefill", 8192, 128): "gemm_mxf4_gptoss_prefill_T8192.md",
+            ("dsv3_ep", 4096, 32): "gemm_fp8_dsv3_E32_T4096.md"}.get((workload, T, E))
+    f = ROOT / "profiles" / name if name else None
+    if f is not None and f.exists():
+        m = re.search(r"roofline\.traffic[^\n]*gate-up (\d+) bytes", f.read_text())
+        if m:
+            return float(m.group(1))
     return None
 
 
@@ -181,6 +190,8 @@ def cpu_sample_text(info):
 def run_reference(args):
     from pyhip_b200 import synth
     shape = synth.CONFIGS[args.workload]
+    if args.experts:
+        shape = dataclasses.replace(shape, E=args.experts)
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
@@ -250,6 +261,8 @@ def run_b200(args):
         dist = dist_mod
 
     shape = synth.CONFIGS[args.workload]
+    if args.experts:
+        shape = dataclasses.replace(shape, E=args.experts)
     T, H, I, E, K = (args.tokens or shape.T), shape.H, shape.I, shape.E, shape.K
     strong = args.workload == "mixtral_skew"        # this configuration states a global token count
     if strong and world > 1:
@@ -328,15 +341,23 @@ def run_b200(args):
             fp4 = fp4_dense_rate(dev)
             ach = gu_flops / per_launch_s / 1e12
             roofline = {"bound": "tensor", "achieved": ach, "peak": tpeak, "unit": "TFLOP/s", "frac": ach / tpeak,
-                        "traffic": profiled_traffic(args.workload, T), "kernel": "moe_grouped_gemm_kernel<gate-up>",
+                        "traffic": profiled_traffic(args.workload, T, E), "kernel": "moe_grouped_gemm_kernel<gate-up>",
                         "peak_kind": tpeak_kind + " (dense bf16 GEMM)", "us_per_launch": per_launch_s * 1e6,
                         "down_us_per_launch": ms_dn * 1e3 / args.steps, "algorithmic_flops": gu_flops,
-                        "fp4_dense_measured_tflops": fp4, "frac_of_fp4_measured": ach / fp4 if fp4 else None,
-                        "frac_of_fp4_nominal_9pf": ach / 9000.0,
-                        "note": "three packed-FP4 activation terms per product: the MMA work is 3x the algorithmic flops"}
+                        "fp4_dense_measured_tflops": fp4}
+            if fp8:
+                roofline.update({"frac_of_fp8_nominal_4p5pf": ach / 4500.0,
+                                 "frac_of_half_fp4_measured": 2 * ach / fp4 if fp4 else None,
+                                 "note": "two e4m3 activation terms per product: the MMA work is 2x the algorithmic "
+                                         "flops; the FP8 tensor rate is half the FP4 rate measured here"})
+            else:
+                roofline.update({"frac_of_fp4_measured": ach / fp4 if fp4 else None,
+                                 "frac_of_fp4_nominal_9pf": ach / 9000.0,
+                                 "note": "three packed-FP4 activation terms per product: the MMA work is 3x the "
+                                         "algorithmic flops"})
         else:
             roofline = {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
-                        "traffic": profiled_traffic(args.workload, T), "kernel": "moe_grouped_gemm_kernel<gate-up>",
+                        "traffic": profiled_traffic(args.workload, T, E), "kernel": "moe_grouped_gemm_kernel<gate-up>",
                         "peak_kind": peak_kind, "us_per_launch": per_launch_s * 1e6,
                         "down_us_per_launch": ms_dn * 1e3 / args.steps, "algorithmic_bytes": gu_bytes}
         layer_bytes = synth.algorithmic_bytes(T, H, I, hit, shape.wq)
