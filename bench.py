@@ -284,7 +284,7 @@ def run_b200(args):
         tw, ids = synth.make_routing(T, E, K, shape.routing, 0, skew_seed=0)
         hit = len(set(ids.flatten().tolist()))
         xd, twd, idsd = x.to(dev), tw.to(dev), ids.to(dev)
-        B = pick_block(T, K, E)
+        B = pick_block(T, K, E, fmt)
         plan = get_plan(T, K, E, E, H, I, B, 0, 7.0, dev, weight_format=fmt)
         y = torch.empty(T, H, dtype=torch.bfloat16, device=dev)
 
@@ -457,7 +457,7 @@ def run_b200(args):
         xr, twr, idr = layer.last_local
         n = xr.shape[0]
         pw = prepare_weights(*w_full, weight_format=fmt)
-        plan = get_plan(n, K, E_local, E_local, H, I, pick_block(n, K, E_local), 0, 7.0, dev, weight_format=fmt)
+        plan = get_plan(n, K, E_local, E_local, H, I, pick_block(n, K, E_local, fmt), 0, 7.0, dev, weight_format=fmt)
         plan.sort(idr.contiguous(), twr.contiguous())
         plan.quant_input(xr)
         k_steps = max(3, min(args.steps, 50))

@@ -222,6 +222,17 @@ int b200moe_combine(const b200moe_shape* s, const b200moe_workspace* ws, void* w
                         s->H, (cudaStream_t)stream);
 }
 
+// A workspace laid out for more tokens than the call carries is fine (its offsets and row capacity are
+// used as given); one that is too small is an argument error.
+static int check_capacity(const b200moe_shape* s, const b200moe_workspace* ws) {
+  const int64_t P = (int64_t)s->T * s->K;
+  const int64_t need = std::max<int64_t>((P + (int64_t)s->E_route * (s->B - 1) + s->B - 1) / s->B, 1) * s->B;
+  B200_CHECK_ARG(ws->max_rows >= need && ws->max_rows % s->B == 0,
+                 "workspace holds %lld rows, T=%d needs %lld (blocks of %d)", (long long)ws->max_rows, s->T,
+                 (long long)need, s->B);
+  return 0;
+}
+
 int b200moe_forward(const b200moe_shape* s, const b200moe_workspace* ws, void* workspace, const void* x_bf16,
                     const int32_t* topk_ids, const float* topk_weight, const int32_t* expert_mask,
                     const void* w1_q, const void* w1_scale, const void* w2_q, const void* w2_scale,
@@ -229,6 +240,7 @@ int b200moe_forward(const b200moe_shape* s, const b200moe_workspace* ws, void* w
   if (int rc = check_shape(s)) return rc;
   B200_CHECK_ARG(ws && workspace, "forward: NULL workspace");
   if (s->T == 0) return 0;
+  if (int rc = check_capacity(s, ws)) return rc;
   B200_CHECK_ARG(x_bf16 && topk_ids && topk_weight && y_bf16, "forward: NULL tensor");
   uint8_t* base = (uint8_t*)workspace;
   int rc = b200moe_sort_align(topk_ids, topk_weight, s->T, s->K, s->E_route, s->B, expert_mask,

@@ -70,6 +70,19 @@ def test_null_pointers_are_rejected_without_launch(L):
     assert sb.value == 8 * 2 * 1 * 2 * 512
 
 
+def test_workspace_too_small_for_the_token_count_is_rejected(L):
+    """A workspace laid out for more tokens than a call carries is accepted; a smaller one is an
+    argument error raised before anything is launched (dummy non-null pointers are never touched)."""
+    small = _lib.Shape(T=8, K=2, E=8, E_route=8, H=256, I=128, B=32, weight_format=0, activation=0, swiglu_limit=7.0, act_terms=0)
+    big = _lib.Shape(T=4096, K=2, E=8, E_route=8, H=256, I=128, B=32, weight_format=0, activation=0, swiglu_limit=7.0, act_terms=0)
+    ws_small = _lib.workspace_layout(small)
+    p = ctypes.c_void_p(4096)
+    rc = L.b200moe_forward(ctypes.byref(big), ctypes.byref(ws_small), p, p, p, p, None, p, p, p, p, p, None)
+    assert rc < 0 and b"workspace holds" in L.b200moe_last_error()
+    assert L.b200moe_gather_sum(None, None, 4, 2, 64, None, None) < 0
+    assert L.b200moe_gather_sum(None, None, 0, 2, 64, None, None) == 0      # empty batch: nothing to do
+
+
 def test_python_surface_fails_loudly_without_cuda():
     import torch
     from pyhip_b200 import QuantType, fused_moe

@@ -242,3 +242,19 @@ def test_gather_sum_kernel_matches_fp32_sum():
     got = ep.gather_sum(rows.to(DEV), pos.to(DEV)).cpu()
     assert torch.equal(got, want)
     assert float(got[7].float().abs().max()) == 0.0
+
+
+def test_varying_token_counts_share_one_workspace():
+    """Beyond 512 tokens the wrapper lays the workspace out for the count rounded up to 512, so calls whose
+    batch varies (expert-parallel dispatch) reuse one allocation; results must not depend on the capacity."""
+    import importlib
+    fm = importlib.import_module("pyhip_b200.fused_moe")
+    H, I, E, K = 512, 256, 8, 2
+    w = synth.make_weights_mxfp4(E, H, I, seed=6)
+    fm._workspace_cache.clear()
+    for T in (600, 1000, 1024, 513):
+        x = synth.make_hidden(T, H, T)
+        tw, ids = synth.make_routing(T, E, K, seed=T)
+        ref = orc.torch_moe_oracle_mxfp4(x, *w, tw, ids)
+        _assert_close(_run_layer(x, tw, ids, w, block_size_M=64), ref, f"T={T}")
+    assert len(fm._workspace_cache) == 1
