@@ -2,4 +2,7 @@
 from .fused_moe import (ActivationType, QuantType, PreparedWeights, fused_moe, moe_sorting,  # noqa: F401
                         prepare_weights)
 
-__all__ = ["ActivationType", "QuantType", "PreparedWeights", "fused_moe", "moe_sorting", "prepare_weights"]
+from .linear import linear_fp8_128x128, linear_mxfp4  # noqa: F401,E402
+
+__all__ = ["ActivationType", "QuantType", "PreparedWeights", "fused_moe", "moe_sorting", "prepare_weights",
+           "linear_mxfp4", "linear_fp8_128x128"]

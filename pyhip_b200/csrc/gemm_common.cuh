@@ -27,6 +27,37 @@ __device__ __forceinline__ float gateup_act(float g, float u, int activation, fl
   return bf16r(g * __frcp_rn(1.f + __expf(-1.702f * g)) * (u + 1.f));
 }
 
+// Two elements at once with packed bf16 conversions (half the conversion instructions); the same
+// roundings as gateup_act, result already in bf16.
+__device__ __forceinline__ float2 bf16r2(float a, float b) { return __bfloat1622float2(__floats2bfloat162_rn(a, b)); }
+__device__ __forceinline__ __nv_bfloat162 gateup_act2(float g0, float u0, float g1, float u1, int activation,
+                                                      float limit) {
+  float2 g = bf16r2(g0, g1), u = bf16r2(u0, u1);
+  if (activation == B200MOE_ACT_SILU) {
+    const float2 s = bf16r2(g.x * __frcp_rn(1.f + __expf(-g.x)), g.y * __frcp_rn(1.f + __expf(-g.y)));
+    return __floats2bfloat162_rn(s.x * u.x, s.y * u.y);
+  }
+  g.x = fminf(g.x, limit);
+  g.y = fminf(g.y, limit);
+  u.x = fminf(fmaxf(u.x, -limit), limit);
+  u.y = fminf(fmaxf(u.y, -limit), limit);
+  return __floats2bfloat162_rn(g.x * __frcp_rn(1.f + __expf(-1.702f * g.x)) * (u.x + 1.f),
+                               g.y * __frcp_rn(1.f + __expf(-1.702f * g.y)) * (u.y + 1.f));
+}
+
+// (a0, a1) += s * (v0, v1) as one packed fp32x2 instruction (two FMAs per issue slot); v0/v1 are raw
+// accumulator words as tcgen05.ld returns them
+__device__ __forceinline__ void ffma2_scaled(float& a0, float& a1, float s, uint32_t v0, uint32_t v1) {
+  asm("{\n\t.reg .b64 a, v, c;\n\t"
+      "mov.b64 a, {%0, %1};\n\t"
+      "mov.b64 v, {%2, %3};\n\t"
+      "mov.b64 c, {%4, %4};\n\t"
+      "fma.rn.f32x2 a, v, c, a;\n\t"
+      "mov.b64 {%0, %1}, a;\n\t}"
+      : "+f"(a0), "+f"(a1)
+      : "r"(v0), "r"(v1), "f"(s));
+}
+
 // descriptor halves: the high word is constant per layout, the low word carries the address
 constexpr uint32_t kDescHiSw = (1024u >> 4) | (1u << 14) | (2u << 29);   // SBO 1024, version 1, 128-byte swizzle
 constexpr uint32_t kDescHiSf = (128u >> 4) | (1u << 14);                   // SBO 128, version 1, no swizzle

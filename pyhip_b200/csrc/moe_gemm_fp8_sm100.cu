@@ -285,6 +285,34 @@ __global__ void __launch_bounds__(kThreads, 1) moe_grouped_gemm_fp8_kernel(const
           if (lane == 0) mbar_arrive(smem_u32(&ctl->stg_empty));
           ph ^= 1;
         }
+      } else if (!GATEUP) {
+        // down projection: two 128-feature halves per tile, staging rows -> out2 rows as 16-byte vectors
+        const uint32_t stg = stage0 + (uint32_t)S * geo.stage_bytes;
+        uint32_t ph = 0;
+        bool ok = true;
+        for (int w = blockIdx.x; w < total_work && ok; w += gridDim.x) {
+          const int b = w / p.MT, m = w - b * p.MT;
+          const int r0 = b * B;
+          int nvalid = 0;
+          for (int q = 0; q < B; q += 32) {
+            const uint32_t id = (q + lane < B) ? p.sorted_ids[r0 + q + lane] : 0xFFFFFFFFu;
+            nvalid += __popc(__ballot_sync(0xffffffffu, (int)(id >> 24) < p.topk && (int)(id & 0xFFFFFFu) < p.T));
+          }
+          for (int hf = 0; hf < 2; ++hf) {
+            if (!mbar_wait(smem_u32(&ctl->stg_full), ph, abort_word, 0x901)) { ok = false; break; }
+            const int f0 = m * 2 * kTileM + hf * kTileM;
+            if (f0 < p.rows) {
+              for (int idx = lane; idx < nvalid * 16; idx += 32) {
+                const int n = idx >> 4, v = idx & 15;
+                const uint4 val = ld_shared_v4(stg + (uint32_t)n * kStagePitch + v * 16);
+                *reinterpret_cast<uint4*>(p.out2 + ((int64_t)r0 + n) * p.rows + f0 + v * 8) = val;
+              }
+            }
+            __syncwarp();
+            if (lane == 0) mbar_arrive(smem_u32(&ctl->stg_empty));
+            ph ^= 1;
+          }
+        }
       }
     }
   } else if (warp >= 12) {
@@ -327,6 +355,7 @@ __global__ void __launch_bounds__(kThreads, 1) moe_grouped_gemm_fp8_kernel(const
     const int row_local = quad * 32 + lane;
     const uint32_t stg = stage0 + (uint32_t)S * geo.stage_bytes;
     const bool fused = GATEUP && p.h_out == nullptr;
+    const bool staged = fused || !GATEUP;      // finished tiles leave through the staging buffer and the store warp
     const int row_blocks = (GATEUP ? 2 * p.rows : p.rows) / kTileM;   // weight-scale rows per expert
     uint32_t acc = 0, acc_phase = 0;
     bool alive = true;
@@ -383,9 +412,9 @@ __global__ void __launch_bounds__(kThreads, 1) moe_grouped_gemm_fp8_kernel(const
           for (int ci = 0; ci < kMaxChunks; ++ci) {
             if ((2 * ci + half) * 16 < nvalid) {
 #pragma unroll
-              for (int n = 0; n < 16; ++n) {
-                if (part == 0) ag[ci * 16 + n] = fmaf(sc[0], __uint_as_float(v[ci][n]), ag[ci * 16 + n]);
-                else au[ci * 16 + n] = fmaf(sc[1], __uint_as_float(v[ci][n]), au[ci * 16 + n]);
+              for (int n = 0; n < 16; n += 2) {
+                if (part == 0) ffma2_scaled(ag[ci * 16 + n], ag[ci * 16 + n + 1], sc[0], v[ci][n], v[ci][n + 1]);
+                else ffma2_scaled(au[ci * 16 + n], au[ci * 16 + n + 1], sc[1], v[ci][n], v[ci][n + 1]);
               }
             }
           }
@@ -395,7 +424,7 @@ __global__ void __launch_bounds__(kThreads, 1) moe_grouped_gemm_fp8_kernel(const
       }
       // one vote per tile: a warp whose wait gave up has set the shared abort word, so the others'
       // waits return at once and every epilogue warp leaves before the next named barrier
-      if (fused && alive) alive = mbar_wait(smem_u32(&ctl->stg_empty), stg_phase ^ 1, abort_word, 0x800);
+      if (staged && alive) alive = mbar_wait(smem_u32(&ctl->stg_empty), stg_phase ^ 1, abort_word, 0x800);
       if (!epi_all(alive)) break;
       const long long tt0 = clock64();
 
@@ -419,29 +448,46 @@ __global__ void __launch_bounds__(kThreads, 1) moe_grouped_gemm_fp8_kernel(const
               }
             } else {
 #pragma unroll
-              for (int n = 0; n < 16; ++n) {
+              for (int n = 0; n < 16; n += 2) {
                 if (c0 + n < nvalid) {
-                  float v = gateup_act(ag[ci * 16 + n], au[ci * 16 + n], p.activation, p.swiglu_limit);
-                  if (!j_ok) v = 0.f;
-                  st_shared_u16(stg + (uint32_t)(c0 + n) * kStagePitch + row_local * 2,
-                                __bfloat16_as_ushort(__float2bfloat16_rn(v)));
+                  __nv_bfloat162 v = gateup_act2(ag[ci * 16 + n], au[ci * 16 + n], ag[ci * 16 + n + 1], au[ci * 16 + n + 1],
+                                                 p.activation, p.swiglu_limit);
+                  if (!j_ok) v = __floats2bfloat162_rn(0.f, 0.f);
+                  st_shared_u16(stg + (uint32_t)(c0 + n) * kStagePitch + row_local * 2, __bfloat16_as_ushort(v.x));
+                  if (c0 + n + 1 < nvalid)
+                    st_shared_u16(stg + (uint32_t)(c0 + n + 1) * kStagePitch + row_local * 2, __bfloat16_as_ushort(v.y));
                 }
               }
             }
           } else {
-            const bool j2_ok = j + kTileM < p.rows;
 #pragma unroll
-            for (int n = 0; n < 16; ++n) {
-              if (c0 + n < nvalid) {
-                __nv_bfloat16* row = p.out2 + ((int64_t)r0 + c0 + n) * p.rows + j;
-                if (j_ok) row[0] = __float2bfloat16_rn(ag[ci * 16 + n]);
-                if (j2_ok) row[kTileM] = __float2bfloat16_rn(au[ci * 16 + n]);
-              }
-            }
+            for (int n = 0; n < 16; ++n)
+              if (c0 + n < nvalid)
+                st_shared_u16(stg + (uint32_t)(c0 + n) * kStagePitch + row_local * 2,
+                              __bfloat16_as_ushort(__float2bfloat16_rn(ag[ci * 16 + n])));
           }
         }
       }
-      if (fused) {          // hand the staged tile to the store warp
+      if (staged) {          // hand the staged tile to the store warp
+        __syncwarp();
+        if (lane == 0) mbar_arrive(smem_u32(&ctl->stg_full));
+        stg_phase ^= 1;
+      }
+      if (!GATEUP) {
+        // second weight tile of the pair (features j + 128): same route once the store warp has drained the first
+        const bool ok2 = mbar_wait(smem_u32(&ctl->stg_empty), stg_phase ^ 1, abort_word, 0x801);
+        if (!epi_all(ok2)) break;
+#pragma unroll
+        for (int ci = 0; ci < kMaxChunks; ++ci) {
+          const int c0 = (2 * ci + half) * 16;
+          if (c0 < nvalid) {
+#pragma unroll
+            for (int n = 0; n < 16; ++n)
+              if (c0 + n < nvalid)
+                st_shared_u16(stg + (uint32_t)(c0 + n) * kStagePitch + row_local * 2,
+                              __bfloat16_as_ushort(__float2bfloat16_rn(au[ci * 16 + n])));
+          }
+        }
         __syncwarp();
         if (lane == 0) mbar_arrive(smem_u32(&ctl->stg_full));
         stg_phase ^= 1;
@@ -509,7 +555,7 @@ int launch_grouped_gemm_fp8(const GemmArgs& a, cudaStream_t st) {
     if (rc) return rc;
   }
   const StageGeom geo = stage_geom(a.N);
-  const int staging = (a.gateup && a.h_out == nullptr) ? a.N * kStagePitch : 0;
+  const int staging = (!a.gateup || a.h_out == nullptr) ? a.N * kStagePitch : 0;   // fused gate-up and down leave through it
   int stages = std::min((kSmemLimit - 1024 - kCtlBytes - staging) / geo.stage_bytes, kMaxStages);
   B200_CHECK_ARG(stages >= 2, "fp8 grouped gemm: tile does not fit shared memory");
   p.stages = stages;

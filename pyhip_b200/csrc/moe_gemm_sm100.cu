@@ -400,12 +400,14 @@ moe_grouped_gemm_kernel(const __grid_constant__ GemmParams p) {
             // h (already rounded to bf16, as the oracle's h is) goes to the staging tile,
             // token-major, for the block-wise re-quantisation below
 #pragma unroll
-            for (int n = 0; n < 16; ++n) {
+            for (int n = 0; n < 16; n += 2) {
               if (c0 + n < nvalid) {
-                float v = gateup_act(__uint_as_float(g[n]), __uint_as_float(u[n]), p.activation, p.swiglu_limit);
-                if (!j_ok) v = 0.f;
-                st_shared_u16(stg + (uint32_t)(c0 + n) * kStagePitch + row_local * 2,
-                              __bfloat16_as_ushort(__float2bfloat16_rn(v)));
+                __nv_bfloat162 v = gateup_act2(__uint_as_float(g[n]), __uint_as_float(u[n]), __uint_as_float(g[n + 1]),
+                                               __uint_as_float(u[n + 1]), p.activation, p.swiglu_limit);
+                if (!j_ok) v = __floats2bfloat162_rn(0.f, 0.f);
+                st_shared_u16(stg + (uint32_t)(c0 + n) * kStagePitch + row_local * 2, __bfloat16_as_ushort(v.x));
+                if (c0 + n + 1 < nvalid)
+                  st_shared_u16(stg + (uint32_t)(c0 + n + 1) * kStagePitch + row_local * 2, __bfloat16_as_ushort(v.y));
               }
             }
           }

@@ -2,7 +2,9 @@
 the copy engine's FP4 unpacking into 128-byte-swizzled shared memory, and the shared->tensor
 memory scale copy."""
 import ctypes
+import os
 import pathlib
+import tempfile
 
 import numpy as np
 import pytest
@@ -11,7 +13,7 @@ import torch
 from pyhip_b200 import _lib
 
 pytestmark = pytest.mark.gpu
-OUT = pathlib.Path(__file__).resolve().parents[1] / "gpurun_out"
+OUT = pathlib.Path(os.environ.get("B200MOE_PROBE_DUMP", tempfile.gettempdir()))   # where the probe images are saved
 
 
 def _probe(which, inp: torch.Tensor, out_words: int):
