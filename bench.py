@@ -1,18 +1,24 @@
 """Benchmark of the fused-MoE hot path.
 
-    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference] [--tokens T]
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference] [--workload W] [--tokens T] [--sweep]
 
-One "step" is one MoE layer call on one batch of synthetic tokens.  At N=1 the workload is the
-gpt-oss-120b-shaped MXFP4 layer (H=I=2880, E=128, top-4) at T=64 decode tokens -- the
-weight-streaming regime the headline metric is quoted on.  At N>1 the same layer runs
-expert-parallel, one process per GPU (torchrun), T tokens per GPU, with the dispatch/combine
-all-to-all over NCCL inside the timed region.
+One "step" is one MoE layer call on one batch of synthetic tokens.  At N=1 the default workload is
+the gpt-oss-120b-shaped MXFP4 layer (H=I=2880, E=128, top-4) at T=64 decode tokens -- the
+weight-streaming regime the headline metric is quoted on.  `--workload` selects the other
+configurations: gptoss_prefill (T=8192), dsv3_ep (DeepSeek-V3-shaped FP8 128x128, T=4096 per GPU),
+mixtral_skew (E=8, Zipf load, T=16384 in total).  At N>1 the layer runs expert-parallel, one process
+per GPU (torchrun), with the exchange over NCCL inside the timed region: all-gather + reduce-scatter
+at decode sizes, all-to-all-v dispatch/combine above 512 tokens per GPU.
 
 Prints ONE JSON line (rank 0).  `value` = tokens/s with inputs resident in HBM, timed with CUDA
-events over exactly K steps; `e2e` = the same through the public `fused_moe` call with pinned
-host buffers copied in and the result copied out every step; `roofline` = the gate-up grouped
-GEMM (the dominant kernel) against the measured HBM copy rate; `cpu_baseline` = the CPU oracle
-timed on a bounded sample of the same workload.  `--impl reference` times only that CPU path.
+events over exactly K steps (a CUDA-graph replay of the call's five launches at N=1); `e2e` = the
+same through the public `fused_moe` call with pinned host buffers copied in and the result copied
+out every step; `roofline` = the gate-up grouped GEMM (the dominant kernel) timed alone: against the
+measured HBM copy rate where the launch is bandwidth-bound, against the measured dense bf16 rate --
+with the dense FP4 MMA rate measured in the same run beside it -- where it is compute-bound;
+`cpu_baseline` = the CPU oracle timed on a bounded sample of the same workload.  `--impl reference`
+times only that CPU path.  Extra keys: `layer` (whole-call GB/s and TFLOP/s), `sweep`, and at N>1
+`local_expert_ms_per_rank` (load balance) and `rank0_phase_ms` (where a step's time goes).
 """
 import argparse
 import dataclasses
@@ -489,7 +495,10 @@ def run_b200(args):
                 "e2e": {"value": T * world * args.steps / (ms_e2e * 1e-3), "unit": UNIT,
                         "h2d_bytes_per_step": x.numel() * 2 + tw.numel() * 4 + ids.numel() * 4,
                         "d2h_bytes_per_step": T * H * 2},
-                "gpu_launches": launches_per_step * args.steps, "roofline": roofline, "cpu_baseline": None,
+                # this library's kernels per step on every rank: the five of the layer, plus the gather-sum
+                # combine in the dispatch form of the exchange (NCCL's kernels are not counted)
+                "gpu_launches": (launches_per_step + (1 if T > layer.small_batch else 0)) * args.steps,
+                "roofline": roofline, "cpu_baseline": None,
                 "local_expert_ms_per_rank": [round(float(b.item()), 4) for b in busy_all],
                 "rank0_phase_ms": phases}
         print(json.dumps(line), flush=True)
