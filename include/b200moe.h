@@ -85,6 +85,15 @@ int b200moe_sort_align(const int32_t* topk_ids, const float* topk_weight, int32_
                        float* sorted_weights, int32_t* sorted_expert_ids, int32_t* num_valid_ids,
                        int32_t* loc, void* stream);
 
+/* The same with a token count that lives on the device: tokens at and beyond *num_local_tokens take no
+ * part (their pairs are dropped, their loc entries read -1, num_valid_ids[1] = the live count), so a call
+ * captured into a CUDA graph at a fixed, padded T serves smaller batches -- the reference's
+ * num_local_tokens argument (src/contrib/fused_moe.py:48-49,63,145,304,371).  NULL = all T tokens. */
+int b200moe_sort_align_dyn(const int32_t* topk_ids, const float* topk_weight, int32_t T, int32_t K,
+                           int32_t E_route, int32_t B, const int32_t* expert_mask,
+                           const int32_t* num_local_tokens, uint32_t* sorted_ids, float* sorted_weights,
+                           int32_t* sorted_expert_ids, int32_t* num_valid_ids, int32_t* loc, void* stream);
+
 /* Quantise bf16 rows into `terms` packed-FP4 (E2M1) terms with E8M0 scales per 32, gathered into
  * sorted-row order (stands where the reference calls aiter's per_1x32 activation quantiser
  * followed by moe_mxfp4_sort, tests/contrib/moe/test_moe.py:665-679).
@@ -134,6 +143,14 @@ int b200moe_forward(const b200moe_shape* shape, const b200moe_workspace* ws, voi
                     const void* x_bf16, const int32_t* topk_ids, const float* topk_weight,
                     const int32_t* expert_mask, const void* w1_q, const void* w1_scale_prepared,
                     const void* w2_q, const void* w2_scale_prepared, void* y_bf16, void* stream);
+
+/* Whole layer with a device-side token count (see b200moe_sort_align_dyn); output rows of tokens at and
+ * beyond *num_local_tokens are zero. */
+int b200moe_forward_dyn(const b200moe_shape* shape, const b200moe_workspace* ws, void* workspace,
+                        const void* x_bf16, const int32_t* topk_ids, const float* topk_weight,
+                        const int32_t* expert_mask, const int32_t* num_local_tokens, const void* w1_q,
+                        const void* w1_scale_prepared, const void* w2_q, const void* w2_scale_prepared,
+                        void* y_bf16, void* stream);
 
 /* Whole layer WITHOUT a caller-provided workspace.  No counterpart in the reference (pyhip's
  * wrapper lets torch allocate its intermediates on every call).  It exists for hosts that cannot

@@ -116,15 +116,31 @@ int b200moe_prepare_scales(const b200moe_shape* s, int which, const void* w_s, v
   return launch_repack_scales(w_s, out_scale, s->E, which == 1, which == 1 ? s->I : s->H, Kd, (cudaStream_t)stream);
 }
 
-int b200moe_sort_align(const int32_t* topk_ids, const float* topk_weight, int32_t T, int32_t K, int32_t E_route,
-                       int32_t B, const int32_t* expert_mask, uint32_t* sorted_ids, float* sorted_weights,
-                       int32_t* sorted_expert_ids, int32_t* num_valid_ids, int32_t* loc, void* stream) {
+static int sort_align_impl(const int32_t* topk_ids, const float* topk_weight, int32_t T, int32_t K, int32_t E_route,
+                           int32_t B, const int32_t* expert_mask, const int32_t* num_local_tokens, uint32_t* sorted_ids,
+                           float* sorted_weights, int32_t* sorted_expert_ids, int32_t* num_valid_ids, int32_t* loc,
+                           void* stream) {
   B200_CHECK_ARG(T >= 0 && T < (1 << 24) && K >= 1 && K <= 255, "sort_align: T=%d K=%d out of range", T, K);
   B200_CHECK_ARG(B >= 1, "sort_align: B=%d", B);
   B200_CHECK_ARG(sorted_ids && sorted_weights && sorted_expert_ids && num_valid_ids, "sort_align: NULL output");
   B200_CHECK_ARG(T == 0 || (topk_ids && topk_weight), "sort_align: NULL input");
   return launch_sort_align(topk_ids, topk_weight, T, K, E_route, B, expert_mask, sorted_ids, sorted_weights,
-                           sorted_expert_ids, num_valid_ids, loc, (cudaStream_t)stream);
+                           sorted_expert_ids, num_valid_ids, loc, num_local_tokens, (cudaStream_t)stream);
+}
+
+int b200moe_sort_align(const int32_t* topk_ids, const float* topk_weight, int32_t T, int32_t K, int32_t E_route,
+                       int32_t B, const int32_t* expert_mask, uint32_t* sorted_ids, float* sorted_weights,
+                       int32_t* sorted_expert_ids, int32_t* num_valid_ids, int32_t* loc, void* stream) {
+  return sort_align_impl(topk_ids, topk_weight, T, K, E_route, B, expert_mask, nullptr, sorted_ids, sorted_weights,
+                         sorted_expert_ids, num_valid_ids, loc, stream);
+}
+
+int b200moe_sort_align_dyn(const int32_t* topk_ids, const float* topk_weight, int32_t T, int32_t K, int32_t E_route,
+                           int32_t B, const int32_t* expert_mask, const int32_t* num_local_tokens,
+                           uint32_t* sorted_ids, float* sorted_weights, int32_t* sorted_expert_ids,
+                           int32_t* num_valid_ids, int32_t* loc, void* stream) {
+  return sort_align_impl(topk_ids, topk_weight, T, K, E_route, B, expert_mask, num_local_tokens, sorted_ids,
+                         sorted_weights, sorted_expert_ids, num_valid_ids, loc, stream);
 }
 
 int b200moe_quant_rows(const void* src_bf16, int32_t src_mode, const uint32_t* sorted_ids,
@@ -233,20 +249,20 @@ static int check_capacity(const b200moe_shape* s, const b200moe_workspace* ws) {
   return 0;
 }
 
-int b200moe_forward(const b200moe_shape* s, const b200moe_workspace* ws, void* workspace, const void* x_bf16,
-                    const int32_t* topk_ids, const float* topk_weight, const int32_t* expert_mask,
-                    const void* w1_q, const void* w1_scale, const void* w2_q, const void* w2_scale,
-                    void* y_bf16, void* stream) {
+static int forward_impl(const b200moe_shape* s, const b200moe_workspace* ws, void* workspace, const void* x_bf16,
+                        const int32_t* topk_ids, const float* topk_weight, const int32_t* expert_mask,
+                        const int32_t* num_local_tokens, const void* w1_q, const void* w1_scale, const void* w2_q,
+                        const void* w2_scale, void* y_bf16, void* stream) {
   if (int rc = check_shape(s)) return rc;
   B200_CHECK_ARG(ws && workspace, "forward: NULL workspace");
   if (s->T == 0) return 0;
   if (int rc = check_capacity(s, ws)) return rc;
   B200_CHECK_ARG(x_bf16 && topk_ids && topk_weight && y_bf16, "forward: NULL tensor");
   uint8_t* base = (uint8_t*)workspace;
-  int rc = b200moe_sort_align(topk_ids, topk_weight, s->T, s->K, s->E_route, s->B, expert_mask,
-                              (uint32_t*)(base + ws->off_sorted_ids), (float*)(base + ws->off_sorted_w),
-                              (int32_t*)(base + ws->off_sorted_e), (int32_t*)(base + ws->off_num_valid),
-                              (int32_t*)(base + ws->off_loc), stream);
+  int rc = sort_align_impl(topk_ids, topk_weight, s->T, s->K, s->E_route, s->B, expert_mask, num_local_tokens,
+                           (uint32_t*)(base + ws->off_sorted_ids), (float*)(base + ws->off_sorted_w),
+                           (int32_t*)(base + ws->off_sorted_e), (int32_t*)(base + ws->off_num_valid),
+                           (int32_t*)(base + ws->off_loc), stream);
   if (rc) return rc;
   if (s->weight_format == B200MOE_W_FP8_128)
     rc = b200moe_quant_rows_e4m3(x_bf16, 0, (const uint32_t*)(base + ws->off_sorted_ids),
@@ -262,6 +278,22 @@ int b200moe_forward(const b200moe_shape* s, const b200moe_workspace* ws, void* w
   rc = b200moe_down(s, ws, workspace, w2_q, w2_scale, stream);
   if (rc) return rc;
   return b200moe_combine(s, ws, workspace, topk_weight, y_bf16, stream);
+}
+
+int b200moe_forward(const b200moe_shape* s, const b200moe_workspace* ws, void* workspace, const void* x_bf16,
+                    const int32_t* topk_ids, const float* topk_weight, const int32_t* expert_mask,
+                    const void* w1_q, const void* w1_scale, const void* w2_q, const void* w2_scale,
+                    void* y_bf16, void* stream) {
+  return forward_impl(s, ws, workspace, x_bf16, topk_ids, topk_weight, expert_mask, nullptr, w1_q, w1_scale, w2_q,
+                      w2_scale, y_bf16, stream);
+}
+
+int b200moe_forward_dyn(const b200moe_shape* s, const b200moe_workspace* ws, void* workspace, const void* x_bf16,
+                        const int32_t* topk_ids, const float* topk_weight, const int32_t* expert_mask,
+                        const int32_t* num_local_tokens, const void* w1_q, const void* w1_scale, const void* w2_q,
+                        const void* w2_scale, void* y_bf16, void* stream) {
+  return forward_impl(s, ws, workspace, x_bf16, topk_ids, topk_weight, expert_mask, num_local_tokens, w1_q, w1_scale,
+                      w2_q, w2_scale, y_bf16, stream);
 }
 
 int b200moe_gather_sum(const void* rows_bf16, const int32_t* pos, int32_t T, int32_t slots, int32_t H, void* y_bf16,

@@ -54,7 +54,7 @@ __host__ __device__ static inline int64_t act_sf_index(int64_t block, int kb, in
 // launchers (moe_aux.cu)
 int launch_sort_align(const int32_t* ids, const float* w, int T, int K, int E, int B, const int32_t* mask,
                       uint32_t* sorted_ids, float* sorted_w, int32_t* sorted_e, int32_t* num_valid,
-                      int32_t* loc, cudaStream_t st);
+                      int32_t* loc, const int32_t* num_local, cudaStream_t st);
 int launch_quant_rows(const void* src, int src_mode, const uint32_t* sorted_ids, const int32_t* num_valid,
                       int T, int K, int Kd, int B, int NT, int64_t max_rows, void* q, void* sf, cudaStream_t st);
 int launch_gather_sum(const void* rows, const int32_t* pos, void* y, int T, int S, int H, cudaStream_t st);

@@ -24,7 +24,8 @@ __global__ void __launch_bounds__(kSortWarps * 32, 1)
 sort_align_kernel(const int32_t* __restrict__ ids, const float* __restrict__ w, int T, int K, int E, int B,
                   const int32_t* __restrict__ mask, uint32_t* __restrict__ sorted_ids,
                   float* __restrict__ sorted_w, int32_t* __restrict__ sorted_e,
-                  int32_t* __restrict__ num_valid, int32_t* __restrict__ loc) {
+                  int32_t* __restrict__ num_valid, int32_t* __restrict__ loc,
+                  const int32_t* __restrict__ num_local) {
   extern __shared__ int32_t sm[];
   int32_t* cnt = sm;                        // [kSortWarps][E] per-warp counts, then running offsets
   int32_t* base = sm + kSortWarps * E;      // [E] first sorted row of the expert
@@ -39,13 +40,17 @@ sort_align_kernel(const int32_t* __restrict__ ids, const float* __restrict__ w, 
   const int P = T * K;
   const int seg = ((P + kSortWarps - 1) / kSortWarps + 31) & ~31;
   const int seg_lo = warp * seg, seg_hi = min(P, seg_lo + seg);
+  // tokens at and beyond *num_local (a device value, for batches padded to a fixed T) take no part:
+  // their pairs are dropped and their loc entries read -1
+  const int T_live = (num_local != nullptr) ? min(T, max(num_local[0], 0)) : T;
+  const int live_hi = min(seg_hi, T_live * K);
 
   for (int i = tid; i < kSortWarps * E; i += blockDim.x) cnt[i] = 0;
   __syncthreads();
 
   // pass 1: per-warp histogram of its slice
   for (int i0 = seg_lo; i0 < seg_hi; i0 += 32) {
-    int e = sort_fetch_expert(ids, mask, i0 + lane, seg_hi, E);
+    int e = sort_fetch_expert(ids, mask, i0 + lane, live_hi, E);
     unsigned same = __match_any_sync(0xffffffffu, e);
     if (e >= 0 && lane == __ffs(same) - 1) cnt[warp * E + e] += __popc(same);
   }
@@ -94,7 +99,7 @@ sort_align_kernel(const int32_t* __restrict__ ids, const float* __restrict__ w, 
     }
     if (tid == 0) {
       num_valid[0] = (int)(wsum[32] >> 32);
-      num_valid[1] = T;
+      num_valid[1] = T_live;
     }
   }
   __syncthreads();
@@ -103,7 +108,7 @@ sort_align_kernel(const int32_t* __restrict__ ids, const float* __restrict__ w, 
   const uint32_t lt_mask = (1u << lane) - 1u;
   for (int i0 = seg_lo; i0 < seg_hi; i0 += 32) {
     int i = i0 + lane;
-    int e = sort_fetch_expert(ids, mask, i, seg_hi, E);
+    int e = sort_fetch_expert(ids, mask, i, live_hi, E);
     unsigned same = __match_any_sync(0xffffffffu, e);
     int pos = -1;
     if (e >= 0) pos = base[e] + cnt[warp * E + e] + __popc(same & lt_mask);
@@ -135,7 +140,7 @@ sort_align_kernel(const int32_t* __restrict__ ids, const float* __restrict__ w, 
 
 int launch_sort_align(const int32_t* ids, const float* w, int T, int K, int E, int B, const int32_t* mask,
                       uint32_t* sorted_ids, float* sorted_w, int32_t* sorted_e, int32_t* num_valid,
-                      int32_t* loc, cudaStream_t st) {
+                      int32_t* loc, const int32_t* num_local, cudaStream_t st) {
   B200_CHECK_ARG(E >= 1 && E <= kSortWarps * 32, "sort_align: E=%d outside [1,%d]", E, kSortWarps * 32);
   size_t smem = (size_t)(kSortWarps * E + 3 * E + 2) * sizeof(int32_t) + 34 * sizeof(unsigned long long);
   B200_CHECK_ARG(smem <= 200 * 1024, "sort_align: E=%d needs %zu bytes of shared memory", E, smem);
@@ -146,7 +151,7 @@ int launch_sort_align(const int32_t* ids, const float* w, int T, int K, int E, i
     attr_set = true;
   }
   B200_CHECK_CUDA(launch_chained(sort_align_kernel, dim3(1), dim3(kSortWarps * 32), smem, st, ids, w, T, K, E, B, mask,
-                                 sorted_ids, sorted_w, sorted_e, num_valid, loc));
+                                 sorted_ids, sorted_w, sorted_e, num_valid, loc, num_local));
   return 0;
 }
 

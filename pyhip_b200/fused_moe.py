@@ -264,33 +264,37 @@ def get_plan(T, K, E, E_route, H, I, B, activation, swiglu_limit, device, act_te
 
 
 def moe_forward(plan: MoEPlan, pw: PreparedWeights, hidden_states, topk_weight, topk_ids, expert_mask=None,
-                out=None):
-    """One layer call through the C ABI (sort -> quantise -> gate-up -> down -> combine)."""
+                out=None, num_local_tokens=None):
+    """One layer call through the C ABI (sort -> quantise -> gate-up -> down -> combine).
+    ``num_local_tokens``: optional int32 device tensor; tokens at and beyond its value are padding
+    (their output rows are zero)."""
     T, H = hidden_states.shape
     if out is None:
         out = torch.empty((T, H), dtype=torch.bfloat16, device=hidden_states.device)
     if T == 0:
         return out
-    _lib.check(_lib.lib().b200moe_forward(
+    _lib.check(_lib.lib().b200moe_forward_dyn(
         ctypes.byref(plan.shape), ctypes.byref(plan.ws), ctypes.c_void_p(plan.base), _ptr(hidden_states),
-        _ptr(topk_ids), _ptr(topk_weight), _ptr(expert_mask), _ptr(pw.w1_data), _ptr(pw.w1_scale),
-        _ptr(pw.w2_data), _ptr(pw.w2_scale), _ptr(out), _stream()), "forward")
+        _ptr(topk_ids), _ptr(topk_weight), _ptr(expert_mask), _ptr(num_local_tokens), _ptr(pw.w1_data),
+        _ptr(pw.w1_scale), _ptr(pw.w2_data), _ptr(pw.w2_scale), _ptr(out), _stream()), "forward")
     return out
 
 
-def capture_forward(plan: MoEPlan, pw, hidden_states, topk_weight, topk_ids, expert_mask=None, out=None):
+def capture_forward(plan: MoEPlan, pw, hidden_states, topk_weight, topk_ids, expert_mask=None, out=None,
+                    num_local_tokens=None):
     """Capture one layer call (five kernel launches, no host synchronisation inside) into a CUDA
     graph.  Returns (graph, out): ``graph.replay()`` re-runs the layer on the same tensors -- the
-    caller refreshes their contents in place between replays.  Decode-sized calls are bound by the
-    host's launch rate rather than by the GPU; a replay removes that cost."""
+    caller refreshes their contents in place between replays, including the int32 device tensor
+    ``num_local_tokens`` when the batch is padded to a fixed T (the reference's use of that argument,
+    src/contrib/fused_moe.py:48-49)."""
     T, H = hidden_states.shape
     if out is None:
         out = torch.empty((T, H), dtype=torch.bfloat16, device=hidden_states.device)
-    moe_forward(plan, pw, hidden_states, topk_weight, topk_ids, expert_mask, out)   # first-use set-up outside capture
+    moe_forward(plan, pw, hidden_states, topk_weight, topk_ids, expert_mask, out, num_local_tokens)   # first-use set-up outside capture
     torch.cuda.synchronize()
     graph = torch.cuda.CUDAGraph()
     with torch.cuda.graph(graph):
-        moe_forward(plan, pw, hidden_states, topk_weight, topk_ids, expert_mask, out)
+        moe_forward(plan, pw, hidden_states, topk_weight, topk_ids, expert_mask, out, num_local_tokens)
     return graph, out
 
 
@@ -315,8 +319,8 @@ def fused_moe(hidden_states, w1, w2, topk_weight, topk_ids, expert_mask=None,
         raise NotImplementedError(f"activation={activation!r}: Silu and Swiglu are implemented")
     if doweight_stage1 or bias1 is not None or bias2 is not None or a1_scale is not None or a2_scale is not None:
         raise NotImplementedError("doweight_stage1 / bias / pre-quantised activations are not implemented")
-    if num_local_tokens is not None or hidden_pad or intermediate_pad:
-        raise NotImplementedError("num_local_tokens / padding arguments are not implemented")
+    if hidden_pad or intermediate_pad:
+        raise NotImplementedError("padding arguments are not implemented")
     if w1_scale is None or w2_scale is None:
         raise ValueError("quantised weights need w1_scale and w2_scale")
     if dtype not in (None, torch.bfloat16):
@@ -337,17 +341,27 @@ def fused_moe(hidden_states, w1, w2, topk_weight, topk_ids, expert_mask=None,
     ids = topk_ids if topk_ids.dtype == torch.int32 else topk_ids.to(torch.int32)
     tw = topk_weight if topk_weight.dtype == torch.float32 else topk_weight.float()
     mask = None if expert_mask is None else expert_mask.to(torch.int32).contiguous()
-    return moe_forward(plan, pw, hidden_states.contiguous(), tw.contiguous(), ids.contiguous(), mask)
+    return moe_forward(plan, pw, hidden_states.contiguous(), tw.contiguous(), ids.contiguous(), mask,
+                       num_local_tokens=_num_local(num_local_tokens, hidden_states.device))
+
+
+def _num_local(num_local_tokens, device):
+    """The reference's num_local_tokens argument (src/contrib/fused_moe.py:48-49): a device tensor holding the
+    number of leading tokens that are real; the rest of the batch is padding."""
+    if num_local_tokens is None:
+        return None
+    if not torch.is_tensor(num_local_tokens):
+        return torch.tensor([int(num_local_tokens)], dtype=torch.int32, device=device)
+    return num_local_tokens.to(device=device, dtype=torch.int32).reshape(-1)[:1].contiguous()
 
 
 def moe_sorting(topk_ids, topk_weights, num_experts, model_dim, moebuf_dtype, block_size=32, expert_mask=None,
                 num_local_tokens=None, dispatch_policy=0):
     """Same outputs as the reference's sorter (src/contrib/fused_moe.py:56-100):
     (sorted_ids, sorted_weights, sorted_expert_ids, num_valid_ids, moe_out)."""
-    if num_local_tokens is not None:
-        raise NotImplementedError("num_local_tokens")
     T, K = topk_ids.shape
     dev = topk_ids.device
+    nlt = _num_local(num_local_tokens, dev)
     nblk = (T * K + num_experts * (block_size - 1) + block_size - 1) // block_size
     sorted_ids = torch.empty(nblk * block_size, dtype=torch.int32, device=dev)
     sorted_w = torch.empty(nblk * block_size, dtype=torch.float32, device=dev)
@@ -355,8 +369,8 @@ def moe_sorting(topk_ids, topk_weights, num_experts, model_dim, moebuf_dtype, bl
     num_valid = torch.empty(2, dtype=torch.int32, device=dev)
     moe_out = torch.zeros((T, model_dim), dtype=moebuf_dtype, device=dev)
     mask = None if expert_mask is None else expert_mask.to(torch.int32).contiguous()
-    _lib.check(_lib.lib().b200moe_sort_align(
+    _lib.check(_lib.lib().b200moe_sort_align_dyn(
         _ptr(topk_ids.to(torch.int32).contiguous()), _ptr(topk_weights.float().contiguous()), T, K, num_experts,
-        block_size, _ptr(mask), _ptr(sorted_ids), _ptr(sorted_w), _ptr(sorted_e), _ptr(num_valid), None,
+        block_size, _ptr(mask), _ptr(nlt), _ptr(sorted_ids), _ptr(sorted_w), _ptr(sorted_e), _ptr(num_valid), None,
         _stream()), "sort_align")
     return sorted_ids, sorted_w, sorted_e, num_valid, moe_out

@@ -258,3 +258,34 @@ def test_varying_token_counts_share_one_workspace():
         ref = orc.torch_moe_oracle_mxfp4(x, *w, tw, ids)
         _assert_close(_run_layer(x, tw, ids, w, block_size_M=64), ref, f"T={T}")
     assert len(fm._workspace_cache) == 1
+
+
+def test_num_local_tokens_padded_batch_and_graph_replay():
+    """A batch padded to a fixed T with the live count on the device (the reference's num_local_tokens,
+    src/contrib/fused_moe.py:48-49): live rows equal the unpadded call bit for bit, padding rows are zero,
+    and one captured graph serves every count."""
+    import importlib
+    fm = importlib.import_module("pyhip_b200.fused_moe")
+    T, H, I, E, K, B = 64, 512, 256, 8, 2, 16
+    x = synth.make_hidden(T, H, 11)
+    tw, ids = synth.make_routing(T, E, K, seed=11)
+    w = tuple(t.to(DEV) for t in synth.make_weights_mxfp4(E, H, I, seed=11))
+    xd, twd, idsd = x.to(DEV), tw.to(DEV), ids.to(DEV)
+    kw = dict(quant_type=QuantType.per_1x32, w1_scale=w[1], w2_scale=w[3], block_size_M=B)
+    n_dev = torch.zeros(1, dtype=torch.int32, device=DEV)
+    pw = fm.prepare_weights(*w)
+    plan = fm.get_plan(T, K, E, E, H, I, B, 0, 7.0, torch.device(DEV))
+    y = torch.empty(T, H, dtype=torch.bfloat16, device=DEV)
+    graph, _ = fm.capture_forward(plan, pw, xd, twd, idsd, None, y, num_local_tokens=n_dev)
+    for n in (40, 1, 64, 0, 17):
+        n_dev.fill_(n)
+        graph.replay()
+        torch.cuda.synchronize()
+        got = y.cpu()
+        assert float(got[n:].float().abs().max()) == 0.0 if n < T else True
+        if n:
+            want = fused_moe(xd[:n], w[0], w[2], twd[:n], idsd[:n], **kw).cpu()
+            assert torch.equal(got[:n], want), n
+        # the public call with a host integer takes the same route
+        assert torch.equal(fused_moe(xd, w[0], w[2], twd, idsd, num_local_tokens=n, **kw).cpu(), got)
+    plan.check_status()

@@ -57,3 +57,24 @@ def test_all_tokens_to_one_expert_and_empty_experts():
     ids = torch.full((T, K), 63, dtype=torch.int32)
     tw = torch.rand(T, K)
     _check(ids, tw, E, 32)
+
+
+@pytest.mark.parametrize("T,n", [(64, 40), (64, 0), (300, 299), (8, 1)])
+def test_num_local_tokens_sorts_only_the_live_prefix(T, n):
+    """With a device-side live count the sorter treats the batch as its first n tokens
+    (src/contrib/fused_moe.py:48-49,63): same rows, same order; only the sentinel keeps the padded T."""
+    E, K, B = 16, 4, 32
+    tw, ids = synth.make_routing(T, E, K, seed=T + n)
+    dev = torch.device("cuda:0")
+    nl = torch.tensor([n], dtype=torch.int32, device=dev)
+    s_ids, s_w, s_e, nv, _ = moe_sorting(ids.to(dev), tw.to(dev), E, 8, torch.bfloat16, B, num_local_tokens=nl)
+    torch.cuda.synchronize()
+    exp = orc.moe_sorting_oracle(ids[:n], tw[:n], E, B)
+    L = int(exp[3][0])
+    assert nv.cpu().tolist() == [L, n]
+    got_ids = s_ids.cpu().numpy().view(np.uint32)[:L]
+    live = (exp[0][:L] >> 24) < K
+    assert np.array_equal(got_ids[live], exp[0][:L][live])
+    assert np.all(got_ids[~live] == ((K << 24) | T))
+    assert np.array_equal(s_w.cpu().numpy()[:L].view(np.uint32), exp[1][:L].view(np.uint32))
+    assert np.array_equal(s_e.cpu().numpy()[:L // B], exp[2][:L // B])
