@@ -19,7 +19,7 @@
 extern "C" {
 #endif
 
-#define B200MOE_VERSION 1
+#define B200MOE_VERSION 2
 
 /* weight formats */
 #define B200MOE_W_MXFP4 0 /* E2M1 pairs (low nibble = even element) + E8M0 scale per 32 along K */
@@ -56,6 +56,7 @@ typedef struct b200moe_workspace {
   int64_t off_hq;            /* u8 [terms, Lmax, Ipad/2]  gate-up output, same form           */
   int64_t off_hsf;           /* E8M0 scale chunks of hq                                      */
   int64_t off_out2;          /* bf16 [Lmax, H]  down-projection rows in sorted order         */
+  int64_t off_sort_scratch;  /* i32 scratch of the multi-CTA sort (large batches only)       */
 } b200moe_workspace;
 
 int b200moe_version(void);
@@ -93,6 +94,16 @@ int b200moe_sort_align_dyn(const int32_t* topk_ids, const float* topk_weight, in
                            int32_t E_route, int32_t B, const int32_t* expert_mask,
                            const int32_t* num_local_tokens, uint32_t* sorted_ids, float* sorted_weights,
                            int32_t* sorted_expert_ids, int32_t* num_valid_ids, int32_t* loc, void* stream);
+
+/* The same with caller scratch of b200moe_sort_scratch_bytes(E_route) bytes: from 8192 (token, expert) pairs
+ * up the sort is spread over several CTAs (three chained launches; one CTA's store path limits the single-CTA
+ * kernel at prefill sizes).  Outputs are bit-identical.  scratch may be NULL (single CTA). */
+int b200moe_sort_scratch_bytes(int32_t E_route, int64_t* bytes);
+int b200moe_sort_align_ws(const int32_t* topk_ids, const float* topk_weight, int32_t T, int32_t K,
+                          int32_t E_route, int32_t B, const int32_t* expert_mask,
+                          const int32_t* num_local_tokens, uint32_t* sorted_ids, float* sorted_weights,
+                          int32_t* sorted_expert_ids, int32_t* num_valid_ids, int32_t* loc, void* scratch,
+                          int64_t scratch_bytes, void* stream);
 
 /* Quantise bf16 rows into `terms` packed-FP4 (E2M1) terms with E8M0 scales per 32, gathered into
  * sorted-row order (stands where the reference calls aiter's per_1x32 activation quantiser

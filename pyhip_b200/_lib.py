@@ -35,7 +35,8 @@ class Shape(ctypes.Structure):
 
 
 _WS_FIELDS = ["total_bytes", "max_rows", "off_sorted_ids", "off_sorted_w", "off_sorted_e",
-              "off_num_valid", "off_loc", "off_status", "off_xq", "off_xsf", "off_hq", "off_hsf", "off_out2"]
+              "off_num_valid", "off_loc", "off_status", "off_xq", "off_xsf", "off_hq", "off_hsf", "off_out2",
+              "off_sort_scratch"]
 
 
 class Workspace(ctypes.Structure):
@@ -45,7 +46,8 @@ class Workspace(ctypes.Structure):
 EXPORTS = ["b200moe_version", "b200moe_last_error", "b200moe_workspace_layout",
            "b200moe_prepared_scale_bytes", "b200moe_prepare_scales", "b200moe_sort_align",
            "b200moe_quant_rows", "b200moe_quant_rows_e4m3", "b200moe_gateup", "b200moe_down", "b200moe_combine",
-           "b200moe_forward", "b200moe_forward_dyn", "b200moe_sort_align_dyn", "b200moe_forward_static", "b200moe_gather_sum", "b200moe_debug_probe"]
+           "b200moe_forward", "b200moe_forward_dyn", "b200moe_sort_align_dyn", "b200moe_sort_align_ws",
+           "b200moe_sort_scratch_bytes", "b200moe_forward_static", "b200moe_gather_sum", "b200moe_debug_probe"]
 
 
 def build(force: bool = False, verbose: bool = False) -> pathlib.Path:
@@ -88,13 +90,15 @@ def lib() -> ctypes.CDLL:
     L.b200moe_forward.argtypes = [sp, wp, vp, vp, vp, vp, vp, vp, vp, vp, vp, vp, vp]
     L.b200moe_forward_dyn.argtypes = [sp, wp, vp, vp, vp, vp, vp, vp, vp, vp, vp, vp, vp, vp]
     L.b200moe_sort_align_dyn.argtypes = [vp, vp, i32, i32, i32, i32, vp, vp, vp, vp, vp, vp, vp, vp]
+    L.b200moe_sort_align_ws.argtypes = [vp, vp, i32, i32, i32, i32, vp, vp, vp, vp, vp, vp, vp, vp, i64, vp]
+    L.b200moe_sort_scratch_bytes.argtypes = [i32, ctypes.POINTER(i64)]
     L.b200moe_forward_static.argtypes = [sp, vp, vp, vp, vp, vp, vp, vp, vp, vp, vp]
     L.b200moe_gather_sum.argtypes = [vp, vp, i32, i32, i32, vp, vp]
     L.b200moe_debug_probe.argtypes = [ctypes.c_int, vp, vp, vp]
     for name in EXPORTS:
         if name not in ("b200moe_version", "b200moe_last_error"):
             getattr(L, name).restype = ctypes.c_int
-    if L.b200moe_version() != 1:
+    if L.b200moe_version() != 2:
         raise RuntimeError("libb200moe.so version mismatch; rebuild it")
     return L
 

@@ -90,6 +90,7 @@ int b200moe_workspace_layout(const b200moe_shape* s, b200moe_workspace* ws) {
     ws->off_hsf = take(nb * (IP / 128) * act_sf_chunks(NT, act_term_stride(s->B, NT, 2)) * kSfChunk);
   }
   ws->off_out2 = take(L * s->H * 2);
+  ws->off_sort_scratch = take(P >= kSortWideMinPairs ? sort_scratch_bytes(s->E_route) : 16);
   ws->total_bytes = off;
   return 0;
 }
@@ -119,11 +120,17 @@ int b200moe_prepare_scales(const b200moe_shape* s, int which, const void* w_s, v
 static int sort_align_impl(const int32_t* topk_ids, const float* topk_weight, int32_t T, int32_t K, int32_t E_route,
                            int32_t B, const int32_t* expert_mask, const int32_t* num_local_tokens, uint32_t* sorted_ids,
                            float* sorted_weights, int32_t* sorted_expert_ids, int32_t* num_valid_ids, int32_t* loc,
-                           void* stream) {
+                           void* scratch, int64_t scratch_bytes, void* stream) {
   B200_CHECK_ARG(T >= 0 && T < (1 << 24) && K >= 1 && K <= 255, "sort_align: T=%d K=%d out of range", T, K);
   B200_CHECK_ARG(B >= 1, "sort_align: B=%d", B);
   B200_CHECK_ARG(sorted_ids && sorted_weights && sorted_expert_ids && num_valid_ids, "sort_align: NULL output");
   B200_CHECK_ARG(T == 0 || (topk_ids && topk_weight), "sort_align: NULL input");
+  // large batches: several CTAs over caller scratch (one CTA's store path limits the single-CTA kernel)
+  if ((int64_t)T * K >= kSortWideMinPairs && scratch != nullptr && scratch_bytes >= sort_scratch_bytes(E_route) &&
+      ((uintptr_t)scratch & 3) == 0)
+    return launch_sort_align_wide(topk_ids, topk_weight, T, K, E_route, B, expert_mask, sorted_ids, sorted_weights,
+                                  sorted_expert_ids, num_valid_ids, loc, num_local_tokens, scratch,
+                                  (cudaStream_t)stream);
   return launch_sort_align(topk_ids, topk_weight, T, K, E_route, B, expert_mask, sorted_ids, sorted_weights,
                            sorted_expert_ids, num_valid_ids, loc, num_local_tokens, (cudaStream_t)stream);
 }
@@ -132,7 +139,7 @@ int b200moe_sort_align(const int32_t* topk_ids, const float* topk_weight, int32_
                        int32_t B, const int32_t* expert_mask, uint32_t* sorted_ids, float* sorted_weights,
                        int32_t* sorted_expert_ids, int32_t* num_valid_ids, int32_t* loc, void* stream) {
   return sort_align_impl(topk_ids, topk_weight, T, K, E_route, B, expert_mask, nullptr, sorted_ids, sorted_weights,
-                         sorted_expert_ids, num_valid_ids, loc, stream);
+                         sorted_expert_ids, num_valid_ids, loc, nullptr, 0, stream);
 }
 
 int b200moe_sort_align_dyn(const int32_t* topk_ids, const float* topk_weight, int32_t T, int32_t K, int32_t E_route,
@@ -140,7 +147,21 @@ int b200moe_sort_align_dyn(const int32_t* topk_ids, const float* topk_weight, in
                            uint32_t* sorted_ids, float* sorted_weights, int32_t* sorted_expert_ids,
                            int32_t* num_valid_ids, int32_t* loc, void* stream) {
   return sort_align_impl(topk_ids, topk_weight, T, K, E_route, B, expert_mask, num_local_tokens, sorted_ids,
-                         sorted_weights, sorted_expert_ids, num_valid_ids, loc, stream);
+                         sorted_weights, sorted_expert_ids, num_valid_ids, loc, nullptr, 0, stream);
+}
+
+int b200moe_sort_scratch_bytes(int32_t E_route, int64_t* bytes) {
+  B200_CHECK_ARG(E_route >= 1 && bytes != nullptr, "sort_scratch_bytes: bad argument");
+  *bytes = sort_scratch_bytes(E_route);
+  return 0;
+}
+
+int b200moe_sort_align_ws(const int32_t* topk_ids, const float* topk_weight, int32_t T, int32_t K, int32_t E_route,
+                          int32_t B, const int32_t* expert_mask, const int32_t* num_local_tokens,
+                          uint32_t* sorted_ids, float* sorted_weights, int32_t* sorted_expert_ids,
+                          int32_t* num_valid_ids, int32_t* loc, void* scratch, int64_t scratch_bytes, void* stream) {
+  return sort_align_impl(topk_ids, topk_weight, T, K, E_route, B, expert_mask, num_local_tokens, sorted_ids,
+                         sorted_weights, sorted_expert_ids, num_valid_ids, loc, scratch, scratch_bytes, stream);
 }
 
 int b200moe_quant_rows(const void* src_bf16, int32_t src_mode, const uint32_t* sorted_ids,
@@ -262,7 +283,8 @@ static int forward_impl(const b200moe_shape* s, const b200moe_workspace* ws, voi
   int rc = sort_align_impl(topk_ids, topk_weight, s->T, s->K, s->E_route, s->B, expert_mask, num_local_tokens,
                            (uint32_t*)(base + ws->off_sorted_ids), (float*)(base + ws->off_sorted_w),
                            (int32_t*)(base + ws->off_sorted_e), (int32_t*)(base + ws->off_num_valid),
-                           (int32_t*)(base + ws->off_loc), stream);
+                           (int32_t*)(base + ws->off_loc), base + ws->off_sort_scratch, sort_scratch_bytes(s->E_route),
+                           stream);
   if (rc) return rc;
   if (s->weight_format == B200MOE_W_FP8_128)
     rc = b200moe_quant_rows_e4m3(x_bf16, 0, (const uint32_t*)(base + ws->off_sorted_ids),

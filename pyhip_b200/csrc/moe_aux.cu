@@ -156,6 +156,199 @@ int launch_sort_align(const int32_t* ids, const float* w, int T, int K, int E, i
 }
 
 // =====================================================================================
+// The same sort spread over several CTAs, for batches whose (token, expert) pairs number in the tens of
+// thousands: one CTA's store path is the limit there (three scattered 4-byte stores per pair).  Three
+// chained launches over caller scratch: per-(CTA, warp) histograms of contiguous slices -> one CTA turns them
+// into offsets (slice order = the required stable order) and does the per-expert part -> every warp
+// scatters its slice.  Bit-identical to the single-CTA kernel.
+// scratch: int32 [slices = G*32][E] histograms/offsets, then [E] first sorted row of each expert.
+// =====================================================================================
+constexpr int kSortMaxCtas = 64;
+
+__host__ __device__ inline int sort_slice_pairs(int P, int G) {       // pairs per CTA: whole warps x 32 lanes
+  return ((P + G - 1) / G + 1023) & ~1023;
+}
+
+__global__ void __launch_bounds__(kSortWarps * 32, 1)
+sort_count_kernel(const int32_t* __restrict__ ids, const int32_t* __restrict__ mask, int T, int K, int E,
+                  const int32_t* __restrict__ num_local, int slice, int32_t* __restrict__ hist) {
+  extern __shared__ int32_t sm[];          // [kSortWarps][E]
+  grid_dep_launch();
+  grid_dep_wait();
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int P = T * K;
+  const int T_live = (num_local != nullptr) ? min(T, max(num_local[0], 0)) : T;
+  const int per_warp = slice / kSortWarps;
+  const int lo = min(P, blockIdx.x * slice + warp * per_warp), hi = min(P, lo + per_warp);
+  const int live_hi = min(hi, T_live * K);
+  int32_t* cnt = sm + warp * E;
+  for (int e = lane; e < E; e += 32) cnt[e] = 0;
+  __syncwarp();
+  for (int i0 = lo; i0 < hi; i0 += 32) {
+    int e = sort_fetch_expert(ids, mask, i0 + lane, live_hi, E);
+    unsigned same = __match_any_sync(0xffffffffu, e);
+    if (e >= 0 && lane == __ffs(same) - 1) cnt[e] += __popc(same);
+    __syncwarp();
+  }
+  int32_t* row = hist + ((int64_t)blockIdx.x * kSortWarps + warp) * E;
+  for (int e = lane; e < E; e += 32) row[e] = cnt[e];
+}
+
+__global__ void __launch_bounds__(kSortWarps * 32, 1)
+sort_scan_kernel(int32_t* __restrict__ hist, int S, int T, int K, int E, int B, const int32_t* __restrict__ mask,
+                 const int32_t* __restrict__ num_local, uint32_t* __restrict__ sorted_ids,
+                 float* __restrict__ sorted_w, int32_t* __restrict__ sorted_e, int32_t* __restrict__ num_valid) {
+  __shared__ int32_t part[kSortWarps * 32];      // partial sums [threads per expert][E]
+  __shared__ int32_t total[kSortWarps * 32], base[kSortWarps * 32], lid[kSortWarps * 32];
+  __shared__ unsigned long long wsum[34];
+  grid_dep_launch();
+  grid_dep_wait();
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  // several threads per expert share the walk over the S slices
+  const int tpe = max(1, (int)blockDim.x / E);
+  const int e_of = tid % E, j = tid / E;
+  const int chunk = (S + tpe - 1) / tpe;
+  const int s0 = min(S, j * chunk), s1 = min(S, s0 + chunk);
+  const bool walker = j < tpe;
+  if (walker) {
+    int sum = 0;
+    for (int sidx = s0; sidx < s1; ++sidx) sum += hist[(int64_t)sidx * E + e_of];
+    part[j * E + e_of] = sum;
+  }
+  __syncthreads();
+  if (walker) {
+    int run = 0;
+    for (int jj = 0; jj < j; ++jj) run += part[jj * E + e_of];
+    for (int sidx = s0; sidx < s1; ++sidx) {
+      const int c = hist[(int64_t)sidx * E + e_of];
+      hist[(int64_t)sidx * E + e_of] = run;
+      run += c;
+    }
+    if (j == tpe - 1) total[e_of] = run;
+  }
+  __syncthreads();
+  const int T_live = (num_local != nullptr) ? min(T, max(num_local[0], 0)) : T;
+  {
+    const int e = tid;
+    int padded = 0, live = 0;
+    if (e < E) {
+      padded = (total[e] + B - 1) / B * B;
+      live = (mask == nullptr || mask[e] != 0) ? 1 : 0;
+    }
+    const unsigned long long v = ((unsigned long long)(unsigned)padded << 32) | (unsigned)live;
+    unsigned long long incl = v;
+    for (int d = 1; d < 32; d <<= 1) {
+      unsigned long long o = __shfl_up_sync(0xffffffffu, incl, d);
+      if (lane >= d) incl += o;
+    }
+    if (lane == 31) wsum[warp] = incl;
+    __syncthreads();
+    if (warp == 0) {
+      const unsigned long long sv = wsum[lane];
+      unsigned long long si = sv;
+      for (int d = 1; d < 32; d <<= 1) {
+        unsigned long long o = __shfl_up_sync(0xffffffffu, si, d);
+        if (lane >= d) si += o;
+      }
+      wsum[lane] = si - sv;
+      if (lane == 31) wsum[32] = si;
+    }
+    __syncthreads();
+    const unsigned long long excl = wsum[warp] + incl - v;
+    if (e < E) {
+      base[e] = (int)(excl >> 32);
+      lid[e] = (int)(excl & 0xffffffffu);
+      hist[(int64_t)S * E + e] = base[e];          // for the scatter launch
+    }
+    if (tid == 0) {
+      num_valid[0] = (int)(wsum[32] >> 32);
+      num_valid[1] = T_live;
+    }
+  }
+  __syncthreads();
+  // padding rows and per-block expert ids: all threads share the rows of all experts
+  const uint32_t sentinel = ((uint32_t)K << 24) | (uint32_t)T;
+  for (int e = warp; e < E; e += kSortWarps) {
+    const int n = total[e];
+    if (n == 0) continue;
+    const int b0 = base[e], n_pad = (n + B - 1) / B * B;
+    for (int p = b0 + n + lane; p < b0 + n_pad; p += 32) {
+      sorted_ids[p] = sentinel;
+      sorted_w[p] = 0.f;
+    }
+    for (int blk = b0 / B + lane; blk < (b0 + n_pad) / B; blk += 32) sorted_e[blk] = lid[e];
+  }
+}
+
+__global__ void __launch_bounds__(kSortWarps * 32, 1)
+sort_scatter_kernel(const int32_t* __restrict__ ids, const float* __restrict__ w, const int32_t* __restrict__ mask,
+                    int T, int K, int E, const int32_t* __restrict__ num_local, int slice, int S,
+                    const int32_t* __restrict__ hist, uint32_t* __restrict__ sorted_ids,
+                    float* __restrict__ sorted_w, int32_t* __restrict__ loc) {
+  extern __shared__ int32_t sm[];          // [kSortWarps][E] running offsets, then [E] expert bases
+  grid_dep_launch();
+  grid_dep_wait();
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int P = T * K;
+  const int T_live = (num_local != nullptr) ? min(T, max(num_local[0], 0)) : T;
+  const int per_warp = slice / kSortWarps;
+  const int lo = min(P, blockIdx.x * slice + warp * per_warp), hi = min(P, lo + per_warp);
+  const int live_hi = min(hi, T_live * K);
+  int32_t* cnt = sm + warp * E;
+  int32_t* base = sm + kSortWarps * E;
+  const int32_t* row = hist + ((int64_t)blockIdx.x * kSortWarps + warp) * E;
+  for (int e = lane; e < E; e += 32) cnt[e] = row[e];
+  for (int e = tid; e < E; e += blockDim.x) base[e] = hist[(int64_t)S * E + e];
+  __syncthreads();
+  const uint32_t lt_mask = (1u << lane) - 1u;
+  for (int i0 = lo; i0 < hi; i0 += 32) {
+    const int i = i0 + lane;
+    int e = sort_fetch_expert(ids, mask, i, live_hi, E);
+    unsigned same = __match_any_sync(0xffffffffu, e);
+    int pos = -1;
+    if (e >= 0) pos = base[e] + cnt[e] + __popc(same & lt_mask);
+    __syncwarp();
+    if (e >= 0 && lane == __ffs(same) - 1) cnt[e] += __popc(same);
+    __syncwarp();
+    if (i < hi) {
+      if (pos >= 0) {
+        sorted_ids[pos] = ((uint32_t)(i % K) << 24) | (uint32_t)(i / K);
+        sorted_w[pos] = w[i];
+      }
+      if (loc != nullptr) loc[i] = pos;
+    }
+  }
+}
+
+int64_t sort_scratch_bytes(int E) { return ((int64_t)kSortMaxCtas * kSortWarps + 1) * E * (int64_t)sizeof(int32_t); }
+
+int launch_sort_align_wide(const int32_t* ids, const float* w, int T, int K, int E, int B, const int32_t* mask,
+                           uint32_t* sorted_ids, float* sorted_w, int32_t* sorted_e, int32_t* num_valid,
+                           int32_t* loc, const int32_t* num_local, void* scratch, cudaStream_t st) {
+  B200_CHECK_ARG(E >= 1 && E <= kSortWarps * 32, "sort_align: E=%d outside [1,%d]", E, kSortWarps * 32);
+  const int P = T * K;
+  const int G = std::max(1, std::min(kSortMaxCtas, (P + 2047) / 2048));
+  const int slice = sort_slice_pairs(P, G);
+  const int S = G * kSortWarps;
+  const size_t smem = (size_t)(kSortWarps * E + E) * sizeof(int32_t);
+  B200_CHECK_ARG(smem <= 200 * 1024, "sort_align: E=%d needs %zu bytes of shared memory", E, smem);
+  static bool attr_set = false;
+  if (!attr_set) {
+    B200_CHECK_CUDA(cudaFuncSetAttribute(sort_count_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
+    B200_CHECK_CUDA(cudaFuncSetAttribute(sort_scatter_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
+    attr_set = true;
+  }
+  int32_t* hist = (int32_t*)scratch;
+  B200_CHECK_CUDA(launch_chained(sort_count_kernel, dim3(G), dim3(kSortWarps * 32), smem, st, ids, mask, T, K, E,
+                                 num_local, slice, hist));
+  B200_CHECK_CUDA(launch_chained(sort_scan_kernel, dim3(1), dim3(kSortWarps * 32), 0, st, hist, S, T, K, E, B, mask,
+                                 num_local, sorted_ids, sorted_w, sorted_e, num_valid));
+  B200_CHECK_CUDA(launch_chained(sort_scatter_kernel, dim3(G), dim3(kSortWarps * 32), smem, st, ids, w, mask, T, K, E,
+                                 num_local, slice, S, (const int32_t*)hist, sorted_ids, sorted_w, loc));
+  return 0;
+}
+
+// =====================================================================================
 // activation quantiser: bf16 row -> NT packed-FP4 (E2M1) terms with per-32 E8M0 scales, written
 // in sorted-row order.  One thread per 32-element block.  Term t quantises what the previous
 // terms left over:

@@ -170,6 +170,9 @@ class MoEPlan:
         off = (-self.buf.data_ptr()) % 1024
         self.base = self.buf.data_ptr() + off
         self._view = self.buf[off:off + self.ws.total_bytes]
+        sb = ctypes.c_int64()
+        _lib.check(_lib.lib().b200moe_sort_scratch_bytes(E_route, ctypes.byref(sb)), "sort_scratch_bytes")
+        self.sort_scratch_bytes = sb.value if T * K >= 8192 else 0     # the layout reserves it from that size up
         self.status().zero_()
 
     def set_tokens(self, T: int):
@@ -199,9 +202,10 @@ class MoEPlan:
     def sort(self, topk_ids, topk_weight, expert_mask=None):
         s = self.shape
         ids_o, w_o, e_o, nv_o, loc_o = self.sort_outputs()
-        _lib.check(_lib.lib().b200moe_sort_align(
-            _ptr(topk_ids), _ptr(topk_weight), s.T, s.K, s.E_route, s.B, _ptr(expert_mask), _ptr(ids_o),
-            _ptr(w_o), _ptr(e_o), _ptr(nv_o), _ptr(loc_o), _stream()), "sort_align")
+        _lib.check(_lib.lib().b200moe_sort_align_ws(
+            _ptr(topk_ids), _ptr(topk_weight), s.T, s.K, s.E_route, s.B, _ptr(expert_mask), None, _ptr(ids_o),
+            _ptr(w_o), _ptr(e_o), _ptr(nv_o), _ptr(loc_o), ctypes.c_void_p(self.base + self.ws.off_sort_scratch),
+            self.sort_scratch_bytes, _stream()), "sort_align")
         return ids_o, w_o, e_o, nv_o, loc_o
 
     def quant_input(self, x):
@@ -369,8 +373,11 @@ def moe_sorting(topk_ids, topk_weights, num_experts, model_dim, moebuf_dtype, bl
     num_valid = torch.empty(2, dtype=torch.int32, device=dev)
     moe_out = torch.zeros((T, model_dim), dtype=moebuf_dtype, device=dev)
     mask = None if expert_mask is None else expert_mask.to(torch.int32).contiguous()
-    _lib.check(_lib.lib().b200moe_sort_align_dyn(
+    sb = ctypes.c_int64()
+    _lib.check(_lib.lib().b200moe_sort_scratch_bytes(num_experts, ctypes.byref(sb)), "sort_scratch_bytes")
+    scratch = torch.empty(sb.value, dtype=torch.uint8, device=dev) if T * K >= 8192 else None   # several CTAs from there
+    _lib.check(_lib.lib().b200moe_sort_align_ws(
         _ptr(topk_ids.to(torch.int32).contiguous()), _ptr(topk_weights.float().contiguous()), T, K, num_experts,
         block_size, _ptr(mask), _ptr(nlt), _ptr(sorted_ids), _ptr(sorted_w), _ptr(sorted_e), _ptr(num_valid), None,
-        _stream()), "sort_align")
+        _ptr(scratch), sb.value if scratch is not None else 0, _stream()), "sort_align")
     return sorted_ids, sorted_w, sorted_e, num_valid, moe_out

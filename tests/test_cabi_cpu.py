@@ -23,12 +23,12 @@ def test_every_declared_symbol_is_exported(L):
     assert declared == set(_lib.EXPORTS)
     for name in declared:
         assert hasattr(L, name), name
-    assert L.b200moe_version() == 1
+    assert L.b200moe_version() == 2
 
 
 def test_struct_sizes_match_header():
     assert ctypes.sizeof(_lib.Shape) == 44
-    assert ctypes.sizeof(_lib.Workspace) == 13 * 8
+    assert ctypes.sizeof(_lib.Workspace) == 14 * 8
 
 
 def test_workspace_layout_arithmetic(L):
