@@ -150,7 +150,9 @@ __device__ __forceinline__ uint4 ld_shared_v4(uint32_t addr) {
 }
 
 // quantise 32 floats to E2M1 with a shared E8M0 scale (same rule as the stand-alone quantiser):
-// q gets 16 bytes (low nibble = even element), x is replaced by the residual
+// q gets 16 bytes (low nibble = even element); with RESIDUAL x is replaced by what the term left
+// (the input of the next term; the last term of a row does not need it)
+template <bool RESIDUAL = true>
 __device__ __forceinline__ int quant_block32_fp4(float (&x)[32], uint4& q) {
   float amax = 0.f;
 #pragma unroll
@@ -164,17 +166,20 @@ __device__ __forceinline__ int quant_block32_fp4(float (&x)[32], uint4& q) {
     const __nv_fp4x2_storage_t pk =
         __nv_cvt_float2_to_fp4x2(make_float2(x[i] * inv, x[i + 1] * inv), __NV_E2M1, cudaRoundNearest);
     w[i >> 3] |= (uint32_t)pk << (((i >> 1) & 3) * 8);
-    __half2_raw h = __nv_cvt_fp4x2_to_halfraw2(pk, __NV_E2M1);
-    const float2 f = __half22float2(*reinterpret_cast<__half2*>(&h));
-    x[i] -= f.x * sc;
-    x[i + 1] -= f.y * sc;
+    if (RESIDUAL) {
+      __half2_raw h = __nv_cvt_fp4x2_to_halfraw2(pk, __NV_E2M1);
+      const float2 f = __half22float2(*reinterpret_cast<__half2*>(&h));
+      x[i] -= f.x * sc;
+      x[i + 1] -= f.y * sc;
+    }
   }
   q = make_uint4(w[0], w[1], w[2], w[3]);
   return e;
 }
 
 // quantise 32 floats to e4m3 with a shared E8M0 scale: e = max(biased_exp(amax) - 7, 0) puts the
-// block maximum in [128, 256) (never saturates); q gets 32 bytes, x is replaced by the residual
+// block maximum in [128, 256) (never saturates); q gets 32 bytes, with RESIDUAL x is replaced by the residual
+template <bool RESIDUAL = true>
 __device__ __forceinline__ int quant_block32_e4m3(float (&x)[32], uint4& q0, uint4& q1) {
   float amax = 0.f;
 #pragma unroll
@@ -188,10 +193,12 @@ __device__ __forceinline__ int quant_block32_e4m3(float (&x)[32], uint4& q0, uin
     const __nv_fp8x2_storage_t pk =
         __nv_cvt_float2_to_fp8x2(make_float2(x[i] * inv, x[i + 1] * inv), __NV_SATFINITE, __NV_E4M3);
     w[i >> 2] |= (uint32_t)pk << ((i & 2) * 8);
-    __half2_raw h = __nv_cvt_fp8x2_to_halfraw2(pk, __NV_E4M3);
-    const float2 f = __half22float2(*reinterpret_cast<__half2*>(&h));
-    x[i] -= f.x * sc;
-    x[i + 1] -= f.y * sc;
+    if (RESIDUAL) {
+      __half2_raw h = __nv_cvt_fp8x2_to_halfraw2(pk, __NV_E4M3);
+      const float2 f = __half22float2(*reinterpret_cast<__half2*>(&h));
+      x[i] -= f.x * sc;
+      x[i + 1] -= f.y * sc;
+    }
   }
   q0 = make_uint4(w[0], w[1], w[2], w[3]);
   q1 = make_uint4(w[4], w[5], w[6], w[7]);

@@ -395,7 +395,7 @@ quant_rows_kernel(const __nv_bfloat16* __restrict__ src, int src_mode, const uin
     }
     for (int t = 0; t < NT; ++t) {
       uint4 pk;
-      const int e = quant_block32_fp4(x, pk);
+      const int e = (t + 1 < NT) ? quant_block32_fp4<true>(x, pk) : quant_block32_fp4<false>(x, pk);
       *reinterpret_cast<uint4*>(q + t * term_stride + r * (KP / 2) + j * 16) = pk;
       sf[act_sf_index(r / B, j >> 2, KB, B, NT, TS, t, (int)(r % B), j & 3)] = (uint8_t)e;
     }
@@ -458,7 +458,7 @@ quant_rows_e4m3_kernel(const __nv_bfloat16* __restrict__ src, int src_mode, cons
 #pragma unroll
     for (int t = 0; t < 2; ++t) {
       uint4 q0, q1;
-      const int e = quant_block32_e4m3(x, q0, q1);
+      const int e = (t == 0) ? quant_block32_e4m3<true>(x, q0, q1) : quant_block32_e4m3<false>(x, q0, q1);
       uint4* dst = reinterpret_cast<uint4*>(q + t * term_stride + r * Kd + j * 32);
       dst[0] = q0;
       dst[1] = q1;

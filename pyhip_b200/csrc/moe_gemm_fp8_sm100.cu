@@ -274,7 +274,7 @@ __global__ void __launch_bounds__(kThreads, 1) moe_grouped_gemm_fp8_kernel(const
   #pragma unroll
             for (int t = 0; t < kTerms; ++t) {
               uint4 q0, q1;
-              const int ex = quant_block32_e4m3(x, q0, q1);
+              const int ex = (t + 1 < kTerms) ? quant_block32_e4m3<true>(x, q0, q1) : quant_block32_e4m3<false>(x, q0, q1);
               uint4* dst = reinterpret_cast<uint4*>(p.oq + t * p.oq_term_stride + r * p.out_k + m * kTileM + q * 32);
               dst[0] = q0;
               dst[1] = q1;

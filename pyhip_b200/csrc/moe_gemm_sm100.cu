@@ -449,7 +449,7 @@ moe_grouped_gemm_kernel(const __grid_constant__ GemmParams p) {
           const int64_t r = (int64_t)r0 + n;
           for (int t = 0; t < NT; ++t) {
             uint4 pk;
-            const int e = quant_block32_fp4(x, pk);
+            const int e = (t + 1 < NT) ? quant_block32_fp4<true>(x, pk) : quant_block32_fp4<false>(x, pk);
             *reinterpret_cast<uint4*>(p.oq + t * p.oq_term_stride + r * oq_pitch + (m * kTileM + q * 32) / 2) = pk;
             p.osf[act_sf_index(b, m, p.out_kb, B, NT, p.out_ts, t, n, q)] = (uint8_t)e;
           }
