@@ -161,7 +161,7 @@ int launch_sort_align(const int32_t* ids, const float* w, int T, int K, int E, i
 // chained launches over caller scratch: per-(CTA, warp) histograms of contiguous slices -> one CTA turns them
 // into offsets (slice order = the required stable order) and does the per-expert part -> every warp
 // scatters its slice.  Bit-identical to the single-CTA kernel.
-// scratch: int32 [slices = G*32][E] histograms/offsets, then [E] first sorted row of each expert.
+// scratch: int32 [slices = G*32][E] histograms, [slices][E] offsets, then [E] first sorted row of each expert.
 // =====================================================================================
 constexpr int kSortMaxCtas = 64;
 
@@ -195,7 +195,8 @@ sort_count_kernel(const int32_t* __restrict__ ids, const int32_t* __restrict__ m
 }
 
 __global__ void __launch_bounds__(kSortWarps * 32, 1)
-sort_scan_kernel(int32_t* __restrict__ hist, int S, int T, int K, int E, int B, const int32_t* __restrict__ mask,
+sort_scan_kernel(const int32_t* __restrict__ hist, int32_t* __restrict__ offs, int S, int T, int K, int E, int B,
+                 const int32_t* __restrict__ mask,
                  const int32_t* __restrict__ num_local, uint32_t* __restrict__ sorted_ids,
                  float* __restrict__ sorted_w, int32_t* __restrict__ sorted_e, int32_t* __restrict__ num_valid) {
   __shared__ int32_t part[kSortWarps * 32];      // partial sums [threads per expert][E]
@@ -219,9 +220,10 @@ sort_scan_kernel(int32_t* __restrict__ hist, int S, int T, int K, int E, int B, 
   if (walker) {
     int run = 0;
     for (int jj = 0; jj < j; ++jj) run += part[jj * E + e_of];
+    // counts are read from one array and offsets written to another, so the loads do not wait for the stores
     for (int sidx = s0; sidx < s1; ++sidx) {
       const int c = hist[(int64_t)sidx * E + e_of];
-      hist[(int64_t)sidx * E + e_of] = run;
+      offs[(int64_t)sidx * E + e_of] = run;
       run += c;
     }
     if (j == tpe - 1) total[e_of] = run;
@@ -258,7 +260,7 @@ sort_scan_kernel(int32_t* __restrict__ hist, int S, int T, int K, int E, int B, 
     if (e < E) {
       base[e] = (int)(excl >> 32);
       lid[e] = (int)(excl & 0xffffffffu);
-      hist[(int64_t)S * E + e] = base[e];          // for the scatter launch
+      offs[(int64_t)S * E + e] = base[e];          // for the scatter launch
     }
     if (tid == 0) {
       num_valid[0] = (int)(wsum[32] >> 32);
@@ -320,7 +322,7 @@ sort_scatter_kernel(const int32_t* __restrict__ ids, const float* __restrict__ w
   }
 }
 
-int64_t sort_scratch_bytes(int E) { return ((int64_t)kSortMaxCtas * kSortWarps + 1) * E * (int64_t)sizeof(int32_t); }
+int64_t sort_scratch_bytes(int E) { return (2ll * kSortMaxCtas * kSortWarps + 1) * E * (int64_t)sizeof(int32_t); }
 
 int launch_sort_align_wide(const int32_t* ids, const float* w, int T, int K, int E, int B, const int32_t* mask,
                            uint32_t* sorted_ids, float* sorted_w, int32_t* sorted_e, int32_t* num_valid,
@@ -341,10 +343,11 @@ int launch_sort_align_wide(const int32_t* ids, const float* w, int T, int K, int
   int32_t* hist = (int32_t*)scratch;
   B200_CHECK_CUDA(launch_chained(sort_count_kernel, dim3(G), dim3(kSortWarps * 32), smem, st, ids, mask, T, K, E,
                                  num_local, slice, hist));
-  B200_CHECK_CUDA(launch_chained(sort_scan_kernel, dim3(1), dim3(kSortWarps * 32), 0, st, hist, S, T, K, E, B, mask,
-                                 num_local, sorted_ids, sorted_w, sorted_e, num_valid));
+  int32_t* offs = hist + (int64_t)S * E;
+  B200_CHECK_CUDA(launch_chained(sort_scan_kernel, dim3(1), dim3(kSortWarps * 32), 0, st, (const int32_t*)hist, offs, S,
+                                 T, K, E, B, mask, num_local, sorted_ids, sorted_w, sorted_e, num_valid));
   B200_CHECK_CUDA(launch_chained(sort_scatter_kernel, dim3(G), dim3(kSortWarps * 32), smem, st, ids, w, mask, T, K, E,
-                                 num_local, slice, S, (const int32_t*)hist, sorted_ids, sorted_w, loc));
+                                 num_local, slice, S, (const int32_t*)offs, sorted_ids, sorted_w, loc));
   return 0;
 }
 
