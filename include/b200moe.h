@@ -77,6 +77,14 @@ int b200moe_prepared_scale_bytes(const b200moe_shape* shape, int which, int64_t*
 int b200moe_prepare_scales(const b200moe_shape* shape, int which, const void* w_s, void* out_scale,
                            void* stream);
 
+/* Router: fp32 logits [T, E] -> top-k ids [T, K] (descending score, ties to the lower id) and weights [T, K].
+ * The reference leaves routing outside the operator (torch.topk in tests/contrib/moe/test_moe_sorting.py:81-84,
+ * aiter's fused_topk in tests/contrib/moe/test_fused_moe.py:38,87); this is that step as one launch in front of
+ * b200moe_sort_align.  scoring 0 = softmax, 1 = sigmoid; renormalize != 0 divides the k weights by their sum.
+ * E <= 1024. */
+int b200moe_route_topk(const float* logits, int32_t T, int32_t E, int32_t K, int32_t scoring,
+                       int32_t renormalize, int32_t* topk_ids, float* topk_weight, void* stream);
+
 /* Token->expert sort/align: replaces aiter.moe_sorting as called at src/contrib/fused_moe.py:283,
  * 301-305 and 368-372 (contract: fused_moe.py:56-100; ck_tile reference_moe_sorting.hpp:14-117).
  * Deterministic; only [0, num_valid[0]) of the outputs is defined.  expert_mask may be NULL.

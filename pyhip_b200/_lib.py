@@ -47,7 +47,7 @@ EXPORTS = ["b200moe_version", "b200moe_last_error", "b200moe_workspace_layout",
            "b200moe_prepared_scale_bytes", "b200moe_prepare_scales", "b200moe_sort_align",
            "b200moe_quant_rows", "b200moe_quant_rows_e4m3", "b200moe_gateup", "b200moe_down", "b200moe_combine",
            "b200moe_forward", "b200moe_forward_dyn", "b200moe_sort_align_dyn", "b200moe_sort_align_ws",
-           "b200moe_sort_scratch_bytes", "b200moe_forward_static", "b200moe_gather_sum", "b200moe_debug_probe"]
+           "b200moe_sort_scratch_bytes", "b200moe_route_topk", "b200moe_forward_static", "b200moe_gather_sum", "b200moe_debug_probe"]
 
 
 def build(force: bool = False, verbose: bool = False) -> pathlib.Path:
@@ -92,6 +92,7 @@ def lib() -> ctypes.CDLL:
     L.b200moe_sort_align_dyn.argtypes = [vp, vp, i32, i32, i32, i32, vp, vp, vp, vp, vp, vp, vp, vp]
     L.b200moe_sort_align_ws.argtypes = [vp, vp, i32, i32, i32, i32, vp, vp, vp, vp, vp, vp, vp, vp, i64, vp]
     L.b200moe_sort_scratch_bytes.argtypes = [i32, ctypes.POINTER(i64)]
+    L.b200moe_route_topk.argtypes = [vp, i32, i32, i32, i32, i32, vp, vp, vp]
     L.b200moe_forward_static.argtypes = [sp, vp, vp, vp, vp, vp, vp, vp, vp, vp, vp]
     L.b200moe_gather_sum.argtypes = [vp, vp, i32, i32, i32, vp, vp]
     L.b200moe_debug_probe.argtypes = [ctypes.c_int, vp, vp, vp]

@@ -318,6 +318,13 @@ int b200moe_forward_dyn(const b200moe_shape* s, const b200moe_workspace* ws, voi
                       w2_q, w2_scale, y_bf16, stream);
 }
 
+int b200moe_route_topk(const float* logits, int32_t T, int32_t E, int32_t K, int32_t scoring, int32_t renormalize,
+                       int32_t* topk_ids, float* topk_weight, void* stream) {
+  B200_CHECK_ARG(T >= 0, "route_topk: T=%d", T);
+  B200_CHECK_ARG(T == 0 || (logits && topk_ids && topk_weight), "route_topk: NULL pointer");
+  return launch_route_topk(logits, T, E, K, scoring, renormalize, topk_ids, topk_weight, (cudaStream_t)stream);
+}
+
 int b200moe_gather_sum(const void* rows_bf16, const int32_t* pos, int32_t T, int32_t slots, int32_t H, void* y_bf16,
                        void* stream) {
   B200_CHECK_ARG(T >= 0 && slots >= 1 && H > 0, "gather_sum: bad sizes T=%d slots=%d H=%d", T, slots, H);

@@ -61,6 +61,8 @@ int64_t sort_scratch_bytes(int E);
 int launch_sort_align_wide(const int32_t* ids, const float* w, int T, int K, int E, int B, const int32_t* mask,
                            uint32_t* sorted_ids, float* sorted_w, int32_t* sorted_e, int32_t* num_valid,
                            int32_t* loc, const int32_t* num_local, void* scratch, cudaStream_t st);
+int launch_route_topk(const float* logits, int T, int E, int K, int scoring, int renorm, int32_t* ids, float* weights,
+                      cudaStream_t st);
 int launch_quant_rows(const void* src, int src_mode, const uint32_t* sorted_ids, const int32_t* num_valid,
                       int T, int K, int Kd, int B, int NT, int64_t max_rows, void* q, void* sf, cudaStream_t st);
 int launch_gather_sum(const void* rows, const int32_t* pos, void* y, int T, int S, int H, cudaStream_t st);

@@ -582,6 +582,90 @@ int launch_gather_sum(const void* rows, const int32_t* pos, void* y, int T, int 
 }
 
 // =====================================================================================
+// router: fp32 logits [T, E] -> top-k expert ids (descending score, ties to the lower id) and weights.
+// One warp per token; lane l holds experts l, l+32, ...  softmax scores are exp(x - max) / sum, sigmoid
+// scores 1 / (1 + exp(-x)); with `renorm` the k weights are divided by their sum (the softmax
+// denominator cancels there, so it is never formed).
+// =====================================================================================
+constexpr int kRouteMaxPerLane = 32;          // E <= 1024
+
+__global__ void __launch_bounds__(256)
+route_topk_kernel(const float* __restrict__ logits, int T, int E, int K, int scoring, int renorm,
+                  int32_t* __restrict__ ids, float* __restrict__ weights) {
+  grid_dep_launch();
+  grid_dep_wait();
+  const int lane = threadIdx.x & 31;
+  const int warps_per_cta = blockDim.x >> 5;
+  for (int t = blockIdx.x * warps_per_cta + (threadIdx.x >> 5); t < T; t += gridDim.x * warps_per_cta) {
+    const float* row = logits + (int64_t)t * E;
+    float v[kRouteMaxPerLane];
+    float mx = -INFINITY;
+#pragma unroll
+    for (int i = 0; i < kRouteMaxPerLane; ++i) {
+      const int e = lane + 32 * i;
+      v[i] = (e < E) ? row[e] : -INFINITY;
+      mx = fmaxf(mx, v[i]);
+    }
+    for (int d = 16; d > 0; d >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, d));
+    float sum = 0.f;
+#pragma unroll
+    for (int i = 0; i < kRouteMaxPerLane; ++i) {
+      const int e = lane + 32 * i;
+      if (e < E) {
+        v[i] = (scoring == 0) ? expf(v[i] - mx) : 1.f / (1.f + expf(-v[i]));
+        sum += v[i];
+      } else {
+        v[i] = -1.f;            // scores are non-negative: never selected
+      }
+    }
+    for (int d = 16; d > 0; d >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, d);
+    const float inv_all = (scoring == 0) ? 1.f / sum : 1.f;
+    float wsum = 0.f, my_w = 0.f;     // lane k keeps the k-th selection
+    int my_id = 0;
+    for (int k = 0; k < K; ++k) {
+      float best = -1.f;
+      int best_e = 0x7fffffff;
+#pragma unroll
+      for (int i = 0; i < kRouteMaxPerLane; ++i) {
+        const int e = lane + 32 * i;
+        if (v[i] > best) { best = v[i]; best_e = e; }     // ascending e within the lane: ties keep the lower id
+      }
+      for (int d = 16; d > 0; d >>= 1) {
+        const float ob = __shfl_xor_sync(0xffffffffu, best, d);
+        const int oe = __shfl_xor_sync(0xffffffffu, best_e, d);
+        if (ob > best || (ob == best && oe < best_e)) { best = ob; best_e = oe; }
+      }
+#pragma unroll
+      for (int i = 0; i < kRouteMaxPerLane; ++i)
+        if (lane + 32 * i == best_e) v[i] = -1.f;
+      wsum += best;
+      if ((k & 31) == lane) { my_w = best; my_id = best_e; }
+      if ((k & 31) == 31 || k == K - 1) {          // flush a group of up to 32 selections (K > 32 is unusual)
+        const int k0 = k & ~31;
+        if (k0 + lane <= k) {
+          ids[(int64_t)t * K + k0 + lane] = my_id;
+          weights[(int64_t)t * K + k0 + lane] = my_w;      // scaled below
+        }
+      }
+    }
+    __syncwarp();
+    const float scale = renorm ? 1.f / wsum : inv_all;
+    for (int k = lane; k < K; k += 32) weights[(int64_t)t * K + k] *= scale;
+  }
+}
+
+int launch_route_topk(const float* logits, int T, int E, int K, int scoring, int renorm, int32_t* ids, float* weights,
+                      cudaStream_t st) {
+  B200_CHECK_ARG(E >= 1 && E <= 32 * kRouteMaxPerLane && K >= 1 && K <= E, "route_topk: E=%d K=%d", E, K);
+  B200_CHECK_ARG(scoring == 0 || scoring == 1, "route_topk: scoring=%d (0 softmax, 1 sigmoid)", scoring);
+  if (T == 0) return 0;
+  const int blocks = std::min((T + 7) / 8, 148 * 8);
+  B200_CHECK_CUDA(launch_chained(route_topk_kernel, dim3(blocks), dim3(256), 0, st, logits, T, E, K, scoring, renorm, ids,
+                                 weights));
+  return 0;
+}
+
+// =====================================================================================
 // weight-scale repack: [E, R, Kd/32] bytes -> [E, MT, KB, 2, 512] chunks in tensor-memory order.
 // A chunk = 128 rows x 4 scales.  The two chunks of a group are the tiles one pipeline stage
 // carries: gate rows [mt*128, +128) and up rows I + [mt*128, +128) of w1 (R = 2I), or rows

@@ -349,6 +349,24 @@ def fused_moe(hidden_states, w1, w2, topk_weight, topk_ids, expert_mask=None,
                        num_local_tokens=_num_local(num_local_tokens, hidden_states.device))
 
 
+def fused_topk(hidden_states, gating_output, topk: int, renormalize: bool = True, scoring: str = "softmax"):
+    """Router step with the call shape of aiter's fused_topk as the reference uses it
+    (tests/contrib/moe/test_fused_moe.py:38,87): fp32 logits [T, E] -> (topk_weights f32 [T, topk],
+    topk_ids i32 [T, topk]), ids in descending score order.  `hidden_states` is only consulted for the
+    token count, as in the reference."""
+    if not gating_output.is_cuda:
+        raise RuntimeError("fused_topk runs on a CUDA device only (sm_100a); there is no CPU path")
+    T, E = gating_output.shape
+    if hidden_states is not None and hidden_states.shape[0] != T:
+        raise ValueError("hidden_states and gating_output disagree on the token count")
+    logits = gating_output.float().contiguous()
+    ids = torch.empty(T, topk, dtype=torch.int32, device=logits.device)
+    w = torch.empty(T, topk, dtype=torch.float32, device=logits.device)
+    _lib.check(_lib.lib().b200moe_route_topk(_ptr(logits), T, E, topk, {"softmax": 0, "sigmoid": 1}[scoring],
+                                             1 if renormalize else 0, _ptr(ids), _ptr(w), _stream()), "route_topk")
+    return w, ids
+
+
 def _num_local(num_local_tokens, device):
     """The reference's num_local_tokens argument (src/contrib/fused_moe.py:48-49): a device tensor holding the
     number of leading tokens that are real; the rest of the batch is padding."""
