@@ -11,7 +11,9 @@ convention (`expert_mask`, src/contrib/fused_moe.py:134,210-212) and a single-pr
   3. the local fused-MoE on the received rows (ids re-based to the local range; ids owned by
      other ranks fall outside [0, E_local) and are dropped by the sorter),
   4. combine all-to-all-v of the per-rank partial outputs back to the source rank, summed there
-     in fp32 in ascending rank (= ascending expert) order.
+     in fp32 in ascending rank (= ascending expert) order by one kernel (`gather_sum`).
+The plan of step 2 (`plan_positions`) has no data-dependent shapes, so the counts exchanged in
+step 1 are the only values the host reads in a call.
 
 For small batches (decode) the exchange degenerates gracefully into its fixed-shape form: every
 rank receives every token (all-gather of rows and routing), runs its local experts on all of them
@@ -20,8 +22,8 @@ shapes from step to step -- at T <= `small_batch` tokens per rank the bytes are 
 two latencies saved are not.
 
 All collectives are NCCL (`torch.distributed`); device kernels never touch peer memory.  The
-integer plumbing (`plan_dispatch`, `scatter_back`) is backend-agnostic and is exercised with gloo
-CPU ranks in the tests.
+integer plumbing (`plan_positions`, and the compact `plan_dispatch` / `scatter_back` pair the tests
+compare it with) is backend-agnostic and is exercised with gloo CPU ranks in the tests.
 """
 from __future__ import annotations
 
