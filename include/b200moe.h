@@ -117,8 +117,9 @@ int b200moe_sort_align_ws(const int32_t* topk_ids, const float* topk_weight, int
  * sorted-row order (stands where the reference calls aiter's per_1x32 activation quantiser
  * followed by moe_mxfp4_sort, tests/contrib/moe/test_moe.py:665-679).
  *   src_mode 0: src is [T, Kd], row = token.   src_mode 1: src is [T, K, Kd], row = token*K + k.
- *   q: u8 [terms, max_rows, Kpad/2], Kpad = Kd rounded up to 128.  sf: per (block of B sorted
- *   rows, 128-wide k-block) a group of 512-byte chunks. */
+ *   q: u8 [terms, max_rows, Kpad/2], Kpad = Kd rounded up to 256.  sf: per (block of B sorted
+ *   rows, 128-wide k-block) a group of 512-byte chunks.  Only the rows of live (token, k) pairs are
+ *   written; the padding rows of a block stay as they were. */
 int b200moe_quant_rows(const void* src_bf16, int32_t src_mode, const uint32_t* sorted_ids,
                        const int32_t* num_valid_ids, int32_t T, int32_t K, int32_t Kd, int32_t B,
                        int32_t terms, int64_t max_rows, void* q, void* sf, void* stream);

@@ -376,7 +376,10 @@ quant_rows_kernel(const __nv_bfloat16* __restrict__ src, int src_mode, const uin
     const int j = (int)(g % nb);
     const uint32_t id = sorted_ids[r];
     const int tok = (int)(id & 0xFFFFFFu), kk = (int)(id >> 24);
-    const bool valid = (kk < K) && (tok < T) && (j * 32 < Kd);
+    // padding rows of a block are left unwritten: every token column of the GEMMs depends on its own row
+    // only, and no kernel reads the columns of padding rows
+    if (kk >= K || tok >= T) continue;
+    const bool valid = j * 32 < Kd;       // blocks of the K padding are written as zeros (finite scales)
     float x[32];
     if (valid) {
       const int64_t srow = (src_mode == 0) ? (int64_t)tok : ((int64_t)tok * K + kk);
@@ -438,7 +441,8 @@ quant_rows_e4m3_kernel(const __nv_bfloat16* __restrict__ src, int src_mode, cons
     const int j = (int)(g % nb);
     const uint32_t id = sorted_ids[r];
     const int tok = (int)(id & 0xFFFFFFu), kk = (int)(id >> 24);
-    const bool valid = (kk < K) && (tok < T);
+    if (kk >= K || tok >= T) continue;    // padding rows are left unwritten (see quant_rows_kernel)
+    const bool valid = true;
     float x[32];
     if (valid) {
       const int64_t srow = (src_mode == 0) ? (int64_t)tok : ((int64_t)tok * K + kk);
