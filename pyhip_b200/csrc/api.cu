@@ -226,6 +226,9 @@ int b200moe_gateup(const b200moe_shape* s, const b200moe_workspace* ws, void* wo
     return launch_grouped_gemm_fp8(g, (cudaStream_t)stream);
   }
   g.out_kp = (int)kp_of(s->I);
+  // the rows of the down projection are not live yet: their region serves as staging scratch of the gate-up
+  g.gstage = base + ws->off_out2;
+  g.gstage_bytes = ws->max_rows * (int64_t)s->H * 2;
   return launch_grouped_gemm(g, (cudaStream_t)stream);
 }
 

@@ -95,6 +95,8 @@ struct GemmArgs {
   void* oq; void* osf;   // gate-up fused re-quantisation ([NT, max_rows, out_kp/2] + scale chunks)
   int out_kp;          // row pitch of oq_* (I padded to 128) and chunk count per row block
   void* out2;          // down: bf16 [max_rows, H]
+  void* gstage;        // gate-up: scratch for per-CTA staging tiles in global memory (may be null)
+  int64_t gstage_bytes;
 };
 int launch_grouped_gemm(const GemmArgs& a, cudaStream_t st);
 // FP8 128x128-block variant (moe_gemm_fp8_sm100.cu): w_data = e4m3 bytes [E, parts*rows, Kd], w_scale = fp32

@@ -77,6 +77,7 @@ struct GemmParams {
   int64_t oq_term_stride;
   int B, NT, rows, KB, MT, E, topk, T, stages, out_kp, out_kb, out_ts, activation;
   int k_tail_steps;    // 64-wide k-steps of the last stage that hold data (the rest of it is zero padding)
+  uint8_t* gstage;     // per-CTA staging tiles in global memory (L2) instead of shared memory, or null
   float swiglu_limit;
 };
 
@@ -339,6 +340,8 @@ moe_grouped_gemm_kernel(const __grid_constant__ GemmParams p) {
     const int row_local = quad * 32 + lane;
     const int64_t oq_pitch = p.out_kp / 2;
     const uint32_t stg = stage0 + (uint32_t)S * geo.stage_bytes;   // bf16 staging tile [B][kStagePitch]
+    // the same tile in global memory (it stays in L2) when that frees the shared memory of one more pipeline stage
+    uint8_t* const gstg = p.gstage ? p.gstage + (size_t)blockIdx.x * B * kStagePitch : nullptr;
     const bool fused = GATEUP && p.h_out == nullptr;
     int acc = 0;
     uint32_t acc_phase = 0;
@@ -405,9 +408,17 @@ moe_grouped_gemm_kernel(const __grid_constant__ GemmParams p) {
                 __nv_bfloat162 v = gateup_act2(__uint_as_float(g[n]), __uint_as_float(u[n]), __uint_as_float(g[n + 1]),
                                                __uint_as_float(u[n + 1]), p.activation, p.swiglu_limit);
                 if (!j_ok) v = __floats2bfloat162_rn(0.f, 0.f);
-                st_shared_u16(stg + (uint32_t)(c0 + n) * kStagePitch + row_local * 2, __bfloat16_as_ushort(v.x));
-                if (c0 + n + 1 < nvalid)
-                  st_shared_u16(stg + (uint32_t)(c0 + n + 1) * kStagePitch + row_local * 2, __bfloat16_as_ushort(v.y));
+                if (gstg) {
+                  *reinterpret_cast<unsigned short*>(gstg + (size_t)(c0 + n) * kStagePitch + row_local * 2) =
+                      __bfloat16_as_ushort(v.x);
+                  if (c0 + n + 1 < nvalid)
+                    *reinterpret_cast<unsigned short*>(gstg + (size_t)(c0 + n + 1) * kStagePitch + row_local * 2) =
+                        __bfloat16_as_ushort(v.y);
+                } else {
+                  st_shared_u16(stg + (uint32_t)(c0 + n) * kStagePitch + row_local * 2, __bfloat16_as_ushort(v.x));
+                  if (c0 + n + 1 < nvalid)
+                    st_shared_u16(stg + (uint32_t)(c0 + n + 1) * kStagePitch + row_local * 2, __bfloat16_as_ushort(v.y));
+                }
               }
             }
           }
@@ -437,7 +448,8 @@ moe_grouped_gemm_kernel(const __grid_constant__ GemmParams p) {
           float x[32];
 #pragma unroll
           for (int v4 = 0; v4 < 4; ++v4) {
-            const uint4 raw = ld_shared_v4(stg + (uint32_t)n * kStagePitch + q * 64 + v4 * 16);
+            const uint4 raw = gstg ? __ldcg(reinterpret_cast<const uint4*>(gstg + (size_t)n * kStagePitch + q * 64 + v4 * 16))
+                                   : ld_shared_v4(stg + (uint32_t)n * kStagePitch + q * 64 + v4 * 16);
             const __nv_bfloat162* b2 = reinterpret_cast<const __nv_bfloat162*>(&raw);
 #pragma unroll
             for (int t = 0; t < 4; ++t) {
@@ -581,8 +593,16 @@ int launch_grouped_gemm(const GemmArgs& a, cudaStream_t st) {
   }
 
   const StageGeom geo = stage_geom(2, a.N, a.NT);
-  const int staging = (a.gateup && a.h_out == nullptr) ? a.N * kStagePitch : 0;
+  int staging = (a.gateup && a.h_out == nullptr) ? a.N * kStagePitch : 0;
   int stages = (kSmemLimit - 2048 - staging) / geo.stage_bytes;
+  // two stages are too few to cover the load latency: where moving the staging tile of the fused epilogue to
+  // global memory (one tile per CTA, L2-resident) buys a third, do that
+  if (staging && stages < 3 && (kSmemLimit - 2048) / geo.stage_bytes >= 3 && a.gstage != nullptr &&
+      a.gstage_bytes >= (int64_t)device_sm_count() * staging) {
+    p.gstage = (uint8_t*)a.gstage;
+    staging = 0;
+    stages = (kSmemLimit - 2048) / geo.stage_bytes;
+  }
   stages = std::min(stages, kMaxStages);
   B200_CHECK_ARG(stages >= 2, "grouped gemm: tile does not fit shared memory");
   p.stages = stages;
