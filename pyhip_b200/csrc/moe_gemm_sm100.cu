@@ -228,7 +228,26 @@ moe_grouped_gemm_kernel(const __grid_constant__ GemmParams p) {
     bool ok = true;
     long long t_wait_acc = 0, t_wait_full = 0;
     const long long t_begin = clock64();
+    // Per-term MMAs cover only the live rows of the block (rounded up to 16): the padding rows that end an
+    // expert's last block cost neither tensor time nor operand reads.  The row ids of the NEXT item are
+    // fetched while the current one is multiplied, so the count is ready without a stall.
+    uint32_t nid[4];
+    auto fetch_ids = [&](int w, uint32_t (&r)[4]) {
+      const int r0 = (w / p.MT) * B;
+#pragma unroll
+      for (int q = 0; q < 4; ++q) r[q] = (w < total_work && q * 32 + lane < B) ? p.sorted_ids[r0 + q * 32 + lane] : 0xFFFFFFFFu;
+    };
+    fetch_ids(blockIdx.x, nid);
     for (int w = blockIdx.x; w < total_work && ok; w += gridDim.x) {
+      int nlive = 0;
+#pragma unroll
+      for (int q = 0; q < 4; ++q)
+        nlive += __popc(__ballot_sync(0xffffffffu, (int)(nid[q] >> 24) < p.topk && (int)(nid[q] & 0xFFFFFFu) < p.T));
+      fetch_ids(w + gridDim.x, nid);
+      const uint32_t n_mma = merged ? (uint32_t)ncol : (uint32_t)min(B, max(16, (nlive + 15) & ~15));
+      uint32_t idesc_w[2];
+#pragma unroll
+      for (int s = 0; s < 2; ++s) idesc_w[s] = (idesc[s] & ~(0x3Fu << 17)) | ((n_mma >> 3) << 17);
       const long long ta0 = clock64();
       if (!mbar_wait(smem_u32(&ctl->tmem_empty[acc]), acc_phase ^ 1, abort_word, 0x200 + acc)) break;
       t_wait_acc += clock64() - ta0;
@@ -255,7 +274,7 @@ moe_grouped_gemm_kernel(const __grid_constant__ GemmParams p) {
 #pragma unroll
             for (int s = 0; s < 2 * kSub; ++s) {
               const uint32_t sa = sfa_t + 8 * (s >> 1), sb = sfb_t + 16 * (s >> 1);
-              if (s < nsteps) umma_mxf4(d0, a_lo + 2 * s, b_lo + 2 * s, idesc[s & 1], sa, sb, s == 0 ? first : 1u);
+              if (s < nsteps) umma_mxf4(d0, a_lo + 2 * s, b_lo + 2 * s, idesc_w[s & 1], sa, sb, s == 0 ? first : 1u);
             }
           } else {
 #pragma unroll
@@ -265,7 +284,7 @@ moe_grouped_gemm_kernel(const __grid_constant__ GemmParams p) {
               for (int t = 0; t < kMaxTerms; ++t) {
                 if (t < NT && s < nsteps) {
                   const uint32_t accum = (s == 0 && t == 0) ? first : 1u;
-                  umma_mxf4(d0, a_lo + 2 * s, b_lo + t * term_lo + 2 * s, idesc[s & 1], sa, sb + 4 * t, accum);
+                  umma_mxf4(d0, a_lo + 2 * s, b_lo + t * term_lo + 2 * s, idesc_w[s & 1], sa, sb + 4 * t, accum);
                 }
               }
             }
