@@ -4,7 +4,8 @@
  * enqueues work on that stream and returns without synchronising.  Return value: 0 = ok,
  * negative = argument error (nothing was launched), positive = CUDA error code.
  * b200moe_last_error() describes the last non-zero return of the calling thread.
- * The library owns no device memory: the caller provides every buffer, including the workspace.
+ * The caller provides every buffer, including the workspace; the one exception is the fixed scratch array
+ * behind b200moe_forward_static (see there), which is part of the library image.
  *
  * Reference interfaces these replace (paths inside tingqli/pyhip):
  *   - kernels are reached there through ctypes + hipModuleLaunchKernel with raw data_ptr()
@@ -19,7 +20,7 @@
 extern "C" {
 #endif
 
-#define B200MOE_VERSION 2
+#define B200MOE_VERSION 3
 
 /* weight formats */
 #define B200MOE_W_MXFP4 0 /* E2M1 pairs (low nibble = even element) + E8M0 scale per 32 along K */
@@ -28,17 +29,37 @@ extern "C" {
 #define B200MOE_ACT_SILU 0   /* silu(gate) * up                        (test_moe.py:74-75) */
 #define B200MOE_ACT_SWIGLU 1 /* clamped gate*sigmoid(1.702 gate)*(up+1) (test_moe.py:76-81) */
 
+/* how the down stage returns its rows to token order */
+#define B200MOE_COMBINE_GATHER 0 /* sorted rows -> workspace, then a gather-sum launch in ascending expert order:
+                                    bitwise reproducible, the arithmetic of the reference's torch oracle
+                                    (tests/contrib/moe/test_moe.py:107-117) */
+#define B200MOE_COMBINE_FUSED 1  /* the down epilogue multiplies by the routing weight and adds into the zeroed
+                                    output with packed-bf16 reductions -- the reference kernels' own epilogue
+                                    (src/contrib/moe.py:703-787 global_atomic_pk_add_bf16); the order of the K
+                                    bf16 additions of a token is not fixed */
+/* activation operand of the FP8 (128x128-block) GEMMs */
+#define B200MOE_ACTQ_TERMS 0   /* two e4m3 terms with E8M0 scales per 32 (default; exact for bf16 inputs to ~2^-9) */
+#define B200MOE_ACTQ_1X128 1   /* one e4m3 value with an fp32 scale per token and 128 channels, scale = amax/448:
+                                  the reference's per_1x128 activation quantiser (src/contrib/fused_moe.py:276-281,375-381) */
+
 /* Shape of one MoE layer call.  B (rows per sorted block = token tile of the GEMMs) is a multiple
  * of 16 up to 128.  E is the number of experts whose weights are present (local experts under expert
  * parallelism); E_route is the size of the routing id space (E_route >= E; equal without a mask).
- * act_terms: how many packed-FP4 terms represent one activation row inside the GEMMs (2..4;
- * 0 = default 3; 4 reproduces bf16 activations to ~1e-4 of the block maximum). */
+ * act_terms: how many packed-FP4 terms represent one activation row inside the MXFP4 GEMMs (1..4; 0 = default 3).
+ *   1 is the plain per-1x32 MXFP4 activation format of the reference's a4w4 kernels
+ *   (tests/contrib/moe/test_moe.py:665-679, src/contrib/moe_gemm_mxfp4.py:972); 3 keeps the layer within
+ *   cosine 0.9999 of the bf16-activation oracle; 4 reproduces bf16 activations to ~1e-4 of the block maximum.
+ * doweight_stage1: the routing weight multiplies the gate-up output instead of the down output
+ *   (the aiter flag of that name, src/contrib/fused_moe.py:137). */
 typedef struct b200moe_shape {
   int32_t T, K, E, E_route, H, I, B;
   int32_t weight_format;
   int32_t activation;
   float swiglu_limit;
   int32_t act_terms;
+  int32_t combine_mode;
+  int32_t act_quant;
+  int32_t doweight_stage1;
 } b200moe_shape;
 
 /* Byte sizes and offsets of the caller-provided workspace (all offsets 1024-byte aligned). */
@@ -117,7 +138,7 @@ int b200moe_sort_align_ws(const int32_t* topk_ids, const float* topk_weight, int
  * sorted-row order (stands where the reference calls aiter's per_1x32 activation quantiser
  * followed by moe_mxfp4_sort, tests/contrib/moe/test_moe.py:665-679).
  *   src_mode 0: src is [T, Kd], row = token.   src_mode 1: src is [T, K, Kd], row = token*K + k.
- *   q: u8 [terms, max_rows, Kpad/2], Kpad = Kd rounded up to 256.  sf: per (block of B sorted
+ *   terms 1..4.  q: u8 [terms, max_rows, Kpad/2], Kpad = Kd rounded up to 256.  sf: per (block of B sorted
  *   rows, 128-wide k-block) a group of 512-byte chunks.  Only the rows of live (token, k) pairs are
  *   written; the padding rows of a block stay as they were. */
 int b200moe_quant_rows(const void* src_bf16, int32_t src_mode, const uint32_t* sorted_ids,
@@ -138,27 +159,39 @@ int b200moe_quant_rows_e4m3(const void* src_bf16, int32_t src_mode, const uint32
  * scale image and the sort arrays.
  *   With weight_format B200MOE_W_FP8_128 (replaces moe_gemm_8wave_g1u1, src/contrib/moe_gemm_8wave.py:131-765):
  *   w1_q is e4m3 [E,2I,H] and w1_scale_prepared is the raw fp32 [E, 2I/128, H/128] scale tensor.
+ *   bias1 : NULL or fp32 [E, 2I] (gate then up), added to the bf16-rounded products before the activation
+ *           (the aiter argument of that name, src/contrib/fused_moe.py:151; the reference asserts it absent).
  *   h_out != NULL : bf16 [T, K, I] scattered by (token,k) like the reference (moe.py:651-655)
  *   h_out == NULL : the result is re-quantised in sorted-row order into workspace hq for
  *                   b200moe_down (fused path). */
 int b200moe_gateup(const b200moe_shape* shape, const b200moe_workspace* ws, void* workspace,
-                   const void* w1_q, const void* w1_scale_prepared, void* h_out, void* stream);
+                   const void* w1_q, const void* w1_scale_prepared, const float* bias1, void* h_out,
+                   void* stream);
 
 /* Down grouped GEMM: replaces moe_2stage_splitk(with_silu=False) / moe_gemm_mxfp4(gate_up=False)
- * (src/contrib/moe.py:703-787, src/contrib/moe_gemm_mxfp4.py:1291-1398).  Reads workspace hq,
- * writes bf16 rows in sorted order to workspace out2. */
+ * (src/contrib/moe.py:703-787, src/contrib/moe_gemm_mxfp4.py:1291-1398).  Reads workspace hq.
+ *   bias2 : NULL or fp32 [E, H].
+ *   combine_mode GATHER: writes bf16 rows in sorted order to workspace out2 (y_bf16 is ignored; follow with
+ *     b200moe_combine).
+ *   combine_mode FUSED: y_bf16 [T, H] must hold zeros; every row of the result is multiplied by its routing
+ *     weight (workspace sorted_w; 1 with doweight_stage1) and added into it. */
 int b200moe_down(const b200moe_shape* shape, const b200moe_workspace* ws, void* workspace,
-                 const void* w2_q, const void* w2_scale_prepared, void* stream);
+                 const void* w2_q, const void* w2_scale_prepared, const float* bias2, void* y_bf16,
+                 void* stream);
 
 /* Weighted combine back to token order: y[t] = sum_k w[t,k] * out2[loc[t,k]] accumulated in bf16
  * in ascending expert order, the order of the reference's torch oracle
  * (tests/contrib/moe/test_moe.py:107-117); replaces moe_gemm_final_reduce_bf16
- * (src/contrib/moe_gemm_mxfp4.py:199-282) / stage2_out.sum(dim=1) (src/contrib/fused_moe.py:565). */
+ * (src/contrib/moe_gemm_mxfp4.py:199-282) / stage2_out.sum(dim=1) (src/contrib/fused_moe.py:565).
+ * With doweight_stage1 the weights are not applied again. */
 int b200moe_combine(const b200moe_shape* shape, const b200moe_workspace* ws, void* workspace,
                     const float* topk_weight, void* y_bf16, void* stream);
 
-/* Whole layer: sort_align -> quant_rows(x) -> gateup (fused re-quantisation) -> down -> combine.
- * Replaces the body of pyhip.contrib.fused_moe.fused_moe (src/contrib/fused_moe.py:268-576). */
+/* Whole layer.  Replaces the body of pyhip.contrib.fused_moe.fused_moe (src/contrib/fused_moe.py:268-576).
+ *   large batches: sort_align -> quant_rows(x) -> gateup (fused re-quantisation) -> down [-> combine]
+ *   at most 256 (token, expert) pairs: sort/align and the input quantiser are ONE launch (every CTA repeats
+ *   the small sort in shared memory; with T = 1 this is the reference's batch-1 shortcut, src/contrib/moe.py:41-188),
+ *   so a decode step with combine_mode FUSED is three launches. */
 int b200moe_forward(const b200moe_shape* shape, const b200moe_workspace* ws, void* workspace,
                     const void* x_bf16, const int32_t* topk_ids, const float* topk_weight,
                     const int32_t* expert_mask, const void* w1_q, const void* w1_scale_prepared,
@@ -172,6 +205,25 @@ int b200moe_forward_dyn(const b200moe_shape* shape, const b200moe_workspace* ws,
                         const void* w1_scale_prepared, const void* w2_q, const void* w2_scale_prepared,
                         void* y_bf16, void* stream);
 
+/* Whole layer with every optional tensor of the aiter-shaped signature (src/contrib/fused_moe.py:128-155):
+ * expert_mask, num_local_tokens, bias1, bias2 may be NULL. */
+typedef struct b200moe_io {
+  const void* x_bf16;              /* [T, H] */
+  const int32_t* topk_ids;         /* [T, K] */
+  const float* topk_weight;        /* [T, K] */
+  const int32_t* expert_mask;      /* [E_route] or NULL */
+  const int32_t* num_local_tokens; /* device scalar or NULL */
+  const void* w1_q;
+  const void* w1_scale_prepared;
+  const void* w2_q;
+  const void* w2_scale_prepared;
+  const float* bias1;              /* [E, 2I] or NULL */
+  const float* bias2;              /* [E, H] or NULL */
+  void* y_bf16;                    /* [T, H] */
+} b200moe_io;
+int b200moe_forward_ex(const b200moe_shape* shape, const b200moe_workspace* ws, void* workspace,
+                       const b200moe_io* io, void* stream);
+
 /* Whole layer WITHOUT a caller-provided workspace.  No counterpart in the reference (pyhip's
  * wrapper lets torch allocate its intermediates on every call).  It exists for hosts that cannot
  * allocate device memory when the layer runs -- e.g. a serving process that gave all free HBM to
@@ -181,12 +233,18 @@ int b200moe_forward_dyn(const b200moe_shape* shape, const b200moe_workspace* ws,
  * (b200moe_workspace_layout) is larger is refused with an argument error.  All calls on a device
  * share that array: calls whose GPU work may overlap must be serialised by the caller.  The first
  * call on each device performs a one-time address look-up and should be made outside stream
- * capture.  Same arguments and result as b200moe_forward otherwise; allocates nothing. */
+ * capture, with the stream's device current.  Same arguments and result as b200moe_forward otherwise;
+ * allocates nothing. */
 #define B200MOE_STATIC_SCRATCH_BYTES (48ll << 20)
 int b200moe_forward_static(const b200moe_shape* shape, const void* x_bf16, const int32_t* topk_ids,
                            const float* topk_weight, const int32_t* expert_mask, const void* w1_q,
                            const void* w1_scale_prepared, const void* w2_q, const void* w2_scale_prepared,
                            void* y_bf16, void* stream);
+/* The 16 device-side status words the latest b200moe_forward_static call with this shape left on the current
+ * device, copied to host memory asynchronously on `stream` (synchronise before reading; the next call clears
+ * them).  Word 0 != 0: a bounded wait inside a kernel gave up; word 2 != 0: an expert id outside the weight image.
+ * No counterpart in the reference. */
+int b200moe_static_status(const b200moe_shape* shape, int32_t* status_host16, void* stream);
 
 /* Expert-parallel combine.  No counterpart in the reference, which has no dispatch/combine (expert
  * parallelism exists there only as the expert_mask input convention, src/contrib/fused_moe.py:134,210-212).
@@ -196,17 +254,27 @@ int b200moe_forward_static(const b200moe_shape* shape, const void* x_bf16, const
 int b200moe_gather_sum(const void* rows_bf16, const int32_t* pos, int32_t T, int32_t slots, int32_t H,
                        void* y_bf16, void* stream);
 
-/* Hardware known-answer probes used by the GPU test-suite (tiny, single CTA, bounded waits).
+/* Expert-parallel dispatch plan in one launch.  No counterpart in the reference (see b200moe_gather_sum).
+ * Rank d owns experts [d*experts_per_rank, (d+1)*experts_per_rank); a token travels once to every rank that
+ * owns at least one of its K experts.
+ *   pos    i32 [T, world]  position of the token in the rank-major send buffer (ascending rank, ascending
+ *                          token within a rank), -1 where the rank owns none of its experts
+ *   counts i32 [world]     tokens bound for each rank
+ *   rows   i32 [T*world]   token at every send-buffer position; only [0, sum(counts)) is written
+ * world <= 32.  Deterministic (no atomics). */
+int b200moe_ep_plan(const int32_t* topk_ids, int32_t T, int32_t K, int32_t experts_per_rank, int32_t world,
+                    int32_t* pos, int32_t* counts, int32_t* rows, void* stream);
+
+/* Hardware known-answer probes used by the GPU test-suite and the benchmark (bounded waits).
  *   which = 1: TMA load of one 128-row x 256-element packed-FP4 tile (128-byte swizzle) from `in`
  *              (16384 bytes) -> `out` receives the 16384-byte shared-memory image.
  *   which = 2: 512 bytes `in` -> shared -> tcgen05.cp 32x128b.warpx4 -> tcgen05.ld;
  *              `out` receives u32 [128 lanes][4 columns].
- *   which = 3: tensor-core issue-rate measurement (kind::mxf4, 128 x N x 64); `in` = i32 {scale copies per
- *              four MMAs, N, count, accumulators, extra commit every so many groups of four MMAs (0 = none),
- *              issue mode (0 lane test, 1 elected lane, 2 whole warp with the election inside each MMA)}; `out` = u32 {issue cycles, cycles until complete, status}.
- *   which = 4: the same measurement on one CTA per SM at once (whole-chip dense FP4 rate when timed by
- *              the caller with stream events); `out` = u32 [SM count][3].
- * out[last] status word: 0 = ok, non-zero = a bounded wait ran out. */
+ *   which = 4: whole-chip dense MMA rate: one CTA per SM issues `count` block-scaled MMAs of 128 x N x (64 for
+ *              FP4, 32 for FP8) from resident shared-memory tiles; the caller times the launch with stream events.
+ *              `in` = i32 {kind (0 = kind::mxf4, 1 = kind::mxf8f6f4 e4m3), N, count}; `out` = u32 [SM count][3]
+ *              {issue cycles, cycles until complete, status}.
+ * status word: 0 = ok, non-zero = a bounded wait ran out. */
 int b200moe_debug_probe(int which, const void* in, void* out, void* stream);
 
 #ifdef __cplusplus

@@ -47,18 +47,19 @@ def max_abs(x: torch.Tensor, y: torch.Tensor) -> float:
 # --------------------------------------------------------------------------------------
 # weight formats
 # --------------------------------------------------------------------------------------
+_E2M1_PAIRS = torch.from_numpy(np.stack([_E2M1[np.arange(256) & 0xF], _E2M1[np.arange(256) >> 4]], axis=1))
+
+
 def dequant_mxfp4(packed: torch.Tensor, scale: torch.Tensor, dtype=torch.bfloat16) -> torch.Tensor:
     """Packed E2M1 (low nibble = even element) times 2**(e-127) per 32 along K, then cast
-    (tests/contrib/moe/test_moe.py:164-166; pk_fp4.hpp:122-129; e8m0.hpp:12-24)."""
-    p = packed.cpu().numpy().astype(np.uint8)
-    codes = np.empty(p.shape[:-1] + (p.shape[-1] * 2,), dtype=np.uint8)
-    codes[..., 0::2] = p & 0xF
-    codes[..., 1::2] = p >> 4
-    vals = _E2M1[codes]
+    (tests/contrib/moe/test_moe.py:164-166; pk_fp4.hpp:122-129; e8m0.hpp:12-24).  A 256-entry table maps a
+    byte to its two values, so the work is one gather and one multiply (threaded by torch)."""
+    packed = packed.cpu()
+    vals = _E2M1_PAIRS[packed.long()].reshape(*packed.shape[:-1], packed.shape[-1] * 2)
     K = vals.shape[-1]
-    sc = np.ldexp(np.float32(1.0), scale.cpu().numpy().astype(np.int32) - 127).astype(np.float32)
-    out = vals.reshape(vals.shape[:-1] + (K // 32, 32)) * sc[..., None]
-    return torch.from_numpy(out.reshape(vals.shape)).to(dtype)
+    sc = torch.ldexp(torch.ones(scale.shape, dtype=torch.float32), scale.cpu().int() - 127)
+    out = vals.reshape(*vals.shape[:-1], K // 32, 32) * sc.unsqueeze(-1)
+    return out.reshape(vals.shape).to(dtype)
 
 
 def dequant_fp8_128x128(q: torch.Tensor, scale: torch.Tensor, dtype=torch.bfloat16) -> torch.Tensor:
@@ -144,31 +145,100 @@ def _gateup_activation(gate, up, activation="silu", swiglu_limit=None):
     raise ValueError(activation)
 
 
+def act_quant_mxfp4(x: torch.Tensor) -> torch.Tensor:
+    """Per-1x32 MXFP4 activation quantiser followed by its dequantisation: E8M0 scale
+    2**(floor(log2 amax) - 2) per 32 along K (the OCP MX rule), E2M1 codes rounded to nearest even with
+    saturation.  This is the a4w4 activation format of the reference (aiter's per_1x32 quantiser,
+    tests/contrib/moe/test_moe.py:665-679; dequantised for the check exactly as
+    tests/contrib/moe/test_mxfp4.py:102-236 and src/contrib/moe_gemm_ref.py:82-89,114-123 do).  aiter itself is
+    not vendored, so its rounding of ties / the scale is unpinned; encodings follow pk_fp4.hpp / e8m0.hpp."""
+    codes, exps = fp4_terms_quant(x, 1)
+    return fp4_terms_dequant(codes, exps).to(x.dtype)
+
+
+def act_quant_fp8_1x128(x: torch.Tensor):
+    """Per-token, per-128-channel e4m3 quantiser with an fp32 scale = amax / 448 (1.0 for an all-zero block):
+    the reference's per_1x128 activation format (src/contrib/fused_moe.py:276-281,375-381; the only in-repo
+    statement of the rule is the per-tensor one, tests/contrib/moe/test_moe.py:130-137).
+    Returns (q float8_e4m3fn [..., K], scale float32 [..., K/128])."""
+    xf = x.float()
+    K = xf.shape[-1]
+    blk = xf.reshape(*xf.shape[:-1], K // 128, 128)
+    amax = blk.abs().amax(dim=-1)
+    scale = torch.where(amax > 0, amax / 448.0, torch.ones_like(amax))
+    q = (blk / scale.unsqueeze(-1)).clamp(-448.0, 448.0).to(torch.float8_e4m3fn)
+    return q.reshape(xf.shape), scale
+
+
+def act_dequant_fp8_1x128(q: torch.Tensor, scale: torch.Tensor) -> torch.Tensor:
+    """fp32 values of a 1x128-quantised tensor (src/contrib/moe_gemm_ref.py:72-80)."""
+    K = q.shape[-1]
+    return (q.float().reshape(*q.shape[:-1], K // 128, 128) * scale.unsqueeze(-1)).reshape(q.shape)
+
+
 def torch_moe_oracle(hidden, w1, w2, topk_weight, topk_ids, activation="silu",
-                     swiglu_limit=None, expert_weights=None):
+                     swiglu_limit=None, expert_weights=None, act_quant="none", bias1=None, bias2=None,
+                     doweight_stage1=False):
     """The reference's dequantise-then-matmul layer (tests/contrib/moe/test_moe.py:86-118):
     expert by expert, bf16 matmuls, silu(gate)*up, times the routing weight, cast to the
     activation dtype and accumulated into the output with index_add_ in expert order.
 
     ``w1`` [E,2I,H] / ``w2`` [E,H,I] are dequantised weights in the activation dtype, or
     ``expert_weights(e) -> (w1_e, w2_e)`` produces them one expert at a time (bounds host
-    memory for the large configurations)."""
+    memory for the large configurations).
+
+    ``act_quant``: "none" (bf16 activations, the layer oracle as written), "mxfp4" (x and h pass through
+    the per-1x32 MXFP4 quantiser first: the a4w4 check of tests/contrib/moe/test_mxfp4.py) or "fp8_1x128"
+    (x and h pass through the per-token 1x128 e4m3 quantiser and the products are formed in fp32, as
+    src/contrib/moe_gemm_ref.py:72-80,126 does).
+    ``bias1`` [E, 2I] / ``bias2`` [E, H]: per-expert biases added to the (bf16) projection outputs -- the
+    reference asserts them absent (src/contrib/fused_moe.py:262-263), the semantics are the gpt-oss layer's.
+    ``doweight_stage1``: the routing weight multiplies h instead of the down output
+    (tests/contrib/moe/test_fused_moe.py:280,311)."""
     T, H = hidden.shape
     ids = topk_ids.long()
     out = torch.zeros((T, H), dtype=hidden.dtype)
     E = w1.shape[0] if expert_weights is None else None
     e_list = range(E) if expert_weights is None else sorted(e for e in set(ids.flatten().tolist()) if e >= 0)
     ids_kt = ids.t().contiguous()                     # [K, T]: where() walks k-major like the
+    if act_quant == "mxfp4":
+        hidden_q = act_quant_mxfp4(hidden)
+    elif act_quant == "fp8_1x128":
+        hidden_q = act_dequant_fp8_1x128(*act_quant_fp8_1x128(hidden))       # fp32
+    elif act_quant == "none":
+        hidden_q = hidden
+    else:
+        raise ValueError(act_quant)
+
+    def mm(a, w):
+        if act_quant == "fp8_1x128":
+            return (a.float() @ w.float().t()).to(hidden.dtype)
+        return a @ w.t()
+
     for e in e_list:                                  # reference's permuted one-hot mask
         k_idx, t_idx = torch.where(ids_kt == e)
         if t_idx.numel() == 0:
             continue
         w1_e, w2_e = (w1[e], w2[e]) if expert_weights is None else expert_weights(e)
         inter = w1_e.shape[0] // 2
-        cur = hidden[t_idx]
-        act = _gateup_activation(cur @ w1_e[:inter].t(), cur @ w1_e[inter:].t(),
-                                 activation, swiglu_limit)
-        y = (act @ w2_e.t()) * topk_weight[t_idx, k_idx, None]
+        cur = hidden_q[t_idx]
+        gate, up = mm(cur, w1_e[:inter]), mm(cur, w1_e[inter:])
+        if bias1 is not None:
+            gate = gate + bias1[e, :inter].to(gate.dtype)
+            up = up + bias1[e, inter:].to(up.dtype)
+        act = _gateup_activation(gate, up, activation, swiglu_limit)
+        wts = topk_weight[t_idx, k_idx, None]
+        if doweight_stage1:
+            act = (act * wts).to(hidden.dtype)
+        if act_quant == "mxfp4":
+            act = act_quant_mxfp4(act)
+        elif act_quant == "fp8_1x128":
+            act = act_dequant_fp8_1x128(*act_quant_fp8_1x128(act))
+        y = mm(act, w2_e)
+        if bias2 is not None:
+            y = y + bias2[e].to(y.dtype)
+        if not doweight_stage1:
+            y = y * wts
         out.index_add_(0, t_idx, y.to(hidden.dtype))
     return out
 

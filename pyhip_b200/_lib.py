@@ -24,6 +24,9 @@ NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", 
 
 W_MXFP4, W_FP8_128 = 0, 1
 ACT_SILU, ACT_SWIGLU = 0, 1
+COMBINE_GATHER, COMBINE_FUSED = 0, 1
+ACTQ_TERMS, ACTQ_1X128 = 0, 1
+ABI_VERSION = 3
 
 
 class Shape(ctypes.Structure):
@@ -31,7 +34,8 @@ class Shape(ctypes.Structure):
                 ("E_route", ctypes.c_int32), ("H", ctypes.c_int32), ("I", ctypes.c_int32),
                 ("B", ctypes.c_int32), ("weight_format", ctypes.c_int32),
                 ("activation", ctypes.c_int32), ("swiglu_limit", ctypes.c_float),
-                ("act_terms", ctypes.c_int32)]
+                ("act_terms", ctypes.c_int32), ("combine_mode", ctypes.c_int32),
+                ("act_quant", ctypes.c_int32), ("doweight_stage1", ctypes.c_int32)]
 
 
 _WS_FIELDS = ["total_bytes", "max_rows", "off_sorted_ids", "off_sorted_w", "off_sorted_e",
@@ -43,11 +47,19 @@ class Workspace(ctypes.Structure):
     _fields_ = [(n, ctypes.c_int64) for n in _WS_FIELDS]
 
 
+class Io(ctypes.Structure):
+    """b200moe_io: every tensor of one layer call (optional ones may be None)."""
+    _fields_ = [(n, ctypes.c_void_p) for n in ("x_bf16", "topk_ids", "topk_weight", "expert_mask", "num_local_tokens",
+                                               "w1_q", "w1_scale_prepared", "w2_q", "w2_scale_prepared", "bias1",
+                                               "bias2", "y_bf16")]
+
+
 EXPORTS = ["b200moe_version", "b200moe_last_error", "b200moe_workspace_layout",
            "b200moe_prepared_scale_bytes", "b200moe_prepare_scales", "b200moe_sort_align",
            "b200moe_quant_rows", "b200moe_quant_rows_e4m3", "b200moe_gateup", "b200moe_down", "b200moe_combine",
            "b200moe_forward", "b200moe_forward_dyn", "b200moe_sort_align_dyn", "b200moe_sort_align_ws",
-           "b200moe_sort_scratch_bytes", "b200moe_route_topk", "b200moe_forward_static", "b200moe_gather_sum", "b200moe_debug_probe"]
+           "b200moe_sort_scratch_bytes", "b200moe_route_topk", "b200moe_forward_static", "b200moe_gather_sum", "b200moe_debug_probe",
+           "b200moe_forward_ex", "b200moe_static_status", "b200moe_ep_plan"]
 
 
 def build(force: bool = False, verbose: bool = False) -> pathlib.Path:
@@ -84,8 +96,10 @@ def lib() -> ctypes.CDLL:
     L.b200moe_sort_align.argtypes = [vp, vp, i32, i32, i32, i32, vp, vp, vp, vp, vp, vp, vp]
     L.b200moe_quant_rows.argtypes = [vp, i32, vp, vp, i32, i32, i32, i32, i32, i64, vp, vp, vp]
     L.b200moe_quant_rows_e4m3.argtypes = [vp, i32, vp, vp, i32, i32, i32, i32, i64, vp, vp, vp]
-    L.b200moe_gateup.argtypes = [sp, wp, vp, vp, vp, vp, vp]
-    L.b200moe_down.argtypes = [sp, wp, vp, vp, vp, vp]
+    L.b200moe_gateup.argtypes = [sp, wp, vp, vp, vp, vp, vp, vp]
+    L.b200moe_down.argtypes = [sp, wp, vp, vp, vp, vp, vp, vp]
+    L.b200moe_forward_ex.argtypes = [sp, wp, vp, ctypes.POINTER(Io), vp]
+    L.b200moe_static_status.argtypes = [sp, vp, vp]
     L.b200moe_combine.argtypes = [sp, wp, vp, vp, vp, vp]
     L.b200moe_forward.argtypes = [sp, wp, vp, vp, vp, vp, vp, vp, vp, vp, vp, vp, vp]
     L.b200moe_forward_dyn.argtypes = [sp, wp, vp, vp, vp, vp, vp, vp, vp, vp, vp, vp, vp, vp]
@@ -95,11 +109,12 @@ def lib() -> ctypes.CDLL:
     L.b200moe_route_topk.argtypes = [vp, i32, i32, i32, i32, i32, vp, vp, vp]
     L.b200moe_forward_static.argtypes = [sp, vp, vp, vp, vp, vp, vp, vp, vp, vp, vp]
     L.b200moe_gather_sum.argtypes = [vp, vp, i32, i32, i32, vp, vp]
+    L.b200moe_ep_plan.argtypes = [vp, i32, i32, i32, i32, vp, vp, vp, vp]
     L.b200moe_debug_probe.argtypes = [ctypes.c_int, vp, vp, vp]
     for name in EXPORTS:
         if name not in ("b200moe_version", "b200moe_last_error"):
             getattr(L, name).restype = ctypes.c_int
-    if L.b200moe_version() != 2:
+    if L.b200moe_version() != ABI_VERSION:
         raise RuntimeError("libb200moe.so version mismatch; rebuild it")
     return L
 

@@ -36,8 +36,12 @@ static int check_shape(const b200moe_shape* s) {
   }
   B200_CHECK_ARG(s->activation == B200MOE_ACT_SILU || s->activation == B200MOE_ACT_SWIGLU,
                  "activation %d unknown", s->activation);
-  B200_CHECK_ARG(s->act_terms == 0 || (s->act_terms >= 2 && s->act_terms <= 4), "act_terms=%d not in {0,2,3,4}",
-                 s->act_terms);
+  B200_CHECK_ARG(s->act_terms >= 0 && s->act_terms <= 4, "act_terms=%d not in [0,4]", s->act_terms);
+  B200_CHECK_ARG(s->combine_mode == B200MOE_COMBINE_GATHER || s->combine_mode == B200MOE_COMBINE_FUSED,
+                 "combine_mode %d unknown", s->combine_mode);
+  B200_CHECK_ARG(s->act_quant == B200MOE_ACTQ_TERMS, "act_quant %d unknown", s->act_quant);
+  B200_CHECK_ARG(s->doweight_stage1 == 0 || s->doweight_stage1 == 1, "doweight_stage1=%d must be 0 or 1",
+                 s->doweight_stage1);
   return 0;
 }
 
@@ -173,7 +177,7 @@ int b200moe_quant_rows(const void* src_bf16, int32_t src_mode, const uint32_t* s
   B200_CHECK_ARG(((uintptr_t)src_bf16 & 15) == 0 && ((uintptr_t)q & 15) == 0,
                  "quant_rows: source and destination must be 16-byte aligned");
   return launch_quant_rows(src_bf16, src_mode, sorted_ids, num_valid_ids, T, K, Kd, B, terms, max_rows, q, sf,
-                           (cudaStream_t)stream);
+                           nullptr, 0, (cudaStream_t)stream);
 }
 
 int b200moe_quant_rows_e4m3(const void* src_bf16, int32_t src_mode, const uint32_t* sorted_ids,
@@ -185,7 +189,7 @@ int b200moe_quant_rows_e4m3(const void* src_bf16, int32_t src_mode, const uint32
   B200_CHECK_ARG(((uintptr_t)src_bf16 & 15) == 0 && ((uintptr_t)q & 15) == 0,
                  "quant_rows: source and destination must be 16-byte aligned");
   return launch_quant_rows_e4m3(src_bf16, src_mode, sorted_ids, num_valid_ids, T, K, Kd, B, max_rows, q, sf,
-                                (cudaStream_t)stream);
+                                nullptr, 0, (cudaStream_t)stream);
 }
 
 static void fill_common(GemmArgs& g, const b200moe_shape* s, const b200moe_workspace* ws, uint8_t* base) {
@@ -198,13 +202,14 @@ static void fill_common(GemmArgs& g, const b200moe_shape* s, const b200moe_works
   g.swiglu_limit = s->swiglu_limit > 0.f ? s->swiglu_limit : 7.0f;
   g.max_rows = ws->max_rows;
   g.sorted_ids = (const uint32_t*)(base + ws->off_sorted_ids);
+  g.sorted_w = (const float*)(base + ws->off_sorted_w);
   g.sorted_e = (const int32_t*)(base + ws->off_sorted_e);
   g.num_valid = (const int32_t*)(base + ws->off_num_valid);
   g.status = (int32_t*)(base + ws->off_status);
 }
 
 int b200moe_gateup(const b200moe_shape* s, const b200moe_workspace* ws, void* workspace, const void* w1_q,
-                   const void* w1_scale, void* h_out, void* stream) {
+                   const void* w1_scale, const float* bias1, void* h_out, void* stream) {
   if (int rc = check_shape(s)) return rc;
   B200_CHECK_ARG(ws && workspace && w1_q && w1_scale, "gateup: NULL pointer");
   B200_CHECK_ARG(((uintptr_t)workspace & 1023) == 0, "gateup: workspace must be 1024-byte aligned");
@@ -219,6 +224,8 @@ int b200moe_gateup(const b200moe_shape* s, const b200moe_workspace* ws, void* wo
   g.a_q = base + ws->off_xq;
   g.asf = base + ws->off_xsf;
   g.h_out = h_out;
+  g.bias = bias1;
+  g.weight_stage1 = s->doweight_stage1;
   g.oq = base + ws->off_hq;
   g.osf = base + ws->off_hsf;
   if (s->weight_format == B200MOE_W_FP8_128) {
@@ -233,9 +240,10 @@ int b200moe_gateup(const b200moe_shape* s, const b200moe_workspace* ws, void* wo
 }
 
 int b200moe_down(const b200moe_shape* s, const b200moe_workspace* ws, void* workspace, const void* w2_q,
-                 const void* w2_scale, void* stream) {
+                 const void* w2_scale, const float* bias2, void* y_bf16, void* stream) {
   if (int rc = check_shape(s)) return rc;
   B200_CHECK_ARG(ws && workspace && w2_q && w2_scale, "down: NULL pointer");
+  B200_CHECK_ARG(s->combine_mode != B200MOE_COMBINE_FUSED || y_bf16 != nullptr, "down: the fused combine needs y");
   B200_CHECK_ARG(((uintptr_t)workspace & 1023) == 0, "down: workspace must be 1024-byte aligned");
   uint8_t* base = (uint8_t*)workspace;
   GemmArgs g = {};
@@ -248,6 +256,9 @@ int b200moe_down(const b200moe_shape* s, const b200moe_workspace* ws, void* work
   g.a_q = base + ws->off_hq;
   g.asf = base + ws->off_hsf;
   g.out2 = base + ws->off_out2;
+  g.bias = bias2;
+  g.y = s->combine_mode == B200MOE_COMBINE_FUSED ? y_bf16 : nullptr;
+  if (s->doweight_stage1) g.sorted_w = nullptr;     // weights already applied upstream
   if (s->weight_format == B200MOE_W_FP8_128) return launch_grouped_gemm_fp8(g, (cudaStream_t)stream);
   return launch_grouped_gemm(g, (cudaStream_t)stream);
 }
@@ -255,70 +266,108 @@ int b200moe_down(const b200moe_shape* s, const b200moe_workspace* ws, void* work
 int b200moe_combine(const b200moe_shape* s, const b200moe_workspace* ws, void* workspace, const float* topk_weight,
                     void* y_bf16, void* stream) {
   if (int rc = check_shape(s)) return rc;
-  B200_CHECK_ARG(ws && workspace && (s->T == 0 || (topk_weight && y_bf16)), "combine: NULL pointer");
+  B200_CHECK_ARG(ws && workspace && (s->T == 0 || y_bf16), "combine: NULL pointer");
+  B200_CHECK_ARG(s->T == 0 || topk_weight || s->doweight_stage1, "combine: NULL routing weights");
+  if (s->doweight_stage1) topk_weight = nullptr;
   B200_CHECK_ARG(((uintptr_t)y_bf16 & 15) == 0, "combine: output must be 16-byte aligned");
   uint8_t* base = (uint8_t*)workspace;
   return launch_combine(base + ws->off_out2, (const int32_t*)(base + ws->off_loc), topk_weight, y_bf16, s->T, s->K,
                         s->H, (cudaStream_t)stream);
 }
 
-// A workspace laid out for more tokens than the call carries is fine (its offsets and row capacity are
-// used as given); one that is too small is an argument error.
+// A workspace laid out for more tokens than the call carries is fine (its offsets and row capacity are used as
+// given); one that is too small in ANY region is an argument error: the layout is recomputed for the call's shape
+// and every region of the caller's descriptor must be at least as large (a descriptor laid out for another K, B
+// or E_route can have enough rows and still too small a scale or index region).
 static int check_capacity(const b200moe_shape* s, const b200moe_workspace* ws) {
-  const int64_t P = (int64_t)s->T * s->K;
-  const int64_t need = std::max<int64_t>((P + (int64_t)s->E_route * (s->B - 1) + s->B - 1) / s->B, 1) * s->B;
-  B200_CHECK_ARG(ws->max_rows >= need && ws->max_rows % s->B == 0,
+  b200moe_workspace need;
+  if (int rc = b200moe_workspace_layout(s, &need)) return rc;
+  B200_CHECK_ARG(ws->max_rows >= need.max_rows && ws->max_rows % s->B == 0,
                  "workspace holds %lld rows, T=%d needs %lld (blocks of %d)", (long long)ws->max_rows, s->T,
-                 (long long)need, s->B);
+                 (long long)need.max_rows, s->B);
+  static int64_t b200moe_workspace::* const kOff[] = {
+      &b200moe_workspace::off_sorted_ids, &b200moe_workspace::off_sorted_w, &b200moe_workspace::off_sorted_e,
+      &b200moe_workspace::off_num_valid,  &b200moe_workspace::off_loc,      &b200moe_workspace::off_status,
+      &b200moe_workspace::off_xq,         &b200moe_workspace::off_xsf,      &b200moe_workspace::off_hq,
+      &b200moe_workspace::off_hsf,        &b200moe_workspace::off_out2,     &b200moe_workspace::off_sort_scratch,
+      &b200moe_workspace::total_bytes};
+  constexpr int n = sizeof(kOff) / sizeof(kOff[0]);
+  for (int i = 0; i + 1 < n; ++i) {
+    const int64_t have = ws->*kOff[i + 1] - ws->*kOff[i], want = need.*kOff[i + 1] - need.*kOff[i];
+    B200_CHECK_ARG(ws->*kOff[i] >= 0 && have >= want,
+                   "workspace region %d holds %lld bytes, this call needs %lld (was the descriptor laid out for "
+                   "another K, B or E_route?)", i, (long long)have, (long long)want);
+  }
   return 0;
 }
 
-static int forward_impl(const b200moe_shape* s, const b200moe_workspace* ws, void* workspace, const void* x_bf16,
-                        const int32_t* topk_ids, const float* topk_weight, const int32_t* expert_mask,
-                        const int32_t* num_local_tokens, const void* w1_q, const void* w1_scale, const void* w2_q,
-                        const void* w2_scale, void* y_bf16, void* stream) {
+static int forward_impl(const b200moe_shape* s, const b200moe_workspace* ws, void* workspace, const b200moe_io* io,
+                        void* stream) {
   if (int rc = check_shape(s)) return rc;
-  B200_CHECK_ARG(ws && workspace, "forward: NULL workspace");
+  B200_CHECK_ARG(ws && workspace && io, "forward: NULL workspace");
   if (s->T == 0) return 0;
   if (int rc = check_capacity(s, ws)) return rc;
-  B200_CHECK_ARG(x_bf16 && topk_ids && topk_weight && y_bf16, "forward: NULL tensor");
+  B200_CHECK_ARG(io->x_bf16 && io->topk_ids && io->topk_weight && io->y_bf16, "forward: NULL tensor");
+  B200_CHECK_ARG(((uintptr_t)io->y_bf16 & 15) == 0, "forward: output must be 16-byte aligned");
   uint8_t* base = (uint8_t*)workspace;
-  int rc = sort_align_impl(topk_ids, topk_weight, s->T, s->K, s->E_route, s->B, expert_mask, num_local_tokens,
-                           (uint32_t*)(base + ws->off_sorted_ids), (float*)(base + ws->off_sorted_w),
-                           (int32_t*)(base + ws->off_sorted_e), (int32_t*)(base + ws->off_num_valid),
-                           (int32_t*)(base + ws->off_loc), base + ws->off_sort_scratch, sort_scratch_bytes(s->E_route),
-                           stream);
+  const bool fp8w = s->weight_format == B200MOE_W_FP8_128;
+  const bool fused = s->combine_mode == B200MOE_COMBINE_FUSED;
+  // the fused combine accumulates into y: the quantiser launch clears it first
+  void* zero_ptr = fused ? io->y_bf16 : nullptr;
+  const int64_t zero_bytes = fused ? (int64_t)s->T * s->H * 2 : 0;
+  uint32_t* sorted_ids = (uint32_t*)(base + ws->off_sorted_ids);
+  float* sorted_w = (float*)(base + ws->off_sorted_w);
+  int32_t* sorted_e = (int32_t*)(base + ws->off_sorted_e);
+  int32_t* num_valid = (int32_t*)(base + ws->off_num_valid);
+  int32_t* loc = (int32_t*)(base + ws->off_loc);
+  int rc;
+  if (sort_quant_small_ok(s->T, s->K, s->E_route)) {
+    rc = launch_sort_quant_small(fp8w ? 1 : 0, io->x_bf16, io->topk_ids, io->topk_weight, s->T, s->K, s->E_route, s->B,
+                                 io->expert_mask, io->num_local_tokens, sorted_ids, sorted_w, sorted_e, num_valid, loc,
+                                 s->H, terms_of(s), ws->max_rows, base + ws->off_xq, base + ws->off_xsf, zero_ptr,
+                                 zero_bytes, (cudaStream_t)stream);
+    if (rc) return rc;
+  } else {
+    rc = sort_align_impl(io->topk_ids, io->topk_weight, s->T, s->K, s->E_route, s->B, io->expert_mask,
+                         io->num_local_tokens, sorted_ids, sorted_w, sorted_e, num_valid, loc,
+                         base + ws->off_sort_scratch, sort_scratch_bytes(s->E_route), stream);
+    if (rc) return rc;
+    if (fp8w)
+      rc = launch_quant_rows_e4m3(io->x_bf16, 0, sorted_ids, num_valid, s->T, s->K, s->H, s->B, ws->max_rows,
+                                  base + ws->off_xq, base + ws->off_xsf, zero_ptr, zero_bytes, (cudaStream_t)stream);
+    else
+      rc = launch_quant_rows(io->x_bf16, 0, sorted_ids, num_valid, s->T, s->K, s->H, s->B, terms_of(s), ws->max_rows,
+                             base + ws->off_xq, base + ws->off_xsf, zero_ptr, zero_bytes, (cudaStream_t)stream);
+    if (rc) return rc;
+  }
+  rc = b200moe_gateup(s, ws, workspace, io->w1_q, io->w1_scale_prepared, io->bias1, nullptr, stream);
   if (rc) return rc;
-  if (s->weight_format == B200MOE_W_FP8_128)
-    rc = b200moe_quant_rows_e4m3(x_bf16, 0, (const uint32_t*)(base + ws->off_sorted_ids),
-                                 (const int32_t*)(base + ws->off_num_valid), s->T, s->K, s->H, s->B, ws->max_rows,
-                                 base + ws->off_xq, base + ws->off_xsf, stream);
-  else
-    rc = b200moe_quant_rows(x_bf16, 0, (const uint32_t*)(base + ws->off_sorted_ids),
-                            (const int32_t*)(base + ws->off_num_valid), s->T, s->K, s->H, s->B, terms_of(s),
-                            ws->max_rows, base + ws->off_xq, base + ws->off_xsf, stream);
-  if (rc) return rc;
-  rc = b200moe_gateup(s, ws, workspace, w1_q, w1_scale, nullptr, stream);
-  if (rc) return rc;
-  rc = b200moe_down(s, ws, workspace, w2_q, w2_scale, stream);
-  if (rc) return rc;
-  return b200moe_combine(s, ws, workspace, topk_weight, y_bf16, stream);
+  rc = b200moe_down(s, ws, workspace, io->w2_q, io->w2_scale_prepared, io->bias2, io->y_bf16, stream);
+  if (rc || fused) return rc;
+  return b200moe_combine(s, ws, workspace, io->topk_weight, io->y_bf16, stream);
+}
+
+int b200moe_forward_ex(const b200moe_shape* s, const b200moe_workspace* ws, void* workspace, const b200moe_io* io,
+                       void* stream) {
+  return forward_impl(s, ws, workspace, io, stream);
 }
 
 int b200moe_forward(const b200moe_shape* s, const b200moe_workspace* ws, void* workspace, const void* x_bf16,
                     const int32_t* topk_ids, const float* topk_weight, const int32_t* expert_mask,
                     const void* w1_q, const void* w1_scale, const void* w2_q, const void* w2_scale,
                     void* y_bf16, void* stream) {
-  return forward_impl(s, ws, workspace, x_bf16, topk_ids, topk_weight, expert_mask, nullptr, w1_q, w1_scale, w2_q,
-                      w2_scale, y_bf16, stream);
+  const b200moe_io io = {x_bf16, topk_ids, topk_weight, expert_mask, nullptr, w1_q, w1_scale, w2_q, w2_scale,
+                         nullptr, nullptr, y_bf16};
+  return forward_impl(s, ws, workspace, &io, stream);
 }
 
 int b200moe_forward_dyn(const b200moe_shape* s, const b200moe_workspace* ws, void* workspace, const void* x_bf16,
                         const int32_t* topk_ids, const float* topk_weight, const int32_t* expert_mask,
                         const int32_t* num_local_tokens, const void* w1_q, const void* w1_scale, const void* w2_q,
                         const void* w2_scale, void* y_bf16, void* stream) {
-  return forward_impl(s, ws, workspace, x_bf16, topk_ids, topk_weight, expert_mask, num_local_tokens, w1_q, w1_scale,
-                      w2_q, w2_scale, y_bf16, stream);
+  const b200moe_io io = {x_bf16, topk_ids, topk_weight, expert_mask, num_local_tokens, w1_q, w1_scale, w2_q, w2_scale,
+                         nullptr, nullptr, y_bf16};
+  return forward_impl(s, ws, workspace, &io, stream);
 }
 
 int b200moe_route_topk(const float* logits, int32_t T, int32_t E, int32_t K, int32_t scoring, int32_t renormalize,
@@ -335,6 +384,12 @@ int b200moe_gather_sum(const void* rows_bf16, const int32_t* pos, int32_t T, int
   B200_CHECK_ARG(rows_bf16 && pos && y_bf16, "gather_sum: NULL pointer");
   B200_CHECK_ARG(((uintptr_t)rows_bf16 & 15) == 0 && ((uintptr_t)y_bf16 & 15) == 0, "gather_sum: 16-byte alignment");
   return launch_gather_sum(rows_bf16, pos, y_bf16, T, slots, H, (cudaStream_t)stream);
+}
+
+int b200moe_ep_plan(const int32_t* topk_ids, int32_t T, int32_t K, int32_t experts_per_rank, int32_t world,
+                    int32_t* pos, int32_t* counts, int32_t* rows, void* stream) {
+  B200_CHECK_ARG(pos && counts && rows && (T == 0 || topk_ids), "ep_plan: NULL pointer");
+  return launch_ep_plan(topk_ids, T, K, experts_per_rank, world, pos, counts, rows, (cudaStream_t)stream);
 }
 
 int b200moe_debug_probe(int which, const void* in, void* out, void* stream) {

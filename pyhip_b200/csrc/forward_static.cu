@@ -18,7 +18,10 @@
 //     before it is read; two calls whose GPU work overlaps (different streams, no dependency)
 //     race on it and must be serialised by the caller;
 //   * the first call on each device looks the array's device address up (and the kernels set
-//     their shared-memory attributes); make that first call outside any stream capture.
+//     their shared-memory attributes); make that first call outside any stream capture;
+//   * the device that is current when the call is made must be the device `stream` belongs to;
+//   * the kernels' error words live inside the array too: b200moe_static_status copies the words the
+//     latest call on this device left (the next call clears them).
 // Nothing here calls cudaMalloc, cudaFree or any allocating library routine.
 #include <mutex>
 
@@ -74,4 +77,18 @@ extern "C" int b200moe_forward_static(const b200moe_shape* shape, const void* x_
   B200_CHECK_CUDA(cudaMemsetAsync(base + ws.off_status, 0, 64, (cudaStream_t)stream));
   return b200moe_forward(shape, &ws, base, x_bf16, topk_ids, topk_weight, expert_mask, w1_q, w1_scale_prepared,
                          w2_q, w2_scale_prepared, y_bf16, stream);
+}
+
+// Copies the 16 device-side status words of the latest b200moe_forward_static call with this shape on the current
+// device into host memory (asynchronously on `stream`: synchronise before reading).  Word 0: non-zero when a
+// bounded wait inside a kernel gave up; word 2: non-zero when a block carried an expert id outside the weight image.
+extern "C" int b200moe_static_status(const b200moe_shape* shape, int32_t* status_host16, void* stream) {
+  b200moe_workspace ws;
+  if (int rc = b200moe_workspace_layout(shape, &ws)) return rc;
+  B200_CHECK_ARG(status_host16 != nullptr, "static_status: NULL output");
+  B200_CHECK_ARG(ws.total_bytes <= kStaticScratchBytes, "static_status: shape is beyond the built-in array");
+  unsigned char* base = nullptr;
+  if (int rc = static_scratch_base(&base)) return rc;
+  B200_CHECK_CUDA(cudaMemcpyAsync(status_host16, base + ws.off_status, 64, cudaMemcpyDeviceToHost, (cudaStream_t)stream));
+  return 0;
 }

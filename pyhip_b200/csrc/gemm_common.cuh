@@ -9,6 +9,18 @@
 #include "internal.h"
 #include "ptx_sm100.cuh"
 
+// Cycle counters of the GEMM roles exist only in a -DB200MOE_PROFILE build; the production kernels carry no
+// timing code (the issuing threads are the ones whose instruction rate limits the main loop).
+#ifdef B200MOE_PROFILE
+#define PROF_DECL(name) long long name = 0
+#define PROF_NOW() clock64()
+#define PROF_ADD(acc, t0) acc += clock64() - (t0)
+#else
+#define PROF_DECL(name)
+#define PROF_NOW() 0ll
+#define PROF_ADD(acc, t0) ((void)(t0))
+#endif
+
 namespace b200moe {
 
 __device__ __forceinline__ float bf16r(float x) { return __bfloat162float(__float2bfloat16_rn(x)); }
@@ -63,22 +75,6 @@ constexpr uint32_t kDescHiSw = (1024u >> 4) | (1u << 14) | (2u << 29);   // SBO 
 constexpr uint32_t kDescHiSf = (128u >> 4) | (1u << 14);                   // SBO 128, version 1, no swizzle
 __device__ __forceinline__ uint32_t desc_lo_sw(uint32_t saddr) { return ((saddr >> 4) & 0x3FFFu) | (1u << 16); }
 __device__ __forceinline__ uint32_t desc_lo_sf(uint32_t saddr) { return (saddr >> 4) & 0x3FFFu; }
-
-// The same instruction issued from warp-uniform code: every lane of the (converged) warp executes the call
-// with identical operands, one elected lane issues the MMA.  Keeping the call out of divergent control flow
-// lets the compiler hold descriptors and addresses in uniform registers.
-__device__ __forceinline__ void umma_mxf4_warp(uint32_t d_tmem, uint32_t a_lo, uint32_t b_lo, uint32_t idesc,
-                                               uint32_t sfa_tmem, uint32_t sfb_tmem, uint32_t accumulate) {
-  asm volatile(
-      "{\n\t.reg .pred p, q;\n\t.reg .b64 da, db;\n\t"
-      "setp.ne.b32 p, %4, 0;\n\t"
-      "mov.b64 da, {%1, %7};\n\t"
-      "mov.b64 db, {%2, %7};\n\t"
-      "elect.sync _|q, 0xffffffff;\n\t"
-      "@q tcgen05.mma.cta_group::1.kind::mxf4.block_scale.block32 [%0], da, db, %3, [%5], [%6], p;\n\t}"
-      ::"r"(d_tmem), "r"(a_lo), "r"(b_lo), "r"(idesc), "r"(accumulate), "r"(sfa_tmem), "r"(sfb_tmem), "r"(kDescHiSw)
-      : "memory");
-}
 
 // D[tmem] (+)= A[smem] * B[smem]^T, packed FP4 x packed FP4, K = 64, two E8M0 scales per row
 __device__ __forceinline__ void umma_mxf4(uint32_t d_tmem, uint32_t a_lo, uint32_t b_lo, uint32_t idesc,

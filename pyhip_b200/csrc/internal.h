@@ -63,8 +63,18 @@ int launch_sort_align_wide(const int32_t* ids, const float* w, int T, int K, int
                            int32_t* loc, const int32_t* num_local, void* scratch, cudaStream_t st);
 int launch_route_topk(const float* logits, int T, int E, int K, int scoring, int renorm, int32_t* ids, float* weights,
                       cudaStream_t st);
+// zero_ptr / zero_bytes: an optional region the same launch clears (the output of the fused combine)
 int launch_quant_rows(const void* src, int src_mode, const uint32_t* sorted_ids, const int32_t* num_valid,
-                      int T, int K, int Kd, int B, int NT, int64_t max_rows, void* q, void* sf, cudaStream_t st);
+                      int T, int K, int Kd, int B, int NT, int64_t max_rows, void* q, void* sf, void* zero_ptr,
+                      int64_t zero_bytes, cudaStream_t st);
+// sort/align + input quantiser in one launch for decode-sized batches (fmt 0: packed-FP4 terms, 1: two e4m3 terms)
+bool sort_quant_small_ok(int T, int K, int E);
+int launch_sort_quant_small(int fmt, const void* x, const int32_t* ids, const float* w, int T, int K, int E, int B,
+                            const int32_t* mask, const int32_t* num_local, uint32_t* sorted_ids, float* sorted_w,
+                            int32_t* sorted_e, int32_t* num_valid, int32_t* loc, int Kd, int NT, int64_t max_rows,
+                            void* q, void* sf, void* zero_ptr, int64_t zero_bytes, cudaStream_t st);
+int launch_ep_plan(const int32_t* ids, int T, int K, int epr, int W, int32_t* pos, int32_t* counts, int32_t* rows,
+                   cudaStream_t st);
 int launch_gather_sum(const void* rows, const int32_t* pos, void* y, int T, int S, int H, cudaStream_t st);
 int launch_combine(const void* out2, const int32_t* loc, const float* topk_w, void* y, int T, int K, int H,
                    cudaStream_t st);
@@ -97,13 +107,18 @@ struct GemmArgs {
   void* out2;          // down: bf16 [max_rows, H]
   void* gstage;        // gate-up: scratch for per-CTA staging tiles in global memory (may be null)
   int64_t gstage_bytes;
+  const float* sorted_w;   // routing weight per sorted row (needed by y and weight_stage1)
+  const float* bias;       // fp32 per-expert bias: gate-up [E, 2*rows], down [E, rows]; or null
+  void* y;                 // down: zeroed bf16 [T, rows]; non-null selects the fused weighted scatter-add epilogue
+  int weight_stage1;       // gate-up: apply the routing weight to h
 };
 int launch_grouped_gemm(const GemmArgs& a, cudaStream_t st);
 // FP8 128x128-block variant (moe_gemm_fp8_sm100.cu): w_data = e4m3 bytes [E, parts*rows, Kd], w_scale = fp32
 // [E, parts*rows/128, Kd/128] (used in place), a_q = two e4m3 terms [2, max_rows, Kd], NT ignored
 int launch_grouped_gemm_fp8(const GemmArgs& a, cudaStream_t st);
 int launch_quant_rows_e4m3(const void* src, int src_mode, const uint32_t* sorted_ids, const int32_t* num_valid,
-                           int T, int K, int Kd, int B, int64_t max_rows, void* q, void* sf, cudaStream_t st);
+                           int T, int K, int Kd, int B, int64_t max_rows, void* q, void* sf, void* zero_ptr,
+                           int64_t zero_bytes, cudaStream_t st);
 int encode_map_sw(CUtensorMap* map, CUtensorMapDataType type, int rank, const void* base, const cuuint64_t* dims,
                   const cuuint64_t* strides, const cuuint32_t* box, CUtensorMapSwizzle swizzle,
                   CUtensorMapL2promotion promo, const char* what);

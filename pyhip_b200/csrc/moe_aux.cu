@@ -144,12 +144,8 @@ int launch_sort_align(const int32_t* ids, const float* w, int T, int K, int E, i
   B200_CHECK_ARG(E >= 1 && E <= kSortWarps * 32, "sort_align: E=%d outside [1,%d]", E, kSortWarps * 32);
   size_t smem = (size_t)(kSortWarps * E + 3 * E + 2) * sizeof(int32_t) + 34 * sizeof(unsigned long long);
   B200_CHECK_ARG(smem <= 200 * 1024, "sort_align: E=%d needs %zu bytes of shared memory", E, smem);
-  static bool attr_set = false;
-  if (!attr_set) {
-    B200_CHECK_CUDA(cudaFuncSetAttribute(sort_align_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                         200 * 1024));
-    attr_set = true;
-  }
+  // the attribute belongs to the (function, device) pair and setting it is cheap: do it on every launch
+  B200_CHECK_CUDA(cudaFuncSetAttribute(sort_align_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
   B200_CHECK_CUDA(launch_chained(sort_align_kernel, dim3(1), dim3(kSortWarps * 32), smem, st, ids, w, T, K, E, B, mask,
                                  sorted_ids, sorted_w, sorted_e, num_valid, loc, num_local));
   return 0;
@@ -334,12 +330,8 @@ int launch_sort_align_wide(const int32_t* ids, const float* w, int T, int K, int
   const int S = G * kSortWarps;
   const size_t smem = (size_t)(kSortWarps * E + E) * sizeof(int32_t);
   B200_CHECK_ARG(smem <= 200 * 1024, "sort_align: E=%d needs %zu bytes of shared memory", E, smem);
-  static bool attr_set = false;
-  if (!attr_set) {
-    B200_CHECK_CUDA(cudaFuncSetAttribute(sort_count_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
-    B200_CHECK_CUDA(cudaFuncSetAttribute(sort_scatter_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
-    attr_set = true;
-  }
+  B200_CHECK_CUDA(cudaFuncSetAttribute(sort_count_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
+  B200_CHECK_CUDA(cudaFuncSetAttribute(sort_scatter_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
   int32_t* hist = (int32_t*)scratch;
   B200_CHECK_CUDA(launch_chained(sort_count_kernel, dim3(G), dim3(kSortWarps * 32), smem, st, ids, mask, T, K, E,
                                  num_local, slice, hist));
@@ -352,138 +344,276 @@ int launch_sort_align_wide(const int32_t* ids, const float* w, int T, int K, int
 }
 
 // =====================================================================================
-// activation quantiser: bf16 row -> NT packed-FP4 (E2M1) terms with per-32 E8M0 scales, written
-// in sorted-row order.  One thread per 32-element block.  Term t quantises what the previous
-// terms left over:
+// activation quantisers: bf16 row -> the operand format of the GEMMs, written in sorted-row order.
+// One thread per 32-element block.
+//
+// Packed-FP4 terms (MXFP4 weights).  Term t quantises what the previous terms left over:
 //   e = max(biased_exponent(amax(r)) - 2, 0);  q = e2m1_rne_sat(r * 2^(127-e));  r -= q * 2^(e-127)
 // (amax/2^(e-127) lies in [4,8): the OCP MX scale rule; values above 6 saturate and the next
-// term picks up the rest).  Three terms reproduce a bf16 input to ~2e-3 of the block maximum,
-// four terms to ~1e-4.
+// term picks up the rest).  One term is the plain MXFP4 activation format of the reference's a4w4
+// kernels; three terms reproduce a bf16 input to ~2e-3 of the block maximum, four to ~1e-4.
+//
+// Two e4m3 terms with E8M0 scales (FP8 128x128 weights): q [2, max_rows, Kd] bytes, one scale
+// chunk per term (virtual row = term*128 + r).
 // =====================================================================================
+__device__ __forceinline__ void load_block32(const __nv_bfloat16* src, float (&x)[32]) {
+  const uint4* p = reinterpret_cast<const uint4*>(src);
+#pragma unroll
+  for (int v = 0; v < 4; ++v) {
+    uint4 u = p[v];
+    const __nv_bfloat162* b2 = reinterpret_cast<const __nv_bfloat162*>(&u);
+#pragma unroll
+    for (int t = 0; t < 4; ++t) {
+      float2 f = __bfloat1622float2(b2[t]);
+      x[v * 8 + t * 2] = f.x;
+      x[v * 8 + t * 2 + 1] = f.y;
+    }
+  }
+}
+
+struct QuantGeom {
+  int Kd, KP, B, NT, TS;       // TS: scale row stride between the terms of a block
+  int64_t max_rows;
+  uint8_t* q;
+  uint8_t* sf;
+};
+
+// block j (32 elements) of source row `srow` -> sorted row r, packed-FP4 terms
+__device__ __forceinline__ void quant_unit_fp4(const __nv_bfloat16* src, int64_t srow, int j, int64_t r,
+                                               const QuantGeom& g) {
+  float x[32];
+  if (j * 32 < g.Kd) {
+    load_block32(src + srow * g.Kd + j * 32, x);
+  } else {                      // blocks of the K padding are written as zeros (finite scales)
+#pragma unroll
+    for (int i = 0; i < 32; ++i) x[i] = 0.f;
+  }
+  const int64_t term_stride = g.max_rows * (g.KP / 2);
+  for (int t = 0; t < g.NT; ++t) {
+    uint4 pk;
+    const int e = (t + 1 < g.NT) ? quant_block32_fp4<true>(x, pk) : quant_block32_fp4<false>(x, pk);
+    *reinterpret_cast<uint4*>(g.q + t * term_stride + r * (g.KP / 2) + j * 16) = pk;
+    g.sf[act_sf_index(r / g.B, j >> 2, g.KP / 128, g.B, g.NT, g.TS, t, (int)(r % g.B), j & 3)] = (uint8_t)e;
+  }
+}
+
+// the same for two e4m3 terms (KP == Kd, a multiple of 128)
+__device__ __forceinline__ void quant_unit_e4m3(const __nv_bfloat16* src, int64_t srow, int j, int64_t r,
+                                                const QuantGeom& g) {
+  float x[32];
+  load_block32(src + srow * g.Kd + j * 32, x);
+  const int64_t term_stride = g.max_rows * g.Kd;
+#pragma unroll
+  for (int t = 0; t < 2; ++t) {
+    uint4 q0, q1;
+    const int e = (t == 0) ? quant_block32_e4m3<true>(x, q0, q1) : quant_block32_e4m3<false>(x, q0, q1);
+    uint4* dst = reinterpret_cast<uint4*>(g.q + t * term_stride + r * g.Kd + j * 32);
+    dst[0] = q0;
+    dst[1] = q1;
+    g.sf[act_sf_index(r / g.B, j >> 2, g.Kd / 128, g.B, 2, 128, t, (int)(r % g.B), j & 3)] = (uint8_t)e;
+  }
+}
+
+// grid-stride zero fill in 16-byte vectors (the output buffer of the fused combine)
+__device__ __forceinline__ void zero_fill(uint4* ptr, int64_t nvec) {
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < nvec; i += (int64_t)gridDim.x * blockDim.x)
+    ptr[i] = make_uint4(0, 0, 0, 0);
+}
+
+template <int FMT>    // 0: packed-FP4 terms, 1: two e4m3 terms
 __global__ void __launch_bounds__(256)
 quant_rows_kernel(const __nv_bfloat16* __restrict__ src, int src_mode, const uint32_t* __restrict__ sorted_ids,
-                  const int32_t* __restrict__ num_valid, int T, int K, int Kd, int KP, int B, int NT, int TS,
-                  int64_t max_rows, uint8_t* __restrict__ q, uint8_t* __restrict__ sf) {
-  const int nb = KP / 32;
-  const int KB = KP / 128;
-  const int64_t term_stride = max_rows * (KP / 2);
+                  const int32_t* __restrict__ num_valid, int T, int K, QuantGeom g, uint4* zero_ptr, int64_t zero_vec) {
+  const int nb = g.KP / 32;
   grid_dep_launch();
   grid_dep_wait();
-  const int64_t rows_live = min((int64_t)num_valid[0], max_rows);
-  for (int64_t g = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; g < rows_live * nb;
-       g += (int64_t)gridDim.x * blockDim.x) {
-    const int64_t r = g / nb;
-    const int j = (int)(g % nb);
+  zero_fill(zero_ptr, zero_vec);
+  const int64_t rows_live = min((int64_t)num_valid[0], g.max_rows);
+  for (int64_t u = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; u < rows_live * nb;
+       u += (int64_t)gridDim.x * blockDim.x) {
+    const int64_t r = u / nb;
+    const int j = (int)(u % nb);
     const uint32_t id = sorted_ids[r];
     const int tok = (int)(id & 0xFFFFFFu), kk = (int)(id >> 24);
     // padding rows of a block are left unwritten: every token column of the GEMMs depends on its own row
     // only, and no kernel reads the columns of padding rows
     if (kk >= K || tok >= T) continue;
-    const bool valid = j * 32 < Kd;       // blocks of the K padding are written as zeros (finite scales)
-    float x[32];
-    if (valid) {
-      const int64_t srow = (src_mode == 0) ? (int64_t)tok : ((int64_t)tok * K + kk);
-      const uint4* p = reinterpret_cast<const uint4*>(src + srow * Kd + j * 32);
-#pragma unroll
-      for (int v = 0; v < 4; ++v) {
-        uint4 u = p[v];
-        const __nv_bfloat162* b2 = reinterpret_cast<const __nv_bfloat162*>(&u);
-#pragma unroll
-        for (int t = 0; t < 4; ++t) {
-          float2 f = __bfloat1622float2(b2[t]);
-          x[v * 8 + t * 2] = f.x;
-          x[v * 8 + t * 2 + 1] = f.y;
-        }
-      }
-    } else {
-#pragma unroll
-      for (int i = 0; i < 32; ++i) x[i] = 0.f;
-    }
-    for (int t = 0; t < NT; ++t) {
-      uint4 pk;
-      const int e = (t + 1 < NT) ? quant_block32_fp4<true>(x, pk) : quant_block32_fp4<false>(x, pk);
-      *reinterpret_cast<uint4*>(q + t * term_stride + r * (KP / 2) + j * 16) = pk;
-      sf[act_sf_index(r / B, j >> 2, KB, B, NT, TS, t, (int)(r % B), j & 3)] = (uint8_t)e;
-    }
+    const int64_t srow = (src_mode == 0) ? (int64_t)tok : ((int64_t)tok * K + kk);
+    if (FMT == 0) quant_unit_fp4(src, srow, j, r, g); else quant_unit_e4m3(src, srow, j, r, g);
   }
+}
+
+static int quant_grid(int64_t units) {
+  return (int)std::max<int64_t>(1, std::min<int64_t>((units + 255) / 256, (int64_t)device_sm_count() * 16));
 }
 
 int launch_quant_rows(const void* src, int src_mode, const uint32_t* sorted_ids, const int32_t* num_valid,
-                      int T, int K, int Kd, int B, int NT, int64_t max_rows, void* q, void* sf, cudaStream_t st) {
+                      int T, int K, int Kd, int B, int NT, int64_t max_rows, void* q, void* sf, void* zero_ptr,
+                      int64_t zero_bytes, cudaStream_t st) {
   B200_CHECK_ARG(B >= 16 && B <= 128 && B % 16 == 0, "quant_rows: B=%d is not a multiple of 16 in [16,128]", B);
-  B200_CHECK_ARG(NT >= 2 && NT <= 4, "quant_rows: %d activation terms (2..4 supported)", NT);
+  B200_CHECK_ARG(NT >= 1 && NT <= 4, "quant_rows: %d activation terms (1..4 supported)", NT);
   B200_CHECK_ARG(Kd % 32 == 0, "quant_rows: Kd=%d must be a multiple of 32", Kd);
+  B200_CHECK_ARG(zero_bytes % 16 == 0 && ((uintptr_t)zero_ptr & 15) == 0, "quant_rows: zero region must be 16-byte aligned");
   const int KP = (int)round_up64(Kd, kKPad);
-  int64_t work = max_rows * (KP / 32);
-  int blocks = (int)std::min<int64_t>((work + 255) / 256, 148 * 16);
-  if (blocks < 1) blocks = 1;
-  B200_CHECK_CUDA(launch_chained(quant_rows_kernel, dim3(blocks), dim3(256), 0, st,
-                                 reinterpret_cast<const __nv_bfloat16*>(src), src_mode, sorted_ids, num_valid, T, K, Kd,
-                                 KP, B, NT, act_term_stride(B, NT, 2), max_rows, (uint8_t*)q, (uint8_t*)sf));
+  QuantGeom g = {Kd, KP, B, NT, act_term_stride(B, NT, 2), max_rows, (uint8_t*)q, (uint8_t*)sf};
+  B200_CHECK_CUDA(launch_chained(quant_rows_kernel<0>, dim3(quant_grid(max_rows * (KP / 32))), dim3(256), 0, st,
+                                 reinterpret_cast<const __nv_bfloat16*>(src), src_mode, sorted_ids, num_valid, T, K, g,
+                                 (uint4*)zero_ptr, zero_bytes / 16));
   return 0;
 }
 
-// two-term e4m3 variant (operand of the FP8 GEMMs): q [2, max_rows, Kd] bytes, one scale chunk
-// per term (virtual row = term*128 + r)
+int launch_quant_rows_e4m3(const void* src, int src_mode, const uint32_t* sorted_ids, const int32_t* num_valid,
+                           int T, int K, int Kd, int B, int64_t max_rows, void* q, void* sf, void* zero_ptr,
+                           int64_t zero_bytes, cudaStream_t st) {
+  B200_CHECK_ARG(B >= 16 && B <= 96 && B % 16 == 0, "quant_rows (e4m3): B=%d is not a multiple of 16 in [16,96]", B);
+  B200_CHECK_ARG(Kd % 128 == 0, "quant_rows (e4m3): Kd=%d must be a multiple of 128", Kd);
+  B200_CHECK_ARG(zero_bytes % 16 == 0 && ((uintptr_t)zero_ptr & 15) == 0, "quant_rows: zero region must be 16-byte aligned");
+  QuantGeom g = {Kd, Kd, B, 2, 128, max_rows, (uint8_t*)q, (uint8_t*)sf};
+  B200_CHECK_CUDA(launch_chained(quant_rows_kernel<1>, dim3(quant_grid(max_rows * (Kd / 32))), dim3(256), 0, st,
+                                 reinterpret_cast<const __nv_bfloat16*>(src), src_mode, sorted_ids, num_valid, T, K, g,
+                                 (uint4*)zero_ptr, zero_bytes / 16));
+  return 0;
+}
+
+// =====================================================================================
+// Decode-sized batches (at most kSmallPairs (token, expert) pairs): sort/align and the input
+// quantiser in ONE launch.  Every CTA repeats the whole sort in shared memory -- a few hundred
+// integer operations -- and then quantises its share of the rows, so nothing waits for a
+// single-CTA sort launch; CTA 0 also writes the sort arrays for the GEMMs.  The rank of a pair
+// inside its expert is the number of earlier pairs with the same expert (token-major order), so
+// the result is the same stable order as sort_align_kernel's, bit for bit, with no atomics on
+// the order.  With T = 1 this is the reference's batch-1 shortcut (src/contrib/moe.py:79-84:
+// blocks are taken straight from topk_ids) in this library's data layout.
+// =====================================================================================
+constexpr int kSmallPairs = 256;
+constexpr int kSmallMaxE = 1024;
+
+template <int FMT>
 __global__ void __launch_bounds__(256)
-quant_rows_e4m3_kernel(const __nv_bfloat16* __restrict__ src, int src_mode, const uint32_t* __restrict__ sorted_ids,
-                       const int32_t* __restrict__ num_valid, int T, int K, int Kd, int B, int64_t max_rows,
-                       uint8_t* __restrict__ q, uint8_t* __restrict__ sf) {
-  const int nb = Kd / 32;
-  const int KB = Kd / 128;
-  const int64_t term_stride = max_rows * Kd;
+sort_quant_small_kernel(const __nv_bfloat16* __restrict__ x, const int32_t* __restrict__ ids,
+                        const float* __restrict__ w, int T, int K, int E, const int32_t* __restrict__ mask,
+                        const int32_t* __restrict__ num_local, uint32_t* __restrict__ sorted_ids,
+                        float* __restrict__ sorted_w, int32_t* __restrict__ sorted_e,
+                        int32_t* __restrict__ num_valid, int32_t* __restrict__ loc, QuantGeom g, uint4* zero_ptr,
+                        int64_t zero_vec) {
+  __shared__ int32_t pair_e[kSmallPairs], pair_pos[kSmallPairs];
+  __shared__ int32_t cnt[kSmallMaxE], base[kSmallMaxE], lid[kSmallMaxE];
+  __shared__ unsigned long long wsum[9];
   grid_dep_launch();
   grid_dep_wait();
-  const int64_t rows_live = min((int64_t)num_valid[0], max_rows);
-  for (int64_t g = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; g < rows_live * nb;
-       g += (int64_t)gridDim.x * blockDim.x) {
-    const int64_t r = g / nb;
-    const int j = (int)(g % nb);
-    const uint32_t id = sorted_ids[r];
-    const int tok = (int)(id & 0xFFFFFFu), kk = (int)(id >> 24);
-    if (kk >= K || tok >= T) continue;    // padding rows are left unwritten (see quant_rows_kernel)
-    const bool valid = true;
-    float x[32];
-    if (valid) {
-      const int64_t srow = (src_mode == 0) ? (int64_t)tok : ((int64_t)tok * K + kk);
-      const uint4* p = reinterpret_cast<const uint4*>(src + srow * Kd + j * 32);
+  zero_fill(zero_ptr, zero_vec);
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int P = T * K, B = g.B;
+  const int T_live = (num_local != nullptr) ? min(T, max(num_local[0], 0)) : T;
+  for (int e = tid; e < E; e += 256) cnt[e] = 0;
+  const int my_e = sort_fetch_expert(ids, mask, tid, min(P, T_live * K), E);
+  if (tid < kSmallPairs) pair_e[tid] = my_e;
+  __syncthreads();
+  int rank = 0;
+  if (my_e >= 0) {
+    for (int i = 0; i < tid; ++i) rank += (pair_e[i] == my_e);
+    atomicAdd(&cnt[my_e], 1);            // a count only: its value does not depend on the order of the adds
+  }
+  __syncthreads();
+  // exclusive scan over the experts of (padded rows, emitted expert id); four consecutive experts per thread
+  {
+    unsigned long long v[4], run = 0;
 #pragma unroll
-      for (int v = 0; v < 4; ++v) {
-        uint4 u = p[v];
-        const __nv_bfloat162* b2 = reinterpret_cast<const __nv_bfloat162*>(&u);
-#pragma unroll
-        for (int t = 0; t < 4; ++t) {
-          float2 f = __bfloat1622float2(b2[t]);
-          x[v * 8 + t * 2] = f.x;
-          x[v * 8 + t * 2 + 1] = f.y;
-        }
+    for (int q = 0; q < 4; ++q) {
+      const int e = tid * 4 + q;
+      unsigned long long t = 0;
+      if (e < E) {
+        const unsigned padded = (unsigned)((cnt[e] + B - 1) / B * B);
+        const unsigned live = (mask == nullptr || mask[e] != 0) ? 1u : 0u;
+        t = ((unsigned long long)padded << 32) | live;
       }
-    } else {
-#pragma unroll
-      for (int i = 0; i < 32; ++i) x[i] = 0.f;
+      v[q] = run;
+      run += t;
     }
-#pragma unroll
-    for (int t = 0; t < 2; ++t) {
-      uint4 q0, q1;
-      const int e = (t == 0) ? quant_block32_e4m3<true>(x, q0, q1) : quant_block32_e4m3<false>(x, q0, q1);
-      uint4* dst = reinterpret_cast<uint4*>(q + t * term_stride + r * Kd + j * 32);
-      dst[0] = q0;
-      dst[1] = q1;
-      sf[act_sf_index(r / B, j >> 2, KB, B, 2, 128, t, (int)(r % B), j & 3)] = (uint8_t)e;
+    unsigned long long incl = run;
+    for (int d = 1; d < 32; d <<= 1) {
+      const unsigned long long o = __shfl_up_sync(0xffffffffu, incl, d);
+      if (lane >= d) incl += o;
     }
+    if (lane == 31) wsum[warp] = incl;
+    __syncthreads();
+    if (tid == 0) {
+      unsigned long long acc = 0;
+      for (int i = 0; i < 8; ++i) { const unsigned long long t = wsum[i]; wsum[i] = acc; acc += t; }
+      wsum[8] = acc;
+    }
+    __syncthreads();
+    const unsigned long long off = wsum[warp] + incl - run;
+#pragma unroll
+    for (int q = 0; q < 4; ++q) {
+      const int e = tid * 4 + q;
+      if (e < E) {
+        base[e] = (int)((off + v[q]) >> 32);
+        lid[e] = (int)((off + v[q]) & 0xffffffffu);
+      }
+    }
+  }
+  __syncthreads();
+  const int pos = (my_e >= 0) ? base[my_e] + rank : -1;
+  if (tid < kSmallPairs) pair_pos[tid] = pos;
+  if (blockIdx.x == 0) {
+    if (tid < P) {
+      if (pos >= 0) {
+        sorted_ids[pos] = ((uint32_t)(tid % K) << 24) | (uint32_t)(tid / K);
+        sorted_w[pos] = w[tid];
+      }
+      if (loc != nullptr) loc[tid] = pos;
+    }
+    const uint32_t sentinel = ((uint32_t)K << 24) | (uint32_t)T;
+    for (int e = tid; e < E; e += 256) {
+      const int n = cnt[e];
+      if (n == 0) continue;
+      const int b0 = base[e], n_pad = (n + B - 1) / B * B;
+      for (int r = b0 + n; r < b0 + n_pad; ++r) {
+        sorted_ids[r] = sentinel;
+        sorted_w[r] = 0.f;
+      }
+      for (int blk = b0 / B; blk < (b0 + n_pad) / B; ++blk) sorted_e[blk] = lid[e];
+    }
+    if (tid == 0) {
+      num_valid[0] = (int)(wsum[8] >> 32);
+      num_valid[1] = T_live;
+    }
+  }
+  __syncthreads();
+  // quantise: one unit = (pair, 32-element block of its token's row)
+  const int nb = g.KP / 32;
+  for (int u = blockIdx.x * 256 + tid; u < P * nb; u += gridDim.x * 256) {
+    const int i = u / nb, j = u - i * nb;
+    const int r = pair_pos[i];
+    if (r < 0) continue;
+    if (FMT == 0) quant_unit_fp4(x, i / K, j, r, g); else quant_unit_e4m3(x, i / K, j, r, g);
   }
 }
 
-int launch_quant_rows_e4m3(const void* src, int src_mode, const uint32_t* sorted_ids, const int32_t* num_valid,
-                           int T, int K, int Kd, int B, int64_t max_rows, void* q, void* sf, cudaStream_t st) {
-  B200_CHECK_ARG(B >= 16 && B <= 96 && B % 16 == 0, "quant_rows (e4m3): B=%d is not a multiple of 16 in [16,96]", B);
-  B200_CHECK_ARG(Kd % 128 == 0, "quant_rows (e4m3): Kd=%d must be a multiple of 128", Kd);
-  int64_t work = max_rows * (Kd / 32);
-  int blocks = (int)std::min<int64_t>((work + 255) / 256, 148 * 16);
-  if (blocks < 1) blocks = 1;
-  B200_CHECK_CUDA(launch_chained(quant_rows_e4m3_kernel, dim3(blocks), dim3(256), 0, st,
-                                 reinterpret_cast<const __nv_bfloat16*>(src), src_mode, sorted_ids, num_valid, T, K, Kd,
-                                 B, max_rows, (uint8_t*)q, (uint8_t*)sf));
+bool sort_quant_small_ok(int T, int K, int E) { return (int64_t)T * K <= kSmallPairs && E <= kSmallMaxE && T >= 1; }
+
+int launch_sort_quant_small(int fmt, const void* x, const int32_t* ids, const float* w, int T, int K, int E, int B,
+                            const int32_t* mask, const int32_t* num_local, uint32_t* sorted_ids, float* sorted_w,
+                            int32_t* sorted_e, int32_t* num_valid, int32_t* loc, int Kd, int NT, int64_t max_rows,
+                            void* q, void* sf, void* zero_ptr, int64_t zero_bytes, cudaStream_t st) {
+  B200_CHECK_ARG(sort_quant_small_ok(T, K, E), "sort_quant_small: T*K=%d pairs / E=%d outside the small-batch path", T * K, E);
+  B200_CHECK_ARG(B >= 16 && B <= 128 && B % 16 == 0, "sort_quant_small: B=%d", B);
+  B200_CHECK_ARG(zero_bytes % 16 == 0 && ((uintptr_t)zero_ptr & 15) == 0, "sort_quant_small: zero region must be 16-byte aligned");
+  if (fmt == 0) {
+    B200_CHECK_ARG(NT >= 1 && NT <= 4 && Kd % 32 == 0, "sort_quant_small: terms %d / Kd %d", NT, Kd);
+    const int KP = (int)round_up64(Kd, kKPad);
+    QuantGeom g = {Kd, KP, B, NT, act_term_stride(B, NT, 2), max_rows, (uint8_t*)q, (uint8_t*)sf};
+    B200_CHECK_CUDA(launch_chained(sort_quant_small_kernel<0>, dim3(quant_grid((int64_t)T * K * (KP / 32))), dim3(256), 0,
+                                   st, (const __nv_bfloat16*)x, ids, w, T, K, E, mask, num_local, sorted_ids, sorted_w,
+                                   sorted_e, num_valid, loc, g, (uint4*)zero_ptr, zero_bytes / 16));
+  } else {
+    B200_CHECK_ARG(Kd % 128 == 0 && B <= 96, "sort_quant_small (e4m3): Kd %d / B %d", Kd, B);
+    QuantGeom g = {Kd, Kd, B, 2, 128, max_rows, (uint8_t*)q, (uint8_t*)sf};
+    B200_CHECK_CUDA(launch_chained(sort_quant_small_kernel<1>, dim3(quant_grid((int64_t)T * K * (Kd / 32))), dim3(256), 0,
+                                   st, (const __nv_bfloat16*)x, ids, w, T, K, E, mask, num_local, sorted_ids, sorted_w,
+                                   sorted_e, num_valid, loc, g, (uint4*)zero_ptr, zero_bytes / 16));
+  }
   return 0;
 }
 
@@ -491,6 +621,9 @@ int launch_quant_rows_e4m3(const void* src, int src_mode, const uint32_t* sorted
 // combine: y[t,:] = sum over the token's pairs, in ascending sorted position (= ascending
 // expert id), of bf16(out2[loc] * w), each partial sum rounded to bf16 -- the arithmetic of
 // the reference's index_add_ loop (tests/contrib/moe/test_moe.py:107-117).
+// One warp per token: the token's K positions are ordered once (lane i ends up holding the
+// i-th smallest position and its weight), then the lanes walk the row in 16-byte vectors.
+// topk_w == nullptr: the routing weights were applied upstream (weight 1 here).
 // =====================================================================================
 constexpr int kMaxTopk = 32;
 
@@ -500,33 +633,50 @@ combine_kernel(const __nv_bfloat16* __restrict__ out2, const int32_t* __restrict
   const int vec_per_row = H / 8;
   grid_dep_launch();
   grid_dep_wait();
-  for (int64_t g = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; g < (int64_t)T * vec_per_row;
-       g += (int64_t)gridDim.x * blockDim.x) {
-    const int t = (int)(g / vec_per_row), c = (int)(g % vec_per_row) * 8;
-    float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
-    int last = -1;
-    for (int it = 0; it < K; ++it) {
-      int best = 0x7fffffff, best_k = -1;
-      for (int k = 0; k < K; ++k) {
-        int p = loc[t * K + k];
-        if (p > last && p < best) { best = p; best_k = k; }
-      }
-      if (best_k < 0) break;
-      last = best;
-      const float wv = topk_w[t * K + best_k];
-      uint4 u = *reinterpret_cast<const uint4*>(out2 + (int64_t)best * H + c);
-      const __nv_bfloat16* d = reinterpret_cast<const __nv_bfloat16*>(&u);
+  const int lane = threadIdx.x & 31;
+  const int warps = (gridDim.x * blockDim.x) >> 5;
+  for (int t = (blockIdx.x * blockDim.x + threadIdx.x) >> 5; t < T; t += warps) {
+    const int p = (lane < K) ? loc[t * K + lane] : -1;
+    const float wv = (lane < K) ? (topk_w != nullptr ? topk_w[t * K + lane] : 1.f) : 0.f;
+    int rank = 0;
+    for (int k = 0; k < K; ++k) {
+      const int o = __shfl_sync(0xffffffffu, p, k);
+      rank += (o >= 0 && o < p);
+    }
+    const int n = __popc(__ballot_sync(0xffffffffu, p >= 0));
+    // lane i fetches the pair whose rank is i (positions are distinct)
+    int ps = -1;
+    float ws = 0.f;
+    for (int k = 0; k < K; ++k) {
+      const int o = __shfl_sync(0xffffffffu, p, k), r = __shfl_sync(0xffffffffu, rank, k);
+      const float ow = __shfl_sync(0xffffffffu, wv, k);
+      if (o >= 0 && r == lane) { ps = o; ws = ow; }
+    }
+    for (int c0 = 0; c0 < vec_per_row; c0 += 32) {       // warp-uniform trip count: the shuffles need every lane
+      const int c = c0 + lane;
+      const bool active = c < vec_per_row;
+      float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+      for (int it = 0; it < n; ++it) {
+        const int pos = __shfl_sync(0xffffffffu, ps, it);
+        const float wt = __shfl_sync(0xffffffffu, ws, it);
+        if (active) {
+          const uint4 u = *reinterpret_cast<const uint4*>(out2 + (int64_t)pos * H + c * 8);
+          const __nv_bfloat16* d = reinterpret_cast<const __nv_bfloat16*>(&u);
 #pragma unroll
-      for (int i = 0; i < 8; ++i) {
-        float contrib = __bfloat162float(__float2bfloat16_rn(__bfloat162float(d[i]) * wv));
-        acc[i] = __bfloat162float(__float2bfloat16_rn(acc[i] + contrib));
+          for (int i = 0; i < 8; ++i) {
+            const float contrib = __bfloat162float(__float2bfloat16_rn(__bfloat162float(d[i]) * wt));
+            acc[i] = __bfloat162float(__float2bfloat16_rn(acc[i] + contrib));
+          }
+        }
+      }
+      if (active) {
+        uint4 o;
+        __nv_bfloat16* ob = reinterpret_cast<__nv_bfloat16*>(&o);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) ob[i] = __float2bfloat16_rn(acc[i]);
+        *reinterpret_cast<uint4*>(y + (int64_t)t * H + c * 8) = o;
       }
     }
-    uint4 o;
-    __nv_bfloat16* ob = reinterpret_cast<__nv_bfloat16*>(&o);
-#pragma unroll
-    for (int i = 0; i < 8; ++i) ob[i] = __float2bfloat16_rn(acc[i]);
-    *reinterpret_cast<uint4*>(y + (int64_t)t * H + c) = o;
   }
 }
 
@@ -534,8 +684,7 @@ int launch_combine(const void* out2, const int32_t* loc, const float* topk_w, vo
                    cudaStream_t st) {
   B200_CHECK_ARG(H % 8 == 0 && K <= kMaxTopk, "combine: H %% 8 != 0 or K > %d", kMaxTopk);
   if (T == 0) return 0;
-  int64_t work = (int64_t)T * (H / 8);
-  int blocks = (int)std::min<int64_t>((work + 255) / 256, 148 * 16);
+  const int blocks = (int)std::min<int64_t>(((int64_t)T + 7) / 8, (int64_t)device_sm_count() * 16);
   B200_CHECK_CUDA(launch_chained(combine_kernel, dim3(blocks), dim3(256), 0, st, (const __nv_bfloat16*)out2, loc,
                                  topk_w, (__nv_bfloat16*)y, T, K, H));
   return 0;
@@ -579,9 +728,99 @@ int launch_gather_sum(const void* rows, const int32_t* pos, void* y, int T, int 
   B200_CHECK_ARG(H % 8 == 0 && S >= 1, "gather_sum: H %% 8 != 0 or no slots");
   if (T == 0) return 0;
   int64_t work = (int64_t)T * (H / 8);
-  int blocks = (int)std::min<int64_t>((work + 255) / 256, 148 * 16);
+  int blocks = (int)std::min<int64_t>((work + 255) / 256, device_sm_count() * 16);
   B200_CHECK_CUDA(launch_chained(gather_sum_kernel, dim3(blocks), dim3(256), 0, st, (const __nv_bfloat16*)rows, pos,
                                  (__nv_bfloat16*)y, T, S, H));
+  return 0;
+}
+
+// =====================================================================================
+// expert-parallel dispatch plan, one launch: which tokens travel to which rank and where they sit in
+// the rank-major send buffer.  Rank d owns experts [d*epr, (d+1)*epr); token t goes to rank d once if
+// any of its K experts lives there.  pos[t, d] = position of t in the send buffer (ascending rank,
+// ascending token within a rank) or -1; counts[d] = tokens bound for rank d; rows[p] = token at
+// send-buffer position p for p < sum(counts).  One CTA: every thread owns a contiguous run of
+// tokens, per-rank running counts are scanned across the threads, so the order is fixed (no atomics).
+// =====================================================================================
+constexpr int kPlanThreads = 1024;
+constexpr int kPlanMaxWorld = 32;
+
+__global__ void __launch_bounds__(kPlanThreads, 1)
+ep_plan_kernel(const int32_t* __restrict__ ids, int T, int K, int epr, int W, int32_t* __restrict__ pos,
+               int32_t* __restrict__ counts, int32_t* __restrict__ rows) {
+  extern __shared__ int32_t cnt[];                 // [kPlanThreads][W], then offs[W]
+  int32_t* offs = cnt + kPlanThreads * W;
+  grid_dep_launch();
+  grid_dep_wait();
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int chunk = (T + kPlanThreads - 1) / kPlanThreads;
+  const int t0 = min(T, tid * chunk), t1 = min(T, t0 + chunk);
+  auto needs = [&](int t) {
+    uint32_t m = 0;
+    for (int k = 0; k < K; ++k) {
+      const int id = ids[(int64_t)t * K + k];
+      const int d = min(max(id >= 0 ? id / epr : 0, 0), W - 1);
+      m |= 1u << d;
+    }
+    return m;
+  };
+  for (int d = 0; d < W; ++d) cnt[tid * W + d] = 0;
+  for (int t = t0; t < t1; ++t) {
+    uint32_t m = needs(t);
+    while (m) {
+      const int d = __ffs(m) - 1;
+      m &= m - 1;
+      cnt[tid * W + d] += 1;
+    }
+  }
+  __syncthreads();
+  // exclusive scan over the threads, one warp per destination rank
+  for (int d = warp; d < W; d += kPlanThreads / 32) {
+    int run = 0;
+    for (int base = 0; base < kPlanThreads; base += 32) {
+      const int v = cnt[(base + lane) * W + d];
+      int incl = v;
+      for (int s = 1; s < 32; s <<= 1) {
+        const int o = __shfl_up_sync(0xffffffffu, incl, s);
+        if (lane >= s) incl += o;
+      }
+      cnt[(base + lane) * W + d] = run + incl - v;
+      run += __shfl_sync(0xffffffffu, incl, 31);
+    }
+    if (lane == 0) offs[d] = run;            // total for rank d (turned into an offset below)
+  }
+  __syncthreads();
+  if (tid == 0) {
+    int run = 0;
+    for (int d = 0; d < W; ++d) {
+      const int c = offs[d];
+      counts[d] = c;
+      offs[d] = run;
+      run += c;
+    }
+  }
+  __syncthreads();
+  for (int t = t0; t < t1; ++t) {
+    const uint32_t m = needs(t);
+    for (int d = 0; d < W; ++d) {
+      int p = -1;
+      if (m & (1u << d)) {
+        p = offs[d] + cnt[tid * W + d];
+        cnt[tid * W + d] += 1;
+        rows[p] = t;
+      }
+      pos[(int64_t)t * W + d] = p;
+    }
+  }
+}
+
+int launch_ep_plan(const int32_t* ids, int T, int K, int epr, int W, int32_t* pos, int32_t* counts, int32_t* rows,
+                   cudaStream_t st) {
+  B200_CHECK_ARG(T >= 0 && K >= 1 && epr >= 1 && W >= 1 && W <= kPlanMaxWorld, "ep_plan: T=%d K=%d experts/rank=%d world=%d",
+                 T, K, epr, W);
+  const size_t smem = (size_t)(kPlanThreads * W + W) * sizeof(int32_t);
+  B200_CHECK_CUDA(cudaFuncSetAttribute(ep_plan_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024));
+  B200_CHECK_CUDA(launch_chained(ep_plan_kernel, dim3(1), dim3(kPlanThreads), smem, st, ids, T, K, epr, W, pos, counts, rows));
   return 0;
 }
 
@@ -663,7 +902,7 @@ int launch_route_topk(const float* logits, int T, int E, int K, int scoring, int
   B200_CHECK_ARG(E >= 1 && E <= 32 * kRouteMaxPerLane && K >= 1 && K <= E, "route_topk: E=%d K=%d", E, K);
   B200_CHECK_ARG(scoring == 0 || scoring == 1, "route_topk: scoring=%d (0 softmax, 1 sigmoid)", scoring);
   if (T == 0) return 0;
-  const int blocks = std::min((T + 7) / 8, 148 * 8);
+  const int blocks = std::min((T + 7) / 8, device_sm_count() * 8);
   B200_CHECK_CUDA(launch_chained(route_topk_kernel, dim3(blocks), dim3(256), 0, st, logits, T, E, K, scoring, renorm, ids,
                                  weights));
   return 0;
@@ -704,7 +943,7 @@ int launch_repack_scales(const void* w_s, void* out, int E, bool gateup, int row
   const int KB = (int)round_up64(Kd, kKPad) / 128;
   const int MT = gateup ? (rows + 127) / 128 : (rows + 255) / 256;
   int64_t total = (int64_t)E * MT * KB * 2 * kSfChunk;
-  int blocks = (int)std::min<int64_t>((total + 255) / 256, 148 * 32);
+  int blocks = (int)std::min<int64_t>((total + 255) / 256, device_sm_count() * 32);
   repack_scales_kernel<<<blocks, 256, 0, st>>>((const uint8_t*)w_s, (uint8_t*)out, E, gateup ? 1 : 0, rows, Kd / 32,
                                                MT, KB);
   B200_CHECK_CUDA(cudaGetLastError());

@@ -57,6 +57,10 @@ struct Params {
   int64_t oq_term_stride;
   int B, rows, KB, MT, E, topk, T, stages, out_k, out_kb, activation;
   float swiglu_limit;
+  const float* sorted_w;   // routing weight of every sorted row (fused combine, weights applied in the gate-up stage)
+  const float* bias;       // per-expert bias: gate-up [E, 2*rows] (gate then up), down [E, rows]; or null
+  __nv_bfloat16* y;        // down, fused combine: zeroed [T, rows] output accumulated with bf16x2 reductions; or null
+  int weight_stage1;       // gate-up: multiply h by the routing weight
 };
 
 struct SmemCtl {
@@ -191,21 +195,24 @@ __global__ void __launch_bounds__(kThreads, 1) moe_grouped_gemm_fp8_kernel(const
       int stage = 0;
       uint32_t phase = 0, acc = 0, acc_phase = 0, sf_buf = 0, sf_phase = 0;
       bool ok = true;
-      long long t_acc = 0, t_full = 0, t_sf = 0;     // profiling: cycles spent in each wait
-      const long long t_begin = clock64();
+      PROF_DECL(t_acc);
+      PROF_DECL(t_full);
+      PROF_DECL(t_sf);
+      const long long t_begin = PROF_NOW();
+      (void)t_begin;
       for (int w = blockIdx.x; w < total_work && ok; w += gridDim.x) {
         for (int kb = 0; kb < p.KB; ++kb) {
           // every k-block gets its own accumulator buffer: the epilogue promotes it with the
           // block's fp32 weight scale while the next k-block is being multiplied
-          const long long c0 = clock64();
+          const long long c0 = PROF_NOW();
           ok = mbar_wait(smem_u32(&ctl->tmem_empty[2 * acc + part]), acc_phase ^ 1, abort_word, 0x200 + 2 * acc + part);
-          const long long c1 = clock64();
+          PROF_ADD(t_acc, c0);
+          const long long c1 = PROF_NOW();
           ok = ok && mbar_wait(smem_u32(&ctl->full[stage]), phase, abort_word, 0x300 + stage);
-          const long long c2 = clock64();
+          PROF_ADD(t_full, c1);
+          const long long c2 = PROF_NOW();
           ok = ok && mbar_wait(smem_u32(&ctl->sf_full[sf_buf]), sf_phase, abort_word, 0x500 + sf_buf);
-          t_acc += c1 - c0;
-          t_full += c2 - c1;
-          t_sf += clock64() - c2;
+          PROF_ADD(t_sf, c2);
           if (!ok) break;
           tc_fence_after_sync();
           __syncwarp();
@@ -233,12 +240,14 @@ __global__ void __launch_bounds__(kThreads, 1) moe_grouped_gemm_fp8_kernel(const
           if (++stage == S) { stage = 0; phase ^= 1; }
         }
       }
+#ifdef B200MOE_PROFILE
       if (blockIdx.x == 0 && lane == 0 && part == 0) {   // kilo-cycles: issuer total, waiting for data, for an accumulator, for scales
         p.status[5] = (int32_t)((clock64() - t_begin) >> 10);
         p.status[6] = (int32_t)(t_full >> 10);
         p.status[7] = (int32_t)(t_acc >> 10);
         p.status[4] = (int32_t)(t_sf >> 10);
       }
+#endif
     } else if (warp == 3) {
       // ------------------------------------------------------------------ store warp (fused gate-up only):
       // takes each finished h tile from the staging buffer, re-quantises it into two e4m3 terms with
@@ -271,6 +280,11 @@ __global__ void __launch_bounds__(kThreads, 1) moe_grouped_gemm_fp8_kernel(const
               }
             }
             const int64_t r = (int64_t)r0 + n;
+            if (p.weight_stage1) {
+              const float wr = p.sorted_w[r];
+  #pragma unroll
+              for (int i = 0; i < 32; ++i) x[i] = bf16r(x[i] * wr);
+            }
   #pragma unroll
             for (int t = 0; t < kTerms; ++t) {
               uint4 q0, q1;
@@ -305,7 +319,26 @@ __global__ void __launch_bounds__(kThreads, 1) moe_grouped_gemm_fp8_kernel(const
               for (int idx = lane; idx < nvalid * 16; idx += 32) {
                 const int n = idx >> 4, v = idx & 15;
                 const uint4 val = ld_shared_v4(stg + (uint32_t)n * kStagePitch + v * 16);
-                *reinterpret_cast<uint4*>(p.out2 + ((int64_t)r0 + n) * p.rows + f0 + v * 8) = val;
+                if (p.y == nullptr) {
+                  *reinterpret_cast<uint4*>(p.out2 + ((int64_t)r0 + n) * p.rows + f0 + v * 8) = val;
+                } else {
+                  // fused combine: y[token] += bf16(row * routing weight), 16 bytes per reduction
+                  // (the reference's weighted atomic epilogue, src/contrib/moe.py:703-787)
+                  const uint32_t id = p.sorted_ids[r0 + n];
+                  const float wr = p.sorted_w[r0 + n];
+                  const __nv_bfloat162* b2 = reinterpret_cast<const __nv_bfloat162*>(&val);
+                  uint32_t o[4];
+  #pragma unroll
+                  for (int i = 0; i < 4; ++i) {
+                    const float2 f = __bfloat1622float2(b2[i]);
+                    const __nv_bfloat162 c = __floats2bfloat162_rn(f.x * wr, f.y * wr);
+                    o[i] = *reinterpret_cast<const uint32_t*>(&c);
+                  }
+                  __nv_bfloat16* dst = p.y + (int64_t)(id & 0xFFFFFFu) * p.rows + f0 + v * 8;
+                  asm volatile("red.global.add.noftz.v4.bf16x2 [%0], {%1, %2, %3, %4};" ::"l"(dst), "r"(o[0]), "r"(o[1]),
+                               "r"(o[2]), "r"(o[3])
+                               : "memory");
+                }
               }
             }
             __syncwarp();
@@ -359,10 +392,12 @@ __global__ void __launch_bounds__(kThreads, 1) moe_grouped_gemm_fp8_kernel(const
     const int row_blocks = (GATEUP ? 2 * p.rows : p.rows) / kTileM;   // weight-scale rows per expert
     uint32_t acc = 0, acc_phase = 0;
     bool alive = true;
-    long long t_wait_epi = 0, t_ld = 0, t_fma = 0;
+    PROF_DECL(t_wait_epi);
+    PROF_DECL(t_fma);
     int tile_par = 0;
     uint32_t stg_phase = 0;
-    const long long t_begin_epi = clock64();
+    const long long t_begin_epi = PROF_NOW();
+    (void)t_begin_epi;
     for (int w = blockIdx.x; w < total_work && alive; w += gridDim.x) {
       const int b = w / p.MT, m = w - b * p.MT;
       const int r0 = b * B;
@@ -392,9 +427,9 @@ __global__ void __launch_bounds__(kThreads, 1) moe_grouped_gemm_fp8_kernel(const
         const float sc[2] = {ws[0][kb], ws[1][kb]};
 #pragma unroll
         for (int part = 0; part < 2; ++part) {
-          const long long te0 = clock64();
+          const long long te0 = PROF_NOW();
           const bool ok = mbar_wait(smem_u32(&ctl->tmem_full[2 * acc + part]), acc_phase, abort_word, 0x400 + 2 * acc + part);
-          t_wait_epi += clock64() - te0;
+          PROF_ADD(t_wait_epi, te0);
           if (!ok) { alive = false; break; }      // the vote after the k loop takes every warp out together
           tc_fence_after_sync();
           const uint32_t t0 = tmem_base + ((uint32_t)(quad * 32) << 16) + acc * acc_cols + part * B;
@@ -426,10 +461,21 @@ __global__ void __launch_bounds__(kThreads, 1) moe_grouped_gemm_fp8_kernel(const
       // waits return at once and every epilogue warp leaves before the next named barrier
       if (staged && alive) alive = mbar_wait(smem_u32(&ctl->stg_empty), stg_phase ^ 1, abort_word, 0x800);
       if (!epi_all(alive)) break;
-      const long long tt0 = clock64();
+      const long long tt0 = PROF_NOW();
 
       // ---- tile finished: activation / stores from the register accumulators
       const bool j_ok = j < p.rows;
+      if (p.bias != nullptr) {
+        // the oracle's matmul returns bf16 and the bias is added to that (the consumers below round once more)
+        const float* be = p.bias + (int64_t)e * (GATEUP ? 2 : 1) * p.rows;
+        const float b0 = j_ok ? be[j] : 0.f;
+        const float b1 = GATEUP ? (j_ok ? be[p.rows + j] : 0.f) : (j + kTileM < p.rows ? be[j + kTileM] : 0.f);
+#pragma unroll
+        for (int i = 0; i < kMaxChunks * 16; ++i) {
+          ag[i] = bf16r(ag[i]) + b0;
+          au[i] = bf16r(au[i]) + b1;
+        }
+      }
 #pragma unroll
       for (int ci = 0; ci < kMaxChunks; ++ci) {
         const int c0 = (2 * ci + half) * 16;
@@ -442,7 +488,8 @@ __global__ void __launch_bounds__(kThreads, 1) moe_grouped_gemm_fp8_kernel(const
                 const uint32_t id = __shfl_sync(0xffffffffu, my_id, n);
                 if (c0 + n < nvalid) {
                   const int tok = (int)(id & 0xFFFFFFu), kk = (int)(id >> 24);
-                  const float v = gateup_act(ag[ci * 16 + n], au[ci * 16 + n], p.activation, p.swiglu_limit);
+                  float v = gateup_act(ag[ci * 16 + n], au[ci * 16 + n], p.activation, p.swiglu_limit);
+                  if (p.weight_stage1) v *= p.sorted_w[r0 + c0 + n];
                   if (j_ok) p.h_out[((int64_t)tok * p.topk + kk) * p.rows + j] = __float2bfloat16_rn(v);
                 }
               }
@@ -492,14 +539,15 @@ __global__ void __launch_bounds__(kThreads, 1) moe_grouped_gemm_fp8_kernel(const
         if (lane == 0) mbar_arrive(smem_u32(&ctl->stg_full));
         stg_phase ^= 1;
       }
-      t_fma += clock64() - tt0;
+      PROF_ADD(t_fma, tt0);
     }
-    if (blockIdx.x == 0 && tid_e == 0) {     // kilo-cycles: epilogue total, waiting for an accumulator
+#ifdef B200MOE_PROFILE
+    if (blockIdx.x == 0 && tid_e == 0) {     // kilo-cycles: epilogue total, waiting for an accumulator, after the k loop
       p.status[8] = (int32_t)((clock64() - t_begin_epi) >> 10);
       p.status[9] = (int32_t)(t_wait_epi >> 10);
-      p.status[10] = (int32_t)(t_ld >> 10);
       p.status[11] = (int32_t)(t_fma >> 10);
     }
+#endif
   }
 
   __syncwarp();
@@ -535,6 +583,10 @@ int launch_grouped_gemm_fp8(const GemmArgs& a, cudaStream_t st) {
   p.h_out = (__nv_bfloat16*)a.h_out; p.oq = (uint8_t*)a.oq; p.osf = (uint8_t*)a.osf;
   p.out_k = a.out_kp; p.out_kb = a.out_kp / 128; p.oq_term_stride = a.max_rows * (int64_t)a.out_kp;
   p.out2 = (__nv_bfloat16*)a.out2;
+  p.sorted_w = a.sorted_w; p.bias = a.bias; p.y = a.gateup ? nullptr : (__nv_bfloat16*)a.y;
+  p.weight_stage1 = (a.gateup && a.weight_stage1) ? 1 : 0;
+  B200_CHECK_ARG((p.y == nullptr && p.weight_stage1 == 0) || a.sorted_w != nullptr, "fp8 grouped gemm: routing weights missing");
+  B200_CHECK_ARG(((uintptr_t)p.y & 15) == 0, "fp8 grouped gemm: fused combine needs a 16-byte aligned output");
   if (a.gateup && a.h_out == nullptr)
     B200_CHECK_ARG(a.out_kp == a.rows && a.oq && a.osf, "fp8 gate-up: fused output buffers missing");
   {

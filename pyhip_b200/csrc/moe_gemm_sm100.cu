@@ -35,7 +35,8 @@
 // CTAs running at the same time share activation tiles and neighbouring blocks of an expert share
 // weight tiles in L2.
 // All barrier waits are bounded; a wait that runs out sets status[] and the CTA unwinds (frees its
-// tensor memory) instead of spinning.  status[4..9] carry cycle counters of CTA 0's roles.
+// tensor memory) instead of spinning.  A build with -DB200MOE_PROFILE additionally leaves cycle counters
+// of CTA 0's roles in status[4..9]; the production build carries no timing code.
 #include <cuda_bf16.h>
 #include <cuda_fp4.h>
 #include <cuda_fp8.h>
@@ -79,6 +80,10 @@ struct GemmParams {
   int k_tail_steps;    // 64-wide k-steps of the last stage that hold data (the rest of it is zero padding)
   uint8_t* gstage;     // per-CTA staging tiles in global memory (L2) instead of shared memory, or null
   float swiglu_limit;
+  const float* sorted_w;   // routing weight of every sorted row (fused combine, weights applied in the gate-up stage)
+  const float* bias;       // per-expert bias: gate-up [E, 2*rows] (gate then up), down [E, rows]; or null
+  __nv_bfloat16* y;        // down, fused combine: zeroed [T, rows] output accumulated with bf16x2 reductions; or null
+  int weight_stage1;       // gate-up: multiply h by the routing weight (the down stage then applies none)
 };
 
 struct SmemCtl {
@@ -170,7 +175,7 @@ moe_grouped_gemm_kernel(const __grid_constant__ GemmParams p) {
       uint32_t phase = 0;
       int64_t issued = 0;
       bool ok = true;
-      long long t_wait = 0;
+      PROF_DECL(t_wait);
       const int64_t sfa_step = geo.sfa_bytes;
       for (int w = blockIdx.x; w < total_work && ok; w += gridDim.x) {
         const int b = w / p.MT, m = w - b * p.MT;
@@ -180,9 +185,9 @@ moe_grouped_gemm_kernel(const __grid_constant__ GemmParams p) {
         const uint8_t* sfa = p.w_scale + ((int64_t)e * p.MT + m) * p.KB * sfa_step;   // KB stages of kSub k-blocks
         const uint8_t* sfb = p.asf + (int64_t)b * p.KB * geo.sfb_bytes;
         for (int kb = 0; kb < p.KB; ++kb) {
-          const long long tw0 = clock64();
+          const long long tw0 = PROF_NOW();
           if (!mbar_wait(smem_u32(&ctl->empty[stage]), phase ^ 1, abort_word, 0x100 + stage)) { ok = false; break; }
-          t_wait += clock64() - tw0;
+          PROF_ADD(t_wait, tw0);
           const uint32_t st = stage0 + (uint32_t)stage * geo.stage_bytes;
           const uint32_t full = smem_u32(&ctl->full[stage]);
           mbar_expect_tx(full, geo.tx_bytes);
@@ -196,7 +201,9 @@ moe_grouped_gemm_kernel(const __grid_constant__ GemmParams p) {
           if (++stage == S) { stage = 0; phase ^= 1; }
         }
       }
-      if (blockIdx.x == 0) p.status[4] = (int32_t)(t_wait >> 10);   // profiling: kilo-cycles waiting for a free stage
+#ifdef B200MOE_PROFILE
+      if (blockIdx.x == 0) p.status[4] = (int32_t)(t_wait >> 10);   // kilo-cycles waiting for a free stage
+#endif
       if (!ok || *abort_word) {
         // unwinding: let this CTA's copies still in flight land before shared memory is released
         const int64_t first = issued > S ? issued - S : 0;
@@ -226,8 +233,10 @@ moe_grouped_gemm_kernel(const __grid_constant__ GemmParams p) {
     uint32_t acc_phase = 0;
     uint32_t sf_buf = 0, sf_phase = 0;   // scale columns alternate between two TMEM buffers
     bool ok = true;
-    long long t_wait_acc = 0, t_wait_full = 0;
-    const long long t_begin = clock64();
+    PROF_DECL(t_wait_acc);
+    PROF_DECL(t_wait_full);
+    const long long t_begin = PROF_NOW();
+    (void)t_begin;
     // Per-term MMAs cover only the live rows of the block (rounded up to 16): the padding rows that end an
     // expert's last block cost neither tensor time nor operand reads.  The row ids of the NEXT item are
     // fetched while the current one is multiplied, so the count is ready without a stall.
@@ -248,16 +257,16 @@ moe_grouped_gemm_kernel(const __grid_constant__ GemmParams p) {
       uint32_t idesc_w[2];
 #pragma unroll
       for (int s = 0; s < 2; ++s) idesc_w[s] = (idesc[s] & ~(0x3Fu << 17)) | ((n_mma >> 3) << 17);
-      const long long ta0 = clock64();
+      const long long ta0 = PROF_NOW();
       if (!mbar_wait(smem_u32(&ctl->tmem_empty[acc]), acc_phase ^ 1, abort_word, 0x200 + acc)) break;
-      t_wait_acc += clock64() - ta0;
+      PROF_ADD(t_wait_acc, ta0);
       tc_fence_after_sync();
       const uint32_t d0 = tmem_base + acc * acc_cols + part * ncol;
       for (int kb = 0; kb < p.KB; ++kb) {
-        const long long tf0 = clock64();
+        const long long tf0 = PROF_NOW();
         if (!mbar_wait(smem_u32(&ctl->full[stage]), phase, abort_word, 0x300 + stage)) { ok = false; break; }
         if (!mbar_wait(smem_u32(&ctl->sf_full[sf_buf]), sf_phase, abort_word, 0x500 + sf_buf)) { ok = false; break; }
-        t_wait_full += clock64() - tf0;
+        PROF_ADD(t_wait_full, tf0);
         tc_fence_after_sync();
         __syncwarp();
         if (elect_one()) {       // one issuing lane; descriptors stay in uniform registers
@@ -302,11 +311,13 @@ moe_grouped_gemm_kernel(const __grid_constant__ GemmParams p) {
       __syncwarp();
       if (n_acc == 2) { acc ^= 1; if (acc == 0) acc_phase ^= 1; } else { acc_phase ^= 1; }
     }
-    if (blockIdx.x == 0 && lane == 0 && part == 0) {   // profiling: kilo-cycles of an MMA warp: total, waiting for data, for TMEM
+#ifdef B200MOE_PROFILE
+    if (blockIdx.x == 0 && lane == 0 && part == 0) {   // kilo-cycles of an MMA warp: total, waiting for data, for TMEM
       p.status[5] = (int32_t)((clock64() - t_begin) >> 10);
       p.status[6] = (int32_t)(t_wait_full >> 10);
       p.status[7] = (int32_t)(t_wait_acc >> 10);
     }
+#endif
   } else if (warp >= 10) {
     // ------------------------------------------------------------------ scale-loader warps
     // Four warps, one per TMEM lane quadrant.  A scale chunk in shared memory is 32 rows x 16
@@ -364,8 +375,9 @@ moe_grouped_gemm_kernel(const __grid_constant__ GemmParams p) {
     const bool fused = GATEUP && p.h_out == nullptr;
     int acc = 0;
     uint32_t acc_phase = 0;
-    long long t_wait_epi = 0;
-    const long long t_begin_epi = clock64();
+    PROF_DECL(t_wait_epi);
+    const long long t_begin_epi = PROF_NOW();
+    (void)t_begin_epi;
     for (int w = blockIdx.x; w < total_work; w += gridDim.x) {
       const int b = w / p.MT, m = w - b * p.MT;
       const int r0 = b * B;
@@ -378,13 +390,24 @@ moe_grouped_gemm_kernel(const __grid_constant__ GemmParams p) {
         nvalid += __popc(__ballot_sync(0xffffffffu, (int)(id >> 24) < p.topk && (int)(id & 0xFFFFFFu) < p.T));
       }
       // all eight warps take the same decision, so nobody is left alone at a later barrier
-      const long long te0 = clock64();
+      const long long te0 = PROF_NOW();
       const bool ok = mbar_wait(smem_u32(&ctl->tmem_full[acc]), acc_phase, abort_word, 0x400 + acc);
       if (!epi_all(ok)) break;
-      t_wait_epi += clock64() - te0;
+      PROF_ADD(t_wait_epi, te0);
       tc_fence_after_sync();
       const uint32_t t0 = tmem_base + ((uint32_t)(quad * 32) << 16) + acc * acc_cols;
       const bool j_ok = j < p.rows;
+      const bool j2_ok = !GATEUP && j + kTileM < p.rows;
+      // per-expert bias of this thread's two output features (gate / up of feature j, or features j and j + 128)
+      float bias0 = 0.f, bias1 = 0.f;
+      if (p.bias != nullptr) {
+        int e = p.sorted_e[b];
+        if (e < 0 || e >= p.E) e = 0;
+        const float* be = p.bias + (int64_t)e * (GATEUP ? 2 : 1) * p.rows;
+        if (j_ok) bias0 = be[j];
+        if (GATEUP ? j_ok : j2_ok) bias1 = be[j + (GATEUP ? p.rows : kTileM)];
+      }
+      const bool col_weights = GATEUP ? (p.weight_stage1 != 0) : (p.y != nullptr);
       uint32_t my_id = 0;
       for (int c0 = half * 16; c0 < nvalid; c0 += 32) {
         uint32_t g[16], u[16];
@@ -405,6 +428,17 @@ moe_grouped_gemm_kernel(const __grid_constant__ GemmParams p) {
             }
           }
         }
+        if (p.bias != nullptr) {
+          // the oracle's matmul returns bf16 and the bias is added to that (one more rounding follows below)
+#pragma unroll
+          for (int n = 0; n < 16; ++n) {
+            g[n] = __float_as_uint(bf16r(__uint_as_float(g[n])) + bias0);
+            u[n] = __float_as_uint(bf16r(__uint_as_float(u[n])) + bias1);
+          }
+        }
+        // routing weight of the chunk's token columns (lane n holds column c0 + n)
+        float my_w = 1.f;
+        if (col_weights) my_w = p.sorted_w[min(r0 + c0 + (lane & 15), r0 + B - 1)];
         if (GATEUP) {
           if (!fused) {
             my_id = p.sorted_ids[min(r0 + c0 + lane, r0 + B - 1)];
@@ -413,8 +447,9 @@ moe_grouped_gemm_kernel(const __grid_constant__ GemmParams p) {
               const uint32_t id = __shfl_sync(0xffffffffu, my_id, n);
               if (c0 + n < nvalid) {
                 const int tok = (int)(id & 0xFFFFFFu), kk = (int)(id >> 24);
-                const float v = gateup_act(__uint_as_float(g[n]), __uint_as_float(u[n]), p.activation,
-                                           p.swiglu_limit);
+                float v = gateup_act(__uint_as_float(g[n]), __uint_as_float(u[n]), p.activation,
+                                     p.swiglu_limit);
+                if (p.weight_stage1) v *= __shfl_sync(0xffffffffu, my_w, n);
                 if (j_ok) p.h_out[((int64_t)tok * p.topk + kk) * p.rows + j] = __float2bfloat16_rn(v);
               }
             }
@@ -426,6 +461,10 @@ moe_grouped_gemm_kernel(const __grid_constant__ GemmParams p) {
               if (c0 + n < nvalid) {
                 __nv_bfloat162 v = gateup_act2(__uint_as_float(g[n]), __uint_as_float(u[n]), __uint_as_float(g[n + 1]),
                                                __uint_as_float(u[n + 1]), p.activation, p.swiglu_limit);
+                if (p.weight_stage1) {
+                  const float2 f = __bfloat1622float2(v);
+                  v = __floats2bfloat162_rn(f.x * __shfl_sync(0xffffffffu, my_w, n), f.y * __shfl_sync(0xffffffffu, my_w, n + 1));
+                }
                 if (!j_ok) v = __floats2bfloat162_rn(0.f, 0.f);
                 if (gstg) {
                   *reinterpret_cast<unsigned short*>(gstg + (size_t)(c0 + n) * kStagePitch + row_local * 2) =
@@ -441,14 +480,41 @@ moe_grouped_gemm_kernel(const __grid_constant__ GemmParams p) {
               }
             }
           }
-        } else {
-          const bool j2_ok = j + kTileM < p.rows;
+        } else if (p.y == nullptr) {
 #pragma unroll
           for (int n = 0; n < 16; ++n) {
             if (c0 + n < nvalid) {
               __nv_bfloat16* row = p.out2 + ((int64_t)r0 + c0 + n) * p.rows + j;
               if (j_ok) row[0] = __float2bfloat16_rn(__uint_as_float(g[n]));
               if (j2_ok) row[kTileM] = __float2bfloat16_rn(__uint_as_float(u[n]));
+            }
+          }
+        } else {
+          // Fused combine: y[token, feature] += bf16(bf16(acc) * routing weight), accumulated in HBM/L2 with
+          // packed bf16x2 reductions (the reference's epilogue: src/contrib/moe.py:703-787).  Neighbouring
+          // lanes hold neighbouring features, so a pair of lanes swaps one value per two token columns: the
+          // even lane then owns features (j, j+1) of column n, the odd lane features (j-1, j) of column n+1.
+          my_id = p.sorted_ids[min(r0 + c0 + (lane & 15), r0 + B - 1)];
+          const bool odd = lane & 1;
+          const int jp = j & ~1;
+#pragma unroll
+          for (int n = 0; n < 16; n += 2) {
+            if (c0 + n < nvalid) {
+              const float w0 = __shfl_sync(0xffffffffu, my_w, n), w1 = __shfl_sync(0xffffffffu, my_w, n + 1);
+              const uint32_t id = __shfl_sync(0xffffffffu, my_id, n + (odd ? 1 : 0));
+              const float g0 = bf16r(bf16r(__uint_as_float(g[n])) * w0), g1 = bf16r(bf16r(__uint_as_float(g[n + 1])) * w1);
+              const float u0 = bf16r(bf16r(__uint_as_float(u[n])) * w0), u1 = bf16r(bf16r(__uint_as_float(u[n + 1])) * w1);
+              const float rg = __shfl_xor_sync(0xffffffffu, odd ? g0 : g1, 1);
+              const float ru = __shfl_xor_sync(0xffffffffu, odd ? u0 : u1, 1);
+              if (c0 + n + (odd ? 1 : 0) < nvalid) {
+                __nv_bfloat16* row = p.y + (int64_t)(id & 0xFFFFFFu) * p.rows + jp;
+                if (j_ok)
+                  atomicAdd(reinterpret_cast<__nv_bfloat162*>(row),
+                            odd ? __floats2bfloat162_rn(rg, g1) : __floats2bfloat162_rn(g0, rg));
+                if (j2_ok)
+                  atomicAdd(reinterpret_cast<__nv_bfloat162*>(row + kTileM),
+                            odd ? __floats2bfloat162_rn(ru, u1) : __floats2bfloat162_rn(u0, ru));
+              }
             }
           }
         }
@@ -500,10 +566,12 @@ moe_grouped_gemm_kernel(const __grid_constant__ GemmParams p) {
         }
       }
     }
-    if (blockIdx.x == 0 && tid_e == 0) {   // profiling: kilo-cycles of an epilogue warp: total, waiting for a tile
+#ifdef B200MOE_PROFILE
+    if (blockIdx.x == 0 && tid_e == 0) {   // kilo-cycles of an epilogue warp: total, waiting for a tile
       p.status[8] = (int32_t)((clock64() - t_begin_epi) >> 10);
       p.status[9] = (int32_t)(t_wait_epi >> 10);
     }
+#endif
   }
 
   __syncwarp();
@@ -567,7 +635,7 @@ int encode_map_sw(CUtensorMap* map, CUtensorMapDataType type, int rank, const vo
 int launch_grouped_gemm(const GemmArgs& a, cudaStream_t st) {
   B200_CHECK_ARG(a.N >= 16 && a.N <= 128 && a.N % 16 == 0, "grouped gemm: token tile %d is not a multiple of 16 in [16,128]",
                  a.N);
-  B200_CHECK_ARG(a.NT >= 2 && a.NT <= kMaxTerms, "grouped gemm: %d activation terms (2..4 supported)", a.NT);
+  B200_CHECK_ARG(a.NT >= 1 && a.NT <= kMaxTerms, "grouped gemm: %d activation terms (1..4 supported)", a.NT);
   B200_CHECK_ARG(a.Kd % 32 == 0 && a.rows > 0 && a.E > 0, "grouped gemm: bad shape");
   B200_CHECK_ARG(a.max_rows % a.N == 0, "grouped gemm: max_rows %% B != 0");
   B200_CHECK_ARG(((uintptr_t)a.w_data & 15) == 0 && ((uintptr_t)a.a_q & 15) == 0,
@@ -586,6 +654,10 @@ int launch_grouped_gemm(const GemmArgs& a, cudaStream_t st) {
   p.out_kp = a.out_kp; p.out_kb = a.out_kp / 128; p.out_ts = act_term_stride(a.N, a.NT, 2);
   p.oq_term_stride = a.max_rows * (int64_t)(a.out_kp / 2);
   p.out2 = (__nv_bfloat16*)a.out2;
+  p.sorted_w = a.sorted_w; p.bias = a.bias; p.y = a.gateup ? nullptr : (__nv_bfloat16*)a.y;
+  p.weight_stage1 = (a.gateup && a.weight_stage1) ? 1 : 0;
+  B200_CHECK_ARG((p.y == nullptr && p.weight_stage1 == 0) || a.sorted_w != nullptr, "grouped gemm: routing weights missing");
+  B200_CHECK_ARG(p.y == nullptr || (a.rows % 2 == 0 && ((uintptr_t)p.y & 3) == 0), "grouped gemm: fused combine needs an even row length");
   if (a.gateup && a.h_out == nullptr)
     B200_CHECK_ARG(a.out_kp == (int)round_up64(a.rows, kTileK) && a.oq && a.osf,
                    "gate-up: fused output buffers missing");
@@ -714,71 +786,21 @@ __global__ void __launch_bounds__(128, 1) probe_utccp_kernel(const uint32_t* in,
   if (warp == 0) tmem_dealloc(tbase, 32);
 }
 
-template <int MODE>
-__device__ __forceinline__ void probe_issue(const int32_t* cfg, uint32_t* out, uint32_t tbase, uint32_t a, uint32_t bar,
-                                            uint32_t bar2, volatile uint32_t* abort_word) {
-  const int N = cfg[1], count = cfg[2], nacc = cfg[3], commit_every = cfg[4];
-  const bool one = (MODE != 2) || (threadIdx.x & 31) == 0;    // the lane that does the bookkeeping
-  const uint32_t b = a + 16384, sf = b + 32768;
-  if (one) {
-    utccp_sf(tbase + 448, desc_lo_sf(sf));
-    utccp_sf(tbase + 456, desc_lo_sf(sf + 512));
-    utccp_sf(tbase + 460, desc_lo_sf(sf + 512));
-  }
-  uint32_t idesc[2];
-  for (int s = 0; s < 2; ++s) idesc[s] = make_idesc_block_scaled(kFmtE2M1_mxf4, kFmtE2M1_mxf4, 128, N, 2 * s, 2 * s);
-  const uint32_t a_lo = desc_lo_sw(a), b_lo = desc_lo_sw(b);
-  const uint32_t d1 = tbase + (nacc > 1 ? N : 0);
-  const int ncp = cfg[0];      // scale copies (tcgen05.cp) issued before every group of four MMAs
-  const uint32_t sf_lo = desc_lo_sf(sf);
-  int since_commit = 0;
-  const long long t0 = clock64();
-  for (int i = 0; i < count; i += 4) {
-    if (one)
-      for (int c = 0; c < ncp; ++c) utccp_sf(tbase + 448 + 4 * (c & 7) + ((i >> 2) & 1) * 32, sf_lo + ((c & 1) << 5));
-    if (MODE == 2) {
-      umma_mxf4_warp(tbase, a_lo, b_lo, idesc[0], tbase + 448, tbase + 456, 1);
-      umma_mxf4_warp(d1, a_lo, b_lo, idesc[0], tbase + 448, tbase + 456, 1);
-      umma_mxf4_warp(tbase, a_lo + 2, b_lo + 2, idesc[1], tbase + 448, tbase + 456, 1);
-      umma_mxf4_warp(d1, a_lo + 2, b_lo + 2, idesc[1], tbase + 448, tbase + 456, 1);
-    } else {
-      umma_mxf4(tbase, a_lo, b_lo, idesc[0], tbase + 448, tbase + 456, 1);
-      umma_mxf4(d1, a_lo, b_lo, idesc[0], tbase + 448, tbase + 456, 1);
-      umma_mxf4(tbase, a_lo + 2, b_lo + 2, idesc[1], tbase + 448, tbase + 456, 1);
-      umma_mxf4(d1, a_lo + 2, b_lo + 2, idesc[1], tbase + 448, tbase + 456, 1);
-    }
-    if (commit_every > 0 && ++since_commit == commit_every) {
-      since_commit = 0;
-      if (one) tc_commit(bar2);
-    }
-  }
-  const long long t1 = clock64();
-  if (one) tc_commit(bar);
-  mbar_wait(bar, 0, abort_word, 3);
-  const long long t2 = clock64();
-  if (one) {
-    uint32_t* o = out + 3 * blockIdx.x;
-    o[0] = (uint32_t)(t1 - t0);
-    o[1] = (uint32_t)(t2 - t0);
-    o[2] = *abort_word;
-  }
-}
-
-// Issue-rate probe: `count` MMAs of shape 128 x N x 64 alternating between `nacc` accumulators,
-// one commit, one bounded wait; reports clock cycles.  The results are never read back.
+// Dense MMA rate probe: `count` block-scaled MMAs of shape 128 x N x (64 for packed FP4, 32 for e4m3) alternating
+// between two accumulators, issued by one elected lane from resident pseudo-random tiles with unit scales, one
+// commit, one bounded wait; reports clock cycles.  The results are never read back.  Launched on every SM at
+// once and timed by the caller it gives the chip's dense tensor rate for the kind.
 __global__ void __launch_bounds__(128, 1) probe_mma_rate_kernel(const int32_t* cfg, uint32_t* out) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-  __shared__ uint64_t bar, bar2;
+  __shared__ uint64_t bar;
   __shared__ uint32_t tmem_slot, abort_word;
   const int warp = threadIdx.x >> 5;
-  // pseudo-random FP4 operands (realistic switching activity) and unit scales
   for (int i = threadIdx.x; i < (16384 + 32768 + 1024) / 4; i += blockDim.x)
-    reinterpret_cast<uint32_t*>(smem)[i] = (i < (16384 + 32768) / 4) ? (uint32_t)(i + 1) * 2654435761u : 0x7F7F7F7Fu;
+    reinterpret_cast<uint32_t*>(smem)[i] = (i < (16384 + 32768) / 4) ? ((uint32_t)(i + 1) * 2654435761u) & 0x77777777u : 0x7F7F7F7Fu;
   if (threadIdx.x == 0) {
     abort_word = 0;
     mbar_init(smem_u32(&bar), 1);
-    mbar_init(smem_u32(&bar2), 1);
     fence_mbar_init();
   }
   fence_proxy_async_smem();
@@ -790,16 +812,39 @@ __global__ void __launch_bounds__(128, 1) probe_mma_rate_kernel(const int32_t* c
   __syncthreads();
   tc_fence_after_sync();
   const uint32_t tbase = tmem_slot;
-  const uint32_t sbase = smem_u32(smem);
-  // three ways to confine the issue to one thread: a lane test, an elected lane around the loop, or the whole
-  // warp running the loop with the election inside each MMA
-  const int mode = cfg[5];
-  if (mode == 0) {
-    if (threadIdx.x == 0) probe_issue<0>(cfg, out, tbase, sbase, smem_u32(&bar), smem_u32(&bar2), &abort_word);
-  } else if (mode == 1) {
-    if (warp == 0 && elect_one()) probe_issue<1>(cfg, out, tbase, sbase, smem_u32(&bar), smem_u32(&bar2), &abort_word);
-  } else {
-    if (warp == 0) probe_issue<2>(cfg, out, tbase, sbase, smem_u32(&bar), smem_u32(&bar2), &abort_word);
+  const uint32_t a = smem_u32(smem), b = a + 16384, sf = b + 32768;
+  const int kind = cfg[0], N = cfg[1], count = cfg[2];
+  if (warp == 0 && elect_one()) {
+    utccp_sf(tbase + 448, desc_lo_sf(sf));
+    utccp_sf(tbase + 456, desc_lo_sf(sf + 512));
+    utccp_sf(tbase + 460, desc_lo_sf(sf + 512));
+    const uint32_t fmt = kind == 0 ? kFmtE2M1_mxf4 : kFmtE4M3;
+    uint32_t idesc[2];
+    for (int k = 0; k < 2; ++k) idesc[k] = make_idesc_block_scaled(fmt, fmt, 128, N, kind == 0 ? 2 * k : k, kind == 0 ? 2 * k : k);
+    const uint32_t a_lo = desc_lo_sw(a), b_lo = desc_lo_sw(b);
+    const uint32_t d1 = tbase + N;
+    const long long t0 = clock64();
+    for (int i = 0; i < count; i += 4) {
+      if (kind == 0) {
+        umma_mxf4(tbase, a_lo, b_lo, idesc[0], tbase + 448, tbase + 456, 1);
+        umma_mxf4(d1, a_lo, b_lo, idesc[0], tbase + 448, tbase + 456, 1);
+        umma_mxf4(tbase, a_lo + 2, b_lo + 2, idesc[1], tbase + 448, tbase + 456, 1);
+        umma_mxf4(d1, a_lo + 2, b_lo + 2, idesc[1], tbase + 448, tbase + 456, 1);
+      } else {
+        umma_mxf8(tbase, a_lo, b_lo, idesc[0], tbase + 448, tbase + 456, 1);
+        umma_mxf8(d1, a_lo, b_lo, idesc[0], tbase + 448, tbase + 456, 1);
+        umma_mxf8(tbase, a_lo + 2, b_lo + 2, idesc[1], tbase + 448, tbase + 456, 1);
+        umma_mxf8(d1, a_lo + 2, b_lo + 2, idesc[1], tbase + 448, tbase + 456, 1);
+      }
+    }
+    const long long t1 = clock64();
+    tc_commit(smem_u32(&bar));
+    mbar_wait(smem_u32(&bar), 0, &abort_word, 3);
+    const long long t2 = clock64();
+    uint32_t* o = out + 3 * blockIdx.x;
+    o[0] = (uint32_t)(t1 - t0);
+    o[1] = (uint32_t)(t2 - t0);
+    o[2] = abort_word;
   }
   tc_fence_before_sync();
   __syncthreads();
@@ -824,15 +869,10 @@ int run_debug_probe(int which, const void* in, void* out, cudaStream_t st) {
     B200_CHECK_CUDA(cudaGetLastError());
     return 0;
   }
-  if (which == 3 || which == 4) {
-    static bool attr = false;
-    if (!attr) {
-      B200_CHECK_CUDA(cudaFuncSetAttribute(probe_mma_rate_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                           65536));
-      attr = true;
-    }
-    const int grid = (which == 4) ? device_sm_count() : 1;
-    probe_mma_rate_kernel<<<grid, 128, 16384 + 32768 + 1024 + 1024, st>>>((const int32_t*)in, (uint32_t*)out);
+  if (which == 4) {
+    // the attribute belongs to the (function, device) pair and setting it is cheap: do it on every launch
+    B200_CHECK_CUDA(cudaFuncSetAttribute(probe_mma_rate_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 65536));
+    probe_mma_rate_kernel<<<device_sm_count(), 128, 16384 + 32768 + 1024 + 1024, st>>>((const int32_t*)in, (uint32_t*)out);
     B200_CHECK_CUDA(cudaGetLastError());
     return 0;
   }

@@ -19,7 +19,9 @@ For small batches (decode) the exchange degenerates gracefully into its fixed-sh
 rank receives every token (all-gather of rows and routing), runs its local experts on all of them
 and the partial outputs are summed back with a reduce-scatter.  No counts, no host read, constant
 shapes from step to step -- at T <= `small_batch` tokens per rank the bytes are irrelevant and the
-two latencies saved are not.
+two latencies saved are not.  The fixed-shape form needs the same T on every rank, and every rank
+must pick the same form: both are therefore fixed when the layer is built (`tokens_per_rank`,
+`exchange`), never read off a rank's own batch.
 
 All collectives are NCCL (`torch.distributed`); device kernels never touch peer memory.  The
 integer plumbing (`plan_positions`, and the compact `plan_dispatch` / `scatter_back` pair the tests
@@ -79,6 +81,24 @@ def plan_positions(topk_ids: torch.Tensor, experts_per_rank: int, world: int):
     return pos.to(torch.int32).contiguous(), counts, rows_padded
 
 
+def plan_positions_device(topk_ids: torch.Tensor, experts_per_rank: int, world: int):
+    """`plan_positions` as ONE kernel launch behind the C ABI (CUDA tensors): same `pos`, the same `counts`
+    (int32 here) and the same defined prefix of `rows` (int32, sized T*world; the tail is unwritten)."""
+    import ctypes
+    from . import _lib
+    T, K = topk_ids.shape
+    dev = topk_ids.device
+    ids = topk_ids if (topk_ids.dtype == torch.int32 and topk_ids.is_contiguous()) else topk_ids.to(torch.int32).contiguous()
+    pos = torch.empty(T, world, dtype=torch.int32, device=dev)
+    counts = torch.empty(world, dtype=torch.int32, device=dev)
+    rows = torch.empty(max(T * world, 1), dtype=torch.int32, device=dev)
+    _lib.check(_lib.lib().b200moe_ep_plan(ctypes.c_void_p(ids.data_ptr()), T, K, experts_per_rank, world,
+                                          ctypes.c_void_p(pos.data_ptr()), ctypes.c_void_p(counts.data_ptr()),
+                                          ctypes.c_void_p(rows.data_ptr()),
+                                          ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)), "ep_plan")
+    return pos, counts, rows
+
+
 def gather_sum(rows: torch.Tensor, pos: torch.Tensor) -> torch.Tensor:
     """y[t] = sum_s rows[pos[t, s]] over pos >= 0, fp32 accumulate in slot order, one rounding.
     CUDA tensors go through the library kernel; CPU tensors (the gloo tests of the plumbing) through
@@ -106,23 +126,43 @@ def gather_sum(rows: torch.Tensor, pos: torch.Tensor) -> torch.Tensor:
 class ExpertParallelMoE:
     """One MoE layer sharded by experts.  ``local_fn(x, topk_weight, local_ids) -> y`` computes
     the contribution of this rank's experts for the given rows; by default it is the CUDA
-    `fused_moe` on this rank's prepared weights."""
+    `fused_moe` on this rank's prepared weights.
+
+    ``exchange``: "dispatch" (all-to-all-v, any per-rank batch sizes), "gathered" (all-gather +
+    reduce-scatter, needs ``tokens_per_rank`` tokens on EVERY rank) or "auto": gathered when
+    ``tokens_per_rank`` is given and at most ``small_batch``, dispatch otherwise.  The choice is made here,
+    from values every rank passes identically, so that no rank can issue a different collective."""
 
     def __init__(self, w1, w1_scale, w2, w2_scale, num_experts: int, rank: int, world: int,
                  group: Optional[dist.ProcessGroup] = None, local_fn: Optional[Callable] = None,
-                 small_batch: int = 512, quant_type=None, dispatch_chunks: Optional[int] = None):
+                 small_batch: int = 512, quant_type=None, dispatch_chunks: Optional[int] = None,
+                 exchange: str = "auto", tokens_per_rank: Optional[int] = None, **moe_kwargs):
         if num_experts % world:
             raise ValueError("num_experts must be divisible by the number of ranks")
+        if exchange not in ("auto", "gathered", "dispatch"):
+            raise ValueError(f"exchange={exchange!r}")
+        if exchange == "auto":
+            exchange = "gathered" if (tokens_per_rank is not None and tokens_per_rank <= small_batch) else "dispatch"
+        if exchange == "gathered" and tokens_per_rank is None:
+            raise ValueError("the gathered exchange needs tokens_per_rank: every rank must bring the same token count")
+        self.exchange, self.tokens_per_rank = exchange, tokens_per_rank
         self.E, self.rank, self.world, self.group = num_experts, rank, world, group
         self.E_local = num_experts // world
         self.small_batch = small_batch
         self.dispatch_chunks = dispatch_chunks
         if local_fn is None:
-            from .fused_moe import QuantType, fused_moe
+            from . import _lib
+            from .fused_moe import QuantType, fused_moe, pick_block
             qt = QuantType.per_1x32 if quant_type is None else quant_type
+            fmt = _lib.W_FP8_128 if int(qt) == QuantType.per_128x128 else _lib.W_MXFP4
+            E_all = num_experts
 
             def local_fn(x, tw, ids):
-                return fused_moe(x, w1, w2, tw, ids, quant_type=qt, w1_scale=w1_scale, w2_scale=w2_scale)
+                # rows per LOCAL expert = rows * K / E over the whole routing space (most of a row's K ids
+                # belong to other ranks), which is what sizes the token tile
+                B = pick_block(x.shape[0], ids.shape[1], E_all, fmt)
+                return fused_moe(x, w1, w2, tw, ids, quant_type=qt, w1_scale=w1_scale, w2_scale=w2_scale,
+                                 block_size_M=B, **moe_kwargs)
         self.local_fn = local_fn
         self.last_local = None      # (rows, weights, local ids) of the latest local call, for measurement
         self.busy_events = None     # set to a list to collect (start, end) CUDA events around the local call
@@ -149,15 +189,20 @@ class ExpertParallelMoE:
         dist.all_to_all_single(out, inp, out_splits, in_splits, group=self.group)
 
     def forward(self, x: torch.Tensor, topk_weight: torch.Tensor, topk_ids: torch.Tensor) -> torch.Tensor:
-        if x.shape[0] <= self.small_batch:
+        if self.exchange == "gathered":
             return self.forward_gathered(x, topk_weight, topk_ids)
         return self.forward_dispatch(x, topk_weight, topk_ids)
 
     def forward_gathered(self, x, topk_weight, topk_ids):
         """Fixed-shape exchange: all-gather rows + routing, local experts over all W*T rows (rows
         routed elsewhere are dropped by the sorter), reduce-scatter of the partial outputs.
-        Every rank must call with the same T."""
+        Every rank must call with the same T: the layer's ``tokens_per_rank``, checked here on the host so
+        that a stray batch size raises instead of issuing a mismatched collective."""
         T, H = x.shape
+        if self.tokens_per_rank is not None and T != self.tokens_per_rank:
+            raise ValueError(f"gathered exchange: this rank brought {T} tokens, the layer was built for "
+                             f"{self.tokens_per_rank} on every rank (pad the batch, or build the layer with "
+                             f"exchange='dispatch')")
         K = topk_ids.shape[1]
         W = self.world
         x_all = torch.empty(W * T, H, dtype=x.dtype, device=x.device)
@@ -198,8 +243,10 @@ class ExpertParallelMoE:
         self._mark("start", x)
         ids32 = topk_ids.to(torch.int32)
         meta = torch.cat([ids32, topk_weight.to(torch.float32).view(torch.int32)], dim=1)    # [T, 2K] int32
-        plans = [plan_positions(ids32[bounds[c]:bounds[c + 1]], self.E_local, W) for c in range(nch)]
-        send_counts = torch.stack([p[1] for p in plans], dim=1).contiguous()                 # [W, nch]
+        plan = plan_positions_device if x.is_cuda else plan_positions
+        plans = [plan(ids32[bounds[c]:bounds[c + 1]], self.E_local, W) for c in range(nch)]
+        send_counts = (plans[0][1].reshape(W, 1) if nch == 1 else
+                       torch.stack([p[1] for p in plans], dim=1)).contiguous()              # [W, nch]
         recv_counts = torch.empty_like(send_counts)
         dist.all_to_all_single(recv_counts, send_counts, group=self.group)
         # the only host read of the call: all_to_all_single takes Python split sizes
@@ -211,7 +258,9 @@ class ExpertParallelMoE:
         for c in range(nch):
             s_splits = [counts[0][d][c] for d in range(W)]
             r_splits = [counts[1][d][c] for d in range(W)]
-            rows = plans[c][2][:sum(s_splits)] + bounds[c]
+            rows = plans[c][2][:sum(s_splits)]
+            if bounds[c]:
+                rows = rows + bounds[c]
             n_recv = sum(r_splits)
             x_recv = torch.empty(n_recv, H, dtype=x.dtype, device=x.device)
             m_recv = torch.empty(n_recv, 2 * K, dtype=torch.int32, device=x.device)

@@ -15,7 +15,6 @@ from __future__ import annotations
 import ctypes
 import math
 import enum
-import weakref
 
 import torch
 
@@ -104,7 +103,7 @@ class PreparedWeights:
             raise ValueError("E8M0 scale 0xFF (NaN) is not a valid weight scale")
         L = _lib.lib()
         shape = _lib.Shape(T=0, K=1, E=E, E_route=E, H=self.H, I=self.I, B=32, weight_format=_lib.W_MXFP4,
-                           activation=0, swiglu_limit=0.0, act_terms=0)
+                           activation=0, swiglu_limit=0.0, act_terms=0, combine_mode=0, act_quant=0, doweight_stage1=0)
         out = []
         for which, ws in ((1, s1), (2, s2)):
             sb = ctypes.c_int64()
@@ -139,29 +138,45 @@ class PreparedWeightsFP8:
         self.device = w1.device
 
 
-_prepared_cache: dict = {}
+_prepared_cache: dict = {}          # insertion-ordered: least recently used first
 _workspace_cache: dict = {}
+_PREPARED_CACHE_ENTRIES = 8
 
 
 def prepare_weights(w1, w1_scale, w2, w2_scale, weight_format=_lib.W_MXFP4):
-    """Cached by the identity of the four tensors (weights are static across calls)."""
-    key = (w1.data_ptr(), w1_scale.data_ptr(), w2.data_ptr(), w2_scale.data_ptr(), tuple(w1.shape), weight_format)
-    hit = _prepared_cache.get(key)
-    if hit is not None and hit[0]() is w1:
-        return hit[1]
-    cls = PreparedWeightsFP8 if weight_format == _lib.W_FP8_128 else PreparedWeights
-    pw = cls(w1, w1_scale, w2, w2_scale)
-    _prepared_cache[key] = (weakref.ref(w1), pw)
-    return pw
+    """Prepared form of one layer's weights, cached by the identity of the four tensors and the in-place
+    version counters of the scale tensors (scales updated in place are prepared again).  The cache keeps the
+    `_PREPARED_CACHE_ENTRIES` most recently used layers alive -- an entry references the caller's weight tensors
+    -- and `release_prepared()` drops them all."""
+    key = (w1.data_ptr(), w1_scale.data_ptr(), w2.data_ptr(), w2_scale.data_ptr(), tuple(w1.shape), weight_format,
+           w1_scale._version, w2_scale._version)
+    hit = _prepared_cache.pop(key, None)
+    if hit is None:
+        while len(_prepared_cache) >= _PREPARED_CACHE_ENTRIES:
+            _prepared_cache.pop(next(iter(_prepared_cache)))
+        cls = PreparedWeightsFP8 if weight_format == _lib.W_FP8_128 else PreparedWeights
+        pw = cls(w1, w1_scale, w2, w2_scale)
+        hit = (pw, (w1, w1_scale, w2, w2_scale))      # the sources stay alive, so their addresses identify them
+    _prepared_cache[key] = hit
+    return hit[0]
+
+
+def release_prepared():
+    """Forget every cached prepared weight set and workspace (frees the HBM they pin)."""
+    _prepared_cache.clear()
+    _workspace_cache.clear()
 
 
 class MoEPlan:
     """Shape, workspace layout and workspace tensor of one (T, K, E, H, I, B) problem."""
 
     def __init__(self, T, K, E, E_route, H, I, B, activation, swiglu_limit, device, act_terms=0,
-                 weight_format=_lib.W_MXFP4):
+                 weight_format=_lib.W_MXFP4, combine_mode=_lib.COMBINE_GATHER, act_quant=_lib.ACTQ_TERMS,
+                 doweight_stage1=False):
         self.shape = _lib.Shape(T=T, K=K, E=E, E_route=E_route, H=H, I=I, B=B, weight_format=weight_format,
-                                activation=activation, swiglu_limit=float(swiglu_limit), act_terms=act_terms)
+                                activation=activation, swiglu_limit=float(swiglu_limit), act_terms=act_terms,
+                                combine_mode=combine_mode, act_quant=act_quant,
+                                doweight_stage1=1 if doweight_stage1 else 0)
         self.capacity = T
         self.terms = act_terms or 3
         self.fp8 = weight_format == _lib.W_FP8_128
@@ -237,12 +252,15 @@ class MoEPlan:
             ctypes.c_void_p(base + ws.off_hq), ctypes.c_void_p(base + ws.off_hsf), _stream()),
             "quant_rows")
 
-    def gateup(self, pw, h_out=None):
-        _lib.check(_lib.lib().b200moe_gateup(*self._args(), _ptr(pw.w1_data), _ptr(pw.w1_scale), _ptr(h_out),
-                                             _stream()), "gateup")
+    def gateup(self, pw, h_out=None, bias1=None):
+        _lib.check(_lib.lib().b200moe_gateup(*self._args(), _ptr(pw.w1_data), _ptr(pw.w1_scale), _ptr(bias1),
+                                             _ptr(h_out), _stream()), "gateup")
 
-    def down(self, pw):
-        _lib.check(_lib.lib().b200moe_down(*self._args(), _ptr(pw.w2_data), _ptr(pw.w2_scale), _stream()), "down")
+    def down(self, pw, bias2=None, y=None):
+        """``y`` (zeroed bf16 [T, H]) is the target of the fused combine when the plan was built with
+        combine_mode FUSED; otherwise the rows land in the workspace for `combine`."""
+        _lib.check(_lib.lib().b200moe_down(*self._args(), _ptr(pw.w2_data), _ptr(pw.w2_scale), _ptr(bias2), _ptr(y),
+                                           _stream()), "down")
 
     def combine(self, topk_weight, y):
         _lib.check(_lib.lib().b200moe_combine(*self._args(), _ptr(topk_weight), _ptr(y), _stream()), "combine")
@@ -255,38 +273,68 @@ class MoEPlan:
                                     f"bad expert id flag {st[2]}")
 
 
+_WORKSPACE_CACHE_ENTRIES = 16
+
+
+def _capacity(T: int) -> int:
+    """Token capacity a cached workspace is laid out for: the next power of two up to 512, multiples of 512
+    beyond, so that a decode loop whose batch size wanders reuses a handful of allocations."""
+    if T <= 512:
+        return 1 << max(0, (T - 1).bit_length())
+    return -(-T // 512) * 512
+
+
 def get_plan(T, K, E, E_route, H, I, B, activation, swiglu_limit, device, act_terms=0,
-             weight_format=_lib.W_MXFP4) -> MoEPlan:
-    key = (T, K, E, E_route, H, I, B, activation, float(swiglu_limit), str(device), act_terms, weight_format)
-    plan = _workspace_cache.get(key)
+             weight_format=_lib.W_MXFP4, combine_mode=_lib.COMBINE_GATHER, act_quant=_lib.ACTQ_TERMS,
+             doweight_stage1=False) -> MoEPlan:
+    """Cached plan (shape + workspace).  One workspace per (shape, CUDA stream): calls enqueued on different
+    streams never share scratch memory.  The least recently used entry is dropped when the cache is full."""
+    stream_id = torch.cuda.current_stream(device).cuda_stream if torch.cuda.is_available() else 0
+    key = (T, K, E, E_route, H, I, B, activation, float(swiglu_limit), str(device), act_terms, weight_format,
+           combine_mode, act_quant, bool(doweight_stage1), stream_id)
+    plan = _workspace_cache.pop(key, None)
     if plan is None:
-        if len(_workspace_cache) > 16:
-            _workspace_cache.clear()
-        plan = MoEPlan(T, K, E, E_route, H, I, B, activation, swiglu_limit, device, act_terms, weight_format)
-        _workspace_cache[key] = plan
+        while len(_workspace_cache) >= _WORKSPACE_CACHE_ENTRIES:
+            _workspace_cache.pop(next(iter(_workspace_cache)))
+        plan = MoEPlan(T, K, E, E_route, H, I, B, activation, swiglu_limit, device, act_terms, weight_format,
+                       combine_mode, act_quant, doweight_stage1)
+    _workspace_cache[key] = plan          # (re)insert at the recent end
     return plan
 
 
 def moe_forward(plan: MoEPlan, pw: PreparedWeights, hidden_states, topk_weight, topk_ids, expert_mask=None,
-                out=None, num_local_tokens=None):
-    """One layer call through the C ABI (sort -> quantise -> gate-up -> down -> combine).
-    ``num_local_tokens``: optional int32 device tensor; tokens at and beyond its value are padding
-    (their output rows are zero)."""
+                out=None, num_local_tokens=None, bias1=None, bias2=None):
+    """One layer call through the C ABI (sort -> quantise -> gate-up -> down [-> combine]; decode-sized batches
+    fold the first two into one launch).  ``num_local_tokens``: optional int32 device tensor; tokens at and
+    beyond its value are padding (their output rows are zero)."""
     T, H = hidden_states.shape
     if out is None:
         out = torch.empty((T, H), dtype=torch.bfloat16, device=hidden_states.device)
     if T == 0:
         return out
-    _lib.check(_lib.lib().b200moe_forward_dyn(
-        ctypes.byref(plan.shape), ctypes.byref(plan.ws), ctypes.c_void_p(plan.base), _ptr(hidden_states),
-        _ptr(topk_ids), _ptr(topk_weight), _ptr(expert_mask), _ptr(num_local_tokens), _ptr(pw.w1_data),
-        _ptr(pw.w1_scale), _ptr(pw.w2_data), _ptr(pw.w2_scale), _ptr(out), _stream()), "forward")
+    io = _lib.Io(x_bf16=hidden_states.data_ptr(), topk_ids=topk_ids.data_ptr(), topk_weight=topk_weight.data_ptr(),
+                 expert_mask=None if expert_mask is None else expert_mask.data_ptr(),
+                 num_local_tokens=None if num_local_tokens is None else num_local_tokens.data_ptr(),
+                 w1_q=pw.w1_data.data_ptr(), w1_scale_prepared=pw.w1_scale.data_ptr(), w2_q=pw.w2_data.data_ptr(),
+                 w2_scale_prepared=pw.w2_scale.data_ptr(), bias1=None if bias1 is None else bias1.data_ptr(),
+                 bias2=None if bias2 is None else bias2.data_ptr(), y_bf16=out.data_ptr())
+    _lib.check(_lib.lib().b200moe_forward_ex(ctypes.byref(plan.shape), ctypes.byref(plan.ws),
+                                             ctypes.c_void_p(plan.base), ctypes.byref(io), _stream()), "forward")
     return out
+
+
+def launches_per_call(T: int, K: int, E_route: int, combine_mode: int) -> int:
+    """Kernel launches of one whole-layer call: sort + quantise (one launch up to 256 (token, expert) pairs, two
+    below 8192 pairs, four from there on: the sort is then count / scan / scatter), gate-up, down, and the
+    gather-sum unless the combine is fused into the down epilogue."""
+    pairs = T * K
+    front = 1 if (pairs <= 256 and E_route <= 1024) else (4 if pairs >= 8192 else 2)
+    return front + 2 + (0 if combine_mode == _lib.COMBINE_FUSED else 1)
 
 
 def capture_forward(plan: MoEPlan, pw, hidden_states, topk_weight, topk_ids, expert_mask=None, out=None,
                     num_local_tokens=None):
-    """Capture one layer call (five kernel launches, no host synchronisation inside) into a CUDA
+    """Capture one layer call (three to five kernel launches, no host synchronisation inside) into a CUDA
     graph.  Returns (graph, out): ``graph.replay()`` re-runs the layer on the same tensors -- the
     caller refreshes their contents in place between replays, including the int32 device tensor
     ``num_local_tokens`` when the batch is padded to a fixed T (the reference's use of that argument,
@@ -307,11 +355,20 @@ def fused_moe(hidden_states, w1, w2, topk_weight, topk_ids, expert_mask=None,
               w1_scale=None, w2_scale=None, a1_scale=None, a2_scale=None, block_size_M=None,
               num_local_tokens=None, moe_sorting_dispatch_policy=0, dtype=None, hidden_pad=0,
               intermediate_pad=0, bias1=None, bias2=None, splitk=0, method="auto",
-              swiglu_limit=7.0, act_terms=0):
+              swiglu_limit=7.0, act_terms=0, combine="auto", act_quant="terms"):
     """bf16 hidden states [T,H], router top-k ids [T,K] int32 and weights [T,K] fp32, packed
-    expert weights with their scales -> bf16 [T,H].  ``act_terms`` (extension, 0 = default 3):
-    number of packed-FP4 terms that carry one activation row inside the GEMMs (2..4).  Unsupported combinations raise, as the
-    reference asserts (src/contrib/fused_moe.py:252-266)."""
+    expert weights with their scales -> bf16 [T,H].  Unsupported combinations raise, as the
+    reference asserts (src/contrib/fused_moe.py:252-266).
+
+    Arguments beyond the reference's signature:
+      ``act_terms`` (MXFP4; 0 = default 3): packed-FP4 terms that carry one activation row inside the GEMMs.
+        1 = plain per-1x32 MXFP4 activations, the arithmetic of the reference's a4w4 kernels
+        (tests/contrib/moe/test_moe.py:665-679); 3 keeps the layer within the bf16-activation tolerance.
+      ``combine``: "gather" (deterministic: sorted rows + a gather-sum launch in expert order), "fused" (the down
+        epilogue multiplies by the routing weight and adds into the output with packed-bf16 reductions, the
+        reference kernels' own epilogue, src/contrib/moe.py:703-787) or "auto" (= "gather", the reproducible one).
+      ``bias1`` [E, 2I] / ``bias2`` [E, H]: per-expert biases of the two projections (gpt-oss style).
+    """
     if not hidden_states.is_cuda:
         raise RuntimeError("fused_moe runs on a CUDA device only (sm_100a); there is no CPU path")
     if hidden_states.dtype != torch.bfloat16:
@@ -321,14 +378,18 @@ def fused_moe(hidden_states, w1, w2, topk_weight, topk_ids, expert_mask=None,
     fmt = _lib.W_MXFP4 if int(quant_type) == QuantType.per_1x32 else _lib.W_FP8_128
     if int(activation) not in (ActivationType.Silu, ActivationType.Swiglu):
         raise NotImplementedError(f"activation={activation!r}: Silu and Swiglu are implemented")
-    if doweight_stage1 or bias1 is not None or bias2 is not None or a1_scale is not None or a2_scale is not None:
-        raise NotImplementedError("doweight_stage1 / bias / pre-quantised activations are not implemented")
+    if a1_scale is not None or a2_scale is not None:
+        raise NotImplementedError("pre-quantised activations (a1_scale / a2_scale) are not implemented: pass bf16")
     if hidden_pad or intermediate_pad:
         raise NotImplementedError("padding arguments are not implemented")
     if w1_scale is None or w2_scale is None:
         raise ValueError("quantised weights need w1_scale and w2_scale")
     if dtype not in (None, torch.bfloat16):
         raise NotImplementedError("output dtype must be bfloat16")
+    if combine not in ("auto", "gather", "fused"):
+        raise ValueError(f"combine={combine!r}: 'auto', 'gather' or 'fused'")
+    if act_quant not in ("terms", "1x128"):
+        raise ValueError(f"act_quant={act_quant!r}: 'terms' or '1x128'")
     T, H = hidden_states.shape
     K = topk_ids.shape[1]
     pw = prepare_weights(w1, w1_scale, w2, w2_scale, fmt)
@@ -337,16 +398,25 @@ def fused_moe(hidden_states, w1, w2, topk_weight, topk_ids, expert_mask=None,
     E_route = pw.E if expert_mask is None else int(expert_mask.numel())
     B = int(block_size_M) if block_size_M else pick_block(T, K, pw.E, fmt)
     act = _lib.ACT_SILU if int(activation) == ActivationType.Silu else _lib.ACT_SWIGLU
-    # workspaces are laid out for the token count rounded up to 512 beyond that size, so that calls whose batch
-    # varies from step to step (expert-parallel dispatch) reuse one allocation
-    T_cap = T if T <= 512 else -(-T // 512) * 512
-    plan = get_plan(T_cap, K, pw.E, E_route, H, pw.I, B, act, swiglu_limit, hidden_states.device, act_terms, fmt)
+    cm = _lib.COMBINE_FUSED if combine == "fused" else _lib.COMBINE_GATHER
+    aq = _lib.ACTQ_1X128 if act_quant == "1x128" else _lib.ACTQ_TERMS
+    b1 = b2 = None
+    if bias1 is not None:
+        if tuple(bias1.shape) != (pw.E, 2 * pw.I):
+            raise ValueError(f"bias1 must be [E, 2I] = [{pw.E}, {2 * pw.I}]")
+        b1 = bias1.float().contiguous()
+    if bias2 is not None:
+        if tuple(bias2.shape) != (pw.E, H):
+            raise ValueError(f"bias2 must be [E, H] = [{pw.E}, {H}]")
+        b2 = bias2.float().contiguous()
+    plan = get_plan(_capacity(T), K, pw.E, E_route, H, pw.I, B, act, swiglu_limit, hidden_states.device, act_terms, fmt,
+                    cm, aq, bool(doweight_stage1))
     plan.set_tokens(T)
     ids = topk_ids if topk_ids.dtype == torch.int32 else topk_ids.to(torch.int32)
     tw = topk_weight if topk_weight.dtype == torch.float32 else topk_weight.float()
     mask = None if expert_mask is None else expert_mask.to(torch.int32).contiguous()
     return moe_forward(plan, pw, hidden_states.contiguous(), tw.contiguous(), ids.contiguous(), mask,
-                       num_local_tokens=_num_local(num_local_tokens, hidden_states.device))
+                       num_local_tokens=_num_local(num_local_tokens, hidden_states.device), bias1=b1, bias2=b2)
 
 
 def fused_topk(hidden_states, gating_output, topk: int, renormalize: bool = True, scoring: str = "softmax"):

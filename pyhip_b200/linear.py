@@ -11,12 +11,11 @@ C ABI calls (`b200moe_sort_align`, `b200moe_quant_rows[_e4m3]`, `b200moe_down`).
 from __future__ import annotations
 
 import ctypes
-import weakref
 
 import torch
 
 from . import _lib
-from .fused_moe import _ptr, _stream, get_plan, pick_block
+from .fused_moe import _capacity, _ptr, _stream, get_plan, pick_block
 
 
 class PreparedLinear:
@@ -36,7 +35,7 @@ class PreparedLinear:
             if int(s.max()) > 254:
                 raise ValueError("E8M0 scale 0xFF (NaN) is not a valid weight scale")
             shape = _lib.Shape(T=0, K=1, E=1, E_route=1, H=self.N, I=self.K, B=32, weight_format=_lib.W_MXFP4,
-                               activation=0, swiglu_limit=0.0, act_terms=0)
+                               activation=0, swiglu_limit=0.0, act_terms=0, combine_mode=0, act_quant=0, doweight_stage1=0)
             sb = ctypes.c_int64()
             L = _lib.lib()
             _lib.check(L.b200moe_prepared_scale_bytes(ctypes.byref(shape), 2, ctypes.byref(sb)), "prepared_scale_bytes")
@@ -54,17 +53,19 @@ class PreparedLinear:
             self.w2_scale = weight_scale.float().contiguous()
 
 
-_prepared: dict = {}
+_prepared: dict = {}          # insertion-ordered: least recently used first
+_PREPARED_ENTRIES = 16
 
 
 def _prepare(weight, weight_scale, fmt) -> PreparedLinear:
-    key = (weight.data_ptr(), weight_scale.data_ptr(), tuple(weight.shape), fmt)
-    hit = _prepared.get(key)
-    if hit is not None and hit[0]() is weight:
-        return hit[1]
-    pl = PreparedLinear(weight, weight_scale, fmt)
-    _prepared[key] = (weakref.ref(weight), pl)
-    return pl
+    key = (weight.data_ptr(), weight_scale.data_ptr(), tuple(weight.shape), fmt, weight_scale._version)
+    hit = _prepared.pop(key, None)
+    if hit is None:
+        while len(_prepared) >= _PREPARED_ENTRIES:
+            _prepared.pop(next(iter(_prepared)))
+        hit = (PreparedLinear(weight, weight_scale, fmt), (weight, weight_scale))
+    _prepared[key] = hit
+    return hit[0]
 
 
 def _linear(x, weight, weight_scale, fmt, act_terms, block_size_M):
@@ -79,7 +80,7 @@ def _linear(x, weight, weight_scale, fmt, act_terms, block_size_M):
     if M == 0:
         return torch.empty(0, pl.N, dtype=torch.bfloat16, device=x.device)
     B = int(block_size_M) if block_size_M else pick_block(M, 1, 1, fmt)
-    M_cap = M if M <= 512 else -(-M // 512) * 512
+    M_cap = _capacity(M)
     plan = get_plan(M_cap, 1, 1, 1, pl.N, pl.K, B, _lib.ACT_SILU, 0.0, x.device, act_terms, fmt)
     plan.set_tokens(M)
     ids = torch.zeros(M, 1, dtype=torch.int32, device=x.device)

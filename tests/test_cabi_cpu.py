@@ -23,11 +23,12 @@ def test_every_declared_symbol_is_exported(L):
     assert declared == set(_lib.EXPORTS)
     for name in declared:
         assert hasattr(L, name), name
-    assert L.b200moe_version() == 2
+    assert L.b200moe_version() == 3
 
 
 def test_struct_sizes_match_header():
-    assert ctypes.sizeof(_lib.Shape) == 44
+    assert ctypes.sizeof(_lib.Shape) == 56
+    assert ctypes.sizeof(_lib.Io) == 12 * 8
     assert ctypes.sizeof(_lib.Workspace) == 14 * 8
 
 
@@ -43,7 +44,8 @@ def test_workspace_layout_arithmetic(L):
 
 
 @pytest.mark.parametrize("field,value", [("B", 40), ("H", 100), ("I", 0), ("K", 0), ("T", 1 << 24),
-                                         ("weight_format", 7), ("activation", 9), ("E_route", 4), ("act_terms", 5)])
+                                         ("weight_format", 7), ("activation", 9), ("E_route", 4), ("act_terms", 5),
+                                         ("combine_mode", 2), ("act_quant", 2), ("doweight_stage1", 2)])
 def test_bad_shapes_are_rejected(L, field, value):
     s = _lib.Shape(T=8, K=2, E=8, E_route=8, H=256, I=128, B=32, weight_format=0, activation=0, swiglu_limit=7.0, act_terms=0)
     setattr(s, field, value)
@@ -58,8 +60,10 @@ def test_bad_shapes_are_rejected(L, field, value):
 def test_null_pointers_are_rejected_without_launch(L):
     s = _lib.Shape(T=8, K=2, E=8, E_route=8, H=256, I=128, B=32, weight_format=0, activation=0, swiglu_limit=7.0, act_terms=0)
     ws = _lib.workspace_layout(s)
-    assert L.b200moe_gateup(ctypes.byref(s), ctypes.byref(ws), None, None, None, None, None) < 0
-    assert L.b200moe_down(ctypes.byref(s), ctypes.byref(ws), None, None, None, None) < 0
+    assert L.b200moe_gateup(ctypes.byref(s), ctypes.byref(ws), None, None, None, None, None, None) < 0
+    assert L.b200moe_down(ctypes.byref(s), ctypes.byref(ws), None, None, None, None, None, None) < 0
+    assert L.b200moe_forward_ex(ctypes.byref(s), ctypes.byref(ws), None, None, None) < 0
+    assert L.b200moe_static_status(ctypes.byref(s), None, None) < 0
     assert L.b200moe_forward(ctypes.byref(s), ctypes.byref(ws), None, None, None, None, None, None, None, None,
                              None, None, None) < 0
     assert L.b200moe_sort_align(None, None, 4, 2, 8, 32, None, None, None, None, None, None, None) < 0
@@ -79,6 +83,13 @@ def test_workspace_too_small_for_the_token_count_is_rejected(L):
     p = ctypes.c_void_p(4096)
     rc = L.b200moe_forward(ctypes.byref(big), ctypes.byref(ws_small), p, p, p, p, None, p, p, p, p, p, None)
     assert rc < 0 and b"workspace holds" in L.b200moe_last_error()
+    # enough rows but laid out for another block size / routing space: the index and scale regions are too small
+    other = _lib.Shape(T=64, K=2, E=8, E_route=8, H=256, I=128, B=128, weight_format=0, activation=0, swiglu_limit=7.0, act_terms=0)
+    ws_other = _lib.workspace_layout(other)
+    use = _lib.Shape(T=500, K=2, E=8, E_route=8, H=256, I=128, B=16, weight_format=0, activation=0, swiglu_limit=7.0, act_terms=0)
+    assert ws_other.max_rows >= _lib.workspace_layout(use).max_rows
+    rc = L.b200moe_forward(ctypes.byref(use), ctypes.byref(ws_other), p, p, p, p, None, p, p, p, p, p, None)
+    assert rc < 0 and b"workspace region" in L.b200moe_last_error()
     assert L.b200moe_gather_sum(None, None, 4, 2, 64, None, None) < 0
     assert L.b200moe_gather_sum(None, None, 0, 2, 64, None, None) == 0      # empty batch: nothing to do
 

@@ -19,7 +19,7 @@ def _free_port():
         return s.getsockname()[1]
 
 
-def _worker(rank, world, port, fail_rank, q, small_batch=0, chunks=1):
+def _worker(rank, world, port, fail_rank, q, small_batch=0, chunks=1, uneven=False):
     os.environ["MASTER_ADDR"] = "127.0.0.1"
     os.environ["MASTER_PORT"] = str(port)
     torch.set_num_threads(1)
@@ -27,6 +27,9 @@ def _worker(rank, world, port, fail_rank, q, small_batch=0, chunks=1):
                             timeout=datetime.timedelta(seconds=8 if fail_rank is not None else 60))
     try:
         T, H, I, E, K = 24, 128, 64, 8, 3
+        T_agreed = T
+        if uneven:
+            T += rank               # this rank's batch differs from what the layer was built for
         w = synth.make_weights_mxfp4(E, H, I, seed=2)
         w1, w2 = orc.dequant_mxfp4(w[0], w[1]), orc.dequant_mxfp4(w[2], w[3])
         x = synth.make_hidden(T, H, seed=10 + rank)
@@ -38,7 +41,7 @@ def _worker(rank, world, port, fail_rank, q, small_batch=0, chunks=1):
             return orc.torch_moe_oracle(xr, w1[lo:lo + El], w2[lo:lo + El], twr, ids_local)
 
         layer = ep.ExpertParallelMoE(None, None, None, None, E, rank, world, local_fn=local_fn,
-                                     small_batch=small_batch, dispatch_chunks=chunks)
+                                     small_batch=small_batch, dispatch_chunks=chunks, tokens_per_rank=T_agreed)
         if fail_rank == rank:
             q.put((rank, "skipped"))
             return
@@ -56,11 +59,12 @@ def _worker(rank, world, port, fail_rank, q, small_batch=0, chunks=1):
             pass
 
 
-def _spawn(world, fail_rank=None, small_batch=0, chunks=1):
+def _spawn(world, fail_rank=None, small_batch=0, chunks=1, uneven=False):
     ctx = mp.get_context("spawn")
     q = ctx.Queue()
     port = _free_port()
-    procs = [ctx.Process(target=_worker, args=(r, world, port, fail_rank, q, small_batch, chunks)) for r in range(world)]
+    procs = [ctx.Process(target=_worker, args=(r, world, port, fail_rank, q, small_batch, chunks, uneven))
+             for r in range(world)]
     for p in procs:
         p.start()
     res = dict(q.get(timeout=120) for _ in range(world))
@@ -113,3 +117,28 @@ def test_rank_that_never_joins_is_detected_by_timeout():
     res = _spawn(2, fail_rank=1)
     assert res[1] == "skipped"
     assert isinstance(res[0], str) and res[0].startswith("error:")
+
+
+def test_unequal_batches_raise_on_the_host_in_the_gathered_form_and_work_in_the_dispatch_form():
+    """The exchange form is fixed when the layer is built, from values all ranks share.  A rank whose batch
+    differs from the agreed `tokens_per_rank` gets a ValueError before any collective is issued in the
+    fixed-shape (gathered) form -- rank 0, whose batch matches, sees its peer missing as a timeout/error
+    instead of summing the wrong rows -- while the all-to-all-v form takes unequal batches as they come."""
+    res = _spawn(2, small_batch=512, uneven=True, fail_rank=-1)       # gathered; fail_rank=-1 only shortens the timeout
+    assert res[1] == "error:ValueError"
+    assert isinstance(res[0], str) and res[0].startswith("error:")
+    res = _spawn(2, small_batch=0, uneven=True)                       # dispatch
+    for r in range(2):
+        cos, mx = res[r]
+        assert cos > 0.9999 and mx < 5e-3, (r, cos, mx)
+
+
+def test_exchange_choice_needs_agreed_values():
+    with pytest.raises(ValueError):
+        ep.ExpertParallelMoE(None, None, None, None, 8, 0, 2, local_fn=lambda *a: None, exchange="gathered")
+    layer = ep.ExpertParallelMoE(None, None, None, None, 8, 0, 2, local_fn=lambda *a: None)
+    assert layer.exchange == "dispatch"                               # no agreed token count: the form that needs none
+    layer = ep.ExpertParallelMoE(None, None, None, None, 8, 0, 2, local_fn=lambda *a: None, tokens_per_rank=64)
+    assert layer.exchange == "gathered"
+    layer = ep.ExpertParallelMoE(None, None, None, None, 8, 0, 2, local_fn=lambda *a: None, tokens_per_rank=4096)
+    assert layer.exchange == "dispatch"

@@ -56,7 +56,7 @@ def _sf_rows(sf: np.ndarray, rows: int, KB: int, B: int, NT: int, TS: int) -> np
 _E2M1 = np.array([0, .5, 1, 1.5, 2, 3, 4, 6, -0., -.5, -1, -1.5, -2, -3, -4, -6], dtype=np.float32)
 
 
-@pytest.mark.parametrize("NT", [3, 4, 2])
+@pytest.mark.parametrize("NT", [3, 4, 2, 1])
 def test_quantised_rows_match_oracle_bit_for_bit(NT):
     T, H, I, E, K, B = 40, 288, 160, 8, 2, 32      # H, I multiples of 32 but not of 128
     x, tw, ids, w = _case(T, H, I, E, K, seed=4)
@@ -287,3 +287,135 @@ def test_num_local_tokens_padded_batch_and_graph_replay():
         # the public call with a host integer takes the same route
         assert torch.equal(fused_moe(xd, w[0], w[2], twd, idsd, num_local_tokens=n, **kw).cpu(), got)
     plan.check_status()
+
+
+# --------------------------------------------------------------------------------------------
+# fused combine, decode-sized (three-launch) path, plain MXFP4 activations, biases, stage-1 weights
+# --------------------------------------------------------------------------------------------
+@pytest.mark.parametrize("T", [1, 2, 7, 8, 33, 64, 65, 300])
+def test_fused_combine_matches_oracle_and_the_gather_form(T):
+    """The down epilogue that multiplies by the routing weight and adds into the output (the reference kernels'
+    own epilogue, src/contrib/moe.py:703-787) against the layer oracle; the gather form is the anchor: the two
+    differ only in the order of a token's K bf16 additions."""
+    H, I, E, K = 288, 160, 16, 4
+    x, tw, ids, w = _case(T, H, I, E, K, seed=100 + T)
+    ref = orc.torch_moe_oracle_mxfp4(x, *w, tw, ids)
+    y_f = _run_layer(x, tw, ids, w, combine="fused")
+    y_g = _run_layer(x, tw, ids, w, combine="gather")
+    _assert_close(y_f, ref, f"fused T={T}")
+    _assert_close(y_g, ref, f"gather T={T}")
+    assert orc.max_abs(y_f, y_g) <= 2 ** -7 * max(1.0, float(ref.float().abs().max()))   # a bf16 step or two
+
+
+@pytest.mark.parametrize("T,E,K,mask", [(1, 128, 4, False), (2, 16, 4, False), (7, 16, 4, True), (8, 128, 4, False),
+                                        (64, 128, 4, False), (32, 256, 8, False), (64, 16, 4, True)])
+def test_small_batch_path_sorts_bit_exactly(T, E, K, mask):
+    """Up to 256 (token, expert) pairs the sort runs inside the quantiser launch (every CTA repeats it): the
+    sort arrays it leaves in the workspace must equal the oracle's over the defined prefix."""
+    H, I = 256, 128
+    x = synth.make_hidden(T, H, T)
+    tw, ids = synth.make_routing(T, E, K, seed=T + E)
+    m = None
+    if mask:
+        m = torch.tensor([1, 0] * (E // 2), dtype=torch.int32)
+    E_local = E if m is None else int(m.sum())
+    w = synth.make_weights_mxfp4(E_local, H, I, seed=3)
+    pw = prepare_weights(*(t.to(DEV) for t in w))
+    B = 16
+    plan = get_plan(T, K, E_local, E, H, I, B, 0, 7.0, torch.device(DEV), combine_mode=1)
+    from pyhip_b200.fused_moe import moe_forward
+    y = moe_forward(plan, pw, x.to(DEV), tw.to(DEV), ids.to(DEV), None if m is None else m.to(DEV))
+    torch.cuda.synchronize()
+    plan.check_status()
+    s_ids, s_w, s_e, nv, loc = (t.cpu().numpy() for t in plan.sort_outputs())
+    exp = orc.moe_sorting_oracle(ids, tw, E, B, expert_mask=None if m is None else m.tolist())
+    n = int(exp[3][0])
+    assert nv.tolist() == exp[3].tolist()
+    assert np.array_equal(s_ids.view(np.uint32)[:n], exp[0][:n])
+    assert np.array_equal(s_w[:n].view(np.uint32), exp[1][:n].view(np.uint32))
+    assert np.array_equal(s_e[:n // B], exp[2][:n // B])
+    # loc is the inverse map: pair (t, k) -> sorted position, -1 when its expert is masked out
+    live = (exp[0][:n] >> 24) < K
+    pos = np.nonzero(live)[0]
+    pair = (exp[0][:n][live] & 0xFFFFFF) * K + (exp[0][:n][live] >> 24)
+    want = np.full(T * K, -1, dtype=np.int32)
+    want[pair] = pos
+    assert np.array_equal(loc[:T * K], want)
+    tw_m = tw if m is None else tw * m.bool()[ids.long()].float()
+    keep = None if m is None else m.bool()
+    w_full = w if m is None else tuple(_expand(t, keep) for t in w)
+    _assert_close(y.cpu(), orc.torch_moe_oracle_mxfp4(x, *w_full, tw_m, ids), "small path layer")
+
+
+def _expand(t, keep):
+    """local expert tensors -> full-size tensor with the masked experts left at zero."""
+    full = torch.zeros((keep.numel(),) + tuple(t.shape[1:]), dtype=t.dtype)
+    full[keep] = t
+    return full
+
+
+@pytest.mark.parametrize("T,H,I,E,K", [(32, 512, 256, 8, 2), (300, 288, 160, 16, 4), (5, 2880, 2880, 4, 2)])
+def test_plain_mxfp4_activations_match_the_a4w4_oracle(T, H, I, E, K):
+    """act_terms = 1 is the reference's a4w4 arithmetic (per-1x32 MXFP4 activations): parity is against the
+    oracle that dequantises the same quantised activations, with the reference's own threshold
+    (calc_diff <= 0.01, tests/contrib/moe/test_mxfp4.py:286-299); the distance to the bf16-activation oracle is
+    reported, not asserted."""
+    x, tw, ids, w = _case(T, H, I, E, K, seed=T + 7)
+    ref_q = orc.torch_moe_oracle_mxfp4(x, *w, tw, ids, act_quant="mxfp4")
+    ref = orc.torch_moe_oracle_mxfp4(x, *w, tw, ids)
+    for combine in ("gather", "fused"):
+        y = _run_layer(x, tw, ids, w, act_terms=1, combine=combine)
+        d = orc.calc_diff(y, ref_q)
+        assert d <= 0.01 and orc.cosine(y, ref_q) >= 0.995, f"{combine}: calc_diff {d:.4f} cosine {orc.cosine(y, ref_q):.5f}"
+        print(f"a4w4 T={T} {combine}: calc_diff vs a4w4 oracle {d:.2e}, cosine vs bf16-activation oracle "
+              f"{orc.cosine(y, ref):.5f}")
+
+
+@pytest.mark.parametrize("combine", ["gather", "fused"])
+@pytest.mark.parametrize("activation", ["silu", "swiglu"])
+def test_biases_and_stage1_weights(combine, activation):
+    T, H, I, E, K = 70, 288, 160, 8, 2
+    x, tw, ids, w = _case(T, H, I, E, K, seed=51)
+    g = torch.Generator().manual_seed(9)
+    b1 = (torch.randn(E, 2 * I, generator=g) * 0.1).to(torch.bfloat16)
+    b2 = (torch.randn(E, H, generator=g) * 0.1).to(torch.bfloat16)
+    act = ActivationType.Silu if activation == "silu" else ActivationType.Swiglu
+    for kw, okw in ((dict(bias1=b1.to(DEV), bias2=b2.to(DEV)), dict(bias1=b1, bias2=b2)),
+                    (dict(doweight_stage1=True), dict(doweight_stage1=True)),
+                    (dict(bias1=b1.to(DEV), doweight_stage1=True), dict(bias1=b1, doweight_stage1=True))):
+        ref = orc.torch_moe_oracle_mxfp4(x, *w, tw, ids, activation=activation, swiglu_limit=7.0, **okw)
+        y = _run_layer(x, tw, ids, w, activation=act, combine=combine, **kw)
+        _assert_close(y, ref, f"{sorted(kw)} {combine} {activation}")
+
+
+def test_prepared_scale_image_known_answer():
+    """b200moe_prepare_scales against the byte formula of the scale chunks: chunk (e, m-tile, k-block, part),
+    byte (r % 32) * 16 + (r / 32) * 4 + j holds the scale of weight row r of the tile and 32-block 4*kb + j;
+    rows and k-blocks that do not exist read 127."""
+    E, H, I = 3, 288, 160            # neither a multiple of 128
+    g = torch.Generator().manual_seed(2)
+    s1 = torch.randint(100, 140, (E, 2 * I, H // 32), dtype=torch.uint8, generator=g)
+    s2 = torch.randint(100, 140, (E, H, I // 32), dtype=torch.uint8, generator=g)
+    w1 = torch.zeros(E, 2 * I, H // 2, dtype=torch.uint8)
+    w2 = torch.zeros(E, H, I // 2, dtype=torch.uint8)
+    pw = prepare_weights(w1.to(DEV), s1.to(DEV), w2.to(DEV), s2.to(DEV))
+    torch.cuda.synchronize()
+    for which, src, rows, Kd, got in ((1, s1.numpy(), I, H, pw.w1_scale.cpu().numpy()),
+                                      (2, s2.numpy(), H, I, pw.w2_scale.cpu().numpy())):
+        KB = (Kd + 255) // 256 * 2
+        MT = (rows + 127) // 128 if which == 1 else (rows + 255) // 256
+        img = got.reshape(E, MT, KB, 2, 512)
+        want = np.full_like(img, 127)
+        for e in range(E):
+            for mt in range(MT):
+                for part in range(2):
+                    for r in range(128):
+                        row_in = mt * 128 + r if which == 1 else (2 * mt + part) * 128 + r
+                        if row_in >= rows:
+                            continue
+                        row = part * rows + row_in if which == 1 else row_in
+                        for kb in range(KB):
+                            for j in range(4):
+                                if kb * 4 + j < Kd // 32:
+                                    want[e, mt, kb, part, (r % 32) * 16 + (r // 32) * 4 + j] = src[e, row, kb * 4 + j]
+        assert np.array_equal(img, want), which

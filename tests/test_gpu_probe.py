@@ -4,7 +4,6 @@ memory scale copy."""
 import ctypes
 import os
 import pathlib
-import tempfile
 
 import numpy as np
 import pytest
@@ -13,7 +12,13 @@ import torch
 from pyhip_b200 import _lib
 
 pytestmark = pytest.mark.gpu
-OUT = pathlib.Path(os.environ.get("B200MOE_PROBE_DUMP", tempfile.gettempdir()))   # where the probe images are saved
+DUMP = os.environ.get("B200MOE_PROBE_DUMP")      # directory to save the probe images in (unset: nothing is written)
+
+
+def _dump(name, arr):
+    if DUMP:
+        pathlib.Path(DUMP).mkdir(parents=True, exist_ok=True)
+        np.save(pathlib.Path(DUMP) / name, arr)
 
 
 def _probe(which, inp: torch.Tensor, out_words: int):
@@ -30,8 +35,7 @@ def test_tma_fp4_unpack_image():
     raw = _probe(1, src.cuda(), 4096 + 1)
     assert raw[4096] == 0, "TMA wait ran out"
     img = raw[:4096].view(np.uint8).reshape(128, 128)
-    OUT.mkdir(exist_ok=True)
-    np.save(OUT / "probe_tma_fp4_image.npy", img)
+    _dump("probe_tma_fp4_image.npy", img)
     s = src.numpy()
     for r in range(128):
         for c in range(8):                       # logical 16-byte chunk -> 128-byte-swizzled position
@@ -40,13 +44,23 @@ def test_tma_fp4_unpack_image():
 
 
 def test_scale_copy_to_tensor_memory_layout():
-    src = torch.arange(128, dtype=torch.int32) * 0x01010101 + 0x03020100   # distinct bytes
     src = (torch.arange(512, dtype=torch.int64) % 251).to(torch.uint8)
     raw = _probe(2, src.cuda(), 512 + 1)
     assert raw[512] == 0, "tcgen05.cp wait ran out"
     got = raw[:512].astype(np.uint32).reshape(128, 4)
-    OUT.mkdir(exist_ok=True)
-    np.save(OUT / "probe_utccp.npy", got)
+    _dump("probe_utccp.npy", got)
     words = src.numpy().view(np.uint32).reshape(32, 4)       # 32 rows x 16 bytes
     for lane in range(128):
         assert np.array_equal(got[lane], words[lane % 32]), lane
+
+
+@pytest.mark.parametrize("kind,n", [(0, 256), (1, 256)])
+def test_mma_rate_probe_completes(kind, n):
+    """The whole-chip dense MMA rate probe the benchmark uses for its tensor roofline (FP4 and FP8 kinds):
+    every SM reports, no bounded wait runs out, and the issue loop took a plausible number of cycles."""
+    sms = torch.cuda.get_device_properties(0).multi_processor_count
+    count = 2000
+    cfg = torch.tensor([kind, n, count, 0, 0, 0, 0, 0], dtype=torch.int32, device="cuda:0")
+    raw = _probe(4, cfg, sms * 3).reshape(sms, 3)
+    assert (raw[:, 2] == 0).all(), "a wait ran out"
+    assert (raw[:, 1] > count * 32).all() and (raw[:, 1] < count * 4000).all()

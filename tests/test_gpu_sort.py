@@ -78,3 +78,18 @@ def test_num_local_tokens_sorts_only_the_live_prefix(T, n):
     assert np.all(got_ids[~live] == ((K << 24) | T))
     assert np.array_equal(s_w.cpu().numpy()[:L].view(np.uint32), exp[1][:L].view(np.uint32))
     assert np.array_equal(s_e.cpu().numpy()[:L // B], exp[2][:L // B])
+
+
+def test_reference_golden_sort_vectors_on_the_device():
+    """The fixture holds the outputs of the reference's own moe_sorting_ref (lifted out of
+    src/contrib/fused_moe.py:56-100 and run on CPU, tests/golden/make_golden.py) for a block size of 256:
+    the device sort must reproduce its defined prefix bit for bit."""
+    import pathlib
+    g = np.load(pathlib.Path(__file__).parent / "golden" / "sorting_b256.npz")
+    ids, tw = torch.from_numpy(g["topk_ids"]), torch.from_numpy(g["topk_weight"])
+    E, B, n = int(g["E"]), int(g["B"]), int(g["num_valid"])
+    got = _run(ids, tw, E, B)
+    assert got[3].tolist() == [n, ids.shape[0]]
+    assert np.array_equal(got[0][:n], g["sorted_ids"])
+    assert np.array_equal(got[1][:n].view(np.uint32), g["sorted_weights"].view(np.uint32))
+    assert np.array_equal(got[2][:n // B], g["sorted_expert_ids"])

@@ -221,3 +221,67 @@ def test_tiny_config_parity_bar_is_meaningful():
     x1 = orc.fp4_terms_dequant(*orc.fp4_terms_quant(x, 1)).to(torch.bfloat16)
     got1 = orc.torch_moe_oracle_mxfp4(x1, w1_q, w1_s, w2_q, w2_s, tw, ids)
     assert orc.cosine(got1, ref) < 0.9995
+
+
+# ------------------------------------------------------------------ synthetic routing
+def test_zipf_routing_follows_the_stated_load_law():
+    """The skewed-routing configuration asks for Zipf(s = 1.2) expert load.  `make_routing(..., "zipf")` adds
+    b_e = -c ln(rank_e) to N(0,1) logits before softmax / top-2, with c calibrated on the measured load: the
+    share of (token, expert) pairs per expert, ordered by popularity rank, must fall like rank^-1.2 (log-log
+    slope within 0.15 of -1.2), stay within 0.08 of the Zipf(1.2) shares (top-k without replacement caps the
+    head at 1/K), and leave no expert empty."""
+    from pyhip_b200 import synth
+    T, E, K = 16384, 8, 2
+    _, ids = synth.make_routing(T, E, K, "zipf", seed=0, skew_seed=0)
+    share = np.bincount(ids.flatten().numpy(), minlength=E) / (T * K)
+    gp = torch.Generator().manual_seed(0 * 1000003 + 41)
+    rank = torch.randperm(E, generator=gp).numpy() + 1           # rank_e used by make_routing
+    by_rank = share[np.argsort(rank)]
+    assert np.all(np.diff(by_rank) < 0), by_rank                  # strictly falling with the popularity rank
+    assert by_rank[0] <= 1.0 / K + 1e-9 and by_rank[-1] > 0.0
+    slope = np.polyfit(np.log(np.arange(1, E + 1)), np.log(by_rank), 1)[0]
+    assert abs(slope + 1.2) < 0.15, (slope, by_rank)
+    zipf = 1.0 / np.arange(1, E + 1) ** 1.2
+    zipf /= zipf.sum()
+    assert np.abs(by_rank - zipf).max() < 0.08, (by_rank, zipf)
+    print("measured share by rank", np.round(by_rank, 4).tolist(), "Zipf(1.2)", np.round(zipf, 4).tolist(), "slope", slope)
+
+
+def test_calc_diff_matches_its_definition_and_thresholds():
+    """calc_diff (src/misc.py:131-141) is 0 for identical tensors, 1 for orthogonal ones, and grows with noise:
+    the reference's thresholds (0.02 layer, 0.01 a4w4 gate-up, 1e-3 bf16 path) are ordered accordingly."""
+    g = torch.Generator().manual_seed(0)
+    a = torch.randn(64, 128, generator=g)
+    assert orc.calc_diff(a, a) == 0.0
+    b = torch.zeros_like(a)
+    b[0, 0], a2 = 1.0, torch.zeros_like(a)
+    a2[0, 1] = 1.0
+    assert abs(orc.calc_diff(a2, b) - 1.0) < 1e-12
+    noisy = a + 0.05 * torch.randn(64, 128, generator=g)
+    d = orc.calc_diff(a, noisy)
+    assert 1e-3 < d < 0.01
+    assert abs(d - (1 - orc.cosine(a, noisy))) < 2e-3           # for nearly equal norms the two agree
+
+
+def test_activation_quantiser_modes_of_the_oracle():
+    """act_quant = mxfp4 / fp8_1x128 quantise x and h before the products; the known distances to the
+    bf16-activation layer (cosine ~0.98 and ~0.999) show why those modes are judged against their own oracle."""
+    from pyhip_b200 import synth
+    c = synth.CONFIGS["tiny"]
+    x = synth.make_hidden(c.T, c.H)
+    tw, ids = synth.make_routing(c.T, c.E, c.K)
+    w = synth.make_weights_mxfp4(c.E, c.H, c.I)
+    r0 = orc.torch_moe_oracle_mxfp4(x, *w, tw, ids)
+    r1 = orc.torch_moe_oracle_mxfp4(x, *w, tw, ids, act_quant="mxfp4")
+    assert 0.95 < orc.cosine(r0, r1) < 0.9995
+    wf = synth.make_weights_fp8(c.E, c.H, c.I)
+    q0 = orc.torch_moe_oracle_fp8(x, *wf, tw, ids)
+    q1 = orc.torch_moe_oracle_fp8(x, *wf, tw, ids, act_quant="fp8_1x128")
+    assert 0.998 < orc.cosine(q0, q1) < 0.99999
+    # the 1x128 quantiser: scale = amax/448, values round-trip within one e4m3 step of the block maximum
+    q, s = orc.act_quant_fp8_1x128(x)
+    assert s.shape == (c.T, c.H // 128) and q.dtype == torch.float8_e4m3fn
+    back = orc.act_dequant_fp8_1x128(q, s)
+    amax = x.float().reshape(c.T, -1, 128).abs().amax(-1, keepdim=True)
+    assert float(((back - x.float()).reshape(c.T, -1, 128).abs() / amax).max()) <= 2 ** -4 + 1e-6
+    assert torch.equal(q.float().reshape(c.T, -1, 128).abs().amax(-1), torch.full((c.T, c.H // 128), 448.0))

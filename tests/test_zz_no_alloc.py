@@ -6,13 +6,15 @@ a fixed array inside the library.  The array is shared by all calls and keeps th
 contents, so the check is made on two calls in a row -- the second one, with different routing and
 a different token count, must not be disturbed by what the first left behind -- each compared with
 `b200moe_forward` on a caller-provided workspace.  Both paths run the same kernels, so the outputs
-must agree bit for bit (well inside the tolerance the other layer tests use).
+must agree bit for bit (well inside the tolerance the other layer tests use); the result is also held
+against the CPU oracle, and the status words are read back through `b200moe_static_status`.
 """
 import ctypes
 
 import pytest
 import torch
 
+from oracle import moe_oracle as orc
 from pyhip_b200 import _lib, synth
 from pyhip_b200.fused_moe import get_plan, moe_forward, pick_block, prepare_weights
 
@@ -35,11 +37,13 @@ def _static_forward(shape, x, ids, tw, pw):
 
 def test_static_scratch_matches_workspace_path_on_two_calls_in_a_row():
     H, I, E, K = 288, 160, 16, 4
-    w = tuple(t.to(DEV) for t in synth.make_weights_mxfp4(E, H, I, seed=31))
+    w_host = synth.make_weights_mxfp4(E, H, I, seed=31)
+    w = tuple(t.to(DEV) for t in w_host)
     pw = prepare_weights(*w)
     for call, T in enumerate((48, 5)):                       # second call: fewer rows than the first left behind
-        x = synth.make_hidden(T, H, seed=40 + call).to(DEV)
-        tw, ids = (t.to(DEV) for t in synth.make_routing(T, E, K, "zipf", seed=40 + call))
+        x_host = synth.make_hidden(T, H, seed=40 + call)
+        tw_host, ids_host = synth.make_routing(T, E, K, "zipf", seed=40 + call)
+        x, tw, ids = x_host.to(DEV), tw_host.to(DEV), ids_host.to(DEV)
         B = pick_block(T, K, E)
         plan = get_plan(T, K, E, E, H, I, B, 0, 7.0, torch.device(DEV))
         ref = moe_forward(plan, pw, x, tw, ids)
@@ -47,6 +51,14 @@ def test_static_scratch_matches_workspace_path_on_two_calls_in_a_row():
         torch.cuda.synchronize()
         assert torch.isfinite(got.float()).all()
         assert torch.equal(got.view(torch.int16), ref.view(torch.int16)), f"call {call}"
+        want = orc.torch_moe_oracle_mxfp4(x_host, *w_host, tw_host, ids_host)
+        assert orc.cosine(got.cpu(), want) >= 0.9995 and orc.max_abs(got.cpu(), want) <= 2e-2, f"call {call}"
+        status = (ctypes.c_int32 * 16)()
+        _lib.check(_lib.lib().b200moe_static_status(ctypes.byref(plan.shape), status,
+                                                    ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)),
+                   "static_status")
+        torch.cuda.synchronize()
+        assert status[0] == 0 and status[2] == 0, list(status)
 
 
 def test_shape_beyond_the_built_in_scratch_is_refused():
