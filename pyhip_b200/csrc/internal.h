@@ -107,7 +107,7 @@ struct GemmArgs {
   void* out2;          // down: bf16 [max_rows, H]
   void* gstage;        // gate-up: scratch for per-CTA staging tiles in global memory (may be null)
   int64_t gstage_bytes;
-  const float* sorted_w;   // routing weight per sorted row (needed by y and weight_stage1)
+  const float* sorted_w;   // routing weight per sorted row (weight_stage1 needs it; with y, null means weight 1)
   const float* bias;       // fp32 per-expert bias: gate-up [E, 2*rows], down [E, rows]; or null
   void* y;                 // down: zeroed bf16 [T, rows]; non-null selects the fused weighted scatter-add epilogue
   int weight_stage1;       // gate-up: apply the routing weight to h

@@ -621,8 +621,9 @@ int launch_sort_quant_small(int fmt, const void* x, const int32_t* ids, const fl
 // combine: y[t,:] = sum over the token's pairs, in ascending sorted position (= ascending
 // expert id), of bf16(out2[loc] * w), each partial sum rounded to bf16 -- the arithmetic of
 // the reference's index_add_ loop (tests/contrib/moe/test_moe.py:107-117).
-// One warp per token: the token's K positions are ordered once (lane i ends up holding the
-// i-th smallest position and its weight), then the lanes walk the row in 16-byte vectors.
+// One warp per (token, run of 32 sixteen-byte vectors): the token's K positions are ordered once per warp
+// with shuffles (lane i ends up holding the i-th smallest position and its weight) instead of a K^2 rescan
+// per vector, and a row is spread over several warps so that decode-sized batches still fill the machine.
 // topk_w == nullptr: the routing weights were applied upstream (weight 1 here).
 // =====================================================================================
 constexpr int kMaxTopk = 32;
@@ -631,11 +632,13 @@ __global__ void __launch_bounds__(256)
 combine_kernel(const __nv_bfloat16* __restrict__ out2, const int32_t* __restrict__ loc,
                const float* __restrict__ topk_w, __nv_bfloat16* __restrict__ y, int T, int K, int H) {
   const int vec_per_row = H / 8;
+  const int chunks = (vec_per_row + 31) / 32;
   grid_dep_launch();
   grid_dep_wait();
   const int lane = threadIdx.x & 31;
-  const int warps = (gridDim.x * blockDim.x) >> 5;
-  for (int t = (blockIdx.x * blockDim.x + threadIdx.x) >> 5; t < T; t += warps) {
+  const int64_t warps = ((int64_t)gridDim.x * blockDim.x) >> 5;
+  for (int64_t u = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5; u < (int64_t)T * chunks; u += warps) {
+    const int t = (int)(u / chunks), c = (int)(u % chunks) * 32 + lane;
     const int p = (lane < K) ? loc[t * K + lane] : -1;
     const float wv = (lane < K) ? (topk_w != nullptr ? topk_w[t * K + lane] : 1.f) : 0.f;
     int rank = 0;
@@ -652,30 +655,27 @@ combine_kernel(const __nv_bfloat16* __restrict__ out2, const int32_t* __restrict
       const float ow = __shfl_sync(0xffffffffu, wv, k);
       if (o >= 0 && r == lane) { ps = o; ws = ow; }
     }
-    for (int c0 = 0; c0 < vec_per_row; c0 += 32) {       // warp-uniform trip count: the shuffles need every lane
-      const int c = c0 + lane;
-      const bool active = c < vec_per_row;
-      float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
-      for (int it = 0; it < n; ++it) {
-        const int pos = __shfl_sync(0xffffffffu, ps, it);
-        const float wt = __shfl_sync(0xffffffffu, ws, it);
-        if (active) {
-          const uint4 u = *reinterpret_cast<const uint4*>(out2 + (int64_t)pos * H + c * 8);
-          const __nv_bfloat16* d = reinterpret_cast<const __nv_bfloat16*>(&u);
+    const bool active = c < vec_per_row;
+    float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+    for (int it = 0; it < n; ++it) {              // warp-uniform trip count: the shuffles need every lane
+      const int pos = __shfl_sync(0xffffffffu, ps, it);
+      const float wt = __shfl_sync(0xffffffffu, ws, it);
+      if (active) {
+        const uint4 v = *reinterpret_cast<const uint4*>(out2 + (int64_t)pos * H + c * 8);
+        const __nv_bfloat16* d = reinterpret_cast<const __nv_bfloat16*>(&v);
 #pragma unroll
-          for (int i = 0; i < 8; ++i) {
-            const float contrib = __bfloat162float(__float2bfloat16_rn(__bfloat162float(d[i]) * wt));
-            acc[i] = __bfloat162float(__float2bfloat16_rn(acc[i] + contrib));
-          }
+        for (int i = 0; i < 8; ++i) {
+          const float contrib = __bfloat162float(__float2bfloat16_rn(__bfloat162float(d[i]) * wt));
+          acc[i] = __bfloat162float(__float2bfloat16_rn(acc[i] + contrib));
         }
       }
-      if (active) {
-        uint4 o;
-        __nv_bfloat16* ob = reinterpret_cast<__nv_bfloat16*>(&o);
+    }
+    if (active) {
+      uint4 o;
+      __nv_bfloat16* ob = reinterpret_cast<__nv_bfloat16*>(&o);
 #pragma unroll
-        for (int i = 0; i < 8; ++i) ob[i] = __float2bfloat16_rn(acc[i]);
-        *reinterpret_cast<uint4*>(y + (int64_t)t * H + c * 8) = o;
-      }
+      for (int i = 0; i < 8; ++i) ob[i] = __float2bfloat16_rn(acc[i]);
+      *reinterpret_cast<uint4*>(y + (int64_t)t * H + c * 8) = o;
     }
   }
 }
@@ -684,7 +684,8 @@ int launch_combine(const void* out2, const int32_t* loc, const float* topk_w, vo
                    cudaStream_t st) {
   B200_CHECK_ARG(H % 8 == 0 && K <= kMaxTopk, "combine: H %% 8 != 0 or K > %d", kMaxTopk);
   if (T == 0) return 0;
-  const int blocks = (int)std::min<int64_t>(((int64_t)T + 7) / 8, (int64_t)device_sm_count() * 16);
+  const int64_t units = (int64_t)T * ((H / 8 + 31) / 32);          // warps of work
+  const int blocks = (int)std::min<int64_t>((units + 7) / 8, (int64_t)device_sm_count() * 16);
   B200_CHECK_CUDA(launch_chained(combine_kernel, dim3(blocks), dim3(256), 0, st, (const __nv_bfloat16*)out2, loc,
                                  topk_w, (__nv_bfloat16*)y, T, K, H));
   return 0;

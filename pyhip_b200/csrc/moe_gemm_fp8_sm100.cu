@@ -325,7 +325,7 @@ __global__ void __launch_bounds__(kThreads, 1) moe_grouped_gemm_fp8_kernel(const
                   // fused combine: y[token] += bf16(row * routing weight), 16 bytes per reduction
                   // (the reference's weighted atomic epilogue, src/contrib/moe.py:703-787)
                   const uint32_t id = p.sorted_ids[r0 + n];
-                  const float wr = p.sorted_w[r0 + n];
+                  const float wr = p.sorted_w != nullptr ? p.sorted_w[r0 + n] : 1.f;   // null: applied upstream
                   const __nv_bfloat162* b2 = reinterpret_cast<const __nv_bfloat162*>(&val);
                   uint32_t o[4];
   #pragma unroll
@@ -585,7 +585,7 @@ int launch_grouped_gemm_fp8(const GemmArgs& a, cudaStream_t st) {
   p.out2 = (__nv_bfloat16*)a.out2;
   p.sorted_w = a.sorted_w; p.bias = a.bias; p.y = a.gateup ? nullptr : (__nv_bfloat16*)a.y;
   p.weight_stage1 = (a.gateup && a.weight_stage1) ? 1 : 0;
-  B200_CHECK_ARG((p.y == nullptr && p.weight_stage1 == 0) || a.sorted_w != nullptr, "fp8 grouped gemm: routing weights missing");
+  B200_CHECK_ARG(p.weight_stage1 == 0 || a.sorted_w != nullptr, "fp8 grouped gemm: routing weights missing");
   B200_CHECK_ARG(((uintptr_t)p.y & 15) == 0, "fp8 grouped gemm: fused combine needs a 16-byte aligned output");
   if (a.gateup && a.h_out == nullptr)
     B200_CHECK_ARG(a.out_kp == a.rows && a.oq && a.osf, "fp8 gate-up: fused output buffers missing");

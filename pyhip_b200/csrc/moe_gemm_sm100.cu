@@ -438,7 +438,7 @@ moe_grouped_gemm_kernel(const __grid_constant__ GemmParams p) {
         }
         // routing weight of the chunk's token columns (lane n holds column c0 + n)
         float my_w = 1.f;
-        if (col_weights) my_w = p.sorted_w[min(r0 + c0 + (lane & 15), r0 + B - 1)];
+        if (col_weights && p.sorted_w != nullptr) my_w = p.sorted_w[min(r0 + c0 + (lane & 15), r0 + B - 1)];
         if (GATEUP) {
           if (!fused) {
             my_id = p.sorted_ids[min(r0 + c0 + lane, r0 + B - 1)];
@@ -656,7 +656,7 @@ int launch_grouped_gemm(const GemmArgs& a, cudaStream_t st) {
   p.out2 = (__nv_bfloat16*)a.out2;
   p.sorted_w = a.sorted_w; p.bias = a.bias; p.y = a.gateup ? nullptr : (__nv_bfloat16*)a.y;
   p.weight_stage1 = (a.gateup && a.weight_stage1) ? 1 : 0;
-  B200_CHECK_ARG((p.y == nullptr && p.weight_stage1 == 0) || a.sorted_w != nullptr, "grouped gemm: routing weights missing");
+  B200_CHECK_ARG(p.weight_stage1 == 0 || a.sorted_w != nullptr, "grouped gemm: routing weights missing");
   B200_CHECK_ARG(p.y == nullptr || (a.rows % 2 == 0 && ((uintptr_t)p.y & 3) == 0), "grouped gemm: fused combine needs an even row length");
   if (a.gateup && a.h_out == nullptr)
     B200_CHECK_ARG(a.out_kp == (int)round_up64(a.rows, kTileK) && a.oq && a.osf,
