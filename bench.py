@@ -68,6 +68,8 @@ def parse():
     ap.add_argument("--combine", default="fused", choices=["fused", "gather"],
                     help="fused: weighted scatter-add in the down epilogue; gather: sorted rows + deterministic gather-sum")
     ap.add_argument("--act-terms", type=int, default=0, help="MXFP4 activation terms (0 = default 3; 1 = plain a4w4)")
+    ap.add_argument("--act-quant", default="terms", choices=["terms", "1x128"],
+                    help="FP8 weights: two e4m3 terms with E8M0 scales (default) or the per-token 1x128 fp32-scale format")
     ap.add_argument("--no-extras", action="store_true", help="only the headline workload (no sweep / prefill / config3 / config4)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-graph", action="store_true", help="time direct launches instead of CUDA-graph replays")
@@ -345,7 +347,7 @@ class Case:
         return x, tw, ids
 
 
-def measure_layer(case, T, args, steps, warmup, combine, act_terms=0, local=0, total_ms=None):
+def measure_layer(case, T, args, steps, warmup, combine, act_terms=0, local=0, total_ms=None, act_quant=0):
     """Whole-layer timing at T tokens: graph replay of the call's launches; batches whose expert set fits L2
     rotate over enough different routing sets that every step streams its weights from HBM."""
     import torch
@@ -360,7 +362,8 @@ def measure_layer(case, T, args, steps, warmup, combine, act_terms=0, local=0, t
     hits = [len(set(st[2].flatten().tolist())) for st in sets]
     B = pick_block(T, s.K, s.E, case.fmt)
     cm = _lib.COMBINE_FUSED if combine == "fused" else _lib.COMBINE_GATHER
-    plan = get_plan(T, s.K, s.E, s.E, s.H, s.I, B, 0, 7.0, dev, act_terms=act_terms, weight_format=case.fmt, combine_mode=cm)
+    plan = get_plan(T, s.K, s.E, s.E, s.H, s.I, B, 0, 7.0, dev, act_terms=act_terms, weight_format=case.fmt, combine_mode=cm,
+                    act_quant=act_quant)
     y = torch.empty(T, s.H, dtype=torch.bfloat16, device=dev)
 
     def one_round():
@@ -391,7 +394,8 @@ def measure_layer(case, T, args, steps, warmup, combine, act_terms=0, local=0, t
     layer_bytes = synth.algorithmic_bytes(T, s.H, s.I, hit, s.wq)
     return {"T": T, "ms_per_step": ms, "ms_per_step_min": r["min"] / n_sets, "ms_per_step_max": r["max"] / n_sets,
             "repeats": r["repeats"], "steps_per_region": rounds * n_sets, "tokens_per_s": T / (ms * 1e-3),
-            "experts_hit": hit, "block": B, "combine": combine, "act_terms": act_terms or (2 if case.fp8 else 3),
+            "experts_hit": hit, "block": B, "combine": combine,
+            "act_terms": (1 if act_quant else 2) if case.fp8 else (act_terms or 3),
             "launch": launch_mode, "launches_per_step": launches_per_call(T, s.K, s.E, cm),
             "routing_sets_rotated": n_sets,
             "layer_gbs": layer_bytes / (ms * 1e-3) / 1e9,
@@ -401,7 +405,7 @@ def measure_layer(case, T, args, steps, warmup, combine, act_terms=0, local=0, t
             "clocks": clocks}
 
 
-def measure_gemms(case, T, args, steps, warmup, act_terms=0):
+def measure_gemms(case, T, args, steps, warmup, act_terms=0, act_quant=0):
     """The two grouped GEMMs timed alone on the layer's own sorted / quantised inputs: returns the roofline record
     of the gate-up launch (the dominant kernel)."""
     import torch
@@ -410,7 +414,7 @@ def measure_gemms(case, T, args, steps, warmup, act_terms=0):
     x, tw, ids = (t.to(dev) for t in case.inputs(T, 0))
     hit = len(set(ids.flatten().tolist()))
     B = pick_block(T, s.K, s.E, case.fmt)
-    plan = get_plan(T, s.K, s.E, s.E, s.H, s.I, B, 0, 7.0, dev, act_terms=act_terms, weight_format=case.fmt)
+    plan = get_plan(T, s.K, s.E, s.E, s.H, s.I, B, 0, 7.0, dev, act_terms=act_terms, weight_format=case.fmt, act_quant=act_quant)
     plan.sort(ids, tw)
     plan.quant_input(x)
     k = max(3, min(steps, 200 if T <= 512 else 20))
@@ -438,13 +442,13 @@ def measure_gemms(case, T, args, steps, warmup, act_terms=0):
                 "peak_probe_tflops": probe, "frac_of_probe": ach / probe if probe else None,
                 "peak_probe_kind": "block-scaled MMAs from resident tiles on every SM, this run (the library's rate probe)",
                 "frac_of_bf16_" + bf16_kind.replace(" ", "_"): ach / bf16, "algorithmic_flops": gu_flops,
-                "mma_work_over_algorithmic": (2.0 if case.fp8 else float(act_terms or 3)), **common}
+                "mma_work_over_algorithmic": ((1.0 if act_quant else 2.0) if case.fp8 else float(act_terms or 3)), **common}
     achieved = gu_bytes / per_launch_s / 1e9
     return {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
             "peak_kind": peak_kind, "algorithmic_bytes": gu_bytes, **common}
 
 
-def measure_e2e(case, T, args, steps, warmup, combine, act_terms=0):
+def measure_e2e(case, T, args, steps, warmup, combine, act_terms=0, act_quant='terms'):
     import torch
     from pyhip_b200 import fused_moe
     s, dev = case.shape, case.dev
@@ -458,7 +462,7 @@ def measure_e2e(case, T, args, steps, warmup, combine, act_terms=0):
         tg = twh.to(dev, non_blocking=True)
         ig = idsh.to(dev, non_blocking=True)
         out = fused_moe(xg, w[0], w[2], tg, ig, quant_type=case.qt, w1_scale=w[1], w2_scale=w[3], combine=combine,
-                        act_terms=act_terms)
+                        act_terms=act_terms, act_quant=act_quant if case.fp8 else "terms")
         yh.copy_(out, non_blocking=True)
 
     r = time_repeated(step_e2e, steps, warmup, total_ms=min(args.repeat_ms, 500.0))
@@ -472,11 +476,12 @@ def run_single(args, dev, local):
     case = Case(args.workload, dev, args.experts)
     s = case.shape
     T = args.tokens or s.T
-    head = measure_layer(case, T, args, args.steps, args.warmup, args.combine, args.act_terms, local)
+    aq = 1 if (args.act_quant == '1x128' and case.fp8) else 0
+    head = measure_layer(case, T, args, args.steps, args.warmup, args.combine, args.act_terms, local, act_quant=aq)
     other = "gather" if args.combine == "fused" else "fused"
-    alt = measure_layer(case, T, args, args.steps, args.warmup, other, args.act_terms, local, total_ms=300.0)
-    e2e = measure_e2e(case, T, args, args.steps, args.warmup, args.combine, args.act_terms)
-    roofline = measure_gemms(case, T, args, args.steps, args.warmup, args.act_terms)
+    alt = measure_layer(case, T, args, args.steps, args.warmup, other, args.act_terms, local, total_ms=300.0, act_quant=aq)
+    e2e = measure_e2e(case, T, args, args.steps, args.warmup, args.combine, args.act_terms, args.act_quant)
+    roofline = measure_gemms(case, T, args, args.steps, args.warmup, args.act_terms, act_quant=aq)
     extras = {}
     default_run = not args.no_extras and args.workload == "gptoss_decode" and not args.tokens and not args.experts
     if default_run:
@@ -507,6 +512,13 @@ def run_single(args, dev, local):
             m["roofline"] = measure_gemms(c2, c2.shape.T, args, 10, 3, 0)
             m["dtype"] = c2.dtype_text(0)
             m["workload"] = f"{wl} H{c2.shape.H} I{c2.shape.I} E{c2.shape.E} top{c2.shape.K} T{c2.shape.T} {c2.shape.wq}"
+            if c2.fp8:
+                # the reference's own activation format beside the default: per-token 1x128 e4m3 with fp32 scales
+                m2 = measure_layer(c2, c2.shape.T, args, 10, 3, args.combine, 0, local, total_ms=300.0, act_quant=1)
+                m2["roofline"] = measure_gemms(c2, c2.shape.T, args, 10, 3, 0, act_quant=1)
+                m2["dtype"] = "fp8-e4m3 128x128-block weights x e4m3 activations with fp32 scales per 1x128, f32 accumulate"
+                m2["parity_oracle"] = "oracle that dequantises the same 1x128-quantised activations (cosine >= 0.9995)"
+                m["act_1x128"] = m2
             extras[key] = m
             del c2
             release_prepared()
@@ -584,7 +596,8 @@ def measure_ep(workload, args, rank, world, local, dev, dist, steps, warmup, tot
     E_local = E // world
     w_full = make_w(E_local, H, I, seed=rank, device=dev, distinct=min(distinct, E_local))
     layer = ep.ExpertParallelMoE(w_full[0], w_full[1], w_full[2], w_full[3], E, rank, world, quant_type=qt,
-                                 dispatch_chunks=args.ep_chunks or None, tokens_per_rank=T, combine=args.combine)
+                                 dispatch_chunks=args.ep_chunks or None, tokens_per_rank=T, combine=args.combine,
+                                 **({'act_quant': args.act_quant} if fp8 else {}))
     x = synth.make_hidden(T, H, rank)
     tw, ids = synth.make_routing(T, E, K, shape.routing, rank, skew_seed=0)
     xd, twd, idsd = x.to(dev), tw.to(dev), ids.to(dev)

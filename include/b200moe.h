@@ -153,6 +153,15 @@ int b200moe_quant_rows_e4m3(const void* src_bf16, int32_t src_mode, const uint32
                             const int32_t* num_valid_ids, int32_t T, int32_t K, int32_t Kd, int32_t B,
                             int64_t max_rows, void* q, void* sf, void* stream);
 
+/* The reference's own FP8 activation format (act_quant B200MOE_ACTQ_1X128): one e4m3 value per element with an
+ * fp32 scale = amax / 448 per row and 128 channels (1.0 for an all-zero block); stands where the reference calls
+ * aiter's per_1x128 quantiser with transpose_scale (src/contrib/fused_moe.py:276-281,375-381,449-456).
+ *   q: u8 [max_rows, Kd];  sf: f32 [max_rows / B][Kd / 128][B] -- the B token scales of one sorted block and
+ *   k-block are contiguous (the reference's transposed scale layout, per block). */
+int b200moe_quant_rows_fp8_1x128(const void* src_bf16, int32_t src_mode, const uint32_t* sorted_ids,
+                                 const int32_t* num_valid_ids, int32_t T, int32_t K, int32_t Kd, int32_t B,
+                                 int64_t max_rows, void* q, void* sf, void* stream);
+
 /* Gate-up grouped GEMM + activation: replaces moe_2stage_splitk(with_silu=True) /
  * moe_gemm_mxfp4(gate_up=True) (src/contrib/moe.py:362-702, src/contrib/moe_gemm_mxfp4.py:972-1290).
  * Consumes the quantised rows in workspace (xq), the canonical packed w1 [E,2I,H/2], its prepared

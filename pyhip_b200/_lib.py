@@ -59,7 +59,7 @@ EXPORTS = ["b200moe_version", "b200moe_last_error", "b200moe_workspace_layout",
            "b200moe_quant_rows", "b200moe_quant_rows_e4m3", "b200moe_gateup", "b200moe_down", "b200moe_combine",
            "b200moe_forward", "b200moe_forward_dyn", "b200moe_sort_align_dyn", "b200moe_sort_align_ws",
            "b200moe_sort_scratch_bytes", "b200moe_route_topk", "b200moe_forward_static", "b200moe_gather_sum", "b200moe_debug_probe",
-           "b200moe_forward_ex", "b200moe_static_status", "b200moe_ep_plan"]
+           "b200moe_forward_ex", "b200moe_static_status", "b200moe_ep_plan", "b200moe_quant_rows_fp8_1x128"]
 
 
 def build(force: bool = False, verbose: bool = False) -> pathlib.Path:
@@ -96,6 +96,7 @@ def lib() -> ctypes.CDLL:
     L.b200moe_sort_align.argtypes = [vp, vp, i32, i32, i32, i32, vp, vp, vp, vp, vp, vp, vp]
     L.b200moe_quant_rows.argtypes = [vp, i32, vp, vp, i32, i32, i32, i32, i32, i64, vp, vp, vp]
     L.b200moe_quant_rows_e4m3.argtypes = [vp, i32, vp, vp, i32, i32, i32, i32, i64, vp, vp, vp]
+    L.b200moe_quant_rows_fp8_1x128.argtypes = [vp, i32, vp, vp, i32, i32, i32, i32, i64, vp, vp, vp]
     L.b200moe_gateup.argtypes = [sp, wp, vp, vp, vp, vp, vp, vp]
     L.b200moe_down.argtypes = [sp, wp, vp, vp, vp, vp, vp, vp]
     L.b200moe_forward_ex.argtypes = [sp, wp, vp, ctypes.POINTER(Io), vp]

@@ -39,7 +39,10 @@ static int check_shape(const b200moe_shape* s) {
   B200_CHECK_ARG(s->act_terms >= 0 && s->act_terms <= 4, "act_terms=%d not in [0,4]", s->act_terms);
   B200_CHECK_ARG(s->combine_mode == B200MOE_COMBINE_GATHER || s->combine_mode == B200MOE_COMBINE_FUSED,
                  "combine_mode %d unknown", s->combine_mode);
-  B200_CHECK_ARG(s->act_quant == B200MOE_ACTQ_TERMS, "act_quant %d unknown", s->act_quant);
+  B200_CHECK_ARG(s->act_quant == B200MOE_ACTQ_TERMS || s->act_quant == B200MOE_ACTQ_1X128, "act_quant %d unknown",
+                 s->act_quant);
+  B200_CHECK_ARG(s->act_quant == B200MOE_ACTQ_TERMS || s->weight_format == B200MOE_W_FP8_128,
+                 "act_quant 1x128 belongs to the FP8 128x128 weight format (MXFP4 weights take act_terms)");
   B200_CHECK_ARG(s->doweight_stage1 == 0 || s->doweight_stage1 == 1, "doweight_stage1=%d must be 0 or 1",
                  s->doweight_stage1);
   return 0;
@@ -154,6 +157,18 @@ int b200moe_sort_align_dyn(const int32_t* topk_ids, const float* topk_weight, in
                          sorted_weights, sorted_expert_ids, num_valid_ids, loc, nullptr, 0, stream);
 }
 
+int b200moe_quant_rows_fp8_1x128(const void* src_bf16, int32_t src_mode, const uint32_t* sorted_ids,
+                                 const int32_t* num_valid_ids, int32_t T, int32_t K, int32_t Kd, int32_t B,
+                                 int64_t max_rows, void* q, void* sf, void* stream) {
+  B200_CHECK_ARG(src_mode == 0 || src_mode == 1, "quant_rows: src_mode=%d", src_mode);
+  B200_CHECK_ARG(sorted_ids && num_valid_ids && q && sf, "quant_rows: NULL pointer");
+  B200_CHECK_ARG(T == 0 || src_bf16, "quant_rows: NULL source");
+  B200_CHECK_ARG(((uintptr_t)src_bf16 & 15) == 0 && ((uintptr_t)q & 15) == 0,
+                 "quant_rows: source and destination must be 16-byte aligned");
+  return launch_quant_rows_fp8_1x128(src_bf16, src_mode, sorted_ids, num_valid_ids, T, K, Kd, B, max_rows, q, sf,
+                                     nullptr, 0, (cudaStream_t)stream);
+}
+
 int b200moe_sort_scratch_bytes(int32_t E_route, int64_t* bytes) {
   B200_CHECK_ARG(E_route >= 1 && bytes != nullptr, "sort_scratch_bytes: bad argument");
   *bytes = sort_scratch_bytes(E_route);
@@ -194,6 +209,7 @@ int b200moe_quant_rows_e4m3(const void* src_bf16, int32_t src_mode, const uint32
 
 static void fill_common(GemmArgs& g, const b200moe_shape* s, const b200moe_workspace* ws, uint8_t* base) {
   g.N = s->B;
+  g.act_quant = s->act_quant;
   g.NT = terms_of(s);
   g.E = s->E;
   g.topk = s->K;
@@ -322,7 +338,7 @@ static int forward_impl(const b200moe_shape* s, const b200moe_workspace* ws, voi
   int32_t* loc = (int32_t*)(base + ws->off_loc);
   int rc;
   if (sort_quant_small_ok(s->T, s->K, s->E_route)) {
-    rc = launch_sort_quant_small(fp8w ? 1 : 0, io->x_bf16, io->topk_ids, io->topk_weight, s->T, s->K, s->E_route, s->B,
+    rc = launch_sort_quant_small(fp8w ? (s->act_quant ? 2 : 1) : 0, io->x_bf16, io->topk_ids, io->topk_weight, s->T, s->K, s->E_route, s->B,
                                  io->expert_mask, io->num_local_tokens, sorted_ids, sorted_w, sorted_e, num_valid, loc,
                                  s->H, terms_of(s), ws->max_rows, base + ws->off_xq, base + ws->off_xsf, zero_ptr,
                                  zero_bytes, (cudaStream_t)stream);
@@ -332,7 +348,10 @@ static int forward_impl(const b200moe_shape* s, const b200moe_workspace* ws, voi
                          io->num_local_tokens, sorted_ids, sorted_w, sorted_e, num_valid, loc,
                          base + ws->off_sort_scratch, sort_scratch_bytes(s->E_route), stream);
     if (rc) return rc;
-    if (fp8w)
+    if (fp8w && s->act_quant)
+      rc = launch_quant_rows_fp8_1x128(io->x_bf16, 0, sorted_ids, num_valid, s->T, s->K, s->H, s->B, ws->max_rows,
+                                       base + ws->off_xq, base + ws->off_xsf, zero_ptr, zero_bytes, (cudaStream_t)stream);
+    else if (fp8w)
       rc = launch_quant_rows_e4m3(io->x_bf16, 0, sorted_ids, num_valid, s->T, s->K, s->H, s->B, ws->max_rows,
                                   base + ws->off_xq, base + ws->off_xsf, zero_ptr, zero_bytes, (cudaStream_t)stream);
     else

@@ -70,6 +70,18 @@ __device__ __forceinline__ void ffma2_scaled(float& a0, float& a1, float s, uint
       : "r"(v0), "r"(v1), "f"(s));
 }
 
+// (a0, a1) += (s0, s1) * (v0, v1): the same with one scale per element
+__device__ __forceinline__ void ffma2_pair(float& a0, float& a1, float s0, float s1, uint32_t v0, uint32_t v1) {
+  asm("{\n\t.reg .b64 a, v, c;\n\t"
+      "mov.b64 a, {%0, %1};\n\t"
+      "mov.b64 v, {%2, %3};\n\t"
+      "mov.b64 c, {%4, %5};\n\t"
+      "fma.rn.f32x2 a, v, c, a;\n\t"
+      "mov.b64 {%0, %1}, a;\n\t}"
+      : "+f"(a0), "+f"(a1)
+      : "r"(v0), "r"(v1), "f"(s0), "f"(s1));
+}
+
 // descriptor halves: the high word is constant per layout, the low word carries the address
 constexpr uint32_t kDescHiSw = (1024u >> 4) | (1u << 14) | (2u << 29);   // SBO 1024, version 1, 128-byte swizzle
 constexpr uint32_t kDescHiSf = (128u >> 4) | (1u << 14);                   // SBO 128, version 1, no swizzle

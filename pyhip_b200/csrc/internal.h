@@ -67,7 +67,8 @@ int launch_route_topk(const float* logits, int T, int E, int K, int scoring, int
 int launch_quant_rows(const void* src, int src_mode, const uint32_t* sorted_ids, const int32_t* num_valid,
                       int T, int K, int Kd, int B, int NT, int64_t max_rows, void* q, void* sf, void* zero_ptr,
                       int64_t zero_bytes, cudaStream_t st);
-// sort/align + input quantiser in one launch for decode-sized batches (fmt 0: packed-FP4 terms, 1: two e4m3 terms)
+// sort/align + input quantiser in one launch for decode-sized batches
+// (fmt 0: packed-FP4 terms, 1: two e4m3 terms, 2: e4m3 with fp32 scales per 1x128)
 bool sort_quant_small_ok(int T, int K, int E);
 int launch_sort_quant_small(int fmt, const void* x, const int32_t* ids, const float* w, int T, int K, int E, int B,
                             const int32_t* mask, const int32_t* num_local, uint32_t* sorted_ids, float* sorted_w,
@@ -111,6 +112,7 @@ struct GemmArgs {
   const float* bias;       // fp32 per-expert bias: gate-up [E, 2*rows], down [E, rows]; or null
   void* y;                 // down: zeroed bf16 [T, rows]; non-null selects the fused weighted scatter-add epilogue
   int weight_stage1;       // gate-up: apply the routing weight to h
+  int act_quant;           // FP8 kernel: 0 = two e4m3 terms with E8M0 scales, 1 = one e4m3 term with fp32 scales per 1x128
 };
 int launch_grouped_gemm(const GemmArgs& a, cudaStream_t st);
 // FP8 128x128-block variant (moe_gemm_fp8_sm100.cu): w_data = e4m3 bytes [E, parts*rows, Kd], w_scale = fp32
@@ -119,6 +121,9 @@ int launch_grouped_gemm_fp8(const GemmArgs& a, cudaStream_t st);
 int launch_quant_rows_e4m3(const void* src, int src_mode, const uint32_t* sorted_ids, const int32_t* num_valid,
                            int T, int K, int Kd, int B, int64_t max_rows, void* q, void* sf, void* zero_ptr,
                            int64_t zero_bytes, cudaStream_t st);
+int launch_quant_rows_fp8_1x128(const void* src, int src_mode, const uint32_t* sorted_ids, const int32_t* num_valid,
+                                int T, int K, int Kd, int B, int64_t max_rows, void* q, void* sf, void* zero_ptr,
+                                int64_t zero_bytes, cudaStream_t st);
 int encode_map_sw(CUtensorMap* map, CUtensorMapDataType type, int rank, const void* base, const cuuint64_t* dims,
                   const cuuint64_t* strides, const cuuint32_t* box, CUtensorMapSwizzle swizzle,
                   CUtensorMapL2promotion promo, const char* what);

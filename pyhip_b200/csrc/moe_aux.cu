@@ -414,13 +414,49 @@ __device__ __forceinline__ void quant_unit_e4m3(const __nv_bfloat16* src, int64_
   }
 }
 
+// Per-token, per-128-channel e4m3 with an fp32 scale = amax / 448 (1.0 for an all-zero block): the reference's
+// per_1x128 activation format (src/contrib/fused_moe.py:276-281,375-381).  Four neighbouring threads own the four
+// 32-element quarters of a 128-block and share its amax through shuffles, so every lane of the warp must call this
+// (`live` = this thread has a unit).  q [max_rows, Kd] bytes; scales fp32 [blocks][Kd/128][B] (one contiguous run
+// of B token scales per sorted block and k-block, the order the GEMM's producer copies them in).
+__device__ __forceinline__ void quant_unit_fp8_1x128(const __nv_bfloat16* src, int64_t srow, int j, int64_t r,
+                                                     const QuantGeom& g, bool live) {
+  float x[32];
+  if (live) {
+    load_block32(src + srow * g.Kd + j * 32, x);
+  } else {
+#pragma unroll
+    for (int i = 0; i < 32; ++i) x[i] = 0.f;
+  }
+  float amax = 0.f;
+#pragma unroll
+  for (int i = 0; i < 32; ++i) amax = fmaxf(amax, fabsf(x[i]));
+  amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
+  amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 2));
+  const float scale = amax > 0.f ? __fdiv_rn(amax, 448.f) : 1.f;
+  uint32_t w[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+#pragma unroll
+  for (int i = 0; i < 32; i += 2) {
+    const __nv_fp8x2_storage_t pk = __nv_cvt_float2_to_fp8x2(make_float2(__fdiv_rn(x[i], scale), __fdiv_rn(x[i + 1], scale)),
+                                                              __NV_SATFINITE, __NV_E4M3);
+    w[i >> 2] |= (uint32_t)pk << ((i & 2) * 8);
+  }
+  if (live) {
+    uint4* dst = reinterpret_cast<uint4*>(g.q + r * g.Kd + j * 32);
+    dst[0] = make_uint4(w[0], w[1], w[2], w[3]);
+    dst[1] = make_uint4(w[4], w[5], w[6], w[7]);
+    if ((j & 3) == 0)
+      reinterpret_cast<float*>(g.sf)[((r / g.B) * (g.Kd / 128) + (j >> 2)) * g.B + (int)(r % g.B)] = scale;
+  }
+}
+
 // grid-stride zero fill in 16-byte vectors (the output buffer of the fused combine)
 __device__ __forceinline__ void zero_fill(uint4* ptr, int64_t nvec) {
   for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < nvec; i += (int64_t)gridDim.x * blockDim.x)
     ptr[i] = make_uint4(0, 0, 0, 0);
 }
 
-template <int FMT>    // 0: packed-FP4 terms, 1: two e4m3 terms
+template <int FMT>    // 0: packed-FP4 terms, 1: two e4m3 terms, 2: e4m3 with fp32 scales per 1x128
 __global__ void __launch_bounds__(256)
 quant_rows_kernel(const __nv_bfloat16* __restrict__ src, int src_mode, const uint32_t* __restrict__ sorted_ids,
                   const int32_t* __restrict__ num_valid, int T, int K, QuantGeom g, uint4* zero_ptr, int64_t zero_vec) {
@@ -428,18 +464,23 @@ quant_rows_kernel(const __nv_bfloat16* __restrict__ src, int src_mode, const uin
   grid_dep_launch();
   grid_dep_wait();
   zero_fill(zero_ptr, zero_vec);
-  const int64_t rows_live = min((int64_t)num_valid[0], g.max_rows);
-  for (int64_t u = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; u < rows_live * nb;
-       u += (int64_t)gridDim.x * blockDim.x) {
-    const int64_t r = u / nb;
-    const int j = (int)(u % nb);
+  const int64_t total = min((int64_t)num_valid[0], g.max_rows) * nb;
+  // block-uniform trip count: the 1x128 format shares a block maximum across four lanes with shuffles
+  for (int64_t base = (int64_t)blockIdx.x * blockDim.x; base < total; base += (int64_t)gridDim.x * blockDim.x) {
+    const int64_t u = base + threadIdx.x;
+    const int64_t r = min(u, total - 1) / nb;
+    const int j = (int)(min(u, total - 1) % nb);
     const uint32_t id = sorted_ids[r];
     const int tok = (int)(id & 0xFFFFFFu), kk = (int)(id >> 24);
     // padding rows of a block are left unwritten: every token column of the GEMMs depends on its own row
     // only, and no kernel reads the columns of padding rows
-    if (kk >= K || tok >= T) continue;
+    const bool live = u < total && kk < K && tok < T;
     const int64_t srow = (src_mode == 0) ? (int64_t)tok : ((int64_t)tok * K + kk);
-    if (FMT == 0) quant_unit_fp4(src, srow, j, r, g); else quant_unit_e4m3(src, srow, j, r, g);
+    if (FMT == 2) {
+      quant_unit_fp8_1x128(src, srow, j, r, g, live);
+    } else if (live) {
+      if (FMT == 0) quant_unit_fp4(src, srow, j, r, g); else quant_unit_e4m3(src, srow, j, r, g);
+    }
   }
 }
 
@@ -470,6 +511,20 @@ int launch_quant_rows_e4m3(const void* src, int src_mode, const uint32_t* sorted
   B200_CHECK_ARG(zero_bytes % 16 == 0 && ((uintptr_t)zero_ptr & 15) == 0, "quant_rows: zero region must be 16-byte aligned");
   QuantGeom g = {Kd, Kd, B, 2, 128, max_rows, (uint8_t*)q, (uint8_t*)sf};
   B200_CHECK_CUDA(launch_chained(quant_rows_kernel<1>, dim3(quant_grid(max_rows * (Kd / 32))), dim3(256), 0, st,
+                                 reinterpret_cast<const __nv_bfloat16*>(src), src_mode, sorted_ids, num_valid, T, K, g,
+                                 (uint4*)zero_ptr, zero_bytes / 16));
+  return 0;
+}
+
+int launch_quant_rows_fp8_1x128(const void* src, int src_mode, const uint32_t* sorted_ids, const int32_t* num_valid,
+                                int T, int K, int Kd, int B, int64_t max_rows, void* q, void* sf, void* zero_ptr,
+                                int64_t zero_bytes, cudaStream_t st) {
+  B200_CHECK_ARG(B >= 16 && B <= 96 && B % 16 == 0, "quant_rows (1x128): B=%d is not a multiple of 16 in [16,96]", B);
+  B200_CHECK_ARG(Kd % 128 == 0, "quant_rows (1x128): Kd=%d must be a multiple of 128", Kd);
+  B200_CHECK_ARG(zero_bytes % 16 == 0 && ((uintptr_t)zero_ptr & 15) == 0 && ((uintptr_t)sf & 15) == 0,
+                 "quant_rows: zero region / scales must be 16-byte aligned");
+  QuantGeom g = {Kd, Kd, B, 1, 128, max_rows, (uint8_t*)q, (uint8_t*)sf};
+  B200_CHECK_CUDA(launch_chained(quant_rows_kernel<2>, dim3(quant_grid(max_rows * (Kd / 32))), dim3(256), 0, st,
                                  reinterpret_cast<const __nv_bfloat16*>(src), src_mode, sorted_ids, num_valid, T, K, g,
                                  (uint4*)zero_ptr, zero_bytes / 16));
   return 0;
@@ -583,11 +638,16 @@ sort_quant_small_kernel(const __nv_bfloat16* __restrict__ x, const int32_t* __re
   __syncthreads();
   // quantise: one unit = (pair, 32-element block of its token's row)
   const int nb = g.KP / 32;
-  for (int u = blockIdx.x * 256 + tid; u < P * nb; u += gridDim.x * 256) {
+  for (int base = blockIdx.x * 256; base < P * nb; base += gridDim.x * 256) {     // block-uniform trip count
+    const int u = min(base + tid, P * nb - 1);
     const int i = u / nb, j = u - i * nb;
     const int r = pair_pos[i];
-    if (r < 0) continue;
-    if (FMT == 0) quant_unit_fp4(x, i / K, j, r, g); else quant_unit_e4m3(x, i / K, j, r, g);
+    const bool live = base + tid < P * nb && r >= 0;
+    if (FMT == 2) {
+      quant_unit_fp8_1x128(x, i / K, j, max(r, 0), g, live);
+    } else if (live) {
+      if (FMT == 0) quant_unit_fp4(x, i / K, j, r, g); else quant_unit_e4m3(x, i / K, j, r, g);
+    }
   }
 }
 
@@ -609,10 +669,15 @@ int launch_sort_quant_small(int fmt, const void* x, const int32_t* ids, const fl
                                    sorted_e, num_valid, loc, g, (uint4*)zero_ptr, zero_bytes / 16));
   } else {
     B200_CHECK_ARG(Kd % 128 == 0 && B <= 96, "sort_quant_small (e4m3): Kd %d / B %d", Kd, B);
-    QuantGeom g = {Kd, Kd, B, 2, 128, max_rows, (uint8_t*)q, (uint8_t*)sf};
-    B200_CHECK_CUDA(launch_chained(sort_quant_small_kernel<1>, dim3(quant_grid((int64_t)T * K * (Kd / 32))), dim3(256), 0,
-                                   st, (const __nv_bfloat16*)x, ids, w, T, K, E, mask, num_local, sorted_ids, sorted_w,
-                                   sorted_e, num_valid, loc, g, (uint4*)zero_ptr, zero_bytes / 16));
+    QuantGeom g = {Kd, Kd, B, fmt == 1 ? 2 : 1, 128, max_rows, (uint8_t*)q, (uint8_t*)sf};
+    if (fmt == 1)
+      B200_CHECK_CUDA(launch_chained(sort_quant_small_kernel<1>, dim3(quant_grid((int64_t)T * K * (Kd / 32))), dim3(256), 0,
+                                     st, (const __nv_bfloat16*)x, ids, w, T, K, E, mask, num_local, sorted_ids, sorted_w,
+                                     sorted_e, num_valid, loc, g, (uint4*)zero_ptr, zero_bytes / 16));
+    else
+      B200_CHECK_CUDA(launch_chained(sort_quant_small_kernel<2>, dim3(quant_grid((int64_t)T * K * (Kd / 32))), dim3(256), 0,
+                                     st, (const __nv_bfloat16*)x, ids, w, T, K, E, mask, num_local, sorted_ids, sorted_w,
+                                     sorted_e, num_valid, loc, g, (uint4*)zero_ptr, zero_bytes / 16));
   }
   return 0;
 }

@@ -15,6 +15,12 @@
 //     and add into fp32 registers -- the two-level accumulation the reference's FP8 kernel does
 //     with its FIFO + fmac (src/contrib/moe_gemm_8wave.py:386-405).  Two TMEM accumulator buffers
 //     let the next k-block's MMAs run under the promotion of the current one.
+//   * act_quant 1x128 (the reference's own activation format: one e4m3 value per element with an fp32
+//     scale per token and 128 channels, src/contrib/fused_moe.py:375-381): a single activation term, all
+//     E8M0 scales of the MMA are 1.0, and the promotion multiplies every token column by
+//     sA[token, k-block] * sB[row block, k-block] (src/contrib/moe_gemm_8wave.py:386-405 folds the two the
+//     same way).  The four scale-loader warps form those products once per k-block into a small
+//     shared-memory table that the epilogue warps read with broadcast loads.
 #include <algorithm>
 #include <mutex>
 
@@ -61,6 +67,7 @@ struct Params {
   const float* bias;       // per-expert bias: gate-up [E, 2*rows] (gate then up), down [E, rows]; or null
   __nv_bfloat16* y;        // down, fused combine: zeroed [T, rows] output accumulated with bf16x2 reductions; or null
   int weight_stage1;       // gate-up: multiply h by the routing weight
+  int aq;                  // 1: single e4m3 activation term with fp32 scales per (token, 128 channels)
 };
 
 struct SmemCtl {
@@ -74,6 +81,7 @@ struct SmemCtl {
   uint32_t tmem_base;
   uint32_t abort_word;
   float wscale[2][2][kMaxKB];   // [tile parity][weight tile][k-block]
+  alignas(16) float cscale[2][2][96];       // read as float4; 1x128 mode: [ring slot][weight tile][token column] = sA * sB of one k-block
 };
 static_assert(sizeof(SmemCtl) <= kCtlBytes, "control region");
 
@@ -81,11 +89,11 @@ struct StageGeom {
   int a_bytes, b_bytes, sfb_bytes, stage_bytes;
   uint32_t tx_bytes;
 };
-__host__ __device__ inline StageGeom stage_geom(int B) {
+__host__ __device__ inline StageGeom stage_geom(int B, int aq) {
   StageGeom g;
   g.a_bytes = 2 * kATileBytes;
-  g.b_bytes = kTerms * B * kTileK;
-  g.sfb_bytes = kTerms * kSfChunk;       // one chunk per term (virtual row = term*128 + r)
+  g.b_bytes = (aq ? 1 : kTerms) * B * kTileK;
+  g.sfb_bytes = aq ? B * 4 : kTerms * kSfChunk;   // fp32 per token, or one E8M0 chunk per term (virtual row = term*128 + r)
   g.stage_bytes = (g.a_bytes + g.b_bytes + g.sfb_bytes + 1023) & ~1023;
   g.tx_bytes = (uint32_t)(g.a_bytes + g.b_bytes + g.sfb_bytes);
   return g;
@@ -98,8 +106,9 @@ __global__ void __launch_bounds__(kThreads, 1) moe_grouped_gemm_fp8_kernel(const
   SmemCtl* ctl = reinterpret_cast<SmemCtl*>(smem);
   const uint32_t stage0 = smem_u32(smem) + kCtlBytes;
   const int B = p.B;
-  const StageGeom geo = stage_geom(B);
+  const StageGeom geo = stage_geom(B, p.aq);
   const int S = p.stages;
+  const int nterms = p.aq ? 1 : kTerms;
   const int acc_cols = 2 * B;                  // two weight tiles x B token columns, per accumulator buffer
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -108,7 +117,8 @@ __global__ void __launch_bounds__(kThreads, 1) moe_grouped_gemm_fp8_kernel(const
   if (threadIdx.x == 0) {
     for (int s = 0; s < S; ++s) {
       mbar_init(smem_u32(&ctl->full[s]), 1);
-      mbar_init(smem_u32(&ctl->empty[s]), 2);      // one commit per MMA warp
+      // one commit per MMA warp; in 1x128 mode the four scale-loader warps read the stage's token scales too
+      mbar_init(smem_u32(&ctl->empty[s]), p.aq ? 6 : 2);
     }
     for (int a = 0; a < 2; ++a) {
       for (int h = 0; h < 2; ++h) {
@@ -116,7 +126,7 @@ __global__ void __launch_bounds__(kThreads, 1) moe_grouped_gemm_fp8_kernel(const
         mbar_init(smem_u32(&ctl->tmem_empty[2 * a + h]), 8);
       }
       mbar_init(smem_u32(&ctl->sf_full[a]), 4);
-      mbar_init(smem_u32(&ctl->sf_empty[a]), 2);
+      mbar_init(smem_u32(&ctl->sf_empty[a]), p.aq ? 8 : 2);     // consumers: the MMA warps, or (1x128) the epilogue warps
     }
     mbar_init(smem_u32(&ctl->stg_full), 8);
     mbar_init(smem_u32(&ctl->stg_empty), 1);
@@ -211,7 +221,10 @@ __global__ void __launch_bounds__(kThreads, 1) moe_grouped_gemm_fp8_kernel(const
           ok = ok && mbar_wait(smem_u32(&ctl->full[stage]), phase, abort_word, 0x300 + stage);
           PROF_ADD(t_full, c1);
           const long long c2 = PROF_NOW();
-          ok = ok && mbar_wait(smem_u32(&ctl->sf_full[sf_buf]), sf_phase, abort_word, 0x500 + sf_buf);
+          // 1x128 mode: the MMA's scale columns are constants written once by the scale-loader warps before their
+          // first table is published, so only the very first MMA has to wait for that
+          if (!p.aq || (w == (int)blockIdx.x && kb == 0))
+            ok = ok && mbar_wait(smem_u32(&ctl->sf_full[sf_buf]), sf_phase, abort_word, 0x500 + sf_buf);
           PROF_ADD(t_sf, c2);
           if (!ok) break;
           tc_fence_after_sync();
@@ -226,10 +239,11 @@ __global__ void __launch_bounds__(kThreads, 1) moe_grouped_gemm_fp8_kernel(const
             for (int k = 0; k < 4; ++k) {
   #pragma unroll
               for (int t = 0; t < kTerms; ++t)
-                umma_mxf8(d0, a_lo + 2 * k, b_lo + t * term_lo + 2 * k, idesc[k], sfa_t, sfb_t + 4 * t, (k | t) != 0);
+                if (t < nterms)
+                  umma_mxf8(d0, a_lo + 2 * k, b_lo + t * term_lo + 2 * k, idesc[k], sfa_t, sfb_t + 4 * t, (k | t) != 0);
             }
             tc_commit(smem_u32(&ctl->empty[stage]));
-            tc_commit(smem_u32(&ctl->sf_empty[sf_buf]));
+            if (!p.aq) tc_commit(smem_u32(&ctl->sf_empty[sf_buf]));
             tc_commit(smem_u32(&ctl->tmem_full[2 * acc + part]));
           }
           __syncwarp();
@@ -265,8 +279,10 @@ __global__ void __launch_bounds__(kThreads, 1) moe_grouped_gemm_fp8_kernel(const
             nvalid += __popc(__ballot_sync(0xffffffffu, (int)(id >> 24) < p.topk && (int)(id & 0xFFFFFFu) < p.T));
           }
           if (!mbar_wait(smem_u32(&ctl->stg_full), ph, abort_word, 0x900)) break;
-          for (int unit = lane; unit < nvalid * 4; unit += 32) {
-            const int n = unit >> 2, q = unit & 3;
+          for (int unit0 = 0; unit0 < nvalid * 4; unit0 += 32) {       // warp-uniform trip count (shuffles below)
+            const int unit = unit0 + lane;
+            const bool live = unit < nvalid * 4;
+            const int n = min(unit, nvalid * 4 - 1) >> 2, q = unit & 3;
             float x[32];
   #pragma unroll
             for (int v4 = 0; v4 < 4; ++v4) {
@@ -285,14 +301,37 @@ __global__ void __launch_bounds__(kThreads, 1) moe_grouped_gemm_fp8_kernel(const
   #pragma unroll
               for (int i = 0; i < 32; ++i) x[i] = bf16r(x[i] * wr);
             }
+            if (p.aq) {
+              // one fp32 scale per row and 128 features = this tile: the row's four lanes share the maximum
+              float amax = 0.f;
   #pragma unroll
-            for (int t = 0; t < kTerms; ++t) {
-              uint4 q0, q1;
-              const int ex = (t + 1 < kTerms) ? quant_block32_e4m3<true>(x, q0, q1) : quant_block32_e4m3<false>(x, q0, q1);
-              uint4* dst = reinterpret_cast<uint4*>(p.oq + t * p.oq_term_stride + r * p.out_k + m * kTileM + q * 32);
-              dst[0] = q0;
-              dst[1] = q1;
-              p.osf[act_sf_index(b, m, p.out_kb, B, kTerms, 128, t, n, q)] = (uint8_t)ex;
+              for (int i = 0; i < 32; ++i) amax = fmaxf(amax, fabsf(x[i]));
+              amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
+              amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 2));
+              const float scale = amax > 0.f ? __fdiv_rn(amax, 448.f) : 1.f;
+              uint32_t wq[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+  #pragma unroll
+              for (int i = 0; i < 32; i += 2) {
+                const __nv_fp8x2_storage_t pk = __nv_cvt_float2_to_fp8x2(
+                    make_float2(__fdiv_rn(x[i], scale), __fdiv_rn(x[i + 1], scale)), __NV_SATFINITE, __NV_E4M3);
+                wq[i >> 2] |= (uint32_t)pk << ((i & 2) * 8);
+              }
+              if (live) {
+                uint4* dst = reinterpret_cast<uint4*>(p.oq + r * p.out_k + m * kTileM + q * 32);
+                dst[0] = make_uint4(wq[0], wq[1], wq[2], wq[3]);
+                dst[1] = make_uint4(wq[4], wq[5], wq[6], wq[7]);
+                if (q == 0) reinterpret_cast<float*>(p.osf)[((int64_t)b * p.out_kb + m) * B + n] = scale;
+              }
+            } else if (live) {
+  #pragma unroll
+              for (int t = 0; t < kTerms; ++t) {
+                uint4 q0, q1;
+                const int ex = (t + 1 < kTerms) ? quant_block32_e4m3<true>(x, q0, q1) : quant_block32_e4m3<false>(x, q0, q1);
+                uint4* dst = reinterpret_cast<uint4*>(p.oq + t * p.oq_term_stride + r * p.out_k + m * kTileM + q * 32);
+                dst[0] = q0;
+                dst[1] = q1;
+                p.osf[act_sf_index(b, m, p.out_kb, B, kTerms, 128, t, n, q)] = (uint8_t)ex;
+              }
             }
           }
           __syncwarp();
@@ -354,28 +393,73 @@ __global__ void __launch_bounds__(kThreads, 1) moe_grouped_gemm_fp8_kernel(const
     // Weight operand: E8M0 scale 1.0 everywhere, written once.  Activation operand: the two terms'
     // scale chunks of every stage, shared memory -> registers -> this warp's TMEM lane quadrant.
     const uint32_t lane_base = (uint32_t)((warp & 3) * 32) << 16;
-    tmem_st_32x32b_x4(tmem_base + lane_base + kSfCol0, make_uint4(0x7F7F7F7Fu, 0x7F7F7F7Fu, 0x7F7F7F7Fu, 0x7F7F7F7Fu));
+    const uint4 ones = make_uint4(0x7F7F7F7Fu, 0x7F7F7F7Fu, 0x7F7F7F7Fu, 0x7F7F7F7Fu);
+    tmem_st_32x32b_x4(tmem_base + lane_base + kSfCol0, ones);
     int stage = 0;
     uint32_t phase = 0, sf_buf = 0, sf_phase = 0;
     bool ok = true;
-    for (int w = blockIdx.x; w < total_work && ok; w += gridDim.x) {
-      for (int kb = 0; kb < p.KB; ++kb) {
-        if (!mbar_wait(smem_u32(&ctl->full[stage]), phase, abort_word, 0x600 + stage) ||
-            !mbar_wait(smem_u32(&ctl->sf_empty[sf_buf]), sf_phase ^ 1, abort_word, 0x700 + sf_buf)) {
-          ok = false;
-          break;
+    if (p.aq) {
+      // 1x128 activations: every E8M0 scale of the MMA is 1.0 (written once, weight and activation side); per
+      // k-block these warps form c[tile][token] = sA[token, kb] * sB[tile's row block, kb] for the promotion
+#pragma unroll
+      for (int c = 0; c < 4; ++c) tmem_st_32x32b_x4(tmem_base + lane_base + kSfCol0 + 4 + 4 * c, ones);
+      tmem_st_wait();
+      tc_fence_before_sync();
+      const int tcol = (warp & 3) * 32 + lane;             // token column of this thread (live when < B)
+      const int row_blocks = (GATEUP ? 2 * p.rows : p.rows) / kTileM;
+      for (int w = blockIdx.x; w < total_work && ok; w += gridDim.x) {
+        const int b = w / p.MT, m = w - b * p.MT;
+        int e = p.sorted_e[b];
+        if (e < 0 || e >= p.E) e = 0;
+        const int rb0 = GATEUP ? m : 2 * m;
+        const int rb1 = GATEUP ? p.rows / kTileM + m : min(2 * m + 1, row_blocks - 1);
+        const float* s0 = p.w_scale + ((int64_t)e * row_blocks + rb0) * p.KB;
+        const float* s1 = p.w_scale + ((int64_t)e * row_blocks + rb1) * p.KB;
+        float n0 = s0[0], n1 = s1[0];                      // next k-block's weight scales, fetched one step ahead
+        for (int kb = 0; kb < p.KB; ++kb) {
+          const float w0 = n0, w1 = n1;
+          if (kb + 1 < p.KB) { n0 = s0[kb + 1]; n1 = s1[kb + 1]; }
+          if (!mbar_wait(smem_u32(&ctl->full[stage]), phase, abort_word, 0x600 + stage) ||
+              !mbar_wait(smem_u32(&ctl->sf_empty[sf_buf]), sf_phase ^ 1, abort_word, 0x700 + sf_buf)) {
+            ok = false;
+            break;
+          }
+          if (tcol < B) {
+            const float sa = *reinterpret_cast<const float*>(smem + kCtlBytes + (size_t)stage * geo.stage_bytes + geo.a_bytes +
+                                                             geo.b_bytes + tcol * 4);
+            ctl->cscale[sf_buf][0][tcol] = sa * w0;
+            ctl->cscale[sf_buf][1][tcol] = sa * w1;
+          }
+          __syncwarp();
+          if (lane == 0) {
+            mbar_arrive(smem_u32(&ctl->sf_full[sf_buf]));     // release: the table entries above are visible to the waiters
+            mbar_arrive(smem_u32(&ctl->empty[stage]));        // this warp is done with the stage's token scales
+          }
+          if (sf_buf == 1) sf_phase ^= 1;
+          sf_buf ^= 1;
+          if (++stage == S) { stage = 0; phase ^= 1; }
         }
-        const uint32_t sf_s = stage0 + (uint32_t)stage * geo.stage_bytes + geo.a_bytes + geo.b_bytes + lane * 16;
-        const uint32_t sfb_t = tmem_base + lane_base + kSfCol0 + 4 + sf_buf * 8;
-        tmem_st_32x32b_x4(sfb_t, ld_shared_v4(sf_s));
-        tmem_st_32x32b_x4(sfb_t + 4, ld_shared_v4(sf_s + kSfChunk));
-        tmem_st_wait();
-        tc_fence_before_sync();
-        __syncwarp();
-        if (lane == 0) mbar_arrive(smem_u32(&ctl->sf_full[sf_buf]));
-        if (sf_buf == 1) sf_phase ^= 1;
-        sf_buf ^= 1;
-        if (++stage == S) { stage = 0; phase ^= 1; }
+      }
+    } else {
+      for (int w = blockIdx.x; w < total_work && ok; w += gridDim.x) {
+        for (int kb = 0; kb < p.KB; ++kb) {
+          if (!mbar_wait(smem_u32(&ctl->full[stage]), phase, abort_word, 0x600 + stage) ||
+              !mbar_wait(smem_u32(&ctl->sf_empty[sf_buf]), sf_phase ^ 1, abort_word, 0x700 + sf_buf)) {
+            ok = false;
+            break;
+          }
+          const uint32_t sf_s = stage0 + (uint32_t)stage * geo.stage_bytes + geo.a_bytes + geo.b_bytes + lane * 16;
+          const uint32_t sfb_t = tmem_base + lane_base + kSfCol0 + 4 + sf_buf * 8;
+          tmem_st_32x32b_x4(sfb_t, ld_shared_v4(sf_s));
+          tmem_st_32x32b_x4(sfb_t + 4, ld_shared_v4(sf_s + kSfChunk));
+          tmem_st_wait();
+          tc_fence_before_sync();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(smem_u32(&ctl->sf_full[sf_buf]));
+          if (sf_buf == 1) sf_phase ^= 1;
+          sf_buf ^= 1;
+          if (++stage == S) { stage = 0; phase ^= 1; }
+        }
       }
     }
   } else {
@@ -391,6 +475,7 @@ __global__ void __launch_bounds__(kThreads, 1) moe_grouped_gemm_fp8_kernel(const
     const bool staged = fused || !GATEUP;      // finished tiles leave through the staging buffer and the store warp
     const int row_blocks = (GATEUP ? 2 * p.rows : p.rows) / kTileM;   // weight-scale rows per expert
     uint32_t acc = 0, acc_phase = 0;
+    uint32_t cs_buf = 0, cs_phase = 0;      // 1x128 mode: ring slot of the per-column scale table
     bool alive = true;
     PROF_DECL(t_wait_epi);
     PROF_DECL(t_fma);
@@ -420,11 +505,17 @@ __global__ void __launch_bounds__(kThreads, 1) moe_grouped_gemm_fp8_kernel(const
       // the tile's weight-block scales go to shared memory first: a global load inside the k loop would sit
       // in front of every accumulator hand-back (the arrive has release semantics)
       float (*ws)[kMaxKB] = ctl->wscale[tile_par];
-      for (int i = tid_e; i < 2 * p.KB; i += 256) ws[i >= p.KB][i >= p.KB ? i - p.KB : i] = (i >= p.KB ? s1 : s0)[i >= p.KB ? i - p.KB : i];
-      tile_par ^= 1;
-      epi_sync();
+      if (!p.aq) {
+        for (int i = tid_e; i < 2 * p.KB; i += 256) ws[i >= p.KB][i >= p.KB ? i - p.KB : i] = (i >= p.KB ? s1 : s0)[i >= p.KB ? i - p.KB : i];
+        tile_par ^= 1;
+        epi_sync();
+      }
       for (int kb = 0; kb < p.KB && alive; ++kb) {
-        const float sc[2] = {ws[0][kb], ws[1][kb]};
+        const float sc[2] = {p.aq ? 0.f : ws[0][kb], p.aq ? 0.f : ws[1][kb]};
+        if (p.aq) {
+          // the k-block's per-column scale table (token scale x weight-block scale), made by the scale-loader warps
+          if (!mbar_wait(smem_u32(&ctl->sf_full[cs_buf]), cs_phase, abort_word, 0x480 + cs_buf)) { alive = false; break; }
+        }
 #pragma unroll
         for (int part = 0; part < 2; ++part) {
           const long long te0 = PROF_NOW();
@@ -443,16 +534,43 @@ __global__ void __launch_bounds__(kThreads, 1) moe_grouped_gemm_fp8_kernel(const
           tc_fence_before_sync();
           __syncwarp();
           if (lane == 0) mbar_arrive(smem_u32(&ctl->tmem_empty[2 * acc + part]));
+          if (p.aq) {
 #pragma unroll
-          for (int ci = 0; ci < kMaxChunks; ++ci) {
-            if ((2 * ci + half) * 16 < nvalid) {
+            for (int ci = 0; ci < kMaxChunks; ++ci) {
+              if ((2 * ci + half) * 16 < nvalid) {
+                const float4* cv = reinterpret_cast<const float4*>(&ctl->cscale[cs_buf][part][(2 * ci + half) * 16]);
 #pragma unroll
-              for (int n = 0; n < 16; n += 2) {
-                if (part == 0) ffma2_scaled(ag[ci * 16 + n], ag[ci * 16 + n + 1], sc[0], v[ci][n], v[ci][n + 1]);
-                else ffma2_scaled(au[ci * 16 + n], au[ci * 16 + n + 1], sc[1], v[ci][n], v[ci][n + 1]);
+                for (int n4 = 0; n4 < 4; ++n4) {
+                  const float4 c = cv[n4];                  // same address in every lane: a broadcast load
+                  const int n = n4 * 4;
+                  if (part == 0) {
+                    ffma2_pair(ag[ci * 16 + n], ag[ci * 16 + n + 1], c.x, c.y, v[ci][n], v[ci][n + 1]);
+                    ffma2_pair(ag[ci * 16 + n + 2], ag[ci * 16 + n + 3], c.z, c.w, v[ci][n + 2], v[ci][n + 3]);
+                  } else {
+                    ffma2_pair(au[ci * 16 + n], au[ci * 16 + n + 1], c.x, c.y, v[ci][n], v[ci][n + 1]);
+                    ffma2_pair(au[ci * 16 + n + 2], au[ci * 16 + n + 3], c.z, c.w, v[ci][n + 2], v[ci][n + 3]);
+                  }
+                }
+              }
+            }
+          } else {
+#pragma unroll
+            for (int ci = 0; ci < kMaxChunks; ++ci) {
+              if ((2 * ci + half) * 16 < nvalid) {
+#pragma unroll
+                for (int n = 0; n < 16; n += 2) {
+                  if (part == 0) ffma2_scaled(ag[ci * 16 + n], ag[ci * 16 + n + 1], sc[0], v[ci][n], v[ci][n + 1]);
+                  else ffma2_scaled(au[ci * 16 + n], au[ci * 16 + n + 1], sc[1], v[ci][n], v[ci][n + 1]);
+                }
               }
             }
           }
+        }
+        if (p.aq && alive) {
+          __syncwarp();
+          if (lane == 0) mbar_arrive(smem_u32(&ctl->sf_empty[cs_buf]));     // this warp has read the table
+          if (cs_buf == 1) cs_phase ^= 1;
+          cs_buf ^= 1;
         }
         if (acc == 1) acc_phase ^= 1;
         acc ^= 1;
@@ -585,6 +703,7 @@ int launch_grouped_gemm_fp8(const GemmArgs& a, cudaStream_t st) {
   p.out2 = (__nv_bfloat16*)a.out2;
   p.sorted_w = a.sorted_w; p.bias = a.bias; p.y = a.gateup ? nullptr : (__nv_bfloat16*)a.y;
   p.weight_stage1 = (a.gateup && a.weight_stage1) ? 1 : 0;
+  p.aq = a.act_quant ? 1 : 0;
   B200_CHECK_ARG(p.weight_stage1 == 0 || a.sorted_w != nullptr, "fp8 grouped gemm: routing weights missing");
   B200_CHECK_ARG(((uintptr_t)p.y & 15) == 0, "fp8 grouped gemm: fused combine needs a 16-byte aligned output");
   if (a.gateup && a.h_out == nullptr)
@@ -599,14 +718,16 @@ int launch_grouped_gemm_fp8(const GemmArgs& a, cudaStream_t st) {
     if (rc) return rc;
   }
   {
-    cuuint64_t dims[3] = {(cuuint64_t)a.Kd, (cuuint64_t)a.max_rows, (cuuint64_t)kTerms};
+    const cuuint32_t terms = p.aq ? 1u : (cuuint32_t)kTerms;
+    cuuint64_t dims[3] = {(cuuint64_t)a.Kd, (cuuint64_t)a.max_rows, (cuuint64_t)terms};
     cuuint64_t strides[2] = {(cuuint64_t)a.Kd, (cuuint64_t)a.Kd * (cuuint64_t)a.max_rows};
-    cuuint32_t box[3] = {kTileK, (cuuint32_t)a.N, (cuuint32_t)kTerms};
+    cuuint32_t box[3] = {kTileK, (cuuint32_t)a.N, terms};
     int rc = encode_map_sw(&p.tmA, CU_TENSOR_MAP_DATA_TYPE_UINT8, 3, a.a_q, dims, strides, box,
                            CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, "fp8 activations");
     if (rc) return rc;
   }
-  const StageGeom geo = stage_geom(a.N);
+  const StageGeom geo = stage_geom(a.N, p.aq);
+  B200_CHECK_ARG(!p.aq || ((uintptr_t)a.asf & 15) == 0, "fp8 grouped gemm: activation scales must be 16-byte aligned");
   const int staging = (!a.gateup || a.h_out == nullptr) ? a.N * kStagePitch : 0;   // fused gate-up and down leave through it
   int stages = std::min((kSmemLimit - 1024 - kCtlBytes - staging) / geo.stage_bytes, kMaxStages);
   B200_CHECK_ARG(stages >= 2, "fp8 grouped gemm: tile does not fit shared memory");

@@ -180,6 +180,7 @@ class MoEPlan:
         self.capacity = T
         self.terms = act_terms or 3
         self.fp8 = weight_format == _lib.W_FP8_128
+        self.aq = act_quant
         self.ws = _lib.workspace_layout(self.shape)
         self.buf = torch.empty(self.ws.total_bytes + 1024, dtype=torch.uint8, device=device)
         off = (-self.buf.data_ptr()) % 1024
@@ -228,9 +229,9 @@ class MoEPlan:
         ids_o, _, _, nv_o, _ = self.sort_outputs()
         base = self.base
         if self.fp8:
-            _lib.check(_lib.lib().b200moe_quant_rows_e4m3(
-                _ptr(x), 0, _ptr(ids_o), _ptr(nv_o), s.T, s.K, s.H, s.B, ws.max_rows,
-                ctypes.c_void_p(base + ws.off_xq), ctypes.c_void_p(base + ws.off_xsf), _stream()), "quant_rows_e4m3")
+            fn = _lib.lib().b200moe_quant_rows_fp8_1x128 if self.aq else _lib.lib().b200moe_quant_rows_e4m3
+            _lib.check(fn(_ptr(x), 0, _ptr(ids_o), _ptr(nv_o), s.T, s.K, s.H, s.B, ws.max_rows,
+                          ctypes.c_void_p(base + ws.off_xq), ctypes.c_void_p(base + ws.off_xsf), _stream()), "quant_rows (fp8)")
             return
         _lib.check(_lib.lib().b200moe_quant_rows(
             _ptr(x), 0, _ptr(ids_o), _ptr(nv_o), s.T, s.K, s.H, s.B, self.terms, ws.max_rows,
@@ -243,9 +244,9 @@ class MoEPlan:
         ids_o, _, _, nv_o, _ = self.sort_outputs()
         base = self.base
         if self.fp8:
-            _lib.check(_lib.lib().b200moe_quant_rows_e4m3(
-                _ptr(h), 1, _ptr(ids_o), _ptr(nv_o), s.T, s.K, s.I, s.B, ws.max_rows,
-                ctypes.c_void_p(base + ws.off_hq), ctypes.c_void_p(base + ws.off_hsf), _stream()), "quant_rows_e4m3")
+            fn = _lib.lib().b200moe_quant_rows_fp8_1x128 if self.aq else _lib.lib().b200moe_quant_rows_e4m3
+            _lib.check(fn(_ptr(h), 1, _ptr(ids_o), _ptr(nv_o), s.T, s.K, s.I, s.B, ws.max_rows,
+                          ctypes.c_void_p(base + ws.off_hq), ctypes.c_void_p(base + ws.off_hsf), _stream()), "quant_rows (fp8)")
             return
         _lib.check(_lib.lib().b200moe_quant_rows(
             _ptr(h), 1, _ptr(ids_o), _ptr(nv_o), s.T, s.K, s.I, s.B, self.terms, ws.max_rows,
@@ -367,6 +368,10 @@ def fused_moe(hidden_states, w1, w2, topk_weight, topk_ids, expert_mask=None,
       ``combine``: "gather" (deterministic: sorted rows + a gather-sum launch in expert order), "fused" (the down
         epilogue multiplies by the routing weight and adds into the output with packed-bf16 reductions, the
         reference kernels' own epilogue, src/contrib/moe.py:703-787) or "auto" (= "gather", the reproducible one).
+      ``act_quant`` (FP8 weights): "terms" (default: two e4m3 terms with E8M0 scales per 32, exact for bf16 inputs
+        to ~2^-9 of the block maximum) or "1x128" (the reference's own per-token, per-128-channel e4m3 format with
+        fp32 scales, src/contrib/fused_moe.py:375-381: half the operand bytes and MMA work, judged against the
+        oracle that dequantises the same quantised activations).
       ``bias1`` [E, 2I] / ``bias2`` [E, H]: per-expert biases of the two projections (gpt-oss style).
     """
     if not hidden_states.is_cuda:
@@ -390,6 +395,8 @@ def fused_moe(hidden_states, w1, w2, topk_weight, topk_ids, expert_mask=None,
         raise ValueError(f"combine={combine!r}: 'auto', 'gather' or 'fused'")
     if act_quant not in ("terms", "1x128"):
         raise ValueError(f"act_quant={act_quant!r}: 'terms' or '1x128'")
+    if act_quant == "1x128" and fmt != _lib.W_FP8_128:
+        raise ValueError("act_quant='1x128' belongs to per_128x128 (FP8) weights; MXFP4 weights take act_terms")
     T, H = hidden_states.shape
     K = topk_ids.shape[1]
     pw = prepare_weights(w1, w1_scale, w2, w2_scale, fmt)

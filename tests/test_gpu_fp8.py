@@ -113,3 +113,99 @@ def test_deepseek_shaped_slice():
     tw, ids = synth.make_routing(T, E, K, "sigmoid", seed=1)
     w = synth.make_weights_fp8(E, H, I, seed=1)
     _close(_run(x, tw, ids, w), orc.torch_moe_oracle_fp8(x, *w, tw, ids), "dsv3 slice")
+
+
+# --------------------------------------------------------------------------------------------
+# per-token 1x128 activations (the reference's own FP8 activation format), fused combine
+# --------------------------------------------------------------------------------------------
+def test_1x128_rows_match_oracle_bit_for_bit():
+    T, H, I, E, K, B = 40, 384, 256, 8, 2, 32
+    x = synth.make_hidden(T, H, 4)
+    x[3, 128:256] = 0                                    # an all-zero block takes scale 1.0
+    tw, ids = synth.make_routing(T, E, K, seed=4)
+    plan = get_plan(T, K, E, E, H, I, B, 0, 7.0, torch.device(DEV), weight_format=_lib.W_FP8_128, act_quant=_lib.ACTQ_1X128)
+    s_ids, _, _, nv, _ = plan.sort(ids.to(DEV), tw.to(DEV))
+    plan.quant_input(x.to(DEV))
+    torch.cuda.synchronize()
+    n, L = int(nv[0]), plan.ws.max_rows
+    q = plan.region("xq", L * H).cpu().view(torch.float8_e4m3fn).float().numpy().reshape(L, H)[:n]
+    sc = plan.region("xsf", L // B * (H // 128) * B * 4, torch.float32).cpu().numpy().reshape(L // B, H // 128, B)
+    sid = s_ids.cpu().numpy().view(np.uint32)[:n]
+    tok, kk = sid & 0xFFFFFF, sid >> 24
+    eq, es = orc.act_quant_fp8_1x128(x)
+    eq, es = eq.float().numpy(), es.numpy()
+    for r in range(n):
+        if kk[r] < K:
+            assert np.array_equal(q[r], eq[tok[r]]), r
+            assert np.array_equal(sc[r // B, :, r % B], es[tok[r]]), r
+
+
+def _close_q(y, ref_q, ref, what):
+    """Against the oracle that dequantises the same 1x128-quantised activations; the distance to the
+    bf16-activation oracle is reported."""
+    assert torch.isfinite(y.float()).all(), what
+    cos, mx = orc.cosine(y, ref_q), orc.max_abs(y, ref_q)
+    bound = MAX_ABS * max(1.0, float(ref_q.float().abs().max()))
+    print(f"{what}: vs 1x128 oracle cosine {cos:.6f} max_abs {mx:.3e}; vs bf16-activation oracle cosine {orc.cosine(y, ref):.6f}")
+    assert cos >= COS and mx <= bound, f"{what}: cosine {cos:.6f} max_abs {mx:.3e} (bound {bound:.3e})"
+
+
+@pytest.mark.parametrize("T,H,I,E,K,B", [(32, 256, 128, 4, 2, 32), (150, 256, 384, 4, 2, 64), (300, 384, 128, 4, 2, 96),
+                                         (7, 512, 256, 8, 2, 16)])
+def test_1x128_stage_chain_matches_its_oracle(T, H, I, E, K, B):
+    x = synth.make_hidden(T, H, T)
+    tw, ids = synth.make_routing(T, E, K, seed=T)
+    w = synth.make_weights_fp8(E, H, I, seed=T)
+    pw = prepare_weights(*(t.to(DEV) for t in w), weight_format=_lib.W_FP8_128)
+    plan = get_plan(T, K, E, E, H, I, B, 0, 7.0, torch.device(DEV), weight_format=_lib.W_FP8_128, act_quant=_lib.ACTQ_1X128)
+    plan.sort(ids.to(DEV), tw.to(DEV))
+    plan.quant_input(x.to(DEV))
+    h = torch.zeros(T, K, I, dtype=torch.bfloat16, device=DEV)
+    plan.gateup(pw, h)
+    plan.quant_hidden(h)
+    plan.down(pw)
+    y = torch.empty(T, H, dtype=torch.bfloat16, device=DEV)
+    plan.combine(tw.to(DEV), y)
+    torch.cuda.synchronize()
+    plan.check_status()
+    _close_q(y.cpu(), orc.torch_moe_oracle_fp8(x, *w, tw, ids, act_quant="fp8_1x128"),
+             orc.torch_moe_oracle_fp8(x, *w, tw, ids), "1x128 stage chain")
+
+
+@pytest.mark.parametrize("T", [1, 8, 33, 257])
+@pytest.mark.parametrize("combine", ["gather", "fused"])
+def test_1x128_fused_layer(T, combine):
+    H, I, E, K = 384, 256, 16, 4
+    x = synth.make_hidden(T, H, T)
+    tw, ids = synth.make_routing(T, E, K, "zipf", seed=T)
+    w = synth.make_weights_fp8(E, H, I, seed=3)
+    _close_q(_run(x, tw, ids, w, act_quant="1x128", combine=combine),
+             orc.torch_moe_oracle_fp8(x, *w, tw, ids, act_quant="fp8_1x128"), orc.torch_moe_oracle_fp8(x, *w, tw, ids),
+             f"1x128 layer T={T} {combine}")
+
+
+@pytest.mark.parametrize("act_quant", ["terms", "1x128"])
+def test_fp8_fused_combine_biases_and_stage1_weights(act_quant):
+    T, H, I, E, K = 70, 256, 128, 8, 2
+    x = synth.make_hidden(T, H, 5)
+    tw, ids = synth.make_routing(T, E, K, seed=5)
+    w = synth.make_weights_fp8(E, H, I, seed=5)
+    g = torch.Generator().manual_seed(9)
+    b1 = (torch.randn(E, 2 * I, generator=g) * 0.1).to(torch.bfloat16)
+    b2 = (torch.randn(E, H, generator=g) * 0.1).to(torch.bfloat16)
+    okw = {} if act_quant == "terms" else {"act_quant": "fp8_1x128"}
+    for combine in ("gather", "fused"):
+        for kw, ok in ((dict(), dict()), (dict(bias1=b1.to(DEV), bias2=b2.to(DEV)), dict(bias1=b1, bias2=b2)),
+                       (dict(doweight_stage1=True), dict(doweight_stage1=True))):
+            ref = orc.torch_moe_oracle_fp8(x, *w, tw, ids, **ok, **okw)
+            _close(_run(x, tw, ids, w, combine=combine, act_quant=act_quant, **kw), ref, f"fp8 {act_quant} {combine} {sorted(kw)}")
+
+
+def test_deepseek_shaped_slice_1x128():
+    T, H, I, E, K = 100, 7168, 2048, 8, 8
+    x = synth.make_hidden(T, H, 1)
+    tw, ids = synth.make_routing(T, E, K, "sigmoid", seed=1)
+    w = synth.make_weights_fp8(E, H, I, seed=1)
+    _close_q(_run(x, tw, ids, w, act_quant="1x128", combine="fused"),
+             orc.torch_moe_oracle_fp8(x, *w, tw, ids, act_quant="fp8_1x128"), orc.torch_moe_oracle_fp8(x, *w, tw, ids),
+             "dsv3 slice 1x128")
