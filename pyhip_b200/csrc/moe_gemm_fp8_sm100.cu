@@ -478,6 +478,7 @@ __global__ void __launch_bounds__(kThreads, 1) moe_grouped_gemm_fp8_kernel(const
     uint32_t cs_buf = 0, cs_phase = 0;      // 1x128 mode: ring slot of the per-column scale table
     bool alive = true;
     PROF_DECL(t_wait_epi);
+    PROF_DECL(t_wait_cs);
     PROF_DECL(t_fma);
     int tile_par = 0;
     uint32_t stg_phase = 0;
@@ -514,7 +515,9 @@ __global__ void __launch_bounds__(kThreads, 1) moe_grouped_gemm_fp8_kernel(const
         const float sc[2] = {p.aq ? 0.f : ws[0][kb], p.aq ? 0.f : ws[1][kb]};
         if (p.aq) {
           // the k-block's per-column scale table (token scale x weight-block scale), made by the scale-loader warps
+          const long long tc0 = PROF_NOW();
           if (!mbar_wait(smem_u32(&ctl->sf_full[cs_buf]), cs_phase, abort_word, 0x480 + cs_buf)) { alive = false; break; }
+          PROF_ADD(t_wait_cs, tc0);
         }
 #pragma unroll
         for (int part = 0; part < 2; ++part) {
@@ -663,6 +666,7 @@ __global__ void __launch_bounds__(kThreads, 1) moe_grouped_gemm_fp8_kernel(const
     if (blockIdx.x == 0 && tid_e == 0) {     // kilo-cycles: epilogue total, waiting for an accumulator, after the k loop
       p.status[8] = (int32_t)((clock64() - t_begin_epi) >> 10);
       p.status[9] = (int32_t)(t_wait_epi >> 10);
+      p.status[10] = (int32_t)(t_wait_cs >> 10);
       p.status[11] = (int32_t)(t_fma >> 10);
     }
 #endif
