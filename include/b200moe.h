@@ -25,6 +25,10 @@ extern "C" {
 /* weight formats */
 #define B200MOE_W_MXFP4 0 /* E2M1 pairs (low nibble = even element) + E8M0 scale per 32 along K */
 #define B200MOE_W_FP8_128 1 /* e4m3 + fp32 scale per 128x128 block */
+#define B200MOE_W_FP8_ROW 2 /* e4m3 + one fp32 scale per output row, w_scale [E, 2I] / [E, H]: the reference's
+                               per-token-per-channel FP8 weights (tests/contrib/moe/test_moe.py:123-128); its per-tensor
+                               weights (:130-137) are the same with a row's scale repeated.  The scale tensors are passed
+                               in place as the *_scale_prepared arguments */
 /* activation functions of the gate-up stage */
 #define B200MOE_ACT_SILU 0   /* silu(gate) * up                        (test_moe.py:74-75) */
 #define B200MOE_ACT_SWIGLU 1 /* clamped gate*sigmoid(1.702 gate)*(up+1) (test_moe.py:76-81) */

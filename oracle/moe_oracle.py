@@ -71,6 +71,14 @@ def dequant_fp8_128x128(q: torch.Tensor, scale: torch.Tensor, dtype=torch.bfloat
     return out.reshape(*lead, N, K)
 
 
+def dequant_fp8_rows(q: torch.Tensor, scale: torch.Tensor, dtype=torch.bfloat16) -> torch.Tensor:
+    """e4m3 value cast to bf16 times the fp32 scale of its output row (or of its expert), cast to bf16
+    (tests/contrib/moe/test_moe.py:127,136).  q [..., N, K]; scale [..., N] or [...] (per tensor)."""
+    sc = scale.float()
+    sc = sc.reshape(*sc.shape, 1, 1) if sc.dim() == q.dim() - 2 else sc.unsqueeze(-1)
+    return (q.to(dtype) * sc).to(dtype)
+
+
 # --------------------------------------------------------------------------------------
 # token -> expert sort / align
 # --------------------------------------------------------------------------------------
@@ -250,8 +258,10 @@ def torch_moe_oracle_mxfp4(hidden, w1_q, w1_s, w2_q, w2_s, topk_weight, topk_ids
     return torch_moe_oracle(hidden, None, None, topk_weight, topk_ids, expert_weights=ew, **kw)
 
 
-def torch_moe_oracle_fp8(hidden, w1_q, w1_s, w2_q, w2_s, topk_weight, topk_ids, **kw):
+def torch_moe_oracle_fp8(hidden, w1_q, w1_s, w2_q, w2_s, topk_weight, topk_ids, row_scaled=False, **kw):
     def ew(e):
+        if row_scaled:
+            return dequant_fp8_rows(w1_q[e], w1_s[e], hidden.dtype), dequant_fp8_rows(w2_q[e], w2_s[e], hidden.dtype)
         return (dequant_fp8_128x128(w1_q[e], w1_s[e], hidden.dtype),
                 dequant_fp8_128x128(w2_q[e], w2_s[e], hidden.dtype))
     return torch_moe_oracle(hidden, None, None, topk_weight, topk_ids, expert_weights=ew, **kw)

@@ -28,11 +28,11 @@ static int check_shape(const b200moe_shape* s) {
   B200_CHECK_ARG(s->H >= 32 && s->H % 32 == 0, "H=%d must be a positive multiple of 32", s->H);
   B200_CHECK_ARG(s->I >= 32 && s->I % 32 == 0, "I=%d must be a positive multiple of 32", s->I);
   B200_CHECK_ARG(s->H % 8 == 0, "H must be a multiple of 8");
-  B200_CHECK_ARG(s->weight_format == B200MOE_W_MXFP4 || s->weight_format == B200MOE_W_FP8_128,
-                 "weight_format %d unknown", s->weight_format);
-  if (s->weight_format == B200MOE_W_FP8_128) {
-    B200_CHECK_ARG(s->H % 128 == 0 && s->I % 128 == 0, "FP8 128x128 weights need H and I to be multiples of 128");
-    B200_CHECK_ARG(s->B <= 96, "FP8 128x128 weights: B=%d exceeds 96", s->B);
+  B200_CHECK_ARG(s->weight_format == B200MOE_W_MXFP4 || s->weight_format == B200MOE_W_FP8_128 ||
+                 s->weight_format == B200MOE_W_FP8_ROW, "weight_format %d unknown", s->weight_format);
+  if (s->weight_format != B200MOE_W_MXFP4) {
+    B200_CHECK_ARG(s->H % 128 == 0 && s->I % 128 == 0, "FP8 weights need H and I to be multiples of 128");
+    B200_CHECK_ARG(s->B <= 96, "FP8 weights: B=%d exceeds 96", s->B);
   }
   B200_CHECK_ARG(s->activation == B200MOE_ACT_SILU || s->activation == B200MOE_ACT_SWIGLU,
                  "activation %d unknown", s->activation);
@@ -64,7 +64,7 @@ const char* b200moe_last_error(void) { return g_err; }
 int b200moe_workspace_layout(const b200moe_shape* s, b200moe_workspace* ws) {
   if (int rc = check_shape(s)) return rc;
   B200_CHECK_ARG(ws != nullptr, "workspace descriptor is NULL");
-  const bool fp8w = s->weight_format == B200MOE_W_FP8_128;
+  const bool fp8w = s->weight_format != B200MOE_W_MXFP4;
   const int NT = fp8w ? 2 : terms_of(s);
   const int64_t P = (int64_t)s->T * s->K;
   const int64_t nblk = (P + (int64_t)s->E_route * (s->B - 1) + s->B - 1) / s->B;
@@ -210,6 +210,7 @@ int b200moe_quant_rows_e4m3(const void* src_bf16, int32_t src_mode, const uint32
 static void fill_common(GemmArgs& g, const b200moe_shape* s, const b200moe_workspace* ws, uint8_t* base) {
   g.N = s->B;
   g.act_quant = s->act_quant;
+  g.w_row_scaled = s->weight_format == B200MOE_W_FP8_ROW;
   g.NT = terms_of(s);
   g.E = s->E;
   g.topk = s->K;
@@ -244,7 +245,7 @@ int b200moe_gateup(const b200moe_shape* s, const b200moe_workspace* ws, void* wo
   g.weight_stage1 = s->doweight_stage1;
   g.oq = base + ws->off_hq;
   g.osf = base + ws->off_hsf;
-  if (s->weight_format == B200MOE_W_FP8_128) {
+  if (s->weight_format != B200MOE_W_MXFP4) {
     g.out_kp = s->I;
     return launch_grouped_gemm_fp8(g, (cudaStream_t)stream);
   }
@@ -275,7 +276,7 @@ int b200moe_down(const b200moe_shape* s, const b200moe_workspace* ws, void* work
   g.bias = bias2;
   g.y = s->combine_mode == B200MOE_COMBINE_FUSED ? y_bf16 : nullptr;
   if (s->doweight_stage1) g.sorted_w = nullptr;     // weights already applied upstream
-  if (s->weight_format == B200MOE_W_FP8_128) return launch_grouped_gemm_fp8(g, (cudaStream_t)stream);
+  if (s->weight_format != B200MOE_W_MXFP4) return launch_grouped_gemm_fp8(g, (cudaStream_t)stream);
   return launch_grouped_gemm(g, (cudaStream_t)stream);
 }
 
@@ -326,7 +327,7 @@ static int forward_impl(const b200moe_shape* s, const b200moe_workspace* ws, voi
   B200_CHECK_ARG(io->x_bf16 && io->topk_ids && io->topk_weight && io->y_bf16, "forward: NULL tensor");
   B200_CHECK_ARG(((uintptr_t)io->y_bf16 & 15) == 0, "forward: output must be 16-byte aligned");
   uint8_t* base = (uint8_t*)workspace;
-  const bool fp8w = s->weight_format == B200MOE_W_FP8_128;
+  const bool fp8w = s->weight_format != B200MOE_W_MXFP4;
   const bool fused = s->combine_mode == B200MOE_COMBINE_FUSED;
   // the fused combine accumulates into y: the quantiser launch clears it first
   void* zero_ptr = fused ? io->y_bf16 : nullptr;

@@ -113,6 +113,7 @@ struct GemmArgs {
   void* y;                 // down: zeroed bf16 [T, rows]; non-null selects the fused weighted scatter-add epilogue
   int weight_stage1;       // gate-up: apply the routing weight to h
   int act_quant;           // FP8 kernel: 0 = two e4m3 terms with E8M0 scales, 1 = one e4m3 term with fp32 scales per 1x128
+  int w_row_scaled;        // FP8 kernel: w_scale holds one fp32 scale per weight row [E, parts*rows] (not per 128x128 block)
 };
 int launch_grouped_gemm(const GemmArgs& a, cudaStream_t st);
 // FP8 128x128-block variant (moe_gemm_fp8_sm100.cu): w_data = e4m3 bytes [E, parts*rows, Kd], w_scale = fp32

@@ -15,6 +15,10 @@
 //     and add into fp32 registers -- the two-level accumulation the reference's FP8 kernel does
 //     with its FIFO + fmac (src/contrib/moe_gemm_8wave.py:386-405).  Two TMEM accumulator buffers
 //     let the next k-block's MMAs run under the promotion of the current one.
+//   * row-scaled weights (one fp32 scale per output row: the reference's per-token-per-channel and per-tensor FP8
+//     weight formats, tests/contrib/moe/test_moe.py:123-138,190-200): the scale does not change along K, so the
+//     MMAs accumulate over all k-blocks in tensor memory and the epilogue multiplies each accumulator row by its
+//     scale once per tile -- in this orientation a thread owns one weight row, so that is one scalar per thread.
 //   * act_quant 1x128 (the reference's own activation format: one e4m3 value per element with an fp32
 //     scale per token and 128 channels, src/contrib/fused_moe.py:375-381): a single activation term, all
 //     E8M0 scales of the MMA are 1.0, and the promotion multiplies every token column by
@@ -68,6 +72,7 @@ struct Params {
   __nv_bfloat16* y;        // down, fused combine: zeroed [T, rows] output accumulated with bf16x2 reductions; or null
   int weight_stage1;       // gate-up: multiply h by the routing weight
   int aq;                  // 1: single e4m3 activation term with fp32 scales per (token, 128 channels)
+  int rowsc;               // 1: w_scale is [E, parts*rows], one scale per weight row, constant along K
 };
 
 struct SmemCtl {
@@ -214,8 +219,11 @@ __global__ void __launch_bounds__(kThreads, 1) moe_grouped_gemm_fp8_kernel(const
         for (int kb = 0; kb < p.KB; ++kb) {
           // every k-block gets its own accumulator buffer: the epilogue promotes it with the
           // block's fp32 weight scale while the next k-block is being multiplied
+          // (row-scaled weights: one accumulator per TILE, multiplied into across all k-blocks)
+          const bool first_kb = !p.rowsc || kb == 0, last_kb = !p.rowsc || kb == p.KB - 1;
           const long long c0 = PROF_NOW();
-          ok = mbar_wait(smem_u32(&ctl->tmem_empty[2 * acc + part]), acc_phase ^ 1, abort_word, 0x200 + 2 * acc + part);
+          if (first_kb)
+            ok = mbar_wait(smem_u32(&ctl->tmem_empty[2 * acc + part]), acc_phase ^ 1, abort_word, 0x200 + 2 * acc + part);
           PROF_ADD(t_acc, c0);
           const long long c1 = PROF_NOW();
           ok = ok && mbar_wait(smem_u32(&ctl->full[stage]), phase, abort_word, 0x300 + stage);
@@ -240,17 +248,20 @@ __global__ void __launch_bounds__(kThreads, 1) moe_grouped_gemm_fp8_kernel(const
   #pragma unroll
               for (int t = 0; t < kTerms; ++t)
                 if (t < nterms)
-                  umma_mxf8(d0, a_lo + 2 * k, b_lo + t * term_lo + 2 * k, idesc[k], sfa_t, sfb_t + 4 * t, (k | t) != 0);
+                  umma_mxf8(d0, a_lo + 2 * k, b_lo + t * term_lo + 2 * k, idesc[k], sfa_t, sfb_t + 4 * t,
+                            (k | t) != 0 || !first_kb);
             }
             tc_commit(smem_u32(&ctl->empty[stage]));
             if (!p.aq) tc_commit(smem_u32(&ctl->sf_empty[sf_buf]));
-            tc_commit(smem_u32(&ctl->tmem_full[2 * acc + part]));
+            if (last_kb) tc_commit(smem_u32(&ctl->tmem_full[2 * acc + part]));
           }
           __syncwarp();
           if (sf_buf == 1) sf_phase ^= 1;
           sf_buf ^= 1;
-          if (acc == 1) acc_phase ^= 1;
-          acc ^= 1;
+          if (last_kb) {
+            if (acc == 1) acc_phase ^= 1;
+            acc ^= 1;
+          }
           if (++stage == S) { stage = 0; phase ^= 1; }
         }
       }
@@ -494,6 +505,13 @@ __global__ void __launch_bounds__(kThreads, 1) moe_grouped_gemm_fp8_kernel(const
       const int rb1 = GATEUP ? p.rows / kTileM + m : min(2 * m + 1, row_blocks - 1);
       const float* s0 = p.w_scale + ((int64_t)e * row_blocks + rb0) * p.KB;
       const float* s1 = p.w_scale + ((int64_t)e * row_blocks + rb1) * p.KB;
+      // row-scaled weights: this thread's two weight rows carry one scale each for the whole tile
+      float rs0 = 0.f, rs1 = 0.f;
+      if (p.rowsc) {
+        const float* rs = p.w_scale + (int64_t)e * (GATEUP ? 2 : 1) * p.rows;
+        if (j < p.rows) rs0 = rs[j];
+        if (GATEUP ? j < p.rows : j + kTileM < p.rows) rs1 = rs[j + (GATEUP ? p.rows : kTileM)];
+      }
       int nvalid = 0;
       for (int q = 0; q < B; q += 32) {
         const uint32_t id = (q + lane < B) ? p.sorted_ids[r0 + q + lane] : 0xFFFFFFFFu;
@@ -506,13 +524,14 @@ __global__ void __launch_bounds__(kThreads, 1) moe_grouped_gemm_fp8_kernel(const
       // the tile's weight-block scales go to shared memory first: a global load inside the k loop would sit
       // in front of every accumulator hand-back (the arrive has release semantics)
       float (*ws)[kMaxKB] = ctl->wscale[tile_par];
-      if (!p.aq) {
+      if (!p.aq && !p.rowsc) {
         for (int i = tid_e; i < 2 * p.KB; i += 256) ws[i >= p.KB][i >= p.KB ? i - p.KB : i] = (i >= p.KB ? s1 : s0)[i >= p.KB ? i - p.KB : i];
         tile_par ^= 1;
         epi_sync();
       }
-      for (int kb = 0; kb < p.KB && alive; ++kb) {
-        const float sc[2] = {p.aq ? 0.f : ws[0][kb], p.aq ? 0.f : ws[1][kb]};
+      const int kb_rounds = p.rowsc ? 1 : p.KB;        // accumulator hand-overs per tile
+      for (int kb = 0; kb < kb_rounds && alive; ++kb) {
+        const float sc[2] = {p.rowsc ? rs0 : (p.aq ? 0.f : ws[0][kb]), p.rowsc ? rs1 : (p.aq ? 0.f : ws[1][kb])};
         if (p.aq) {
           // the k-block's per-column scale table (token scale x weight-block scale), made by the scale-loader warps
           const long long tc0 = PROF_NOW();
@@ -691,7 +710,7 @@ int launch_grouped_gemm_fp8(const GemmArgs& a, cudaStream_t st) {
                  a.N);
   B200_CHECK_ARG(a.Kd % 128 == 0 && a.rows % 128 == 0 && a.E > 0, "fp8 grouped gemm: K and rows must be multiples of 128");
   B200_CHECK_ARG(a.max_rows % a.N == 0, "fp8 grouped gemm: max_rows %% B != 0");
-  B200_CHECK_ARG(a.Kd / kTileK <= kMaxKB, "fp8 grouped gemm: K=%d exceeds %d", a.Kd, kMaxKB * kTileK);
+  B200_CHECK_ARG(a.w_row_scaled || a.Kd / kTileK <= kMaxKB, "fp8 grouped gemm: K=%d exceeds %d", a.Kd, kMaxKB * kTileK);
   B200_CHECK_ARG(((uintptr_t)a.w_data & 15) == 0 && ((uintptr_t)a.a_q & 15) == 0 && ((uintptr_t)a.w_scale & 3) == 0,
                  "fp8 grouped gemm: operand tensors must be 16-byte aligned");
   Params p;
@@ -708,6 +727,8 @@ int launch_grouped_gemm_fp8(const GemmArgs& a, cudaStream_t st) {
   p.sorted_w = a.sorted_w; p.bias = a.bias; p.y = a.gateup ? nullptr : (__nv_bfloat16*)a.y;
   p.weight_stage1 = (a.gateup && a.weight_stage1) ? 1 : 0;
   p.aq = a.act_quant ? 1 : 0;
+  p.rowsc = a.w_row_scaled ? 1 : 0;
+  B200_CHECK_ARG(!(p.aq && p.rowsc), "fp8 grouped gemm: 1x128 activations are not offered with row-scaled weights");
   B200_CHECK_ARG(p.weight_stage1 == 0 || a.sorted_w != nullptr, "fp8 grouped gemm: routing weights missing");
   B200_CHECK_ARG(((uintptr_t)p.y & 15) == 0, "fp8 grouped gemm: fused combine needs a 16-byte aligned output");
   if (a.gateup && a.h_out == nullptr)

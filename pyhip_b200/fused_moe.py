@@ -119,10 +119,12 @@ class PreparedWeights:
 
 
 class PreparedWeightsFP8:
-    """FP8 (e4m3) expert weights with one fp32 scale per 128x128 block
-    (tests/contrib/moe/test_moe.py:201-260): consumed entirely in place."""
+    """FP8 (e4m3) expert weights, consumed entirely in place, with either one fp32 scale per 128x128 block
+    (tests/contrib/moe/test_moe.py:201-260) or one per output row -- the reference's per-token-per-channel format,
+    scales [E, N] or [E, N, 1]; its per-tensor format, scales [E], is expanded to one value per row here
+    (tests/contrib/moe/test_moe.py:123-138)."""
 
-    def __init__(self, w1, w1_scale, w2, w2_scale):
+    def __init__(self, w1, w1_scale, w2, w2_scale, row_scaled=False):
         if not w1.is_cuda:
             raise ValueError("weights must be CUDA tensors")
         E, N1, H = w1.shape
@@ -130,11 +132,21 @@ class PreparedWeightsFP8:
         if tuple(w2.shape) != (E, H, self.I):
             raise ValueError(f"w2 shape {tuple(w2.shape)} does not match w1 {tuple(w1.shape)}")
         if H % 128 or self.I % 128:
-            raise ValueError("per_128x128 weights need H and I to be multiples of 128")
-        if w1_scale.numel() != E * (N1 // 128) * (H // 128) or w2_scale.numel() != E * (H // 128) * (self.I // 128):
-            raise ValueError("scale tensors must hold one fp32 scale per 128x128 block")
+            raise ValueError("FP8 weights need H and I to be multiples of 128")
+        if row_scaled:
+            def rows(sc, n):
+                sc = sc.float().to(w1.device)
+                if sc.numel() == E:                           # per-tensor: one scale per expert
+                    sc = sc.reshape(E, 1).expand(E, n)
+                elif sc.numel() != E * n:
+                    raise ValueError("scale tensors must hold one fp32 scale per expert or per output row")
+                return sc.reshape(E, n).contiguous()
+            self.w1_scale, self.w2_scale = rows(w1_scale, N1), rows(w2_scale, H)
+        else:
+            if w1_scale.numel() != E * (N1 // 128) * (H // 128) or w2_scale.numel() != E * (H // 128) * (self.I // 128):
+                raise ValueError("scale tensors must hold one fp32 scale per 128x128 block")
+            self.w1_scale, self.w2_scale = w1_scale.float().contiguous(), w2_scale.float().contiguous()
         self.w1_data, self.w2_data = w1.contiguous().view(torch.uint8), w2.contiguous().view(torch.uint8)
-        self.w1_scale, self.w2_scale = w1_scale.float().contiguous(), w2_scale.float().contiguous()
         self.device = w1.device
 
 
@@ -154,8 +166,10 @@ def prepare_weights(w1, w1_scale, w2, w2_scale, weight_format=_lib.W_MXFP4):
     if hit is None:
         while len(_prepared_cache) >= _PREPARED_CACHE_ENTRIES:
             _prepared_cache.pop(next(iter(_prepared_cache)))
-        cls = PreparedWeightsFP8 if weight_format == _lib.W_FP8_128 else PreparedWeights
-        pw = cls(w1, w1_scale, w2, w2_scale)
+        if weight_format == _lib.W_MXFP4:
+            pw = PreparedWeights(w1, w1_scale, w2, w2_scale)
+        else:
+            pw = PreparedWeightsFP8(w1, w1_scale, w2, w2_scale, row_scaled=weight_format == _lib.W_FP8_ROW)
         hit = (pw, (w1, w1_scale, w2, w2_scale))      # the sources stay alive, so their addresses identify them
     _prepared_cache[key] = hit
     return hit[0]
@@ -179,7 +193,7 @@ class MoEPlan:
                                 doweight_stage1=1 if doweight_stage1 else 0)
         self.capacity = T
         self.terms = act_terms or 3
-        self.fp8 = weight_format == _lib.W_FP8_128
+        self.fp8 = weight_format != _lib.W_MXFP4
         self.aq = act_quant
         self.ws = _lib.workspace_layout(self.shape)
         self.buf = torch.empty(self.ws.total_bytes + 1024, dtype=torch.uint8, device=device)
@@ -378,9 +392,11 @@ def fused_moe(hidden_states, w1, w2, topk_weight, topk_ids, expert_mask=None,
         raise RuntimeError("fused_moe runs on a CUDA device only (sm_100a); there is no CPU path")
     if hidden_states.dtype != torch.bfloat16:
         raise TypeError("hidden_states must be bfloat16")
-    if int(quant_type) not in (QuantType.per_1x32, QuantType.per_128x128):
-        raise NotImplementedError(f"quant_type={quant_type!r}: per_1x32 (MXFP4) and per_128x128 (FP8) are implemented")
-    fmt = _lib.W_MXFP4 if int(quant_type) == QuantType.per_1x32 else _lib.W_FP8_128
+    fmt = {int(QuantType.per_1x32): _lib.W_MXFP4, int(QuantType.per_128x128): _lib.W_FP8_128,
+           int(QuantType.per_Token): _lib.W_FP8_ROW, int(QuantType.per_Tensor): _lib.W_FP8_ROW}.get(int(quant_type))
+    if fmt is None:
+        raise NotImplementedError(f"quant_type={quant_type!r}: per_1x32 (MXFP4), per_128x128, per_Token and per_Tensor "
+                                  "(FP8) are implemented")
     if int(activation) not in (ActivationType.Silu, ActivationType.Swiglu):
         raise NotImplementedError(f"activation={activation!r}: Silu and Swiglu are implemented")
     if a1_scale is not None or a2_scale is not None:

@@ -110,3 +110,21 @@ def dequantize_fp8_128x128(q: torch.Tensor, scale: torch.Tensor,
     blk = q.to(dtype).reshape(E, N // FP8_BLOCK, FP8_BLOCK, K // FP8_BLOCK, FP8_BLOCK)
     out = (blk * scale.reshape(E, N // FP8_BLOCK, 1, K // FP8_BLOCK, 1)).to(dtype)
     return out.reshape(E, N, K)
+
+
+def quantize_fp8_per_row(w: torch.Tensor):
+    """[E, N, K] float -> e4m3 weights + one fp32 scale per output row [E, N], scale = amax_row / 448: the
+    per-token-per-channel weight format (tests/contrib/moe/test_moe.py:123-128; the arithmetic of the per-tensor
+    rule at :130-137 applied row by row)."""
+    amax = w.float().abs().amax(dim=-1)
+    scale = torch.where(amax > 0, amax / FP8_MAX, torch.ones_like(amax))
+    q = (w.float() / scale.unsqueeze(-1)).clamp(-FP8_MAX, FP8_MAX).to(torch.float8_e4m3fn)
+    return q, scale
+
+
+def quantize_fp8_per_tensor(w: torch.Tensor):
+    """[E, N, K] float -> e4m3 weights + one fp32 scale per expert [E] (tests/contrib/moe/test_moe.py:130-137)."""
+    scale = w.float().abs().amax(dim=(1, 2)) / FP8_MAX
+    scale = torch.where(scale > 0, scale, torch.ones_like(scale))
+    q = (w.float() / scale.view(-1, 1, 1)).clamp(-FP8_MAX, FP8_MAX).to(torch.float8_e4m3fn)
+    return q, scale

@@ -209,3 +209,35 @@ def test_deepseek_shaped_slice_1x128():
     _close_q(_run(x, tw, ids, w, act_quant="1x128", combine="fused"),
              orc.torch_moe_oracle_fp8(x, *w, tw, ids, act_quant="fp8_1x128"), orc.torch_moe_oracle_fp8(x, *w, tw, ids),
              "dsv3 slice 1x128")
+
+
+# --------------------------------------------------------------------------------------------
+# row-scaled FP8 weights: per-token-per-channel and per-tensor (tests/contrib/moe/test_moe.py:123-138,190-200)
+# --------------------------------------------------------------------------------------------
+def _rows_case(T, H, I, E, K, seed, per_tensor):
+    from pyhip_b200 import quant
+    g = torch.Generator().manual_seed(seed)
+    w1f = torch.randn(E, 2 * I, H, generator=g) * 0.02
+    w2f = torch.randn(E, H, I, generator=g) * 0.02
+    # uneven row magnitudes, so that a wrong row <-> scale pairing cannot pass
+    w1f *= torch.linspace(0.5, 2.0, 2 * I)[None, :, None]
+    w2f *= torch.linspace(2.0, 0.5, H)[None, :, None]
+    q = quant.quantize_fp8_per_tensor if per_tensor else quant.quantize_fp8_per_row
+    (w1_q, w1_s), (w2_q, w2_s) = q(w1f), q(w2f)
+    x = synth.make_hidden(T, H, seed)
+    tw, ids = synth.make_routing(T, E, K, seed=seed)
+    return x, tw, ids, (w1_q, w1_s, w2_q, w2_s)
+
+
+@pytest.mark.parametrize("per_tensor", [False, True])
+@pytest.mark.parametrize("T,H,I,E,K", [(1, 256, 128, 4, 2), (70, 384, 256, 8, 2), (300, 256, 384, 4, 2), (40, 2048, 512, 8, 4)])
+def test_row_scaled_fp8_weights_match_the_layer_oracle(per_tensor, T, H, I, E, K):
+    x, tw, ids, w = _rows_case(T, H, I, E, K, 60 + T, per_tensor)
+    ref = orc.torch_moe_oracle_fp8(x, *w, tw, ids, row_scaled=True)
+    qt = QuantType.per_Tensor if per_tensor else QuantType.per_Token
+    for combine in ("gather", "fused"):
+        w1_q, w1_s, w2_q, w2_s = (t.to(DEV) for t in w)
+        y = fused_moe(x.to(DEV), w1_q, w2_q, tw.to(DEV), ids.to(DEV), quant_type=qt, w1_scale=w1_s, w2_scale=w2_s,
+                      combine=combine)
+        torch.cuda.synchronize()
+        _close(y.cpu(), ref, f"row-scaled fp8 per_tensor={per_tensor} T={T} {combine}")
