@@ -378,9 +378,18 @@ struct QuantGeom {
   uint8_t* sf;
 };
 
-// block j (32 elements) of source row `srow` -> sorted row r, packed-FP4 terms
-__device__ __forceinline__ void quant_unit_fp4(const __nv_bfloat16* src, int64_t srow, int j, int64_t r,
-                                               const QuantGeom& g) {
+// One quantised unit = block j (32 elements) of a source row, held in registers between its computation (which
+// needs only the source row) and its store (which needs the sorted row): the decode path computes the unit
+// while the sort is still being worked out.
+struct QuantUnit {
+  uint4 q[8];        // packed-FP4 terms: q[t]; e4m3 terms: q[2t], q[2t+1]; 1x128: q[0], q[1]
+  int e[4];          // E8M0 exponents of the terms
+  float scale;       // 1x128: the block's fp32 scale
+};
+
+// block j of source row `srow`: packed-FP4 terms
+__device__ __forceinline__ void quant_compute_fp4(const __nv_bfloat16* src, int64_t srow, int j, const QuantGeom& g,
+                                                  QuantUnit& u) {
   float x[32];
   if (j * 32 < g.Kd) {
     load_block32(src + srow * g.Kd + j * 32, x);
@@ -388,39 +397,47 @@ __device__ __forceinline__ void quant_unit_fp4(const __nv_bfloat16* src, int64_t
 #pragma unroll
     for (int i = 0; i < 32; ++i) x[i] = 0.f;
   }
+#pragma unroll
+  for (int t = 0; t < 4; ++t)
+    if (t < g.NT) u.e[t] = (t + 1 < g.NT) ? quant_block32_fp4<true>(x, u.q[t]) : quant_block32_fp4<false>(x, u.q[t]);
+}
+__device__ __forceinline__ void quant_store_fp4(int j, int64_t r, const QuantGeom& g, const QuantUnit& u) {
   const int64_t term_stride = g.max_rows * (g.KP / 2);
-  for (int t = 0; t < g.NT; ++t) {
-    uint4 pk;
-    const int e = (t + 1 < g.NT) ? quant_block32_fp4<true>(x, pk) : quant_block32_fp4<false>(x, pk);
-    *reinterpret_cast<uint4*>(g.q + t * term_stride + r * (g.KP / 2) + j * 16) = pk;
-    g.sf[act_sf_index(r / g.B, j >> 2, g.KP / 128, g.B, g.NT, g.TS, t, (int)(r % g.B), j & 3)] = (uint8_t)e;
+#pragma unroll
+  for (int t = 0; t < 4; ++t) {
+    if (t < g.NT) {
+      *reinterpret_cast<uint4*>(g.q + t * term_stride + r * (g.KP / 2) + j * 16) = u.q[t];
+      g.sf[act_sf_index(r / g.B, j >> 2, g.KP / 128, g.B, g.NT, g.TS, t, (int)(r % g.B), j & 3)] = (uint8_t)u.e[t];
+    }
   }
 }
 
 // the same for two e4m3 terms (KP == Kd, a multiple of 128)
-__device__ __forceinline__ void quant_unit_e4m3(const __nv_bfloat16* src, int64_t srow, int j, int64_t r,
-                                                const QuantGeom& g) {
+__device__ __forceinline__ void quant_compute_e4m3(const __nv_bfloat16* src, int64_t srow, int j, const QuantGeom& g,
+                                                   QuantUnit& u) {
   float x[32];
   load_block32(src + srow * g.Kd + j * 32, x);
+  u.e[0] = quant_block32_e4m3<true>(x, u.q[0], u.q[1]);
+  u.e[1] = quant_block32_e4m3<false>(x, u.q[2], u.q[3]);
+}
+__device__ __forceinline__ void quant_store_e4m3(int j, int64_t r, const QuantGeom& g, const QuantUnit& u) {
   const int64_t term_stride = g.max_rows * g.Kd;
 #pragma unroll
   for (int t = 0; t < 2; ++t) {
-    uint4 q0, q1;
-    const int e = (t == 0) ? quant_block32_e4m3<true>(x, q0, q1) : quant_block32_e4m3<false>(x, q0, q1);
     uint4* dst = reinterpret_cast<uint4*>(g.q + t * term_stride + r * g.Kd + j * 32);
-    dst[0] = q0;
-    dst[1] = q1;
-    g.sf[act_sf_index(r / g.B, j >> 2, g.Kd / 128, g.B, 2, 128, t, (int)(r % g.B), j & 3)] = (uint8_t)e;
+    dst[0] = u.q[2 * t];
+    dst[1] = u.q[2 * t + 1];
+    g.sf[act_sf_index(r / g.B, j >> 2, g.Kd / 128, g.B, 2, 128, t, (int)(r % g.B), j & 3)] = (uint8_t)u.e[t];
   }
 }
 
 // Per-token, per-128-channel e4m3 with an fp32 scale = amax / 448 (1.0 for an all-zero block): the reference's
 // per_1x128 activation format (src/contrib/fused_moe.py:276-281,375-381).  Four neighbouring threads own the four
-// 32-element quarters of a 128-block and share its amax through shuffles, so every lane of the warp must call this
-// (`live` = this thread has a unit).  q [max_rows, Kd] bytes; scales fp32 [blocks][Kd/128][B] (one contiguous run
-// of B token scales per sorted block and k-block, the order the GEMM's producer copies them in).
-__device__ __forceinline__ void quant_unit_fp8_1x128(const __nv_bfloat16* src, int64_t srow, int j, int64_t r,
-                                                     const QuantGeom& g, bool live) {
+// 32-element quarters of a 128-block and share its amax through shuffles, so every lane of the warp must call the
+// compute step (`live` = this thread has a unit).  q [max_rows, Kd] bytes; scales fp32 [blocks][Kd/128][B] (one
+// contiguous run of B token scales per sorted block and k-block, the order the GEMM's producer copies them in).
+__device__ __forceinline__ void quant_compute_fp8_1x128(const __nv_bfloat16* src, int64_t srow, int j, const QuantGeom& g,
+                                                        bool live, QuantUnit& u) {
   float x[32];
   if (live) {
     load_block32(src + srow * g.Kd + j * 32, x);
@@ -441,13 +458,27 @@ __device__ __forceinline__ void quant_unit_fp8_1x128(const __nv_bfloat16* src, i
                                                               __NV_SATFINITE, __NV_E4M3);
     w[i >> 2] |= (uint32_t)pk << ((i & 2) * 8);
   }
-  if (live) {
-    uint4* dst = reinterpret_cast<uint4*>(g.q + r * g.Kd + j * 32);
-    dst[0] = make_uint4(w[0], w[1], w[2], w[3]);
-    dst[1] = make_uint4(w[4], w[5], w[6], w[7]);
-    if ((j & 3) == 0)
-      reinterpret_cast<float*>(g.sf)[((r / g.B) * (g.Kd / 128) + (j >> 2)) * g.B + (int)(r % g.B)] = scale;
-  }
+  u.q[0] = make_uint4(w[0], w[1], w[2], w[3]);
+  u.q[1] = make_uint4(w[4], w[5], w[6], w[7]);
+  u.scale = scale;
+}
+__device__ __forceinline__ void quant_store_fp8_1x128(int j, int64_t r, const QuantGeom& g, const QuantUnit& u) {
+  uint4* dst = reinterpret_cast<uint4*>(g.q + r * g.Kd + j * 32);
+  dst[0] = u.q[0];
+  dst[1] = u.q[1];
+  if ((j & 3) == 0)
+    reinterpret_cast<float*>(g.sf)[((r / g.B) * (g.Kd / 128) + (j >> 2)) * g.B + (int)(r % g.B)] = u.scale;
+}
+
+template <int FMT>    // 0: packed-FP4 terms, 1: two e4m3 terms, 2: e4m3 with fp32 scales per 1x128
+__device__ __forceinline__ void quant_compute(const __nv_bfloat16* src, int64_t srow, int j, const QuantGeom& g, bool live,
+                                              QuantUnit& u) {
+  if (FMT == 2) quant_compute_fp8_1x128(src, srow, j, g, live, u);
+  else if (live) { if (FMT == 0) quant_compute_fp4(src, srow, j, g, u); else quant_compute_e4m3(src, srow, j, g, u); }
+}
+template <int FMT>
+__device__ __forceinline__ void quant_store(int j, int64_t r, const QuantGeom& g, const QuantUnit& u) {
+  if (FMT == 0) quant_store_fp4(j, r, g, u); else if (FMT == 1) quant_store_e4m3(j, r, g, u); else quant_store_fp8_1x128(j, r, g, u);
 }
 
 // grid-stride zero fill in 16-byte vectors (the output buffer of the fused combine)
@@ -476,14 +507,13 @@ quant_rows_kernel(const __nv_bfloat16* __restrict__ src, int src_mode, const uin
     // only, and no kernel reads the columns of padding rows
     const bool live = u < total && kk < K && tok < T;
     const int64_t srow = (src_mode == 0) ? (int64_t)tok : ((int64_t)tok * K + kk);
-    if (FMT == 2) {
-      quant_unit_fp8_1x128(src, srow, j, r, g, live);
-    } else if (live) {
-      if (FMT == 0) quant_unit_fp4(src, srow, j, r, g); else quant_unit_e4m3(src, srow, j, r, g);
-    }
+    QuantUnit qu;
+    quant_compute<FMT>(src, srow, j, g, live, qu);
+    if (live) quant_store<FMT>(j, r, g, qu);
   }
 }
 
+static int small_grid(int64_t units) { return (int)std::max<int64_t>(1, (units + 255) / 256); }   // one unit per thread
 static int quant_grid(int64_t units) {
   return (int)std::max<int64_t>(1, std::min<int64_t>((units + 255) / 256, (int64_t)device_sm_count() * 16));
 }
@@ -559,6 +589,14 @@ sort_quant_small_kernel(const __nv_bfloat16* __restrict__ x, const int32_t* __re
   zero_fill(zero_ptr, zero_vec);
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int P = T * K, B = g.B;
+  // This thread's unit = (pair, 32-element block of the pair's token row).  Its source row is known without the
+  // sort, so the row is loaded and quantised into registers first: the loads are in flight while the sort runs.
+  const int nb = g.KP / 32;
+  const int my_u = min(blockIdx.x * 256 + tid, P * nb - 1);
+  const int my_pair = my_u / nb, my_j = my_u - my_pair * nb;
+  const bool have_unit = blockIdx.x * 256 + tid < P * nb;
+  QuantUnit qu;
+  quant_compute<FMT>(x, my_pair / K, my_j, g, have_unit, qu);
   const int T_live = (num_local != nullptr) ? min(T, max(num_local[0], 0)) : T;
   for (int e = tid; e < E; e += 256) cnt[e] = 0;
   const int my_e = sort_fetch_expert(ids, mask, tid, min(P, T_live * K), E);
@@ -636,19 +674,9 @@ sort_quant_small_kernel(const __nv_bfloat16* __restrict__ x, const int32_t* __re
     }
   }
   __syncthreads();
-  // quantise: one unit = (pair, 32-element block of its token's row)
-  const int nb = g.KP / 32;
-  for (int base = blockIdx.x * 256; base < P * nb; base += gridDim.x * 256) {     // block-uniform trip count
-    const int u = min(base + tid, P * nb - 1);
-    const int i = u / nb, j = u - i * nb;
-    const int r = pair_pos[i];
-    const bool live = base + tid < P * nb && r >= 0;
-    if (FMT == 2) {
-      quant_unit_fp8_1x128(x, i / K, j, max(r, 0), g, live);
-    } else if (live) {
-      if (FMT == 0) quant_unit_fp4(x, i / K, j, r, g); else quant_unit_e4m3(x, i / K, j, r, g);
-    }
-  }
+  // store the unit computed above at its pair's sorted row (pairs that were dropped have none)
+  const int r = pair_pos[my_pair];
+  if (have_unit && r >= 0) quant_store<FMT>(my_j, r, g, qu);
 }
 
 bool sort_quant_small_ok(int T, int K, int E) { return (int64_t)T * K <= kSmallPairs && E <= kSmallMaxE && T >= 1; }
@@ -664,18 +692,18 @@ int launch_sort_quant_small(int fmt, const void* x, const int32_t* ids, const fl
     B200_CHECK_ARG(NT >= 1 && NT <= 4 && Kd % 32 == 0, "sort_quant_small: terms %d / Kd %d", NT, Kd);
     const int KP = (int)round_up64(Kd, kKPad);
     QuantGeom g = {Kd, KP, B, NT, act_term_stride(B, NT, 2), max_rows, (uint8_t*)q, (uint8_t*)sf};
-    B200_CHECK_CUDA(launch_chained(sort_quant_small_kernel<0>, dim3(quant_grid((int64_t)T * K * (KP / 32))), dim3(256), 0,
+    B200_CHECK_CUDA(launch_chained(sort_quant_small_kernel<0>, dim3(small_grid((int64_t)T * K * (KP / 32))), dim3(256), 0,
                                    st, (const __nv_bfloat16*)x, ids, w, T, K, E, mask, num_local, sorted_ids, sorted_w,
                                    sorted_e, num_valid, loc, g, (uint4*)zero_ptr, zero_bytes / 16));
   } else {
     B200_CHECK_ARG(Kd % 128 == 0 && B <= 96, "sort_quant_small (e4m3): Kd %d / B %d", Kd, B);
     QuantGeom g = {Kd, Kd, B, fmt == 1 ? 2 : 1, 128, max_rows, (uint8_t*)q, (uint8_t*)sf};
     if (fmt == 1)
-      B200_CHECK_CUDA(launch_chained(sort_quant_small_kernel<1>, dim3(quant_grid((int64_t)T * K * (Kd / 32))), dim3(256), 0,
+      B200_CHECK_CUDA(launch_chained(sort_quant_small_kernel<1>, dim3(small_grid((int64_t)T * K * (Kd / 32))), dim3(256), 0,
                                      st, (const __nv_bfloat16*)x, ids, w, T, K, E, mask, num_local, sorted_ids, sorted_w,
                                      sorted_e, num_valid, loc, g, (uint4*)zero_ptr, zero_bytes / 16));
     else
-      B200_CHECK_CUDA(launch_chained(sort_quant_small_kernel<2>, dim3(quant_grid((int64_t)T * K * (Kd / 32))), dim3(256), 0,
+      B200_CHECK_CUDA(launch_chained(sort_quant_small_kernel<2>, dim3(small_grid((int64_t)T * K * (Kd / 32))), dim3(256), 0,
                                      st, (const __nv_bfloat16*)x, ids, w, T, K, E, mask, num_local, sorted_ids, sorted_w,
                                      sorted_e, num_valid, loc, g, (uint4*)zero_ptr, zero_bytes / 16));
   }
