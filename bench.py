@@ -60,7 +60,7 @@ def parse():
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--tokens", type=int, default=0, help="tokens per GPU per step (0 = the workload's own)")
     ap.add_argument("--workload", default="gptoss_decode", choices=["gptoss_decode", "gptoss_prefill", "dsv3_ep", "mixtral_skew"],
-                    help="gptoss_*: MXFP4 weights (BASELINE configs 1, 2); dsv3_ep: FP8 128x128 weights (config 3)")
+                    help="gptoss_*: MXFP4 weights (decode / prefill); dsv3_ep: FP8 128x128 weights; mixtral_skew: MXFP4, Zipf load")
     ap.add_argument("--experts", type=int, default=0,
                     help="override the number of experts (0 = the workload's own); for small profiling captures")
     ap.add_argument("--ep-chunks", type=int, default=0,
@@ -77,11 +77,12 @@ def parse():
     return ap.parse_args()
 
 
-def profiled_traffic(workload, T, E):
-    """DRAM bytes per gate-up launch from the committed ncu summary of this workload, else None."""
-    name = {("gptoss_decode", 64, 128): "gemm_mxf4_gptoss_decode_T64.md",
-            ("gptoss_prefill", 8192, 128): "gemm_mxf4_gptoss_prefill_T8192.md",
-            ("dsv3_ep", 4096, 32): "gemm_fp8_dsv3_E32_T4096.md"}.get((workload, T, E))
+def profiled_traffic(shape, T):
+    """DRAM bytes per gate-up launch (dram__bytes_read.sum + dram__bytes_write.sum of one ncu capture) from the
+    committed summary of this shape and token count, else None."""
+    name = {(2880, 2880, 128, 64, "mxfp4"): "gemm_mxf4_gptoss_decode_T64.md",
+            (2880, 2880, 128, 8192, "mxfp4"): "gemm_mxf4_gptoss_prefill_T8192.md",
+            (7168, 2048, 32, 4096, "fp8_128"): "gemm_fp8_dsv3_E32_T4096.md"}.get((shape.H, shape.I, shape.E, T, shape.wq))
     f = ROOT / "profiles" / name if name else None
     if f is not None and f.exists():
         m = re.search(r"roofline\.traffic[^\n]*gate-up (\d+) bytes", f.read_text())
@@ -429,7 +430,7 @@ def measure_gemms(case, T, args, steps, warmup, act_terms=0, act_quant=0):
     nominal = FP8_NOMINAL_TFLOPS if case.fp8 else FP4_NOMINAL_TFLOPS
     common = {"kernel": "moe_grouped_gemm_fp8_kernel<gate-up>" if case.fp8 else "moe_grouped_gemm_kernel<gate-up>",
               "us_per_launch": per_launch_s * 1e6, "us_per_launch_min": gu["min"] * 1e3,
-              "down_us_per_launch": dn["ms"] * 1e3, "traffic": profiled_traffic(case.workload, T, s.E)}
+              "down_us_per_launch": dn["ms"] * 1e3, "traffic": profiled_traffic(s, T) if not (act_terms == 1 or act_quant) else None}
     # weight-streaming regime (few rows per expert): HBM roofline; from 64 rows per expert on the launch is scored
     # against the dense tensor rate of its format, as the configurations state (the gpt-oss prefill shape sits at
     # the ridge: at the nominal rates its tensor time is 0.7 of its HBM time)

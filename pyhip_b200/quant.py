@@ -64,7 +64,7 @@ def e8m0_to_float(b: torch.Tensor) -> torch.Tensor:
 
 def quantize_mxfp4(w: torch.Tensor):
     """Quantise along the last axis in blocks of 32: shared scale 2**floor(log2(absmax/6)),
-    elements rounded to E2M1 with saturation (the rule BASELINE config 0 states).
+    elements rounded to E2M1 with saturation (the rule the tiny benchmark configuration states: floor(log2(absmax/6))).
 
     Returns (packed uint8 [..., K/2], scale uint8 [..., K/32])."""
     K = w.shape[-1]
