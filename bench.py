@@ -48,6 +48,7 @@ sys.path.insert(0, str(ROOT))
 METRIC = "moe_layer_tokens_per_s"
 UNIT = "tokens/s"
 L2_BYTES = 126e6
+PAIRS = {"auto": 0, "off": 1, "on": 2}
 FP4_NOMINAL_TFLOPS = 9000.0
 FP8_NOMINAL_TFLOPS = 4500.0
 
@@ -70,6 +71,8 @@ def parse():
     ap.add_argument("--act-terms", type=int, default=0, help="MXFP4 activation terms (0 = default 3; 1 = plain a4w4)")
     ap.add_argument("--act-quant", default="terms", choices=["terms", "1x128"],
                     help="FP8 weights: two e4m3 terms with E8M0 scales (default) or the per-token 1x128 fp32-scale format")
+    ap.add_argument("--cta-pairs", default="auto", choices=["auto", "off", "on"],
+                    help="MXFP4 GEMMs on CTA pairs (tcgen05.mma.cta_group::2): auto = in the compute-bound regime")
     ap.add_argument("--no-extras", action="store_true", help="only the headline workload (no sweep / prefill / config3 / config4)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-graph", action="store_true", help="time direct launches instead of CUDA-graph replays")
@@ -364,7 +367,7 @@ def measure_layer(case, T, args, steps, warmup, combine, act_terms=0, local=0, t
     B = pick_block(T, s.K, s.E, case.fmt)
     cm = _lib.COMBINE_FUSED if combine == "fused" else _lib.COMBINE_GATHER
     plan = get_plan(T, s.K, s.E, s.E, s.H, s.I, B, 0, 7.0, dev, act_terms=act_terms, weight_format=case.fmt, combine_mode=cm,
-                    act_quant=act_quant)
+                    act_quant=act_quant, cta_pairs=PAIRS[args.cta_pairs])
     y = torch.empty(T, s.H, dtype=torch.bfloat16, device=dev)
 
     def one_round():
@@ -415,7 +418,8 @@ def measure_gemms(case, T, args, steps, warmup, act_terms=0, act_quant=0):
     x, tw, ids = (t.to(dev) for t in case.inputs(T, 0))
     hit = len(set(ids.flatten().tolist()))
     B = pick_block(T, s.K, s.E, case.fmt)
-    plan = get_plan(T, s.K, s.E, s.E, s.H, s.I, B, 0, 7.0, dev, act_terms=act_terms, weight_format=case.fmt, act_quant=act_quant)
+    plan = get_plan(T, s.K, s.E, s.E, s.H, s.I, B, 0, 7.0, dev, act_terms=act_terms, weight_format=case.fmt, act_quant=act_quant,
+                    cta_pairs=PAIRS[args.cta_pairs])
     plan.sort(ids, tw)
     plan.quant_input(x)
     k = max(3, min(steps, 200 if T <= 512 else 20))
@@ -463,7 +467,7 @@ def measure_e2e(case, T, args, steps, warmup, combine, act_terms=0, act_quant='t
         tg = twh.to(dev, non_blocking=True)
         ig = idsh.to(dev, non_blocking=True)
         out = fused_moe(xg, w[0], w[2], tg, ig, quant_type=case.qt, w1_scale=w[1], w2_scale=w[3], combine=combine,
-                        act_terms=act_terms, act_quant=act_quant if case.fp8 else "terms")
+                        act_terms=act_terms, act_quant=act_quant if case.fp8 else "terms", cta_pairs=args.cta_pairs)
         yh.copy_(out, non_blocking=True)
 
     r = time_repeated(step_e2e, steps, warmup, total_ms=min(args.repeat_ms, 500.0))
@@ -598,7 +602,7 @@ def measure_ep(workload, args, rank, world, local, dev, dist, steps, warmup, tot
     w_full = make_w(E_local, H, I, seed=rank, device=dev, distinct=min(distinct, E_local))
     layer = ep.ExpertParallelMoE(w_full[0], w_full[1], w_full[2], w_full[3], E, rank, world, quant_type=qt,
                                  dispatch_chunks=args.ep_chunks or None, tokens_per_rank=T, combine=args.combine,
-                                 **({'act_quant': args.act_quant} if fp8 else {}))
+                                 **({'act_quant': args.act_quant} if fp8 else {'cta_pairs': args.cta_pairs}))
     x = synth.make_hidden(T, H, rank)
     tw, ids = synth.make_routing(T, E, K, shape.routing, rank, skew_seed=0)
     xd, twd, idsd = x.to(dev), tw.to(dev), ids.to(dev)

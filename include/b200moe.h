@@ -64,6 +64,9 @@ typedef struct b200moe_shape {
   int32_t combine_mode;
   int32_t act_quant;
   int32_t doweight_stage1;
+  int32_t cta_pairs;   /* MXFP4 GEMMs on CTA pairs (tcgen05.mma.cta_group::2: two CTAs of a cluster share one token tile, each
+                          fetching half of it): 0 = in the compute-bound regime (token tiles of 64 rows and more whose
+                          activation terms are separate instructions), 1 = never, 2 = wherever the tile allows it */
 } b200moe_shape;
 
 /* Byte sizes and offsets of the caller-provided workspace (all offsets 1024-byte aligned). */

@@ -35,7 +35,7 @@ class Shape(ctypes.Structure):
                 ("B", ctypes.c_int32), ("weight_format", ctypes.c_int32),
                 ("activation", ctypes.c_int32), ("swiglu_limit", ctypes.c_float),
                 ("act_terms", ctypes.c_int32), ("combine_mode", ctypes.c_int32),
-                ("act_quant", ctypes.c_int32), ("doweight_stage1", ctypes.c_int32)]
+                ("act_quant", ctypes.c_int32), ("doweight_stage1", ctypes.c_int32), ("cta_pairs", ctypes.c_int32)]
 
 
 _WS_FIELDS = ["total_bytes", "max_rows", "off_sorted_ids", "off_sorted_w", "off_sorted_e",

@@ -45,6 +45,7 @@ static int check_shape(const b200moe_shape* s) {
                  "act_quant 1x128 belongs to the FP8 128x128 weight format (MXFP4 weights take act_terms)");
   B200_CHECK_ARG(s->doweight_stage1 == 0 || s->doweight_stage1 == 1, "doweight_stage1=%d must be 0 or 1",
                  s->doweight_stage1);
+  B200_CHECK_ARG(s->cta_pairs >= 0 && s->cta_pairs <= 2, "cta_pairs=%d must be 0 (auto), 1 (off) or 2 (on)", s->cta_pairs);
   return 0;
 }
 
@@ -210,6 +211,7 @@ int b200moe_quant_rows_e4m3(const void* src_bf16, int32_t src_mode, const uint32
 static void fill_common(GemmArgs& g, const b200moe_shape* s, const b200moe_workspace* ws, uint8_t* base) {
   g.N = s->B;
   g.act_quant = s->act_quant;
+  g.pair_mode = s->cta_pairs;
   g.w_row_scaled = s->weight_format == B200MOE_W_FP8_ROW;
   g.NT = terms_of(s);
   g.E = s->E;

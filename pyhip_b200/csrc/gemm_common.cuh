@@ -101,6 +101,19 @@ __device__ __forceinline__ void umma_mxf4(uint32_t d_tmem, uint32_t a_lo, uint32
         "r"(kDescHiSw)
       : "memory");
 }
+// the same across a CTA pair: M = 256 (128 rows from each CTA's shared memory), N/2 token rows from each CTA
+__device__ __forceinline__ void umma_mxf4_pair(uint32_t d_tmem, uint32_t a_lo, uint32_t b_lo, uint32_t idesc,
+                                               uint32_t sfa_tmem, uint32_t sfb_tmem, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t.reg .b64 da, db;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "mov.b64 da, {%1, %7};\n\t"
+      "mov.b64 db, {%2, %7};\n\t"
+      "tcgen05.mma.cta_group::2.kind::mxf4.block_scale.block32 [%0], da, db, %3, [%5], [%6], p;\n\t}"
+      ::"r"(d_tmem), "r"(a_lo), "r"(b_lo), "r"(idesc), "r"(accumulate), "r"(sfa_tmem), "r"(sfb_tmem),
+        "r"(kDescHiSw)
+      : "memory");
+}
 __device__ __forceinline__ void utccp_sf(uint32_t taddr, uint32_t lo) {
   asm volatile(
       "{\n\t.reg .b64 d;\n\t"

@@ -114,6 +114,7 @@ struct GemmArgs {
   int weight_stage1;       // gate-up: apply the routing weight to h
   int act_quant;           // FP8 kernel: 0 = two e4m3 terms with E8M0 scales, 1 = one e4m3 term with fp32 scales per 1x128
   int w_row_scaled;        // FP8 kernel: w_scale holds one fp32 scale per weight row [E, parts*rows] (not per 128x128 block)
+  int pair_mode;           // MXFP4 kernel: CTA pairs (cta_group::2): 0 = in the compute-bound regime, 1 = never, 2 = wherever possible
 };
 int launch_grouped_gemm(const GemmArgs& a, cudaStream_t st);
 // FP8 128x128-block variant (moe_gemm_fp8_sm100.cu): w_data = e4m3 bytes [E, parts*rows, Kd], w_scale = fp32
@@ -133,19 +134,31 @@ int device_sm_count();
 // Launch `kernel` so that it may begin (prologue only: every kernel of this library calls
 // grid_dep_wait() before it touches global memory) while the previous kernel in the stream drains.
 template <typename... KArgs, typename... Args>
-inline cudaError_t launch_chained(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t st,
-                                  Args&&... args) {
+inline cudaError_t launch_chained_cluster(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t st,
+                                          int cluster_x, Args&&... args) {
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = grid;
   cfg.blockDim = block;
   cfg.dynamicSmemBytes = smem;
   cfg.stream = st;
-  cudaLaunchAttribute at[1];
+  cudaLaunchAttribute at[2];
   at[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
   at[0].val.programmaticStreamSerializationAllowed = 1;
-  cfg.attrs = at;
   cfg.numAttrs = 1;
+  if (cluster_x > 1) {          // thread-block clusters of cluster_x CTAs along x (grid.x is a multiple of it)
+    at[1].id = cudaLaunchAttributeClusterDimension;
+    at[1].val.clusterDim.x = (unsigned)cluster_x;
+    at[1].val.clusterDim.y = 1;
+    at[1].val.clusterDim.z = 1;
+    cfg.numAttrs = 2;
+  }
+  cfg.attrs = at;
   return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+}
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch_chained(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t st,
+                                  Args&&... args) {
+  return launch_chained_cluster(kernel, grid, block, smem, st, 1, static_cast<Args&&>(args)...);
 }
 int run_debug_probe(int which, const void* in, void* out, cudaStream_t st);
 

@@ -31,6 +31,13 @@
 //               tensor memory (tcgen05.st, one warp per lane quadrant, two TMEM scale buffers).
 //               tcgen05.cp would do the same copy but runs in the MMA's own in-order pipe at
 //               ~70-100 cycles per chunk, which was the limiter at small token tiles.
+// In the compute-bound regime (PAIR) two CTAs of a cluster share one token tile: tcgen05.mma.cta_group::2 with
+// M = 256 takes 128 weight rows from each CTA's shared memory and HALF of the token rows from each, so every CTA
+// fetches its own weight tiles and only half of the token tile (the launches there sit on the L2-to-SM path, and the
+// token tile is more than half of a stage's bytes with three terms).  Each CTA keeps its own accumulators, scale
+// columns, scale loaders and epilogue for ITS 128-row weight tiles; the even CTA issues all MMAs, its commits arrive
+// on both CTAs' barriers, and the odd CTA's scale loaders and epilogue warps arrive on the even CTA's barriers.  No
+// multicast loads anywhere.
 // Persistent CTAs walk the work list (sorted block, weight tile pair) in block-major order so that
 // CTAs running at the same time share activation tiles and neighbouring blocks of an expert share
 // weight tiles in L2.
@@ -84,6 +91,7 @@ struct GemmParams {
   const float* bias;       // per-expert bias: gate-up [E, 2*rows] (gate then up), down [E, rows]; or null
   __nv_bfloat16* y;        // down, fused combine: zeroed [T, rows] output accumulated with bf16x2 reductions; or null
   int weight_stage1;       // gate-up: multiply h by the routing weight (the down stage then applies none)
+  int MTp;                 // PAIR: work items per sorted block (two consecutive weight-tile items, one per CTA of the pair)
 };
 
 struct SmemCtl {
@@ -102,10 +110,10 @@ struct StageGeom {
   int a_bytes, b_bytes, sfa_bytes, sfb_bytes, stage_bytes;
   uint32_t tx_bytes;
 };
-__host__ __device__ inline StageGeom stage_geom(int parts, int B, int NT) {
+__host__ __device__ inline StageGeom stage_geom(int parts, int B, int NT, bool pair = false) {
   StageGeom g;
   g.a_bytes = parts * kATileBytes;
-  g.b_bytes = NT * B * kRowBytes;
+  g.b_bytes = NT * (pair ? B / 2 : B) * kRowBytes;     // a CTA of a pair holds half of the token rows
   g.sfa_bytes = kSub * parts * kSfChunk;
   g.sfb_bytes = kSub * act_sf_chunks(NT, act_term_stride(B, NT, parts)) * kSfChunk;
   g.stage_bytes = (g.a_bytes + g.b_bytes + g.sfa_bytes + g.sfb_bytes + 1023) & ~1023;
@@ -113,19 +121,21 @@ __host__ __device__ inline StageGeom stage_geom(int parts, int B, int NT) {
   return g;
 }
 
-template <bool GATEUP>
+template <bool GATEUP, bool PAIR>
 __global__ void __launch_bounds__(kThreads, 1)
 moe_grouped_gemm_kernel(const __grid_constant__ GemmParams p) {
   constexpr int NA = 2;   // weight tiles per stage
+  const uint32_t cta_rank = PAIR ? cluster_cta_rank() : 0u;    // 0: the CTA that issues the pair's MMAs
+  const int NB = PAIR ? p.B / 2 : p.B;                         // token rows of the stage's tile held by THIS CTA
   extern __shared__ uint8_t smem_raw[];
   // 1024-byte alignment covers every swizzle atom used here
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   SmemCtl* ctl = reinterpret_cast<SmemCtl*>(smem);
   const uint32_t stage0 = smem_u32(smem) + 1024;
   const int B = p.B, NT = p.NT;
-  const StageGeom geo = stage_geom(NA, B, NT);
+  const StageGeom geo = stage_geom(NA, B, NT, PAIR);
   const int S = p.stages;
-  const bool merged = act_merged(B, NT, NA);   // all terms in one MMA (N = NT*B)
+  const bool merged = !PAIR && act_merged(B, NT, NA);   // all terms in one MMA (N = NT*B)
   const int ncol = merged ? NT * B : B;        // TMEM columns of one accumulator
   const int acc_cols = NA * ncol;
   const int n_acc = (2 * acc_cols <= kAccColsLimit) ? 2 : 1;
@@ -141,8 +151,9 @@ moe_grouped_gemm_kernel(const __grid_constant__ GemmParams p) {
     }
     for (int a = 0; a < 2; ++a) {
       mbar_init(smem_u32(&ctl->tmem_full[a]), 2);
-      mbar_init(smem_u32(&ctl->tmem_empty[a]), 8);
-      mbar_init(smem_u32(&ctl->sf_full[a]), 4);
+      // PAIR: the issuing CTA waits for the epilogue warps and the scale loaders of BOTH CTAs
+      mbar_init(smem_u32(&ctl->tmem_empty[a]), PAIR ? 16 : 8);
+      mbar_init(smem_u32(&ctl->sf_full[a]), PAIR ? 8 : 4);
       mbar_init(smem_u32(&ctl->sf_empty[a]), 2);
     }
     ctl->abort_word = 0;
@@ -150,11 +161,17 @@ moe_grouped_gemm_kernel(const __grid_constant__ GemmParams p) {
     fence_proxy_async_smem();
   }
   if (warp == 1) {
-    tmem_alloc(smem_u32(&ctl->tmem_base), kTmemCols);
-    tmem_relinquish();
+    if (PAIR) {
+      tmem_alloc_pair(smem_u32(&ctl->tmem_base), kTmemCols);
+      tmem_relinquish_pair();
+    } else {
+      tmem_alloc(smem_u32(&ctl->tmem_base), kTmemCols);
+      tmem_relinquish();
+    }
   }
   tc_fence_before_sync();
   __syncthreads();
+  if (PAIR) cluster_sync_all();      // the partner's barriers exist before anything arrives on them
   tc_fence_after_sync();
   const uint32_t tmem_base = ctl->tmem_base;
   // This CTA holds its tensor memory now, so CTAs of the next kernel may be scheduled beside it without
@@ -164,7 +181,13 @@ moe_grouped_gemm_kernel(const __grid_constant__ GemmParams p) {
 
   const int64_t rows_live = min((int64_t)p.num_valid[0], p.max_rows);
   const int n_blocks = (int)(rows_live / B);
-  const int total_work = n_blocks * p.MT;
+  // work items per sorted block, and how far apart a CTA's consecutive items are: a pair of CTAs takes ONE item (two
+  // consecutive weight-tile items of the unpaired numbering, one per CTA)
+  const int items_per_block = PAIR ? p.MTp : p.MT;
+  const int total_work = n_blocks * items_per_block;
+  const int total_work_mma = (PAIR && cta_rank != 0) ? 0 : total_work;     // only the even CTA of a pair issues MMAs
+  const int w_first = PAIR ? (int)(blockIdx.x >> 1) : (int)blockIdx.x;
+  const int w_step = PAIR ? (int)(gridDim.x >> 1) : (int)gridDim.x;
 
   if (warp == 0) {
     // ------------------------------------------------------------------ TMA producer
@@ -177,12 +200,15 @@ moe_grouped_gemm_kernel(const __grid_constant__ GemmParams p) {
       bool ok = true;
       PROF_DECL(t_wait);
       const int64_t sfa_step = geo.sfa_bytes;
-      for (int w = blockIdx.x; w < total_work && ok; w += gridDim.x) {
-        const int b = w / p.MT, m = w - b * p.MT;
+      for (int w = w_first; w < total_work && ok; w += w_step) {
+        // (PAIR: item w covers weight-tile items 2*mp and 2*mp + 1 of the block; this CTA takes the one of its rank)
+        const int b = w / items_per_block, m = PAIR ? 2 * (w - b * items_per_block) + (int)cta_rank : w - b * items_per_block;
+        const bool tile_live = m < p.MT;
+        const int ms = tile_live ? m : p.MT - 1;       // a tile beyond the last one borrows its neighbour's (finite) scales
         int e = p.sorted_e[b];
         if (e < 0 || e >= p.E) { p.status[2] = 1; e = 0; }
         const int r0 = b * B;
-        const uint8_t* sfa = p.w_scale + ((int64_t)e * p.MT + m) * p.KB * sfa_step;   // KB stages of kSub k-blocks
+        const uint8_t* sfa = p.w_scale + ((int64_t)e * p.MT + ms) * p.KB * sfa_step;   // KB stages of kSub k-blocks
         const uint8_t* sfb = p.asf + (int64_t)b * p.KB * geo.sfb_bytes;
         for (int kb = 0; kb < p.KB; ++kb) {
           const long long tw0 = PROF_NOW();
@@ -190,9 +216,19 @@ moe_grouped_gemm_kernel(const __grid_constant__ GemmParams p) {
           PROF_ADD(t_wait, tw0);
           const uint32_t st = stage0 + (uint32_t)stage * geo.stage_bytes;
           const uint32_t full = smem_u32(&ctl->full[stage]);
-          mbar_expect_tx(full, geo.tx_bytes);
-          tma_load_4d(st, &p.tmW, full, kb * kTileK, m * (GATEUP ? kTileM : 2 * kTileM), 0, e);
-          tma_load_3d(st + geo.a_bytes, &p.tmA, full, kb * kTileK, r0, 0);
+          if (PAIR) {
+            // The weight tiles and this CTA's half of the token tile complete bytes on the ISSUING CTA's barrier (it
+            // alone consumes them, through the MMAs); the scale chunks are consumed by this CTA's own scale loaders
+            // and complete on the local barrier.
+            const uint32_t ab = (uint32_t)(geo.a_bytes + geo.b_bytes), sf = (uint32_t)(geo.sfa_bytes + geo.sfb_bytes);
+            mbar_expect_tx(full, cta_rank == 0 ? 2 * ab + sf : sf);
+            tma_load_4d_pair(st, &p.tmW, full, kb * kTileK, m * (GATEUP ? kTileM : 2 * kTileM), 0, e);
+            tma_load_3d_pair(st + geo.a_bytes, &p.tmA, full, kb * kTileK, r0 + (int)cta_rank * NB, 0);
+          } else {
+            mbar_expect_tx(full, geo.tx_bytes);
+            tma_load_4d(st, &p.tmW, full, kb * kTileK, m * (GATEUP ? kTileM : 2 * kTileM), 0, e);
+            tma_load_3d(st + geo.a_bytes, &p.tmA, full, kb * kTileK, r0, 0);
+          }
           bulk_load(st + geo.a_bytes + geo.b_bytes, sfa, (uint32_t)geo.sfa_bytes, full);
           bulk_load(st + geo.a_bytes + geo.b_bytes + geo.sfa_bytes, sfb, (uint32_t)geo.sfb_bytes, full);
           sfa += sfa_step;
@@ -225,8 +261,8 @@ moe_grouped_gemm_kernel(const __grid_constant__ GemmParams p) {
     uint32_t idesc[2];
 #pragma unroll
     for (int s = 0; s < 2; ++s)
-      idesc[s] = make_idesc_block_scaled(kFmtE2M1_mxf4, kFmtE2M1_mxf4, kTileM, (uint32_t)ncol, 2 * s, 2 * s);
-    const uint32_t term_lo = (uint32_t)(B * kRowBytes) >> 4;   // descriptor step from one term to the next
+      idesc[s] = make_idesc_block_scaled(kFmtE2M1_mxf4, kFmtE2M1_mxf4, PAIR ? 2 * kTileM : kTileM, (uint32_t)ncol, 2 * s, 2 * s);
+    const uint32_t term_lo = (uint32_t)(NB * kRowBytes) >> 4;   // descriptor step from one term to the next
     int stage = 0;
     uint32_t phase = 0;
     int acc = 0;
@@ -235,6 +271,7 @@ moe_grouped_gemm_kernel(const __grid_constant__ GemmParams p) {
     bool ok = true;
     PROF_DECL(t_wait_acc);
     PROF_DECL(t_wait_full);
+    PROF_DECL(t_wait_sf);
     const long long t_begin = PROF_NOW();
     (void)t_begin;
     // Per-term MMAs cover only the live rows of the block (rounded up to 16): the padding rows that end an
@@ -242,18 +279,19 @@ moe_grouped_gemm_kernel(const __grid_constant__ GemmParams p) {
     // fetched while the current one is multiplied, so the count is ready without a stall.
     uint32_t nid[4];
     auto fetch_ids = [&](int w, uint32_t (&r)[4]) {
-      const int r0 = (w / p.MT) * B;
+      const int r0 = (w / items_per_block) * B;
 #pragma unroll
       for (int q = 0; q < 4; ++q) r[q] = (w < total_work && q * 32 + lane < B) ? p.sorted_ids[r0 + q * 32 + lane] : 0xFFFFFFFFu;
     };
-    fetch_ids(blockIdx.x, nid);
-    for (int w = blockIdx.x; w < total_work && ok; w += gridDim.x) {
+    fetch_ids(w_first, nid);
+    for (int w = w_first; w < total_work_mma && ok; w += w_step) {
       int nlive = 0;
 #pragma unroll
       for (int q = 0; q < 4; ++q)
         nlive += __popc(__ballot_sync(0xffffffffu, (int)(nid[q] >> 24) < p.topk && (int)(nid[q] & 0xFFFFFFu) < p.T));
-      fetch_ids(w + gridDim.x, nid);
-      const uint32_t n_mma = merged ? (uint32_t)ncol : (uint32_t)min(B, max(16, (nlive + 15) & ~15));
+      fetch_ids(w + w_step, nid);
+      // (PAIR: the token rows are split between the CTAs at a fixed row, so the instruction always spans the tile)
+      const uint32_t n_mma = (merged || PAIR) ? (uint32_t)ncol : (uint32_t)min(B, max(16, (nlive + 15) & ~15));
       uint32_t idesc_w[2];
 #pragma unroll
       for (int s = 0; s < 2; ++s) idesc_w[s] = (idesc[s] & ~(0x3Fu << 17)) | ((n_mma >> 3) << 17);
@@ -265,8 +303,10 @@ moe_grouped_gemm_kernel(const __grid_constant__ GemmParams p) {
       for (int kb = 0; kb < p.KB; ++kb) {
         const long long tf0 = PROF_NOW();
         if (!mbar_wait(smem_u32(&ctl->full[stage]), phase, abort_word, 0x300 + stage)) { ok = false; break; }
-        if (!mbar_wait(smem_u32(&ctl->sf_full[sf_buf]), sf_phase, abort_word, 0x500 + sf_buf)) { ok = false; break; }
         PROF_ADD(t_wait_full, tf0);
+        const long long ts0 = PROF_NOW();
+        if (!mbar_wait(smem_u32(&ctl->sf_full[sf_buf]), sf_phase, abort_word, 0x500 + sf_buf)) { ok = false; break; }
+        PROF_ADD(t_wait_sf, ts0);
         tc_fence_after_sync();
         __syncwarp();
         if (elect_one()) {       // one issuing lane; descriptors stay in uniform registers
@@ -293,13 +333,19 @@ moe_grouped_gemm_kernel(const __grid_constant__ GemmParams p) {
               for (int t = 0; t < kMaxTerms; ++t) {
                 if (t < NT && s < nsteps) {
                   const uint32_t accum = (s == 0 && t == 0) ? first : 1u;
-                  umma_mxf4(d0, a_lo + 2 * s, b_lo + t * term_lo + 2 * s, idesc_w[s & 1], sa, sb + 4 * t, accum);
+                  if (PAIR) umma_mxf4_pair(d0, a_lo + 2 * s, b_lo + t * term_lo + 2 * s, idesc_w[s & 1], sa, sb + 4 * t, accum);
+                  else umma_mxf4(d0, a_lo + 2 * s, b_lo + t * term_lo + 2 * s, idesc_w[s & 1], sa, sb + 4 * t, accum);
                 }
               }
             }
           }
-          tc_commit(smem_u32(&ctl->empty[stage]));
-          tc_commit(smem_u32(&ctl->sf_empty[sf_buf]));
+          if (PAIR) {      // both CTAs' producers and scale loaders wait for these
+            tc_commit_pair(smem_u32(&ctl->empty[stage]));
+            tc_commit_pair(smem_u32(&ctl->sf_empty[sf_buf]));
+          } else {
+            tc_commit(smem_u32(&ctl->empty[stage]));
+            tc_commit(smem_u32(&ctl->sf_empty[sf_buf]));
+          }
         }
         __syncwarp();
         if (sf_buf == 1) sf_phase ^= 1;
@@ -307,15 +353,18 @@ moe_grouped_gemm_kernel(const __grid_constant__ GemmParams p) {
         if (++stage == S) { stage = 0; phase ^= 1; }
       }
       if (!ok) break;
-      if (lane == 0) tc_commit(smem_u32(&ctl->tmem_full[acc]));
+      if (lane == 0) {
+        if (PAIR) tc_commit_pair(smem_u32(&ctl->tmem_full[acc])); else tc_commit(smem_u32(&ctl->tmem_full[acc]));
+      }
       __syncwarp();
       if (n_acc == 2) { acc ^= 1; if (acc == 0) acc_phase ^= 1; } else { acc_phase ^= 1; }
     }
 #ifdef B200MOE_PROFILE
-    if (blockIdx.x == 0 && lane == 0 && part == 0) {   // kilo-cycles of an MMA warp: total, waiting for data, for TMEM
+    if (blockIdx.x == 0 && lane == 0 && part == 0) {   // kilo-cycles of an MMA warp: total, waiting for data, for TMEM, for scale columns (status[10])
       p.status[5] = (int32_t)((clock64() - t_begin) >> 10);
       p.status[6] = (int32_t)(t_wait_full >> 10);
       p.status[7] = (int32_t)(t_wait_acc >> 10);
+      p.status[10] = (int32_t)(t_wait_sf >> 10);
     }
 #endif
   } else if (warp >= 10) {
@@ -328,7 +377,7 @@ moe_grouped_gemm_kernel(const __grid_constant__ GemmParams p) {
     int stage = 0;
     uint32_t phase = 0, sf_buf = 0, sf_phase = 0;
     bool ok = true;
-    for (int w = blockIdx.x; w < total_work && ok; w += gridDim.x) {
+    for (int w = w_first; w < total_work && ok; w += w_step) {
       for (int kb = 0; kb < p.KB; ++kb) {
         if (!mbar_wait(smem_u32(&ctl->full[stage]), phase, abort_word, 0x600 + stage) ||
             !mbar_wait(smem_u32(&ctl->sf_empty[sf_buf]), sf_phase ^ 1, abort_word, 0x700 + sf_buf)) {
@@ -353,7 +402,9 @@ moe_grouped_gemm_kernel(const __grid_constant__ GemmParams p) {
         tmem_st_wait();
         tc_fence_before_sync();
         __syncwarp();
-        if (lane == 0) mbar_arrive(smem_u32(&ctl->sf_full[sf_buf]));
+        if (lane == 0) {
+          if (PAIR) mbar_arrive_leader(smem_u32(&ctl->sf_full[sf_buf])); else mbar_arrive(smem_u32(&ctl->sf_full[sf_buf]));
+        }
         if (sf_buf == 1) sf_phase ^= 1;
         sf_buf ^= 1;
         if (++stage == S) { stage = 0; phase ^= 1; }
@@ -378,8 +429,9 @@ moe_grouped_gemm_kernel(const __grid_constant__ GemmParams p) {
     PROF_DECL(t_wait_epi);
     const long long t_begin_epi = PROF_NOW();
     (void)t_begin_epi;
-    for (int w = blockIdx.x; w < total_work; w += gridDim.x) {
-      const int b = w / p.MT, m = w - b * p.MT;
+    for (int w = w_first; w < total_work; w += w_step) {
+      const int b = w / items_per_block, m = PAIR ? 2 * (w - b * items_per_block) + (int)cta_rank : w - b * items_per_block;
+      const bool tile_live = m < p.MT;      // PAIR: the odd CTA's tile of the last item may lie beyond the weight rows
       const int r0 = b * B;
       // output feature of this thread: gate-up pairs gate/up of feature j; down holds j and j+128
       const int j = (GATEUP ? m * kTileM : m * 2 * kTileM) + row_local;
@@ -389,6 +441,7 @@ moe_grouped_gemm_kernel(const __grid_constant__ GemmParams p) {
         const uint32_t id = (q + lane < B) ? p.sorted_ids[r0 + q + lane] : 0xFFFFFFFFu;
         nvalid += __popc(__ballot_sync(0xffffffffu, (int)(id >> 24) < p.topk && (int)(id & 0xFFFFFFu) < p.T));
       }
+      if (!tile_live) nvalid = 0;       // nothing to read or store; the barrier protocol below still runs
       // all eight warps take the same decision, so nobody is left alone at a later barrier
       const long long te0 = PROF_NOW();
       const bool ok = mbar_wait(smem_u32(&ctl->tmem_full[acc]), acc_phase, abort_word, 0x400 + acc);
@@ -521,7 +574,9 @@ moe_grouped_gemm_kernel(const __grid_constant__ GemmParams p) {
       }
       tc_fence_before_sync();
       if (fused) epi_sync(); else __syncwarp();      // staging tile complete, TMEM reads done
-      if (lane == 0) mbar_arrive(smem_u32(&ctl->tmem_empty[acc]));
+      if (lane == 0) {       // PAIR: the issuing CTA reuses the accumulators once both CTAs' epilogues have read theirs
+        if (PAIR) mbar_arrive_leader(smem_u32(&ctl->tmem_empty[acc])); else mbar_arrive(smem_u32(&ctl->tmem_empty[acc]));
+      }
       if (n_acc == 2) { acc ^= 1; if (acc == 0) acc_phase ^= 1; } else { acc_phase ^= 1; }
 
       if (fused) {
@@ -582,7 +637,10 @@ moe_grouped_gemm_kernel(const __grid_constant__ GemmParams p) {
     p.status[0] = (int32_t)ctl->abort_word;
     p.status[1] = (int32_t)blockIdx.x;
   }
-  if (warp == 1) tmem_dealloc(tmem_base, kTmemCols);
+  if (PAIR) cluster_sync_all();     // neither CTA leaves while the other's MMAs or barrier arrivals may still touch it
+  if (warp == 1) {
+    if (PAIR) tmem_dealloc_pair(tmem_base, kTmemCols); else tmem_dealloc(tmem_base, kTmemCols);
+  }
 }
 
 // ------------------------------------------------------------------------------------
@@ -674,50 +732,47 @@ int launch_grouped_gemm(const GemmArgs& a, cudaStream_t st) {
                            CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, "weights");
     if (rc) return rc;
   }
+  // CTA pairs (tcgen05.mma.cta_group::2) in the compute-bound regime: large token tiles whose terms are separate
+  // instructions.  pair_mode 0 = this choice, 1 = never, 2 = wherever the tile allows it.
+  // (a single term is the same instruction stream stacked or not, and its scale layout is the same too)
+  const bool pair_ok = (!act_merged(a.N, a.NT, 2) || a.NT == 1) && a.N % 16 == 0 && device_sm_count() >= 2;
+  const bool pair = pair_ok && a.pair_mode != 1 && (a.pair_mode == 2 || a.N >= 64);
+  p.MTp = (p.MT + 1) / 2;
   {
     cuuint64_t dims[3] = {(cuuint64_t)KP, (cuuint64_t)a.max_rows, (cuuint64_t)a.NT};
     cuuint64_t strides[2] = {(cuuint64_t)KP / 2, (cuuint64_t)(KP / 2) * (cuuint64_t)a.max_rows};
-    cuuint32_t box[3] = {kTileK, (cuuint32_t)a.N, (cuuint32_t)a.NT};
+    cuuint32_t box[3] = {kTileK, (cuuint32_t)(pair ? a.N / 2 : a.N), (cuuint32_t)a.NT};   // a CTA of a pair fetches half of the rows
     int rc = encode_map_sw(&p.tmA, CU_TENSOR_MAP_DATA_TYPE_16U4_ALIGN8B, 3, a.a_q, dims, strides, box,
                            CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, "activations");
     if (rc) return rc;
   }
 
-  const StageGeom geo = stage_geom(2, a.N, a.NT);
+  const StageGeom geo = stage_geom(2, a.N, a.NT, pair);
   int staging = (a.gateup && a.h_out == nullptr) ? a.N * kStagePitch : 0;
   int stages = (kSmemLimit - 2048 - staging) / geo.stage_bytes;
   // two stages are too few to cover the load latency: where moving the staging tile of the fused epilogue to
-  // global memory (one tile per CTA, L2-resident) buys a third, do that
-  if (staging && stages < 3 && (kSmemLimit - 2048) / geo.stage_bytes >= 3 && a.gstage != nullptr &&
+  // global memory (one tile per CTA, L2-resident) buys a third (a fourth for CTA pairs), do that
+  const int stages_g = (kSmemLimit - 2048) / geo.stage_bytes;
+  if (staging && stages < (pair ? 4 : 3) && stages_g > stages && a.gstage != nullptr &&
       a.gstage_bytes >= (int64_t)device_sm_count() * staging) {
     p.gstage = (uint8_t*)a.gstage;
     staging = 0;
-    stages = (kSmemLimit - 2048) / geo.stage_bytes;
+    stages = stages_g;
   }
   stages = std::min(stages, kMaxStages);
   B200_CHECK_ARG(stages >= 2, "grouped gemm: tile does not fit shared memory");
   p.stages = stages;
   const size_t smem = 2048 + (size_t)stages * geo.stage_bytes + staging;
 
-  const int64_t max_work = (a.max_rows / a.N) * p.MT;
-  const int grid = (int)std::min<int64_t>(device_sm_count(), std::max<int64_t>(max_work, 1));
-  static bool attr[2][64] = {};
-  int dev = 0;
-  cudaGetDevice(&dev);
-  bool& done = attr[a.gateup ? 1 : 0][dev & 63];
-  if (a.gateup) {
-    if (!done)
-      B200_CHECK_CUDA(cudaFuncSetAttribute(moe_grouped_gemm_kernel<true>,
-                                           cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemLimit));
-    done = true;
-    B200_CHECK_CUDA(launch_chained(moe_grouped_gemm_kernel<true>, dim3(grid), dim3(kThreads), smem, st, p));
-  } else {
-    if (!done)
-      B200_CHECK_CUDA(cudaFuncSetAttribute(moe_grouped_gemm_kernel<false>,
-                                           cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemLimit));
-    done = true;
-    B200_CHECK_CUDA(launch_chained(moe_grouped_gemm_kernel<false>, dim3(grid), dim3(kThreads), smem, st, p));
-  }
+  const int64_t max_work = (a.max_rows / a.N) * (pair ? p.MTp : p.MT);
+  const int sms = device_sm_count();
+  const int grid = pair ? 2 * (int)std::min<int64_t>(sms / 2, std::max<int64_t>(max_work, 1))
+                        : (int)std::min<int64_t>(sms, std::max<int64_t>(max_work, 1));
+  void (*kernel)(GemmParams) = a.gateup ? (pair ? moe_grouped_gemm_kernel<true, true> : moe_grouped_gemm_kernel<true, false>)
+                                        : (pair ? moe_grouped_gemm_kernel<false, true> : moe_grouped_gemm_kernel<false, false>);
+  // the attribute belongs to the (function, device) pair and setting it is cheap: do it on every launch
+  B200_CHECK_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemLimit));
+  B200_CHECK_CUDA(launch_chained_cluster(kernel, dim3(grid), dim3(kThreads), smem, st, pair ? 2 : 1, p));
   B200_CHECK_CUDA(cudaGetLastError());
   return 0;
 }

@@ -186,11 +186,11 @@ class MoEPlan:
 
     def __init__(self, T, K, E, E_route, H, I, B, activation, swiglu_limit, device, act_terms=0,
                  weight_format=_lib.W_MXFP4, combine_mode=_lib.COMBINE_GATHER, act_quant=_lib.ACTQ_TERMS,
-                 doweight_stage1=False):
+                 doweight_stage1=False, cta_pairs=0):
         self.shape = _lib.Shape(T=T, K=K, E=E, E_route=E_route, H=H, I=I, B=B, weight_format=weight_format,
                                 activation=activation, swiglu_limit=float(swiglu_limit), act_terms=act_terms,
                                 combine_mode=combine_mode, act_quant=act_quant,
-                                doweight_stage1=1 if doweight_stage1 else 0)
+                                doweight_stage1=1 if doweight_stage1 else 0, cta_pairs=cta_pairs)
         self.capacity = T
         self.terms = act_terms or 3
         self.fp8 = weight_format != _lib.W_MXFP4
@@ -301,18 +301,18 @@ def _capacity(T: int) -> int:
 
 def get_plan(T, K, E, E_route, H, I, B, activation, swiglu_limit, device, act_terms=0,
              weight_format=_lib.W_MXFP4, combine_mode=_lib.COMBINE_GATHER, act_quant=_lib.ACTQ_TERMS,
-             doweight_stage1=False) -> MoEPlan:
+             doweight_stage1=False, cta_pairs=0) -> MoEPlan:
     """Cached plan (shape + workspace).  One workspace per (shape, CUDA stream): calls enqueued on different
     streams never share scratch memory.  The least recently used entry is dropped when the cache is full."""
     stream_id = torch.cuda.current_stream(device).cuda_stream if torch.cuda.is_available() else 0
     key = (T, K, E, E_route, H, I, B, activation, float(swiglu_limit), str(device), act_terms, weight_format,
-           combine_mode, act_quant, bool(doweight_stage1), stream_id)
+           combine_mode, act_quant, bool(doweight_stage1), cta_pairs, stream_id)
     plan = _workspace_cache.pop(key, None)
     if plan is None:
         while len(_workspace_cache) >= _WORKSPACE_CACHE_ENTRIES:
             _workspace_cache.pop(next(iter(_workspace_cache)))
         plan = MoEPlan(T, K, E, E_route, H, I, B, activation, swiglu_limit, device, act_terms, weight_format,
-                       combine_mode, act_quant, doweight_stage1)
+                       combine_mode, act_quant, doweight_stage1, cta_pairs)
     _workspace_cache[key] = plan          # (re)insert at the recent end
     return plan
 
@@ -370,7 +370,7 @@ def fused_moe(hidden_states, w1, w2, topk_weight, topk_ids, expert_mask=None,
               w1_scale=None, w2_scale=None, a1_scale=None, a2_scale=None, block_size_M=None,
               num_local_tokens=None, moe_sorting_dispatch_policy=0, dtype=None, hidden_pad=0,
               intermediate_pad=0, bias1=None, bias2=None, splitk=0, method="auto",
-              swiglu_limit=7.0, act_terms=0, combine="auto", act_quant="terms"):
+              swiglu_limit=7.0, act_terms=0, combine="auto", act_quant="terms", cta_pairs="auto"):
     """bf16 hidden states [T,H], router top-k ids [T,K] int32 and weights [T,K] fp32, packed
     expert weights with their scales -> bf16 [T,H].  Unsupported combinations raise, as the
     reference asserts (src/contrib/fused_moe.py:252-266).
@@ -387,6 +387,8 @@ def fused_moe(hidden_states, w1, w2, topk_weight, topk_ids, expert_mask=None,
         fp32 scales, src/contrib/fused_moe.py:375-381: half the operand bytes and MMA work, judged against the
         oracle that dequantises the same quantised activations).
       ``bias1`` [E, 2I] / ``bias2`` [E, H]: per-expert biases of the two projections (gpt-oss style).
+      ``cta_pairs`` (MXFP4): "auto" runs the GEMMs on CTA pairs (tcgen05.mma.cta_group::2) in the compute-bound regime,
+        "off" never, "on" wherever the tile allows it.
     """
     if not hidden_states.is_cuda:
         raise RuntimeError("fused_moe runs on a CUDA device only (sm_100a); there is no CPU path")
@@ -411,6 +413,8 @@ def fused_moe(hidden_states, w1, w2, topk_weight, topk_ids, expert_mask=None,
         raise ValueError(f"combine={combine!r}: 'auto', 'gather' or 'fused'")
     if act_quant not in ("terms", "1x128"):
         raise ValueError(f"act_quant={act_quant!r}: 'terms' or '1x128'")
+    if cta_pairs not in ("auto", "off", "on"):
+        raise ValueError(f"cta_pairs={cta_pairs!r}: 'auto', 'off' or 'on'")
     if act_quant == "1x128" and fmt != _lib.W_FP8_128:
         raise ValueError("act_quant='1x128' belongs to per_128x128 (FP8) weights; MXFP4 weights take act_terms")
     T, H = hidden_states.shape
@@ -433,7 +437,7 @@ def fused_moe(hidden_states, w1, w2, topk_weight, topk_ids, expert_mask=None,
             raise ValueError(f"bias2 must be [E, H] = [{pw.E}, {H}]")
         b2 = bias2.float().contiguous()
     plan = get_plan(_capacity(T), K, pw.E, E_route, H, pw.I, B, act, swiglu_limit, hidden_states.device, act_terms, fmt,
-                    cm, aq, bool(doweight_stage1))
+                    cm, aq, bool(doweight_stage1), {"auto": 0, "off": 1, "on": 2}[cta_pairs])
     plan.set_tokens(T)
     ids = topk_ids if topk_ids.dtype == torch.int32 else topk_ids.to(torch.int32)
     tw = topk_weight if topk_weight.dtype == torch.float32 else topk_weight.float()

@@ -27,7 +27,7 @@ def test_every_declared_symbol_is_exported(L):
 
 
 def test_struct_sizes_match_header():
-    assert ctypes.sizeof(_lib.Shape) == 56
+    assert ctypes.sizeof(_lib.Shape) == 60
     assert ctypes.sizeof(_lib.Io) == 12 * 8
     assert ctypes.sizeof(_lib.Workspace) == 14 * 8
 
@@ -45,7 +45,7 @@ def test_workspace_layout_arithmetic(L):
 
 @pytest.mark.parametrize("field,value", [("B", 40), ("H", 100), ("I", 0), ("K", 0), ("T", 1 << 24),
                                          ("weight_format", 7), ("activation", 9), ("E_route", 4), ("act_terms", 5),
-                                         ("combine_mode", 2), ("act_quant", 2), ("doweight_stage1", 2)])
+                                         ("combine_mode", 2), ("act_quant", 2), ("doweight_stage1", 2), ("cta_pairs", 3)])
 def test_bad_shapes_are_rejected(L, field, value):
     s = _lib.Shape(T=8, K=2, E=8, E_route=8, H=256, I=128, B=32, weight_format=0, activation=0, swiglu_limit=7.0, act_terms=0)
     setattr(s, field, value)

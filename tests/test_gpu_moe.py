@@ -419,3 +419,27 @@ def test_prepared_scale_image_known_answer():
                                 if kb * 4 + j < Kd // 32:
                                     want[e, mt, kb, part, (r % 32) * 16 + (r // 32) * 4 + j] = src[e, row, kb * 4 + j]
         assert np.array_equal(img, want), which
+
+
+# --------------------------------------------------------------------------------------------
+# CTA pairs (tcgen05.mma.cta_group::2): the same layer, bit for bit
+# --------------------------------------------------------------------------------------------
+@pytest.mark.parametrize("T,H,I,E,K,B,terms", [(300, 384, 128, 4, 2, 96, 0), (150, 256, 384, 4, 2, 64, 4), (400, 512, 256, 8, 2, 80, 3),
+                                               (260, 288, 160, 4, 2, 96, 1), (1, 256, 128, 4, 2, 96, 0), (700, 2880, 384, 4, 2, 96, 0)])
+def test_cta_pairs_match_the_single_cta_kernels_bit_for_bit(T, H, I, E, K, B, terms):
+    """Two CTAs of a cluster share one token tile (each fetches half of it, the even CTA issues M = 256 MMAs for both):
+    products and accumulation order per output element are those of the single-CTA kernels, so the deterministic
+    (GATHER) layer output must be identical bit for bit -- and within the tolerance of the oracle like any other."""
+    x, tw, ids, w = _case(T, H, I, E, K, seed=300 + T)
+    kw = dict(block_size_M=B, act_terms=terms, combine="gather")
+    y_off = _run_layer(x, tw, ids, w, cta_pairs="off", **kw)
+    y_on = _run_layer(x, tw, ids, w, cta_pairs="on", **kw)
+    assert torch.equal(y_on.view(torch.int16), y_off.view(torch.int16))
+    ref = orc.torch_moe_oracle_mxfp4(x, *w, tw, ids, **({"act_quant": "mxfp4"} if terms == 1 else {}))
+    if terms == 1:
+        assert orc.calc_diff(y_on, ref) <= 0.01
+    else:
+        cos, mx = orc.cosine(y_on, ref), orc.max_abs(y_on, ref)
+        assert cos >= COS and mx <= MAX_ABS * max(1.0, float(ref.float().abs().max())), (cos, mx)
+    y_f = _run_layer(x, tw, ids, w, cta_pairs="on", block_size_M=B, act_terms=terms, combine="fused")
+    assert orc.max_abs(y_f, y_on) <= 2 ** -6 * max(1.0, float(ref.float().abs().max()))
