@@ -290,6 +290,9 @@ int b200moe_ep_plan(const int32_t* topk_ids, int32_t T, int32_t K, int32_t exper
  *              FP4, 32 for FP8) from resident shared-memory tiles; the caller times the launch with stream events.
  *              `in` = i32 {kind (0 = kind::mxf4, 1 = kind::mxf8f6f4 e4m3), N, count}; `out` = u32 [SM count][3]
  *              {issue cycles, cycles until complete, status}.
+ *   which = 5: a bounded wait that is MADE to run out (a barrier nothing arrives on): `in` = i32 {limit in
+ *              microseconds}; `out` = u32 {status word = 0xBEEF (the wait's id), 1 if the wait succeeded, microseconds
+ *              waited}.  The kernel returns normally and the context stays usable.
  * status word: 0 = ok, non-zero = a bounded wait ran out. */
 int b200moe_debug_probe(int which, const void* in, void* out, void* stream);
 

@@ -906,6 +906,28 @@ __global__ void __launch_bounds__(128, 1) probe_mma_rate_kernel(const int32_t* c
   if (warp == 0) tmem_dealloc(tbase, 512);
 }
 
+// The bounded wait itself, made to run out: a barrier that nothing ever arrives on, a limit of in[0] microseconds.
+// The kernel must come back with the wait's id in the status word and the context must stay usable -- this is how
+// every role of the GEMM kernels gives up on a wait instead of hanging the GPU.
+__global__ void __launch_bounds__(32, 1) probe_wait_expiry_kernel(const int32_t* in, uint32_t* out) {
+  __shared__ uint64_t bar;
+  __shared__ uint32_t abort_word;
+  if (threadIdx.x == 0) {
+    abort_word = 0;
+    mbar_init(smem_u32(&bar), 1);
+    fence_mbar_init();
+  }
+  __syncwarp();
+  if (threadIdx.x == 0) {
+    const uint64_t t0 = global_timer_ns();
+    const bool ok = mbar_wait(smem_u32(&bar), 0, &abort_word, 0xBEEFu, (uint64_t)max(in[0], 1) * 1000ull);
+    const uint64_t dt = global_timer_ns() - t0;
+    out[0] = abort_word;
+    out[1] = ok ? 1u : 0u;
+    out[2] = (uint32_t)(dt / 1000ull);        // microseconds the wait lasted
+  }
+}
+
 int run_debug_probe(int which, const void* in, void* out, cudaStream_t st) {
   if (which == 1) {
     CUtensorMap map;
@@ -928,6 +950,11 @@ int run_debug_probe(int which, const void* in, void* out, cudaStream_t st) {
     // the attribute belongs to the (function, device) pair and setting it is cheap: do it on every launch
     B200_CHECK_CUDA(cudaFuncSetAttribute(probe_mma_rate_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 65536));
     probe_mma_rate_kernel<<<device_sm_count(), 128, 16384 + 32768 + 1024 + 1024, st>>>((const int32_t*)in, (uint32_t*)out);
+    B200_CHECK_CUDA(cudaGetLastError());
+    return 0;
+  }
+  if (which == 5) {
+    probe_wait_expiry_kernel<<<1, 32, 0, st>>>((const int32_t*)in, (uint32_t*)out);
     B200_CHECK_CUDA(cudaGetLastError());
     return 0;
   }

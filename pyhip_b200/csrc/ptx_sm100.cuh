@@ -94,14 +94,14 @@ __device__ __forceinline__ bool mbar_try_wait_hint(uint32_t bar, uint32_t parity
 constexpr uint64_t kWaitLimitNs = 2000000000ull;
 
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile uint32_t* abort_word,
-                                          uint32_t who) {
+                                          uint32_t who, uint64_t limit_ns = kWaitLimitNs) {
   if (mbar_try_wait(bar, parity)) return true;
   uint64_t t0 = global_timer_ns();
   uint32_t spins = 0;
   while (!mbar_try_wait_hint(bar, parity, 2000u)) {
     if ((++spins & 63u) == 0) {
       if (*abort_word) return false;
-      if (global_timer_ns() - t0 > kWaitLimitNs) {
+      if (global_timer_ns() - t0 > limit_ns) {
         *abort_word = who;
         return false;
       }

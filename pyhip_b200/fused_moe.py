@@ -55,8 +55,9 @@ def pick_block(T: int, K: int, E: int, weight_format: int = _lib.W_MXFP4) -> int
     from shared memory, so cost(B) = E[ceil(n/B)] * (128 + B) with n ~ Normal(mu, mu(1-1/E)) under
     uniform routing.  96 is the largest tile whose two accumulator buffers fit tensor memory.
     Measured on the gpt-oss shape: T=4096 0.94 ms at 80 vs 1.06 ms at 96, T=8192 1.60 ms at 96 vs 1.70 ms
-    at 80, as the model predicts.  The FP8 kernel pays a fixed promotion cost per tile and k-block, so
-    there the fewest tiles win: always 96."""
+    at 80, as the model predicts.  The FP8 kernels pay a fixed promotion cost per tile and k-block on top (modelled as
+    64 more rows), so fewer tiles win more often there: 96 unless a smaller tile covers the experts' rows with the same
+    number of tiles (about 128 rows per expert: two tiles of 80 instead of two of 96)."""
     per_expert = (T * K) / max(E, 1)
     if per_expert <= 4:
         return 16
@@ -64,17 +65,16 @@ def pick_block(T: int, K: int, E: int, weight_format: int = _lib.W_MXFP4) -> int
         return 32
     if per_expert <= 48:
         return 64
-    if weight_format == _lib.W_FP8_128:
-        return 96
+    fp8 = weight_format != _lib.W_MXFP4
     sigma = math.sqrt(max(per_expert * (1.0 - 1.0 / max(E, 1)), 1e-6))
     lo, hi = max(1, int(per_expert - 4 * sigma)), int(per_expert + 4 * sigma) + 1
     best, best_cost = 96, None
-    for B in (96, 80, 64, 48):
+    for B in ((96, 80, 64) if fp8 else (96, 80, 64, 48)):
         wsum = cost = 0.0
         for n in range(lo, hi + 1):
             wgt = math.exp(-0.5 * ((n - per_expert) / sigma) ** 2)
             wsum += wgt
-            cost += wgt * (-(-n // B)) * (128 + B)
+            cost += wgt * (-(-n // B)) * (128 + B + (64 if fp8 else 0))
         cost /= wsum
         if best_cost is None or cost < best_cost * 0.98:      # prefer the larger tile on a near tie
             best, best_cost = B, cost

@@ -64,3 +64,14 @@ def test_mma_rate_probe_completes(kind, n):
     raw = _probe(4, cfg, sms * 3).reshape(sms, 3)
     assert (raw[:, 2] == 0).all(), "a wait ran out"
     assert (raw[:, 1] > count * 32).all() and (raw[:, 1] < count * 4000).all()
+
+
+def test_a_wait_that_runs_out_reports_and_leaves_the_context_usable():
+    """Failure detection on the device without a fault: a barrier that nothing ever arrives on, a 3 ms limit.  The wait
+    gives up, the kernel writes the wait's id into its status word and returns; the next launch on the same context
+    works.  This is the path every role of the GEMM kernels takes when a wait runs out (their limit is two seconds)."""
+    cfg = torch.tensor([3000], dtype=torch.int32, device="cuda:0")
+    raw = _probe(5, cfg, 4)
+    assert raw[0] == 0xBEEF and raw[1] == 0
+    assert 3000 <= raw[2] < 500000, raw[2]
+    test_scale_copy_to_tensor_memory_layout()          # the context is alive and the library still works
