@@ -167,7 +167,7 @@ int b200moe_quant_rows_fp8_1x128(const void* src_bf16, int32_t src_mode, const u
   B200_CHECK_ARG(((uintptr_t)src_bf16 & 15) == 0 && ((uintptr_t)q & 15) == 0,
                  "quant_rows: source and destination must be 16-byte aligned");
   return launch_quant_rows_fp8_1x128(src_bf16, src_mode, sorted_ids, num_valid_ids, T, K, Kd, B, max_rows, q, sf,
-                                     nullptr, 0, (cudaStream_t)stream);
+                                     nullptr, 0, nullptr, (cudaStream_t)stream);
 }
 
 int b200moe_sort_scratch_bytes(int32_t E_route, int64_t* bytes) {
@@ -193,7 +193,7 @@ int b200moe_quant_rows(const void* src_bf16, int32_t src_mode, const uint32_t* s
   B200_CHECK_ARG(((uintptr_t)src_bf16 & 15) == 0 && ((uintptr_t)q & 15) == 0,
                  "quant_rows: source and destination must be 16-byte aligned");
   return launch_quant_rows(src_bf16, src_mode, sorted_ids, num_valid_ids, T, K, Kd, B, terms, max_rows, q, sf,
-                           nullptr, 0, (cudaStream_t)stream);
+                           nullptr, 0, nullptr, (cudaStream_t)stream);
 }
 
 int b200moe_quant_rows_e4m3(const void* src_bf16, int32_t src_mode, const uint32_t* sorted_ids,
@@ -205,7 +205,7 @@ int b200moe_quant_rows_e4m3(const void* src_bf16, int32_t src_mode, const uint32
   B200_CHECK_ARG(((uintptr_t)src_bf16 & 15) == 0 && ((uintptr_t)q & 15) == 0,
                  "quant_rows: source and destination must be 16-byte aligned");
   return launch_quant_rows_e4m3(src_bf16, src_mode, sorted_ids, num_valid_ids, T, K, Kd, B, max_rows, q, sf,
-                                nullptr, 0, (cudaStream_t)stream);
+                                nullptr, 0, nullptr, (cudaStream_t)stream);
 }
 
 static void fill_common(GemmArgs& g, const b200moe_shape* s, const b200moe_workspace* ws, uint8_t* base) {
@@ -353,13 +353,13 @@ static int forward_impl(const b200moe_shape* s, const b200moe_workspace* ws, voi
     if (rc) return rc;
     if (fp8w && s->act_quant)
       rc = launch_quant_rows_fp8_1x128(io->x_bf16, 0, sorted_ids, num_valid, s->T, s->K, s->H, s->B, ws->max_rows,
-                                       base + ws->off_xq, base + ws->off_xsf, zero_ptr, zero_bytes, (cudaStream_t)stream);
+                                       base + ws->off_xq, base + ws->off_xsf, zero_ptr, zero_bytes, loc, (cudaStream_t)stream);
     else if (fp8w)
       rc = launch_quant_rows_e4m3(io->x_bf16, 0, sorted_ids, num_valid, s->T, s->K, s->H, s->B, ws->max_rows,
-                                  base + ws->off_xq, base + ws->off_xsf, zero_ptr, zero_bytes, (cudaStream_t)stream);
+                                  base + ws->off_xq, base + ws->off_xsf, zero_ptr, zero_bytes, loc, (cudaStream_t)stream);
     else
       rc = launch_quant_rows(io->x_bf16, 0, sorted_ids, num_valid, s->T, s->K, s->H, s->B, terms_of(s), ws->max_rows,
-                             base + ws->off_xq, base + ws->off_xsf, zero_ptr, zero_bytes, (cudaStream_t)stream);
+                             base + ws->off_xq, base + ws->off_xsf, zero_ptr, zero_bytes, loc, (cudaStream_t)stream);
     if (rc) return rc;
   }
   rc = b200moe_gateup(s, ws, workspace, io->w1_q, io->w1_scale_prepared, io->bias1, nullptr, stream);

@@ -63,10 +63,12 @@ int launch_sort_align_wide(const int32_t* ids, const float* w, int T, int K, int
                            int32_t* loc, const int32_t* num_local, void* scratch, cudaStream_t st);
 int launch_route_topk(const float* logits, int T, int E, int K, int scoring, int renorm, int32_t* ids, float* weights,
                       cudaStream_t st);
-// zero_ptr / zero_bytes: an optional region the same launch clears (the output of the fused combine)
+// zero_ptr / zero_bytes: an optional region the same launch clears (the output of the fused combine).
+// loc (with src_mode 0): the sort's [T, K] table of sorted positions; when given, every token is quantised once and
+// stored at its K rows instead of once per sorted row.
 int launch_quant_rows(const void* src, int src_mode, const uint32_t* sorted_ids, const int32_t* num_valid,
                       int T, int K, int Kd, int B, int NT, int64_t max_rows, void* q, void* sf, void* zero_ptr,
-                      int64_t zero_bytes, cudaStream_t st);
+                      int64_t zero_bytes, const int32_t* loc, cudaStream_t st);
 // sort/align + input quantiser in one launch for decode-sized batches
 // (fmt 0: packed-FP4 terms, 1: two e4m3 terms, 2: e4m3 with fp32 scales per 1x128)
 bool sort_quant_small_ok(int T, int K, int E);
@@ -122,10 +124,10 @@ int launch_grouped_gemm(const GemmArgs& a, cudaStream_t st);
 int launch_grouped_gemm_fp8(const GemmArgs& a, cudaStream_t st);
 int launch_quant_rows_e4m3(const void* src, int src_mode, const uint32_t* sorted_ids, const int32_t* num_valid,
                            int T, int K, int Kd, int B, int64_t max_rows, void* q, void* sf, void* zero_ptr,
-                           int64_t zero_bytes, cudaStream_t st);
+                           int64_t zero_bytes, const int32_t* loc, cudaStream_t st);
 int launch_quant_rows_fp8_1x128(const void* src, int src_mode, const uint32_t* sorted_ids, const int32_t* num_valid,
                                 int T, int K, int Kd, int B, int64_t max_rows, void* q, void* sf, void* zero_ptr,
-                                int64_t zero_bytes, cudaStream_t st);
+                                int64_t zero_bytes, const int32_t* loc, cudaStream_t st);
 int encode_map_sw(CUtensorMap* map, CUtensorMapDataType type, int rank, const void* base, const cuuint64_t* dims,
                   const cuuint64_t* strides, const cuuint32_t* box, CUtensorMapSwizzle swizzle,
                   CUtensorMapL2promotion promo, const char* what);

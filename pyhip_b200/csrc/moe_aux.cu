@@ -513,6 +513,33 @@ quant_rows_kernel(const __nv_bfloat16* __restrict__ src, int src_mode, const uin
   }
 }
 
+// The layer input quantised once per TOKEN and stored at each of its K sorted rows (`loc[t, k]`, -1 where the pair was
+// dropped): a token's row is read and quantised once instead of once per (token, expert) pair.
+template <int FMT>
+__global__ void __launch_bounds__(256)
+quant_tokens_kernel(const __nv_bfloat16* __restrict__ src, const int32_t* __restrict__ loc, int T, int K, QuantGeom g,
+                    uint4* zero_ptr, int64_t zero_vec) {
+  const int nb = g.KP / 32;
+  grid_dep_launch();
+  grid_dep_wait();
+  zero_fill(zero_ptr, zero_vec);
+  const int64_t total = (int64_t)T * nb;
+  for (int64_t base = (int64_t)blockIdx.x * blockDim.x; base < total; base += (int64_t)gridDim.x * blockDim.x) {
+    const int64_t u = base + threadIdx.x;
+    const int64_t t = min(u, total - 1) / nb;
+    const int j = (int)(min(u, total - 1) % nb);
+    const bool live = u < total;
+    QuantUnit qu;
+    quant_compute<FMT>(src, t, j, g, live, qu);
+    if (live) {
+      for (int k = 0; k < K; ++k) {
+        const int r = loc[t * K + k];
+        if (r >= 0 && r < g.max_rows) quant_store<FMT>(j, r, g, qu);
+      }
+    }
+  }
+}
+
 static int small_grid(int64_t units) { return (int)std::max<int64_t>(1, (units + 255) / 256); }   // one unit per thread
 static int quant_grid(int64_t units) {
   return (int)std::max<int64_t>(1, std::min<int64_t>((units + 255) / 256, (int64_t)device_sm_count() * 16));
@@ -520,13 +547,18 @@ static int quant_grid(int64_t units) {
 
 int launch_quant_rows(const void* src, int src_mode, const uint32_t* sorted_ids, const int32_t* num_valid,
                       int T, int K, int Kd, int B, int NT, int64_t max_rows, void* q, void* sf, void* zero_ptr,
-                      int64_t zero_bytes, cudaStream_t st) {
+                      int64_t zero_bytes, const int32_t* loc, cudaStream_t st) {
   B200_CHECK_ARG(B >= 16 && B <= 128 && B % 16 == 0, "quant_rows: B=%d is not a multiple of 16 in [16,128]", B);
   B200_CHECK_ARG(NT >= 1 && NT <= 4, "quant_rows: %d activation terms (1..4 supported)", NT);
   B200_CHECK_ARG(Kd % 32 == 0, "quant_rows: Kd=%d must be a multiple of 32", Kd);
   B200_CHECK_ARG(zero_bytes % 16 == 0 && ((uintptr_t)zero_ptr & 15) == 0, "quant_rows: zero region must be 16-byte aligned");
   const int KP = (int)round_up64(Kd, kKPad);
   QuantGeom g = {Kd, KP, B, NT, act_term_stride(B, NT, 2), max_rows, (uint8_t*)q, (uint8_t*)sf};
+  if (loc != nullptr && src_mode == 0) {        // once per token, stored at its K sorted rows
+    B200_CHECK_CUDA(launch_chained(quant_tokens_kernel<0>, dim3(quant_grid((int64_t)T * (KP / 32))), dim3(256), 0, st,
+                                   reinterpret_cast<const __nv_bfloat16*>(src), loc, T, K, g, (uint4*)zero_ptr, zero_bytes / 16));
+    return 0;
+  }
   B200_CHECK_CUDA(launch_chained(quant_rows_kernel<0>, dim3(quant_grid(max_rows * (KP / 32))), dim3(256), 0, st,
                                  reinterpret_cast<const __nv_bfloat16*>(src), src_mode, sorted_ids, num_valid, T, K, g,
                                  (uint4*)zero_ptr, zero_bytes / 16));
@@ -535,11 +567,16 @@ int launch_quant_rows(const void* src, int src_mode, const uint32_t* sorted_ids,
 
 int launch_quant_rows_e4m3(const void* src, int src_mode, const uint32_t* sorted_ids, const int32_t* num_valid,
                            int T, int K, int Kd, int B, int64_t max_rows, void* q, void* sf, void* zero_ptr,
-                           int64_t zero_bytes, cudaStream_t st) {
+                           int64_t zero_bytes, const int32_t* loc, cudaStream_t st) {
   B200_CHECK_ARG(B >= 16 && B <= 96 && B % 16 == 0, "quant_rows (e4m3): B=%d is not a multiple of 16 in [16,96]", B);
   B200_CHECK_ARG(Kd % 128 == 0, "quant_rows (e4m3): Kd=%d must be a multiple of 128", Kd);
   B200_CHECK_ARG(zero_bytes % 16 == 0 && ((uintptr_t)zero_ptr & 15) == 0, "quant_rows: zero region must be 16-byte aligned");
   QuantGeom g = {Kd, Kd, B, 2, 128, max_rows, (uint8_t*)q, (uint8_t*)sf};
+  if (loc != nullptr && src_mode == 0) {
+    B200_CHECK_CUDA(launch_chained(quant_tokens_kernel<1>, dim3(quant_grid((int64_t)T * (Kd / 32))), dim3(256), 0, st,
+                                   reinterpret_cast<const __nv_bfloat16*>(src), loc, T, K, g, (uint4*)zero_ptr, zero_bytes / 16));
+    return 0;
+  }
   B200_CHECK_CUDA(launch_chained(quant_rows_kernel<1>, dim3(quant_grid(max_rows * (Kd / 32))), dim3(256), 0, st,
                                  reinterpret_cast<const __nv_bfloat16*>(src), src_mode, sorted_ids, num_valid, T, K, g,
                                  (uint4*)zero_ptr, zero_bytes / 16));
@@ -548,12 +585,17 @@ int launch_quant_rows_e4m3(const void* src, int src_mode, const uint32_t* sorted
 
 int launch_quant_rows_fp8_1x128(const void* src, int src_mode, const uint32_t* sorted_ids, const int32_t* num_valid,
                                 int T, int K, int Kd, int B, int64_t max_rows, void* q, void* sf, void* zero_ptr,
-                                int64_t zero_bytes, cudaStream_t st) {
+                                int64_t zero_bytes, const int32_t* loc, cudaStream_t st) {
   B200_CHECK_ARG(B >= 16 && B <= 96 && B % 16 == 0, "quant_rows (1x128): B=%d is not a multiple of 16 in [16,96]", B);
   B200_CHECK_ARG(Kd % 128 == 0, "quant_rows (1x128): Kd=%d must be a multiple of 128", Kd);
   B200_CHECK_ARG(zero_bytes % 16 == 0 && ((uintptr_t)zero_ptr & 15) == 0 && ((uintptr_t)sf & 15) == 0,
                  "quant_rows: zero region / scales must be 16-byte aligned");
   QuantGeom g = {Kd, Kd, B, 1, 128, max_rows, (uint8_t*)q, (uint8_t*)sf};
+  if (loc != nullptr && src_mode == 0) {
+    B200_CHECK_CUDA(launch_chained(quant_tokens_kernel<2>, dim3(quant_grid((int64_t)T * (Kd / 32))), dim3(256), 0, st,
+                                   reinterpret_cast<const __nv_bfloat16*>(src), loc, T, K, g, (uint4*)zero_ptr, zero_bytes / 16));
+    return 0;
+  }
   B200_CHECK_CUDA(launch_chained(quant_rows_kernel<2>, dim3(quant_grid(max_rows * (Kd / 32))), dim3(256), 0, st,
                                  reinterpret_cast<const __nv_bfloat16*>(src), src_mode, sorted_ids, num_valid, T, K, g,
                                  (uint4*)zero_ptr, zero_bytes / 16));
