@@ -157,7 +157,8 @@ int launch_sort_align(const int32_t* ids, const float* w, int T, int K, int E, i
 // chained launches over caller scratch: per-(CTA, warp) histograms of contiguous slices -> one CTA turns them
 // into offsets (slice order = the required stable order) and does the per-expert part -> every warp
 // scatters its slice.  Bit-identical to the single-CTA kernel.
-// scratch: int32 [slices = G*32][E] histograms, [slices][E] offsets, then [E] first sorted row of each expert.
+// scratch: int32 [slices = G*32][E] counts per warp, [G][E] counts per CTA, [G][E] offsets per CTA, then [E] first
+// sorted row of each expert.
 // =====================================================================================
 constexpr int kSortMaxCtas = 64;
 
@@ -167,7 +168,8 @@ __host__ __device__ inline int sort_slice_pairs(int P, int G) {       // pairs p
 
 __global__ void __launch_bounds__(kSortWarps * 32, 1)
 sort_count_kernel(const int32_t* __restrict__ ids, const int32_t* __restrict__ mask, int T, int K, int E,
-                  const int32_t* __restrict__ num_local, int slice, int32_t* __restrict__ hist) {
+                  const int32_t* __restrict__ num_local, int slice, int32_t* __restrict__ hist,
+                  int32_t* __restrict__ ctot) {
   extern __shared__ int32_t sm[];          // [kSortWarps][E]
   grid_dep_launch();
   grid_dep_wait();
@@ -188,6 +190,13 @@ sort_count_kernel(const int32_t* __restrict__ ids, const int32_t* __restrict__ m
   }
   int32_t* row = hist + ((int64_t)blockIdx.x * kSortWarps + warp) * E;
   for (int e = lane; e < E; e += 32) row[e] = cnt[e];
+  __syncthreads();
+  // the CTA's own total per expert: the scan launch walks one row per CTA, not one per warp
+  for (int e = tid; e < E; e += blockDim.x) {
+    int sum = 0;
+    for (int wi = 0; wi < kSortWarps; ++wi) sum += sm[wi * E + e];
+    ctot[(int64_t)blockIdx.x * E + e] = sum;
+  }
 }
 
 __global__ void __launch_bounds__(kSortWarps * 32, 1)
@@ -280,8 +289,9 @@ sort_scan_kernel(const int32_t* __restrict__ hist, int32_t* __restrict__ offs, i
 
 __global__ void __launch_bounds__(kSortWarps * 32, 1)
 sort_scatter_kernel(const int32_t* __restrict__ ids, const float* __restrict__ w, const int32_t* __restrict__ mask,
-                    int T, int K, int E, const int32_t* __restrict__ num_local, int slice, int S,
-                    const int32_t* __restrict__ hist, uint32_t* __restrict__ sorted_ids,
+                    int T, int K, int E, const int32_t* __restrict__ num_local, int slice, int G,
+                    const int32_t* __restrict__ hist, const int32_t* __restrict__ coffs,
+                    uint32_t* __restrict__ sorted_ids,
                     float* __restrict__ sorted_w, int32_t* __restrict__ loc) {
   extern __shared__ int32_t sm[];          // [kSortWarps][E] running offsets, then [E] expert bases
   grid_dep_launch();
@@ -296,7 +306,17 @@ sort_scatter_kernel(const int32_t* __restrict__ ids, const float* __restrict__ w
   int32_t* base = sm + kSortWarps * E;
   const int32_t* row = hist + ((int64_t)blockIdx.x * kSortWarps + warp) * E;
   for (int e = lane; e < E; e += 32) cnt[e] = row[e];
-  for (int e = tid; e < E; e += blockDim.x) base[e] = hist[(int64_t)S * E + e];
+  __syncthreads();
+  // counts of this CTA's warps -> where each warp's first row of an expert goes, relative to the expert's first row
+  for (int e = tid; e < E; e += blockDim.x) {
+    int run = coffs[(int64_t)blockIdx.x * E + e];
+    for (int wi = 0; wi < kSortWarps; ++wi) {
+      const int c = sm[wi * E + e];
+      sm[wi * E + e] = run;
+      run += c;
+    }
+    base[e] = coffs[(int64_t)G * E + e];
+  }
   __syncthreads();
   const uint32_t lt_mask = (1u << lane) - 1u;
   for (int i0 = lo; i0 < hi; i0 += 32) {
@@ -332,14 +352,16 @@ int launch_sort_align_wide(const int32_t* ids, const float* w, int T, int K, int
   B200_CHECK_ARG(smem <= 200 * 1024, "sort_align: E=%d needs %zu bytes of shared memory", E, smem);
   B200_CHECK_CUDA(cudaFuncSetAttribute(sort_count_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
   B200_CHECK_CUDA(cudaFuncSetAttribute(sort_scatter_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
-  int32_t* hist = (int32_t*)scratch;
+  int32_t* hist = (int32_t*)scratch;                 // [S][E] counts per warp
+  int32_t* ctot = hist + (int64_t)S * E;             // [G][E] counts per CTA
+  int32_t* coffs = ctot + (int64_t)G * E;            // [G][E] offsets per CTA, then [E] first row of each expert
   B200_CHECK_CUDA(launch_chained(sort_count_kernel, dim3(G), dim3(kSortWarps * 32), smem, st, ids, mask, T, K, E,
-                                 num_local, slice, hist));
-  int32_t* offs = hist + (int64_t)S * E;
-  B200_CHECK_CUDA(launch_chained(sort_scan_kernel, dim3(1), dim3(kSortWarps * 32), 0, st, (const int32_t*)hist, offs, S,
+                                 num_local, slice, hist, ctot));
+  B200_CHECK_CUDA(launch_chained(sort_scan_kernel, dim3(1), dim3(kSortWarps * 32), 0, st, (const int32_t*)ctot, coffs, G,
                                  T, K, E, B, mask, num_local, sorted_ids, sorted_w, sorted_e, num_valid));
   B200_CHECK_CUDA(launch_chained(sort_scatter_kernel, dim3(G), dim3(kSortWarps * 32), smem, st, ids, w, mask, T, K, E,
-                                 num_local, slice, S, (const int32_t*)offs, sorted_ids, sorted_w, loc));
+                                 num_local, slice, G, (const int32_t*)hist, (const int32_t*)coffs, sorted_ids, sorted_w,
+                                 loc));
   return 0;
 }
 
