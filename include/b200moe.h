@@ -29,6 +29,10 @@ extern "C" {
                                per-token-per-channel FP8 weights (tests/contrib/moe/test_moe.py:123-128); its per-tensor
                                weights (:130-137) are the same with a row's scale repeated.  The scale tensors are passed
                                in place as the *_scale_prepared arguments */
+#define B200MOE_W_BF16 3 /* unquantised bf16 weights w1 [E,2I,H] / w2 [E,H,I], no scales (the *_scale arguments are
+                            ignored and may be NULL): the reference wrapper's QuantType.No
+                            (src/contrib/fused_moe.py:253; torch form tests/contrib/moe/test_moe.py:86-118).  Activations
+                            stay bf16 (act_terms / act_quant do not apply), products accumulate in fp32 */
 /* activation functions of the gate-up stage */
 #define B200MOE_ACT_SILU 0   /* silu(gate) * up                        (test_moe.py:74-75) */
 #define B200MOE_ACT_SWIGLU 1 /* clamped gate*sigmoid(1.702 gate)*(up+1) (test_moe.py:76-81) */
@@ -177,9 +181,11 @@ int b200moe_quant_rows_fp8_1x128(const void* src_bf16, int32_t src_mode, const u
  *   w1_q is e4m3 [E,2I,H] and w1_scale_prepared is the raw fp32 [E, 2I/128, H/128] scale tensor.
  *   bias1 : NULL or fp32 [E, 2I] (gate then up), added to the bf16-rounded products before the activation
  *           (the aiter argument of that name, src/contrib/fused_moe.py:151; the reference asserts it absent).
+ *   With weight_format B200MOE_W_BF16 (replaces moe_2stage_splitk on bf16 weights, src/contrib/moe.py:362-702):
+ *   w1_q is bf16 [E,2I,H], w1_scale_prepared is ignored, h_out must be NULL.
  *   h_out != NULL : bf16 [T, K, I] scattered by (token,k) like the reference (moe.py:651-655)
- *   h_out == NULL : the result is re-quantised in sorted-row order into workspace hq for
- *                   b200moe_down (fused path). */
+ *   h_out == NULL : the result is re-quantised (bf16 weights: stored as bf16) in sorted-row order into
+ *                   workspace hq for b200moe_down (fused path). */
 int b200moe_gateup(const b200moe_shape* shape, const b200moe_workspace* ws, void* workspace,
                    const void* w1_q, const void* w1_scale_prepared, const float* bias1, void* h_out,
                    void* stream);

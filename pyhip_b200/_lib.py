@@ -18,11 +18,12 @@ import subprocess
 PKG_DIR = pathlib.Path(__file__).resolve().parent
 CSRC = PKG_DIR / "csrc"
 LIB_PATH = PKG_DIR / "libb200moe.so"
-SOURCES = ["api.cu", "moe_aux.cu", "moe_gemm_sm100.cu", "moe_gemm_fp8_sm100.cu", "forward_static.cu"]
+SOURCES = ["api.cu", "moe_aux.cu", "moe_gemm_sm100.cu", "moe_gemm_fp8_sm100.cu", "moe_gemm_bf16_sm100.cu",
+           "forward_static.cu"]
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
               "-shared", "-Xcompiler", "-fPIC"]
 
-W_MXFP4, W_FP8_128, W_FP8_ROW = 0, 1, 2
+W_MXFP4, W_FP8_128, W_FP8_ROW, W_BF16 = 0, 1, 2, 3
 ACT_SILU, ACT_SWIGLU = 0, 1
 COMBINE_GATHER, COMBINE_FUSED = 0, 1
 ACTQ_TERMS, ACTQ_1X128 = 0, 1

@@ -18,6 +18,11 @@ int set_error(int code, const char* fmt, ...) {
   return code;
 }
 
+static bool is_fp8(const b200moe_shape* s) {
+  return s->weight_format == B200MOE_W_FP8_128 || s->weight_format == B200MOE_W_FP8_ROW;
+}
+static bool is_bf16(const b200moe_shape* s) { return s->weight_format == B200MOE_W_BF16; }
+
 static int check_shape(const b200moe_shape* s) {
   B200_CHECK_ARG(s != nullptr, "shape is NULL");
   B200_CHECK_ARG(s->T >= 0 && s->T < (1 << 24), "T=%d outside [0, 2^24)", s->T);
@@ -29,8 +34,9 @@ static int check_shape(const b200moe_shape* s) {
   B200_CHECK_ARG(s->I >= 32 && s->I % 32 == 0, "I=%d must be a positive multiple of 32", s->I);
   B200_CHECK_ARG(s->H % 8 == 0, "H must be a multiple of 8");
   B200_CHECK_ARG(s->weight_format == B200MOE_W_MXFP4 || s->weight_format == B200MOE_W_FP8_128 ||
-                 s->weight_format == B200MOE_W_FP8_ROW, "weight_format %d unknown", s->weight_format);
-  if (s->weight_format != B200MOE_W_MXFP4) {
+                 s->weight_format == B200MOE_W_FP8_ROW || s->weight_format == B200MOE_W_BF16,
+                 "weight_format %d unknown", s->weight_format);
+  if (is_fp8(s)) {
     B200_CHECK_ARG(s->H % 128 == 0 && s->I % 128 == 0, "FP8 weights need H and I to be multiples of 128");
     B200_CHECK_ARG(s->B <= 96, "FP8 weights: B=%d exceeds 96", s->B);
   }
@@ -65,7 +71,7 @@ const char* b200moe_last_error(void) { return g_err; }
 int b200moe_workspace_layout(const b200moe_shape* s, b200moe_workspace* ws) {
   if (int rc = check_shape(s)) return rc;
   B200_CHECK_ARG(ws != nullptr, "workspace descriptor is NULL");
-  const bool fp8w = s->weight_format != B200MOE_W_MXFP4;
+  const bool fp8w = is_fp8(s);
   const int NT = fp8w ? 2 : terms_of(s);
   const int64_t P = (int64_t)s->T * s->K;
   const int64_t nblk = (P + (int64_t)s->E_route * (s->B - 1) + s->B - 1) / s->B;
@@ -86,7 +92,12 @@ int b200moe_workspace_layout(const b200moe_shape* s, b200moe_workspace* ws) {
   ws->off_num_valid = take(8);
   ws->off_loc = take(std::max<int64_t>(P, 1) * 4);
   ws->off_status = take(64);
-  if (fp8w) {   // two e4m3 terms, one byte per element, one scale chunk per term
+  if (is_bf16(s)) {   // bf16 rows in sorted order, no scales
+    ws->off_xq = take(L * s->H * 2);
+    ws->off_xsf = take(16);
+    ws->off_hq = take(L * s->I * 2);
+    ws->off_hsf = take(16);
+  } else if (fp8w) {   // two e4m3 terms, one byte per element, one scale chunk per term
     ws->off_xq = take(2 * L * s->H);
     ws->off_xsf = take(nb * (s->H / 128) * 2 * kSfChunk);
     ws->off_hq = take(2 * L * s->I);
@@ -230,7 +241,7 @@ static void fill_common(GemmArgs& g, const b200moe_shape* s, const b200moe_works
 int b200moe_gateup(const b200moe_shape* s, const b200moe_workspace* ws, void* workspace, const void* w1_q,
                    const void* w1_scale, const float* bias1, void* h_out, void* stream) {
   if (int rc = check_shape(s)) return rc;
-  B200_CHECK_ARG(ws && workspace && w1_q && w1_scale, "gateup: NULL pointer");
+  B200_CHECK_ARG(ws && workspace && w1_q && (w1_scale || is_bf16(s)), "gateup: NULL pointer");
   B200_CHECK_ARG(((uintptr_t)workspace & 1023) == 0, "gateup: workspace must be 1024-byte aligned");
   uint8_t* base = (uint8_t*)workspace;
   GemmArgs g = {};
@@ -247,7 +258,11 @@ int b200moe_gateup(const b200moe_shape* s, const b200moe_workspace* ws, void* wo
   g.weight_stage1 = s->doweight_stage1;
   g.oq = base + ws->off_hq;
   g.osf = base + ws->off_hsf;
-  if (s->weight_format != B200MOE_W_MXFP4) {
+  if (is_bf16(s)) {
+    B200_CHECK_ARG(h_out == nullptr, "gateup: bf16 weights write h in sorted-row order only (h_out must be NULL)");
+    return launch_grouped_gemm_bf16(g, (cudaStream_t)stream);
+  }
+  if (is_fp8(s)) {
     g.out_kp = s->I;
     return launch_grouped_gemm_fp8(g, (cudaStream_t)stream);
   }
@@ -261,7 +276,7 @@ int b200moe_gateup(const b200moe_shape* s, const b200moe_workspace* ws, void* wo
 int b200moe_down(const b200moe_shape* s, const b200moe_workspace* ws, void* workspace, const void* w2_q,
                  const void* w2_scale, const float* bias2, void* y_bf16, void* stream) {
   if (int rc = check_shape(s)) return rc;
-  B200_CHECK_ARG(ws && workspace && w2_q && w2_scale, "down: NULL pointer");
+  B200_CHECK_ARG(ws && workspace && w2_q && (w2_scale || is_bf16(s)), "down: NULL pointer");
   B200_CHECK_ARG(s->combine_mode != B200MOE_COMBINE_FUSED || y_bf16 != nullptr, "down: the fused combine needs y");
   B200_CHECK_ARG(((uintptr_t)workspace & 1023) == 0, "down: workspace must be 1024-byte aligned");
   uint8_t* base = (uint8_t*)workspace;
@@ -278,7 +293,8 @@ int b200moe_down(const b200moe_shape* s, const b200moe_workspace* ws, void* work
   g.bias = bias2;
   g.y = s->combine_mode == B200MOE_COMBINE_FUSED ? y_bf16 : nullptr;
   if (s->doweight_stage1) g.sorted_w = nullptr;     // weights already applied upstream
-  if (s->weight_format != B200MOE_W_MXFP4) return launch_grouped_gemm_fp8(g, (cudaStream_t)stream);
+  if (is_bf16(s)) return launch_grouped_gemm_bf16(g, (cudaStream_t)stream);
+  if (is_fp8(s)) return launch_grouped_gemm_fp8(g, (cudaStream_t)stream);
   return launch_grouped_gemm(g, (cudaStream_t)stream);
 }
 
@@ -329,7 +345,7 @@ static int forward_impl(const b200moe_shape* s, const b200moe_workspace* ws, voi
   B200_CHECK_ARG(io->x_bf16 && io->topk_ids && io->topk_weight && io->y_bf16, "forward: NULL tensor");
   B200_CHECK_ARG(((uintptr_t)io->y_bf16 & 15) == 0, "forward: output must be 16-byte aligned");
   uint8_t* base = (uint8_t*)workspace;
-  const bool fp8w = s->weight_format != B200MOE_W_MXFP4;
+  const bool fp8w = is_fp8(s);
   const bool fused = s->combine_mode == B200MOE_COMBINE_FUSED;
   // the fused combine accumulates into y: the quantiser launch clears it first
   void* zero_ptr = fused ? io->y_bf16 : nullptr;
@@ -341,7 +357,7 @@ static int forward_impl(const b200moe_shape* s, const b200moe_workspace* ws, voi
   int32_t* loc = (int32_t*)(base + ws->off_loc);
   int rc;
   if (sort_quant_small_ok(s->T, s->K, s->E_route)) {
-    rc = launch_sort_quant_small(fp8w ? (s->act_quant ? 2 : 1) : 0, io->x_bf16, io->topk_ids, io->topk_weight, s->T, s->K, s->E_route, s->B,
+    rc = launch_sort_quant_small(is_bf16(s) ? 3 : fp8w ? (s->act_quant ? 2 : 1) : 0, io->x_bf16, io->topk_ids, io->topk_weight, s->T, s->K, s->E_route, s->B,
                                  io->expert_mask, io->num_local_tokens, sorted_ids, sorted_w, sorted_e, num_valid, loc,
                                  s->H, terms_of(s), ws->max_rows, base + ws->off_xq, base + ws->off_xsf, zero_ptr,
                                  zero_bytes, (cudaStream_t)stream);
@@ -351,7 +367,10 @@ static int forward_impl(const b200moe_shape* s, const b200moe_workspace* ws, voi
                          io->num_local_tokens, sorted_ids, sorted_w, sorted_e, num_valid, loc,
                          base + ws->off_sort_scratch, sort_scratch_bytes(s->E_route), stream);
     if (rc) return rc;
-    if (fp8w && s->act_quant)
+    if (is_bf16(s))
+      rc = launch_gather_rows_bf16(io->x_bf16, loc, s->T, s->K, s->H, s->B, ws->max_rows, base + ws->off_xq, zero_ptr,
+                                   zero_bytes, (cudaStream_t)stream);
+    else if (fp8w && s->act_quant)
       rc = launch_quant_rows_fp8_1x128(io->x_bf16, 0, sorted_ids, num_valid, s->T, s->K, s->H, s->B, ws->max_rows,
                                        base + ws->off_xq, base + ws->off_xsf, zero_ptr, zero_bytes, loc, (cudaStream_t)stream);
     else if (fp8w)

@@ -122,6 +122,12 @@ int launch_grouped_gemm(const GemmArgs& a, cudaStream_t st);
 // FP8 128x128-block variant (moe_gemm_fp8_sm100.cu): w_data = e4m3 bytes [E, parts*rows, Kd], w_scale = fp32
 // [E, parts*rows/128, Kd/128] (used in place), a_q = two e4m3 terms [2, max_rows, Kd], NT ignored
 int launch_grouped_gemm_fp8(const GemmArgs& a, cudaStream_t st);
+// bf16-weight variant (moe_gemm_bf16_sm100.cu): w_data = bf16 [E, parts*rows, Kd], a_q = bf16 token rows
+// [max_rows, Kd] in sorted order; gate-up writes h as bf16 [max_rows, rows] to `oq`; scales and NT are ignored
+int launch_grouped_gemm_bf16(const GemmArgs& a, cudaStream_t st);
+// the layer input copied (bf16, no quantisation) to each token's sorted rows; also clears zero_ptr
+int launch_gather_rows_bf16(const void* src, const int32_t* loc, int T, int K, int Kd, int B, int64_t max_rows, void* q,
+                            void* zero_ptr, int64_t zero_bytes, cudaStream_t st);
 int launch_quant_rows_e4m3(const void* src, int src_mode, const uint32_t* sorted_ids, const int32_t* num_valid,
                            int T, int K, int Kd, int B, int64_t max_rows, void* q, void* sf, void* zero_ptr,
                            int64_t zero_bytes, const int32_t* loc, cudaStream_t st);

@@ -492,15 +492,35 @@ __device__ __forceinline__ void quant_store_fp8_1x128(int j, int64_t r, const Qu
     reinterpret_cast<float*>(g.sf)[((r / g.B) * (g.Kd / 128) + (j >> 2)) * g.B + (int)(r % g.B)] = u.scale;
 }
 
-template <int FMT>    // 0: packed-FP4 terms, 1: two e4m3 terms, 2: e4m3 with fp32 scales per 1x128
+// unquantised bf16 rows (bf16 weights): the unit is the 32 elements themselves, copied into sorted-row order
+__device__ __forceinline__ void quant_compute_copy(const __nv_bfloat16* src, int64_t srow, int j, const QuantGeom& g,
+                                                   QuantUnit& u) {
+  const uint4* p = reinterpret_cast<const uint4*>(src + srow * g.Kd + j * 32);
+#pragma unroll
+  for (int v = 0; v < 4; ++v) u.q[v] = p[v];
+}
+__device__ __forceinline__ void quant_store_copy(int j, int64_t r, const QuantGeom& g, const QuantUnit& u) {
+  uint4* p = reinterpret_cast<uint4*>(g.q + (r * g.Kd + j * 32) * 2);
+#pragma unroll
+  for (int v = 0; v < 4; ++v) p[v] = u.q[v];
+}
+
+template <int FMT>    // 0: packed-FP4 terms, 1: two e4m3 terms, 2: e4m3 with fp32 scales per 1x128, 3: bf16 as is
 __device__ __forceinline__ void quant_compute(const __nv_bfloat16* src, int64_t srow, int j, const QuantGeom& g, bool live,
                                               QuantUnit& u) {
   if (FMT == 2) quant_compute_fp8_1x128(src, srow, j, g, live, u);
-  else if (live) { if (FMT == 0) quant_compute_fp4(src, srow, j, g, u); else quant_compute_e4m3(src, srow, j, g, u); }
+  else if (live) {
+    if (FMT == 0) quant_compute_fp4(src, srow, j, g, u);
+    else if (FMT == 1) quant_compute_e4m3(src, srow, j, g, u);
+    else quant_compute_copy(src, srow, j, g, u);
+  }
 }
 template <int FMT>
 __device__ __forceinline__ void quant_store(int j, int64_t r, const QuantGeom& g, const QuantUnit& u) {
-  if (FMT == 0) quant_store_fp4(j, r, g, u); else if (FMT == 1) quant_store_e4m3(j, r, g, u); else quant_store_fp8_1x128(j, r, g, u);
+  if (FMT == 0) quant_store_fp4(j, r, g, u);
+  else if (FMT == 1) quant_store_e4m3(j, r, g, u);
+  else if (FMT == 2) quant_store_fp8_1x128(j, r, g, u);
+  else quant_store_copy(j, r, g, u);
 }
 
 // grid-stride zero fill in 16-byte vectors (the output buffer of the fused combine)
@@ -621,6 +641,17 @@ int launch_quant_rows_fp8_1x128(const void* src, int src_mode, const uint32_t* s
   B200_CHECK_CUDA(launch_chained(quant_rows_kernel<2>, dim3(quant_grid(max_rows * (Kd / 32))), dim3(256), 0, st,
                                  reinterpret_cast<const __nv_bfloat16*>(src), src_mode, sorted_ids, num_valid, T, K, g,
                                  (uint4*)zero_ptr, zero_bytes / 16));
+  return 0;
+}
+
+// bf16 weights: the layer input copied into sorted-row order, q = bf16 [max_rows, Kd] (no scales)
+int launch_gather_rows_bf16(const void* src, const int32_t* loc, int T, int K, int Kd, int B, int64_t max_rows, void* q,
+                            void* zero_ptr, int64_t zero_bytes, cudaStream_t st) {
+  B200_CHECK_ARG(Kd % 32 == 0 && loc != nullptr, "gather_rows: Kd=%d must be a multiple of 32 and loc given", Kd);
+  B200_CHECK_ARG(zero_bytes % 16 == 0 && ((uintptr_t)zero_ptr & 15) == 0, "gather_rows: zero region must be 16-byte aligned");
+  QuantGeom g = {Kd, Kd, B, 1, 128, max_rows, (uint8_t*)q, nullptr};
+  B200_CHECK_CUDA(launch_chained(quant_tokens_kernel<3>, dim3(quant_grid((int64_t)T * (Kd / 32))), dim3(256), 0, st,
+                                 reinterpret_cast<const __nv_bfloat16*>(src), loc, T, K, g, (uint4*)zero_ptr, zero_bytes / 16));
   return 0;
 }
 
@@ -757,6 +788,12 @@ int launch_sort_quant_small(int fmt, const void* x, const int32_t* ids, const fl
     const int KP = (int)round_up64(Kd, kKPad);
     QuantGeom g = {Kd, KP, B, NT, act_term_stride(B, NT, 2), max_rows, (uint8_t*)q, (uint8_t*)sf};
     B200_CHECK_CUDA(launch_chained(sort_quant_small_kernel<0>, dim3(small_grid((int64_t)T * K * (KP / 32))), dim3(256), 0,
+                                   st, (const __nv_bfloat16*)x, ids, w, T, K, E, mask, num_local, sorted_ids, sorted_w,
+                                   sorted_e, num_valid, loc, g, (uint4*)zero_ptr, zero_bytes / 16));
+  } else if (fmt == 3) {
+    B200_CHECK_ARG(Kd % 32 == 0, "sort_quant_small (bf16): Kd %d", Kd);
+    QuantGeom g = {Kd, Kd, B, 1, 128, max_rows, (uint8_t*)q, nullptr};
+    B200_CHECK_CUDA(launch_chained(sort_quant_small_kernel<3>, dim3(small_grid((int64_t)T * K * (Kd / 32))), dim3(256), 0,
                                    st, (const __nv_bfloat16*)x, ids, w, T, K, E, mask, num_local, sorted_ids, sorted_w,
                                    sorted_e, num_valid, loc, g, (uint4*)zero_ptr, zero_bytes / 16));
   } else {

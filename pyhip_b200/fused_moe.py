@@ -3,9 +3,9 @@ tingqli/pyhip) in front of the sm_100a kernels.
 
 Same positional / keyword names and argument meaning as the reference; the aiter enums it takes
 (`ActivationType`, `QuantType`) are re-declared here because aiter is not a dependency.  The
-reference wrapper accepts QuantType.No and per_128x128 and reaches MXFP4 only through its raw
-kernels (tests/contrib/moe/test_moe.py:347-374, 638-771); this wrapper adds per_1x32 to the same
-signature: ``w1``/``w2`` are packed E2M1 (uint8 or float4_e2m1fn_x2, low nibble = even element)
+reference wrapper accepts QuantType.No (bf16 weights, no scales) and per_128x128 and reaches MXFP4
+only through its raw kernels (tests/contrib/moe/test_moe.py:347-374, 638-771); this wrapper takes
+both and adds per_1x32 to the same signature: ``w1``/``w2`` are packed E2M1 (uint8 or float4_e2m1fn_x2, low nibble = even element)
 and ``w1_scale``/``w2_scale`` are E8M0 bytes ``[E*N, Kd/32]`` (or ``[E, N, Kd/32]``).
 
 Work is enqueued on ``torch.cuda.current_stream()`` and never synchronises.
@@ -65,7 +65,7 @@ def pick_block(T: int, K: int, E: int, weight_format: int = _lib.W_MXFP4) -> int
         return 32
     if per_expert <= 48:
         return 64
-    fp8 = weight_format != _lib.W_MXFP4
+    fp8 = weight_format in (_lib.W_FP8_128, _lib.W_FP8_ROW)
     sigma = math.sqrt(max(per_expert * (1.0 - 1.0 / max(E, 1)), 1e-6))
     lo, hi = max(1, int(per_expert - 4 * sigma)), int(per_expert + 4 * sigma) + 1
     best, best_cost = 96, None
@@ -150,6 +150,26 @@ class PreparedWeightsFP8:
         self.device = w1.device
 
 
+class PreparedWeightsBF16:
+    """Unquantised bf16 expert weights (the reference wrapper's QuantType.No, src/contrib/fused_moe.py:253):
+    w1 [E, 2I, H], w2 [E, H, I], consumed in place; there are no scales."""
+
+    def __init__(self, w1, w2):
+        if not w1.is_cuda:
+            raise ValueError("weights must be CUDA tensors")
+        if w1.dtype != torch.bfloat16 or w2.dtype != torch.bfloat16:
+            raise TypeError("QuantType.No takes bfloat16 weights")
+        E, N1, H = w1.shape
+        self.E, self.I, self.H = E, N1 // 2, H
+        if tuple(w2.shape) != (E, H, self.I):
+            raise ValueError(f"w2 shape {tuple(w2.shape)} does not match w1 {tuple(w1.shape)}")
+        if H % 32 or self.I % 32:
+            raise ValueError("H and I must be multiples of 32")
+        self.w1_data, self.w2_data = w1.contiguous(), w2.contiguous()
+        self.w1_scale = self.w2_scale = None
+        self.device = w1.device
+
+
 _prepared_cache: dict = {}          # insertion-ordered: least recently used first
 _workspace_cache: dict = {}
 _PREPARED_CACHE_ENTRIES = 8
@@ -160,14 +180,19 @@ def prepare_weights(w1, w1_scale, w2, w2_scale, weight_format=_lib.W_MXFP4):
     version counters of the scale tensors (scales updated in place are prepared again).  The cache keeps the
     `_PREPARED_CACHE_ENTRIES` most recently used layers alive -- an entry references the caller's weight tensors
     -- and `release_prepared()` drops them all."""
-    key = (w1.data_ptr(), w1_scale.data_ptr(), w2.data_ptr(), w2_scale.data_ptr(), tuple(w1.shape), weight_format,
-           w1_scale._version, w2_scale._version)
+    if weight_format == _lib.W_BF16:
+        key = (w1.data_ptr(), 0, w2.data_ptr(), 0, tuple(w1.shape), weight_format, 0, 0)
+    else:
+        key = (w1.data_ptr(), w1_scale.data_ptr(), w2.data_ptr(), w2_scale.data_ptr(), tuple(w1.shape), weight_format,
+               w1_scale._version, w2_scale._version)
     hit = _prepared_cache.pop(key, None)
     if hit is None:
         while len(_prepared_cache) >= _PREPARED_CACHE_ENTRIES:
             _prepared_cache.pop(next(iter(_prepared_cache)))
         if weight_format == _lib.W_MXFP4:
             pw = PreparedWeights(w1, w1_scale, w2, w2_scale)
+        elif weight_format == _lib.W_BF16:
+            pw = PreparedWeightsBF16(w1, w2)
         else:
             pw = PreparedWeightsFP8(w1, w1_scale, w2, w2_scale, row_scaled=weight_format == _lib.W_FP8_ROW)
         hit = (pw, (w1, w1_scale, w2, w2_scale))      # the sources stay alive, so their addresses identify them
@@ -193,7 +218,8 @@ class MoEPlan:
                                 doweight_stage1=1 if doweight_stage1 else 0, cta_pairs=cta_pairs)
         self.capacity = T
         self.terms = act_terms or 3
-        self.fp8 = weight_format != _lib.W_MXFP4
+        self.fp8 = weight_format in (_lib.W_FP8_128, _lib.W_FP8_ROW)
+        self.bf16 = weight_format == _lib.W_BF16
         self.aq = act_quant
         self.ws = _lib.workspace_layout(self.shape)
         self.buf = torch.empty(self.ws.total_bytes + 1024, dtype=torch.uint8, device=device)
@@ -242,6 +268,8 @@ class MoEPlan:
         s, ws = self.shape, self.ws
         ids_o, _, _, nv_o, _ = self.sort_outputs()
         base = self.base
+        if self.bf16:
+            raise NotImplementedError("bf16 weights: the stage-by-stage surface starts at the whole-layer call")
         if self.fp8:
             fn = _lib.lib().b200moe_quant_rows_fp8_1x128 if self.aq else _lib.lib().b200moe_quant_rows_e4m3
             _lib.check(fn(_ptr(x), 0, _ptr(ids_o), _ptr(nv_o), s.T, s.K, s.H, s.B, ws.max_rows,
@@ -330,8 +358,9 @@ def moe_forward(plan: MoEPlan, pw: PreparedWeights, hidden_states, topk_weight, 
     io = _lib.Io(x_bf16=hidden_states.data_ptr(), topk_ids=topk_ids.data_ptr(), topk_weight=topk_weight.data_ptr(),
                  expert_mask=None if expert_mask is None else expert_mask.data_ptr(),
                  num_local_tokens=None if num_local_tokens is None else num_local_tokens.data_ptr(),
-                 w1_q=pw.w1_data.data_ptr(), w1_scale_prepared=pw.w1_scale.data_ptr(), w2_q=pw.w2_data.data_ptr(),
-                 w2_scale_prepared=pw.w2_scale.data_ptr(), bias1=None if bias1 is None else bias1.data_ptr(),
+                 w1_q=pw.w1_data.data_ptr(), w1_scale_prepared=None if pw.w1_scale is None else pw.w1_scale.data_ptr(),
+                 w2_q=pw.w2_data.data_ptr(), w2_scale_prepared=None if pw.w2_scale is None else pw.w2_scale.data_ptr(),
+                 bias1=None if bias1 is None else bias1.data_ptr(),
                  bias2=None if bias2 is None else bias2.data_ptr(), y_bf16=out.data_ptr())
     _lib.check(_lib.lib().b200moe_forward_ex(ctypes.byref(plan.shape), ctypes.byref(plan.ws),
                                              ctypes.c_void_p(plan.base), ctypes.byref(io), _stream()), "forward")
@@ -394,19 +423,22 @@ def fused_moe(hidden_states, w1, w2, topk_weight, topk_ids, expert_mask=None,
         raise RuntimeError("fused_moe runs on a CUDA device only (sm_100a); there is no CPU path")
     if hidden_states.dtype != torch.bfloat16:
         raise TypeError("hidden_states must be bfloat16")
-    fmt = {int(QuantType.per_1x32): _lib.W_MXFP4, int(QuantType.per_128x128): _lib.W_FP8_128,
-           int(QuantType.per_Token): _lib.W_FP8_ROW, int(QuantType.per_Tensor): _lib.W_FP8_ROW}.get(int(quant_type))
+    fmt = {int(QuantType.No): _lib.W_BF16, int(QuantType.per_1x32): _lib.W_MXFP4,
+           int(QuantType.per_128x128): _lib.W_FP8_128, int(QuantType.per_Token): _lib.W_FP8_ROW,
+           int(QuantType.per_Tensor): _lib.W_FP8_ROW}.get(int(quant_type))
     if fmt is None:
-        raise NotImplementedError(f"quant_type={quant_type!r}: per_1x32 (MXFP4), per_128x128, per_Token and per_Tensor "
-                                  "(FP8) are implemented")
+        raise NotImplementedError(f"quant_type={quant_type!r}: No (bf16 weights), per_1x32 (MXFP4), per_128x128, per_Token "
+                                  "and per_Tensor (FP8) are implemented")
     if int(activation) not in (ActivationType.Silu, ActivationType.Swiglu):
         raise NotImplementedError(f"activation={activation!r}: Silu and Swiglu are implemented")
     if a1_scale is not None or a2_scale is not None:
         raise NotImplementedError("pre-quantised activations (a1_scale / a2_scale) are not implemented: pass bf16")
     if hidden_pad or intermediate_pad:
         raise NotImplementedError("padding arguments are not implemented")
-    if w1_scale is None or w2_scale is None:
+    if fmt != _lib.W_BF16 and (w1_scale is None or w2_scale is None):
         raise ValueError("quantised weights need w1_scale and w2_scale")
+    if fmt == _lib.W_BF16 and (act_terms or w1.dtype != torch.bfloat16):
+        raise ValueError("quant_type=No takes bfloat16 weights and no act_terms (activations stay bf16)")
     if dtype not in (None, torch.bfloat16):
         raise NotImplementedError("output dtype must be bfloat16")
     if combine not in ("auto", "gather", "fused"):

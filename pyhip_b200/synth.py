@@ -87,6 +87,13 @@ def make_weights_mxfp4(E: int, H: int, I: int, seed: int = 0, experts=None):
     return w1_q, w1_s, w2_q, w2_s
 
 
+def make_weights_bf16(E: int, H: int, I: int, seed: int = 0):
+    """Unquantised weights of the same draw: w1 bf16 [E,2I,H] (gate rows then up rows), w2 bf16 [E,H,I]."""
+    w1 = torch.stack([_expert_weight(e, 2 * I, H, seed, 0) for e in range(E)]).to(torch.bfloat16)
+    w2 = torch.stack([_expert_weight(e, H, I, seed, 1) for e in range(E)]).to(torch.bfloat16)
+    return w1, w2
+
+
 def make_weights_mxfp4_fast(E: int, H: int, I: int, seed: int = 0, device="cpu", distinct: int = 8):
     """Benchmark-sized MXFP4 weights: ``distinct`` experts are drawn and quantised exactly as
     in make_weights_mxfp4, the rest repeat them cyclically with their bytes rolled by the

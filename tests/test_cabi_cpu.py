@@ -43,6 +43,18 @@ def test_workspace_layout_arithmetic(L):
     assert ws.off_xsf - ws.off_xq >= 3 * ws.max_rows * 3072 // 2
 
 
+def test_workspace_layout_for_bf16_weights(L):
+    """Unquantised weights: the row regions hold bf16 rows in sorted order (2 bytes per element), no scale regions."""
+    s = _lib.Shape(T=64, K=4, E=128, E_route=128, H=2880, I=2880, B=32, weight_format=_lib.W_BF16, activation=0,
+                   swiglu_limit=7.0, act_terms=0)
+    ws = _lib.workspace_layout(s)
+    assert ws.off_xsf - ws.off_xq >= ws.max_rows * 2880 * 2
+    assert ws.off_hsf - ws.off_hq >= ws.max_rows * 2880 * 2
+    assert ws.off_hq - ws.off_xsf == 1024 and ws.off_out2 - ws.off_hsf == 1024
+    s.act_quant = 1
+    assert L.b200moe_workspace_layout(ctypes.byref(s), ctypes.byref(_lib.Workspace())) < 0
+
+
 @pytest.mark.parametrize("field,value", [("B", 40), ("H", 100), ("I", 0), ("K", 0), ("T", 1 << 24),
                                          ("weight_format", 7), ("activation", 9), ("E_route", 4), ("act_terms", 5),
                                          ("combine_mode", 2), ("act_quant", 2), ("doweight_stage1", 2), ("cta_pairs", 3)])
