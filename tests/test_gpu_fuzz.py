@@ -1,7 +1,7 @@
 """GPU tier: seeded random layer configurations against the CPU oracle.
 
 Each case draws a shape (ragged token counts, hidden sizes that are not multiples of the k-tile, expert counts from 2
-to 64, top-k up to 8), a routing law, a sort block, an activation format, the combine form, the CTA-pair switch and the
+to 64, top-k up to 8), a routing law, a sort block, a weight format (MXFP4, FP8 128x128, bf16), an activation format, the combine form, the CTA-pair switch and the
 optional arguments (expert mask, a live-token count below T, biases, stage-1 weights) from one seed, runs the layer
 through the public call and compares with the oracle called with the same options.  The fixed cases of the other
 files pin single features; these cover their combinations.
@@ -35,8 +35,8 @@ def _close(y, ref, what, a4w4=False):
     assert cos >= COS and mx <= bound, f"{what}: cosine {cos:.6f} max_abs {mx:.3e} bound {bound:.3e}"
 
 
-def _draw(seed, fp8):
-    r = random.Random(seed * 7919 + (1 if fp8 else 0))
+def _draw(seed, fp8, bf16=False):
+    r = random.Random(seed * 7919 + (1 if fp8 else 0) + (2 if bf16 else 0))
     step = 128 if fp8 else 32
     c = dict(
         T=r.choice([1, 2, 3, 5, 8, 17, 31, 64, 65, 100, 129, 255, 300, 513]),
@@ -49,18 +49,22 @@ def _draw(seed, fp8):
     c["K"] = r.randint(1, min(c["E"], 8))
     if fp8:
         c["act"] = r.choice(["terms", "terms", "1x128"])
-    else:
+    elif not bf16:
         c["terms"] = r.choice([0, 0, 3, 4, 1])
     return c
 
 
-def _run_case(seed, fp8):
-    c = _draw(seed, fp8)
+def _run_case(seed, fp8, bf16=False):
+    c = _draw(seed, fp8, bf16)
     T, H, I, E, K = c["T"], c["H"], c["I"], c["E"], c["K"]
     what = f"seed {seed} {c}"
     x = synth.make_hidden(T, H, seed)
     tw, ids = synth.make_routing(T, E, K, c["routing"], seed)
-    w = (synth.make_weights_fp8 if fp8 else synth.make_weights_mxfp4)(E, H, I, seed=seed)
+    if bf16:
+        w1, w2 = synth.make_weights_bf16(E, H, I, seed=seed)
+        w = (w1, None, w2, None)
+    else:
+        w = (synth.make_weights_fp8 if fp8 else synth.make_weights_mxfp4)(E, H, I, seed=seed)
     g = torch.Generator().manual_seed(seed)
     kw, okw = {}, {}
     if c["bias"]:
@@ -81,23 +85,23 @@ def _run_case(seed, fp8):
         keep = torch.rand(E, generator=g) < 0.6
         keep[int(ids[0, 0])] = True                       # at least one expert stays
         kw["expert_mask"] = keep.to(torch.int32).to(DEV)
-    w_local = tuple(t[keep] for t in w)
+    w_local = tuple(None if t is None else t[keep].to(DEV) for t in w)
     if "bias1" in kw:
         kw["bias1"], kw["bias2"] = kw["bias1"][keep].to(DEV), kw["bias2"][keep].to(DEV)
     if fp8:
         kw["act_quant"] = c["act"]
         if c["act"] == "1x128":
             okw["act_quant"] = "fp8_1x128"
-    else:
+    elif not bf16:
         kw["act_terms"] = c["terms"]
         if c["terms"] == 1:
             okw["act_quant"] = "mxfp4"
     if c["B"]:
         kw["block_size_M"] = c["B"]
     act = ActivationType.Silu if c["activation"] == "silu" else ActivationType.Swiglu
-    qt = QuantType.per_128x128 if fp8 else QuantType.per_1x32
-    y = fused_moe(x.to(DEV), w_local[0].to(DEV), w_local[2].to(DEV), tw.to(DEV), ids.to(DEV), quant_type=qt,
-                  w1_scale=w_local[1].to(DEV), w2_scale=w_local[3].to(DEV), activation=act, combine=c["combine"],
+    qt = QuantType.No if bf16 else QuantType.per_128x128 if fp8 else QuantType.per_1x32
+    y = fused_moe(x.to(DEV), w_local[0], w_local[2], tw.to(DEV), ids.to(DEV), quant_type=qt,
+                  w1_scale=w_local[1], w2_scale=w_local[3], activation=act, combine=c["combine"],
                   cta_pairs=c["pairs"], **kw)
     torch.cuda.synchronize()
     y = y.cpu()
@@ -108,9 +112,12 @@ def _run_case(seed, fp8):
         return
     # the masked layer is the full one with the dropped experts' routing weights set to zero
     tw_m = tw * keep[ids.long()].float()
-    oracle = orc.torch_moe_oracle_fp8 if fp8 else orc.torch_moe_oracle_mxfp4
-    ref = oracle(x[:n], *w, tw_m[:n], ids[:n], activation=c["activation"], swiglu_limit=7.0, **okw)
-    _close(y[:n], ref, what, a4w4=not fp8 and c["terms"] == 1)
+    if bf16:
+        ref = orc.torch_moe_oracle(x[:n], w[0], w[2], tw_m[:n], ids[:n], activation=c["activation"], swiglu_limit=7.0, **okw)
+    else:
+        oracle = orc.torch_moe_oracle_fp8 if fp8 else orc.torch_moe_oracle_mxfp4
+        ref = oracle(x[:n], *w, tw_m[:n], ids[:n], activation=c["activation"], swiglu_limit=7.0, **okw)
+    _close(y[:n], ref, what, a4w4=c.get("terms") == 1)
 
 
 @pytest.mark.parametrize("seed", range(28))
@@ -121,3 +128,8 @@ def test_random_mxfp4_layers(seed):
 @pytest.mark.parametrize("seed", range(16))
 def test_random_fp8_layers(seed):
     _run_case(seed, fp8=True)
+
+
+@pytest.mark.parametrize("seed", range(16))
+def test_random_bf16_weight_layers(seed):
+    _run_case(seed, fp8=False, bf16=True)
