@@ -51,6 +51,7 @@ L2_BYTES = 126e6
 PAIRS = {"auto": 0, "off": 1, "on": 2}
 FP4_NOMINAL_TFLOPS = 9000.0
 FP8_NOMINAL_TFLOPS = 4500.0
+BF16_NOMINAL_TFLOPS = 2250.0
 
 
 def parse():
@@ -71,6 +72,8 @@ def parse():
     ap.add_argument("--act-terms", type=int, default=0, help="MXFP4 activation terms (0 = default 3; 1 = plain a4w4)")
     ap.add_argument("--act-quant", default="terms", choices=["terms", "1x128"],
                     help="FP8 weights: two e4m3 terms with E8M0 scales (default) or the per-token 1x128 fp32-scale format")
+    ap.add_argument("--weights", default="native", choices=["native", "bf16"],
+                    help="bf16: the same shape with unquantised bf16 weights (QuantType.No; one GPU, implies --no-extras)")
     ap.add_argument("--cta-pairs", default="auto", choices=["auto", "off", "on"],
                     help="MXFP4 GEMMs on CTA pairs (tcgen05.mma.cta_group::2): auto = in the compute-bound regime")
     ap.add_argument("--no-extras", action="store_true", help="only the headline workload (no sweep / prefill / config3 / config4)")
@@ -311,7 +314,9 @@ def time_repeated(fn, steps, warmup, dist=None, total_ms=1000.0, min_rep=5, max_
 # ---------------------------------------------------------------------------------------------------
 # one GPU
 # ---------------------------------------------------------------------------------------------------
-def dtype_text(fp8, act_terms):
+def dtype_text(fp8, act_terms, bf16=False):
+    if bf16:
+        return "bf16 weights x bf16 activations (kind::f16), f32 accumulate"
     if fp8:
         return "fp8-e4m3 128x128-block weights x 2-term e4m3 activations (kind::mxf8f6f4), f32 accumulate"
     nt = act_terms or 3
@@ -322,13 +327,26 @@ def dtype_text(fp8, act_terms):
 class Case:
     """Weights, prepared weights and helpers of one workload on one device."""
 
-    def __init__(self, workload, dev, experts=0):
+    def __init__(self, workload, dev, experts=0, weights="native"):
         import torch
-        from pyhip_b200 import QuantType, synth
+        from pyhip_b200 import QuantType, _lib, synth
         from pyhip_b200.fused_moe import prepare_weights
         shape = synth.CONFIGS[workload]
         if experts:
             shape = dataclasses.replace(shape, E=experts)
+        self.bf16 = weights == "bf16"
+        if self.bf16:
+            # the same shape with unquantised weights, drawn on the device (N(0, 0.02), as the quantised sets are)
+            shape = dataclasses.replace(shape, wq="bf16")
+            self.workload, self.shape, self.dev = workload, shape, dev
+            self.fp8, self.fmt, self.qt, self.wbytes = False, _lib.W_BF16, QuantType.No, 2.0
+            g = torch.Generator(device=dev).manual_seed(0)
+            w1 = (torch.randn(shape.E, 2 * shape.I, shape.H, generator=g, device=dev) * 0.02).to(torch.bfloat16)
+            w2 = (torch.randn(shape.E, shape.H, shape.I, generator=g, device=dev) * 0.02).to(torch.bfloat16)
+            self.w = (w1, None, w2, None)
+            self.pw = prepare_weights(w1, None, w2, None, weight_format=self.fmt)
+            torch.cuda.synchronize()
+            return
         self.workload, self.shape, self.dev = workload, shape, dev
         self.fp8 = shape.wq == "fp8_128"
         self.fmt = 1 if self.fp8 else 0
@@ -341,7 +359,7 @@ class Case:
         torch.cuda.synchronize()
 
     def dtype_text(self, act_terms):
-        return dtype_text(self.fp8, act_terms)
+        return dtype_text(self.fp8, act_terms, self.bf16)
 
     def inputs(self, T, seed=0):
         from pyhip_b200 import synth
@@ -399,7 +417,7 @@ def measure_layer(case, T, args, steps, warmup, combine, act_terms=0, local=0, t
     return {"T": T, "ms_per_step": ms, "ms_per_step_min": r["min"] / n_sets, "ms_per_step_max": r["max"] / n_sets,
             "repeats": r["repeats"], "steps_per_region": rounds * n_sets, "tokens_per_s": T / (ms * 1e-3),
             "experts_hit": hit, "block": B, "combine": combine,
-            "act_terms": (1 if act_quant else 2) if case.fp8 else (act_terms or 3),
+            "act_terms": 0 if case.bf16 else (1 if act_quant else 2) if case.fp8 else (act_terms or 3),
             "launch": launch_mode, "launches_per_step": launches_per_call(T, s.K, s.E, cm),
             "routing_sets_rotated": n_sets,
             "layer_gbs": layer_bytes / (ms * 1e-3) / 1e9,
@@ -420,8 +438,14 @@ def measure_gemms(case, T, args, steps, warmup, act_terms=0, act_quant=0):
     B = pick_block(T, s.K, s.E, case.fmt)
     plan = get_plan(T, s.K, s.E, s.E, s.H, s.I, B, 0, 7.0, dev, act_terms=act_terms, weight_format=case.fmt, act_quant=act_quant,
                     cta_pairs=PAIRS[args.cta_pairs])
-    plan.sort(ids, tw)
-    plan.quant_input(x)
+    if case.bf16:
+        # no stage-by-stage front end for unquantised weights: one whole call leaves the sort arrays and the bf16
+        # rows of both stages in the workspace, and the two GEMMs are then timed on them
+        from pyhip_b200.fused_moe import moe_forward
+        moe_forward(plan, case.pw, x, tw, ids, None, torch.empty(T, s.H, dtype=torch.bfloat16, device=dev))
+    else:
+        plan.sort(ids, tw)
+        plan.quant_input(x)
     k = max(3, min(steps, 200 if T <= 512 else 20))
     gu = time_repeated(lambda: plan.gateup(case.pw, None), k, 3, total_ms=300.0)
     dn = time_repeated(lambda: plan.down(case.pw), k, 3, total_ms=300.0)
@@ -431,17 +455,22 @@ def measure_gemms(case, T, args, steps, warmup, act_terms=0, act_quant=0):
     gu_flops = 4.0 * T * s.K * s.H * s.I
     peak, peak_kind = measured_peaks()
     hbm_time = gu_bytes / (peak * 1e9)
-    nominal = FP8_NOMINAL_TFLOPS if case.fp8 else FP4_NOMINAL_TFLOPS
-    common = {"kernel": "moe_grouped_gemm_fp8_kernel<gate-up>" if case.fp8 else "moe_grouped_gemm_kernel<gate-up>",
+    nominal = BF16_NOMINAL_TFLOPS if case.bf16 else FP8_NOMINAL_TFLOPS if case.fp8 else FP4_NOMINAL_TFLOPS
+    common = {"kernel": ("moe_grouped_gemm_bf16_kernel<gate-up>" if case.bf16 else
+                         "moe_grouped_gemm_fp8_kernel<gate-up>" if case.fp8 else "moe_grouped_gemm_kernel<gate-up>"),
               "us_per_launch": per_launch_s * 1e6, "us_per_launch_min": gu["min"] * 1e3,
               "down_us_per_launch": dn["ms"] * 1e3, "traffic": profiled_traffic(s, T) if not (act_terms == 1 or act_quant) else None}
     # weight-streaming regime (few rows per expert): HBM roofline; from 64 rows per expert on the launch is scored
     # against the dense tensor rate of its format, as the configurations state (the gpt-oss prefill shape sits at
     # the ridge: at the nominal rates its tensor time is 0.7 of its HBM time)
     if T * s.K / s.E >= 64 or gu_flops / (nominal * 1e12) > hbm_time:
-        probe = dense_mma_rate(dev, 1 if case.fp8 else 0)
         ach = gu_flops / per_launch_s / 1e12
         bf16, bf16_kind = measured_peaks("bf16_tflops_sustained" if gu["ms"] > 0.5 else "bf16_tflops")
+        if case.bf16:       # scored against the measured cuBLAS bf16 rate, with the nominal dense figure beside it
+            return {"bound": "tensor", "achieved": ach, "peak": bf16, "unit": "TFLOP/s", "frac": ach / bf16,
+                    "peak_kind": bf16_kind, "frac_of_nominal_bf16_2250": ach / nominal, "algorithmic_flops": gu_flops,
+                    "mma_work_over_algorithmic": 1.0, **common}
+        probe = dense_mma_rate(dev, 1 if case.fp8 else 0)
         return {"bound": "tensor", "achieved": ach, "peak": nominal, "unit": "TFLOP/s", "frac": ach / nominal,
                 "peak_kind": ("nominal dense FP8 (4.5 PFLOP/s)" if case.fp8 else "nominal dense FP4 (9 PFLOP/s)"),
                 "peak_probe_tflops": probe, "frac_of_probe": ach / probe if probe else None,
@@ -478,7 +507,10 @@ def measure_e2e(case, T, args, steps, warmup, combine, act_terms=0, act_quant='t
 def run_single(args, dev, local):
     import torch
     from pyhip_b200 import release_prepared, synth
-    case = Case(args.workload, dev, args.experts)
+    case = Case(args.workload, dev, args.experts, args.weights)
+    is_bf16 = case.bf16
+    if is_bf16:
+        args.no_extras, args.no_cpu_baseline, args.act_terms = True, True, 0
     s = case.shape
     T = args.tokens or s.T
     aq = 1 if (args.act_quant == '1x128' and case.fp8) else 0
@@ -533,11 +565,11 @@ def run_single(args, dev, local):
             "warmup": args.warmup, "ms_per_step": head["ms_per_step"], "ms_per_step_min": head["ms_per_step_min"],
             "ms_per_step_max": head["ms_per_step_max"], "repeats": head["repeats"],
             "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
-            "dtype": dtype_text(s.wq == "fp8_128", args.act_terms), "data": "synthetic",
+            "dtype": dtype_text(s.wq == "fp8_128", args.act_terms, is_bf16), "data": "synthetic",
             "config": {"workload": f"{args.workload} H{s.H} I{s.I} E{s.E} top{s.K} T{T} {s.wq}", "block": head["block"],
                        "combine": args.combine, "launch": head["launch"],
                        "l2": ("inputs larger than L2: %.2f GB of expert weights streamed per step" %
-                              (hit * 3.0 * s.H * s.I * ((1.0 + 4.0 / 16384) if s.wq == "fp8_128" else (0.5 + 1.0 / 32)) / 1e9)
+                              (hit * 3.0 * s.H * s.I * (2.0 if is_bf16 else (1.0 + 4.0 / 16384) if s.wq == "fp8_128" else (0.5 + 1.0 / 32)) / 1e9)
                               + (f"; {head['routing_sets_rotated']} routing sets rotated" if head["routing_sets_rotated"] > 1 else ""))},
             "clocks": head["clocks"], "e2e": e2e, "gpu_launches": head["launches_per_step"] * head["steps_per_region"],
             "roofline": roofline, "cpu_baseline": cpu,

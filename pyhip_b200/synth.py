@@ -179,7 +179,7 @@ def algorithmic_flops(T: int, K: int, H: int, I: int) -> float:
 
 def algorithmic_bytes(T: int, H: int, I: int, experts_hit: int, wq: str = "mxfp4") -> float:
     """Distinct experts' weight+scale bytes plus bf16 input and output."""
-    per = 3.0 * H * I * ((0.5 + 1.0 / 32) if wq == "mxfp4" else (1.0 + 4.0 / 16384))
+    per = 3.0 * H * I * ((0.5 + 1.0 / 32) if wq == "mxfp4" else 2.0 if wq == "bf16" else (1.0 + 4.0 / 16384))
     return experts_hit * per + 2.0 * T * H * 2
 
 
