@@ -191,6 +191,10 @@ def test_empty_batch_and_argument_errors():
     assert y.shape == (0, H)
     with pytest.raises(NotImplementedError):
         fused_moe(torch.zeros(1, H, dtype=torch.bfloat16, device=DEV), w1_q, w2_q, torch.ones(1, K, device=DEV),
+                  torch.zeros(1, K, dtype=torch.int32, device=DEV), quant_type=QuantType.per_1x128, w1_scale=w1_s,
+                  w2_scale=w2_s)
+    with pytest.raises(ValueError):          # QuantType.No means bf16 weights: packed bytes are refused
+        fused_moe(torch.zeros(1, H, dtype=torch.bfloat16, device=DEV), w1_q, w2_q, torch.ones(1, K, device=DEV),
                   torch.zeros(1, K, dtype=torch.int32, device=DEV), quant_type=QuantType.No)
     with pytest.raises(RuntimeError):
         fused_moe(torch.zeros(1, H, dtype=torch.bfloat16), w1_q, w2_q, torch.ones(1, K), torch.zeros(1, K),
