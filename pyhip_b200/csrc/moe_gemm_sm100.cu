@@ -189,18 +189,45 @@ moe_grouped_gemm_kernel(const __grid_constant__ GemmParams p) {
   const int w_first = PAIR ? (int)(blockIdx.x >> 1) : (int)blockIdx.x;
   const int w_step = PAIR ? (int)(gridDim.x >> 1) : (int)gridDim.x;
 
+  // row ids of work item w's sorted block, 32 per lane group (the live rows of a block are a prefix of it)
+  auto fetch_ids = [&](int w, uint32_t (&r)[4]) {
+    const int r0 = (w / items_per_block) * B;
+#pragma unroll
+    for (int q = 0; q < 4; ++q) r[q] = (w < total_work && q * 32 + lane < B) ? p.sorted_ids[r0 + q * 32 + lane] : 0xFFFFFFFFu;
+  };
+  auto live_rows = [&](const uint32_t (&r)[4]) {
+    int n = 0;
+#pragma unroll
+    for (int q = 0; q < 4; ++q)
+      n += __popc(__ballot_sync(0xffffffffu, (int)(r[q] >> 24) < p.topk && (int)(r[q] & 0xFFFFFFu) < p.T));
+    return n;
+  };
+
   if (warp == 0) {
     // ------------------------------------------------------------------ TMA producer
+    // The whole warp walks the loop (PAIR: it counts the block's live rows with ballots); lane 0 waits and issues.
     if (lane == 0) {
       prefetch_tensormap(&p.tmW);
       prefetch_tensormap(&p.tmA);
-      int stage = 0;
-      uint32_t phase = 0;
-      int64_t issued = 0;
-      bool ok = true;
-      PROF_DECL(t_wait);
-      const int64_t sfa_step = geo.sfa_bytes;
-      for (int w = w_first; w < total_work && ok; w += w_step) {
+    }
+    int stage = 0;
+    uint32_t phase = 0;
+    int64_t issued = 0;
+    bool ok = true;
+    PROF_DECL(t_wait);
+    const int64_t sfa_step = geo.sfa_bytes;
+    uint32_t pid[4];
+    if (PAIR) fetch_ids(w_first, pid);
+    for (int w = w_first; w < total_work && ok; w += w_step) {
+      // PAIR: the MMAs span only the live rows of the block (rounded up to 16), half of them from each CTA: this
+      // CTA fetches the token rows from its half's first row on (the box keeps its size; rows beyond are unused)
+      int row_off = 0;
+      if (PAIR) {
+        const int n_mma = min(B, max(16, (live_rows(pid) + 15) & ~15));
+        fetch_ids(w + w_step, pid);
+        row_off = (int)cta_rank * (n_mma / 2);
+      }
+      if (lane == 0) {
         // (PAIR: item w covers weight-tile items 2*mp and 2*mp + 1 of the block; this CTA takes the one of its rank)
         const int b = w / items_per_block, m = PAIR ? 2 * (w - b * items_per_block) + (int)cta_rank : w - b * items_per_block;
         const bool tile_live = m < p.MT;
@@ -223,7 +250,7 @@ moe_grouped_gemm_kernel(const __grid_constant__ GemmParams p) {
             const uint32_t ab = (uint32_t)(geo.a_bytes + geo.b_bytes), sf = (uint32_t)(geo.sfa_bytes + geo.sfb_bytes);
             mbar_expect_tx(full, cta_rank == 0 ? 2 * ab + sf : sf);
             tma_load_4d_pair(st, &p.tmW, full, kb * kTileK, m * (GATEUP ? kTileM : 2 * kTileM), 0, e);
-            tma_load_3d_pair(st + geo.a_bytes, &p.tmA, full, kb * kTileK, r0 + (int)cta_rank * NB, 0);
+            tma_load_3d_pair(st + geo.a_bytes, &p.tmA, full, kb * kTileK, r0 + row_off, 0);
           } else {
             mbar_expect_tx(full, geo.tx_bytes);
             tma_load_4d(st, &p.tmW, full, kb * kTileK, m * (GATEUP ? kTileM : 2 * kTileM), 0, e);
@@ -237,6 +264,9 @@ moe_grouped_gemm_kernel(const __grid_constant__ GemmParams p) {
           if (++stage == S) { stage = 0; phase ^= 1; }
         }
       }
+      ok = __shfl_sync(0xffffffffu, (int)ok, 0) != 0;
+    }
+    if (lane == 0) {
 #ifdef B200MOE_PROFILE
       if (blockIdx.x == 0) p.status[4] = (int32_t)(t_wait >> 10);   // kilo-cycles waiting for a free stage
 #endif
@@ -278,20 +308,12 @@ moe_grouped_gemm_kernel(const __grid_constant__ GemmParams p) {
     // expert's last block cost neither tensor time nor operand reads.  The row ids of the NEXT item are
     // fetched while the current one is multiplied, so the count is ready without a stall.
     uint32_t nid[4];
-    auto fetch_ids = [&](int w, uint32_t (&r)[4]) {
-      const int r0 = (w / items_per_block) * B;
-#pragma unroll
-      for (int q = 0; q < 4; ++q) r[q] = (w < total_work && q * 32 + lane < B) ? p.sorted_ids[r0 + q * 32 + lane] : 0xFFFFFFFFu;
-    };
     fetch_ids(w_first, nid);
     for (int w = w_first; w < total_work_mma && ok; w += w_step) {
-      int nlive = 0;
-#pragma unroll
-      for (int q = 0; q < 4; ++q)
-        nlive += __popc(__ballot_sync(0xffffffffu, (int)(nid[q] >> 24) < p.topk && (int)(nid[q] & 0xFFFFFFu) < p.T));
+      const int nlive = live_rows(nid);
       fetch_ids(w + w_step, nid);
-      // (PAIR: the token rows are split between the CTAs at a fixed row, so the instruction always spans the tile)
-      const uint32_t n_mma = (merged || PAIR) ? (uint32_t)ncol : (uint32_t)min(B, max(16, (nlive + 15) & ~15));
+      // (PAIR: each CTA supplies half of these rows; its producer fetched them from the half's first row on)
+      const uint32_t n_mma = merged ? (uint32_t)ncol : (uint32_t)min(B, max(16, (nlive + 15) & ~15));
       uint32_t idesc_w[2];
 #pragma unroll
       for (int s = 0; s < 2; ++s) idesc_w[s] = (idesc[s] & ~(0x3Fu << 17)) | ((n_mma >> 3) << 17);
