@@ -215,7 +215,26 @@ __global__ void __launch_bounds__(kThreads, 1) moe_grouped_gemm_fp8_kernel(const
       PROF_DECL(t_sf);
       const long long t_begin = PROF_NOW();
       (void)t_begin;
+      // The MMAs cover only the live rows of the block (rounded up to 16): padding rows that end an expert's last
+      // block cost neither tensor time nor operand reads.  The row ids of the NEXT item are fetched while the
+      // current one is multiplied.
+      uint32_t nid[3];
+      auto fetch_ids = [&](int w, uint32_t (&r)[3]) {
+        const int r0 = (w / p.MT) * B;
+#pragma unroll
+        for (int q = 0; q < 3; ++q) r[q] = (w < total_work && q * 32 + lane < B) ? p.sorted_ids[r0 + q * 32 + lane] : 0xFFFFFFFFu;
+      };
+      fetch_ids((int)blockIdx.x, nid);
       for (int w = blockIdx.x; w < total_work && ok; w += gridDim.x) {
+        int nlive = 0;
+#pragma unroll
+        for (int q = 0; q < 3; ++q)
+          nlive += __popc(__ballot_sync(0xffffffffu, (int)(nid[q] >> 24) < p.topk && (int)(nid[q] & 0xFFFFFFu) < p.T));
+        fetch_ids(w + (int)gridDim.x, nid);
+        const uint32_t n_mma = (uint32_t)min(B, max(16, (nlive + 15) & ~15));
+        uint32_t idesc_w[4];
+#pragma unroll
+        for (int k = 0; k < 4; ++k) idesc_w[k] = (idesc[k] & ~(0x3Fu << 17)) | ((n_mma >> 3) << 17);
         for (int kb = 0; kb < p.KB; ++kb) {
           // every k-block gets its own accumulator buffer: the epilogue promotes it with the
           // block's fp32 weight scale while the next k-block is being multiplied
@@ -248,7 +267,7 @@ __global__ void __launch_bounds__(kThreads, 1) moe_grouped_gemm_fp8_kernel(const
   #pragma unroll
               for (int t = 0; t < kTerms; ++t)
                 if (t < nterms)
-                  umma_mxf8(d0, a_lo + 2 * k, b_lo + t * term_lo + 2 * k, idesc[k], sfa_t, sfb_t + 4 * t,
+                  umma_mxf8(d0, a_lo + 2 * k, b_lo + t * term_lo + 2 * k, idesc_w[k], sfa_t, sfb_t + 4 * t,
                             (k | t) != 0 || !first_kb);
             }
             tc_commit(smem_u32(&ctl->empty[stage]));
