@@ -113,6 +113,15 @@ def test_expert_parallel_matches_single_process_oracle(world, small_batch, chunk
         assert cos > 0.9999 and mx < 5e-3, (r, cos, mx)
 
 
+def test_one_expert_per_rank_on_eight_ranks():
+    """The Mixtral-shaped configuration at 8 GPUs leaves ONE expert per rank: every local id is 0 and most of a
+    token's ids belong to other ranks."""
+    res = _spawn(8)
+    for r in range(8):
+        cos, mx = res[r]
+        assert cos > 0.9999 and mx < 5e-3, (r, cos, mx)
+
+
 def test_rank_that_never_joins_is_detected_by_timeout():
     res = _spawn(2, fail_rank=1)
     assert res[1] == "skipped"

@@ -173,6 +173,20 @@ def test_expert_mask_drops_masked_experts():
     _assert_close(y, ref, "masked")
 
 
+@pytest.mark.parametrize("combine", ["gather", "fused"])
+def test_single_local_expert(combine):
+    """One expert of eight lives here (expert parallelism with one expert per GPU): every sorted block carries local
+    id 0 and most (token, expert) pairs are dropped by the mask."""
+    T, H, I, E, K = 200, 256, 128, 8, 2
+    x, tw, ids, w = _case(T, H, I, E, K, routing="zipf", seed=33)
+    for e in (0, 5):
+        keep = torch.zeros(E, dtype=torch.bool)
+        keep[e] = True
+        y = _run_layer(x, tw, ids, tuple(t[keep] for t in w), expert_mask=keep.to(torch.int32).to(DEV), combine=combine)
+        ref = orc.torch_moe_oracle_mxfp4(x, *w, tw * keep[ids.long()].float(), ids)
+        _assert_close(y, ref, f"only expert {e} local, {combine}")
+
+
 def test_deterministic_bitwise():
     T, H, I, E, K = 96, 256, 128, 8, 2
     x, tw, ids, w = _case(T, H, I, E, K, seed=5)
