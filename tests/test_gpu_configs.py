@@ -94,6 +94,32 @@ def test_gptoss_prefill_full_size(gptoss):
     _report(f"config2 gptoss prefill T={T} a4w4 vs bf16-activation oracle", y1, ref, act_terms=1)
 
 
+@pytest.mark.parametrize("T", [64, 8192])
+def test_gptoss_shape_with_unquantised_weights_full_size(T):
+    """The gpt-oss layer shape with bf16 weights (the reference wrapper's QuantType.No): decode and prefill token
+    counts through the kind::f16 kernels against the layer oracle on the same bf16 weights.  Eight distinct experts
+    are drawn and repeated with their rows rolled by the expert index, as the quantised benchmark weights are."""
+    c = synth.CONFIGS["gptoss_decode"]
+    distinct = 8
+    w1b, w2b = synth.make_weights_bf16(distinct, c.H, c.I, seed=0)
+
+    def ew(e):
+        return torch.roll(w1b[e % distinct], e // distinct, 0), torch.roll(w2b[e % distinct], e // distinct, 0)
+    w1 = torch.stack([torch.roll(w1b[e % distinct].to(DEV), e // distinct, 0) for e in range(c.E)])
+    w2 = torch.stack([torch.roll(w2b[e % distinct].to(DEV), e // distinct, 0) for e in range(c.E)])
+    x = synth.make_hidden(T, c.H, 0)
+    tw, ids = synth.make_routing(T, c.E, c.K, c.routing, 0)
+    ref = orc.torch_moe_oracle(x, None, None, tw, ids, expert_weights=ew)
+    for combine in ("gather", "fused"):
+        y = fused_moe(x.to(DEV), w1, w2, tw.to(DEV), ids.to(DEV), quant_type=QuantType.No, combine=combine)
+        torch.cuda.synchronize()
+        _check(_report(f"gpt-oss shape, bf16 weights, T={T} {combine}", y.cpu(), ref))
+    del w1, w2
+    from pyhip_b200 import release_prepared
+    release_prepared()
+    torch.cuda.empty_cache()
+
+
 def test_deepseek_v3_shaped_fp8_full_size():
     c = synth.CONFIGS["dsv3_ep"]
     fw = synth.FastWeights(c.E, c.H, c.I, seed=0, wq="fp8_128", distinct=4)
