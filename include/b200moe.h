@@ -246,6 +246,21 @@ typedef struct b200moe_io {
 int b200moe_forward_ex(const b200moe_shape* shape, const b200moe_workspace* ws, void* workspace,
                        const b200moe_io* io, void* stream);
 
+/* ONE token through the MXFP4 layer: replaces moe_gemm_batch1 (src/contrib/moe.py:41-188), the reference's batch-1
+ * fast path that takes its experts straight from topk_ids with no sort (src/contrib/moe.py:79-84).  Two launches
+ * (gate-up + activation; down + the weighted sum over the token's K experts in ascending expert order with the
+ * oracle's bf16 roundings, tests/contrib/moe/test_moe.py:107-117), no workspace, no activation quantiser: the
+ * products are formed from the bf16 input itself with fp32 block accumulation, and the result is bitwise
+ * reproducible.  shape.T must be 1, shape.K <= 8, weight_format MXFP4; act_terms / combine_mode / B are not used.
+ *   w1_scale / w2_scale : the CANONICAL E8M0 tensors [E, 2I, H/32] / [E, H, I/32] (not the prepared images)
+ *   expert_mask, num_local_tokens, bias1, bias2 : as in b200moe_forward_ex, or NULL
+ *   scratch : b200moe_batch1_scratch_bytes(shape) bytes of device memory, 16-byte aligned (h [K, I] + K ids) */
+int b200moe_batch1_scratch_bytes(const b200moe_shape* shape, int64_t* bytes);
+int b200moe_forward_batch1(const b200moe_shape* shape, const void* x_bf16, const int32_t* topk_ids,
+                           const float* topk_weight, const int32_t* expert_mask, const int32_t* num_local_tokens,
+                           const void* w1_q, const void* w1_scale, const void* w2_q, const void* w2_scale,
+                           const float* bias1, const float* bias2, void* scratch, void* y_bf16, void* stream);
+
 /* Whole layer WITHOUT a caller-provided workspace.  No counterpart in the reference (pyhip's
  * wrapper lets torch allocate its intermediates on every call).  It exists for hosts that cannot
  * allocate device memory when the layer runs -- e.g. a serving process that gave all free HBM to

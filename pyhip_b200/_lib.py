@@ -19,7 +19,7 @@ PKG_DIR = pathlib.Path(__file__).resolve().parent
 CSRC = PKG_DIR / "csrc"
 LIB_PATH = PKG_DIR / "libb200moe.so"
 SOURCES = ["api.cu", "moe_aux.cu", "moe_gemm_sm100.cu", "moe_gemm_fp8_sm100.cu", "moe_gemm_bf16_sm100.cu",
-           "forward_static.cu"]
+           "moe_batch1.cu", "forward_static.cu"]
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
               "-shared", "-Xcompiler", "-fPIC"]
 
@@ -60,7 +60,8 @@ EXPORTS = ["b200moe_version", "b200moe_last_error", "b200moe_workspace_layout",
            "b200moe_quant_rows", "b200moe_quant_rows_e4m3", "b200moe_gateup", "b200moe_down", "b200moe_combine",
            "b200moe_forward", "b200moe_forward_dyn", "b200moe_sort_align_dyn", "b200moe_sort_align_ws",
            "b200moe_sort_scratch_bytes", "b200moe_route_topk", "b200moe_forward_static", "b200moe_gather_sum", "b200moe_debug_probe",
-           "b200moe_forward_ex", "b200moe_static_status", "b200moe_ep_plan", "b200moe_quant_rows_fp8_1x128"]
+           "b200moe_forward_ex", "b200moe_static_status", "b200moe_ep_plan", "b200moe_quant_rows_fp8_1x128",
+           "b200moe_forward_batch1", "b200moe_batch1_scratch_bytes"]
 
 
 def build(force: bool = False, verbose: bool = False) -> pathlib.Path:
@@ -110,6 +111,8 @@ def lib() -> ctypes.CDLL:
     L.b200moe_sort_scratch_bytes.argtypes = [i32, ctypes.POINTER(i64)]
     L.b200moe_route_topk.argtypes = [vp, i32, i32, i32, i32, i32, vp, vp, vp]
     L.b200moe_forward_static.argtypes = [sp, vp, vp, vp, vp, vp, vp, vp, vp, vp, vp]
+    L.b200moe_forward_batch1.argtypes = [sp] + [vp] * 14
+    L.b200moe_batch1_scratch_bytes.argtypes = [sp, ctypes.POINTER(ctypes.c_int64)]
     L.b200moe_gather_sum.argtypes = [vp, vp, i32, i32, i32, vp, vp]
     L.b200moe_ep_plan.argtypes = [vp, i32, i32, i32, i32, vp, vp, vp, vp]
     L.b200moe_debug_probe.argtypes = [ctypes.c_int, vp, vp, vp]

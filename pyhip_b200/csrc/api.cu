@@ -411,6 +411,28 @@ int b200moe_forward_dyn(const b200moe_shape* s, const b200moe_workspace* ws, voi
   return forward_impl(s, ws, workspace, &io, stream);
 }
 
+int b200moe_batch1_scratch_bytes(const b200moe_shape* s, int64_t* bytes) {
+  if (int rc = check_shape(s)) return rc;
+  B200_CHECK_ARG(bytes != nullptr, "batch1_scratch_bytes: NULL pointer");
+  *bytes = batch1_scratch_bytes(s->K, s->I);
+  return 0;
+}
+
+int b200moe_forward_batch1(const b200moe_shape* s, const void* x_bf16, const int32_t* topk_ids, const float* topk_weight,
+                           const int32_t* expert_mask, const int32_t* num_local_tokens, const void* w1_q,
+                           const void* w1_scale, const void* w2_q, const void* w2_scale, const float* bias1,
+                           const float* bias2, void* scratch, void* y_bf16, void* stream) {
+  if (int rc = check_shape(s)) return rc;
+  B200_CHECK_ARG(s->T == 1, "forward_batch1: T=%d (this entry point takes exactly one token)", s->T);
+  B200_CHECK_ARG(s->weight_format == B200MOE_W_MXFP4, "forward_batch1: MXFP4 weights only");
+  B200_CHECK_ARG(x_bf16 && topk_ids && topk_weight && w1_q && w1_scale && w2_q && w2_scale && scratch && y_bf16,
+                 "forward_batch1: NULL pointer");
+  return launch_forward_batch1(x_bf16, topk_ids, topk_weight, expert_mask, num_local_tokens, w1_q, w1_scale, w2_q,
+                               w2_scale, bias1, bias2, scratch, y_bf16, s->H, s->I, s->K, s->E, s->E_route,
+                               s->activation, s->swiglu_limit > 0.f ? s->swiglu_limit : 7.0f, s->doweight_stage1,
+                               (cudaStream_t)stream);
+}
+
 int b200moe_route_topk(const float* logits, int32_t T, int32_t E, int32_t K, int32_t scoring, int32_t renormalize,
                        int32_t* topk_ids, float* topk_weight, void* stream) {
   B200_CHECK_ARG(T >= 0, "route_topk: T=%d", T);

@@ -168,6 +168,12 @@ inline cudaError_t launch_chained(void (*kernel)(KArgs...), dim3 grid, dim3 bloc
                                   Args&&... args) {
   return launch_chained_cluster(kernel, grid, block, smem, st, 1, static_cast<Args&&>(args)...);
 }
+// batch-1 path (moe_batch1.cu): one token, MXFP4 weights with their canonical E8M0 scales, no sort and no quantiser
+int64_t batch1_scratch_bytes(int K, int I);
+int launch_forward_batch1(const void* x, const int32_t* ids, const float* tw, const int32_t* mask, const int32_t* num_local,
+                          const void* w1, const void* s1, const void* w2, const void* s2, const float* bias1,
+                          const float* bias2, void* scratch, void* y, int H, int I, int K, int E, int E_route,
+                          int activation, float swiglu_limit, int stage1, cudaStream_t st);
 int run_debug_probe(int which, const void* in, void* out, cudaStream_t st);
 
 }  // namespace b200moe

@@ -115,6 +115,7 @@ class PreparedWeights:
             out.append(scale)
         self.w1_data, self.w2_data = w1, w2            # consumed in place
         self.w1_scale, self.w2_scale = out
+        self.w1_scale_raw, self.w2_scale_raw = s1.contiguous(), s2.contiguous()   # canonical layout: the batch-1 path reads it
         self.device = w1.device
 
 
@@ -345,15 +346,41 @@ def get_plan(T, K, E, E_route, H, I, B, activation, swiglu_limit, device, act_te
     return plan
 
 
+BATCH1_MAX_TOPK, BATCH1_MAX_DIM = 8, 8192
+
+
+def batch1_eligible(T: int, K: int, H: int, I: int, weight_format: int, act_terms: int) -> bool:
+    """Whether a call can take the two-launch batch-1 path (one token, MXFP4 weights, default activation format; no
+    sort, no quantiser: matrix-vector products from the bf16 input itself), the counterpart of the reference's
+    moe_gemm_batch1 (src/contrib/moe.py:41-188).  It is selected with ``method="batch1"`` only: on this GPU the
+    sorted tensor-core path is the faster one even for a single token (gpt-oss shape: 31.5 us against 38.6 us)."""
+    return (T == 1 and weight_format == _lib.W_MXFP4 and act_terms == 0 and K <= BATCH1_MAX_TOPK and
+            H <= BATCH1_MAX_DIM and I <= BATCH1_MAX_DIM)
+
+
 def moe_forward(plan: MoEPlan, pw: PreparedWeights, hidden_states, topk_weight, topk_ids, expert_mask=None,
-                out=None, num_local_tokens=None, bias1=None, bias2=None):
+                out=None, num_local_tokens=None, bias1=None, bias2=None, batch1=None):
     """One layer call through the C ABI (sort -> quantise -> gate-up -> down [-> combine]; decode-sized batches
-    fold the first two into one launch).  ``num_local_tokens``: optional int32 device tensor; tokens at and
-    beyond its value are padding (their output rows are zero)."""
+    fold the first two into one launch; ``batch1=True`` sends a single token down the batch-1 path instead).
+    ``num_local_tokens``: optional int32 device tensor; tokens at and beyond its value are padding (their output
+    rows are zero)."""
     T, H = hidden_states.shape
     if out is None:
         out = torch.empty((T, H), dtype=torch.bfloat16, device=hidden_states.device)
     if T == 0:
+        return out
+    s = plan.shape
+    if batch1:
+        if not batch1_eligible(T, s.K, s.H, s.I, s.weight_format, s.act_terms):
+            raise ValueError("the batch-1 path takes one token, MXFP4 weights, default act_terms and top-k <= 8")
+        need = ctypes.c_int64()
+        _lib.check(_lib.lib().b200moe_batch1_scratch_bytes(ctypes.byref(s), ctypes.byref(need)), "batch1_scratch_bytes")
+        if plan.ws.off_hsf - plan.ws.off_hq < need.value:
+            raise ValueError("workspace too small for the batch-1 scratch")
+        _lib.check(_lib.lib().b200moe_forward_batch1(
+            ctypes.byref(s), _ptr(hidden_states), _ptr(topk_ids), _ptr(topk_weight), _ptr(expert_mask),
+            _ptr(num_local_tokens), _ptr(pw.w1_data), _ptr(pw.w1_scale_raw), _ptr(pw.w2_data), _ptr(pw.w2_scale_raw),
+            _ptr(bias1), _ptr(bias2), ctypes.c_void_p(plan.base + plan.ws.off_hq), _ptr(out), _stream()), "forward_batch1")
         return out
     io = _lib.Io(x_bf16=hidden_states.data_ptr(), topk_ids=topk_ids.data_ptr(), topk_weight=topk_weight.data_ptr(),
                  expert_mask=None if expert_mask is None else expert_mask.data_ptr(),
@@ -367,10 +394,12 @@ def moe_forward(plan: MoEPlan, pw: PreparedWeights, hidden_states, topk_weight, 
     return out
 
 
-def launches_per_call(T: int, K: int, E_route: int, combine_mode: int) -> int:
+def launches_per_call(T: int, K: int, E_route: int, combine_mode: int, batch1: bool = False) -> int:
     """Kernel launches of one whole-layer call: sort + quantise (one launch up to 256 (token, expert) pairs, two
     below 8192 pairs, four from there on: the sort is then count / scan / scatter), gate-up, down, and the
-    gather-sum unless the combine is fused into the down epilogue."""
+    gather-sum unless the combine is fused into the down epilogue.  The batch-1 path is two launches."""
+    if batch1:
+        return 2
     pairs = T * K
     front = 1 if (pairs <= 256 and E_route <= 1024) else (4 if pairs >= 8192 else 2)
     return front + 2 + (0 if combine_mode == _lib.COMBINE_FUSED else 1)
@@ -416,6 +445,9 @@ def fused_moe(hidden_states, w1, w2, topk_weight, topk_ids, expert_mask=None,
         fp32 scales, src/contrib/fused_moe.py:375-381: half the operand bytes and MMA work, judged against the
         oracle that dequantises the same quantised activations).
       ``bias1`` [E, 2I] / ``bias2`` [E, H]: per-expert biases of the two projections (gpt-oss style).
+      ``method``: "batch1" takes the two-launch batch-1 path (one token, MXFP4 weights: no sort, no activation
+        quantiser, bitwise reproducible; slower than the default on this GPU); any other value, the reference's
+        "auto" / "jit" / "gluon" among them, takes the sorted grouped GEMMs.
       ``cta_pairs`` (MXFP4): "auto" runs the GEMMs on CTA pairs (tcgen05.mma.cta_group::2) in the compute-bound regime,
         "off" never, "on" wherever the tile allows it.
     """
@@ -475,7 +507,8 @@ def fused_moe(hidden_states, w1, w2, topk_weight, topk_ids, expert_mask=None,
     tw = topk_weight if topk_weight.dtype == torch.float32 else topk_weight.float()
     mask = None if expert_mask is None else expert_mask.to(torch.int32).contiguous()
     return moe_forward(plan, pw, hidden_states.contiguous(), tw.contiguous(), ids.contiguous(), mask,
-                       num_local_tokens=_num_local(num_local_tokens, hidden_states.device), bias1=b1, bias2=b2)
+                       num_local_tokens=_num_local(num_local_tokens, hidden_states.device), bias1=b1, bias2=b2,
+                       batch1=method == "batch1")
 
 
 def fused_topk(hidden_states, gating_output, topk: int, renormalize: bool = True, scoring: str = "softmax"):

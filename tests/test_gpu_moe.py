@@ -365,6 +365,50 @@ def test_small_batch_path_sorts_bit_exactly(T, E, K, mask):
     _assert_close(y.cpu(), orc.torch_moe_oracle_mxfp4(x, *w_full, tw_m, ids), "small path layer")
 
 
+@pytest.mark.parametrize("H,I,E,K", [(256, 128, 8, 2), (288, 160, 16, 4), (2880, 2880, 8, 4), (1024, 96, 4, 1), (96, 4096, 16, 8)])
+def test_batch1_path_matches_the_oracle(H, I, E, K):
+    """method="batch1": one token in two launches, no sort and no activation quantiser (the reference's
+    moe_gemm_batch1, src/contrib/moe.py:41-188).  Against the layer oracle with bf16 activations; bitwise
+    reproducible; the default (sorted tensor-core) path on the same input agrees to a bf16 step."""
+    from pyhip_b200.fused_moe import batch1_eligible
+    from pyhip_b200 import _lib
+    assert batch1_eligible(1, K, H, I, _lib.W_MXFP4, 0) and not batch1_eligible(2, K, H, I, _lib.W_MXFP4, 0)
+    assert not batch1_eligible(1, K, H, I, _lib.W_MXFP4, 1) and not batch1_eligible(1, K, H, I, _lib.W_FP8_128, 0)
+    x, tw, ids, w = _case(1, H, I, E, K, seed=H + K)
+    ref = orc.torch_moe_oracle_mxfp4(x, *w, tw, ids)
+    y = _run_layer(x, tw, ids, w, method="batch1")
+    _assert_close(y, ref, "batch-1")
+    assert torch.equal(y.view(torch.int16), _run_layer(x, tw, ids, w, method="batch1").view(torch.int16))
+    y_s = _run_layer(x, tw, ids, w)
+    _assert_close(y_s, ref, "sorted path, one token")
+    with pytest.raises(ValueError):
+        _run_layer(torch.cat([x, x]), torch.cat([tw, tw]), torch.cat([ids, ids]), w, method="batch1")
+    assert orc.max_abs(y, y_s) <= 2 ** -6 * max(1.0, float(ref.float().abs().max()))
+
+
+@pytest.mark.parametrize("activation", ["silu", "swiglu"])
+def test_batch1_mask_biases_stage1_weights_and_padding(activation):
+    H, I, E, K = 288, 160, 8, 3
+    x, tw, ids, w = _case(1, H, I, E, K, seed=77)
+    g = torch.Generator().manual_seed(5)
+    b1 = (torch.randn(E, 2 * I, generator=g) * 0.1).to(torch.bfloat16)
+    b2 = (torch.randn(E, H, generator=g) * 0.1).to(torch.bfloat16)
+    act = ActivationType.Silu if activation == "silu" else ActivationType.Swiglu
+    okw = dict(activation=activation, swiglu_limit=7.0)
+    y = _run_layer(x, tw, ids, w, activation=act, bias1=b1.to(DEV), bias2=b2.to(DEV), method="batch1")
+    _assert_close(y, orc.torch_moe_oracle_mxfp4(x, *w, tw, ids, bias1=b1, bias2=b2, **okw), "biases")
+    y = _run_layer(x, tw, ids, w, activation=act, doweight_stage1=True, method="batch1")
+    _assert_close(y, orc.torch_moe_oracle_mxfp4(x, *w, tw, ids, doweight_stage1=True, **okw), "stage-1 weights")
+    keep = torch.ones(E, dtype=torch.bool)
+    keep[int(ids[0, 0])] = False                       # the token's first expert lives on another rank
+    keep[(int(ids[0, 1]) + 1) % E] = keep[(int(ids[0, 1]) + 1) % E] and True
+    y = _run_layer(x, tw, ids, tuple(t[keep] for t in w), activation=act, expert_mask=keep.to(torch.int32).to(DEV),
+                   method="batch1")
+    _assert_close(y, orc.torch_moe_oracle_mxfp4(x, *w, tw * keep[ids.long()].float(), ids, **okw), "mask")
+    y = _run_layer(x, tw, ids, w, activation=act, num_local_tokens=0, method="batch1")
+    assert float(y.float().abs().max()) == 0.0
+
+
 def _expand(t, keep):
     """local expert tensors -> full-size tensor with the masked experts left at zero."""
     full = torch.zeros((keep.numel(),) + tuple(t.shape[1:]), dtype=t.dtype)
