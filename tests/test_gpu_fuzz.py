@@ -54,8 +54,10 @@ def _draw(seed, fp8, bf16=False):
     return c
 
 
-def _run_case(seed, fp8, bf16=False):
+def _run_case(seed, fp8, bf16=False, force_T1=False):
     c = _draw(seed, fp8, bf16)
+    if force_T1:
+        c["T"], c["terms"], c["live"] = 1, 0, False
     T, H, I, E, K = c["T"], c["H"], c["I"], c["E"], c["K"]
     what = f"seed {seed} {c}"
     x = synth.make_hidden(T, H, seed)
@@ -118,11 +120,23 @@ def _run_case(seed, fp8, bf16=False):
         oracle = orc.torch_moe_oracle_fp8 if fp8 else orc.torch_moe_oracle_mxfp4
         ref = oracle(x[:n], *w, tw_m[:n], ids[:n], activation=c["activation"], swiglu_limit=7.0, **okw)
     _close(y[:n], ref, what, a4w4=c.get("terms") == 1)
+    if T == 1 and not fp8 and not bf16 and c.get("terms") == 0 and K <= 8:
+        # the same call down the batch-1 path (no sort, no activation quantiser)
+        y1 = fused_moe(x.to(DEV), w_local[0], w_local[2], tw.to(DEV), ids.to(DEV), quant_type=qt, w1_scale=w_local[1],
+                       w2_scale=w_local[3], activation=act, combine=c["combine"], method="batch1",
+                       **{k: v for k, v in kw.items() if k != "block_size_M"})
+        torch.cuda.synchronize()
+        _close(y1.cpu()[:n], ref, what + " (batch-1 path)")
 
 
 @pytest.mark.parametrize("seed", range(28))
 def test_random_mxfp4_layers(seed):
     _run_case(seed, fp8=False)
+
+
+@pytest.mark.parametrize("seed", range(100, 112))
+def test_random_single_token_layers_on_both_paths(seed):
+    _run_case(seed, fp8=False, force_T1=True)
 
 
 @pytest.mark.parametrize("seed", range(16))
