@@ -74,6 +74,8 @@ def parse():
                     help="FP8 weights: two e4m3 terms with E8M0 scales (default) or the per-token 1x128 fp32-scale format")
     ap.add_argument("--weights", default="native", choices=["native", "bf16"],
                     help="bf16: the same shape with unquantised bf16 weights (QuantType.No; one GPU, implies --no-extras)")
+    ap.add_argument("--method", default="auto", choices=["auto", "batch1"],
+                    help="batch1: the sort-free one-token path (needs --tokens 1 and MXFP4 weights)")
     ap.add_argument("--cta-pairs", default="auto", choices=["auto", "off", "on"],
                     help="MXFP4 GEMMs on CTA pairs (tcgen05.mma.cta_group::2): auto = in the compute-bound regime")
     ap.add_argument("--no-extras", action="store_true", help="only the headline workload (no sweep / prefill / config3 / config4)")
@@ -369,7 +371,7 @@ class Case:
         return x, tw, ids
 
 
-def measure_layer(case, T, args, steps, warmup, combine, act_terms=0, local=0, total_ms=None, act_quant=0):
+def measure_layer(case, T, args, steps, warmup, combine, act_terms=0, local=0, total_ms=None, act_quant=0, batch1=False):
     """Whole-layer timing at T tokens: graph replay of the call's launches; batches whose expert set fits L2
     rotate over enough different routing sets that every step streams its weights from HBM."""
     import torch
@@ -390,7 +392,7 @@ def measure_layer(case, T, args, steps, warmup, combine, act_terms=0, local=0, t
 
     def one_round():
         for xs, tws, idss in sets:
-            moe_forward(plan, case.pw, xs, tws, idss, None, y)
+            moe_forward(plan, case.pw, xs, tws, idss, None, y, batch1=batch1)
 
     launch_mode = "direct launches"
     fn = one_round
@@ -418,7 +420,8 @@ def measure_layer(case, T, args, steps, warmup, combine, act_terms=0, local=0, t
             "repeats": r["repeats"], "steps_per_region": rounds * n_sets, "tokens_per_s": T / (ms * 1e-3),
             "experts_hit": hit, "block": B, "combine": combine,
             "act_terms": 0 if case.bf16 else (1 if act_quant else 2) if case.fp8 else (act_terms or 3),
-            "launch": launch_mode, "launches_per_step": launches_per_call(T, s.K, s.E, cm),
+            "launch": launch_mode, "launches_per_step": launches_per_call(T, s.K, s.E, cm, batch1),
+            "path": "batch-1 (no sort, CUDA cores)" if batch1 else "sorted grouped GEMMs (tensor cores)",
             "routing_sets_rotated": n_sets,
             "layer_gbs": layer_bytes / (ms * 1e-3) / 1e9,
             "frac_of_hbm_measured": layer_bytes / (ms * 1e-3) / 1e9 / peak,
@@ -496,7 +499,8 @@ def measure_e2e(case, T, args, steps, warmup, combine, act_terms=0, act_quant='t
         tg = twh.to(dev, non_blocking=True)
         ig = idsh.to(dev, non_blocking=True)
         out = fused_moe(xg, w[0], w[2], tg, ig, quant_type=case.qt, w1_scale=w[1], w2_scale=w[3], combine=combine,
-                        act_terms=act_terms, act_quant=act_quant if case.fp8 else "terms", cta_pairs=args.cta_pairs)
+                        act_terms=act_terms, act_quant=act_quant if case.fp8 else "terms", cta_pairs=args.cta_pairs,
+                        method=args.method)
         yh.copy_(out, non_blocking=True)
 
     r = time_repeated(step_e2e, steps, warmup, total_ms=min(args.repeat_ms, 500.0))
@@ -514,17 +518,28 @@ def run_single(args, dev, local):
     s = case.shape
     T = args.tokens or s.T
     aq = 1 if (args.act_quant == '1x128' and case.fp8) else 0
-    head = measure_layer(case, T, args, args.steps, args.warmup, args.combine, args.act_terms, local, act_quant=aq)
+    b1 = args.method == "batch1"
+    head = measure_layer(case, T, args, args.steps, args.warmup, args.combine, args.act_terms, local, act_quant=aq, batch1=b1)
     other = "gather" if args.combine == "fused" else "fused"
-    alt = measure_layer(case, T, args, args.steps, args.warmup, other, args.act_terms, local, total_ms=300.0, act_quant=aq)
+    alt = measure_layer(case, T, args, args.steps, args.warmup, other, args.act_terms, local, total_ms=300.0, act_quant=aq,
+                        batch1=b1)
     e2e = measure_e2e(case, T, args, args.steps, args.warmup, args.combine, args.act_terms, args.act_quant)
-    roofline = measure_gemms(case, T, args, args.steps, args.warmup, args.act_terms, act_quant=aq)
+    if b1:       # two matrix-vector launches: the whole call against the HBM rate
+        peak, peak_kind = measured_peaks()
+        roofline = {"bound": "hbm", "achieved": head["layer_gbs"], "peak": peak, "unit": "GB/s",
+                    "frac": head["layer_gbs"] / peak, "peak_kind": peak_kind, "traffic": None,
+                    "kernel": "batch1_gateup_kernel + batch1_down_kernel (whole call)",
+                    "us_per_launch": head["ms_per_step"] * 1e3 / 2}
+    else:
+        roofline = measure_gemms(case, T, args, args.steps, args.warmup, args.act_terms, act_quant=aq)
     extras = {}
     default_run = not args.no_extras and args.workload == "gptoss_decode" and not args.tokens and not args.experts
     if default_run:
         st = max(20, min(args.steps, 200))
         extras["sweep"] = [measure_layer(case, Ts, args, st, 3, args.combine, args.act_terms, local, total_ms=300.0)
                            for Ts in (1, 8, 32, 256)]
+        # the reference-style sort-free path for one token beside the sweep's T = 1 entry
+        extras["batch1_T1"] = measure_layer(case, 1, args, st, 3, args.combine, 0, local, total_ms=200.0, batch1=True)
         Tp = synth.CONFIGS["gptoss_prefill"].T
         pre = {}
         for nt, name in ((0, "three_term"), (1, "a4w4")):
