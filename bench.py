@@ -1,6 +1,7 @@
 """Benchmark of the fused-MoE hot path.
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference] [--workload W] [--tokens T] [--no-extras]
+                    [--weights bf16] [--method batch1]
 
 One "step" is one MoE layer call on one batch of synthetic tokens.  At N=1 the default workload is
 the gpt-oss-120b-shaped MXFP4 layer (H=I=2880, E=128, top-4) at T=64 decode tokens -- the
@@ -24,7 +25,8 @@ once per step).
 
 Unless `--no-extras` is given the default run also measures, each with its own clock record:
 `sweep` (decode T in {1, 8, 32, 256}; batches whose expert set fits L2 rotate over several routing
-sets so that weights are streamed from HBM every step), `prefill` (gpt-oss shape, T=8192: the default
+sets so that weights are streamed from HBM every step), `batch1_T1` (one token down the sort-free
+matrix-vector path, `--method batch1`, beside the sweep's T=1 entry), `prefill` (gpt-oss shape, T=8192: the default
 three-term activation format and the plain MXFP4 a4w4 format, scored against the dense FP4 rate --
 nominal 9 PFLOP/s and the rate the library's MMA probe measures in the same run), `config3`
 (DeepSeek-V3-shaped FP8 layer, T=4096 per GPU, expert-parallel at N>1) and `config4` (Mixtral-shaped
