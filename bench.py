@@ -464,7 +464,9 @@ def measure_gemms(case, T, args, steps, warmup, act_terms=0, act_quant=0):
     common = {"kernel": ("moe_grouped_gemm_bf16_kernel<gate-up>" if case.bf16 else
                          "moe_grouped_gemm_fp8_kernel<gate-up>" if case.fp8 else "moe_grouped_gemm_kernel<gate-up>"),
               "us_per_launch": per_launch_s * 1e6, "us_per_launch_min": gu["min"] * 1e3,
-              "down_us_per_launch": dn["ms"] * 1e3, "traffic": profiled_traffic(s, T) if not (act_terms == 1 or act_quant) else None}
+              "down_us_per_launch": dn["ms"] * 1e3, "traffic": profiled_traffic(s, T) if not (act_terms == 1 or act_quant) else None,
+              "traffic_source": "dram__bytes_read.sum + dram__bytes_write.sum of the ncu capture summarised under profiles/ "
+                                "(same kernel and shape; not measured in this run)"}
     # weight-streaming regime (few rows per expert): HBM roofline; from 64 rows per expert on the launch is scored
     # against the dense tensor rate of its format, as the configurations state (the gpt-oss prefill shape sits at
     # the ridge: at the nominal rates its tensor time is 0.7 of its HBM time)
